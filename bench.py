@@ -1,0 +1,340 @@
+#!/usr/bin/env python3
+"""Benchmark of the quantised-MoE expert path on B200 (one JSON line on stdout).
+
+Headline workload (N=1): BASELINE config 1 -- one sparse-MoE block, decode, 1 token:
+RMSNorm -> router (512 x 2048 fp32) -> softmax top-10 + renorm -> 10 routed + 1 shared
+IQ3_XXS expert (gate/up 512x2048, down 2048x512) -> SwiGLU -> weighted sum.  A "step"
+is one token through one block; the block rotates over LAYERS independent weight
+copies (> L2) and over a pool of input vectors, so every step streams its weights
+from HBM.
+
+  value     steps/s with inputs and outputs resident in HBM (dnb_moe_block_dev)
+  e2e       the same through dnb_moe_block with host buffers (H2D + D2H inside)
+  roofline  the dominant kernel's algorithmic bytes / its mean launch time, both
+            measured live with events around every launch (dnb_profile_*)
+  cpu_baseline  the multi-threaded CPU port of the reference path on this box's cores
+
+`--impl reference` times that CPU path alone (rank 0 only under torchrun).
+With --gpus N > 1 every rank runs the same block on its own GPU and its own tokens
+(weak scaling, no collective on the data path); value is the sum over ranks of
+steps / max-over-ranks time.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SEED = 0xD3770B200
+E, FF, NE, K = 2048, 512, 512, 10
+IQ3_XXS, Q4_K = 18, 12
+LAYERS = 16          # rotating weight copies: 16 x 17.4 MB touched per cycle > 126 MB L2
+POOL = 64            # distinct input tokens
+ROW_BYTES = {IQ3_XXS: {2048: 784, 512: 196}, Q4_K: {2048: 1152, 512: 288}}
+
+
+def expert_bytes(ty):
+    return FF * ROW_BYTES[ty][E], E * ROW_BYTES[ty][FF]
+
+
+class Clocks:
+    """Samples nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu):
+        self.gpu, self.rows, self.p = gpu, [], None
+
+    def start(self):
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.Q,
+                                       "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                      stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.p = None
+
+    def _read(self):
+        for line in self.p.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.p:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.p.terminate()
+        self.t.join(timeout=2)
+        sm = [float(r[1]) for r in self.rows if len(r) >= 9 and r[1].replace(".", "").isdigit()]
+        mx = [float(r[2]) for r in self.rows if len(r) >= 9 and r[2].replace(".", "").isdigit()]
+        reasons = set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) >= 9:
+                for n, v in zip(names, r[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), float(d.get("bf16_tflops", 1677.1)), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def build_model(ctx, cu, ty, layers, bias):
+    """Expert tables filled on the device; routers (small) from the host generator."""
+    import oracle  # only its seeded host generator is used here (inputs, not results)
+
+    assert ctx.moe_config(layers, E, FF, NE, K)
+    for l in range(layers):
+        assert ctx.synth_experts(l, cu.GATE, ty, E, FF, NE, SEED)
+        assert ctx.synth_experts(l, cu.UP, ty, E, FF, NE, SEED)
+        assert ctx.synth_experts(l, cu.DOWN, ty, FF, E, NE, SEED)
+        assert ctx.synth_experts(l, cu.SHARED_GATE, ty, E, FF, 1, SEED)
+        assert ctx.synth_experts(l, cu.SHARED_UP, ty, E, FF, 1, SEED)
+        assert ctx.synth_experts(l, cu.SHARED_DOWN, ty, FF, E, 1, SEED)
+        rw = oracle.synth_normal(SEED, l * 16 + 6, 0.02, NE * E)
+        rb = oracle.synth_zipf_bias(SEED, l * 16 + 7, 1.1, NE) if bias else None
+        ctx.register_router(l, rw, rb, np.ones(E, np.float32), None)
+    ctx.sync()
+
+
+def run_ours(args, rank, world, local_rank):
+    import oracle
+    from denno_beta_b200 import cuda as cu
+
+    ctx = cu.CudaCtx(local_rank)
+    build_model(ctx, cu, IQ3_XXS, LAYERS, False)
+    pool = oracle.synth_normal(SEED, 7000 + rank, 1.0, POOL * E).reshape(POOL, E)
+    d_pool = ctx.dev_alloc(pool.nbytes)
+    d_out = ctx.dev_alloc(E * 4)
+    ctx.upload(d_pool, pool)
+
+    def dev_step(s):
+        assert ctx.moe_block_dev(s % LAYERS, d_pool + (s % POOL) * E * 4, 1, d_out)
+
+    out_host = np.empty((1, E), np.float32)
+
+    def host_step(s):
+        assert ctx.moe_block_into(s % LAYERS, pool[s % POOL:s % POOL + 1], out_host)
+
+    def barrier():
+        ctx.sync()
+        if world > 1:
+            import torch.distributed as dist
+
+            dist.barrier()
+
+    K_, W_ = args.steps, max(args.warmup, 3)
+    for s in range(W_):
+        dev_step(s)
+    barrier()
+    clocks = Clocks(local_rank)
+    clocks.start()
+    l0 = ctx.launch_count()
+    ctx.timer_start()
+    for s in range(K_):
+        dev_step(W_ + s)
+    ms_dev = ctx.timer_stop()
+    launches = ctx.launch_count() - l0
+    barrier()
+    # end to end through the host-buffer entry point
+    for s in range(W_):
+        host_step(s)
+    barrier()
+    t0 = time.perf_counter()
+    for s in range(K_):
+        host_step(W_ + s)
+    ctx.sync()
+    ms_e2e = (time.perf_counter() - t0) * 1e3
+    clk = clocks.stop()
+    barrier()
+    # per-kernel pass (events around every launch)
+    ctx.profile(True)
+    for s in range(K_):
+        dev_step(W_ + s)
+    prof = ctx.profile_read()
+    ctx.profile(False)
+
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+
+        t = torch.tensor([ms_dev, ms_e2e], dtype=torch.float64, device="cuda:%d" % local_rank)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_dev, ms_e2e = float(t[0]), float(t[1])
+    if rank != 0:
+        ctx.close()
+        return None
+
+    hbm_peak, _, peak_kind = peaks()
+    g_b, d_b = expert_bytes(IQ3_XXS)
+    alg = {  # algorithmic bytes per launch: weight bytes + activations in/out
+        "seg_gate_up_m1": K * 2 * g_b + E * 4 + K * FF * 4,
+        "seg_matmul_m1": K * d_b + K * FF * 4 + K * E * 4,
+        "seg_gate_up_m1_shared": 2 * g_b + E * 4 + FF * 4,
+        "seg_matmul_m1_shared": d_b + FF * 4 + E * 4,
+        "router_logits": NE * E * 4 + E * 4 + NE * 4,
+    }
+    top = max((k for k in prof if k in alg), key=lambda k: prof[k]["ms"])
+    per_launch_s = prof[top]["ms"] / prof[top]["launches"] * 1e-3
+    achieved = alg[top] / per_launch_s / 1e9
+    block_bytes = NE * E * 4 + (K + 1) * (2 * g_b + d_b)
+    res = {
+        "metric": "moe_decode_tok_s", "value": world * K_ / (ms_dev * 1e-3), "unit": "token*layer/s (1 MoE block per step)",
+        "n_gpus": world, "steps": K_, "warmup": W_, "ms_per_step": ms_dev / K_, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "config1: 1 MoE block decode, 1 token, e2048 ff512 512 experts top-10 + 1 shared, IQ3_XXS",
+                   "l2": "inputs larger than L2: %d rotating layer copies (%.0f MB of weights per cycle) and %d tokens"
+                         % (LAYERS, LAYERS * block_bytes / 1e6, POOL),
+                   "parallelism": "replicas x%d" % world if world > 1 else "1 GPU"},
+        "e2e": {"value": world * K_ / (ms_e2e * 1e-3), "unit": "token*layer/s", "h2d_bytes_per_step": E * 4,
+                "d2h_bytes_per_step": E * 4},
+        "gpu_launches": int(launches),
+        "clocks": clk,
+        "roofline": {"bound": "hbm", "kernel": top, "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
+                     "frac": achieved / hbm_peak, "peak_kind": peak_kind, "traffic": None,
+                     "bytes_per_launch": alg[top], "us_per_launch": per_launch_s * 1e6},
+        "block_hbm_gbs": block_bytes / (ms_dev / K_ * 1e-3) / 1e9,
+        "kernels_ms": {k: round(v["ms"], 4) for k, v in prof.items()},
+    }
+    if world == 1 and not args.no_extras:
+        res["extras"] = extras(ctx, cu, oracle)
+    if world == 1 and not args.no_cpu:
+        res["cpu_baseline"] = cpu_baseline(oracle, budget_s=10.0)
+    ctx.close()
+    return res
+
+
+def extras(ctx, cu, oracle):
+    """Config 0 (single Q4_K GEMV 4096x4096, HBM GB/s) on rotating weight copies."""
+    out = {}
+    k = n = 4096
+    rb = 16 * 144
+    copies = 32  # 32 x 9.4 MB = 302 MB > L2
+    w = oracle.synth_blocks(Q4_K, SEED, 9000, n * 16)
+    dw = ctx.dev_alloc(copies * n * rb)
+    for i in range(copies):
+        ctx.upload(dw + i * n * rb, w)
+    x = oracle.synth_normal(SEED, 9001, 1.0, k)
+    dx = ctx.dev_alloc(k * 4)
+    do = ctx.dev_alloc(n * 4)
+    ctx.upload(dx, x)
+    for i in range(8):
+        ctx.gemv_dev(Q4_K, dw + (i % copies) * n * rb, k, n, dx, do, 1)
+    ctx.sync()
+    reps = 256
+    ctx.timer_start()
+    for i in range(reps):
+        ctx.gemv_dev(Q4_K, dw + (i % copies) * n * rb, k, n, dx, do, 1)
+    ms = ctx.timer_stop()
+    alg = n * rb + k * 4 + n * 4
+    out["config0_q4k_gemv_4096"] = {"us_per_gemv": ms / reps * 1e3, "hbm_gbs": alg / (ms / reps * 1e-3) / 1e9,
+                                    "bytes": alg, "launches": reps, "rotating_copies": copies}
+    for p in (dw, dx, do):
+        ctx.dev_free(p)
+    return out
+
+
+def cpu_layer(oracle, ty=IQ3_XXS):
+    nb = lambda rows, cols: rows * cols // 256
+    gate = oracle.synth_blocks(ty, SEED, 0, NE * nb(FF, E))
+    up = oracle.synth_blocks(ty, SEED, 1, NE * nb(FF, E))
+    down = oracle.synth_blocks(ty, SEED, 2, NE * nb(E, FF))
+    sh = (oracle.synth_blocks(ty, SEED, 3, nb(FF, E)), oracle.synth_blocks(ty, SEED, 4, nb(FF, E)),
+          oracle.synth_blocks(ty, SEED, 5, nb(E, FF)))
+    rw = oracle.synth_normal(SEED, 6, 0.02, NE * E).reshape(NE, E)
+    return oracle.Layer(E, FF, NE, K, ty, ty, ty, gate, up, down, rw, norm_w=np.ones(E, np.float32), shared=sh)
+
+
+def cpu_baseline(oracle, budget_s):
+    """The reference path's CPU form (row/expert-parallel lane-split kernels) on this
+    box's cores: tokens of config 1 through one block until `budget_s` has passed."""
+    L = cpu_layer(oracle)
+    pool = oracle.synth_normal(SEED, 7000, 1.0, POOL * E).reshape(POOL, E)
+    oracle.moe_block_mt(L, pool[0])
+    n, t0 = 0, time.perf_counter()
+    while time.perf_counter() - t0 < budget_s:
+        oracle.moe_block_mt(L, pool[n % POOL])
+        n += 1
+    dt = time.perf_counter() - t0
+    return {"value": n / dt, "unit": "token*layer/s", "cores": os.cpu_count(), "kind": "port",
+            "sample": "%d tokens of config 1 through one block in %.1f s (one layer copy, weights in page cache)" % (n, dt)}
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return None
+    import oracle
+
+    L = cpu_layer(oracle)
+    pool = oracle.synth_normal(SEED, 7000, 1.0, POOL * E).reshape(POOL, E)
+    K_, W_ = args.steps, max(args.warmup, 1)
+    K_ = min(K_, 2000)
+    for s in range(W_):
+        oracle.moe_block_mt(L, pool[s % POOL])
+    t0 = time.perf_counter()
+    for s in range(K_):
+        oracle.moe_block_mt(L, pool[(W_ + s) % POOL])
+    dt = time.perf_counter() - t0
+    v = K_ / dt
+    return {
+        "impl": "reference", "metric": "moe_decode_tok_s", "value": v, "unit": "token*layer/s (1 MoE block per step)",
+        "n_gpus": args.gpus, "steps": K_, "warmup": W_, "ms_per_step": dt / K_ * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "config1: 1 MoE block decode, 1 token, e2048 ff512 512 experts top-10 + 1 shared, IQ3_XXS",
+                   "note": "CPU port of the reference's path (the Rust reference cannot be built here: no cargo)"},
+        "cpu_baseline": {"value": v, "unit": "token*layer/s", "cores": os.cpu_count(), "kind": "port",
+                         "sample": "%d tokens, one layer copy" % K_},
+        "e2e": {"value": v, "unit": "token*layer/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=50)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-extras", action="store_true", help="skip the config-0 GEMV line")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        res = run_reference(args, rank)
+    else:
+        if world > 1:
+            import torch
+            import torch.distributed as dist
+
+            torch.cuda.set_device(local_rank)
+            dist.init_process_group("nccl", device_id=torch.device("cuda:%d" % local_rank))
+        res = run_ours(args, rank, world, local_rank)
+        if world > 1:
+            import torch.distributed as dist
+
+            dist.barrier()
+            dist.destroy_process_group()
+    if res is not None:
+        print(json.dumps(res))
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,726 @@
+// extern "C" entry points of libdnb200: context, resident tables and the
+// orchestration of one MoE block (see include/dnb200.h for the contract).
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "dnb_common.cuh"
+
+namespace dnb {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+
+template <typename T>
+static int dev_alloc(T** p, size_t n) {
+    *p = nullptr;
+    if (n == 0) return DNB_OK;
+    DNB_CUDA(cudaMalloc((void**)p, n * sizeof(T)));
+    return DNB_OK;
+}
+
+static void free_ws(Workspace& w) {
+    void* dev[] = {w.xn, w.logits, w.wts, w.act, w.hrow, w.sact, w.sh, w.hin, w.out, w.shcoef, w.sels, w.row_token,
+                   w.pos, w.nseg, w.counts, w.seg_gu, w.seg_dn, w.seg_sh_gu, w.seg_sh_dn};
+    for (void* p : dev)
+        if (p) cudaFree(p);
+    if (w.pinned_in) cudaFreeHost(w.pinned_in);
+    if (w.pinned_out) cudaFreeHost(w.pinned_out);
+    if (w.pinned_sels) cudaFreeHost(w.pinned_sels);
+    if (w.pinned_wts) cudaFreeHost(w.pinned_wts);
+    w = Workspace();
+}
+
+// Device buffers for up to nt tokens (grow-only, like the reference's scratch,
+// cuda.rs:7454-7480).
+static int ensure_ws(dnb_ctx* c, int nt) {
+    Workspace& w = c->ws;
+    if (nt <= w.nt_cap) return DNB_OK;
+    const Model& M = c->model;
+    int cap = w.nt_cap ? w.nt_cap : 1;
+    while (cap < nt) cap *= 2;
+    DNB_CUDA(cudaDeviceSynchronize());
+    free_ws(w);
+    const size_t rows = (size_t)cap * M.k;
+    const int sff = M.sff > 0 ? M.sff : M.ff;
+    int rc = DNB_OK;
+    if ((rc = dev_alloc(&w.xn, (size_t)cap * M.e))) return rc;
+    if ((rc = dev_alloc(&w.hin, (size_t)cap * M.e))) return rc;
+    if ((rc = dev_alloc(&w.out, (size_t)cap * M.e))) return rc;
+    if ((rc = dev_alloc(&w.logits, (size_t)cap * M.ne))) return rc;
+    if ((rc = dev_alloc(&w.wts, rows))) return rc;
+    if ((rc = dev_alloc(&w.sels, rows))) return rc;
+    if ((rc = dev_alloc(&w.act, rows * M.ff))) return rc;
+    if ((rc = dev_alloc(&w.hrow, rows * M.e))) return rc;
+    if ((rc = dev_alloc(&w.sact, (size_t)cap * sff))) return rc;
+    if ((rc = dev_alloc(&w.sh, (size_t)cap * M.e))) return rc;
+    if ((rc = dev_alloc(&w.shcoef, (size_t)cap))) return rc;
+    if ((rc = dev_alloc(&w.row_token, rows))) return rc;
+    if ((rc = dev_alloc(&w.pos, rows))) return rc;
+    if ((rc = dev_alloc(&w.nseg, 1))) return rc;
+    if ((rc = dev_alloc(&w.counts, (size_t)M.ne))) return rc;
+    if ((rc = dev_alloc(&w.seg_gu, (size_t)M.ne))) return rc;
+    if ((rc = dev_alloc(&w.seg_dn, (size_t)M.ne))) return rc;
+    if ((rc = dev_alloc(&w.seg_sh_gu, 1))) return rc;
+    if ((rc = dev_alloc(&w.seg_sh_dn, 1))) return rc;
+    w.pinned_cap = (size_t)cap * M.e * sizeof(float);
+    DNB_CUDA(cudaMallocHost((void**)&w.pinned_in, w.pinned_cap));
+    DNB_CUDA(cudaMallocHost((void**)&w.pinned_out, w.pinned_cap));
+    DNB_CUDA(cudaMallocHost((void**)&w.pinned_sels, rows * sizeof(int32_t)));
+    DNB_CUDA(cudaMallocHost((void**)&w.pinned_wts, rows * sizeof(float)));
+    w.nt_cap = cap;
+    return DNB_OK;
+}
+
+static int grow(Scratch& s, size_t bytes) {
+    if (bytes <= s.cap) return DNB_OK;
+    if (s.p) cudaFree(s.p);
+    s.p = nullptr;
+    s.cap = 0;
+    DNB_CUDA(cudaMalloc(&s.p, bytes));
+    s.cap = bytes;
+    return DNB_OK;
+}
+
+static bool layer_ready(const dnb_ctx* c, int layer, bool need_router) {
+    const Model& M = c->model;
+    if (layer < 0 || layer >= M.n_layer) return false;
+    const Layer& L = M.layers[layer];
+    if (!L.m[0].dev || !L.m[1].dev || !L.m[2].dev) return false;
+    if (need_router && !L.router_w) return false;
+    return true;
+}
+
+// The routed + shared expert half of a block on device buffers.  x: expert input
+// [nt][e]; sels/wts on the device.  Writes out[nt][e].  The shared expert's
+// segment descriptors must already have been published by launch_prep.
+static int experts_dev(dnb_ctx* c, int layer, const float* x, int nt, const int32_t* sels, const float* wts,
+                       float* out) {
+    const Model& M = c->model;
+    const Layer& L = M.layers[layer];
+    Workspace& w = c->ws;
+    cudaStream_t st = c->stream;
+    int rc;
+    const bool shared = L.has_shared();
+    if (shared) {
+        // fork: the shared expert does not depend on the routing
+        DNB_CUDA(cudaEventRecord(c->ev_fork, st));
+        DNB_CUDA(cudaStreamWaitEvent(c->side, c->ev_fork, 0));
+        const int sff = L.m[3].n_out;
+        if ((rc = launch_seg_matmul(c, c->side, L.m[3].type, true, w.seg_sh_gu, nullptr, 1, M.e, sff, x, M.e, nullptr,
+                                    w.sact, nt)))
+            return rc;
+        if ((rc = launch_seg_matmul(c, c->side, L.m[5].type, false, w.seg_sh_dn, nullptr, 1, sff, M.e, w.sact, sff,
+                                    nullptr, w.sh, nt)))
+            return rc;
+        if (L.shared_gate_row)
+            if ((rc = launch_shared_coef(c, c->side, x, L.shared_gate_row, nt, M.e, w.shcoef))) return rc;
+        DNB_CUDA(cudaEventRecord(c->ev_join, c->side));
+    }
+    if ((rc = launch_route_tables(c, st, sels, nt, M.k, M.ne, L, w))) return rc;
+    const int nseg_max = nt * M.k < M.ne ? nt * M.k : M.ne;
+    if ((rc = launch_seg_matmul(c, st, L.m[0].type, true, w.seg_gu, w.nseg, nseg_max, M.e, M.ff, x, M.e, w.row_token,
+                                w.act, nt)))
+        return rc;
+    if ((rc = launch_seg_matmul(c, st, L.m[2].type, false, w.seg_dn, w.nseg, nseg_max, M.ff, M.e, w.act, M.ff, nullptr,
+                                w.hrow, nt)))
+        return rc;
+    if (shared) DNB_CUDA(cudaStreamWaitEvent(st, c->ev_join, 0));
+    return launch_combine(c, st, w.hrow, w.pos, wts, nt, M.k, M.e, shared ? w.sh : nullptr,
+                          (shared && L.shared_gate_row) ? w.shcoef : nullptr, out);
+}
+
+static int block_dev(dnb_ctx* c, int layer, const float* h, int nt, float* out) {
+    const Model& M = c->model;
+    const Layer& L = M.layers[layer];
+    Workspace& w = c->ws;
+    cudaStream_t st = c->stream;
+    int rc;
+    const bool shared = L.has_shared();
+    if (L.norm_w || shared) {
+        if ((rc = launch_prep(c, st, h, L.norm_w, M.eps, nt, M.e, w.xn, shared ? w.seg_sh_gu : nullptr,
+                              shared ? w.seg_sh_dn : nullptr, L.m[3].dev, L.m[4].dev, L.m[5].dev)))
+            return rc;
+    }
+    const float* x = L.norm_w ? w.xn : h;
+    if ((rc = launch_router_logits(c, st, x, nt, M.e, L.router_w, L.router_bias, M.ne, w.logits))) return rc;
+    if ((rc = launch_topk(c, st, w.logits, nt, M.ne, M.k, M.norm_topk, w.sels, w.wts, nullptr))) return rc;
+    return experts_dev(c, layer, x, nt, w.sels, w.wts, out);
+}
+
+}  // namespace dnb
+
+using namespace dnb;
+
+extern "C" {
+
+const char* dnb_last_error(void) { return g_err; }
+
+int dnb_init(int device, dnb_ctx** out) {
+    if (!out) return DNB_ERR_ARG;
+    *out = nullptr;
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess || n == 0) {
+        set_error("no CUDA device (%s); this library has no CPU path", e == cudaSuccess ? "count is 0" : cudaGetErrorString(e));
+        return DNB_ERR_NO_DEVICE;
+    }
+    if (device < 0 || device >= n) {
+        set_error("device %d out of range (0..%d)", device, n - 1);
+        return DNB_ERR_ARG;
+    }
+    DNB_CUDA(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    DNB_CUDA(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10) {
+        set_error("device %d is sm_%d%d; the kernels are built for sm_100a only", device, prop.major, prop.minor);
+        return DNB_ERR_NO_DEVICE;
+    }
+    dnb_ctx* c = new dnb_ctx();
+    c->device = device;
+    c->sm_count = prop.multiProcessorCount;
+    DNB_CUDA(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
+    DNB_CUDA(cudaStreamCreateWithFlags(&c->side, cudaStreamNonBlocking));
+    DNB_CUDA(cudaEventCreateWithFlags(&c->ev_fork, cudaEventDisableTiming));
+    DNB_CUDA(cudaEventCreateWithFlags(&c->ev_join, cudaEventDisableTiming));
+    DNB_CUDA(cudaEventCreate(&c->ev_t0));
+    DNB_CUDA(cudaEventCreate(&c->ev_t1));
+    DNB_CUDA(cudaMalloc((void**)&c->status, sizeof(int)));
+    DNB_CUDA(cudaMemset(c->status, 0, sizeof(int)));
+    *out = c;
+    return DNB_OK;
+}
+
+static void free_layer(Layer& L) {
+    for (auto& t : L.m)
+        if (t.dev && t.owned) cudaFree(t.dev);
+    if (L.router_w) cudaFree(L.router_w);
+    if (L.router_bias) cudaFree(L.router_bias);
+    if (L.norm_w) cudaFree(L.norm_w);
+    if (L.shared_gate_row) cudaFree(L.shared_gate_row);
+    L = Layer();
+}
+
+void dnb_shutdown(dnb_ctx* c) {
+    if (!c) return;
+    cudaSetDevice(c->device);
+    cudaDeviceSynchronize();
+    for (auto& kv : c->matrices) cudaFree(kv.second.dev);
+    for (auto& L : c->model.layers) free_layer(L);
+    free_ws(c->ws);
+    if (c->gemv_x.p) cudaFree(c->gemv_x.p);
+    if (c->gemv_out.p) cudaFree(c->gemv_out.p);
+    if (c->status) cudaFree(c->status);
+    if (c->own_stream && c->stream) cudaStreamDestroy(c->stream);
+    if (!c->own_stream && c->saved_stream) cudaStreamDestroy(c->saved_stream);
+    if (c->flush.p) cudaFree(c->flush.p);
+    if (c->side) cudaStreamDestroy(c->side);
+    cudaEventDestroy(c->ev_fork);
+    cudaEventDestroy(c->ev_join);
+    cudaEventDestroy(c->ev_t0);
+    cudaEventDestroy(c->ev_t1);
+    for (auto& r : c->prof.recs) { cudaEventDestroy(r.a); cudaEventDestroy(r.b); }
+    for (auto& e : c->prof.pool) cudaEventDestroy(e);
+    delete c;
+}
+
+int dnb_set_stream(dnb_ctx* c, void* stream) {
+    if (!c) return DNB_ERR_ARG;
+    DNB_CUDA(cudaSetDevice(c->device));
+    DNB_CUDA(cudaStreamSynchronize(c->stream));
+    if (stream) {
+        if (c->own_stream) c->saved_stream = c->stream;
+        c->stream = (cudaStream_t)stream;
+        c->own_stream = false;
+    } else if (!c->own_stream) {
+        c->stream = c->saved_stream;
+        c->own_stream = true;
+    }
+    return DNB_OK;
+}
+
+int dnb_sync(dnb_ctx* c) {
+    if (!c) return DNB_ERR_ARG;
+    DNB_CUDA(cudaStreamSynchronize(c->stream));
+    DNB_CUDA(cudaStreamSynchronize(c->side));
+    return DNB_OK;
+}
+
+uint64_t dnb_launch_count(dnb_ctx* c) { return c ? c->launches : 0; }
+
+int dnb_timer_start(dnb_ctx* c) {
+    if (!c) return DNB_ERR_ARG;
+    DNB_CUDA(cudaEventRecord(c->ev_t0, c->stream));
+    return DNB_OK;
+}
+
+int dnb_timer_stop(dnb_ctx* c, float* ms) {
+    if (!c || !ms) return DNB_ERR_ARG;
+    DNB_CUDA(cudaEventRecord(c->ev_t1, c->stream));
+    DNB_CUDA(cudaEventSynchronize(c->ev_t1));
+    DNB_CUDA(cudaEventElapsedTime(ms, c->ev_t0, c->ev_t1));
+    return DNB_OK;
+}
+
+int dnb_dev_alloc(dnb_ctx* c, size_t bytes, void** dev) {
+    if (!c || !dev) return DNB_ERR_ARG;
+    DNB_CUDA(cudaSetDevice(c->device));
+    DNB_CUDA(cudaMalloc(dev, bytes));
+    return DNB_OK;
+}
+
+int dnb_dev_free(dnb_ctx* c, void* dev) {
+    if (!c) return DNB_ERR_ARG;
+    DNB_CUDA(cudaFree(dev));
+    return DNB_OK;
+}
+
+int dnb_dev_upload(dnb_ctx* c, void* dev, const void* host, size_t bytes) {
+    if (!c) return DNB_ERR_ARG;
+    DNB_CUDA(cudaMemcpyAsync(dev, host, bytes, cudaMemcpyHostToDevice, c->stream));
+    DNB_CUDA(cudaStreamSynchronize(c->stream));
+    return DNB_OK;
+}
+
+int dnb_dev_download(dnb_ctx* c, void* host, const void* dev, size_t bytes) {
+    if (!c) return DNB_ERR_ARG;
+    DNB_CUDA(cudaMemcpyAsync(host, dev, bytes, cudaMemcpyDeviceToHost, c->stream));
+    DNB_CUDA(cudaStreamSynchronize(c->stream));
+    return DNB_OK;
+}
+
+int dnb_flush_l2(dnb_ctx* c) {
+    if (!c) return DNB_ERR_ARG;
+    const size_t bytes = 256u << 20;  // > 126 MB L2
+    int rc = grow(c->flush, bytes);
+    if (rc) return rc;
+    return launch_fill_u32(c, c->stream, (uint32_t*)c->flush.p, 0u, bytes / 4);
+}
+
+int dnb_profile_enable(dnb_ctx* c, int on) {
+    if (!c) return DNB_ERR_ARG;
+    DNB_CUDA(cudaDeviceSynchronize());
+    for (auto& r : c->prof.recs) { c->prof.pool.push_back(r.a); c->prof.pool.push_back(r.b); }
+    c->prof.recs.clear();
+    c->prof.on = on != 0;
+    return DNB_OK;
+}
+
+int dnb_profile_read(dnb_ctx* c, char* buf, size_t cap) {
+    if (!c || !buf || cap < 64) return DNB_ERR_ARG;
+    DNB_CUDA(cudaDeviceSynchronize());
+    std::map<std::string, std::pair<long, double>> acc;
+    for (auto& r : c->prof.recs) {
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, r.a, r.b) == cudaSuccess) {
+            auto& e = acc[r.name];
+            e.first++;
+            e.second += ms;
+        }
+    }
+    size_t n = 0;
+    n += snprintf(buf + n, cap - n, "{");
+    bool first = true;
+    for (auto& kv : acc) {
+        if (n + 128 >= cap) break;
+        n += snprintf(buf + n, cap - n, "%s\"%s\": {\"launches\": %ld, \"ms\": %.6f}", first ? "" : ", ",
+                      kv.first.c_str(), kv.second.first, kv.second.second);
+        first = false;
+    }
+    snprintf(buf + n, cap - n, "}");
+    return DNB_OK;
+}
+
+// ---- single matrix ---------------------------------------------------------------
+
+int dnb_register_matrix(dnb_ctx* c, uint64_t uid, int type, const void* blocks, size_t bytes, int k, int n) {
+    if (!c || !blocks) return DNB_ERR_ARG;
+    const size_t rb = row_bytes(type, k);
+    if (rb == 0 || !type_supported(type)) {
+        set_error("register_matrix: ggml type %d with k=%d is not handled", type, k);
+        return DNB_DECLINED;
+    }
+    if (n <= 0 || bytes != rb * (size_t)n) {
+        set_error("register_matrix: %zu bytes given, %zu expected for %d rows of %d", bytes, rb * (size_t)n, n, k);
+        return DNB_ERR_ARG;
+    }
+    DNB_CUDA(cudaSetDevice(c->device));
+    auto it = c->matrices.find(uid);
+    if (it != c->matrices.end()) {
+        cudaFree(it->second.dev);
+        c->matrices.erase(it);
+    }
+    Matrix m{type, k, n, rb, nullptr};
+    DNB_CUDA(cudaMalloc((void**)&m.dev, bytes));
+    DNB_CUDA(cudaMemcpy(m.dev, blocks, bytes, cudaMemcpyHostToDevice));
+    c->matrices[uid] = m;
+    return DNB_OK;
+}
+
+int dnb_set_gemv_impl(dnb_ctx* c, int impl) {
+    if (!c || impl < 0 || impl > 1) return DNB_ERR_ARG;
+    c->gemv_impl = impl;
+    return DNB_OK;
+}
+
+static int gemv_dev(dnb_ctx* c, int type, const uint8_t* w, int k, int n, const float* x, float* out, int nvec) {
+    if (c->gemv_impl == 1) {
+        for (int v = 0; v < nvec; ++v) {
+            int rc = launch_gemv_seq(c, c->stream, type, w, x + (size_t)v * k, out + (size_t)v * n, k, n);
+            if (rc) return rc;
+        }
+        return DNB_OK;
+    }
+    const SegDesc sd{w, nullptr, (uint32_t)nvec, 0u};
+    return launch_seg_matmul(c, c->stream, type, false, nullptr, nullptr, 1, k, n, x, k, nullptr, out, nvec, &sd);
+}
+
+int dnb_gemv_dev(dnb_ctx* c, int type, const void* w_dev, int k, int n, const float* x_dev, float* out_dev, int nvec) {
+    if (!c || !w_dev || !x_dev || !out_dev || nvec < 1) return DNB_ERR_ARG;
+    if (row_bytes(type, k) == 0 || !type_supported(type)) {
+        set_error("gemv: ggml type %d with k=%d is not handled", type, k);
+        return DNB_DECLINED;
+    }
+    return gemv_dev(c, type, (const uint8_t*)w_dev, k, n, x_dev, out_dev, nvec);
+}
+
+int dnb_gemv(dnb_ctx* c, uint64_t uid, const float* x, float* out) {
+    if (!c || !x || !out) return DNB_ERR_ARG;
+    auto it = c->matrices.find(uid);
+    if (it == c->matrices.end()) {
+        set_error("gemv: uid %llu is not registered", (unsigned long long)uid);
+        return DNB_DECLINED;
+    }
+    const Matrix& m = it->second;
+    DNB_CUDA(cudaSetDevice(c->device));
+    int rc;
+    if ((rc = grow(c->gemv_x, (size_t)m.k * 4))) return rc;
+    if ((rc = grow(c->gemv_out, (size_t)m.n * 4))) return rc;
+    DNB_CUDA(cudaMemcpyAsync(c->gemv_x.p, x, (size_t)m.k * 4, cudaMemcpyHostToDevice, c->stream));
+    if ((rc = gemv_dev(c, m.type, m.dev, m.k, m.n, (const float*)c->gemv_x.p, (float*)c->gemv_out.p, 1))) return rc;
+    DNB_CUDA(cudaMemcpyAsync(out, c->gemv_out.p, (size_t)m.n * 4, cudaMemcpyDeviceToHost, c->stream));
+    DNB_CUDA(cudaStreamSynchronize(c->stream));
+    return DNB_OK;
+}
+
+// ---- model --------------------------------------------------------------------------
+
+int dnb_moe_config(dnb_ctx* c, int n_layer, int e, int ff, int sff, int ne, int k, float eps, int norm_topk) {
+    if (!c) return DNB_ERR_ARG;
+    if (n_layer < 1 || e < 32 || ff < 32 || ne < 1 || k < 1 || k > ne || e % 32 || ff % 32 || (sff && sff % 32)) {
+        set_error("moe_config: bad shape (layers %d, embd %d, ff %d, shared ff %d, experts %d, used %d)", n_layer, e, ff,
+                  sff, ne, k);
+        return DNB_ERR_ARG;
+    }
+    if (ne > 1024 || k > 32) {
+        set_error("moe_config: the router kernels cover n_expert <= 1024 and k <= 32");
+        return DNB_DECLINED;
+    }
+    DNB_CUDA(cudaSetDevice(c->device));
+    DNB_CUDA(cudaDeviceSynchronize());
+    for (auto& L : c->model.layers) free_layer(L);
+    free_ws(c->ws);
+    Model& M = c->model;
+    M.n_layer = n_layer; M.e = e; M.ff = ff; M.sff = sff; M.ne = ne; M.k = k; M.eps = eps; M.norm_topk = norm_topk;
+    M.layers.assign(n_layer, Layer());
+    return DNB_OK;
+}
+
+static int check_expert_shape(dnb_ctx* c, int layer, int matrix, int type, int n_in, int n_out, int n_expert,
+                              size_t* rb_out) {
+    const Model& M = c->model;
+    if (layer < 0 || layer >= M.n_layer || matrix < 0 || matrix > 5) {
+        set_error("experts: layer %d / matrix %d out of range", layer, matrix);
+        return DNB_ERR_ARG;
+    }
+    const size_t rb = row_bytes(type, n_in);
+    if (rb == 0 || !type_supported(type)) {
+        set_error("experts: ggml type %d with n_in=%d is not handled", type, n_in);
+        return DNB_DECLINED;
+    }
+    const bool shared = matrix >= 3;
+    const bool down = (matrix % 3) == 2;
+    const int ffx = shared ? (M.sff ? M.sff : M.ff) : M.ff;
+    const int want_in = down ? ffx : M.e, want_out = down ? M.e : ffx, want_ne = shared ? 1 : M.ne;
+    if (n_in != want_in || n_out != want_out || n_expert != want_ne) {
+        set_error("experts: matrix %d is [%d x %d] x %d experts, the model needs [%d x %d] x %d", matrix, n_out, n_in,
+                  n_expert, want_out, want_in, want_ne);
+        return DNB_ERR_ARG;
+    }
+    *rb_out = rb;
+    return DNB_OK;
+}
+
+static int install_tensor(dnb_ctx* c, int layer, int matrix, int type, int n_in, int n_out, int n_expert, size_t rb) {
+    Layer& L = c->model.layers[layer];
+    ExpertTensor& t = L.m[matrix];
+    if (t.dev && t.owned) cudaFree(t.dev);
+    t = ExpertTensor();
+    t.type = type; t.n_in = n_in; t.n_out = n_out; t.n_expert = n_expert;
+    t.row_bytes = rb; t.expert_bytes = rb * (size_t)n_out;
+    DNB_CUDA(cudaMalloc((void**)&t.dev, t.expert_bytes * (size_t)n_expert));
+    t.owned = true;
+    return DNB_OK;
+}
+
+int dnb_register_experts(dnb_ctx* c, int layer, int matrix, int type, int n_in, int n_out, int n_expert,
+                         const void* blocks, size_t bytes) {
+    if (!c || !blocks) return DNB_ERR_ARG;
+    size_t rb;
+    int rc = check_expert_shape(c, layer, matrix, type, n_in, n_out, n_expert, &rb);
+    if (rc) return rc;
+    if (bytes != rb * (size_t)n_out * (size_t)n_expert) {
+        set_error("experts: %zu bytes given, %zu expected", bytes, rb * (size_t)n_out * (size_t)n_expert);
+        return DNB_ERR_ARG;
+    }
+    DNB_CUDA(cudaSetDevice(c->device));
+    if ((rc = install_tensor(c, layer, matrix, type, n_in, n_out, n_expert, rb))) return rc;
+    DNB_CUDA(cudaMemcpy(c->model.layers[layer].m[matrix].dev, blocks, bytes, cudaMemcpyHostToDevice));
+    return DNB_OK;
+}
+
+int dnb_synth_experts(dnb_ctx* c, int layer, int matrix, int type, int n_in, int n_out, int n_expert, uint64_t seed) {
+    if (!c) return DNB_ERR_ARG;
+    size_t rb;
+    int rc = check_expert_shape(c, layer, matrix, type, n_in, n_out, n_expert, &rb);
+    if (rc) return rc;
+    DNB_CUDA(cudaSetDevice(c->device));
+    if ((rc = install_tensor(c, layer, matrix, type, n_in, n_out, n_expert, rb))) return rc;
+    const uint64_t n_blocks = (uint64_t)n_expert * n_out * (n_in / block_elems(type));
+    return launch_synth_blocks(c, c->stream, type, seed, (uint64_t)layer * 16 + matrix,
+                               c->model.layers[layer].m[matrix].dev, n_blocks);
+}
+
+int dnb_download_expert(dnb_ctx* c, int layer, int matrix, int expert, void* dst, size_t bytes) {
+    if (!c || !dst || layer < 0 || layer >= c->model.n_layer || matrix < 0 || matrix > 5) return DNB_ERR_ARG;
+    const ExpertTensor& t = c->model.layers[layer].m[matrix];
+    if (!t.dev || expert < 0 || expert >= t.n_expert || bytes != t.expert_bytes) {
+        set_error("download_expert: tensor missing, expert out of range or size mismatch (%zu vs %zu)", bytes,
+                  t.expert_bytes);
+        return DNB_ERR_ARG;
+    }
+    DNB_CUDA(cudaStreamSynchronize(c->stream));
+    DNB_CUDA(cudaMemcpy(dst, t.dev + (size_t)expert * t.expert_bytes, bytes, cudaMemcpyDeviceToHost));
+    return DNB_OK;
+}
+
+static int upload_f32(float** dst, const float* src, size_t n) {
+    if (*dst) cudaFree(*dst);
+    *dst = nullptr;
+    if (!src) return DNB_OK;
+    DNB_CUDA(cudaMalloc((void**)dst, n * sizeof(float)));
+    DNB_CUDA(cudaMemcpy(*dst, src, n * sizeof(float), cudaMemcpyHostToDevice));
+    return DNB_OK;
+}
+
+int dnb_register_router(dnb_ctx* c, int layer, const float* w, const float* bias, const float* norm_w,
+                        const float* shared_gate_row) {
+    if (!c || !w || layer < 0 || layer >= c->model.n_layer) return DNB_ERR_ARG;
+    DNB_CUDA(cudaSetDevice(c->device));
+    const Model& M = c->model;
+    Layer& L = c->model.layers[layer];
+    int rc;
+    if ((rc = upload_f32(&L.router_w, w, (size_t)M.ne * M.e))) return rc;
+    if ((rc = upload_f32(&L.router_bias, bias, (size_t)M.ne))) return rc;
+    if ((rc = upload_f32(&L.norm_w, norm_w, (size_t)M.e))) return rc;
+    if ((rc = upload_f32(&L.shared_gate_row, shared_gate_row, (size_t)M.e))) return rc;
+    return DNB_OK;
+}
+
+// ---- block ----------------------------------------------------------------------------
+
+int dnb_moe_block_dev(dnb_ctx* c, int layer, const float* h_dev, int nt, float* out_dev) {
+    if (!c || !h_dev || !out_dev || nt < 1) return DNB_ERR_ARG;
+    if (!layer_ready(c, layer, true)) {
+        set_error("moe_block: layer %d is not fully registered", layer);
+        return DNB_DECLINED;
+    }
+    int rc = ensure_ws(c, nt);
+    if (rc) return rc;
+    return block_dev(c, layer, h_dev, nt, out_dev);
+}
+
+int dnb_moe_block(dnb_ctx* c, int layer, const float* h, int nt, float* out, int32_t* sels_out, float* wts_out) {
+    if (!c || !h || !out || nt < 1) return DNB_ERR_ARG;
+    if (!layer_ready(c, layer, true)) {
+        set_error("moe_block: layer %d is not fully registered", layer);
+        return DNB_DECLINED;
+    }
+    DNB_CUDA(cudaSetDevice(c->device));
+    int rc = ensure_ws(c, nt);
+    if (rc) return rc;
+    Workspace& w = c->ws;
+    const Model& M = c->model;
+    const size_t bytes = (size_t)nt * M.e * sizeof(float);
+    memcpy(w.pinned_in, h, bytes);
+    DNB_CUDA(cudaMemcpyAsync(w.hin, w.pinned_in, bytes, cudaMemcpyHostToDevice, c->stream));
+    if ((rc = block_dev(c, layer, w.hin, nt, w.out))) return rc;
+    DNB_CUDA(cudaMemcpyAsync(w.pinned_out, w.out, bytes, cudaMemcpyDeviceToHost, c->stream));
+    if (sels_out) DNB_CUDA(cudaMemcpyAsync(w.pinned_sels, w.sels, (size_t)nt * M.k * 4, cudaMemcpyDeviceToHost, c->stream));
+    if (wts_out) DNB_CUDA(cudaMemcpyAsync(w.pinned_wts, w.wts, (size_t)nt * M.k * 4, cudaMemcpyDeviceToHost, c->stream));
+    DNB_CUDA(cudaStreamSynchronize(c->stream));
+    memcpy(out, w.pinned_out, bytes);
+    if (sels_out) memcpy(sels_out, w.pinned_sels, (size_t)nt * M.k * 4);
+    if (wts_out) memcpy(wts_out, w.pinned_wts, (size_t)nt * M.k * 4);
+    return DNB_OK;
+}
+
+int dnb_moe_experts(dnb_ctx* c, int layer, const float* x, int nt, const int32_t* sels, const float* wts, float* out) {
+    if (!c || !x || !sels || !wts || !out || nt < 1) return DNB_ERR_ARG;
+    if (!layer_ready(c, layer, false)) {
+        set_error("moe_experts: layer %d has no expert tensors", layer);
+        return DNB_DECLINED;
+    }
+    const Model& M = c->model;
+    for (int t = 0; t < nt; ++t)
+        for (int s = 0; s < M.k; ++s) {
+            const int32_t e = sels[(size_t)t * M.k + s];
+            if (e < 0 || e >= M.ne || (s > 0 && e <= sels[(size_t)t * M.k + s - 1])) {
+                set_error("moe_experts: token %d slot %d: expert %d out of range or not ascending", t, s, e);
+                return DNB_ERR_ARG;
+            }
+        }
+    DNB_CUDA(cudaSetDevice(c->device));
+    int rc = ensure_ws(c, nt);
+    if (rc) return rc;
+    Workspace& w = c->ws;
+    const size_t bytes = (size_t)nt * M.e * sizeof(float), rows = (size_t)nt * M.k;
+    memcpy(w.pinned_in, x, bytes);
+    memcpy(w.pinned_sels, sels, rows * 4);
+    memcpy(w.pinned_wts, wts, rows * 4);
+    DNB_CUDA(cudaMemcpyAsync(w.hin, w.pinned_in, bytes, cudaMemcpyHostToDevice, c->stream));
+    DNB_CUDA(cudaMemcpyAsync(w.sels, w.pinned_sels, rows * 4, cudaMemcpyHostToDevice, c->stream));
+    DNB_CUDA(cudaMemcpyAsync(w.wts, w.pinned_wts, rows * 4, cudaMemcpyHostToDevice, c->stream));
+    const Layer& L = M.layers[layer];
+    if (L.has_shared())
+        if ((rc = launch_prep(c, c->stream, w.hin, nullptr, M.eps, nt, M.e, nullptr, w.seg_sh_gu, w.seg_sh_dn,
+                              L.m[3].dev, L.m[4].dev, L.m[5].dev)))
+            return rc;
+    if ((rc = experts_dev(c, layer, w.hin, nt, w.sels, w.wts, w.out))) return rc;
+    DNB_CUDA(cudaMemcpyAsync(w.pinned_out, w.out, bytes, cudaMemcpyDeviceToHost, c->stream));
+    DNB_CUDA(cudaStreamSynchronize(c->stream));
+    memcpy(out, w.pinned_out, bytes);
+    return DNB_OK;
+}
+
+int dnb_router_topk(dnb_ctx* c, int layer, const float* x, int nt, int32_t* sels, float* wts, float* rowsum) {
+    if (!c || !x || !sels || !wts || nt < 1) return DNB_ERR_ARG;
+    if (layer < 0 || layer >= c->model.n_layer || !c->model.layers[layer].router_w) {
+        set_error("router_topk: layer %d has no router", layer);
+        return DNB_DECLINED;
+    }
+    DNB_CUDA(cudaSetDevice(c->device));
+    int rc = ensure_ws(c, nt);
+    if (rc) return rc;
+    Workspace& w = c->ws;
+    const Model& M = c->model;
+    const Layer& L = M.layers[layer];
+    const size_t bytes = (size_t)nt * M.e * sizeof(float), rows = (size_t)nt * M.k;
+    memcpy(w.pinned_in, x, bytes);
+    DNB_CUDA(cudaMemcpyAsync(w.hin, w.pinned_in, bytes, cudaMemcpyHostToDevice, c->stream));
+    if ((rc = launch_router_logits(c, c->stream, w.hin, nt, M.e, L.router_w, L.router_bias, M.ne, w.logits))) return rc;
+    if ((rc = launch_topk(c, c->stream, w.logits, nt, M.ne, M.k, M.norm_topk, w.sels, w.wts, rowsum ? w.shcoef : nullptr)))
+        return rc;
+    DNB_CUDA(cudaMemcpyAsync(w.pinned_sels, w.sels, rows * 4, cudaMemcpyDeviceToHost, c->stream));
+    DNB_CUDA(cudaMemcpyAsync(w.pinned_wts, w.wts, rows * 4, cudaMemcpyDeviceToHost, c->stream));
+    if (rowsum) DNB_CUDA(cudaMemcpyAsync(w.pinned_out, w.shcoef, (size_t)nt * 4, cudaMemcpyDeviceToHost, c->stream));
+    DNB_CUDA(cudaStreamSynchronize(c->stream));
+    memcpy(sels, w.pinned_sels, rows * 4);
+    memcpy(wts, w.pinned_wts, rows * 4);
+    if (rowsum) memcpy(rowsum, w.pinned_out, (size_t)nt * 4);
+    return DNB_OK;
+}
+
+int dnb_grouped_gemm(dnb_ctx* c, int layer, int matrix, const uint32_t* segs, int nseg, const float* xs, float* outs) {
+    if (!c || !segs || !xs || !outs || nseg < 1) return DNB_ERR_ARG;
+    if (layer < 0 || layer >= c->model.n_layer || matrix < 0 || matrix > 5 || !c->model.layers[layer].m[matrix].dev) {
+        set_error("grouped_gemm: layer %d matrix %d is not registered", layer, matrix);
+        return DNB_DECLINED;
+    }
+    const ExpertTensor& t = c->model.layers[layer].m[matrix];
+    // segment table contract of moe_expert.rs:8399-8440 (check_segments): m > 0,
+    // offsets contiguous from 0, experts in range
+    size_t row = 0;
+    uint32_t m_max = 0;
+    std::vector<SegDesc> sd(nseg);
+    for (int i = 0; i < nseg; ++i) {
+        const uint32_t ex = segs[4 * i], m = segs[4 * i + 1], xo = segs[4 * i + 2], oo = segs[4 * i + 3];
+        if (m == 0 || ex >= (uint32_t)t.n_expert || xo != row || oo != row) {
+            set_error("grouped_gemm: segment %d (expert %u, m %u, x_off %u, out_off %u) breaks the table contract", i, ex,
+                      m, xo, oo);
+            return DNB_ERR_ARG;
+        }
+        sd[i] = SegDesc{t.dev + (size_t)ex * t.expert_bytes, nullptr, m, (uint32_t)row};
+        row += m;
+        if (m > m_max) m_max = m;
+    }
+    DNB_CUDA(cudaSetDevice(c->device));
+    float *dx = nullptr, *dout = nullptr;
+    SegDesc* dsd = nullptr;
+    DNB_CUDA(cudaMalloc((void**)&dx, row * t.n_in * sizeof(float)));
+    DNB_CUDA(cudaMalloc((void**)&dout, row * t.n_out * sizeof(float)));
+    DNB_CUDA(cudaMalloc((void**)&dsd, nseg * sizeof(SegDesc)));
+    DNB_CUDA(cudaMemcpyAsync(dx, xs, row * t.n_in * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+    DNB_CUDA(cudaMemcpyAsync(dsd, sd.data(), nseg * sizeof(SegDesc), cudaMemcpyHostToDevice, c->stream));
+    int rc = launch_seg_matmul(c, c->stream, t.type, false, dsd, nullptr, nseg, t.n_in, t.n_out, dx, t.n_in, nullptr,
+                               dout, (int)m_max);
+    if (rc == DNB_OK) {
+        cudaError_t e = cudaMemcpyAsync(outs, dout, row * t.n_out * sizeof(float), cudaMemcpyDeviceToHost, c->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+        if (e != cudaSuccess) {
+            set_error("grouped_gemm: %s", cudaGetErrorString(e));
+            rc = DNB_ERR_CUDA;
+        }
+    } else {
+        cudaStreamSynchronize(c->stream);
+    }
+    cudaFree(dx);
+    cudaFree(dout);
+    cudaFree(dsd);
+    return rc;
+}
+
+int dnb_moe_stack_dev(dnb_ctx* c, float* h_dev, int nt) {
+    if (!c || !h_dev || nt < 1) return DNB_ERR_ARG;
+    const Model& M = c->model;
+    for (int l = 0; l < M.n_layer; ++l)
+        if (!layer_ready(c, l, true)) {
+            set_error("moe_stack: layer %d is not fully registered", l);
+            return DNB_DECLINED;
+        }
+    int rc = ensure_ws(c, nt);
+    if (rc) return rc;
+    for (int l = 0; l < M.n_layer; ++l) {
+        if ((rc = block_dev(c, l, h_dev, nt, c->ws.out))) return rc;
+        if ((rc = launch_add_inplace(c, c->stream, h_dev, c->ws.out, (size_t)nt * M.e))) return rc;
+    }
+    return DNB_OK;
+}
+
+int dnb_moe_stack(dnb_ctx* c, const float* h, int nt, float* out) {
+    if (!c || !h || !out || nt < 1) return DNB_ERR_ARG;
+    DNB_CUDA(cudaSetDevice(c->device));
+    if (c->model.n_layer < 1) {
+        set_error("moe_stack: no model configured");
+        return DNB_DECLINED;
+    }
+    int rc = ensure_ws(c, nt);
+    if (rc) return rc;
+    Workspace& w = c->ws;
+    const size_t bytes = (size_t)nt * c->model.e * sizeof(float);
+    memcpy(w.pinned_in, h, bytes);
+    DNB_CUDA(cudaMemcpyAsync(w.hin, w.pinned_in, bytes, cudaMemcpyHostToDevice, c->stream));
+    if ((rc = dnb_moe_stack_dev(c, w.hin, nt))) return rc;
+    DNB_CUDA(cudaMemcpyAsync(w.pinned_out, w.hin, bytes, cudaMemcpyDeviceToHost, c->stream));
+    DNB_CUDA(cudaStreamSynchronize(c->stream));
+    memcpy(out, w.pinned_out, bytes);
+    return DNB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,185 @@
+// Shared declarations of the CUDA library: context, layer tables, error
+// plumbing and the launchers each translation unit exports to api.cu.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+#include <stddef.h>
+#include <map>
+#include <string>
+#include <vector>
+
+#include "dnb200.h"
+
+namespace dnb {
+
+// ---- block formats ---------------------------------------------------------
+constexpr int T_F32 = 0, T_Q5_1 = 7, T_Q8_0 = 8, T_Q4_K = 12, T_Q5_K = 13, T_Q6_K = 14, T_IQ3_XXS = 18;
+
+__host__ __device__ constexpr int type_size(int t) {
+    return t == T_Q4_K ? 144 : t == T_IQ3_XXS ? 98 : t == T_Q6_K ? 210 : t == T_Q8_0 ? 34 : t == T_Q5_K ? 176
+         : t == T_Q5_1 ? 24 : t == T_F32 ? 4 : 0;
+}
+__host__ __device__ constexpr int block_elems(int t) {
+    return (t == T_Q4_K || t == T_IQ3_XXS || t == T_Q6_K || t == T_Q5_K) ? 256
+         : (t == T_Q8_0 || t == T_Q5_1) ? 32 : t == T_F32 ? 1 : 0;
+}
+inline bool type_supported(int t) { return type_size(t) != 0 && t != T_F32; }
+// Bytes of one row of n_in elements, or 0 when n_in is not a whole number of blocks.
+inline size_t row_bytes(int t, long n_in) {
+    const int be = block_elems(t);
+    if (be == 0 || n_in <= 0 || n_in % be) return 0;
+    return (size_t)(n_in / be) * type_size(t);
+}
+
+// ---- resident tensors --------------------------------------------------------
+struct ExpertTensor {          // one of gate / up / down of a layer, expert-major
+    int type = -1;
+    int n_in = 0, n_out = 0, n_expert = 0;
+    size_t row_bytes = 0, expert_bytes = 0;
+    uint8_t* dev = nullptr;
+    bool owned = false;
+};
+
+struct Layer {
+    ExpertTensor m[6];         // 0 gate 1 up 2 down 3 shared-gate 4 shared-up 5 shared-down
+    float* router_w = nullptr;         // [ne][e]
+    float* router_bias = nullptr;      // [ne] or null
+    float* norm_w = nullptr;           // [e] or null
+    float* shared_gate_row = nullptr;  // [e] or null
+    bool has_shared() const { return m[3].dev && m[4].dev && m[5].dev; }
+};
+
+struct Matrix {                // single resident matrix keyed by uid (GEMV path)
+    int type; int k, n; size_t row_bytes; uint8_t* dev;
+};
+
+// One unit of grouped work: `m` token rows against one expert's matrix (or the
+// gate and up matrices together).  Built on the device by the routing kernel.
+struct SegDesc {
+    const uint8_t* wa;
+    const uint8_t* wb;
+    uint32_t m;
+    uint32_t row0;             // first row of the segment in the packed row space
+};
+
+struct Scratch {               // grow-only device scratch of a context
+    void* p = nullptr; size_t cap = 0;
+};
+
+struct Model {
+    int n_layer = 0, e = 0, ff = 0, sff = 0, ne = 0, k = 0;
+    float eps = 1e-6f;
+    int norm_topk = 1;
+    std::vector<Layer> layers;
+};
+
+struct Workspace {             // device buffers of the MoE pipeline, sized for nt_cap tokens
+    int nt_cap = 0;
+    float *xn = nullptr, *logits = nullptr, *wts = nullptr, *act = nullptr, *hrow = nullptr, *sact = nullptr,
+          *sh = nullptr, *hin = nullptr, *out = nullptr, *shcoef = nullptr;
+    int32_t *sels = nullptr, *row_token = nullptr, *pos = nullptr, *nseg = nullptr, *counts = nullptr;
+    SegDesc *seg_gu = nullptr, *seg_dn = nullptr, *seg_sh_gu = nullptr, *seg_sh_dn = nullptr;
+    float* pinned_in = nullptr; float* pinned_out = nullptr; size_t pinned_cap = 0;
+    int32_t* pinned_sels = nullptr; float* pinned_wts = nullptr;
+};
+
+}  // namespace dnb
+
+namespace dnb {
+// Optional per-kernel timing: when enabled every launcher brackets its kernel
+// with a pair of events on the launching stream.
+struct ProfRec { const char* name; cudaEvent_t a, b; };
+struct Profiler {
+    bool on = false;
+    std::vector<ProfRec> recs;      // recorded pairs, in launch order
+    std::vector<cudaEvent_t> pool;  // events ready for reuse
+};
+}  // namespace dnb
+
+struct dnb_ctx {
+    int device = 0;
+    dnb::Profiler prof;
+    cudaStream_t stream = nullptr;      // main stream (owned unless set from outside)
+    cudaStream_t side = nullptr;        // shared-expert stream
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr, ev_t0 = nullptr, ev_t1 = nullptr;
+    cudaStream_t saved_stream = nullptr;  // the context's own stream while an external one is set
+    bool own_stream = true;
+    dnb::Scratch flush;
+    std::map<uint64_t, dnb::Matrix> matrices;
+    dnb::Model model;
+    dnb::Workspace ws;
+    dnb::Scratch gemv_x, gemv_out;
+    int sm_count = 148;
+    int* status = nullptr;              // device status word written by kernels on internal errors
+    uint64_t launches = 0;              // kernels launched by this context (bench accounting)
+    int gemv_impl = 0;                  // 0 = fast (default), 1 = sequential bit-exact
+};
+
+namespace dnb {
+
+void set_error(const char* fmt, ...);
+
+struct ProfScope {
+    dnb_ctx* c; cudaStream_t st; cudaEvent_t b = nullptr;
+    ProfScope(dnb_ctx* c_, cudaStream_t st_, const char* name) : c(c_), st(st_) {
+        if (!c->prof.on || c->prof.recs.size() >= 65536) return;
+        cudaEvent_t ev[2];
+        for (auto& e : ev) {
+            if (!c->prof.pool.empty()) { e = c->prof.pool.back(); c->prof.pool.pop_back(); }
+            else if (cudaEventCreate(&e) != cudaSuccess) return;
+        }
+        cudaEventRecord(ev[0], st);
+        b = ev[1];
+        c->prof.recs.push_back(ProfRec{name, ev[0], ev[1]});
+    }
+    ~ProfScope() { if (b) cudaEventRecord(b, st); }
+};
+#define DNB_CUDA(call)                                                                         \
+    do {                                                                                       \
+        cudaError_t e_ = (call);                                                               \
+        if (e_ != cudaSuccess) {                                                               \
+            dnb::set_error("%s failed: %s (%s:%d)", #call, cudaGetErrorString(e_), __FILE__, __LINE__); \
+            return DNB_ERR_CUDA;                                                               \
+        }                                                                                      \
+    } while (0)
+
+// ---- launchers (defined in the .cu files) -----------------------------------
+// Segmented dequant matmul: for every segment s < *nseg_dev (or nseg_host when
+// nseg_dev is null), rows of seg[s].wa (and wb when fused) times the segment's
+// token rows.  Token i of a segment reads x + row_token[row0 + i] * ldx (or row
+// row0 + i when row_token is null).  fused: out[(row0+i)*n_out + r] =
+// silu(wa_r . x) * (wb_r . x); otherwise out[(row0+i)*n_out + r] = wa_r . x.
+// With seg == null the single segment *single (a host struct) is passed by value.
+int launch_seg_matmul(dnb_ctx* c, cudaStream_t st, int type, bool fused, const SegDesc* seg, const int32_t* nseg_dev,
+                      int nseg_max, int n_in, int n_out, const float* x, int ldx, const int32_t* row_token,
+                      float* out, int m_max, const SegDesc* single = nullptr);
+// Bit-exact-order GEMV (one thread per row, ascending i, no FMA contraction).
+int launch_gemv_seq(dnb_ctx* c, cudaStream_t st, int type, const uint8_t* w, const float* x, float* out, int n_in,
+                    int n_out);
+
+int launch_rmsnorm(dnb_ctx* c, cudaStream_t st, const float* h, const float* w, float eps, int nt, int e, float* out);
+// RMSNorm (skipped when w is null) that also publishes the shared expert's two
+// one-segment descriptors for this call.
+int launch_prep(dnb_ctx* c, cudaStream_t st, const float* h, const float* w, float eps, int nt, int e, float* out,
+                SegDesc* sh_gu, SegDesc* sh_dn, const uint8_t* sg, const uint8_t* su, const uint8_t* sdn);
+int launch_add_inplace(dnb_ctx* c, cudaStream_t st, float* h, const float* d, size_t n);
+int launch_fill_u32(dnb_ctx* c, cudaStream_t st, uint32_t* dst, uint32_t v, size_t n);
+int launch_router_logits(dnb_ctx* c, cudaStream_t st, const float* x, int nt, int e, const float* w_r,
+                         const float* bias, int ne, float* logits);
+int launch_topk(dnb_ctx* c, cudaStream_t st, const float* logits, int nt, int ne, int k, int norm_topk, int32_t* sels,
+                float* wts, float* rowsum);
+// Builds, from sels[nt][k], the expert-major row space: counts, segment
+// descriptors for gate/up and down, row_token[], pos[t][slot] and *nseg.
+int launch_route_tables(dnb_ctx* c, cudaStream_t st, const int32_t* sels, int nt, int k, int ne, const Layer& L,
+                        Workspace& ws);
+int launch_combine(dnb_ctx* c, cudaStream_t st, const float* hrow, const int32_t* pos, const float* wts, int nt,
+                   int k, int e, const float* sh, const float* shcoef, float* out);
+int launch_shared_coef(dnb_ctx* c, cudaStream_t st, const float* x, const float* row, int nt, int e, float* coef);
+int launch_synth_blocks(dnb_ctx* c, cudaStream_t st, int type, uint64_t seed, uint64_t tensor_id, uint8_t* dst,
+                        uint64_t n_blocks);
+int launch_synth_normal(dnb_ctx* c, cudaStream_t st, uint64_t seed, uint64_t tensor_id, float sigma, float* dst,
+                        uint64_t n);
+
+}  // namespace dnb

@@ -1,0 +1,431 @@
+// The small kernels around the expert matmuls: RMSNorm, router logits, softmax +
+// top-k + renorm, the expert-major routing tables, the weighted combine and the
+// shared-expert gate coefficient.
+#include "dnb_common.cuh"
+
+namespace dnb {
+
+// ---- RMSNorm (tensor.rs:1125-1135 rmsnorm_into) --------------------------------
+// One CTA per token row.  ss is a fixed-order tree sum (the CPU sums left to
+// right; the two differ by rounding only).  Also publishes the shared expert's
+// two one-segment work descriptors for this call (m = nt, rows 0..nt-1).
+__global__ void __launch_bounds__(256)
+prep_kernel(const float* __restrict__ h, const float* __restrict__ w, float eps, int e, float* __restrict__ out,
+            SegDesc* sh_gu, SegDesc* sh_dn, const uint8_t* sg, const uint8_t* su, const uint8_t* sdn, uint32_t nt) {
+    if (blockIdx.x == 0 && threadIdx.x == 0 && sh_gu) {
+        sh_gu[0] = SegDesc{sg, su, nt, 0u};
+        sh_dn[0] = SegDesc{sdn, nullptr, nt, 0u};
+    }
+    if (!w) return;
+    __shared__ float red[8];
+    __shared__ float inv_s;
+    const float* xr = h + (size_t)blockIdx.x * e;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < e; i += 256) ss = fmaf(xr[i], xr[i], ss);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.f;
+        for (int i = 0; i < 8; ++i) t += red[i];
+        inv_s = 1.0f / sqrtf(t / (float)e + eps);
+    }
+    __syncthreads();
+    const float inv = inv_s;
+    float* o = out + (size_t)blockIdx.x * e;
+    for (int i = threadIdx.x; i < e; i += 256) o[i] = __fmul_rn(__fmul_rn(xr[i], inv), w[i]);
+}
+
+int launch_rmsnorm(dnb_ctx* c, cudaStream_t st, const float* h, const float* w, float eps, int nt, int e, float* out) {
+    ProfScope prof_(c, st, "rmsnorm");
+    prep_kernel<<<nt, 256, 0, st>>>(h, w, eps, e, out, nullptr, nullptr, nullptr, nullptr, nullptr, 0u);
+    c->launches++;
+    DNB_CUDA(cudaGetLastError());
+    return DNB_OK;
+}
+
+int launch_prep(dnb_ctx* c, cudaStream_t st, const float* h, const float* w, float eps, int nt, int e, float* out,
+                SegDesc* sh_gu, SegDesc* sh_dn, const uint8_t* sg, const uint8_t* su, const uint8_t* sdn) {
+    ProfScope prof_(c, st, "prep_rmsnorm");
+    prep_kernel<<<nt, 256, 0, st>>>(h, w, eps, e, out, sh_gu, sh_dn, sg, su, sdn, (uint32_t)nt);
+    c->launches++;
+    DNB_CUDA(cudaGetLastError());
+    return DNB_OK;
+}
+
+// ---- router logits (linear_gguf.rs:836-964 f32 GEMV; kernels_elem.cu:948-1002,
+// 1085 are the reference GPU forms) -------------------------------------------
+// logits[t][i] = W_r[i] . x_t + bias[i].  One warp per expert row, the row read
+// once as coalesced float4 and applied to up to RT tokens staged in shared memory.
+constexpr int RT = 8;         // tokens per CTA
+constexpr int RROWS = 4;      // expert rows (warps) per CTA
+__global__ void __launch_bounds__(RROWS * 32)
+router_logits_kernel(const float* __restrict__ x, int nt, int e, const float* __restrict__ w_r,
+                     const float* __restrict__ bias, int ne, float* __restrict__ logits) {
+    extern __shared__ __align__(16) float xs[];  // [RT][e]
+    const int t0 = blockIdx.y * RT;
+    const int ntok = min(RT, nt - t0);
+    const int e4 = e >> 2;
+    for (int i = threadIdx.x; i < ntok * e4; i += RROWS * 32)
+        reinterpret_cast<float4*>(xs)[i] = reinterpret_cast<const float4*>(x + (size_t)t0 * e)[i];
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int row = blockIdx.x * RROWS + warp;
+    if (row >= ne) return;
+    const float4* wr = reinterpret_cast<const float4*>(w_r + (size_t)row * e);
+    float acc[RT];
+#pragma unroll
+    for (int t = 0; t < RT; ++t) acc[t] = 0.f;
+    for (int i = lane; i < e4; i += 32) {
+        const float4 wv = __ldg(wr + i);
+#pragma unroll
+        for (int t = 0; t < RT; ++t) {
+            if (t < ntok) {
+                const float4 xv = reinterpret_cast<const float4*>(xs)[t * e4 + i];
+                acc[t] = fmaf(wv.x, xv.x, acc[t]);
+                acc[t] = fmaf(wv.y, xv.y, acc[t]);
+                acc[t] = fmaf(wv.z, xv.z, acc[t]);
+                acc[t] = fmaf(wv.w, xv.w, acc[t]);
+            }
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < RT; ++t) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc[t] += __shfl_xor_sync(0xffffffffu, acc[t], o);
+    }
+    if (lane == 0) {
+        const float b = bias ? bias[row] : 0.f;
+        for (int t = 0; t < ntok; ++t) logits[(size_t)(t0 + t) * ne + row] = bias ? acc[t] + b : acc[t];
+    }
+}
+
+int launch_router_logits(dnb_ctx* c, cudaStream_t st, const float* x, int nt, int e, const float* w_r,
+                         const float* bias, int ne, float* logits) {
+    if (e % 4) {
+        set_error("router: n_embd %d is not a multiple of 4", e);
+        return DNB_DECLINED;
+    }
+    const size_t smem = (size_t)RT * e * sizeof(float);
+    static size_t smem_set = 0;
+    if (smem > smem_set) {
+        DNB_CUDA(cudaFuncSetAttribute(router_logits_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        smem_set = smem;
+    }
+    dim3 grid((ne + RROWS - 1) / RROWS, (nt + RT - 1) / RT);
+    ProfScope prof_(c, st, "router_logits");
+    router_logits_kernel<<<grid, RROWS * 32, smem, st>>>(x, nt, e, w_r, bias, ne, logits);
+    c->launches++;
+    DNB_CUDA(cudaGetLastError());
+    return DNB_OK;
+}
+
+// ---- softmax + top-k + renorm (tensor.rs:1171-1183; moe.rs:188-279;
+// qwen4exp.rs:11802-11821; GPU form kernels_router225.cu:36-171) -----------------
+// One warp per token, ne <= 1024, k <= 32.  Selection rule of the CPU scan
+// (moe.rs:256-279): each round takes the first unused entry and replaces it only
+// by a strictly larger later value, so ties go to the lower index and a NaN is
+// only taken when it is the first unused entry.  Output ascending; renorm sums
+// the selected probabilities in ascending index order, one add at a time.
+__global__ void __launch_bounds__(128)
+topk_kernel(const float* __restrict__ logits, int nt, int ne, int k, int norm_topk, int32_t* __restrict__ sels,
+            float* __restrict__ wts, float* __restrict__ rowsum) {
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (t >= nt) return;
+    const int per = (ne + 31) >> 5;  // <= 32
+    float p[32];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        const int idx = i * 32 + lane;
+        p[i] = (i < per && idx < ne) ? logits[(size_t)t * ne + idx] : -INFINITY;
+        mx = fmaxf(mx, p[i]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        const int idx = i * 32 + lane;
+        if (i < per && idx < ne) {
+            p[i] = expf(p[i] - mx);
+            sum += p[i];
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (sum > 0.f) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) p[i] = p[i] / sum;
+    }
+    uint32_t used = 0;  // bit i: entry i*32+lane taken
+    int my_sel = -1;    // lane j < k keeps the j-th pick
+    float my_p = 0.f;
+    for (int round = 0; round < k; ++round) {
+        // first unused entry of the row and whether it is NaN
+        int first = 0x7fffffff;
+        float best = -INFINITY;
+        int best_i = 0x7fffffff;
+        bool have = false;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            const int idx = i * 32 + lane;
+            if (i < per && idx < ne && !((used >> i) & 1u)) {
+                first = min(first, idx);
+                const float v = p[i];
+                if (v == v && (!have || v > best)) {  // ascending idx inside a lane: strict > keeps the lower
+                    best = v;
+                    best_i = idx;
+                    have = true;
+                }
+            }
+        }
+        int gfirst = first;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) gfirst = min(gfirst, __shfl_xor_sync(0xffffffffu, gfirst, o));
+        // value of the first unused entry (owner lane = gfirst & 31, slot gfirst >> 5)
+        float fv = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+            if (i == (gfirst >> 5)) fv = p[i];
+        fv = __shfl_sync(0xffffffffu, fv, gfirst & 31);
+        int win;
+        if (fv != fv) {
+            win = gfirst;  // a leading NaN is kept by the scan
+        } else {
+            // argmax over non-NaN unused entries, ties to the lower index
+            float bv = have ? best : -INFINITY;
+            int bi = have ? best_i : 0x7fffffff;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) {
+                    bv = ov;
+                    bi = oi;
+                }
+            }
+            win = bi;
+        }
+        if ((win & 31) == lane) used |= 1u << (win >> 5);
+        float wv = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+            if (i == (win >> 5)) wv = p[i];
+        wv = __shfl_sync(0xffffffffu, wv, win & 31);
+        if (lane == round) {
+            my_sel = win;
+            my_p = wv;
+        }
+    }
+    // rank of my pick among the k picks -> ascending order
+    int rank = 0;
+    for (int j = 0; j < k; ++j) {
+        const int other = __shfl_sync(0xffffffffu, my_sel, j);
+        if (lane < k && other < my_sel) rank++;
+    }
+    // gather into sorted lanes: lane r receives the pick whose rank is r
+    int sorted_sel = -1;
+    float sorted_p = 0.f;
+    for (int j = 0; j < k; ++j) {
+        const int rj = __shfl_sync(0xffffffffu, rank, j);
+        const int sj = __shfl_sync(0xffffffffu, my_sel, j);
+        const float pj = __shfl_sync(0xffffffffu, my_p, j);
+        if (lane == rj) {
+            sorted_sel = sj;
+            sorted_p = pj;
+        }
+    }
+    float s = 0.f;
+    for (int j = 0; j < k; ++j) s = __fadd_rn(s, __shfl_sync(0xffffffffu, sorted_p, j));
+    if (lane < k) {
+        float w;
+        if (!norm_topk) w = sorted_p;
+        else if (isfinite(s) && s > 0.f) w = sorted_p / s;
+        else w = 1.0f / (float)k;
+        sels[(size_t)t * k + lane] = sorted_sel;
+        wts[(size_t)t * k + lane] = w;
+    }
+    if (rowsum && lane == 0) rowsum[t] = s;
+}
+
+int launch_topk(dnb_ctx* c, cudaStream_t st, const float* logits, int nt, int ne, int k, int norm_topk, int32_t* sels,
+                float* wts, float* rowsum) {
+    if (ne > 1024 || k > 32 || k < 1 || k > ne) {
+        set_error("topk: n_expert %d / k %d outside the kernel's range (<=1024, <=32)", ne, k);
+        return DNB_DECLINED;
+    }
+    ProfScope prof_(c, st, "router_topk");
+    topk_kernel<<<(nt + 3) / 4, 128, 0, st>>>(logits, nt, ne, k, norm_topk, sels, wts, rowsum);
+    c->launches++;
+    DNB_CUDA(cudaGetLastError());
+    return DNB_OK;
+}
+
+// ---- routing tables -----------------------------------------------------------
+// From sels[nt][k] build the expert-major packed row space the grouped matmuls
+// work in (qwen4exp.rs:18172-18185 by_expert; moe_expert.rs:8309-8390
+// build_grouped_batch; exp_pf.rs:23-31 rows[]): experts in ascending index, the
+// rows of an expert in ascending token order.  One CTA; membership bitmap in
+// shared memory; counts by ballot, so the result does not depend on timing.
+//   row_token[row] = token of the packed row       pos[t*k+slot] = packed row
+//   seg_gu/seg_dn[i] = i-th active expert's matrices, m and first row; *nseg
+__global__ void __launch_bounds__(1024)
+route_tables_kernel(const int32_t* __restrict__ sels, int nt, int k, int ne, const uint8_t* gate, const uint8_t* up,
+                    const uint8_t* down, size_t eb_g, size_t eb_u, size_t eb_d, SegDesc* seg_gu, SegDesc* seg_dn,
+                    int32_t* row_token, int32_t* pos, int32_t* nseg, int32_t* counts_out) {
+    extern __shared__ uint32_t sm[];
+    const int words = (ne + 31) >> 5;
+    uint32_t* bitmap = sm;                       // [nt][words]
+    int* counts = (int*)(sm + (size_t)nt * words);  // [ne]
+    int* offs = counts + ne;                     // [ne] exclusive row offsets
+    int* segi = offs + ne;                       // [ne] segment index of active experts
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = blockDim.x >> 5;
+    for (int i = tid; i < nt * words; i += blockDim.x) bitmap[i] = 0;
+    __syncthreads();
+    for (int i = tid; i < nt * k; i += blockDim.x) {
+        const int e = sels[i];
+        if (e >= 0 && e < ne) atomicOr(&bitmap[(size_t)(i / k) * words + (e >> 5)], 1u << (e & 31));
+    }
+    __syncthreads();
+    for (int e = warp; e < ne; e += nwarp) {
+        int cnt = 0;
+        for (int t0 = 0; t0 < nt; t0 += 32) {
+            const int t = t0 + lane;
+            const bool has = t < nt && ((bitmap[(size_t)t * words + (e >> 5)] >> (e & 31)) & 1u);
+            cnt += __popc(__ballot_sync(0xffffffffu, has));
+        }
+        if (lane == 0) counts[e] = cnt;
+    }
+    __syncthreads();
+    if (tid == 0) {  // ne <= 1024: a serial scan is a few microseconds at most
+        int row = 0, si = 0;
+        for (int e = 0; e < ne; ++e) {
+            offs[e] = row;
+            segi[e] = counts[e] > 0 ? si++ : -1;
+            row += counts[e];
+        }
+        *nseg = si;
+    }
+    __syncthreads();
+    for (int e = tid; e < ne; e += blockDim.x) {
+        if (counts_out) counts_out[e] = counts[e];
+        if (counts[e] > 0) {
+            const int si = segi[e];
+            seg_gu[si] = SegDesc{gate + (size_t)e * eb_g, up + (size_t)e * eb_u, (uint32_t)counts[e], (uint32_t)offs[e]};
+            seg_dn[si] = SegDesc{down + (size_t)e * eb_d, nullptr, (uint32_t)counts[e], (uint32_t)offs[e]};
+        }
+    }
+    for (int e = warp; e < ne; e += nwarp) {
+        if (counts[e] == 0) continue;
+        int run = offs[e];
+        for (int t0 = 0; t0 < nt; t0 += 32) {
+            const int t = t0 + lane;
+            const bool has = t < nt && ((bitmap[(size_t)t * words + (e >> 5)] >> (e & 31)) & 1u);
+            const uint32_t b = __ballot_sync(0xffffffffu, has);
+            if (has) {
+                const int row = run + __popc(b & ((1u << lane) - 1u));
+                row_token[row] = t;
+                for (int s = 0; s < k; ++s)
+                    if (sels[(size_t)t * k + s] == e) pos[(size_t)t * k + s] = row;
+            }
+            run += __popc(b);
+        }
+    }
+}
+
+int launch_route_tables(dnb_ctx* c, cudaStream_t st, const int32_t* sels, int nt, int k, int ne, const Layer& L,
+                        Workspace& ws) {
+    const int words = (ne + 31) >> 5;
+    const size_t smem = ((size_t)nt * words + 3 * (size_t)ne) * 4;
+    if (smem > 200 * 1024) {
+        set_error("route tables: %d tokens x %d experts exceeds one CTA's shared memory", nt, ne);
+        return DNB_DECLINED;
+    }
+    static size_t smem_set = 0;
+    if (smem > smem_set) {
+        DNB_CUDA(cudaFuncSetAttribute(route_tables_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        smem_set = smem;
+    }
+    const int thr = nt * k >= 512 ? 1024 : 256;
+    ProfScope prof_(c, st, "route_tables");
+    route_tables_kernel<<<1, thr, smem, st>>>(sels, nt, k, ne, L.m[0].dev, L.m[1].dev, L.m[2].dev, L.m[0].expert_bytes,
+                                              L.m[1].expert_bytes, L.m[2].expert_bytes, ws.seg_gu, ws.seg_dn,
+                                              ws.row_token, ws.pos, ws.nseg, ws.counts);
+    c->launches++;
+    DNB_CUDA(cudaGetLastError());
+    return DNB_OK;
+}
+
+// ---- weighted combine (kernels_dec_epi.cu:28-46 dno_dec_exp_sum;
+// moe_grouped_gpu.rs:540-565 scatter; qwen4exp.rs:12126-12216) --------------------
+// out[t][j] = sum over slots in ascending order of w[t][s] * h[pos[t][s]][j]
+// (separate multiply and add, as on the CPU), then + coef * sh[t][j].
+__global__ void __launch_bounds__(256)
+combine_kernel(const float* __restrict__ hrow, const int32_t* __restrict__ pos, const float* __restrict__ wts, int k,
+               int e, const float* __restrict__ sh, const float* __restrict__ shcoef, float* __restrict__ out) {
+    const int t = blockIdx.x;
+    __shared__ int32_t prow[32];
+    __shared__ float pw[32];
+    if (threadIdx.x < k) {
+        prow[threadIdx.x] = pos[(size_t)t * k + threadIdx.x];
+        pw[threadIdx.x] = wts[(size_t)t * k + threadIdx.x];
+    }
+    __syncthreads();
+    for (int j = threadIdx.x; j < e; j += 256) {
+        float acc = 0.f;
+        for (int s = 0; s < k; ++s) acc = __fadd_rn(acc, __fmul_rn(pw[s], hrow[(size_t)prow[s] * e + j]));
+        if (sh) {
+            const float v = sh[(size_t)t * e + j];
+            acc = __fadd_rn(acc, shcoef ? __fmul_rn(v, shcoef[t]) : v);
+        }
+        out[(size_t)t * e + j] = acc;
+    }
+}
+
+int launch_combine(dnb_ctx* c, cudaStream_t st, const float* hrow, const int32_t* pos, const float* wts, int nt,
+                   int k, int e, const float* sh, const float* shcoef, float* out) {
+    ProfScope prof_(c, st, "combine");
+    combine_kernel<<<nt, 256, 0, st>>>(hrow, pos, wts, k, e, sh, shcoef, out);
+    c->launches++;
+    DNB_CUDA(cudaGetLastError());
+    return DNB_OK;
+}
+
+// coef[t] = sigmoid(row . x_t)   (hyper.rs:112-114; qwen4exp.rs:12388-12395)
+__global__ void __launch_bounds__(128)
+shared_coef_kernel(const float* __restrict__ x, const float* __restrict__ row, int nt, int e, float* __restrict__ coef) {
+    const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (t >= nt) return;
+    float acc = 0.f;
+    for (int i = lane; i < e; i += 32) acc = fmaf(row[i], x[(size_t)t * e + i], acc);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) coef[t] = 1.0f / (1.0f + expf(-acc));
+}
+
+int launch_shared_coef(dnb_ctx* c, cudaStream_t st, const float* x, const float* row, int nt, int e, float* coef) {
+    ProfScope prof_(c, st, "shared_coef");
+    shared_coef_kernel<<<(nt + 3) / 4, 128, 0, st>>>(x, row, nt, e, coef);
+    c->launches++;
+    DNB_CUDA(cudaGetLastError());
+    return DNB_OK;
+}
+
+// residual: h += delta
+__global__ void add_inplace_kernel(float* __restrict__ h, const float* __restrict__ d, size_t n) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) h[i] = __fadd_rn(h[i], d[i]);
+}
+
+int launch_add_inplace(dnb_ctx* c, cudaStream_t st, float* h, const float* d, size_t n) {
+    ProfScope prof_(c, st, "residual_add");
+    add_inplace_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(h, d, n);
+    c->launches++;
+    DNB_CUDA(cudaGetLastError());
+    return DNB_OK;
+}
+
+}  // namespace dnb

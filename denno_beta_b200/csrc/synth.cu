@@ -1,0 +1,67 @@
+// Device-side fills from the seeded generator of dnb_synth.h, so that expert
+// tables of tens of GB can be created in HBM without staging through the host.
+#include "dnb_common.cuh"
+#include "dnb_synth.h"
+
+namespace dnb {
+
+__global__ void synth_payload_kernel(uint64_t key, uint64_t* dst, uint64_t n_words) {
+    const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n_words) dst[i] = dnb_synth_draw(key, i);
+}
+
+__global__ void synth_tail_kernel(uint64_t key, uint8_t* dst, uint64_t first, uint64_t bytes) {
+    const uint64_t j = first + threadIdx.x;
+    if (j < bytes) dst[j] = dnb_synth_byte(key, j);
+}
+
+__global__ void synth_fix_kernel(int type, uint64_t key, uint8_t* dst, uint64_t n_blocks, int ts) {
+    const uint64_t b = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (b < n_blocks) dnb_synth_fix_block(type, key, b, dst + b * ts);
+}
+
+__global__ void synth_normal_kernel(uint64_t key, float sigma, float* dst, uint64_t n) {
+    const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) dst[i] = (float)(dnb_synth_normal(key, i) * (double)sigma);
+}
+
+__global__ void fill_u32_kernel(uint32_t* dst, uint32_t v, size_t n) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) dst[i] = v;
+}
+
+int launch_synth_blocks(dnb_ctx* c, cudaStream_t st, int type, uint64_t seed, uint64_t tensor_id, uint8_t* dst,
+                        uint64_t n_blocks) {
+    const int ts = dnb_synth_type_size(type);
+    if (ts == 0 || ((uintptr_t)dst & 7)) {
+        set_error("synth: unsupported type %d or unaligned destination", type);
+        return DNB_ERR_ARG;
+    }
+    const uint64_t key = dnb_synth_key(seed, tensor_id);
+    const uint64_t bytes = n_blocks * (uint64_t)ts;
+    const uint64_t words = bytes / 8;
+    if (words) synth_payload_kernel<<<(unsigned)((words + 255) / 256), 256, 0, st>>>(key, (uint64_t*)dst, words);
+    if (bytes % 8) synth_tail_kernel<<<1, 8, 0, st>>>(key, dst, words * 8, bytes);
+    synth_fix_kernel<<<(unsigned)((n_blocks + 255) / 256), 256, 0, st>>>(type, key, dst, n_blocks, ts);
+    c->launches += 2;
+    DNB_CUDA(cudaGetLastError());
+    return DNB_OK;
+}
+
+int launch_synth_normal(dnb_ctx* c, cudaStream_t st, uint64_t seed, uint64_t tensor_id, float sigma, float* dst,
+                        uint64_t n) {
+    const uint64_t key = dnb_synth_key(seed, tensor_id);
+    synth_normal_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(key, sigma, dst, n);
+    c->launches++;
+    DNB_CUDA(cudaGetLastError());
+    return DNB_OK;
+}
+
+int launch_fill_u32(dnb_ctx* c, cudaStream_t st, uint32_t* dst, uint32_t v, size_t n) {
+    fill_u32_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(dst, v, n);
+    c->launches++;
+    DNB_CUDA(cudaGetLastError());
+    return DNB_OK;
+}
+
+}  // namespace dnb

@@ -1,0 +1,266 @@
+"""Host-side mirror of denno-engine's GPU dispatch interface for the MoE expert path.
+
+The functions keep the names, argument meaning and error behaviour of the `pub fn`s
+of crates/denno-engine/src/cuda.rs that model/qwen4exp.rs and model/linear_gguf.rs
+call on this path; each forwards to one C-ABI entry point of libdnb200.  As in the
+reference a `False` return means "the GPU did not run this, nothing was written,
+take your own route" and misuse raises.  There is no CPU fallback in here.
+"""
+import ctypes as C
+
+import numpy as np
+
+from . import _lib
+from ._lib import DnbError, check
+
+# ggml type ids (kquant.rs:72-104)
+Q5_1, Q8_0, Q4_K, Q5_K, Q6_K, IQ3_XXS = 7, 8, 12, 13, 14, 18
+GATE, UP, DOWN, SHARED_GATE, SHARED_UP, SHARED_DOWN = range(6)
+
+TYPE_SIZE = {Q5_1: 24, Q8_0: 34, Q4_K: 144, Q5_K: 176, Q6_K: 210, IQ3_XXS: 98}
+BLOCK_ELEMS = {Q5_1: 32, Q8_0: 32, Q4_K: 256, Q5_K: 256, Q6_K: 256, IQ3_XXS: 256}
+
+
+def row_bytes(ty, n_in):
+    """moe_expert.rs:84-100."""
+    if ty not in TYPE_SIZE or n_in <= 0 or n_in % BLOCK_ELEMS[ty]:
+        raise ValueError("n_in=%d is not a whole number of blocks of ggml type %d" % (n_in, ty))
+    return n_in // BLOCK_ELEMS[ty] * TYPE_SIZE[ty]
+
+
+def _p(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def _f32(a, shape=None):
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    return a if shape is None else a.reshape(shape)
+
+
+_shared = {}
+
+
+def cuda_enabled():
+    """cuda.rs:18029-18044: True when a context on device 0 can be made."""
+    try:
+        shared_ctx()
+        return True
+    except (DnbError, ImportError, OSError):
+        return False
+
+
+def shared_ctx(device=0):
+    """cuda.rs:18066-18082: the lazily created per-device context."""
+    if device not in _shared:
+        _shared[device] = CudaCtx(device)
+    return _shared[device]
+
+
+class CudaCtx:
+    """One device + one stream (cuda.rs CudaCtx).  Not re-entrant."""
+
+    def __init__(self, device=0):
+        self.lib = _lib.load()
+        h = C.c_void_p()
+        check(self.lib.dnb_init(device, C.byref(h)))
+        self.h = h
+        self.device = device
+        self.model = None
+
+    def close(self):
+        if self.h:
+            self.lib.dnb_shutdown(self.h)
+            self.h = None
+
+    # -- plumbing -------------------------------------------------------------
+    def set_stream(self, cuda_stream):
+        check(self.lib.dnb_set_stream(self.h, C.c_void_p(cuda_stream) if cuda_stream else None))
+
+    def sync(self):
+        check(self.lib.dnb_sync(self.h))
+
+    def launch_count(self):
+        return int(self.lib.dnb_launch_count(self.h))
+
+    def timer_start(self):
+        check(self.lib.dnb_timer_start(self.h))
+
+    def timer_stop(self):
+        ms = C.c_float()
+        check(self.lib.dnb_timer_stop(self.h, C.byref(ms)))
+        return ms.value
+
+    def profile(self, on):
+        check(self.lib.dnb_profile_enable(self.h, int(on)))
+
+    def profile_read(self):
+        import json
+        buf = C.create_string_buffer(16384)
+        check(self.lib.dnb_profile_read(self.h, buf, len(buf)))
+        return json.loads(buf.value.decode())
+
+    def flush_l2(self):
+        check(self.lib.dnb_flush_l2(self.h))
+
+    def dev_alloc(self, nbytes):
+        p = C.c_void_p()
+        check(self.lib.dnb_dev_alloc(self.h, nbytes, C.byref(p)))
+        return p.value
+
+    def dev_free(self, ptr):
+        check(self.lib.dnb_dev_free(self.h, C.c_void_p(ptr)))
+
+    def upload(self, ptr, arr):
+        arr = np.ascontiguousarray(arr)
+        check(self.lib.dnb_dev_upload(self.h, C.c_void_p(ptr), _p(arr), arr.nbytes))
+
+    def download(self, ptr, arr):
+        check(self.lib.dnb_dev_download(self.h, _p(arr), C.c_void_p(ptr), arr.nbytes))
+        return arr
+
+    # -- GEMV_V3 path -----------------------------------------------------------
+    def register_matrix(self, uid, ty, blocks, k, n):
+        blocks = np.ascontiguousarray(blocks, dtype=np.uint8)
+        return check(self.lib.dnb_register_matrix(self.h, uid, ty, _p(blocks), blocks.nbytes, k, n), True)
+
+    def gemv(self, uid, x, out):
+        return check(self.lib.dnb_gemv(self.h, uid, _p(x), _p(out)), True)
+
+    def gemv_dev(self, ty, w_ptr, k, n, x_ptr, out_ptr, nvec=1):
+        return check(self.lib.dnb_gemv_dev(self.h, ty, C.c_void_p(w_ptr), k, n, C.c_void_p(x_ptr), C.c_void_p(out_ptr),
+                                           nvec), True)
+
+    def set_gemv_impl(self, impl):
+        check(self.lib.dnb_set_gemv_impl(self.h, impl))
+
+    # -- MoE model ----------------------------------------------------------------
+    def moe_config(self, n_layer, n_embd, n_ff, n_expert, n_expert_used, n_shared_ff=0, rms_eps=1e-6,
+                   norm_topk_prob=True):
+        ok = check(self.lib.dnb_moe_config(self.h, n_layer, n_embd, n_ff, n_shared_ff, n_expert, n_expert_used,
+                                           C.c_float(rms_eps), int(norm_topk_prob)), True)
+        if ok:
+            self.model = dict(n_layer=n_layer, e=n_embd, ff=n_ff, ne=n_expert, k=n_expert_used,
+                              sff=n_shared_ff or n_ff)
+        return ok
+
+    def register_experts(self, layer, matrix, ty, n_in, n_out, n_expert, blocks):
+        blocks = np.ascontiguousarray(blocks, dtype=np.uint8)
+        return check(self.lib.dnb_register_experts(self.h, layer, matrix, ty, n_in, n_out, n_expert, _p(blocks),
+                                                   blocks.nbytes), True)
+
+    def synth_experts(self, layer, matrix, ty, n_in, n_out, n_expert, seed):
+        return check(self.lib.dnb_synth_experts(self.h, layer, matrix, ty, n_in, n_out, n_expert, seed), True)
+
+    def download_expert(self, layer, matrix, expert, nbytes):
+        out = np.empty(nbytes, np.uint8)
+        check(self.lib.dnb_download_expert(self.h, layer, matrix, expert, _p(out), nbytes))
+        return out
+
+    def register_router(self, layer, w, bias=None, norm_w=None, shared_gate_row=None):
+        w = _f32(w)
+        bias = None if bias is None else _f32(bias)
+        norm_w = None if norm_w is None else _f32(norm_w)
+        sgr = None if shared_gate_row is None else _f32(shared_gate_row)
+        assert w.size == self.model["ne"] * self.model["e"]
+        check(self.lib.dnb_register_router(self.h, layer, _p(w), _p(bias), _p(norm_w), _p(sgr)))
+
+    # -- MoE block ------------------------------------------------------------------
+    def moe_block(self, layer, h, want_routing=False):
+        """Host in, host out.  Returns out[nt,e] (and sels, wts) or None when declined."""
+        e, k = self.model["e"], self.model["k"]
+        h = _f32(h, (-1, e))
+        nt = h.shape[0]
+        out = np.empty((nt, e), np.float32)
+        sels = np.empty((nt, k), np.int32) if want_routing else None
+        wts = np.empty((nt, k), np.float32) if want_routing else None
+        if not check(self.lib.dnb_moe_block(self.h, layer, _p(h), nt, _p(out), _p(sels), _p(wts)), True):
+            return None
+        return (out, sels, wts) if want_routing else out
+
+    def moe_block_into(self, layer, h, out):
+        """The allocation-free form used in timed loops (h, out: contiguous fp32 arrays)."""
+        return check(self.lib.dnb_moe_block(self.h, layer, _p(h), h.shape[0], _p(out), None, None), True)
+
+    def moe_block_dev(self, layer, h_ptr, nt, out_ptr):
+        return check(self.lib.dnb_moe_block_dev(self.h, layer, C.c_void_p(h_ptr), nt, C.c_void_p(out_ptr)), True)
+
+    def moe_experts(self, layer, x, sels, wts):
+        e = self.model["e"]
+        x = _f32(x, (-1, e))
+        sels = np.ascontiguousarray(sels, np.int32)
+        wts = _f32(wts)
+        out = np.empty_like(x)
+        if not check(self.lib.dnb_moe_experts(self.h, layer, _p(x), x.shape[0], _p(sels), _p(wts), _p(out)), True):
+            return None
+        return out
+
+    def router_topk(self, layer, x):
+        e, k = self.model["e"], self.model["k"]
+        x = _f32(x, (-1, e))
+        nt = x.shape[0]
+        sels = np.empty((nt, k), np.int32)
+        wts = np.empty((nt, k), np.float32)
+        rowsum = np.empty(nt, np.float32)
+        if not check(self.lib.dnb_router_topk(self.h, layer, _p(x), nt, _p(sels), _p(wts), _p(rowsum)), True):
+            return None
+        return sels, wts, rowsum
+
+    def grouped_gemm(self, layer, matrix, segs, xs, n_out):
+        segs = np.ascontiguousarray(segs, np.uint32)
+        xs = _f32(xs)
+        m_total = int(segs[:, 1].sum())
+        outs = np.empty((m_total, n_out), np.float32)
+        if not check(self.lib.dnb_grouped_gemm(self.h, layer, matrix, _p(segs), segs.shape[0], _p(xs), _p(outs)), True):
+            return None
+        return outs
+
+    def moe_stack(self, h):
+        e = self.model["e"]
+        h = _f32(h, (-1, e))
+        out = np.empty_like(h)
+        if not check(self.lib.dnb_moe_stack(self.h, _p(h), h.shape[0], _p(out)), True):
+            return None
+        return out
+
+    def moe_stack_dev(self, h_ptr, nt):
+        return check(self.lib.dnb_moe_stack_dev(self.h, C.c_void_p(h_ptr), nt), True)
+
+
+# ---- free functions with the reference's names ----------------------------------
+
+_registered = {}
+
+
+def maybe_gpu_gguf_gemv_into(uid, ty, blocks, k, n, x, out):
+    """cuda.rs:21028-21036.  Weights go resident on first use of `uid`; out[n] is
+    written only when True is returned."""
+    x = _f32(x)
+    if x.size != k or out.size != n or out.dtype != np.float32:
+        raise ValueError("gemv: x has %d elements (k=%d), out %d (n=%d)" % (x.size, k, out.size, n))
+    ctx = shared_ctx()
+    key = (ctx.device, uid)
+    if key not in _registered:
+        if ty not in TYPE_SIZE or k % BLOCK_ELEMS[ty]:
+            return False
+        if not ctx.register_matrix(uid, ty, blocks, k, n):
+            return False
+        _registered[key] = (ty, k, n)
+    elif _registered[key] != (ty, k, n):
+        raise ValueError("gemv: uid %d was registered as %r" % (uid, _registered[key]))
+    return ctx.gemv(uid, x, out)
+
+
+def pf_router_dev_topk(ctx, layer, xs):
+    """cuda.rs:48695-48708: (sels, wts, rowsum) for nt rows, or None."""
+    return ctx.router_topk(layer, xs)
+
+
+def moe_seg_layer_sum(ctx, layer, sels, w, x):
+    """cuda.rs:8088-8107: selected experts of one layer for one token (or nt tokens),
+    weighted sum in ascending expert order, shared expert added.  None = declined."""
+    return ctx.moe_experts(layer, x, sels, w)
+
+
+def moe_grouped_gemm_layer(ctx, layer, matrix, segs, xs, n_out):
+    """cuda.rs:7065-7075 on one matrix: per-segment expert GEMM on packed rows."""
+    return ctx.grouped_gemm(layer, matrix, segs, xs, n_out)

@@ -1,0 +1,164 @@
+/* dnb200 -- B200 (sm_100a) implementation of denno-beta's quantised MoE expert
+ * matmul path, behind a C ABI.
+ *
+ * Every entry point replaces one `pub fn` of denno-engine's GPU dispatch module
+ * (crates/denno-engine/src/cuda.rs) or one piece of state it keeps; the reference
+ * line is cited at each declaration.  Conventions kept from the reference
+ * (cuda.rs:21024-21027, 8120-8126, 8785-8788):
+ *
+ *   return  0  DNB_OK        the GPU computed the result
+ *   return  1  DNB_DECLINED  the call did not run and wrote nothing; the caller may
+ *                            take its own CPU route (unknown block type, shape the
+ *                            kernels do not cover, layer not registered)
+ *   return <0  misuse or a CUDA failure; dnb_last_error() has the text
+ *
+ * Host slices are borrowed for the duration of the call only.  Device memory is
+ * owned by the library.  One context drives one device through one stream and is
+ * not re-entrant; use one context per GPU.  The same inputs give the same bits on
+ * every run (no order-dependent atomics anywhere).
+ *
+ * There is no CPU fallback inside the library: without a CUDA device dnb_init
+ * fails with DNB_ERR_NO_DEVICE.
+ */
+#ifndef DNB200_H
+#define DNB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DNB_OK 0
+#define DNB_DECLINED 1
+#define DNB_ERR_ARG (-1)
+#define DNB_ERR_CUDA (-2)
+#define DNB_ERR_NO_DEVICE (-3)
+#define DNB_ERR_STATE (-4)
+
+/* ggml type ids (kquant.rs:72-104) of the block formats the kernels decode. */
+#define DNB_GGML_Q5_1 7
+#define DNB_GGML_Q8_0 8
+#define DNB_GGML_Q4_K 12
+#define DNB_GGML_Q5_K 13
+#define DNB_GGML_Q6_K 14
+#define DNB_GGML_IQ3_XXS 18
+
+/* matrix slots of a MoE layer */
+#define DNB_MAT_GATE 0
+#define DNB_MAT_UP 1
+#define DNB_MAT_DOWN 2
+#define DNB_MAT_SHARED_GATE 3
+#define DNB_MAT_SHARED_UP 4
+#define DNB_MAT_SHARED_DOWN 5
+
+typedef struct dnb_ctx dnb_ctx;
+
+/* ---- context ----------------------------------------------------------------
+ * cuda.rs:18029-18103 (cuda_enabled / shared_ctx / make_current_on_this_thread). */
+int dnb_init(int device, dnb_ctx** out);
+void dnb_shutdown(dnb_ctx* ctx);
+const char* dnb_last_error(void);
+/* Run on a stream the caller owns (e.g. the framework's current stream) instead
+ * of the context's own; pass NULL to go back.  cuda.rs:100-111 (stream set-up). */
+int dnb_set_stream(dnb_ctx* ctx, void* cuda_stream);
+int dnb_sync(dnb_ctx* ctx);
+/* Kernels launched by this context since creation. */
+uint64_t dnb_launch_count(dnb_ctx* ctx);
+/* Device-side timing on the context's stream: start, ... calls ..., stop -> ms. */
+int dnb_timer_start(dnb_ctx* ctx);
+int dnb_timer_stop(dnb_ctx* ctx, float* ms);
+/* Per-kernel device timing for benchmarks (the reference's DENNO_SEG_PROF,
+ * model/seg_prof.rs:1-22, cuda.rs:8417-8432): while enabled, every kernel launch is
+ * bracketed by events; dnb_profile_read writes a JSON object
+ * {"kernel": {"launches": n, "ms": total}, ...} into buf.  Enabling clears it. */
+int dnb_profile_enable(dnb_ctx* ctx, int on);
+int dnb_profile_read(dnb_ctx* ctx, char* buf, size_t cap);
+/* Device memory helpers for callers that keep activations on the GPU. */
+int dnb_dev_alloc(dnb_ctx* ctx, size_t bytes, void** dev);
+int dnb_dev_free(dnb_ctx* ctx, void* dev);
+int dnb_dev_upload(dnb_ctx* ctx, void* dev, const void* host, size_t bytes);
+int dnb_dev_download(dnb_ctx* ctx, void* host, const void* dev, size_t bytes);
+/* Overwrite `bytes` of device scratch larger than L2 (benchmark hygiene). */
+int dnb_flush_l2(dnb_ctx* ctx);
+
+/* ---- single resident matrix: the GEMV_V3 path ---------------------------------
+ * cuda.rs:21028-21111 (maybe_gpu_gguf_gemv_into): weights are uploaded once per
+ * `uid` and stay resident (weights_for_gguf); the call copies x in, runs one
+ * dequant-GEMV and copies out back.  out[r] = sum_i dequant(W)[r][i] * x[i]. */
+int dnb_register_matrix(dnb_ctx* ctx, uint64_t uid, int ggml_type, const void* blocks, size_t bytes, int k, int n);
+int dnb_gemv(dnb_ctx* ctx, uint64_t uid, const float* x, float* out);
+/* The same kernel on device pointers: nvec activation vectors x[v][k] -> out[v][n]
+ * (kernels_moe_v3.cu:216-266 is the reference kernel of this shape). */
+int dnb_gemv_dev(dnb_ctx* ctx, int ggml_type, const void* w_dev, int k, int n, const float* x_dev, float* out_dev,
+                 int nvec);
+/* 0: fast lane-split kernels (default).  1: the sequential-order kernel whose fp32
+ * results equal the CPU scalar path bit for bit (kernels_moe.cu contract,
+ * cuda.rs:44991-45057). */
+int dnb_set_gemv_impl(dnb_ctx* ctx, int impl);
+
+/* ---- MoE model: resident expert table ----------------------------------------
+ * Replaces the VRAM/RAM/SSD expert tiers (expert_vram.rs:1-60; use at
+ * qwen4exp.rs:12600-12629): every expert of every layer is resident. */
+int dnb_moe_config(dnb_ctx* ctx, int n_layer, int n_embd, int n_ff, int n_shared_ff, int n_expert, int n_expert_used,
+                   float rms_eps, int norm_topk_prob);
+/* One expert tensor, expert-major as in GGUF (moe_expert.rs:49-82 ExpertSlice):
+ * expert i occupies bytes [i*n_out*row_bytes, (i+1)*n_out*row_bytes).  `blocks`
+ * is a host pointer, copied. */
+int dnb_register_experts(dnb_ctx* ctx, int layer, int matrix, int ggml_type, int n_in, int n_out, int n_expert,
+                         const void* blocks, size_t bytes);
+/* Router row matrix ffn_gate_inp [n_expert][n_embd] fp32 (linear_gguf.rs:836-964),
+ * optional per-expert logit bias (moe.rs:327-338), optional RMSNorm weight applied
+ * to the block input (tensor.rs:1125-1135), optional shared-expert gate row
+ * ffn_gate_inp_shexp (qwen4exp.rs:12388-12395; NULL = coefficient 1.0 as in
+ * moe.rs:386-403).  Host pointers, copied. */
+int dnb_register_router(dnb_ctx* ctx, int layer, const float* w, const float* bias, const float* norm_w,
+                        const float* shared_gate_row);
+/* Fill one expert tensor in place on the device from the seeded generator of
+ * dnb_synth.h (tensor id = layer*16 + matrix).  For benchmarks whose expert table
+ * is too large to stage through the host. */
+int dnb_synth_experts(dnb_ctx* ctx, int layer, int matrix, int ggml_type, int n_in, int n_out, int n_expert,
+                      uint64_t seed);
+/* Copy expert `expert` of a registered tensor back to the host (parity checks). */
+int dnb_download_expert(dnb_ctx* ctx, int layer, int matrix, int expert, void* dst, size_t bytes);
+
+/* ---- MoE block -----------------------------------------------------------------
+ * One sparse-MoE block for nt tokens: (RMSNorm) -> router -> softmax -> top-k ->
+ * renorm -> routed experts (gate/up GEMV, SwiGLU, down GEMV) -> weighted sum in
+ * ascending expert index -> + shared expert.
+ *   decode : qwen4exp.rs:11659 moe_ffn_quant_impl -> cuda.rs:8088 moe_seg_layer_sum
+ *            / cuda.rs:8825 moe_experts_iq_layer_sum_overlap
+ *   prefill: qwen4exp.rs:17921 moe_ffn_quant_batch_full -> cuda.rs:48695
+ *            pf_router_dev_topk + cuda.rs:10919 moe_experts_iq_pf_layer /
+ *            cuda.rs:7065 moe_grouped_gemm_layer + moe_grouped_gpu.rs:540 scatter
+ * h, out: host [nt][n_embd].  sels_out [nt][k] / wts_out [nt][k] may be NULL. */
+int dnb_moe_block(dnb_ctx* ctx, int layer, const float* h, int nt, float* out, int32_t* sels_out, float* wts_out);
+/* Same with device pointers; nothing is copied and the call does not synchronise. */
+int dnb_moe_block_dev(dnb_ctx* ctx, int layer, const float* h_dev, int nt, float* out_dev);
+/* The routed-expert half only, with the selection given by the caller
+ * (cuda.rs:8088-8107 moe_seg_layer_sum: sels ascending, routing weights w):
+ * out[t] = sum_s w[t][s] * down(silu(gate x_t) * up x_t) (+ shared expert).
+ * x is the expert input (already normalised), host [nt][n_embd]. */
+int dnb_moe_experts(dnb_ctx* ctx, int layer, const float* x, int nt, const int32_t* sels, const float* wts,
+                    float* out);
+/* Router only (cuda.rs:48695-48708 pf_router_dev_topk): logits = W_r x + bias,
+ * softmax, top-k (ties to the lower index, output ascending), renorm.
+ * x host [nt][n_embd]; sels [nt][k], wts [nt][k], rowsum [nt] (sum of the selected
+ * probabilities before renorm; may be NULL). */
+int dnb_router_topk(dnb_ctx* ctx, int layer, const float* x, int nt, int32_t* sels, float* wts, float* rowsum);
+/* Grouped per-expert GEMM on packed rows (cuda.rs:7065-7075 moe_grouped_gemm_layer,
+ * moe_expert.rs:8455 grouped_expert_gemm_cpu): segs[nseg][4] = (expert, m, x_off,
+ * out_off) with offsets in rows; xs host [m_total][n_in]; outs host
+ * [m_total][n_out]. */
+int dnb_grouped_gemm(dnb_ctx* ctx, int layer, int matrix, const uint32_t* segs, int nseg, const float* xs,
+                     float* outs);
+/* A stack of the configured layers with identity mixers: h <- h + block_l(h) for
+ * l = 0..n_layer-1 (device-resident between layers).  h host [nt][n_embd] in/out. */
+int dnb_moe_stack(dnb_ctx* ctx, const float* h, int nt, float* out);
+int dnb_moe_stack_dev(dnb_ctx* ctx, float* h_dev, int nt);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DNB200_H */

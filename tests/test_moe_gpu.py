@@ -1,0 +1,202 @@
+"""GPU parity of the MoE block (decode and chunked prefill) against the CPU oracle."""
+import numpy as np
+import pytest
+
+from helpers import SEED, check_block, make_layer, rel_err
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def small(orc):
+    """A small model with both headline formats: layer 0 IQ3_XXS, layer 1 Q4_K (Zipf bias,
+    shared-expert gate row), layer 2 Q6_K experts with a Q8_0 down projection."""
+    from denno_beta_b200 import cuda as cu
+
+    c = cu.CudaCtx(0)
+    e, ff, ne, k = 512, 256, 32, 4
+    assert c.moe_config(3, e, ff, ne, k)
+    layers = [
+        make_layer(orc, c, 0, orc.IQ3_XXS, e, ff, ne, k),
+        make_layer(orc, c, 1, orc.Q4_K, e, ff, ne, k, bias=True, gate_row=True),
+        make_layer(orc, c, 2, orc.Q6_K, e, ff, ne, k, ty_down=orc.Q8_0, shared=False),
+    ]
+    yield c, layers
+    c.close()
+
+
+@pytest.mark.parametrize("layer", [0, 1, 2])
+@pytest.mark.parametrize("nt", [1, 2, 3, 5, 8, 33])
+def test_block_small(orc, small, layer, nt):
+    c, layers = small
+    L = layers[layer]
+    h = orc.synth_normal(SEED, 900 + nt, 1.0, nt * L.e).reshape(nt, L.e)
+    out, sels, wts = c.moe_block(layer, h, want_routing=True)
+    err, redo = check_block(orc, L, h, out, sels, wts)
+    assert err <= 1e-3, "layer %d nt %d: %.3g" % (layer, nt, err)
+    assert redo == 0
+    out2 = c.moe_block(layer, h)
+    assert np.array_equal(out.view(np.uint32), out2.view(np.uint32)), "not bit-identical run to run"
+
+
+def test_batch_equals_token_by_token(orc, small):
+    """qwen4exp.rs:28259 (batch prefill == sequential): every token of a chunk gets the
+    bits it gets when it is run alone."""
+    c, layers = small
+    nt = 21
+    for layer in (0, 1):
+        h = orc.synth_normal(SEED, 950 + layer, 1.0, nt * layers[layer].e).reshape(nt, -1)
+        batch = c.moe_block(layer, h)
+        for t in (0, 7, 20):
+            one = c.moe_block(layer, h[t:t + 1])
+            assert np.array_equal(batch[t].view(np.uint32), one[0].view(np.uint32))
+
+
+def test_experts_with_given_selection(orc, small):
+    """cuda.rs:8088 moe_seg_layer_sum: selection and weights supplied by the caller."""
+    from denno_beta_b200 import _lib, cuda as cu
+
+    c, layers = small
+    L = layers[1]
+    nt = 4
+    x = orc.synth_normal(SEED, 970, 1.0, nt * L.e).reshape(nt, L.e)
+    sels = np.array([[0, 1, 2, 3], [5, 9, 17, 31], [0, 10, 20, 30], [28, 29, 30, 31]], np.int32)
+    wts = np.abs(orc.synth_normal(SEED, 971, 1.0, nt * L.k)).reshape(nt, L.k).astype(np.float32)
+    got = cu.moe_seg_layer_sum(c, 1, sels, wts, x)
+    want = orc.moe_experts_given(L, x, sels, wts)
+    assert rel_err(got, want) <= 1e-3
+    with pytest.raises(_lib.DnbError):  # not ascending: misuse (cuda.rs:8120-8126 returns Err)
+        c.moe_experts(1, x, sels[:, ::-1], wts)
+
+
+def test_router_topk(orc, small):
+    from denno_beta_b200 import cuda as cu
+
+    c, layers = small
+    L = layers[1]
+    nt = 64
+    x = orc.synth_normal(SEED, 980, 1.0, nt * L.e).reshape(nt, L.e)
+    sels, wts, rowsum = cu.pf_router_dev_topk(c, 1, x)
+    osels, owts, probs = orc.router(x, L.keep["router_w"], L.keep["router_bias"], L.k)
+    assert np.array_equal(sels, osels)
+    assert np.all(np.diff(sels, axis=1) > 0)
+    assert np.max(np.abs(wts - owts)) < 2e-6
+    want_rowsum = np.take_along_axis(probs, osels, 1).sum(1)
+    assert np.max(np.abs(rowsum - want_rowsum)) < 2e-6
+
+
+def test_grouped_gemm(orc, small):
+    from denno_beta_b200 import _lib, cuda as cu
+
+    c, layers = small
+    L = layers[1]
+    segs = np.array([[3, 9, 0, 0], [0, 4, 9, 9], [31, 1, 13, 13], [7, 2, 14, 14]], np.uint32)
+    m_total = 16
+    xs = orc.synth_normal(SEED, 990, 1.0, m_total * L.e).reshape(m_total, L.e)
+    got = cu.moe_grouped_gemm_layer(c, 1, cu.GATE, segs, xs, L.ff)
+    want = orc.grouped_gemm(orc.Q4_K, L.keep["gate"], L.e, L.ff, segs, xs)
+    assert rel_err(got, want) <= 2e-5
+    bad = segs.copy()
+    bad[2, 2] = 12  # gap in x_off: moe_expert.rs:8399-8440 check_segments rejects it
+    with pytest.raises(_lib.DnbError):
+        c.grouped_gemm(1, cu.GATE, bad, xs, L.ff)
+
+
+@pytest.fixture(scope="module")
+def config1(orc):
+    """BASELINE config 1 at full size: e 2048, ff 512, 512 experts, top-10 + shared, IQ3_XXS."""
+    from denno_beta_b200 import cuda as cu
+
+    c = cu.CudaCtx(0)
+    assert c.moe_config(1, 2048, 512, 512, 10)
+    L = make_layer(orc, c, 0, orc.IQ3_XXS, 2048, 512, 512, 10)
+    yield c, L
+    c.close()
+
+
+def test_config1_decode(orc, config1):
+    c, L = config1
+    h = orc.synth_normal(SEED, 2000, 1.0, 2048)
+    out, sels, wts = c.moe_block(0, h, want_routing=True)
+    err, redo = check_block(orc, L, h.reshape(1, -1), out, sels, wts)
+    assert err <= 1e-3 and redo == 0
+    out2 = c.moe_block(0, h)
+    assert np.array_equal(out.view(np.uint32), out2.view(np.uint32))
+
+
+def test_config1_batches(orc, config1):
+    c, L = config1
+    for nt in (8, 32):
+        h = orc.synth_normal(SEED, 2100 + nt, 1.0, nt * 2048).reshape(nt, 2048)
+        out, sels, wts = c.moe_block(0, h, want_routing=True)
+        idx = [0, nt // 2, nt - 1]
+        err, _ = check_block(orc, L, h[idx], out[idx], sels[idx], wts[idx])
+        assert err <= 1e-3
+
+
+@pytest.fixture(scope="module")
+def config2(orc):
+    """BASELINE config 2 at full size: the same block with Q4_K experts and a Zipf router bias."""
+    from denno_beta_b200 import cuda as cu
+
+    c = cu.CudaCtx(0)
+    assert c.moe_config(1, 2048, 512, 512, 10)
+    L = make_layer(orc, c, 0, orc.Q4_K, 2048, 512, 512, 10, bias=True)
+    yield c, L
+    c.close()
+
+
+def test_config2_prefill_chunk(orc, config2):
+    c, L = config2
+    nt = 512
+    h = orc.synth_normal(SEED, 3000, 1.0, nt * 2048).reshape(nt, 2048)
+    out, sels, wts = c.moe_block(0, h, want_routing=True)
+    # Zipf skew: some experts see > 100 tokens, most see 0-2
+    counts = np.bincount(sels.ravel(), minlength=512)
+    assert counts.max() > 100 and np.median(counts) <= 2
+    # oracle on a sample of tokens (each token's result is independent of the others)
+    idx = np.array([0, 1, 17, 100, 255, 256, 300, 511])
+    err, redo = check_block(orc, L, h[idx], out[idx], sels[idx], wts[idx])
+    assert err <= 1e-3, err
+    # routing of the whole chunk against the oracle's router
+    x = orc.rmsnorm(h, np.ones(2048, np.float32))
+    osels, _, _ = orc.router(x, L.keep["router_w"], L.keep["router_bias"], 10)
+    assert np.mean(np.any(osels != sels, axis=1)) <= 0.01
+    # chunk == token by token, bit for bit
+    for t in (3, 200, 511):
+        one = c.moe_block(0, h[t:t + 1])
+        assert np.array_equal(out[t].view(np.uint32), one[0].view(np.uint32))
+    # ragged tail chunk (14,018 = 27 x 512 + 194)
+    out194 = c.moe_block(0, h[:194])
+    assert np.array_equal(out194.view(np.uint32), out[:194].view(np.uint32))
+
+
+def test_stack_residual(orc, small):
+    """identity mixers: h <- h + block_l(h), layers in order, device-resident in between."""
+    c, layers = small
+    nt = 3
+    h = orc.synth_normal(SEED, 4000, 1.0, nt * 512).reshape(nt, 512)
+    got = c.moe_stack(h)
+    ref = h.copy()
+    for L in layers:
+        o, _, _ = orc.moe_block(L, ref)
+        ref = (ref + o).astype(np.float32)
+    assert rel_err(got, ref) <= 1e-3
+
+
+def test_synth_device_equals_host(orc, small):
+    from denno_beta_b200 import cuda as cu
+
+    c = cu.CudaCtx(0)
+    try:
+        assert c.moe_config(1, 512, 256, 8, 2)
+        for ty in (orc.Q4_K, orc.IQ3_XXS, orc.Q6_K, orc.Q8_0):
+            assert c.synth_experts(0, cu.GATE, ty, 512, 256, 8, 1234)
+            nb = 8 * 256 * 512 // orc.blck_size(ty)
+            host = orc.synth_blocks(ty, 1234, 0, nb)
+            eb = host.size // 8
+            for ex in (0, 7):
+                dev = c.download_expert(0, cu.GATE, ex, eb)
+                assert np.array_equal(dev, host[ex * eb:(ex + 1) * eb]), "type %d expert %d" % (ty, ex)
+    finally:
+        c.close()
