@@ -19,6 +19,7 @@ SIGNATURES = {
     "dnb_set_stream": (_i, [_vp, _vp]),
     "dnb_sync": (_i, [_vp]),
     "dnb_launch_count": (_u64, [_vp]),
+    "dnb_device_status": (_i, [_vp, C.POINTER(C.c_int)]),
     "dnb_timer_start": (_i, [_vp]),
     "dnb_timer_stop": (_i, [_vp, _fp]),
     "dnb_profile_enable": (_i, [_vp, _i]),

@@ -47,7 +47,7 @@ static int ensure_ws(dnb_ctx* c, int nt) {
     while (cap < nt) cap *= 2;
     DNB_CUDA(cudaDeviceSynchronize());
     free_ws(w);
-    const size_t rows = (size_t)cap * M.k;
+    const size_t rows = (size_t)cap * (M.k + 1);  // + the shared expert's row in the decode path
     const int sff = M.sff > 0 ? M.sff : M.ff;
     int rc = DNB_OK;
     if ((rc = dev_alloc(&w.xn, (size_t)cap * M.e))) return rc;
@@ -65,8 +65,8 @@ static int ensure_ws(dnb_ctx* c, int nt) {
     if ((rc = dev_alloc(&w.pos, rows))) return rc;
     if ((rc = dev_alloc(&w.nseg, 1))) return rc;
     if ((rc = dev_alloc(&w.counts, (size_t)M.ne))) return rc;
-    if ((rc = dev_alloc(&w.seg_gu, (size_t)M.ne))) return rc;
-    if ((rc = dev_alloc(&w.seg_dn, (size_t)M.ne))) return rc;
+    if ((rc = dev_alloc(&w.seg_gu, (size_t)M.ne + 1))) return rc;
+    if ((rc = dev_alloc(&w.seg_dn, (size_t)M.ne + 1))) return rc;
     if ((rc = dev_alloc(&w.seg_sh_gu, 1))) return rc;
     if ((rc = dev_alloc(&w.seg_sh_dn, 1))) return rc;
     w.pinned_cap = (size_t)cap * M.e * sizeof(float);
@@ -136,12 +136,48 @@ static int experts_dev(dnb_ctx* c, int layer, const float* x, int nt, const int3
                           (shared && L.shared_gate_row) ? w.shcoef : nullptr, out);
 }
 
+// One token: fused router kernel, gate/up and down GEMVs over the k routed experts
+// plus the shared expert as one more segment, weighted sum.  Four launches.
+// Returns DNB_DECLINED when a shape or type combination is outside this path.
+static int block_dev_decode(dnb_ctx* c, int layer, const float* h, float* out) {
+    const Model& M = c->model;
+    const Layer& L = M.layers[layer];
+    Workspace& w = c->ws;
+    cudaStream_t st = c->stream;
+    const bool shared = L.has_shared();
+    const bool fold = shared && L.m[3].type == L.m[0].type && L.m[4].type == L.m[1].type &&
+                      L.m[5].type == L.m[2].type && L.m[3].n_out == M.ff;
+    if (shared && !fold) return DNB_DECLINED;
+    if (L.m[0].type != L.m[1].type) return DNB_DECLINED;
+    int rc = launch_router_decode(c, st, h, M, L, w, fold, c->ticket);
+    if (rc) return rc;
+    const int nseg = M.k + (fold ? 1 : 0);
+    rc = launch_seg_gemv_m1(c, st, L.m[0].type, true, true, w.seg_gu, nullptr, nseg, M.e, M.ff, w.xn, M.e, nullptr, w.act,
+                            nullptr, "gemv_gate_up");
+    if (rc == DNB_DECLINED)
+        rc = launch_seg_matmul(c, st, L.m[0].type, true, w.seg_gu, nullptr, nseg, M.e, M.ff, w.xn, M.e, w.row_token, w.act, 1);
+    if (rc) return rc;
+    rc = launch_seg_gemv_m1(c, st, L.m[2].type, false, false, w.seg_dn, nullptr, nseg, M.ff, M.e, w.act, M.ff, nullptr,
+                            w.hrow, nullptr, "gemv_down");
+    if (rc == DNB_DECLINED)
+        rc = launch_seg_matmul(c, st, L.m[2].type, false, w.seg_dn, nullptr, nseg, M.ff, M.e, w.act, M.ff, nullptr, w.hrow, 1);
+    if (rc) return rc;
+    if (fold && L.shared_gate_row)
+        if ((rc = launch_shared_coef(c, st, w.xn, L.shared_gate_row, 1, M.e, w.shcoef))) return rc;
+    return launch_combine(c, st, w.hrow, w.pos, w.wts, 1, M.k, M.e, fold ? w.hrow + (size_t)M.k * M.e : nullptr,
+                          (fold && L.shared_gate_row) ? w.shcoef : nullptr, out);
+}
+
 static int block_dev(dnb_ctx* c, int layer, const float* h, int nt, float* out) {
     const Model& M = c->model;
     const Layer& L = M.layers[layer];
     Workspace& w = c->ws;
     cudaStream_t st = c->stream;
     int rc;
+    if (nt == 1 && c->decode_fast) {
+        rc = block_dev_decode(c, layer, h, out);
+        if (rc != DNB_DECLINED) return rc;
+    }
     const bool shared = L.has_shared();
     if (L.norm_w || shared) {
         if ((rc = launch_prep(c, st, h, L.norm_w, M.eps, nt, M.e, w.xn, shared ? w.seg_sh_gu : nullptr,
@@ -193,6 +229,8 @@ int dnb_init(int device, dnb_ctx** out) {
     DNB_CUDA(cudaEventCreate(&c->ev_t1));
     DNB_CUDA(cudaMalloc((void**)&c->status, sizeof(int)));
     DNB_CUDA(cudaMemset(c->status, 0, sizeof(int)));
+    DNB_CUDA(cudaMalloc((void**)&c->ticket, sizeof(unsigned int)));
+    DNB_CUDA(cudaMemset(c->ticket, 0, sizeof(unsigned int)));
     *out = c;
     return DNB_OK;
 }
@@ -217,6 +255,7 @@ void dnb_shutdown(dnb_ctx* c) {
     if (c->gemv_x.p) cudaFree(c->gemv_x.p);
     if (c->gemv_out.p) cudaFree(c->gemv_out.p);
     if (c->status) cudaFree(c->status);
+    if (c->ticket) cudaFree(c->ticket);
     if (c->own_stream && c->stream) cudaStreamDestroy(c->stream);
     if (!c->own_stream && c->saved_stream) cudaStreamDestroy(c->saved_stream);
     if (c->flush.p) cudaFree(c->flush.p);
@@ -253,6 +292,13 @@ int dnb_sync(dnb_ctx* c) {
 }
 
 uint64_t dnb_launch_count(dnb_ctx* c) { return c ? c->launches : 0; }
+
+int dnb_device_status(dnb_ctx* c, int* status) {
+    if (!c || !status) return DNB_ERR_ARG;
+    DNB_CUDA(cudaStreamSynchronize(c->stream));
+    DNB_CUDA(cudaMemcpy(status, c->status, sizeof(int), cudaMemcpyDeviceToHost));
+    return DNB_OK;
+}
 
 int dnb_timer_start(dnb_ctx* c) {
     if (!c) return DNB_ERR_ARG;
@@ -364,8 +410,9 @@ int dnb_register_matrix(dnb_ctx* c, uint64_t uid, int type, const void* blocks, 
 }
 
 int dnb_set_gemv_impl(dnb_ctx* c, int impl) {
-    if (!c || impl < 0 || impl > 1) return DNB_ERR_ARG;
-    c->gemv_impl = impl;
+    if (!c || impl < 0 || impl > 2) return DNB_ERR_ARG;
+    c->gemv_impl = impl == 1 ? 1 : 0;
+    c->decode_fast = impl != 2;
     return DNB_OK;
 }
 
@@ -378,6 +425,11 @@ static int gemv_dev(dnb_ctx* c, int type, const uint8_t* w, int k, int n, const 
         return DNB_OK;
     }
     const SegDesc sd{w, nullptr, (uint32_t)nvec, 0u};
+    if (nvec == 1 && c->decode_fast && (((uintptr_t)w) & 15) == 0) {
+        const int rc = launch_seg_gemv_m1(c, c->stream, type, false, true, nullptr, nullptr, 1, k, n, x, k, nullptr, out, &sd,
+                                          "gemv_single");
+        if (rc != DNB_DECLINED) return rc;
+    }
     return launch_seg_matmul(c, c->stream, type, false, nullptr, nullptr, 1, k, n, x, k, nullptr, out, nvec, &sd);
 }
 

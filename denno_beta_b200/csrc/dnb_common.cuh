@@ -113,8 +113,10 @@ struct dnb_ctx {
     dnb::Scratch gemv_x, gemv_out;
     int sm_count = 148;
     int* status = nullptr;              // device status word written by kernels on internal errors
+    unsigned int* ticket = nullptr;     // "last CTA" counter of the fused decode router (self-resetting)
     uint64_t launches = 0;              // kernels launched by this context (bench accounting)
     int gemv_impl = 0;                  // 0 = fast (default), 1 = sequential bit-exact
+    bool decode_fast = true;            // one-token calls take the bulk-copy GEMV + fused router path
 };
 
 namespace dnb {
@@ -168,6 +170,12 @@ int launch_add_inplace(dnb_ctx* c, cudaStream_t st, float* h, const float* d, si
 int launch_fill_u32(dnb_ctx* c, cudaStream_t st, uint32_t* dst, uint32_t v, size_t n);
 int launch_router_logits(dnb_ctx* c, cudaStream_t st, const float* x, int nt, int e, const float* w_r,
                          const float* bias, int ne, float* logits);
+int launch_router_decode(dnb_ctx* c, cudaStream_t st, const float* h, const Model& M, const Layer& L, Workspace& w,
+                         bool fold_shared, unsigned int* ticket);
+// Decode GEMV staged by the bulk-copy engine (gemv_bulk.cu); DNB_DECLINED = shape not covered.
+int launch_seg_gemv_m1(dnb_ctx* c, cudaStream_t st, int type, bool fused, bool xshared, const SegDesc* seg,
+                       const int32_t* nseg_dev, int nseg_max, int n_in, int n_out, const float* x, int ldx,
+                       const int32_t* row_token, float* out, const SegDesc* single, const char* pname);
 int launch_topk(dnb_ctx* c, cudaStream_t st, const float* logits, int nt, int ne, int k, int norm_topk, int32_t* sels,
                 float* wts, float* rowsum);
 // Builds, from sels[nt][k], the expert-major row space: counts, segment

@@ -1,0 +1,263 @@
+// Decode GEMV (one token per segment), staged by the bulk-copy engine.
+//
+// The decode matmuls are tiny for a B200: 4-9 MB per launch, i.e. 30-60 KB per SM.
+// What bounds them is not bandwidth but how soon every byte is in flight.  Here a
+// warp owns a small group of consecutive rows (one contiguous byte range of the
+// expert matrix, a multiple of 16 bytes) and its lane 0 issues ONE cp.async.bulk
+// for it (two when gate and up are fused) the moment the kernel starts, completing
+// on the warp's own mbarrier.  No thread spends instructions on the copy and no
+// CTA-wide barrier stands between the copy and the math: a warp waits only for its
+// own rows.  The grid is sized so that every CTA is resident at once, so the whole
+// launch's weight bytes are requested within the first microsecond.
+//
+// The math is the register decode of formats.cuh (lanes split a row into
+// 32-element units, fixed xor-shuffle tree), so the bits are identical run to run.
+// Reference kernels of this role: kernels_seg_k.cu:201-241, kernels_exp_iq_v2.cu:
+// 259-319 (one warp per row, plain loads).
+#include "dnb_common.cuh"
+#include "formats.cuh"
+#include "dnb_iq_tables.h"
+
+namespace dnb {
+
+__constant__ uint32_t c_grid3xxs_b[256];
+static bool g_tables_b[64] = {false};
+
+static int upload_tables_b(int device) {
+    if (device < 0 || device >= 64) return DNB_ERR_ARG;
+    if (g_tables_b[device]) return DNB_OK;
+    DNB_CUDA(cudaMemcpyToSymbol(c_grid3xxs_b, dnb_iq3xxs_grid, sizeof(c_grid3xxs_b)));
+    g_tables_b[device] = true;
+    return DNB_OK;
+}
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after ~2^22 polls (tens of milliseconds), records the
+// failure in *status and reports false; the caller then skips its math.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, int* status) {
+    for (int i = 0; i < (1 << 22); ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    if (status) atomicExch(status, 1);
+    return false;
+}
+
+__device__ __forceinline__ float silu_b(float v) { return v / (1.0f + expf(-v)); }
+
+constexpr int kWarps = 8;
+
+// Stage n_in floats of x into slot order: xs4[k * nunits + u] (float4), see formats.cuh.
+template <int T>
+__device__ __forceinline__ void stage_x(float* xs, const float* xr, int n_in, int nunits, int tid, int nthr) {
+    for (int i = tid; i < n_in; i += nthr) {
+        int u, sl;
+        slot_of<T>(i, u, sl);
+        xs[((((sl >> 2)) * nunits + u) << 2) + (sl & 3)] = xr[i];
+    }
+}
+
+// grid.x CTAs of 8 warps; warp index wi = blockIdx.x*8 + warp -> (segment wi / gps, row group wi % gps).
+// Dynamic shared memory: [8 mbarriers | pad to 128][IqLut][8 x item bytes (x2 fused)][x]
+template <int T, bool FUSED, int LPR, bool XSHARED>
+__global__ void __launch_bounds__(kWarps * 32)
+gemv_bulk_kernel(const SegDesc* __restrict__ seg, const int32_t* __restrict__ nseg_dev, int nseg_host, SegDesc single,
+                 int n_in, int n_out, int rb, int rg, int gps, const float* __restrict__ x, int ldx,
+                 const int32_t* __restrict__ row_token, float* __restrict__ out, int* status) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
+    constexpr int lut_bytes = (T == T_IQ3_XXS) ? (int)sizeof(IqLut) : 0;
+    IqLut* lut = reinterpret_cast<IqLut*>(smem + 128);
+    const int item_bytes = rg * rb;  // multiple of 16 by construction
+    const int per_warp = (FUSED ? 2 : 1) * item_bytes;
+    uint8_t* wbase = smem + 128 + lut_bytes;
+    float* xbase = reinterpret_cast<float*>(wbase + kWarps * per_warp);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int nseg = nseg_dev ? *nseg_dev : nseg_host;
+    const long wi = (long)blockIdx.x * kWarps + warp;
+    const int s = (int)(wi / gps), grp = (int)(wi % gps);
+    bool active = s < nseg;
+    SegDesc sd = SegDesc{nullptr, nullptr, 0u, 0u};
+    if (active) sd = seg ? seg[s] : single;
+    active = active && sd.m > 0;
+    uint8_t* wa = wbase + warp * per_warp;
+    uint8_t* wb = wa + item_bytes;
+    uint64_t* bar = bars + warp;
+
+    if (lane == 0) {
+        mbar_init(bar, 1);
+        mbar_fence_init();
+        if (active) {
+            mbar_expect_tx(bar, (uint32_t)per_warp);
+            bulk_g2s(wa, sd.wa + (size_t)grp * item_bytes, (uint32_t)item_bytes, bar);
+            if constexpr (FUSED) bulk_g2s(wb, sd.wb + (size_t)grp * item_bytes, (uint32_t)item_bytes, bar);
+        }
+    }
+    __syncwarp();
+
+    const int nunits = n_in >> 5;
+    if constexpr (T == T_IQ3_XXS) {
+        for (int i = tid; i < 256; i += kWarps * 32) lut->grid3xxs[i] = c_grid3xxs_b[i];
+    }
+    const float4* xs4;
+    if constexpr (XSHARED) {
+        stage_x<T>(xbase, x, n_in, nunits, tid, kWarps * 32);
+        xs4 = reinterpret_cast<const float4*>(xbase);
+    } else {
+        float* xw = xbase + (size_t)warp * n_in;
+        if (active) {
+            const uint32_t prow = sd.row0;
+            const float* xr = x + (size_t)(row_token ? row_token[prow] : (int32_t)prow) * ldx;
+            stage_x<T>(xw, xr, n_in, nunits, lane, 32);
+        }
+        xs4 = reinterpret_cast<const float4*>(xw);
+    }
+    __syncthreads();
+    if (!active) return;
+    if (!mbar_wait_bounded(bar, 0, status)) return;
+
+    constexpr int GPW = 32 / LPR;
+    const int sub = lane % LPR, gidx = lane / LPR;
+    const int rounds = (rg + GPW - 1) / GPW;
+    for (int it = 0; it < rounds; ++it) {
+        const int rr = it * GPW + gidx;
+        const bool valid = rr < rg;
+        float acc_a = 0.f, acc_b = 0.f;
+        if (valid) {
+            const uint8_t* ra = wa + rr * rb;
+            const uint8_t* rbp = wb + rr * rb;
+            for (int u = sub; u < nunits; u += LPR) {
+                float w[32];
+                float4 xv[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) xv[k] = xs4[k * nunits + u];
+                decode_unit<T>(ra, u, lut, w);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    acc_a = fmaf(w[4 * k], xv[k].x, acc_a);
+                    acc_a = fmaf(w[4 * k + 1], xv[k].y, acc_a);
+                    acc_a = fmaf(w[4 * k + 2], xv[k].z, acc_a);
+                    acc_a = fmaf(w[4 * k + 3], xv[k].w, acc_a);
+                }
+                if constexpr (FUSED) {
+                    decode_unit<T>(rbp, u, lut, w);
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) {
+                        acc_b = fmaf(w[4 * k], xv[k].x, acc_b);
+                        acc_b = fmaf(w[4 * k + 1], xv[k].y, acc_b);
+                        acc_b = fmaf(w[4 * k + 2], xv[k].z, acc_b);
+                        acc_b = fmaf(w[4 * k + 3], xv[k].w, acc_b);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int o = LPR / 2; o > 0; o >>= 1) {
+            acc_a += __shfl_xor_sync(0xffffffffu, acc_a, o);
+            if constexpr (FUSED) acc_b += __shfl_xor_sync(0xffffffffu, acc_b, o);
+        }
+        if (valid && sub == 0) {
+            const size_t o = (size_t)sd.row0 * n_out + (size_t)grp * rg + rr;
+            out[o] = FUSED ? silu_b(acc_a) * acc_b : acc_a;
+        }
+    }
+}
+
+static int gcd_i(int a, int b) { return b ? gcd_i(b, a % b) : a; }
+
+template <int T, bool FUSED, int LPR, bool XSHARED>
+static int launch_cfg(dnb_ctx* c, cudaStream_t st, const SegDesc* seg, const int32_t* nseg_dev, int nseg_max,
+                      SegDesc single, int n_in, int n_out, const float* x, int ldx, const int32_t* row_token,
+                      float* out, const char* pname) {
+    const int rb = (int)row_bytes(T, n_in);
+    constexpr int GPW = 32 / LPR;
+    const int gmin = 16 / gcd_i(rb, 16);            // rows whose bytes make a multiple of 16
+    int step = gmin * GPW / gcd_i(gmin, GPW);       // lcm
+    if (n_out % step) return DNB_DECLINED;          // caller falls back to the tiled kernel
+    int rg = step;
+    const int target = 3072;                        // bytes per warp per matrix
+    while (rg * 2 * rb <= target && n_out % (rg * 2) == 0) rg *= 2;
+    const int gps = n_out / rg;
+    const int item_bytes = rg * rb;
+    const size_t smem = 128 + (T == T_IQ3_XXS ? sizeof(IqLut) : 0) + (size_t)kWarps * (FUSED ? 2 : 1) * item_bytes +
+                        (size_t)(XSHARED ? 1 : kWarps) * n_in * sizeof(float);
+    if (smem > 200 * 1024) return DNB_DECLINED;
+    auto kern = gemv_bulk_kernel<T, FUSED, LPR, XSHARED>;
+    static size_t smem_set = 0;
+    if (smem > smem_set) {
+        DNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        smem_set = smem;
+    }
+    const long warps = (long)nseg_max * gps;
+    const int grid = (int)((warps + kWarps - 1) / kWarps);
+    ProfScope prof_(c, st, pname);
+    kern<<<grid, kWarps * 32, smem, st>>>(seg, nseg_dev, nseg_max, single, n_in, n_out, rb, rg, gps, x, ldx, row_token,
+                                          out, c->status);
+    c->launches++;
+    DNB_CUDA(cudaGetLastError());
+    return DNB_OK;
+}
+
+template <int T>
+static int launch_t(dnb_ctx* c, cudaStream_t st, bool fused, bool xshared, const SegDesc* seg, const int32_t* nseg_dev,
+                    int nseg_max, SegDesc single, int n_in, int n_out, const float* x, int ldx,
+                    const int32_t* row_token, float* out, const char* pname) {
+    const bool wide = (n_in / 32) >= 32;
+#define DNB_B(F, L, X) \
+    return launch_cfg<T, F, L, X>(c, st, seg, nseg_dev, nseg_max, single, n_in, n_out, x, ldx, row_token, out, pname)
+    if (fused) {
+        if (wide) { if (xshared) DNB_B(true, 32, true); else DNB_B(true, 32, false); }
+        else      { if (xshared) DNB_B(true, 16, true); else DNB_B(true, 16, false); }
+    } else {
+        if (wide) { if (xshared) DNB_B(false, 32, true); else DNB_B(false, 32, false); }
+        else      { if (xshared) DNB_B(false, 16, true); else DNB_B(false, 16, false); }
+    }
+#undef DNB_B
+}
+
+// Every segment has exactly one token row.  xshared: all segments read the same
+// activation row `x` (then x points at that row and row_token is ignored).
+// Returns DNB_DECLINED when the shape does not fit this kernel (the caller then
+// uses the tiled kernel of seg_matmul.cu).
+int launch_seg_gemv_m1(dnb_ctx* c, cudaStream_t st, int type, bool fused, bool xshared, const SegDesc* seg,
+                       const int32_t* nseg_dev, int nseg_max, int n_in, int n_out, const float* x, int ldx,
+                       const int32_t* row_token, float* out, const SegDesc* single_p, const char* pname) {
+    const SegDesc single = single_p ? *single_p : SegDesc{nullptr, nullptr, 0u, 0u};
+    if (!seg && !single_p) return DNB_ERR_ARG;
+    if (row_bytes(type, n_in) == 0 || n_in % 32 || n_out <= 0 || nseg_max <= 0) return DNB_DECLINED;
+    int rc = upload_tables_b(c->device);
+    if (rc != DNB_OK) return rc;
+    switch (type) {
+        case T_Q4_K: return launch_t<T_Q4_K>(c, st, fused, xshared, seg, nseg_dev, nseg_max, single, n_in, n_out, x, ldx, row_token, out, pname);
+        case T_Q5_K: return launch_t<T_Q5_K>(c, st, fused, xshared, seg, nseg_dev, nseg_max, single, n_in, n_out, x, ldx, row_token, out, pname);
+        case T_Q6_K: return launch_t<T_Q6_K>(c, st, fused, xshared, seg, nseg_dev, nseg_max, single, n_in, n_out, x, ldx, row_token, out, pname);
+        case T_IQ3_XXS: return launch_t<T_IQ3_XXS>(c, st, fused, xshared, seg, nseg_dev, nseg_max, single, n_in, n_out, x, ldx, row_token, out, pname);
+        case T_Q8_0: return launch_t<T_Q8_0>(c, st, fused, xshared, seg, nseg_dev, nseg_max, single, n_in, n_out, x, ldx, row_token, out, pname);
+        case T_Q5_1: return launch_t<T_Q5_1>(c, st, fused, xshared, seg, nseg_dev, nseg_max, single, n_in, n_out, x, ldx, row_token, out, pname);
+        default: return DNB_DECLINED;
+    }
+}
+
+}  // namespace dnb

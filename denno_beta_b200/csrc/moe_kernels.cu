@@ -9,7 +9,21 @@ namespace dnb {
 // One CTA per token row.  ss is a fixed-order tree sum (the CPU sums left to
 // right; the two differ by rounding only).  Also publishes the shared expert's
 // two one-segment work descriptors for this call (m = nt, rows 0..nt-1).
-__global__ void __launch_bounds__(256)
+// 1/rms of one row with a fixed summation order shared by every kernel that
+// normalises: thread v of 128 adds x[v]^2, x[v+128]^2, ... (fma), a 32-lane xor
+// tree per warp, then (w0 + w1) + (w2 + w3).
+__device__ __forceinline__ float rms_inv_128(const float* __restrict__ xr, int e, float eps, float* red /*[4]*/) {
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < e; i += 128) ss = fmaf(xr[i], xr[i], ss);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    const float t = (red[0] + red[1]) + (red[2] + red[3]);
+    return 1.0f / sqrtf(t / (float)e + eps);
+}
+
+__global__ void __launch_bounds__(128)
 prep_kernel(const float* __restrict__ h, const float* __restrict__ w, float eps, int e, float* __restrict__ out,
             SegDesc* sh_gu, SegDesc* sh_dn, const uint8_t* sg, const uint8_t* su, const uint8_t* sdn, uint32_t nt) {
     if (blockIdx.x == 0 && threadIdx.x == 0 && sh_gu) {
@@ -17,29 +31,16 @@ prep_kernel(const float* __restrict__ h, const float* __restrict__ w, float eps,
         sh_dn[0] = SegDesc{sdn, nullptr, nt, 0u};
     }
     if (!w) return;
-    __shared__ float red[8];
-    __shared__ float inv_s;
+    __shared__ float red[4];
     const float* xr = h + (size_t)blockIdx.x * e;
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < e; i += 256) ss = fmaf(xr[i], xr[i], ss);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        float t = 0.f;
-        for (int i = 0; i < 8; ++i) t += red[i];
-        inv_s = 1.0f / sqrtf(t / (float)e + eps);
-    }
-    __syncthreads();
-    const float inv = inv_s;
+    const float inv = rms_inv_128(xr, e, eps, red);
     float* o = out + (size_t)blockIdx.x * e;
-    for (int i = threadIdx.x; i < e; i += 256) o[i] = __fmul_rn(__fmul_rn(xr[i], inv), w[i]);
+    for (int i = threadIdx.x; i < e; i += 128) o[i] = __fmul_rn(__fmul_rn(xr[i], inv), w[i]);
 }
 
 int launch_rmsnorm(dnb_ctx* c, cudaStream_t st, const float* h, const float* w, float eps, int nt, int e, float* out) {
     ProfScope prof_(c, st, "rmsnorm");
-    prep_kernel<<<nt, 256, 0, st>>>(h, w, eps, e, out, nullptr, nullptr, nullptr, nullptr, nullptr, 0u);
+    prep_kernel<<<nt, 128, 0, st>>>(h, w, eps, e, out, nullptr, nullptr, nullptr, nullptr, nullptr, 0u);
     c->launches++;
     DNB_CUDA(cudaGetLastError());
     return DNB_OK;
@@ -48,7 +49,7 @@ int launch_rmsnorm(dnb_ctx* c, cudaStream_t st, const float* h, const float* w, 
 int launch_prep(dnb_ctx* c, cudaStream_t st, const float* h, const float* w, float eps, int nt, int e, float* out,
                 SegDesc* sh_gu, SegDesc* sh_dn, const uint8_t* sg, const uint8_t* su, const uint8_t* sdn) {
     ProfScope prof_(c, st, "prep_rmsnorm");
-    prep_kernel<<<nt, 256, 0, st>>>(h, w, eps, e, out, sh_gu, sh_dn, sg, su, sdn, (uint32_t)nt);
+    prep_kernel<<<nt, 128, 0, st>>>(h, w, eps, e, out, sh_gu, sh_dn, sg, su, sdn, (uint32_t)nt);
     c->launches++;
     DNB_CUDA(cudaGetLastError());
     return DNB_OK;
@@ -123,132 +124,171 @@ int launch_router_logits(dnb_ctx* c, cudaStream_t st, const float* x, int nt, in
 
 // ---- softmax + top-k + renorm (tensor.rs:1171-1183; moe.rs:188-279;
 // qwen4exp.rs:11802-11821; GPU form kernels_router225.cu:36-171) -----------------
-// One warp per token, ne <= 1024, k <= 32.  Selection rule of the CPU scan
-// (moe.rs:256-279): each round takes the first unused entry and replaces it only
-// by a strictly larger later value, so ties go to the lower index and a NaN is
-// only taken when it is the first unused entry.  Output ascending; renorm sums
-// the selected probabilities in ascending index order, one add at a time.
-__global__ void __launch_bounds__(128)
-topk_kernel(const float* __restrict__ logits, int nt, int ne, int k, int norm_topk, int32_t* __restrict__ sels,
-            float* __restrict__ wts, float* __restrict__ rowsum) {
-    const int lane = threadIdx.x & 31;
-    const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
-    if (t >= nt) return;
-    const int per = (ne + 31) >> 5;  // <= 32
-    float p[32];
+// One CTA of 128 threads per token, ne <= 1024, k <= 32.  Thread v holds entries
+// v, v+128, ...  Everything that depends on evaluation order is fixed:
+//   softmax denominator: per-thread partials in ascending index, then the tree
+//     ((s[l]+s[l+64]) + (s[l+32]+s[l+96])) followed by a 32-lane xor tree;
+//   selection: the CPU scan's rule (moe.rs:256-279) -- a strictly larger value
+//     wins, ties go to the lower index, and a NaN is taken only when it is the
+//     first unused entry;
+//   renorm: the selected probabilities summed in ascending expert index, one add
+//     at a time, as on the CPU.
+// The same function serves the per-token kernel and the tail of the fused decode
+// router, so a token gets the same routing bits on either path.
+struct TopkSmem {
+    float red[128];
+    float cand_v[4];
+    int cand_i[4];
+    int cand_first[4];
+    float bcast;
+    int ibcast;
+    int sel[32];
+    float pv[32];
+    int ssel[32];
+    float spv[32];
+};
+
+__device__ __forceinline__ void topk_block(const float* __restrict__ logit_row, int ne, int k, int norm_topk,
+                                           TopkSmem& sm, int32_t* __restrict__ sels_out, float* __restrict__ wts_out,
+                                           float* __restrict__ rowsum_out) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    float p[8];
     float mx = -INFINITY;
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-        const int idx = i * 32 + lane;
-        p[i] = (i < per && idx < ne) ? logits[(size_t)t * ne + idx] : -INFINITY;
-        mx = fmaxf(mx, p[i]);
+    for (int j = 0; j < 8; ++j) {
+        const int idx = j * 128 + tid;
+        p[j] = idx < ne ? logit_row[idx] : -INFINITY;
+        mx = fmaxf(mx, p[j]);
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    float sum = 0.f;
+    if (lane == 0) sm.cand_v[warp] = mx;
+    __syncthreads();
+    mx = fmaxf(fmaxf(sm.cand_v[0], sm.cand_v[1]), fmaxf(sm.cand_v[2], sm.cand_v[3]));
+    float part = 0.f;
+    bool any_nan = false;
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-        const int idx = i * 32 + lane;
-        if (i < per && idx < ne) {
-            p[i] = expf(p[i] - mx);
-            sum += p[i];
+    for (int j = 0; j < 8; ++j) {
+        if (j * 128 + tid < ne) {
+            p[j] = expf(p[j] - mx);
+            part += p[j];
+            any_nan |= (p[j] != p[j]);
         }
     }
+    sm.red[tid] = part;
+    const int nan_block = __syncthreads_or(any_nan ? 1 : 0);
+    if (warp == 0) {
+        float a = (sm.red[lane] + sm.red[lane + 64]) + (sm.red[lane + 32] + sm.red[lane + 96]);
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+        if (lane == 0) sm.bcast = a;
+    }
+    __syncthreads();
+    const float sum = sm.bcast;
     if (sum > 0.f) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) p[i] = p[i] / sum;
+        for (int j = 0; j < 8; ++j) p[j] = p[j] / sum;
     }
-    uint32_t used = 0;  // bit i: entry i*32+lane taken
-    int my_sel = -1;    // lane j < k keeps the j-th pick
-    float my_p = 0.f;
+    uint32_t used = 0;
     for (int round = 0; round < k; ++round) {
-        // first unused entry of the row and whether it is NaN
-        int first = 0x7fffffff;
         float best = -INFINITY;
-        int best_i = 0x7fffffff;
-        bool have = false;
+        int best_i = 0x7fffffff, first = 0x7fffffff;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-            const int idx = i * 32 + lane;
-            if (i < per && idx < ne && !((used >> i) & 1u)) {
+        for (int j = 0; j < 8; ++j) {
+            const int idx = j * 128 + tid;
+            if (idx < ne && !((used >> j) & 1u)) {
                 first = min(first, idx);
-                const float v = p[i];
-                if (v == v && (!have || v > best)) {  // ascending idx inside a lane: strict > keeps the lower
+                const float v = p[j];
+                if (v == v && (best_i == 0x7fffffff || v > best)) {
                     best = v;
                     best_i = idx;
-                    have = true;
                 }
             }
         }
-        int gfirst = first;
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) gfirst = min(gfirst, __shfl_xor_sync(0xffffffffu, gfirst, o));
-        // value of the first unused entry (owner lane = gfirst & 31, slot gfirst >> 5)
-        float fv = 0.f;
-#pragma unroll
-        for (int i = 0; i < 32; ++i)
-            if (i == (gfirst >> 5)) fv = p[i];
-        fv = __shfl_sync(0xffffffffu, fv, gfirst & 31);
-        int win;
-        if (fv != fv) {
-            win = gfirst;  // a leading NaN is kept by the scan
-        } else {
-            // argmax over non-NaN unused entries, ties to the lower index
-            float bv = have ? best : -INFINITY;
-            int bi = have ? best_i : 0x7fffffff;
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-                if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) {
-                    bv = ov;
-                    bi = oi;
-                }
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+            first = min(first, __shfl_xor_sync(0xffffffffu, first, o));
+            if (oi != 0x7fffffff && (best_i == 0x7fffffff || ov > best || (ov == best && oi < best_i))) {
+                best = ov;
+                best_i = oi;
             }
-            win = bi;
         }
-        if ((win & 31) == lane) used |= 1u << (win >> 5);
-        float wv = 0.f;
+        if (lane == 0) {
+            sm.cand_v[warp] = best;
+            sm.cand_i[warp] = best_i;
+            sm.cand_first[warp] = first;
+        }
+        __syncthreads();
+        float bv = sm.cand_v[0];
+        int bi = sm.cand_i[0], gfirst = sm.cand_first[0];
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-            if (i == (win >> 5)) wv = p[i];
-        wv = __shfl_sync(0xffffffffu, wv, win & 31);
-        if (lane == round) {
-            my_sel = win;
-            my_p = wv;
+        for (int w = 1; w < 4; ++w) {
+            const float ov = sm.cand_v[w];
+            const int oi = sm.cand_i[w];
+            gfirst = min(gfirst, sm.cand_first[w]);
+            if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) {
+                bv = ov;
+                bi = oi;
+            }
         }
-    }
-    // rank of my pick among the k picks -> ascending order
-    int rank = 0;
-    for (int j = 0; j < k; ++j) {
-        const int other = __shfl_sync(0xffffffffu, my_sel, j);
-        if (lane < k && other < my_sel) rank++;
-    }
-    // gather into sorted lanes: lane r receives the pick whose rank is r
-    int sorted_sel = -1;
-    float sorted_p = 0.f;
-    for (int j = 0; j < k; ++j) {
-        const int rj = __shfl_sync(0xffffffffu, rank, j);
-        const int sj = __shfl_sync(0xffffffffu, my_sel, j);
-        const float pj = __shfl_sync(0xffffffffu, my_p, j);
-        if (lane == rj) {
-            sorted_sel = sj;
-            sorted_p = pj;
+        int win = bi;
+        if (nan_block) {  // rare path: does the scan's first unused entry hold a NaN?
+            if ((gfirst & 127) == tid) {
+                float fv = 0.f;
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    if (j == (gfirst >> 7)) fv = p[j];
+                sm.ibcast = (fv != fv) ? 1 : 0;
+            }
+            __syncthreads();
+            if (sm.ibcast || bi == 0x7fffffff) win = gfirst;
         }
+        if ((win & 127) == tid) {
+            used |= 1u << (win >> 7);
+            float wv = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (j == (win >> 7)) wv = p[j];
+            sm.sel[round] = win;
+            sm.pv[round] = wv;
+        }
+        __syncthreads();
     }
-    float s = 0.f;
-    for (int j = 0; j < k; ++j) s = __fadd_rn(s, __shfl_sync(0xffffffffu, sorted_p, j));
-    if (lane < k) {
+    if (tid < k) {
+        const int mine = sm.sel[tid];
+        int rank = 0;
+        for (int j = 0; j < k; ++j) rank += (sm.sel[j] < mine) ? 1 : 0;
+        sm.ssel[rank] = mine;
+        sm.spv[rank] = sm.pv[tid];
+    }
+    __syncthreads();
+    if (tid == 0) {
+        float s = 0.f;
+        for (int j = 0; j < k; ++j) s = __fadd_rn(s, sm.spv[j]);
+        sm.bcast = s;
+    }
+    __syncthreads();
+    const float s = sm.bcast;
+    if (tid < k) {
         float w;
-        if (!norm_topk) w = sorted_p;
-        else if (isfinite(s) && s > 0.f) w = sorted_p / s;
+        if (!norm_topk) w = sm.spv[tid];
+        else if (isfinite(s) && s > 0.f) w = sm.spv[tid] / s;
         else w = 1.0f / (float)k;
-        sels[(size_t)t * k + lane] = sorted_sel;
-        wts[(size_t)t * k + lane] = w;
+        sels_out[tid] = sm.ssel[tid];
+        wts_out[tid] = w;
     }
-    if (rowsum && lane == 0) rowsum[t] = s;
+    if (rowsum_out && tid == 0) *rowsum_out = s;
+}
+
+__global__ void __launch_bounds__(128)
+topk_kernel(const float* __restrict__ logits, int nt, int ne, int k, int norm_topk, int32_t* __restrict__ sels,
+            float* __restrict__ wts, float* __restrict__ rowsum) {
+    __shared__ TopkSmem sm;
+    const int t = blockIdx.x;
+    topk_block(logits + (size_t)t * ne, ne, k, norm_topk, sm, sels + (size_t)t * k, wts + (size_t)t * k,
+               rowsum ? rowsum + t : nullptr);
 }
 
 int launch_topk(dnb_ctx* c, cudaStream_t st, const float* logits, int nt, int ne, int k, int norm_topk, int32_t* sels,
@@ -258,7 +298,106 @@ int launch_topk(dnb_ctx* c, cudaStream_t st, const float* logits, int nt, int ne
         return DNB_DECLINED;
     }
     ProfScope prof_(c, st, "router_topk");
-    topk_kernel<<<(nt + 3) / 4, 128, 0, st>>>(logits, nt, ne, k, norm_topk, sels, wts, rowsum);
+    topk_kernel<<<nt, 128, 0, st>>>(logits, nt, ne, k, norm_topk, sels, wts, rowsum);
+    c->launches++;
+    DNB_CUDA(cudaGetLastError());
+    return DNB_OK;
+}
+
+// ---- fused decode router --------------------------------------------------------
+// One token: RMSNorm + router logits + (in the CTA that finishes last) softmax,
+// top-k, renorm and the work descriptors of the k routed experts and the shared
+// expert.  Replaces four launches of the general path.  The "last CTA" is found
+// with one atomic ticket; the values it reads were published with a fence before
+// each ticket, and the arithmetic it runs has a fixed order, so the result does
+// not depend on which CTA happens to be last.
+//   seg_gu[s] / seg_dn[s], s < k: expert sels[s], one row each, packed row s
+//   seg_gu[k] / seg_dn[k]: the shared expert (when given), packed row k
+//   pos[s] = s, row_token[s] = 0
+__global__ void __launch_bounds__(128)
+router_decode_kernel(const float* __restrict__ h, const float* __restrict__ norm_w, float eps, int e,
+                     const float* __restrict__ w_r, const float* __restrict__ bias, int ne, int k, int norm_topk,
+                     float* __restrict__ xn, float* __restrict__ logits, int32_t* __restrict__ sels,
+                     float* __restrict__ wts, const uint8_t* gate, const uint8_t* up, const uint8_t* down, size_t eb_g,
+                     size_t eb_u, size_t eb_d, const uint8_t* sg, const uint8_t* su, const uint8_t* sdn,
+                     SegDesc* seg_gu, SegDesc* seg_dn, int32_t* row_token, int32_t* pos, int32_t* nseg,
+                     unsigned int* ticket) {
+    extern __shared__ __align__(16) float xs[];  // [e]
+    __shared__ float red[4];
+    __shared__ int is_last;
+    __shared__ TopkSmem sm;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (norm_w) {
+        const float inv = rms_inv_128(h, e, eps, red);
+        for (int i = tid; i < e; i += 128) xs[i] = __fmul_rn(__fmul_rn(h[i], inv), norm_w[i]);
+    } else {
+        for (int i = tid; i < e; i += 128) xs[i] = h[i];
+    }
+    __syncthreads();
+    if (blockIdx.x == 0 && xn)
+        for (int i = tid; i < e; i += 128) xn[i] = xs[i];
+    const int row = blockIdx.x * 4 + warp;
+    if (row < ne) {
+        const float4* wr = reinterpret_cast<const float4*>(w_r + (size_t)row * e);
+        const float4* x4 = reinterpret_cast<const float4*>(xs);
+        float acc = 0.f;
+        for (int i = lane; i < (e >> 2); i += 32) {
+            const float4 wv = __ldg(wr + i);
+            const float4 xv = x4[i];
+            acc = fmaf(wv.x, xv.x, acc);
+            acc = fmaf(wv.y, xv.y, acc);
+            acc = fmaf(wv.z, xv.z, acc);
+            acc = fmaf(wv.w, xv.w, acc);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (lane == 0) logits[row] = bias ? acc + bias[row] : acc;
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const unsigned int t = atomicAdd(ticket, 1u);
+        is_last = (t == gridDim.x - 1) ? 1 : 0;
+        if (is_last) *ticket = 0u;  // ready for the next launch
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    topk_block(logits, ne, k, norm_topk, sm, sels, wts, nullptr);
+    __syncthreads();
+    if (tid < k) {
+        const int ex = sm.ssel[tid];
+        seg_gu[tid] = SegDesc{gate + (size_t)ex * eb_g, up + (size_t)ex * eb_u, 1u, (uint32_t)tid};
+        seg_dn[tid] = SegDesc{down + (size_t)ex * eb_d, nullptr, 1u, (uint32_t)tid};
+        row_token[tid] = 0;
+        pos[tid] = tid;
+    }
+    if (tid == 0) {
+        if (sg) {
+            seg_gu[k] = SegDesc{sg, su, 1u, (uint32_t)k};
+            seg_dn[k] = SegDesc{sdn, nullptr, 1u, (uint32_t)k};
+            row_token[k] = 0;
+        }
+        *nseg = k + (sg ? 1 : 0);
+    }
+}
+
+int launch_router_decode(dnb_ctx* c, cudaStream_t st, const float* h, const Model& M, const Layer& L, Workspace& w,
+                         bool fold_shared, unsigned int* ticket) {
+    if (M.e % 4 || M.ne > 1024 || M.k > 32) return DNB_DECLINED;
+    const size_t smem = (size_t)M.e * sizeof(float);
+    static size_t smem_set = 0;
+    if (smem > 160 * 1024) return DNB_DECLINED;
+    if (smem > smem_set) {
+        DNB_CUDA(cudaFuncSetAttribute(router_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        smem_set = smem;
+    }
+    ProfScope prof_(c, st, "router_decode_fused");
+    router_decode_kernel<<<(M.ne + 3) / 4, 128, smem, st>>>(
+        h, L.norm_w, M.eps, M.e, L.router_w, L.router_bias, M.ne, M.k, M.norm_topk, w.xn, w.logits, w.sels, w.wts,
+        L.m[0].dev, L.m[1].dev, L.m[2].dev, L.m[0].expert_bytes, L.m[1].expert_bytes, L.m[2].expert_bytes,
+        fold_shared ? L.m[3].dev : nullptr, fold_shared ? L.m[4].dev : nullptr, fold_shared ? L.m[5].dev : nullptr,
+        w.seg_gu, w.seg_dn, w.row_token, w.pos, w.nseg, ticket);
     c->launches++;
     DNB_CUDA(cudaGetLastError());
     return DNB_OK;

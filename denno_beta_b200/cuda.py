@@ -82,6 +82,11 @@ class CudaCtx:
     def launch_count(self):
         return int(self.lib.dnb_launch_count(self.h))
 
+    def device_status(self):
+        v = C.c_int(0)
+        check(self.lib.dnb_device_status(self.h, C.byref(v)))
+        return v.value
+
     def timer_start(self):
         check(self.lib.dnb_timer_start(self.h))
 

@@ -66,6 +66,8 @@ int dnb_set_stream(dnb_ctx* ctx, void* cuda_stream);
 int dnb_sync(dnb_ctx* ctx);
 /* Kernels launched by this context since creation. */
 uint64_t dnb_launch_count(dnb_ctx* ctx);
+/* Status word the kernels write when a bounded wait gave up (0 = clean). */
+int dnb_device_status(dnb_ctx* ctx, int* status);
 /* Device-side timing on the context's stream: start, ... calls ..., stop -> ms. */
 int dnb_timer_start(dnb_ctx* ctx);
 int dnb_timer_stop(dnb_ctx* ctx, float* ms);
@@ -95,7 +97,9 @@ int dnb_gemv_dev(dnb_ctx* ctx, int ggml_type, const void* w_dev, int k, int n, c
                  int nvec);
 /* 0: fast lane-split kernels (default).  1: the sequential-order kernel whose fp32
  * results equal the CPU scalar path bit for bit (kernels_moe.cu contract,
- * cuda.rs:44991-45057). */
+ * cuda.rs:44991-45057).  2: fast kernels, but one-token calls take the general
+ * tiled kernels instead of the bulk-copy decode kernels (A/B checks: both give
+ * the same bits). */
 int dnb_set_gemv_impl(dnb_ctx* ctx, int impl);
 
 /* ---- MoE model: resident expert table ----------------------------------------

@@ -52,6 +52,24 @@ def test_batch_equals_token_by_token(orc, small):
             assert np.array_equal(batch[t].view(np.uint32), one[0].view(np.uint32))
 
 
+def test_decode_kernels_agree_with_tiled_kernels(orc, small):
+    """One-token calls take the bulk-copy GEMV + fused router kernels; the general
+    tiled kernels must give the same bits (set_gemv_impl(2) forces them)."""
+    c, layers = small
+    for layer in (0, 1, 2):
+        h = orc.synth_normal(SEED, 960 + layer, 1.0, layers[layer].e)
+        fast = c.moe_block(layer, h, want_routing=True)
+        c.set_gemv_impl(2)
+        try:
+            tiled = c.moe_block(layer, h, want_routing=True)
+        finally:
+            c.set_gemv_impl(0)
+        assert np.array_equal(fast[1], tiled[1])
+        assert np.array_equal(fast[2].view(np.uint32), tiled[2].view(np.uint32))
+        assert np.array_equal(fast[0].view(np.uint32), tiled[0].view(np.uint32))
+    assert c.device_status() == 0
+
+
 def test_experts_with_given_selection(orc, small):
     """cuda.rs:8088 moe_seg_layer_sum: selection and weights supplied by the caller."""
     from denno_beta_b200 import _lib, cuda as cu
