@@ -22,12 +22,15 @@ SIGNATURES = {
     "dnb_device_status": (_i, [_vp, C.POINTER(C.c_int)]),
     "dnb_timer_start": (_i, [_vp]),
     "dnb_timer_stop": (_i, [_vp, _fp]),
+    "dnb_use_graphs": (_i, [_vp, _i]),
+    "dnb_stall": (_i, [_vp, _f]),
     "dnb_profile_enable": (_i, [_vp, _i]),
     "dnb_profile_read": (_i, [_vp, C.c_char_p, _sz]),
     "dnb_dev_alloc": (_i, [_vp, _sz, C.POINTER(_vp)]),
     "dnb_dev_free": (_i, [_vp, _vp]),
     "dnb_dev_upload": (_i, [_vp, _vp, _vp, _sz]),
     "dnb_dev_download": (_i, [_vp, _vp, _vp, _sz]),
+    "dnb_dev_copy": (_i, [_vp, _vp, _vp, _sz]),
     "dnb_flush_l2": (_i, [_vp]),
     "dnb_register_matrix": (_i, [_vp, _u64, _i, _vp, _sz, _i, _i]),
     "dnb_gemv": (_i, [_vp, _u64, _vp, _vp]),

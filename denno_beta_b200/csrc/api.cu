@@ -17,6 +17,8 @@ void set_error(const char* fmt, ...) {
     va_end(ap);
 }
 
+static void drop_graphs(dnb_ctx* c);
+
 template <typename T>
 static int dev_alloc(T** p, size_t n) {
     *p = nullptr;
@@ -46,6 +48,7 @@ static int ensure_ws(dnb_ctx* c, int nt) {
     int cap = w.nt_cap ? w.nt_cap : 1;
     while (cap < nt) cap *= 2;
     DNB_CUDA(cudaDeviceSynchronize());
+    drop_graphs(c);
     free_ws(w);
     const size_t rows = (size_t)cap * (M.k + 1);  // + the shared expert's row in the decode path
     const int sff = M.sff > 0 ? M.sff : M.ff;
@@ -85,6 +88,56 @@ static int grow(Scratch& s, size_t bytes) {
     s.cap = 0;
     DNB_CUDA(cudaMalloc(&s.p, bytes));
     s.cap = bytes;
+    return DNB_OK;
+}
+
+static void drop_graphs(dnb_ctx* c) {
+    for (auto& kv : c->graphs)
+        if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
+    c->graphs.clear();
+}
+
+// Run `enqueue` (a sequence of launches on c->stream) directly the first time a
+// key is seen, capture it into a CUDA graph the second time, replay it afterwards.
+// One replay costs the host one call instead of one per kernel.
+template <class F>
+static int run_graphed(dnb_ctx* c, const GraphKey& key, F enqueue) {
+    if (!c->use_graphs || c->prof.on) return enqueue();
+    auto it = c->graphs.find(key);
+    if (it == c->graphs.end()) {
+        c->graphs[key] = GraphEntry();
+        return enqueue();
+    }
+    if (!it->second.exec) {
+        const uint64_t l0 = c->launches;
+        DNB_CUDA(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
+        const int rc = enqueue();
+        cudaGraph_t g = nullptr;
+        const cudaError_t e = cudaStreamEndCapture(c->stream, &g);
+        const uint64_t n = c->launches - l0;
+        c->launches = l0;
+        if (rc != DNB_OK || e != cudaSuccess || !g) {
+            if (g) cudaGraphDestroy(g);
+            c->graphs.erase(it);
+            cudaGetLastError();
+            if (rc != DNB_OK) return rc;
+            c->use_graphs = false;  // capture is not possible here: stay on direct launches
+            return enqueue();
+        }
+        cudaGraphExec_t ex = nullptr;
+        const cudaError_t e2 = cudaGraphInstantiate(&ex, g, 0);
+        cudaGraphDestroy(g);
+        if (e2 != cudaSuccess) {
+            c->graphs.erase(it);
+            cudaGetLastError();
+            c->use_graphs = false;
+            return enqueue();
+        }
+        it->second.exec = ex;
+        it->second.kernels = n;
+    }
+    DNB_CUDA(cudaGraphLaunch(it->second.exec, c->stream));
+    c->launches += it->second.kernels;
     return DNB_OK;
 }
 
@@ -249,6 +302,7 @@ void dnb_shutdown(dnb_ctx* c) {
     if (!c) return;
     cudaSetDevice(c->device);
     cudaDeviceSynchronize();
+    drop_graphs(c);
     for (auto& kv : c->matrices) cudaFree(kv.second.dev);
     for (auto& L : c->model.layers) free_layer(L);
     free_ws(c->ws);
@@ -273,6 +327,7 @@ int dnb_set_stream(dnb_ctx* c, void* stream) {
     if (!c) return DNB_ERR_ARG;
     DNB_CUDA(cudaSetDevice(c->device));
     DNB_CUDA(cudaStreamSynchronize(c->stream));
+    drop_graphs(c);
     if (stream) {
         if (c->own_stream) c->saved_stream = c->stream;
         c->stream = (cudaStream_t)stream;
@@ -341,12 +396,31 @@ int dnb_dev_download(dnb_ctx* c, void* host, const void* dev, size_t bytes) {
     return DNB_OK;
 }
 
+int dnb_dev_copy(dnb_ctx* c, void* dst, const void* src, size_t bytes) {
+    if (!c) return DNB_ERR_ARG;
+    DNB_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, c->stream));
+    return DNB_OK;
+}
+
 int dnb_flush_l2(dnb_ctx* c) {
     if (!c) return DNB_ERR_ARG;
     const size_t bytes = 256u << 20;  // > 126 MB L2
     int rc = grow(c->flush, bytes);
     if (rc) return rc;
     return launch_fill_u32(c, c->stream, (uint32_t*)c->flush.p, 0u, bytes / 4);
+}
+
+int dnb_use_graphs(dnb_ctx* c, int on) {
+    if (!c) return DNB_ERR_ARG;
+    DNB_CUDA(cudaDeviceSynchronize());
+    drop_graphs(c);
+    c->use_graphs = on != 0;
+    return DNB_OK;
+}
+
+int dnb_stall(dnb_ctx* c, float ms) {
+    if (!c) return DNB_ERR_ARG;
+    return launch_stall(c, c->stream, ms);
 }
 
 int dnb_profile_enable(dnb_ctx* c, int on) {
@@ -476,6 +550,7 @@ int dnb_moe_config(dnb_ctx* c, int n_layer, int e, int ff, int sff, int ne, int 
     }
     DNB_CUDA(cudaSetDevice(c->device));
     DNB_CUDA(cudaDeviceSynchronize());
+    drop_graphs(c);
     for (auto& L : c->model.layers) free_layer(L);
     free_ws(c->ws);
     Model& M = c->model;
@@ -510,6 +585,8 @@ static int check_expert_shape(dnb_ctx* c, int layer, int matrix, int type, int n
 }
 
 static int install_tensor(dnb_ctx* c, int layer, int matrix, int type, int n_in, int n_out, int n_expert, size_t rb) {
+    DNB_CUDA(cudaDeviceSynchronize());
+    drop_graphs(c);
     Layer& L = c->model.layers[layer];
     ExpertTensor& t = L.m[matrix];
     if (t.dev && t.owned) cudaFree(t.dev);
@@ -578,6 +655,8 @@ int dnb_register_router(dnb_ctx* c, int layer, const float* w, const float* bias
     const Model& M = c->model;
     Layer& L = c->model.layers[layer];
     int rc;
+    DNB_CUDA(cudaDeviceSynchronize());
+    drop_graphs(c);
     if ((rc = upload_f32(&L.router_w, w, (size_t)M.ne * M.e))) return rc;
     if ((rc = upload_f32(&L.router_bias, bias, (size_t)M.ne))) return rc;
     if ((rc = upload_f32(&L.norm_w, norm_w, (size_t)M.e))) return rc;
@@ -595,7 +674,7 @@ int dnb_moe_block_dev(dnb_ctx* c, int layer, const float* h_dev, int nt, float* 
     }
     int rc = ensure_ws(c, nt);
     if (rc) return rc;
-    return block_dev(c, layer, h_dev, nt, out_dev);
+    return run_graphed(c, GraphKey{1, layer, nt, h_dev, out_dev}, [&]() { return block_dev(c, layer, h_dev, nt, out_dev); });
 }
 
 int dnb_moe_block(dnb_ctx* c, int layer, const float* h, int nt, float* out, int32_t* sels_out, float* wts_out) {
@@ -611,11 +690,19 @@ int dnb_moe_block(dnb_ctx* c, int layer, const float* h, int nt, float* out, int
     const Model& M = c->model;
     const size_t bytes = (size_t)nt * M.e * sizeof(float);
     memcpy(w.pinned_in, h, bytes);
-    DNB_CUDA(cudaMemcpyAsync(w.hin, w.pinned_in, bytes, cudaMemcpyHostToDevice, c->stream));
-    if ((rc = block_dev(c, layer, w.hin, nt, w.out))) return rc;
-    DNB_CUDA(cudaMemcpyAsync(w.pinned_out, w.out, bytes, cudaMemcpyDeviceToHost, c->stream));
-    if (sels_out) DNB_CUDA(cudaMemcpyAsync(w.pinned_sels, w.sels, (size_t)nt * M.k * 4, cudaMemcpyDeviceToHost, c->stream));
-    if (wts_out) DNB_CUDA(cudaMemcpyAsync(w.pinned_wts, w.wts, (size_t)nt * M.k * 4, cudaMemcpyDeviceToHost, c->stream));
+    const bool routing = sels_out || wts_out;
+    rc = run_graphed(c, GraphKey{routing ? 3 : 2, layer, nt, nullptr, nullptr}, [&]() -> int {
+        DNB_CUDA(cudaMemcpyAsync(w.hin, w.pinned_in, bytes, cudaMemcpyHostToDevice, c->stream));
+        const int r = block_dev(c, layer, w.hin, nt, w.out);
+        if (r) return r;
+        DNB_CUDA(cudaMemcpyAsync(w.pinned_out, w.out, bytes, cudaMemcpyDeviceToHost, c->stream));
+        if (routing) {
+            DNB_CUDA(cudaMemcpyAsync(w.pinned_sels, w.sels, (size_t)nt * M.k * 4, cudaMemcpyDeviceToHost, c->stream));
+            DNB_CUDA(cudaMemcpyAsync(w.pinned_wts, w.wts, (size_t)nt * M.k * 4, cudaMemcpyDeviceToHost, c->stream));
+        }
+        return DNB_OK;
+    });
+    if (rc) return rc;
     DNB_CUDA(cudaStreamSynchronize(c->stream));
     memcpy(out, w.pinned_out, bytes);
     if (sels_out) memcpy(sels_out, w.pinned_sels, (size_t)nt * M.k * 4);
@@ -748,11 +835,14 @@ int dnb_moe_stack_dev(dnb_ctx* c, float* h_dev, int nt) {
         }
     int rc = ensure_ws(c, nt);
     if (rc) return rc;
-    for (int l = 0; l < M.n_layer; ++l) {
-        if ((rc = block_dev(c, l, h_dev, nt, c->ws.out))) return rc;
-        if ((rc = launch_add_inplace(c, c->stream, h_dev, c->ws.out, (size_t)nt * M.e))) return rc;
-    }
-    return DNB_OK;
+    return run_graphed(c, GraphKey{4, 0, nt, h_dev, nullptr}, [&]() -> int {
+        for (int l = 0; l < M.n_layer; ++l) {
+            int r = block_dev(c, l, h_dev, nt, c->ws.out);
+            if (r) return r;
+            if ((r = launch_add_inplace(c, c->stream, h_dev, c->ws.out, (size_t)nt * M.e))) return r;
+        }
+        return DNB_OK;
+    });
 }
 
 int dnb_moe_stack(dnb_ctx* c, const float* h, int nt, float* out) {

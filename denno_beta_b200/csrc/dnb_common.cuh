@@ -98,9 +98,28 @@ struct Profiler {
 };
 }  // namespace dnb
 
+namespace dnb {
+// Captured launch sequences, replayed with one cudaGraphLaunch.  Keyed by what the
+// sequence depends on: entry point, layer, token count and the device pointers.
+struct GraphKey {
+    int kind, layer, nt;
+    const void *a, *b;
+    bool operator<(const GraphKey& o) const {
+        if (kind != o.kind) return kind < o.kind;
+        if (layer != o.layer) return layer < o.layer;
+        if (nt != o.nt) return nt < o.nt;
+        if (a != o.a) return a < o.a;
+        return b < o.b;
+    }
+};
+struct GraphEntry { cudaGraphExec_t exec = nullptr; uint64_t kernels = 0; };
+}  // namespace dnb
+
 struct dnb_ctx {
     int device = 0;
     dnb::Profiler prof;
+    bool use_graphs = true;
+    std::map<dnb::GraphKey, dnb::GraphEntry> graphs;   // null exec = seen once, not captured yet
     cudaStream_t stream = nullptr;      // main stream (owned unless set from outside)
     cudaStream_t side = nullptr;        // shared-expert stream
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr, ev_t0 = nullptr, ev_t1 = nullptr;
@@ -167,6 +186,7 @@ int launch_rmsnorm(dnb_ctx* c, cudaStream_t st, const float* h, const float* w, 
 int launch_prep(dnb_ctx* c, cudaStream_t st, const float* h, const float* w, float eps, int nt, int e, float* out,
                 SegDesc* sh_gu, SegDesc* sh_dn, const uint8_t* sg, const uint8_t* su, const uint8_t* sdn);
 int launch_add_inplace(dnb_ctx* c, cudaStream_t st, float* h, const float* d, size_t n);
+int launch_stall(dnb_ctx* c, cudaStream_t st, float ms);
 int launch_fill_u32(dnb_ctx* c, cudaStream_t st, uint32_t* dst, uint32_t v, size_t n);
 int launch_router_logits(dnb_ctx* c, cudaStream_t st, const float* x, int nt, int e, const float* w_r,
                          const float* bias, int ne, float* logits);

@@ -57,6 +57,26 @@ int launch_synth_normal(dnb_ctx* c, cudaStream_t st, uint64_t seed, uint64_t ten
     return DNB_OK;
 }
 
+// Keeps the stream busy for about `ms` milliseconds (bounded by the clock, it
+// always ends): work enqueued behind it then runs back to back, which is how the
+// per-kernel timing pass removes host launch gaps from its event intervals.
+__global__ void stall_kernel(long long cycles) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < cycles) {
+    }
+}
+
+int launch_stall(dnb_ctx* c, cudaStream_t st, float ms) {
+    if (ms < 0.f) ms = 0.f;
+    if (ms > 200.f) ms = 200.f;
+    int khz = 1900000;
+    cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, c->device);
+    stall_kernel<<<1, 1, 0, st>>>((long long)((double)ms * (double)khz));
+    c->launches++;
+    DNB_CUDA(cudaGetLastError());
+    return DNB_OK;
+}
+
 int launch_fill_u32(dnb_ctx* c, cudaStream_t st, uint32_t* dst, uint32_t v, size_t n) {
     fill_u32_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(dst, v, n);
     c->launches++;

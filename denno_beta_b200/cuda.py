@@ -95,6 +95,12 @@ class CudaCtx:
         check(self.lib.dnb_timer_stop(self.h, C.byref(ms)))
         return ms.value
 
+    def use_graphs(self, on):
+        check(self.lib.dnb_use_graphs(self.h, int(on)))
+
+    def stall(self, ms):
+        check(self.lib.dnb_stall(self.h, C.c_float(ms)))
+
     def profile(self, on):
         check(self.lib.dnb_profile_enable(self.h, int(on)))
 
@@ -118,6 +124,9 @@ class CudaCtx:
     def upload(self, ptr, arr):
         arr = np.ascontiguousarray(arr)
         check(self.lib.dnb_dev_upload(self.h, C.c_void_p(ptr), _p(arr), arr.nbytes))
+
+    def dev_copy(self, dst, src, nbytes):
+        check(self.lib.dnb_dev_copy(self.h, C.c_void_p(dst), C.c_void_p(src), nbytes))
 
     def download(self, ptr, arr):
         check(self.lib.dnb_dev_download(self.h, _p(arr), C.c_void_p(ptr), arr.nbytes))

@@ -71,6 +71,14 @@ int dnb_device_status(dnb_ctx* ctx, int* status);
 /* Device-side timing on the context's stream: start, ... calls ..., stop -> ms. */
 int dnb_timer_start(dnb_ctx* ctx);
 int dnb_timer_stop(dnb_ctx* ctx, float* ms);
+/* Launch sequences of the block and stack entry points are captured into CUDA
+ * graphs on their second use and replayed afterwards (one host call per replay
+ * instead of one per kernel; the reference pays 4-5 launches and a wait per layer,
+ * cuda.rs:8238-8384).  on = 0 goes back to direct launches. */
+int dnb_use_graphs(dnb_ctx* ctx, int on);
+/* Occupy the stream for about `ms` milliseconds (clock-bounded, at most 200), so
+ * that work enqueued behind it runs without host launch gaps. */
+int dnb_stall(dnb_ctx* ctx, float ms);
 /* Per-kernel device timing for benchmarks (the reference's DENNO_SEG_PROF,
  * model/seg_prof.rs:1-22, cuda.rs:8417-8432): while enabled, every kernel launch is
  * bracketed by events; dnb_profile_read writes a JSON object
@@ -82,6 +90,8 @@ int dnb_dev_alloc(dnb_ctx* ctx, size_t bytes, void** dev);
 int dnb_dev_free(dnb_ctx* ctx, void* dev);
 int dnb_dev_upload(dnb_ctx* ctx, void* dev, const void* host, size_t bytes);
 int dnb_dev_download(dnb_ctx* ctx, void* host, const void* dev, size_t bytes);
+/* Device-to-device copy on the context's stream; does not synchronise. */
+int dnb_dev_copy(dnb_ctx* ctx, void* dst, const void* src, size_t bytes);
 /* Overwrite `bytes` of device scratch larger than L2 (benchmark hygiene). */
 int dnb_flush_l2(dnb_ctx* ctx);
 

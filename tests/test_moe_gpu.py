@@ -70,6 +70,30 @@ def test_decode_kernels_agree_with_tiled_kernels(orc, small):
     assert c.device_status() == 0
 
 
+def test_graph_replay_gives_the_same_bits(orc, small):
+    """The block and stack entry points replay a captured CUDA graph from their third
+    call on; replays, direct launches and different inputs through the same graph must
+    all give the bits of the first call."""
+    c, layers = small
+    e = layers[0].e
+    for nt in (1, 6):
+        h1 = orc.synth_normal(SEED, 1100 + nt, 1.0, nt * e).reshape(nt, e)
+        h2 = orc.synth_normal(SEED, 1200 + nt, 1.0, nt * e).reshape(nt, e)
+        first = [c.moe_block(0, h).copy() for h in (h1, h2)]
+        for _ in range(3):
+            for h, want in zip((h1, h2), first):
+                assert np.array_equal(c.moe_block(0, h).view(np.uint32), want.view(np.uint32))
+        c.use_graphs(False)
+        try:
+            assert np.array_equal(c.moe_block(0, h1).view(np.uint32), first[0].view(np.uint32))
+        finally:
+            c.use_graphs(True)
+        s1 = c.moe_stack(h1)
+        for _ in range(3):
+            assert np.array_equal(c.moe_stack(h1).view(np.uint32), s1.view(np.uint32))
+    assert c.device_status() == 0
+
+
 def test_experts_with_given_selection(orc, small):
     """cuda.rs:8088 moe_seg_layer_sum: selection and weights supplied by the caller."""
     from denno_beta_b200 import _lib, cuda as cu
