@@ -203,6 +203,7 @@ def run_ours(args, rank, world, local_rank):
     alg = {  # algorithmic bytes per launch: weight bytes + activations in/out
         "gemv_gate_up": (K + 1) * 2 * g_b + E * 4 + (K + 1) * FF * 4,
         "gemv_down": (K + 1) * d_b + (K + 1) * FF * 4 + (K + 1) * E * 4,
+        "gemv_down_combine": (K + 1) * d_b + (K + 1) * FF * 4 + E * 4,
         "router_decode_fused": NE * E * 4 + 2 * E * 4 + NE * 4,
         "seg_gate_up_m1": K * 2 * g_b + E * 4 + K * FF * 4,
         "seg_matmul_m1": K * d_b + K * FF * 4 + K * E * 4,

@@ -189,10 +189,12 @@ static int experts_dev(dnb_ctx* c, int layer, const float* x, int nt, const int3
                           (shared && L.shared_gate_row) ? w.shcoef : nullptr, out);
 }
 
-// One token: fused router kernel, gate/up and down GEMVs over the k routed experts
-// plus the shared expert as one more segment, weighted sum.  Four launches.
+// One token: fused router kernel, gate/up GEMV over the k routed experts plus the
+// shared expert as one more segment, down GEMV with the weighted sum fused in.
+// Three launches.  With `residual` (== out for the in-place stack) the result is
+// residual + block(h).
 // Returns DNB_DECLINED when a shape or type combination is outside this path.
-static int block_dev_decode(dnb_ctx* c, int layer, const float* h, float* out) {
+static int block_dev_decode(dnb_ctx* c, int layer, const float* h, float* out, const float* residual) {
     const Model& M = c->model;
     const Layer& L = M.layers[layer];
     Workspace& w = c->ws;
@@ -210,15 +212,21 @@ static int block_dev_decode(dnb_ctx* c, int layer, const float* h, float* out) {
     if (rc == DNB_DECLINED)
         rc = launch_seg_matmul(c, st, L.m[0].type, true, w.seg_gu, nullptr, nseg, M.e, M.ff, w.xn, M.e, w.row_token, w.act, 1);
     if (rc) return rc;
+    if (fold && L.shared_gate_row)
+        if ((rc = launch_shared_coef(c, st, w.xn, L.shared_gate_row, 1, M.e, w.shcoef))) return rc;
+    const float* coef = (fold && L.shared_gate_row) ? w.shcoef : nullptr;
+    rc = launch_down_combine(c, st, L.m[2].type, w.seg_dn, nseg, M.k, M.ff, M.e, w.act, w.wts, coef, fold, residual, out);
+    if (rc != DNB_DECLINED) return rc;
     rc = launch_seg_gemv_m1(c, st, L.m[2].type, false, false, w.seg_dn, nullptr, nseg, M.ff, M.e, w.act, M.ff, nullptr,
                             w.hrow, nullptr, "gemv_down");
     if (rc == DNB_DECLINED)
         rc = launch_seg_matmul(c, st, L.m[2].type, false, w.seg_dn, nullptr, nseg, M.ff, M.e, w.act, M.ff, nullptr, w.hrow, 1);
     if (rc) return rc;
-    if (fold && L.shared_gate_row)
-        if ((rc = launch_shared_coef(c, st, w.xn, L.shared_gate_row, 1, M.e, w.shcoef))) return rc;
-    return launch_combine(c, st, w.hrow, w.pos, w.wts, 1, M.k, M.e, fold ? w.hrow + (size_t)M.k * M.e : nullptr,
-                          (fold && L.shared_gate_row) ? w.shcoef : nullptr, out);
+    if ((rc = launch_combine(c, st, w.hrow, w.pos, w.wts, 1, M.k, M.e, fold ? w.hrow + (size_t)M.k * M.e : nullptr, coef,
+                             residual ? w.out : out)))
+        return rc;
+    if (residual) return launch_add_inplace(c, st, out, w.out, (size_t)M.e);
+    return DNB_OK;
 }
 
 static int block_dev(dnb_ctx* c, int layer, const float* h, int nt, float* out) {
@@ -228,7 +236,7 @@ static int block_dev(dnb_ctx* c, int layer, const float* h, int nt, float* out) 
     cudaStream_t st = c->stream;
     int rc;
     if (nt == 1 && c->decode_fast) {
-        rc = block_dev_decode(c, layer, h, out);
+        rc = block_dev_decode(c, layer, h, out, nullptr);
         if (rc != DNB_DECLINED) return rc;
     }
     const bool shared = L.has_shared();
@@ -837,6 +845,11 @@ int dnb_moe_stack_dev(dnb_ctx* c, float* h_dev, int nt) {
     if (rc) return rc;
     return run_graphed(c, GraphKey{4, 0, nt, h_dev, nullptr}, [&]() -> int {
         for (int l = 0; l < M.n_layer; ++l) {
+            if (nt == 1 && c->decode_fast) {
+                const int rd = block_dev_decode(c, l, h_dev, h_dev, h_dev);
+                if (rd == DNB_OK) continue;
+                if (rd != DNB_DECLINED) return rd;
+            }
             int r = block_dev(c, l, h_dev, nt, c->ws.out);
             if (r) return r;
             if ((r = launch_add_inplace(c, c->stream, h_dev, c->ws.out, (size_t)nt * M.e))) return r;

@@ -136,6 +136,7 @@ struct dnb_ctx {
     uint64_t launches = 0;              // kernels launched by this context (bench accounting)
     int gemv_impl = 0;                  // 0 = fast (default), 1 = sequential bit-exact
     bool decode_fast = true;            // one-token calls take the bulk-copy GEMV + fused router path
+    bool use_pdl = true;                // programmatic dependent launch between the decode kernels
 };
 
 namespace dnb {
@@ -166,6 +167,30 @@ struct ProfScope {
         }                                                                                      \
     } while (0)
 
+// Programmatic dependent launch: with pdl = true the kernel may start while the
+// previous kernel on the stream is still running; it must execute pdl_wait()
+// before it reads anything that kernel wrote.  Everything before pdl_wait() (weight
+// prefetch of data no kernel writes) then overlaps the predecessor's tail.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool pdl,
+                            Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#endif
+
 // ---- launchers (defined in the .cu files) -----------------------------------
 // Segmented dequant matmul: for every segment s < *nseg_dev (or nseg_host when
 // nseg_dev is null), rows of seg[s].wa (and wb when fused) times the segment's
@@ -192,6 +217,12 @@ int launch_router_logits(dnb_ctx* c, cudaStream_t st, const float* x, int nt, in
                          const float* bias, int ne, float* logits);
 int launch_router_decode(dnb_ctx* c, cudaStream_t st, const float* h, const Model& M, const Layer& L, Workspace& w,
                          bool fold_shared, unsigned int* ticket);
+// Decode down projection of all segments with the weighted sum fused in:
+// out[r] = (residual ? residual[r] : 0) + sum_s wts[s] * (W_s act_s)[r] (+ coef * shared).
+// DNB_DECLINED = shape not covered.
+int launch_down_combine(dnb_ctx* c, cudaStream_t st, int type, const SegDesc* seg, int nseg, int k, int n_in, int n_out,
+                        const float* act, const float* wts, const float* shcoef, bool has_shared,
+                        const float* residual, float* out);
 // Decode GEMV staged by the bulk-copy engine (gemv_bulk.cu); DNB_DECLINED = shape not covered.
 int launch_seg_gemv_m1(dnb_ctx* c, cudaStream_t st, int type, bool fused, bool xshared, const SegDesc* seg,
                        const int32_t* nseg_dev, int nseg_max, int n_in, int n_out, const float* x, int ldx,

@@ -95,6 +95,21 @@ gemv_bulk_kernel(const SegDesc* __restrict__ seg, const int32_t* __restrict__ ns
     float* xbase = reinterpret_cast<float*>(wbase + kWarps * per_warp);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    uint8_t* wa = wbase + warp * per_warp;
+    uint8_t* wb = wa + item_bytes;
+    uint64_t* bar = bars + warp;
+
+    if constexpr (T == T_IQ3_XXS) {
+        for (int i = tid; i < 256; i += kWarps * 32) lut->grid3xxs[i] = c_grid3xxs_b[i];
+    }
+    if (lane == 0) {
+        mbar_init(bar, 1);
+        mbar_fence_init();
+    }
+    // Everything above touches nothing another kernel writes.  The segment table,
+    // the token count and x come from the kernel before this one.
+    pdl_wait();
+    pdl_launch_dependents();
     const int nseg = nseg_dev ? *nseg_dev : nseg_host;
     const long wi = (long)blockIdx.x * kWarps + warp;
     const int s = (int)(wi / gps), grp = (int)(wi % gps);
@@ -102,13 +117,7 @@ gemv_bulk_kernel(const SegDesc* __restrict__ seg, const int32_t* __restrict__ ns
     SegDesc sd = SegDesc{nullptr, nullptr, 0u, 0u};
     if (active) sd = seg ? seg[s] : single;
     active = active && sd.m > 0;
-    uint8_t* wa = wbase + warp * per_warp;
-    uint8_t* wb = wa + item_bytes;
-    uint64_t* bar = bars + warp;
-
     if (lane == 0) {
-        mbar_init(bar, 1);
-        mbar_fence_init();
         if (active) {
             mbar_expect_tx(bar, (uint32_t)per_warp);
             bulk_g2s(wa, sd.wa + (size_t)grp * item_bytes, (uint32_t)item_bytes, bar);
@@ -118,9 +127,6 @@ gemv_bulk_kernel(const SegDesc* __restrict__ seg, const int32_t* __restrict__ ns
     __syncwarp();
 
     const int nunits = n_in >> 5;
-    if constexpr (T == T_IQ3_XXS) {
-        for (int i = tid; i < 256; i += kWarps * 32) lut->grid3xxs[i] = c_grid3xxs_b[i];
-    }
     const float4* xs4;
     if constexpr (XSHARED) {
         stage_x<T>(xbase, x, n_in, nunits, tid, kWarps * 32);
@@ -185,6 +191,136 @@ gemv_bulk_kernel(const SegDesc* __restrict__ seg, const int32_t* __restrict__ ns
     }
 }
 
+// ---- decode down projection + weighted sum -------------------------------------
+// One CTA owns R consecutive output rows for ALL segments (the k routed experts and
+// the shared one): thread 0 issues one bulk copy per segment (R rows are one
+// contiguous range of that expert's matrix), the CTA stages every segment's
+// activation vector, each lane group computes its row for each segment in turn,
+// and R threads then add the segments up in ascending order with separate multiply
+// and add roundings -- the order of kernels_dec_epi.cu:28-46 / qwen4exp.rs:12126-
+// 12216.  No partial results go through global memory and nothing is atomic.
+template <int T, int LPR>
+__global__ void __launch_bounds__(kWarps * 32)
+down_combine_kernel(const SegDesc* __restrict__ seg, int nseg, int k, int n_in, int n_out, int rb,
+                    const float* __restrict__ act, const float* __restrict__ wts, const float* __restrict__ shcoef,
+                    int has_shared, const float* __restrict__ residual, float* __restrict__ out, int* status) {
+    constexpr int GPW = 32 / LPR;
+    constexpr int R = kWarps * GPW;
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t* bar = reinterpret_cast<uint64_t*>(smem);
+    constexpr int lut_bytes = (T == T_IQ3_XXS) ? (int)sizeof(IqLut) : 0;
+    IqLut* lut = reinterpret_cast<IqLut*>(smem + 128);
+    const int tile_bytes = R * rb;  // multiple of 16 (checked by the launcher)
+    uint8_t* wbase = smem + 128 + lut_bytes;
+    float* xs = reinterpret_cast<float*>(wbase + (size_t)nseg * tile_bytes);
+    float* hs = xs + (size_t)nseg * n_in;  // [nseg][R]
+    float* ws = hs + nseg * R;             // [nseg] routing weights (+ shared coefficient)
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int r0 = blockIdx.x * R;
+    const int nunits = n_in >> 5;
+    if constexpr (T == T_IQ3_XXS) {
+        for (int i = tid; i < 256; i += kWarps * 32) lut->grid3xxs[i] = c_grid3xxs_b[i];
+    }
+    if (tid == 0) {
+        mbar_init(bar, 1);
+        mbar_fence_init();
+        // The segment table was written two kernels back (the router); the kernel
+        // in between waited for the router before it let this one start, so the
+        // table is complete and the weights can be requested before pdl_wait().
+        mbar_expect_tx(bar, (uint32_t)(nseg * tile_bytes));
+        for (int s = 0; s < nseg; ++s)
+            bulk_g2s(wbase + (size_t)s * tile_bytes, seg[s].wa + (size_t)r0 * rb, (uint32_t)tile_bytes, bar);
+    }
+    pdl_wait();               // act[] comes from the gate/up kernel
+    pdl_launch_dependents();
+    for (int s = 0; s < nseg; ++s) stage_x<T>(xs + (size_t)s * n_in, act + (size_t)s * n_in, n_in, nunits, tid, kWarps * 32);
+    if (tid < nseg) ws[tid] = tid < k ? wts[tid] : (shcoef ? shcoef[0] : 1.0f);
+    __syncthreads();
+    const bool ok = mbar_wait_bounded(bar, 0, status);
+    const int sub = lane % LPR, row = warp * GPW + lane / LPR;
+    for (int s = 0; s < nseg; ++s) {
+        float acc = 0.f;
+        if (ok) {
+            const uint8_t* ra = wbase + (size_t)s * tile_bytes + row * rb;
+            const float4* xs4 = reinterpret_cast<const float4*>(xs + (size_t)s * n_in);
+            for (int u = sub; u < nunits; u += LPR) {
+                float w[32];
+                float4 xv[8];
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk) xv[kk] = xs4[kk * nunits + u];
+                decode_unit<T>(ra, u, lut, w);
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk) {
+                    acc = fmaf(w[4 * kk], xv[kk].x, acc);
+                    acc = fmaf(w[4 * kk + 1], xv[kk].y, acc);
+                    acc = fmaf(w[4 * kk + 2], xv[kk].z, acc);
+                    acc = fmaf(w[4 * kk + 3], xv[kk].w, acc);
+                }
+            }
+        }
+#pragma unroll
+        for (int o = LPR / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (sub == 0) hs[s * R + row] = acc;
+    }
+    __syncthreads();
+    if (tid < R && ok) {
+        float acc = 0.f;
+        for (int s = 0; s < k; ++s) acc = __fadd_rn(acc, __fmul_rn(ws[s], hs[s * R + tid]));
+        if (has_shared) {
+            const float v = hs[k * R + tid];
+            acc = __fadd_rn(acc, shcoef ? __fmul_rn(v, ws[k]) : v);
+        }
+        if (residual) acc = __fadd_rn(residual[r0 + tid], acc);
+        out[r0 + tid] = acc;
+    }
+}
+
+template <int T, int LPR>
+static int launch_dc(dnb_ctx* c, cudaStream_t st, const SegDesc* seg, int nseg, int k, int n_in, int n_out,
+                     const float* act, const float* wts, const float* shcoef, bool has_shared, const float* residual,
+                     float* out) {
+    constexpr int R = kWarps * (32 / LPR);
+    const int rb = (int)row_bytes(T, n_in);
+    if (n_out % R || (R * rb) % 16) return DNB_DECLINED;
+    const size_t smem = 128 + (T == T_IQ3_XXS ? sizeof(IqLut) : 0) + (size_t)nseg * R * rb +
+                        (size_t)nseg * n_in * sizeof(float) + (size_t)nseg * R * sizeof(float) + (size_t)nseg * 4 + 16;
+    if (smem > 200 * 1024) return DNB_DECLINED;
+    auto kern = down_combine_kernel<T, LPR>;
+    static size_t smem_set = 0;
+    if (smem > smem_set) {
+        DNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        smem_set = smem;
+    }
+    ProfScope prof_(c, st, "gemv_down_combine");
+    DNB_CUDA(launch_k(kern, dim3(n_out / R), dim3(kWarps * 32), smem, st, c->use_pdl, seg, nseg, k, n_in, n_out, rb, act, wts,
+                      shcoef, has_shared ? 1 : 0, residual, out, c->status));
+    c->launches++;
+    return DNB_OK;
+}
+
+int launch_down_combine(dnb_ctx* c, cudaStream_t st, int type, const SegDesc* seg, int nseg, int k, int n_in, int n_out,
+                        const float* act, const float* wts, const float* shcoef, bool has_shared,
+                        const float* residual, float* out) {
+    if (row_bytes(type, n_in) == 0 || n_in % 32 || nseg < 1 || nseg > 40) return DNB_DECLINED;
+    int rc = upload_tables_b(c->device);
+    if (rc != DNB_OK) return rc;
+    const bool wide = (n_in / 32) >= 32;
+#define DNB_DC(TT)                                                                                                      \
+    case TT:                                                                                                            \
+        return wide ? launch_dc<TT, 32>(c, st, seg, nseg, k, n_in, n_out, act, wts, shcoef, has_shared, residual, out)  \
+                    : launch_dc<TT, 16>(c, st, seg, nseg, k, n_in, n_out, act, wts, shcoef, has_shared, residual, out);
+    switch (type) {
+        DNB_DC(T_Q4_K)
+        DNB_DC(T_Q5_K)
+        DNB_DC(T_Q6_K)
+        DNB_DC(T_IQ3_XXS)
+        DNB_DC(T_Q8_0)
+        DNB_DC(T_Q5_1)
+        default: return DNB_DECLINED;
+    }
+#undef DNB_DC
+}
+
 static int gcd_i(int a, int b) { return b ? gcd_i(b, a % b) : a; }
 
 template <int T, bool FUSED, int LPR, bool XSHARED>
@@ -213,10 +349,9 @@ static int launch_cfg(dnb_ctx* c, cudaStream_t st, const SegDesc* seg, const int
     const long warps = (long)nseg_max * gps;
     const int grid = (int)((warps + kWarps - 1) / kWarps);
     ProfScope prof_(c, st, pname);
-    kern<<<grid, kWarps * 32, smem, st>>>(seg, nseg_dev, nseg_max, single, n_in, n_out, rb, rg, gps, x, ldx, row_token,
-                                          out, c->status);
+    DNB_CUDA(launch_k(kern, dim3(grid), dim3(kWarps * 32), smem, st, c->use_pdl, seg, nseg_dev, nseg_max, single, n_in, n_out,
+                      rb, rg, gps, x, ldx, row_token, out, c->status));
     c->launches++;
-    DNB_CUDA(cudaGetLastError());
     return DNB_OK;
 }
 

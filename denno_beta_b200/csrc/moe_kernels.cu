@@ -314,6 +314,7 @@ int launch_topk(dnb_ctx* c, cudaStream_t st, const float* logits, int nt, int ne
 //   seg_gu[s] / seg_dn[s], s < k: expert sels[s], one row each, packed row s
 //   seg_gu[k] / seg_dn[k]: the shared expert (when given), packed row k
 //   pos[s] = s, row_token[s] = 0
+template <int NV>  // NV = n_embd / 128: float4 words of a router row per lane
 __global__ void __launch_bounds__(128)
 router_decode_kernel(const float* __restrict__ h, const float* __restrict__ norm_w, float eps, int e,
                      const float* __restrict__ w_r, const float* __restrict__ bias, int ne, int k, int norm_topk,
@@ -327,6 +328,17 @@ router_decode_kernel(const float* __restrict__ h, const float* __restrict__ norm
     __shared__ int is_last;
     __shared__ TopkSmem sm;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int row = blockIdx.x * 4 + warp;
+    // The router rows are constants of the layer: fetch this warp's row before
+    // waiting for the kernel that produces h (it overlaps that kernel's tail).
+    float4 wv[NV];
+    if (row < ne) {
+        const float4* wr = reinterpret_cast<const float4*>(w_r + (size_t)row * e);
+#pragma unroll
+        for (int j = 0; j < NV; ++j) wv[j] = __ldg(wr + lane + 32 * j);
+    }
+    pdl_wait();
+    pdl_launch_dependents();
     if (norm_w) {
         const float inv = rms_inv_128(h, e, eps, red);
         for (int i = tid; i < e; i += 128) xs[i] = __fmul_rn(__fmul_rn(h[i], inv), norm_w[i]);
@@ -336,18 +348,16 @@ router_decode_kernel(const float* __restrict__ h, const float* __restrict__ norm
     __syncthreads();
     if (blockIdx.x == 0 && xn)
         for (int i = tid; i < e; i += 128) xn[i] = xs[i];
-    const int row = blockIdx.x * 4 + warp;
     if (row < ne) {
-        const float4* wr = reinterpret_cast<const float4*>(w_r + (size_t)row * e);
         const float4* x4 = reinterpret_cast<const float4*>(xs);
         float acc = 0.f;
-        for (int i = lane; i < (e >> 2); i += 32) {
-            const float4 wv = __ldg(wr + i);
-            const float4 xv = x4[i];
-            acc = fmaf(wv.x, xv.x, acc);
-            acc = fmaf(wv.y, xv.y, acc);
-            acc = fmaf(wv.z, xv.z, acc);
-            acc = fmaf(wv.w, xv.w, acc);
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            const float4 xv = x4[lane + 32 * j];
+            acc = fmaf(wv[j].x, xv.x, acc);
+            acc = fmaf(wv[j].y, xv.y, acc);
+            acc = fmaf(wv[j].z, xv.z, acc);
+            acc = fmaf(wv[j].w, xv.w, acc);
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
@@ -382,25 +392,34 @@ router_decode_kernel(const float* __restrict__ h, const float* __restrict__ norm
     }
 }
 
+template <int NV>
+static int launch_router_decode_t(dnb_ctx* c, cudaStream_t st, const float* h, const Model& M, const Layer& L,
+                                  Workspace& w, bool fold_shared, unsigned int* ticket) {
+    const size_t smem = (size_t)M.e * sizeof(float);
+    ProfScope prof_(c, st, "router_decode_fused");
+    DNB_CUDA(launch_k(router_decode_kernel<NV>, dim3((M.ne + 3) / 4), dim3(128), smem, st, c->use_pdl, h,
+                      (const float*)L.norm_w, M.eps, M.e, (const float*)L.router_w, (const float*)L.router_bias, M.ne, M.k,
+                      M.norm_topk, w.xn, w.logits, w.sels, w.wts, (const uint8_t*)L.m[0].dev, (const uint8_t*)L.m[1].dev,
+                      (const uint8_t*)L.m[2].dev, L.m[0].expert_bytes, L.m[1].expert_bytes, L.m[2].expert_bytes,
+                      (const uint8_t*)(fold_shared ? L.m[3].dev : nullptr),
+                      (const uint8_t*)(fold_shared ? L.m[4].dev : nullptr),
+                      (const uint8_t*)(fold_shared ? L.m[5].dev : nullptr), w.seg_gu, w.seg_dn, w.row_token, w.pos,
+                      w.nseg, ticket));
+    c->launches++;
+    return DNB_OK;
+}
+
 int launch_router_decode(dnb_ctx* c, cudaStream_t st, const float* h, const Model& M, const Layer& L, Workspace& w,
                          bool fold_shared, unsigned int* ticket) {
-    if (M.e % 4 || M.ne > 1024 || M.k > 32) return DNB_DECLINED;
-    const size_t smem = (size_t)M.e * sizeof(float);
-    static size_t smem_set = 0;
-    if (smem > 160 * 1024) return DNB_DECLINED;
-    if (smem > smem_set) {
-        DNB_CUDA(cudaFuncSetAttribute(router_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        smem_set = smem;
+    if (M.e % 128 || M.ne > 1024 || M.k > 32 || M.e > 8192) return DNB_DECLINED;
+    switch (M.e / 128) {
+        case 4: return launch_router_decode_t<4>(c, st, h, M, L, w, fold_shared, ticket);
+        case 8: return launch_router_decode_t<8>(c, st, h, M, L, w, fold_shared, ticket);
+        case 16: return launch_router_decode_t<16>(c, st, h, M, L, w, fold_shared, ticket);
+        case 20: return launch_router_decode_t<20>(c, st, h, M, L, w, fold_shared, ticket);
+        case 32: return launch_router_decode_t<32>(c, st, h, M, L, w, fold_shared, ticket);
+        default: return DNB_DECLINED;
     }
-    ProfScope prof_(c, st, "router_decode_fused");
-    router_decode_kernel<<<(M.ne + 3) / 4, 128, smem, st>>>(
-        h, L.norm_w, M.eps, M.e, L.router_w, L.router_bias, M.ne, M.k, M.norm_topk, w.xn, w.logits, w.sels, w.wts,
-        L.m[0].dev, L.m[1].dev, L.m[2].dev, L.m[0].expert_bytes, L.m[1].expert_bytes, L.m[2].expert_bytes,
-        fold_shared ? L.m[3].dev : nullptr, fold_shared ? L.m[4].dev : nullptr, fold_shared ? L.m[5].dev : nullptr,
-        w.seg_gu, w.seg_dn, w.row_token, w.pos, w.nseg, ticket);
-    c->launches++;
-    DNB_CUDA(cudaGetLastError());
-    return DNB_OK;
 }
 
 // ---- routing tables -----------------------------------------------------------
