@@ -163,4 +163,124 @@ __device__ __forceinline__ void decode_unit(const uint8_t* row, int u, const IqL
     }
 }
 
+// ---- decode fast path: x in registers, factored dot products ------------------
+// For one-token GEMVs a lane keeps the 32 activations of a unit in registers and
+// streams rows past them.  unit_dot returns sum_i w_i * x_i over the unit without
+// materialising w_i, using conversions that cost one or two instructions per
+// element and are exact:
+//   Q4_K   : a nibble q is placed in byte 2 of the float 0x43000000, which is
+//            128 + q exactly; sum (128+q) x is corrected by 128 * sum x, a per-lane
+//            constant, and the sub-block scale and min are applied to the sums
+//            (d1*S - (128*d1 + m1)*Sx).  About five of fp32's 24 bits go to the
+//            bias, leaving the result far inside the 1e-3 bar.
+//   IQ3_XXS: two grid bytes become the fp16 pair (1024+g0, 1024+g1) by a byte
+//            permute, one half2 subtract removes the bias exactly, the two sign bits
+//            are moved to bits 15/31 by one integer multiply and applied by xor,
+//            and db multiplies the sub-block sum once.
+// Other formats decode to registers and use the same fma order as decode_unit.
+template <int T>
+struct XUnit {
+    float x[32];
+    float s0, s1;  // sums of slots 0-15 / 16-31 (Q4_K, Q5_K)
+};
+
+template <int T>
+__device__ __forceinline__ void load_x_unit(const float4* __restrict__ xs4, int nunits, int u, XUnit<T>& X) {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const float4 v = xs4[k * nunits + u];
+        X.x[4 * k] = v.x;
+        X.x[4 * k + 1] = v.y;
+        X.x[4 * k + 2] = v.z;
+        X.x[4 * k + 3] = v.w;
+    }
+    X.s0 = 0.f;
+    X.s1 = 0.f;
+    if constexpr (T == T_Q4_K) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            X.s0 += X.x[i];
+            X.s1 += X.x[16 + i];
+        }
+    }
+}
+
+// float(128 + byte j of w), w holding one value < 128 per byte
+template <int J>
+__device__ __forceinline__ float magic128(uint32_t w) {
+    return __uint_as_float(__byte_perm(w, 0x43000000u, 0x7054u | (J << 8)));
+}
+
+template <int T>
+__device__ __forceinline__ float unit_dot(const uint8_t* row, int u, const IqLut* lut, const XUnit<T>& X) {
+    if constexpr (T == T_Q4_K) {
+        const int b = u >> 3, j = (u >> 1) & 3, h = u & 1;
+        const uint8_t* blk = row + b * 144;
+        const float d = h2f(ld16(blk)), dmin = h2f(ld16(blk + 2));
+        int sc1, m1, sc2, m2;
+        scale_min_k4(2 * j, blk + 4, sc1, m1);
+        scale_min_k4(2 * j + 1, blk + 4, sc2, m2);
+        const uint4 qv = *reinterpret_cast<const uint4*>(blk + 16 + 32 * j + 16 * h);
+        const uint32_t qw[4] = {qv.x, qv.y, qv.z, qv.w};
+        float slo = 0.f, shi = 0.f;
+#pragma unroll
+        for (int wi = 0; wi < 4; ++wi) {
+            const uint32_t lo = qw[wi] & 0x0F0F0F0Fu, hi = (qw[wi] >> 4) & 0x0F0F0F0Fu;
+            slo = fmaf(magic128<0>(lo), X.x[4 * wi], slo);
+            slo = fmaf(magic128<1>(lo), X.x[4 * wi + 1], slo);
+            slo = fmaf(magic128<2>(lo), X.x[4 * wi + 2], slo);
+            slo = fmaf(magic128<3>(lo), X.x[4 * wi + 3], slo);
+            shi = fmaf(magic128<0>(hi), X.x[16 + 4 * wi], shi);
+            shi = fmaf(magic128<1>(hi), X.x[16 + 4 * wi + 1], shi);
+            shi = fmaf(magic128<2>(hi), X.x[16 + 4 * wi + 2], shi);
+            shi = fmaf(magic128<3>(hi), X.x[16 + 4 * wi + 3], shi);
+        }
+        const float d1 = d * (float)sc1, d2 = d * (float)sc2;
+        const float c1 = fmaf(128.0f, d1, dmin * (float)m1), c2 = fmaf(128.0f, d2, dmin * (float)m2);
+        float r = d1 * slo;
+        r = fmaf(-c1, X.s0, r);
+        r = fmaf(d2, shi, r);
+        r = fmaf(-c2, X.s1, r);
+        return r;
+    } else if constexpr (T == T_IQ3_XXS) {
+        const int b = u >> 3, ib = u & 7;
+        const uint8_t* blk = row + b * 98;
+        const float d = h2f(ld16(blk));
+        const uint32_t aux = ld16(blk + 66 + 4 * ib) | (ld16(blk + 68 + 4 * ib) << 16);
+        const float db = d * (0.5f + (float)(aux >> 28)) * 0.5f;
+        const __half2 k1024 = __half2half2(__ushort_as_half((unsigned short)0x6400));
+        float acc = 0.f;
+#pragma unroll
+        for (int l = 0; l < 4; ++l) {
+            const uint32_t idx = ld16(blk + 2 + 8 * ib + 2 * l);
+            const uint32_t code = (aux >> (7 * l)) & 127u;
+            const uint32_t sg = code | ((__popc(code) & 1u) << 7);
+            const uint32_t g1 = lut->grid3xxs[idx & 0xFFu], g2 = lut->grid3xxs[idx >> 8];
+            uint32_t p[4];
+            p[0] = __byte_perm(g1, 0x64646464u, 0x5140u);
+            p[1] = __byte_perm(g1, 0x64646464u, 0x7362u);
+            p[2] = __byte_perm(g2, 0x64646464u, 0x5140u);
+            p[3] = __byte_perm(g2, 0x64646464u, 0x7362u);
+            const uint32_t mul[4] = {0x40008000u, 0x10002000u, 0x04000800u, 0x01000200u};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                __half2 hv = __hsub2(*reinterpret_cast<const __half2*>(&p[q]), k1024);
+                uint32_t hb = *reinterpret_cast<const uint32_t*>(&hv);
+                hb ^= (sg * mul[q]) & 0x80008000u;
+                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hb));
+                acc = fmaf(f.x, X.x[8 * l + 2 * q], acc);
+                acc = fmaf(f.y, X.x[8 * l + 2 * q + 1], acc);
+            }
+        }
+        return db * acc;
+    } else {
+        float w[32];
+        decode_unit<T>(row, u, lut, w);
+        float acc = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) acc = fmaf(w[i], X.x[i], acc);
+        return acc;
+    }
+}
+
 }  // namespace dnb

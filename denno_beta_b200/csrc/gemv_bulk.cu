@@ -67,6 +67,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
 __device__ __forceinline__ float silu_b(float v) { return v / (1.0f + expf(-v)); }
 
 constexpr int kWarps = 8;
+constexpr int kMaxRounds = 4;  // row rounds per warp in the decode GEMV
 
 // Stage n_in floats of x into slot order: xs4[k * nunits + u] (float4), see formats.cuh.
 template <int T>
@@ -146,47 +147,36 @@ gemv_bulk_kernel(const SegDesc* __restrict__ seg, const int32_t* __restrict__ ns
 
     constexpr int GPW = 32 / LPR;
     const int sub = lane % LPR, gidx = lane / LPR;
-    const int rounds = (rg + GPW - 1) / GPW;
-    for (int it = 0; it < rounds; ++it) {
-        const int rr = it * GPW + gidx;
-        const bool valid = rr < rg;
-        float acc_a = 0.f, acc_b = 0.f;
-        if (valid) {
-            const uint8_t* ra = wa + rr * rb;
-            const uint8_t* rbp = wb + rr * rb;
-            for (int u = sub; u < nunits; u += LPR) {
-                float w[32];
-                float4 xv[8];
+    const int rounds = (rg + GPW - 1) / GPW;  // <= kMaxRounds (launcher)
+    float acc_a[kMaxRounds], acc_b[kMaxRounds];
 #pragma unroll
-                for (int k = 0; k < 8; ++k) xv[k] = xs4[k * nunits + u];
-                decode_unit<T>(ra, u, lut, w);
+    for (int it = 0; it < kMaxRounds; ++it) { acc_a[it] = 0.f; acc_b[it] = 0.f; }
+    for (int u = sub; u < nunits; u += LPR) {
+        XUnit<T> X;
+        load_x_unit<T>(xs4, nunits, u, X);
 #pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    acc_a = fmaf(w[4 * k], xv[k].x, acc_a);
-                    acc_a = fmaf(w[4 * k + 1], xv[k].y, acc_a);
-                    acc_a = fmaf(w[4 * k + 2], xv[k].z, acc_a);
-                    acc_a = fmaf(w[4 * k + 3], xv[k].w, acc_a);
-                }
-                if constexpr (FUSED) {
-                    decode_unit<T>(rbp, u, lut, w);
-#pragma unroll
-                    for (int k = 0; k < 8; ++k) {
-                        acc_b = fmaf(w[4 * k], xv[k].x, acc_b);
-                        acc_b = fmaf(w[4 * k + 1], xv[k].y, acc_b);
-                        acc_b = fmaf(w[4 * k + 2], xv[k].z, acc_b);
-                        acc_b = fmaf(w[4 * k + 3], xv[k].w, acc_b);
-                    }
-                }
+        for (int it = 0; it < kMaxRounds; ++it) {
+            const int rr = it * GPW + gidx;
+            if (it < rounds && rr < rg) {
+                acc_a[it] += unit_dot<T>(wa + rr * rb, u, lut, X);
+                if constexpr (FUSED) acc_b[it] += unit_dot<T>(wb + rr * rb, u, lut, X);
             }
         }
+    }
 #pragma unroll
-        for (int o = LPR / 2; o > 0; o >>= 1) {
-            acc_a += __shfl_xor_sync(0xffffffffu, acc_a, o);
-            if constexpr (FUSED) acc_b += __shfl_xor_sync(0xffffffffu, acc_b, o);
-        }
-        if (valid && sub == 0) {
-            const size_t o = (size_t)sd.row0 * n_out + (size_t)grp * rg + rr;
-            out[o] = FUSED ? silu_b(acc_a) * acc_b : acc_a;
+    for (int it = 0; it < kMaxRounds; ++it) {
+        if (it < rounds) {  // uniform across the warp
+            float a = acc_a[it], bq = acc_b[it];
+#pragma unroll
+            for (int o = LPR / 2; o > 0; o >>= 1) {
+                a += __shfl_xor_sync(0xffffffffu, a, o);
+                if constexpr (FUSED) bq += __shfl_xor_sync(0xffffffffu, bq, o);
+            }
+            const int rr = it * GPW + gidx;
+            if (rr < rg && sub == 0) {
+                const size_t o = (size_t)sd.row0 * n_out + (size_t)grp * rg + rr;
+                out[o] = FUSED ? silu_b(a) * bq : a;
+            }
         }
     }
 }
@@ -244,18 +234,9 @@ down_combine_kernel(const SegDesc* __restrict__ seg, int nseg, int k, int n_in, 
             const uint8_t* ra = wbase + (size_t)s * tile_bytes + row * rb;
             const float4* xs4 = reinterpret_cast<const float4*>(xs + (size_t)s * n_in);
             for (int u = sub; u < nunits; u += LPR) {
-                float w[32];
-                float4 xv[8];
-#pragma unroll
-                for (int kk = 0; kk < 8; ++kk) xv[kk] = xs4[kk * nunits + u];
-                decode_unit<T>(ra, u, lut, w);
-#pragma unroll
-                for (int kk = 0; kk < 8; ++kk) {
-                    acc = fmaf(w[4 * kk], xv[kk].x, acc);
-                    acc = fmaf(w[4 * kk + 1], xv[kk].y, acc);
-                    acc = fmaf(w[4 * kk + 2], xv[kk].z, acc);
-                    acc = fmaf(w[4 * kk + 3], xv[kk].w, acc);
-                }
+                XUnit<T> X;
+                load_x_unit<T>(xs4, nunits, u, X);
+                acc += unit_dot<T>(ra, u, lut, X);
             }
         }
 #pragma unroll
@@ -334,7 +315,8 @@ static int launch_cfg(dnb_ctx* c, cudaStream_t st, const SegDesc* seg, const int
     if (n_out % step) return DNB_DECLINED;          // caller falls back to the tiled kernel
     int rg = step;
     const int target = 3072;                        // bytes per warp per matrix
-    while (rg * 2 * rb <= target && n_out % (rg * 2) == 0) rg *= 2;
+    while (rg * 2 * rb <= target && n_out % (rg * 2) == 0 && rg * 2 <= kMaxRounds * GPW) rg *= 2;
+    if (rg > kMaxRounds * GPW) return DNB_DECLINED;
     const int gps = n_out / rg;
     const int item_bytes = rg * rb;
     const size_t smem = 128 + (T == T_IQ3_XXS ? sizeof(IqLut) : 0) + (size_t)kWarps * (FUSED ? 2 : 1) * item_bytes +
