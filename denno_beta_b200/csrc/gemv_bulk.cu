@@ -82,7 +82,7 @@ __device__ __forceinline__ void stage_x(float* xs, const float* xr, int n_in, in
 // grid.x CTAs of 8 warps; warp index wi = blockIdx.x*8 + warp -> (segment wi / gps, row group wi % gps).
 // Dynamic shared memory: [8 mbarriers | pad to 128][IqLut][8 x item bytes (x2 fused)][x]
 template <int T, bool FUSED, int LPR, bool XSHARED>
-__global__ void __launch_bounds__(kWarps * 32)
+__global__ void __launch_bounds__(kWarps * 32, 4)
 gemv_bulk_kernel(const SegDesc* __restrict__ seg, const int32_t* __restrict__ nseg_dev, int nseg_host, SegDesc single,
                  int n_in, int n_out, int rb, int rg, int gps, const float* __restrict__ x, int ldx,
                  const int32_t* __restrict__ row_token, float* __restrict__ out, int* status) {
@@ -189,13 +189,17 @@ gemv_bulk_kernel(const SegDesc* __restrict__ seg, const int32_t* __restrict__ ns
 // and R threads then add the segments up in ascending order with separate multiply
 // and add roundings -- the order of kernels_dec_epi.cu:28-46 / qwen4exp.rs:12126-
 // 12216.  No partial results go through global memory and nothing is atomic.
+constexpr int kDcWarps = 16;  // warps per CTA of the down+combine kernel
+constexpr int kDcRows = 8;    // output rows per CTA
+
 template <int T, int LPR>
-__global__ void __launch_bounds__(kWarps * 32)
+__global__ void __launch_bounds__(kDcWarps * 32)
 down_combine_kernel(const SegDesc* __restrict__ seg, int nseg, int k, int n_in, int n_out, int rb,
                     const float* __restrict__ act, const float* __restrict__ wts, const float* __restrict__ shcoef,
                     int has_shared, const float* __restrict__ residual, float* __restrict__ out, int* status) {
     constexpr int GPW = 32 / LPR;
-    constexpr int R = kWarps * GPW;
+    constexpr int R = kDcRows;
+    constexpr int NT = kDcWarps * 32;
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t* bar = reinterpret_cast<uint64_t*>(smem);
     constexpr int lut_bytes = (T == T_IQ3_XXS) ? (int)sizeof(IqLut) : 0;
@@ -209,7 +213,7 @@ down_combine_kernel(const SegDesc* __restrict__ seg, int nseg, int k, int n_in, 
     const int r0 = blockIdx.x * R;
     const int nunits = n_in >> 5;
     if constexpr (T == T_IQ3_XXS) {
-        for (int i = tid; i < 256; i += kWarps * 32) lut->grid3xxs[i] = c_grid3xxs_b[i];
+        for (int i = tid; i < 256; i += NT) lut->grid3xxs[i] = c_grid3xxs_b[i];
     }
     if (tid == 0) {
         mbar_init(bar, 1);
@@ -223,14 +227,20 @@ down_combine_kernel(const SegDesc* __restrict__ seg, int nseg, int k, int n_in, 
     }
     pdl_wait();               // act[] comes from the gate/up kernel
     pdl_launch_dependents();
-    for (int s = 0; s < nseg; ++s) stage_x<T>(xs + (size_t)s * n_in, act + (size_t)s * n_in, n_in, nunits, tid, kWarps * 32);
+    for (int s = 0; s < nseg; ++s) stage_x<T>(xs + (size_t)s * n_in, act + (size_t)s * n_in, n_in, nunits, tid, NT);
     if (tid < nseg) ws[tid] = tid < k ? wts[tid] : (shcoef ? shcoef[0] : 1.0f);
     __syncthreads();
     const bool ok = mbar_wait_bounded(bar, 0, status);
-    const int sub = lane % LPR, row = warp * GPW + lane / LPR;
-    for (int s = 0; s < nseg; ++s) {
+    // (segment, row) pairs are dealt to the lane groups of all warps round-robin
+    const int sub = lane % LPR;
+    const int npairs = nseg * R;
+    const int passes = (npairs + kDcWarps * GPW - 1) / (kDcWarps * GPW);
+    for (int ps = 0; ps < passes; ++ps) {
+        const int pr = (ps * kDcWarps + warp) * GPW + lane / LPR;
+        const bool valid = pr < npairs;
+        const int s = valid ? pr / R : 0, row = valid ? pr % R : 0;
         float acc = 0.f;
-        if (ok) {
+        if (ok && valid) {
             const uint8_t* ra = wbase + (size_t)s * tile_bytes + row * rb;
             const float4* xs4 = reinterpret_cast<const float4*>(xs + (size_t)s * n_in);
             for (int u = sub; u < nunits; u += LPR) {
@@ -241,7 +251,7 @@ down_combine_kernel(const SegDesc* __restrict__ seg, int nseg, int k, int n_in, 
         }
 #pragma unroll
         for (int o = LPR / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-        if (sub == 0) hs[s * R + row] = acc;
+        if (valid && sub == 0) hs[s * R + row] = acc;
     }
     __syncthreads();
     if (tid < R && ok) {
@@ -260,7 +270,7 @@ template <int T, int LPR>
 static int launch_dc(dnb_ctx* c, cudaStream_t st, const SegDesc* seg, int nseg, int k, int n_in, int n_out,
                      const float* act, const float* wts, const float* shcoef, bool has_shared, const float* residual,
                      float* out) {
-    constexpr int R = kWarps * (32 / LPR);
+    constexpr int R = kDcRows;
     const int rb = (int)row_bytes(T, n_in);
     if (n_out % R || (R * rb) % 16) return DNB_DECLINED;
     const size_t smem = 128 + (T == T_IQ3_XXS ? sizeof(IqLut) : 0) + (size_t)nseg * R * rb +
@@ -273,8 +283,8 @@ static int launch_dc(dnb_ctx* c, cudaStream_t st, const SegDesc* seg, int nseg, 
         smem_set = smem;
     }
     ProfScope prof_(c, st, "gemv_down_combine");
-    DNB_CUDA(launch_k(kern, dim3(n_out / R), dim3(kWarps * 32), smem, st, c->use_pdl, seg, nseg, k, n_in, n_out, rb, act, wts,
-                      shcoef, has_shared ? 1 : 0, residual, out, c->status));
+    DNB_CUDA(launch_k(kern, dim3(n_out / R), dim3(kDcWarps * 32), smem, st, c->use_pdl, seg, nseg, k, n_in, n_out, rb, act,
+                      wts, shcoef, has_shared ? 1 : 0, residual, out, c->status));
     c->launches++;
     return DNB_OK;
 }
@@ -314,7 +324,7 @@ static int launch_cfg(dnb_ctx* c, cudaStream_t st, const SegDesc* seg, const int
     int step = gmin * GPW / gcd_i(gmin, GPW);       // lcm
     if (n_out % step) return DNB_DECLINED;          // caller falls back to the tiled kernel
     int rg = step;
-    const int target = 3072;                        // bytes per warp per matrix
+    const int target = 1600;                        // bytes per warp per matrix: short per-warp chains, many warps
     while (rg * 2 * rb <= target && n_out % (rg * 2) == 0 && rg * 2 <= kMaxRounds * GPW) rg *= 2;
     if (rg > kMaxRounds * GPW) return DNB_DECLINED;
     const int gps = n_out / rg;

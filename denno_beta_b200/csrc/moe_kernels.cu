@@ -190,6 +190,53 @@ __device__ __forceinline__ void topk_block(const float* __restrict__ logit_row, 
         for (int j = 0; j < 8; ++j) p[j] = p[j] / sum;
     }
     uint32_t used = 0;
+    if (!nan_block) {
+        // Fast path (no NaN anywhere): values map to order-preserving integer keys, a
+        // warp finds its maximum and the lowest index holding it with two redux
+        // instructions, the four warps meet through double-buffered shared slots
+        // (one barrier per round), and only the thread that owned the winner rescans
+        // its entries.  Same rule: larger value first, ties to the lower index.
+        uint32_t key[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const uint32_t ub = __float_as_uint(p[j]);
+            key[j] = (j * 128 + tid < ne) ? ((ub & 0x80000000u) ? ~ub : (ub | 0x80000000u)) : 0u;
+        }
+        uint32_t bk = 0u;
+        int bi = 0x7fffffff;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if (j * 128 + tid < ne && key[j] > bk) { bk = key[j]; bi = j * 128 + tid; }
+        for (int round = 0; round < k; ++round) {
+            const uint32_t wm = __reduce_max_sync(0xffffffffu, bk);
+            const uint32_t wi = __reduce_min_sync(0xffffffffu, (bk == wm && bi != 0x7fffffff) ? (uint32_t)bi : 0x7fffffffu);
+            uint32_t* slot = reinterpret_cast<uint32_t*>(sm.red) + (round & 1) * 8;
+            if (lane == 0) { slot[warp] = wm; slot[4 + warp] = wi; }
+            __syncthreads();
+            uint32_t gm = slot[0], gi = slot[4];
+#pragma unroll
+            for (int w = 1; w < 4; ++w) {
+                const uint32_t om = slot[w], oi = slot[4 + w];
+                if (om > gm || (om == gm && oi < gi)) { gm = om; gi = oi; }
+            }
+            const int win = (int)gi;
+            if ((win & 127) == tid) {
+                used |= 1u << (win >> 7);
+                float wv = 0.f;
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    if (j == (win >> 7)) wv = p[j];
+                sm.sel[round] = win;
+                sm.pv[round] = wv;
+                bk = 0u;
+                bi = 0x7fffffff;
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    if (j * 128 + tid < ne && !((used >> j) & 1u) && key[j] > bk) { bk = key[j]; bi = j * 128 + tid; }
+            }
+        }
+        __syncthreads();
+    } else
     for (int round = 0; round < k; ++round) {
         float best = -INFINITY;
         int best_i = 0x7fffffff, first = 0x7fffffff;
