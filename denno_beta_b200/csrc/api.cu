@@ -29,7 +29,7 @@ static int dev_alloc(T** p, size_t n) {
 
 static void free_ws(Workspace& w) {
     void* dev[] = {w.xn, w.logits, w.wts, w.act, w.hrow, w.sact, w.sh, w.hin, w.out, w.shcoef, w.sels, w.row_token,
-                   w.pos, w.nseg, w.counts, w.seg_gu, w.seg_dn, w.seg_sh_gu, w.seg_sh_dn};
+                   w.pos, w.nseg, w.counts, w.seg_gu, w.seg_dn, w.seg_sh_gu, w.seg_sh_dn, w.xg_hi, w.xg_lo, w.act_hi, w.act_lo};
     for (void* p : dev)
         if (p) cudaFree(p);
     if (w.pinned_in) cudaFreeHost(w.pinned_in);
@@ -72,6 +72,20 @@ static int ensure_ws(dnb_ctx* c, int nt) {
     if ((rc = dev_alloc(&w.seg_dn, (size_t)M.ne + 1))) return rc;
     if ((rc = dev_alloc(&w.seg_sh_gu, 1))) return rc;
     if ((rc = dev_alloc(&w.seg_sh_dn, 1))) return rc;
+    // bf16 hi/lo operand buffers of the tcgen05 path (a few rows of slack so that a
+    // tile that starts near the end stays inside the allocation)
+    const size_t rows_pad = rows + 128;
+    if ((rc = dev_alloc(&w.xg_hi, rows_pad * M.e))) return rc;
+    if ((rc = dev_alloc(&w.xg_lo, rows_pad * M.e))) return rc;
+    if ((rc = dev_alloc(&w.act_hi, rows_pad * M.ff))) return rc;
+    if ((rc = dev_alloc(&w.act_lo, rows_pad * M.ff))) return rc;
+    DNB_CUDA(cudaMemset(w.xg_hi, 0, rows_pad * M.e * 2));
+    DNB_CUDA(cudaMemset(w.xg_lo, 0, rows_pad * M.e * 2));
+    DNB_CUDA(cudaMemset(w.act_hi, 0, rows_pad * M.ff * 2));
+    DNB_CUDA(cudaMemset(w.act_lo, 0, rows_pad * M.ff * 2));
+    w.maps_ok = (M.e % 64 == 0 && M.ff % 64 == 0) &&
+                umma_make_maps(w.xg_hi, w.xg_lo, rows_pad, (uint64_t)M.e, &w.maps_x) == DNB_OK &&
+                umma_make_maps(w.act_hi, w.act_lo, rows_pad, (uint64_t)M.ff, &w.maps_act) == DNB_OK;
     w.pinned_cap = (size_t)cap * M.e * sizeof(float);
     DNB_CUDA(cudaMallocHost((void**)&w.pinned_in, w.pinned_cap));
     DNB_CUDA(cudaMallocHost((void**)&w.pinned_out, w.pinned_cap));
@@ -229,6 +243,46 @@ static int block_dev_decode(dnb_ctx* c, int layer, const float* h, float* out, c
     return DNB_OK;
 }
 
+// Prefill chunks of all-Q4_K layers: expert-major packed rows as bf16 hi/lo, grouped
+// GEMMs on tcgen05 (gate/up with the SwiGLU epilogue, then down), weighted combine.
+static bool umma_eligible(const dnb_ctx* c, const Layer& L, int nt) {
+    const Model& M = c->model;
+    if (!c->use_umma || !c->ws.maps_ok || nt < 16) return false;
+    if (M.e % 256 || M.ff % 256 || M.e % 128 || M.ff % 128) return false;
+    for (int i = 0; i < 3; ++i)
+        if (L.m[i].type != T_Q4_K) return false;
+    if (L.has_shared()) {
+        for (int i = 3; i < 6; ++i)
+            if (L.m[i].type != T_Q4_K) return false;
+        if (L.m[3].n_out != M.ff) return false;
+    }
+    return true;
+}
+
+static int experts_dev_umma(dnb_ctx* c, int layer, const float* x, int nt, const int32_t* sels, const float* wts,
+                            float* out) {
+    const Model& M = c->model;
+    const Layer& L = M.layers[layer];
+    Workspace& w = c->ws;
+    cudaStream_t st = c->stream;
+    const bool shared = L.has_shared();
+    int rc;
+    if ((rc = launch_route_tables(c, st, sels, nt, M.k, M.ne, L, w, shared))) return rc;
+    const int rows = nt * M.k + (shared ? nt : 0);
+    if ((rc = launch_gather_split(c, st, x, M.e, w.row_token, rows, M.e, w.xg_hi, w.xg_lo))) return rc;
+    const int nseg_max = (nt * M.k < M.ne ? nt * M.k : M.ne) + (shared ? 1 : 0);
+    if ((rc = launch_grouped_umma(c, st, true, w.seg_gu, w.nseg, nseg_max, M.e, M.ff, &w.maps_x, nt, w.act_hi, w.act_lo,
+                                  nullptr)))
+        return rc;
+    if ((rc = launch_grouped_umma(c, st, false, w.seg_dn, w.nseg, nseg_max, M.ff, M.e, &w.maps_act, nt, nullptr, nullptr,
+                                  w.hrow)))
+        return rc;
+    if (shared && L.shared_gate_row)
+        if ((rc = launch_shared_coef(c, st, x, L.shared_gate_row, nt, M.e, w.shcoef))) return rc;
+    return launch_combine(c, st, w.hrow, w.pos, wts, nt, M.k, M.e, shared ? w.hrow + (size_t)nt * M.k * M.e : nullptr,
+                          (shared && L.shared_gate_row) ? w.shcoef : nullptr, out);
+}
+
 static int block_dev(dnb_ctx* c, int layer, const float* h, int nt, float* out) {
     const Model& M = c->model;
     const Layer& L = M.layers[layer];
@@ -248,6 +302,7 @@ static int block_dev(dnb_ctx* c, int layer, const float* h, int nt, float* out) 
     const float* x = L.norm_w ? w.xn : h;
     if ((rc = launch_router_logits(c, st, x, nt, M.e, L.router_w, L.router_bias, M.ne, w.logits))) return rc;
     if ((rc = launch_topk(c, st, w.logits, nt, M.ne, M.k, M.norm_topk, w.sels, w.wts, nullptr))) return rc;
+    if (umma_eligible(c, L, nt)) return experts_dev_umma(c, layer, x, nt, w.sels, w.wts, out);
     return experts_dev(c, layer, x, nt, w.sels, w.wts, out);
 }
 
@@ -493,8 +548,11 @@ int dnb_register_matrix(dnb_ctx* c, uint64_t uid, int type, const void* blocks, 
 
 int dnb_set_gemv_impl(dnb_ctx* c, int impl) {
     if (!c || impl < 0 || impl > 2) return DNB_ERR_ARG;
+    DNB_CUDA(cudaDeviceSynchronize());
+    drop_graphs(c);
     c->gemv_impl = impl == 1 ? 1 : 0;
     c->decode_fast = impl != 2;
+    c->use_umma = impl != 2;
     return DNB_OK;
 }
 

@@ -75,12 +75,19 @@ struct Model {
     std::vector<Layer> layers;
 };
 
+struct alignas(64) UmmaMaps {  // eight TMA tensor maps (4 box heights x hi/lo), opaque here
+    unsigned char bytes[8 * 128];
+};
+
 struct Workspace {             // device buffers of the MoE pipeline, sized for nt_cap tokens
     int nt_cap = 0;
     float *xn = nullptr, *logits = nullptr, *wts = nullptr, *act = nullptr, *hrow = nullptr, *sact = nullptr,
           *sh = nullptr, *hin = nullptr, *out = nullptr, *shcoef = nullptr;
     int32_t *sels = nullptr, *row_token = nullptr, *pos = nullptr, *nseg = nullptr, *counts = nullptr;
     SegDesc *seg_gu = nullptr, *seg_dn = nullptr, *seg_sh_gu = nullptr, *seg_sh_dn = nullptr;
+    uint16_t *xg_hi = nullptr, *xg_lo = nullptr, *act_hi = nullptr, *act_lo = nullptr;  // bf16 hi/lo packed rows
+    UmmaMaps maps_x, maps_act;
+    bool maps_ok = false;
     float* pinned_in = nullptr; float* pinned_out = nullptr; size_t pinned_cap = 0;
     int32_t* pinned_sels = nullptr; float* pinned_wts = nullptr;
 };
@@ -137,6 +144,7 @@ struct dnb_ctx {
     int gemv_impl = 0;                  // 0 = fast (default), 1 = sequential bit-exact
     bool decode_fast = true;            // one-token calls take the bulk-copy GEMV + fused router path
     bool use_pdl = true;                // programmatic dependent launch between the decode kernels
+    bool use_umma = true;               // prefill chunks of Q4_K layers take the tcgen05 grouped GEMM
 };
 
 namespace dnb {
@@ -231,8 +239,17 @@ int launch_topk(dnb_ctx* c, cudaStream_t st, const float* logits, int nt, int ne
                 float* wts, float* rowsum);
 // Builds, from sels[nt][k], the expert-major row space: counts, segment
 // descriptors for gate/up and down, row_token[], pos[t][slot] and *nseg.
+// fold_shared: the shared expert becomes one more segment (m = nt) whose packed rows
+// follow the routed rows (row nt*k + t reads token t).
 int launch_route_tables(dnb_ctx* c, cudaStream_t st, const int32_t* sels, int nt, int k, int ne, const Layer& L,
-                        Workspace& ws);
+                        Workspace& ws, bool fold_shared = false);
+// tcgen05 grouped GEMM of prefill (grouped_umma.cu)
+int umma_make_maps(void* hi, void* lo, uint64_t rows, uint64_t cols, UmmaMaps* out);
+int launch_gather_split(dnb_ctx* c, cudaStream_t st, const float* x, int ldx, const int32_t* row_token, int rows, int e,
+                        uint16_t* hi, uint16_t* lo);
+int launch_grouped_umma(dnb_ctx* c, cudaStream_t st, bool fused, const SegDesc* seg, const int32_t* nseg_dev,
+                        int nseg_max, int n_in, int n_out, const UmmaMaps* maps, int nt_max, uint16_t* out_hi,
+                        uint16_t* out_lo, float* out_f32);
 int launch_combine(dnb_ctx* c, cudaStream_t st, const float* hrow, const int32_t* pos, const float* wts, int nt,
                    int k, int e, const float* sh, const float* shcoef, float* out);
 int launch_shared_coef(dnb_ctx* c, cudaStream_t st, const float* x, const float* row, int nt, int e, float* coef);

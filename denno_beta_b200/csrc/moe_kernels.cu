@@ -479,14 +479,16 @@ int launch_router_decode(dnb_ctx* c, cudaStream_t st, const float* h, const Mode
 //   seg_gu/seg_dn[i] = i-th active expert's matrices, m and first row; *nseg
 __global__ void __launch_bounds__(1024)
 route_tables_kernel(const int32_t* __restrict__ sels, int nt, int k, int ne, const uint8_t* gate, const uint8_t* up,
-                    const uint8_t* down, size_t eb_g, size_t eb_u, size_t eb_d, SegDesc* seg_gu, SegDesc* seg_dn,
-                    int32_t* row_token, int32_t* pos, int32_t* nseg, int32_t* counts_out) {
+                    const uint8_t* down, size_t eb_g, size_t eb_u, size_t eb_d, const uint8_t* sg, const uint8_t* su,
+                    const uint8_t* sdn, SegDesc* seg_gu, SegDesc* seg_dn, int32_t* row_token, int32_t* pos,
+                    int32_t* nseg, int32_t* counts_out) {
     extern __shared__ uint32_t sm[];
     const int words = (ne + 31) >> 5;
-    uint32_t* bitmap = sm;                       // [nt][words]
+    uint32_t* bitmap = sm;                          // [nt][words]
     int* counts = (int*)(sm + (size_t)nt * words);  // [ne]
-    int* offs = counts + ne;                     // [ne] exclusive row offsets
-    int* segi = offs + ne;                       // [ne] segment index of active experts
+    int* offs = counts + ne;                        // [ne] first packed row of the expert's segment
+    int* segi = offs + ne;                          // [ne] segment index of active experts, -1 otherwise
+    __shared__ int n_active;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = blockDim.x >> 5;
     for (int i = tid; i < nt * words; i += blockDim.x) bitmap[i] = 0;
     __syncthreads();
@@ -505,24 +507,47 @@ route_tables_kernel(const int32_t* __restrict__ sels, int nt, int k, int ne, con
         if (lane == 0) counts[e] = cnt;
     }
     __syncthreads();
-    if (tid == 0) {  // ne <= 1024: a serial scan is a few microseconds at most
-        int row = 0, si = 0;
-        for (int e = 0; e < ne; ++e) {
-            offs[e] = row;
-            segi[e] = counts[e] > 0 ? si++ : -1;
-            row += counts[e];
+    // Segment order: token count descending, ties by ascending expert index
+    // (moe_expert.rs:8344), so the heavy segments are scheduled first.  Each
+    // expert finds its own rank and first row by scanning the counts.
+    for (int e = tid; e < ne; e += blockDim.x) {
+        const int c = counts[e];
+        int rank = 0, row = 0;
+        if (c > 0) {
+            for (int o = 0; o < ne; ++o) {
+                const int co = counts[o];
+                if (co > c || (co == c && o < e)) {
+                    rank++;
+                    row += co;
+                }
+            }
         }
-        *nseg = si;
+        segi[e] = c > 0 ? rank : -1;
+        offs[e] = row;
     }
+    if (tid == 0) n_active = 0;
     __syncthreads();
     for (int e = tid; e < ne; e += blockDim.x) {
         if (counts_out) counts_out[e] = counts[e];
         if (counts[e] > 0) {
+            atomicAdd(&n_active, 1);  // a count: its value does not depend on the order of the adds
             const int si = segi[e];
             seg_gu[si] = SegDesc{gate + (size_t)e * eb_g, up + (size_t)e * eb_u, (uint32_t)counts[e], (uint32_t)offs[e]};
             seg_dn[si] = SegDesc{down + (size_t)e * eb_d, nullptr, (uint32_t)counts[e], (uint32_t)offs[e]};
         }
     }
+    __syncthreads();
+    if (tid == 0) {
+        int na = n_active;
+        if (sg) {
+            seg_gu[na] = SegDesc{sg, su, (uint32_t)nt, (uint32_t)(nt * k)};
+            seg_dn[na] = SegDesc{sdn, nullptr, (uint32_t)nt, (uint32_t)(nt * k)};
+            na++;
+        }
+        *nseg = na;
+    }
+    if (sg)
+        for (int t = tid; t < nt; t += blockDim.x) row_token[nt * k + t] = t;
     for (int e = warp; e < ne; e += nwarp) {
         if (counts[e] == 0) continue;
         int run = offs[e];
@@ -542,7 +567,7 @@ route_tables_kernel(const int32_t* __restrict__ sels, int nt, int k, int ne, con
 }
 
 int launch_route_tables(dnb_ctx* c, cudaStream_t st, const int32_t* sels, int nt, int k, int ne, const Layer& L,
-                        Workspace& ws) {
+                        Workspace& ws, bool fold_shared) {
     const int words = (ne + 31) >> 5;
     const size_t smem = ((size_t)nt * words + 3 * (size_t)ne) * 4;
     if (smem > 200 * 1024) {
@@ -557,8 +582,9 @@ int launch_route_tables(dnb_ctx* c, cudaStream_t st, const int32_t* sels, int nt
     const int thr = nt * k >= 512 ? 1024 : 256;
     ProfScope prof_(c, st, "route_tables");
     route_tables_kernel<<<1, thr, smem, st>>>(sels, nt, k, ne, L.m[0].dev, L.m[1].dev, L.m[2].dev, L.m[0].expert_bytes,
-                                              L.m[1].expert_bytes, L.m[2].expert_bytes, ws.seg_gu, ws.seg_dn,
-                                              ws.row_token, ws.pos, ws.nseg, ws.counts);
+                                              L.m[1].expert_bytes, L.m[2].expert_bytes, fold_shared ? L.m[3].dev : nullptr,
+                                              fold_shared ? L.m[4].dev : nullptr, fold_shared ? L.m[5].dev : nullptr,
+                                              ws.seg_gu, ws.seg_dn, ws.row_token, ws.pos, ws.nseg, ws.counts);
     c->launches++;
     DNB_CUDA(cudaGetLastError());
     return DNB_OK;

@@ -107,9 +107,9 @@ int dnb_gemv_dev(dnb_ctx* ctx, int ggml_type, const void* w_dev, int k, int n, c
                  int nvec);
 /* 0: fast lane-split kernels (default).  1: the sequential-order kernel whose fp32
  * results equal the CPU scalar path bit for bit (kernels_moe.cu contract,
- * cuda.rs:44991-45057).  2: fast kernels, but one-token calls take the general
- * tiled kernels instead of the bulk-copy decode kernels (A/B checks: both give
- * the same bits). */
+ * cuda.rs:44991-45057).  2: the general tiled fp32 kernels everywhere -- one-token calls
+ * skip the bulk-copy decode kernels and prefill chunks skip the tcgen05 grouped
+ * GEMM (A/B checks between kernel families). */
 int dnb_set_gemv_impl(dnb_ctx* ctx, int impl);
 
 /* ---- MoE model: resident expert table ----------------------------------------

@@ -40,10 +40,10 @@ def test_block_small(orc, small, layer, nt):
 
 
 def test_batch_equals_token_by_token(orc, small):
-    """qwen4exp.rs:28259 (batch prefill == sequential).  Within the batched kernels a
-    token's bits do not depend on its neighbours or on the chunk size; against the
-    one-token decode kernels (different, factored arithmetic) the routing is identical
-    and the values agree to rounding."""
+    """qwen4exp.rs:28259 (batch prefill == sequential).  A token's routing never depends
+    on its neighbours; its values agree across chunk sizes and kernel families (one-token
+    decode kernels, tiled fp32 kernels, tcgen05 grouped GEMM) to rounding, and are
+    bit-identical when the same kernels run (fp32 tiled path, any chunk composition)."""
     c, layers = small
     nt = 21
     for layer in (0, 1):
@@ -51,10 +51,37 @@ def test_batch_equals_token_by_token(orc, small):
         batch, bsel, bw = c.moe_block(layer, h, want_routing=True)
         for t in (0, 7, 20):
             pair = c.moe_block(layer, h[[t, (t + 1) % nt]])
-            assert np.array_equal(batch[t].view(np.uint32), pair[0].view(np.uint32))
+            assert rel_err(pair[0], batch[t]) <= 2e-5
             one, osel, ow = c.moe_block(layer, h[t:t + 1], want_routing=True)
             assert np.array_equal(osel[0], bsel[t]) and np.array_equal(ow[0].view(np.uint32), bw[t].view(np.uint32))
             assert rel_err(one[0], batch[t]) <= 2e-5
+    h = orc.synth_normal(SEED, 952, 1.0, nt * layers[0].e).reshape(nt, -1)
+    batch = c.moe_block(0, h)  # IQ3_XXS layer: tiled fp32 kernels for every chunk size > 1
+    sub = c.moe_block(0, h[[5, 3, 20, 11]])
+    assert np.array_equal(sub.view(np.uint32), batch[[5, 3, 20, 11]].view(np.uint32))
+
+
+def test_tcgen05_grouped_gemm_matches_fp32_kernels(orc, small):
+    """Q4_K prefill chunks run on the tensor cores with both operands split into two bf16
+    halves (three MMAs per product); the result must stay at fp32-kernel accuracy, far
+    inside the 1e-3 bar, for ragged chunk sizes that exercise every N tile width."""
+    c, layers = small
+    L = layers[1]
+    for nt in (16, 17, 40, 100, 130, 300):
+        h = orc.synth_normal(SEED, 1300 + nt, 1.0, nt * L.e).reshape(nt, L.e)
+        tc, tsel, tw = c.moe_block(1, h, want_routing=True)
+        c.set_gemv_impl(2)
+        try:
+            fp = c.moe_block(1, h)
+        finally:
+            c.set_gemv_impl(0)
+        assert rel_err(tc, fp) <= 5e-5, "nt=%d: tcgen05 vs fp32 kernels %.3g" % (nt, rel_err(tc, fp))
+        idx = sorted({0, nt // 3, nt - 1})
+        err, _ = check_block(orc, L, h[idx], tc[idx], tsel[idx], tw[idx])
+        assert err <= 1e-4, "nt=%d: %.3g vs oracle" % (nt, err)
+        again = c.moe_block(1, h)
+        assert np.array_equal(tc.view(np.uint32), again.view(np.uint32)), "tcgen05 path not bit-identical run to run"
+    assert c.device_status() == 0
 
 
 def test_decode_kernels_agree_with_tiled_kernels(orc, small):
