@@ -235,9 +235,13 @@ def run_ours(args, rank, world, local_rank):
     }
     if world == 1 and not args.no_extras:
         res["extras"] = extras(ctx, cu, oracle)
+        ctx.close()
+        ctx = None
+        res["extras"]["config2_q4k_prefill_512"] = prefill_extras(cu, oracle, local_rank)
     if world == 1 and not args.no_cpu:
         res["cpu_baseline"] = cpu_baseline(oracle, budget_s=10.0)
-    ctx.close()
+    if ctx is not None:
+        ctx.close()
     return res
 
 
@@ -270,6 +274,52 @@ def extras(ctx, cu, oracle):
                                     "frac_of_measured_hbm": alg / (ms / reps * 1e-3) / 1e9 / peaks()[0]}
     for p in (dw, dx, do):
         ctx.dev_free(p)
+    return out
+
+
+def prefill_extras(cu, oracle, device):
+    """Config 2: one MoE block, one 512-token chunk, Q4_K experts, Zipf router bias.
+    Rotates over 4 layer copies (3.6 GB of weights); tokens stay on the device."""
+    layers, nt = 4, 512
+    ctx = cu.CudaCtx(device)
+    out = {}
+    try:
+        build_model(ctx, cu, Q4_K, layers, True)
+        h = oracle.synth_normal(SEED, 8000, 1.0, nt * E).reshape(nt, E)
+        d_h = ctx.dev_alloc(h.nbytes)
+        d_o = ctx.dev_alloc(h.nbytes)
+        ctx.upload(d_h, h)
+        for l in range(2 * layers):
+            assert ctx.moe_block_dev(l % layers, d_h, nt, d_o)
+        ctx.sync()
+        reps = 24
+        ctx.stall(5.0)
+        ctx.timer_start()
+        for l in range(reps):
+            assert ctx.moe_block_dev(l % layers, d_h, nt, d_o)
+        ms = ctx.timer_stop() / reps
+        ctx.profile(True)
+        for l in range(layers):
+            ctx.stall(2.0)
+            assert ctx.moe_block_dev(l % layers, d_h, nt, d_o)
+        prof = ctx.profile_read()
+        ctx.profile(False)
+        sels = ctx.router_topk(0, oracle.rmsnorm(h, np.ones(E, np.float32)))[0]
+        counts = np.bincount(sels.ravel(), minlength=NE)
+        active = int((counts > 0).sum())
+        flops = 2.0 * 3 * E * FF * (nt * K + nt) + 2.0 * nt * NE * E
+        g_b, d_b = expert_bytes(Q4_K)
+        bytes_ = (active + 1) * (2 * g_b + d_b) + NE * E * 4 + 2 * nt * E * 4
+        hbm, tf, _ = peaks()
+        out = {"ms_per_chunk_layer": ms, "tok_per_s_layer": nt / (ms * 1e-3), "algorithmic_tflops": flops / (ms * 1e-3) / 1e12,
+               "frac_of_measured_bf16": flops / (ms * 1e-3) / 1e12 / tf, "algorithmic_gbs": bytes_ / (ms * 1e-3) / 1e9,
+               "frac_of_measured_hbm": bytes_ / (ms * 1e-3) / 1e9 / hbm, "active_experts": active,
+               "max_tokens_per_expert": int(counts.max()), "median_tokens_per_expert": float(np.median(counts)),
+               "kernels_ms_per_layer": {k: round(v["ms"] / layers, 4) for k, v in prof.items()}}
+        ctx.dev_free(d_h)
+        ctx.dev_free(d_o)
+    finally:
+        ctx.close()
     return out
 
 

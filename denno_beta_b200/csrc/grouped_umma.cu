@@ -15,9 +15,10 @@
 //
 // Precision.  The path's bar is max|err| <= 1e-3 of the output RMS, which a single
 // bf16 rounding of both operands misses by several times.  Each operand is
-// therefore split into two bf16 numbers (hi = upper 16 bits of the fp32 value,
-// lo = the remainder, truncated), and three MMAs hi*hi + hi*lo + lo*hi accumulate
-// into the same TMEM tile; the dropped lo*lo term is below 2^-16 relative.
+// therefore split into two bf16 numbers (hi = the value rounded to bf16, lo = the
+// exact remainder truncated to bf16), and three MMAs hi*hi + hi*lo + lo*hi
+// accumulate into the same TMEM tile; the dropped lo*lo term is about 2^-18
+// relative per product.
 //
 // Operands.
 //   A (weights): four warps dequantise Q4_K bytes straight from global memory,
@@ -37,6 +38,7 @@
 // Every wait is bounded; a wait that gives up sets *status and the CTA falls
 // through to the common teardown (TMEM is always freed).
 #include <cuda.h>
+#include <cuda_bf16.h>
 
 #include "dnb_common.cuh"
 #include "formats.cuh"
@@ -132,12 +134,13 @@ struct Maps {            // tensor maps of the B operand: box heights 16, 32, 64
     CUtensorMap lo[4];
 };
 
-// Split an fp32 value into hi (upper 16 bits, i.e. bf16 by truncation) and lo =
-// bf16-truncated remainder; returns the two bf16 bit patterns.
+// Split two fp32 values into bf16 pairs: hi = round-to-nearest bf16, lo = the exact
+// remainder a - hi truncated to bf16.  (Rounding hi to nearest halves |lo| compared
+// with truncation and so quarters the dropped lo*lo term.)
 __device__ __forceinline__ void split2(float a, float b, uint32_t& hi_pair, uint32_t& lo_pair) {
-    const uint32_t ab = __float_as_uint(a), bb = __float_as_uint(b);
-    hi_pair = __byte_perm(ab, bb, 0x7632);
-    const float al = a - __uint_as_float(ab & 0xFFFF0000u), bl = b - __uint_as_float(bb & 0xFFFF0000u);
+    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);  // .x = a (low half), .y = b
+    hi_pair = *reinterpret_cast<const uint32_t*>(&h);
+    const float al = a - __uint_as_float(hi_pair << 16), bl = b - __uint_as_float(hi_pair & 0xFFFF0000u);
     lo_pair = __byte_perm(__float_as_uint(al), __float_as_uint(bl), 0x7632);
 }
 
@@ -294,10 +297,10 @@ grouped_q4k_umma_kernel(const SegDesc* __restrict__ seg, const int32_t* __restri
                         if constexpr (NMAT == 2) {
                             const float gv = __uint_as_float(g[j2]), uv = __uint_as_float(u[j2]);
                             const float a = gv / (1.0f + expf(-gv)) * uv;
-                            const uint32_t ab = __float_as_uint(a);
-                            const float al = a - __uint_as_float(ab & 0xFFFF0000u);
+                            const uint16_t ah = __bfloat16_as_ushort(__float2bfloat16_rn(a));
+                            const float al = a - __uint_as_float((uint32_t)ah << 16);
                             const size_t o = (prow0 + t) * (size_t)n_out + r0 + r;
-                            out_hi[o] = (uint16_t)(ab >> 16);
+                            out_hi[o] = ah;
                             out_lo[o] = (uint16_t)(__float_as_uint(al) >> 16);
                         } else {
                             out_f32[(prow0 + t) * (size_t)n_out + r0 + r] = __uint_as_float(g[j2]);
