@@ -45,6 +45,7 @@ SIGNATURES = {
     "dnb_moe_block_dev": (_i, [_vp, _i, _vp, _i, _vp]),
     "dnb_moe_experts": (_i, [_vp, _i, _vp, _i, _vp, _vp, _vp]),
     "dnb_router_topk": (_i, [_vp, _i, _vp, _i, _vp, _vp, _vp]),
+    "dnb_router_topk_static": (_i, [_vp, _i, _vp, _i, _vp, _vp, _vp]),
     "dnb_grouped_gemm": (_i, [_vp, _i, _i, _vp, _i, _vp, _vp]),
     "dnb_moe_stack": (_i, [_vp, _vp, _i, _vp]),
     "dnb_moe_stack_dev": (_i, [_vp, _vp, _i]),

@@ -102,6 +102,20 @@ router_logits_kernel(const float* __restrict__ x, int nt, int e, const float* __
     }
 }
 
+// Dynamic shared memory the router kernel has been allowed so far, per device (only raised).
+static size_t g_router_smem[64] = {0};
+static int router_smem_at_least(int device, size_t bytes) {
+    if (device < 0 || device >= 64) return DNB_ERR_ARG;
+    if (bytes <= g_router_smem[device]) return DNB_OK;
+    if (bytes > 200 * 1024) {
+        set_error("router: n_embd needs %zu B of shared memory", bytes);
+        return DNB_DECLINED;
+    }
+    DNB_CUDA(cudaFuncSetAttribute(router_logits_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    g_router_smem[device] = bytes;
+    return DNB_OK;
+}
+
 int launch_router_logits(dnb_ctx* c, cudaStream_t st, const float* x, int nt, int e, const float* w_r,
                          const float* bias, int ne, float* logits) {
     if (e % 4) {
@@ -109,11 +123,8 @@ int launch_router_logits(dnb_ctx* c, cudaStream_t st, const float* x, int nt, in
         return DNB_DECLINED;
     }
     const size_t smem = (size_t)RT * e * sizeof(float);
-    static size_t smem_set = 0;
-    if (smem > smem_set) {
-        DNB_CUDA(cudaFuncSetAttribute(router_logits_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        smem_set = smem;
-    }
+    int rc = router_smem_at_least(c->device, smem);
+    if (rc) return rc;
     dim3 grid((ne + RROWS - 1) / RROWS, (nt + RT - 1) / RT);
     ProfScope prof_(c, st, "router_logits");
     router_logits_kernel<<<grid, RROWS * 32, smem, st>>>(x, nt, e, w_r, bias, ne, logits);
@@ -468,6 +479,69 @@ int launch_router_decode(dnb_ctx* c, cudaStream_t st, const float* h, const Mode
         default: return DNB_DECLINED;
     }
 }
+
+// ---- router + top-k without any allocation -----------------------------------------
+// The logits between the two router kernels normally live in the context's
+// grow-only workspace, which is (re)allocated on demand.  Some callers must not
+// allocate at all once they are running: a serving loop that has pinned its memory
+// budget at start-up, a plugin host that forbids cudaMalloc on its inference thread
+// (an allocation synchronises the whole device and stalls every other stream), or
+// code between cudaStreamBeginCapture and EndCapture, where cudaMalloc is illegal.
+// For them the same two kernels run with the logits in this fixed array, which every
+// GPU that loads the library carries until the process exits (256 KiB).
+constexpr int kStaticLogits = 65536;  // nt * n_expert must not exceed this
+static __device__ __align__(256) float g_static_logits[kStaticLogits];
+static float* g_static_logits_ptr[64] = {nullptr};  // device address of the array, per device
+
+}  // namespace dnb
+
+extern "C" int dnb_router_topk_static(dnb_ctx* c, int layer, const float* x_dev, int nt, int32_t* sels_dev,
+                                      float* wts_dev, float* rowsum_dev) {
+    using namespace dnb;
+    if (!c || !x_dev || !sels_dev || !wts_dev || nt < 1) return DNB_ERR_ARG;
+    const Model& M = c->model;
+    if (layer < 0 || layer >= M.n_layer || !M.layers[layer].router_w) {
+        set_error("router_topk_static: layer %d has no router", layer);
+        return DNB_DECLINED;
+    }
+    if ((long)nt * M.ne > kStaticLogits) {
+        set_error("router_topk_static: %d tokens x %d experts = %ld logits exceed the static scratch of %d; "
+                  "use dnb_router_topk or split the call", nt, M.ne, (long)nt * M.ne, kStaticLogits);
+        return DNB_ERR_ARG;
+    }
+    if (M.e % 4 || M.ne > 1024 || M.k > 32) {
+        set_error("router_topk_static: shape outside the router kernels' range");
+        return DNB_DECLINED;
+    }
+    if (c->device < 0 || c->device >= 64) return DNB_ERR_ARG;
+    // One-time set-up per device: in host code the array's name is only a handle,
+    // its device address has to be asked for (with that device current).
+    const size_t smem = (size_t)RT * M.e * sizeof(float);
+    if (!g_static_logits_ptr[c->device]) {
+        DNB_CUDA(cudaSetDevice(c->device));
+        float* p = nullptr;
+        DNB_CUDA(cudaGetSymbolAddress((void**)&p, g_static_logits));
+        const int rc = router_smem_at_least(c->device, 200 * 1024);  // the most the router kernel is ever given
+        if (rc) return rc;
+        g_static_logits_ptr[c->device] = p;
+    }
+    if (smem > g_router_smem[c->device]) {
+        set_error("router_topk_static: n_embd %d needs more shared memory than the router kernel has", M.e);
+        return DNB_DECLINED;
+    }
+    float* logits = g_static_logits_ptr[c->device];
+    const Layer& L = M.layers[layer];
+    const dim3 grid((M.ne + RROWS - 1) / RROWS, (nt + RT - 1) / RT);
+    // every logit of the [nt][n_expert] range is written before it is read, so the
+    // previous call's contents need no clearing
+    router_logits_kernel<<<grid, RROWS * 32, smem, c->stream>>>(x_dev, nt, M.e, L.router_w, L.router_bias, M.ne, logits);
+    topk_kernel<<<nt, 128, 0, c->stream>>>(logits, nt, M.ne, M.k, M.norm_topk, sels_dev, wts_dev, rowsum_dev);
+    c->launches += 2;
+    DNB_CUDA(cudaGetLastError());
+    return DNB_OK;
+}
+
+namespace dnb {
 
 // ---- routing tables -----------------------------------------------------------
 // From sels[nt][k] build the expert-major packed row space the grouped matmuls

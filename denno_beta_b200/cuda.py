@@ -219,6 +219,12 @@ class CudaCtx:
             return None
         return sels, wts, rowsum
 
+    def router_topk_static(self, layer, x_ptr, nt, sels_ptr, wts_ptr, rowsum_ptr=None):
+        """Allocation-free router + top-k on device pointers (asynchronous; see dnb200.h)."""
+        return check(self.lib.dnb_router_topk_static(self.h, layer, C.c_void_p(x_ptr), nt, C.c_void_p(sels_ptr),
+                                                     C.c_void_p(wts_ptr),
+                                                     C.c_void_p(rowsum_ptr) if rowsum_ptr else None), True)
+
     def grouped_gemm(self, layer, matrix, segs, xs, n_out):
         segs = np.ascontiguousarray(segs, np.uint32)
         xs = _f32(xs)

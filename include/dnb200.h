@@ -161,6 +161,23 @@ int dnb_moe_experts(dnb_ctx* ctx, int layer, const float* x, int nt, const int32
  * x host [nt][n_embd]; sels [nt][k], wts [nt][k], rowsum [nt] (sum of the selected
  * probabilities before renorm; may be NULL). */
 int dnb_router_topk(dnb_ctx* ctx, int layer, const float* x, int nt, int32_t* sels, float* wts, float* rowsum);
+/* Router + top-k for callers that must not allocate: a serving loop with a fixed
+ * memory budget, a host that forbids cudaMalloc on its inference thread, or code
+ * inside a stream capture.  (No counterpart in the reference: its router path grows
+ * its scratch on demand, cuda.rs:7454-7480.)  Same kernels and same results as
+ * dnb_router_topk, but all of x, sels [nt][k], wts [nt][k] and rowsum [nt] (may be
+ * NULL) are DEVICE pointers supplied by the caller, the call runs asynchronously on
+ * the context's stream, and the logits between the two kernels live in a fixed
+ * 256 KiB array inside the library instead of the workspace: nt * n_expert must not
+ * exceed 65536, larger calls are rejected with DNB_ERR_ARG.  The call performs no
+ * cudaMalloc/cudaFree and no other allocating call.  The first call on each device
+ * looks up the array's device address (cudaGetSymbolAddress) and sets a kernel
+ * attribute; make that first call before any stream capture begins.  All calls on
+ * a device share the one array: two calls that overlap on the GPU (different
+ * streams or contexts) race; calls on one stream are ordered and safe.  Nothing in
+ * the array needs to start at zero (every logit in range is rewritten per call). */
+int dnb_router_topk_static(dnb_ctx* ctx, int layer, const float* x_dev, int nt, int32_t* sels_dev, float* wts_dev,
+                           float* rowsum_dev);
 /* Grouped per-expert GEMM on packed rows (cuda.rs:7065-7075 moe_grouped_gemm_layer,
  * moe_expert.rs:8455 grouped_expert_gemm_cpu): segs[nseg][4] = (expert, m, x_off,
  * out_off) with offsets in rows; xs host [m_total][n_in]; outs host
