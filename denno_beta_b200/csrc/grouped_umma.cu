@@ -21,16 +21,16 @@
 // relative per product.
 //
 // Operands.
-//   A (weights): four warps dequantise Q4_K bytes straight from global memory,
-//      one row per thread and 64 elements per stage, split to hi/lo bf16 and store
+//   A (weights): eight warps dequantise Q4_K bytes straight from global memory,
+//      two threads per row and 64 elements per stage, split to hi/lo bf16 and store
 //      the two tiles in the K-major 128-byte-swizzled layout the MMA reads.
 //   B (activations): a pre-pass gathers the routed token rows into the expert-major
 //      packed order and splits them into hi/lo bf16 buffers once per layer; the
 //      tiles then arrive by TMA (cp.async.bulk.tensor.2d, 128B swizzle), N rows x 64
 //      elements, signalled on the stage's mbarrier.
-// Pipeline: `full[s]` (4 producer-warp arrivals + TMA bytes) -> MMA thread ->
+// Pipeline: `full[s]` (8 producer-warp arrivals + TMA bytes) -> MMA thread ->
 // tcgen05.commit -> `empty[s]`; after the last stage a commit on `accum`.
-// Epilogue: the four producer warps read their 32 TMEM lanes (= weight rows) with
+// Epilogue: producer warps 0-3 read their 32 TMEM lanes (= weight rows) with
 // tcgen05.ld; gate/up tiles are combined as silu(g)*u and written as hi/lo bf16 in
 // packed-row order (the B operand of the down GEMM); down tiles are written as
 // fp32 rows for the weighted combine.
@@ -50,7 +50,8 @@ namespace um {
 constexpr int BK = 64;            // K elements per stage (one 128-byte swizzle row of bf16)
 constexpr int TILE_M = 128;       // weight rows per CTA
 constexpr int A_TILE = TILE_M * BK * 2;   // 16 KB
-constexpr int NTHREADS = 192;     // warps 0-3 producers/epilogue, warp 4 TMA, warp 5 MMA + TMEM
+constexpr int PWARPS = 8;         // producer warps: two threads per weight row (low / high nibble half of a stage)
+constexpr int NTHREADS = (PWARPS + 2) * 32;  // warps 0-7 producers (0-3 also epilogue), warp 8 TMA, warp 9 MMA + TMEM
 
 __device__ __forceinline__ uint32_t s32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mb_init(uint64_t* b, uint32_t n) {
@@ -148,7 +149,7 @@ __device__ __forceinline__ void split2(float a, float b, uint32_t& hi_pair, uint
 // the swizzled tiles.  hdr = first 16 bytes of the block, q0/q1 = the chunk's 32 qs
 // bytes.  Element k of the stage: k < 32 low nibble of byte k, k >= 32 high nibble of
 // byte k - 32 (kquant.rs:505-526).
-__device__ __forceinline__ void dequant_q4k_stage(const uint4& hdr, const uint4& q0, const uint4& q1, int j,
+__device__ __forceinline__ void dequant_q4k_stage(const uint4& hdr, const uint4& q0, const uint4& q1, int j, int half,
                                                   uint8_t* tile_hi, uint8_t* tile_lo, int r) {
     const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xFFFF)));
     const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
@@ -157,40 +158,31 @@ __device__ __forceinline__ void dequant_q4k_stage(const uint4& hdr, const uint4&
         const uint32_t w = i < 4 ? hdr.y : (i < 8 ? hdr.z : hdr.w);
         return (w >> (8 * (i & 3))) & 0xFFu;
     };
-    uint32_t sc1, m1, sc2, m2;
-    {
-        const int a = 2 * j, b = 2 * j + 1;
-        if (a < 4) { sc1 = sb(a) & 63; m1 = sb(a + 4) & 63; }
-        else { sc1 = (sb(a + 4) & 0xF) | ((sb(a - 4) >> 6) << 4); m1 = (sb(a + 4) >> 4) | ((sb(a) >> 6) << 4); }
-        if (b < 4) { sc2 = sb(b) & 63; m2 = sb(b + 4) & 63; }
-        else { sc2 = (sb(b + 4) & 0xF) | ((sb(b - 4) >> 6) << 4); m2 = (sb(b + 4) >> 4) | ((sb(b) >> 6) << 4); }
-    }
-    const float d1 = d * (float)sc1, d2 = d * (float)sc2;
-    const float c1 = fmaf(128.0f, d1, dmin * (float)m1), c2 = fmaf(128.0f, d2, dmin * (float)m2);
+    // this thread's sub-block: 2j (low nibbles, k 0..31) or 2j + 1 (high nibbles, k 32..63)
+    const int a = 2 * j + half;
+    uint32_t sc, mn;
+    if (a < 4) { sc = sb(a) & 63; mn = sb(a + 4) & 63; }
+    else { sc = (sb(a + 4) & 0xF) | ((sb(a - 4) >> 6) << 4); mn = (sb(a + 4) >> 4) | ((sb(a) >> 6) << 4); }
+    const float d1 = d * (float)sc;
+    const float c1 = fmaf(128.0f, d1, dmin * (float)mn);
     const uint32_t rowoff = (uint32_t)(r >> 3) * 1024u + (uint32_t)(r & 7) * 128u;
     const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+    const int sh = half * 4;
 #pragma unroll
-    for (int g = 0; g < 4; ++g) {  // 8 low-nibble elements k = 8g..8g+7 and 8 high-nibble elements k = 32+8g..
-        uint32_t hl[4], ll[4], hh[4], lh[4];
+    for (int g = 0; g < 4; ++g) {  // 8 elements k = 32*half + 8g .. +7 from bytes 8g..8g+7
+        uint32_t hv[4], lv[4];
 #pragma unroll
         for (int w2 = 0; w2 < 2; ++w2) {
-            const uint32_t w = qw[2 * g + w2];
-            const uint32_t lo = w & 0x0F0F0F0Fu, hi = (w >> 4) & 0x0F0F0F0Fu;
+            const uint32_t nib = (qw[2 * g + w2] >> sh) & 0x0F0F0F0Fu;
             // w = d1 * q - m1 evaluated as d1 * (128 + q) - (128 d1 + m1): one fma on an exact float
-            const float a0 = fmaf(d1, magic128<0>(lo), -c1), a1 = fmaf(d1, magic128<1>(lo), -c1);
-            const float a2 = fmaf(d1, magic128<2>(lo), -c1), a3 = fmaf(d1, magic128<3>(lo), -c1);
-            const float b0 = fmaf(d2, magic128<0>(hi), -c2), b1 = fmaf(d2, magic128<1>(hi), -c2);
-            const float b2 = fmaf(d2, magic128<2>(hi), -c2), b3 = fmaf(d2, magic128<3>(hi), -c2);
-            split2(a0, a1, hl[2 * w2], ll[2 * w2]);
-            split2(a2, a3, hl[2 * w2 + 1], ll[2 * w2 + 1]);
-            split2(b0, b1, hh[2 * w2], lh[2 * w2]);
-            split2(b2, b3, hh[2 * w2 + 1], lh[2 * w2 + 1]);
+            const float a0 = fmaf(d1, magic128<0>(nib), -c1), a1 = fmaf(d1, magic128<1>(nib), -c1);
+            const float a2 = fmaf(d1, magic128<2>(nib), -c1), a3 = fmaf(d1, magic128<3>(nib), -c1);
+            split2(a0, a1, hv[2 * w2], lv[2 * w2]);
+            split2(a2, a3, hv[2 * w2 + 1], lv[2 * w2 + 1]);
         }
-        const uint32_t cl = ((uint32_t)(g ^ (r & 7))) << 4, ch = ((uint32_t)((4 + g) ^ (r & 7))) << 4;
-        *reinterpret_cast<uint4*>(tile_hi + rowoff + cl) = make_uint4(hl[0], hl[1], hl[2], hl[3]);
-        *reinterpret_cast<uint4*>(tile_lo + rowoff + cl) = make_uint4(ll[0], ll[1], ll[2], ll[3]);
-        *reinterpret_cast<uint4*>(tile_hi + rowoff + ch) = make_uint4(hh[0], hh[1], hh[2], hh[3]);
-        *reinterpret_cast<uint4*>(tile_lo + rowoff + ch) = make_uint4(lh[0], lh[1], lh[2], lh[3]);
+        const uint32_t col = ((uint32_t)((4 * half + g) ^ (r & 7))) << 4;
+        *reinterpret_cast<uint4*>(tile_hi + rowoff + col) = make_uint4(hv[0], hv[1], hv[2], hv[3]);
+        *reinterpret_cast<uint4*>(tile_lo + rowoff + col) = make_uint4(lv[0], lv[1], lv[2], lv[3]);
     }
 }
 
@@ -228,13 +220,13 @@ grouped_q4k_umma_kernel(const SegDesc* __restrict__ seg, const int32_t* __restri
 
     if (tid == 0) {
         for (int i = 0; i < STAGES; ++i) {
-            mb_init(&full[i], 5);    // 4 producer warps + the TMA thread's expect_tx arrival
+            mb_init(&full[i], PWARPS + 1);  // producer warps + the TMA thread's expect_tx arrival
             mb_init(&empty[i], 1);   // one tcgen05.commit
         }
         mb_init(accum, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 5) {
+    if (warp == PWARPS + 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(tmem_slot)), "r"(TM_COLS)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -245,9 +237,9 @@ grouped_q4k_umma_kernel(const SegDesc* __restrict__ seg, const int32_t* __restri
     const uint32_t tmem_base = *tmem_slot;
     bool ok = true;
 
-    if (warp < 4) {
-        // ---------------- producers: dequantise one weight row per thread ----------------
-        const int r = tid;  // 0..127
+    if (warp < PWARPS) {
+        // ---------------- producers: two threads per weight row ----------------
+        const int r = tid & 127, half = tid >> 7;
         const uint8_t* rowa = sd.wa + (size_t)(r0 + r) * rb;
         const uint8_t* rowb = (NMAT == 2) ? sd.wb + (size_t)(r0 + r) * rb : nullptr;
         uint4 hdr_a, qa0, qa1, hdr_b, qb0, qb1;
@@ -273,16 +265,16 @@ grouped_q4k_umma_kernel(const SegDesc* __restrict__ seg, const int32_t* __restri
             if (c >= STAGES) ok = mb_wait(&empty[st], ph ^ 1u, status, 2);
             if (!ok) break;
             uint8_t* sa = smem + st * STAGE_BYTES;
-            dequant_q4k_stage(ha, a0, a1, c & 3, sa, sa + A_TILE, r);
-            if constexpr (NMAT == 2) dequant_q4k_stage(hb, b0, b1, c & 3, sa + 2 * A_TILE, sa + 3 * A_TILE, r);
+            dequant_q4k_stage(ha, a0, a1, c & 3, half, sa, sa + A_TILE, r);
+            if constexpr (NMAT == 2) dequant_q4k_stage(hb, b0, b1, c & 3, half, sa + 2 * A_TILE, sa + 3 * A_TILE, r);
             fence_async_smem();   // generic-proxy stores -> visible to the tensor core's async proxy
             __syncwarp();
             if (lane == 0) mb_arrive(&full[st]);
         }
         // ---------------- epilogue: TMEM lane = weight row ----------------
-        if (ok) ok = mb_wait(accum, 0, status, 3);
+        if (ok && warp < 4) ok = mb_wait(accum, 0, status, 3);
         tc_fence_after();
-        if (ok) {
+        if (ok && warp < 4) {
             const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
             const size_t prow0 = (size_t)sd.row0 + t0;
             for (int c0 = 0; c0 < N; c0 += 16) {
@@ -310,7 +302,7 @@ grouped_q4k_umma_kernel(const SegDesc* __restrict__ seg, const int32_t* __restri
             }
         }
         tc_fence_before();
-    } else if (warp == 4) {
+    } else if (warp == PWARPS) {
         // ---------------- TMA: activation tiles ----------------
         if (lane == 0) {
             const CUtensorMap* mh = &maps.hi[nsel];
@@ -359,7 +351,7 @@ grouped_q4k_umma_kernel(const SegDesc* __restrict__ seg, const int32_t* __restri
         __syncwarp();
     }
     __syncthreads();
-    if (warp == 5) {
+    if (warp == PWARPS + 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TM_COLS) : "memory");
     }

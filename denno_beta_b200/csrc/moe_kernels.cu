@@ -60,7 +60,8 @@ int launch_prep(dnb_ctx* c, cudaStream_t st, const float* h, const float* w, flo
 // logits[t][i] = W_r[i] . x_t + bias[i].  One warp per expert row, the row read
 // once as coalesced float4 and applied to up to RT tokens staged in shared memory.
 constexpr int RT = 8;         // tokens per CTA
-constexpr int RROWS = 4;      // expert rows (warps) per CTA
+constexpr int RROWS = 4;      // warps per CTA
+constexpr int RW = 4;         // expert rows per warp
 __global__ void __launch_bounds__(RROWS * 32)
 router_logits_kernel(const float* __restrict__ x, int nt, int e, const float* __restrict__ w_r,
                      const float* __restrict__ bias, int ne, float* __restrict__ logits) {
@@ -72,33 +73,54 @@ router_logits_kernel(const float* __restrict__ x, int nt, int e, const float* __
         reinterpret_cast<float4*>(xs)[i] = reinterpret_cast<const float4*>(x + (size_t)t0 * e)[i];
     __syncthreads();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int row = blockIdx.x * RROWS + warp;
-    if (row >= ne) return;
-    const float4* wr = reinterpret_cast<const float4*>(w_r + (size_t)row * e);
-    float acc[RT];
+    // a warp owns RW consecutive expert rows: every activation word read from shared
+    // memory feeds RW rows (the kernel is otherwise bound by that shared-memory traffic)
+    const int row0 = (blockIdx.x * RROWS + warp) * RW;
+    if (row0 >= ne) return;
+    const float4* wr[RW];
 #pragma unroll
-    for (int t = 0; t < RT; ++t) acc[t] = 0.f;
+    for (int r = 0; r < RW; ++r) wr[r] = reinterpret_cast<const float4*>(w_r + (size_t)min(row0 + r, ne - 1) * e);
+    float acc[RW][RT];
+#pragma unroll
+    for (int r = 0; r < RW; ++r)
+#pragma unroll
+        for (int t = 0; t < RT; ++t) acc[r][t] = 0.f;
     for (int i = lane; i < e4; i += 32) {
-        const float4 wv = __ldg(wr + i);
+        float4 wv[RW];
+#pragma unroll
+        for (int r = 0; r < RW; ++r) wv[r] = __ldg(wr[r] + i);
 #pragma unroll
         for (int t = 0; t < RT; ++t) {
             if (t < ntok) {
                 const float4 xv = reinterpret_cast<const float4*>(xs)[t * e4 + i];
-                acc[t] = fmaf(wv.x, xv.x, acc[t]);
-                acc[t] = fmaf(wv.y, xv.y, acc[t]);
-                acc[t] = fmaf(wv.z, xv.z, acc[t]);
-                acc[t] = fmaf(wv.w, xv.w, acc[t]);
+#pragma unroll
+                for (int r = 0; r < RW; ++r) {
+                    acc[r][t] = fmaf(wv[r].x, xv.x, acc[r][t]);
+                    acc[r][t] = fmaf(wv[r].y, xv.y, acc[r][t]);
+                    acc[r][t] = fmaf(wv[r].z, xv.z, acc[r][t]);
+                    acc[r][t] = fmaf(wv[r].w, xv.w, acc[r][t]);
+                }
             }
         }
     }
 #pragma unroll
-    for (int t = 0; t < RT; ++t) {
+    for (int r = 0; r < RW; ++r)
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) acc[t] += __shfl_xor_sync(0xffffffffu, acc[t], o);
-    }
+        for (int t = 0; t < RT; ++t) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) acc[r][t] += __shfl_xor_sync(0xffffffffu, acc[r][t], o);
+        }
     if (lane == 0) {
-        const float b = bias ? bias[row] : 0.f;
-        for (int t = 0; t < ntok; ++t) logits[(size_t)(t0 + t) * ne + row] = bias ? acc[t] + b : acc[t];
+#pragma unroll
+        for (int r = 0; r < RW; ++r) {
+            const int row = row0 + r;
+            if (row < ne) {
+                const float b = bias ? bias[row] : 0.f;
+#pragma unroll
+                for (int t = 0; t < RT; ++t)
+                    if (t < ntok) logits[(size_t)(t0 + t) * ne + row] = bias ? acc[r][t] + b : acc[r][t];
+            }
+        }
     }
 }
 
@@ -125,7 +147,7 @@ int launch_router_logits(dnb_ctx* c, cudaStream_t st, const float* x, int nt, in
     const size_t smem = (size_t)RT * e * sizeof(float);
     int rc = router_smem_at_least(c->device, smem);
     if (rc) return rc;
-    dim3 grid((ne + RROWS - 1) / RROWS, (nt + RT - 1) / RT);
+    dim3 grid((ne + RROWS * RW - 1) / (RROWS * RW), (nt + RT - 1) / RT);
     ProfScope prof_(c, st, "router_logits");
     router_logits_kernel<<<grid, RROWS * 32, smem, st>>>(x, nt, e, w_r, bias, ne, logits);
     c->launches++;
@@ -531,7 +553,7 @@ extern "C" int dnb_router_topk_static(dnb_ctx* c, int layer, const float* x_dev,
     }
     float* logits = g_static_logits_ptr[c->device];
     const Layer& L = M.layers[layer];
-    const dim3 grid((M.ne + RROWS - 1) / RROWS, (nt + RT - 1) / RT);
+    const dim3 grid((M.ne + RROWS * RW - 1) / (RROWS * RW), (nt + RT - 1) / RT);
     // every logit of the [nt][n_expert] range is written before it is read, so the
     // previous call's contents need no clearing
     router_logits_kernel<<<grid, RROWS * 32, smem, c->stream>>>(x_dev, nt, M.e, L.router_w, L.router_bias, M.ne, logits);
