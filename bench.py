@@ -277,10 +277,10 @@ def extras(ctx, cu, oracle):
     return out
 
 
-def prefill_extras(cu, oracle, device):
+def prefill_extras(cu, oracle, device, layers=4):
     """Config 2: one MoE block, one 512-token chunk, Q4_K experts, Zipf router bias.
-    Rotates over 4 layer copies (3.6 GB of weights); tokens stay on the device."""
-    layers, nt = 4, 512
+    Rotates over `layers` layer copies (0.9 GB of weights each); tokens stay on the device."""
+    nt = 512
     ctx = cu.CudaCtx(device)
     out = {}
     try:
@@ -386,6 +386,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=50)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="rotating layer copies (default %d; fewer for profiler captures)" % LAYERS)
+    ap.add_argument("--prefill-only", action="store_true",
+                    help="run only the config-2 prefill measurement (small: for profiler captures)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-extras", action="store_true", help="skip the config-0 GEMV line")
     args = ap.parse_args()
@@ -394,7 +396,12 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.impl == "reference":
+    if args.prefill_only:
+        import oracle
+        from denno_beta_b200 import cuda as cu
+
+        res = {"config2_q4k_prefill_512": prefill_extras(cu, oracle, local_rank, layers=max(args.layers, 1))}
+    elif args.impl == "reference":
         res = run_reference(args, rank)
     else:
         if world > 1:

@@ -242,34 +242,45 @@ grouped_q4k_umma_kernel(const SegDesc* __restrict__ seg, const int32_t* __restri
         const int r = tid & 127, half = tid >> 7;
         const uint8_t* rowa = sd.wa + (size_t)(r0 + r) * rb;
         const uint8_t* rowb = (NMAT == 2) ? sd.wb + (size_t)(r0 + r) * rb : nullptr;
-        uint4 hdr_a, qa0, qa1, hdr_b, qb0, qb1;
-        auto fetch = [&](int c) {
+        // Raw bytes of a stage: header + this stage's 32 qs bytes, per matrix.  Four
+        // register buffers keep the loads of three stages ahead in flight (the rows
+        // are 1152 or 288 bytes apart, so these are latency-bound 32-byte reads).
+        struct Raw { uint4 ha, a0, a1, hb, b0, b1; };
+        Raw buf[4];
+        auto fetch = [&](Raw& q, int c) {
             const int b = c >> 2, j = c & 3;
             const uint8_t* pa = rowa + b * 144;
-            hdr_a = __ldg(reinterpret_cast<const uint4*>(pa));
-            qa0 = __ldcs(reinterpret_cast<const uint4*>(pa + 16 + 32 * j));
-            qa1 = __ldcs(reinterpret_cast<const uint4*>(pa + 32 + 32 * j));
+            q.ha = __ldg(reinterpret_cast<const uint4*>(pa));
+            q.a0 = __ldcs(reinterpret_cast<const uint4*>(pa + 16 + 32 * j));
+            q.a1 = __ldcs(reinterpret_cast<const uint4*>(pa + 32 + 32 * j));
             if constexpr (NMAT == 2) {
                 const uint8_t* pb = rowb + b * 144;
-                hdr_b = __ldg(reinterpret_cast<const uint4*>(pb));
-                qb0 = __ldcs(reinterpret_cast<const uint4*>(pb + 16 + 32 * j));
-                qb1 = __ldcs(reinterpret_cast<const uint4*>(pb + 32 + 32 * j));
+                q.hb = __ldg(reinterpret_cast<const uint4*>(pb));
+                q.b0 = __ldcs(reinterpret_cast<const uint4*>(pb + 16 + 32 * j));
+                q.b1 = __ldcs(reinterpret_cast<const uint4*>(pb + 32 + 32 * j));
             }
         };
-        fetch(0);
-        for (int c = 0; c < nchunks && ok; ++c) {
-            const int st = c % STAGES;
-            const uint32_t ph = (uint32_t)(c / STAGES) & 1u;
-            const uint4 ha = hdr_a, a0 = qa0, a1 = qa1, hb = hdr_b, b0 = qb0, b1 = qb1;
-            if (c + 1 < nchunks) fetch(c + 1);  // next stage's bytes are in flight while this one is decoded
-            if (c >= STAGES) ok = mb_wait(&empty[st], ph ^ 1u, status, 2);
-            if (!ok) break;
-            uint8_t* sa = smem + st * STAGE_BYTES;
-            dequant_q4k_stage(ha, a0, a1, c & 3, half, sa, sa + A_TILE, r);
-            if constexpr (NMAT == 2) dequant_q4k_stage(hb, b0, b1, c & 3, half, sa + 2 * A_TILE, sa + 3 * A_TILE, r);
-            fence_async_smem();   // generic-proxy stores -> visible to the tensor core's async proxy
-            __syncwarp();
-            if (lane == 0) mb_arrive(&full[st]);
+        fetch(buf[0], 0);
+        fetch(buf[1], 1);
+        fetch(buf[2], 2);
+        for (int c4 = 0; c4 < nchunks && ok; c4 += 4) {  // nchunks is a multiple of 4 (n_in % 256 == 0)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int c = c4 + i;
+                if (c + 3 < nchunks) fetch(buf[(i + 3) & 3], c + 3);
+                const int st = c % STAGES;
+                const uint32_t ph = (uint32_t)(c / STAGES) & 1u;
+                if (ok && c >= STAGES) ok = mb_wait(&empty[st], ph ^ 1u, status, 2);
+                if (ok) {
+                    uint8_t* sa = smem + st * STAGE_BYTES;
+                    dequant_q4k_stage(buf[i].ha, buf[i].a0, buf[i].a1, c & 3, half, sa, sa + A_TILE, r);
+                    if constexpr (NMAT == 2)
+                        dequant_q4k_stage(buf[i].hb, buf[i].b0, buf[i].b1, c & 3, half, sa + 2 * A_TILE, sa + 3 * A_TILE, r);
+                    fence_async_smem();   // generic-proxy stores -> visible to the tensor core's async proxy
+                    __syncwarp();
+                    if (lane == 0) mb_arrive(&full[st]);
+                }
+            }
         }
         // ---------------- epilogue: TMEM lane = weight row ----------------
         if (ok && warp < 4) ok = mb_wait(accum, 0, status, 3);

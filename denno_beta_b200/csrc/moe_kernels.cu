@@ -568,94 +568,98 @@ namespace dnb {
 // ---- routing tables -----------------------------------------------------------
 // From sels[nt][k] build the expert-major packed row space the grouped matmuls
 // work in (qwen4exp.rs:18172-18185 by_expert; moe_expert.rs:8309-8390
-// build_grouped_batch; exp_pf.rs:23-31 rows[]): experts in ascending index, the
-// rows of an expert in ascending token order.  One CTA; membership bitmap in
-// shared memory; counts by ballot, so the result does not depend on timing.
+// build_grouped_batch; exp_pf.rs:23-31 rows[]): segments by token count descending
+// (ties: expert ascending), the rows of an expert in ascending token order.  A grid
+// of CTAs, 16 experts each; every CTA rebuilds the membership bitmap and the counts
+// in shared memory, so the result does not depend on timing.
 //   row_token[row] = token of the packed row       pos[t*k+slot] = packed row
 //   seg_gu/seg_dn[i] = i-th active expert's matrices, m and first row; *nseg
-__global__ void __launch_bounds__(1024)
+constexpr int RTE = 16;  // experts per CTA of the routing-table kernel
+
+__global__ void __launch_bounds__(256)
 route_tables_kernel(const int32_t* __restrict__ sels, int nt, int k, int ne, const uint8_t* gate, const uint8_t* up,
                     const uint8_t* down, size_t eb_g, size_t eb_u, size_t eb_d, const uint8_t* sg, const uint8_t* su,
                     const uint8_t* sdn, SegDesc* seg_gu, SegDesc* seg_dn, int32_t* row_token, int32_t* pos,
                     int32_t* nseg, int32_t* counts_out) {
+    // Every CTA rebuilds the (small) membership bitmap and the per-expert counts from
+    // sels, then finishes the table entries of its own RTE experts.  Counts are
+    // integer sums, so their value does not depend on the order of the atomic adds.
     extern __shared__ uint32_t sm[];
     const int words = (ne + 31) >> 5;
     uint32_t* bitmap = sm;                          // [nt][words]
     int* counts = (int*)(sm + (size_t)nt * words);  // [ne]
-    int* offs = counts + ne;                        // [ne] first packed row of the expert's segment
-    int* segi = offs + ne;                          // [ne] segment index of active experts, -1 otherwise
-    __shared__ int n_active;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = blockDim.x >> 5;
     for (int i = tid; i < nt * words; i += blockDim.x) bitmap[i] = 0;
+    for (int i = tid; i < ne; i += blockDim.x) counts[i] = 0;
     __syncthreads();
     for (int i = tid; i < nt * k; i += blockDim.x) {
         const int e = sels[i];
-        if (e >= 0 && e < ne) atomicOr(&bitmap[(size_t)(i / k) * words + (e >> 5)], 1u << (e & 31));
-    }
-    __syncthreads();
-    for (int e = warp; e < ne; e += nwarp) {
-        int cnt = 0;
-        for (int t0 = 0; t0 < nt; t0 += 32) {
-            const int t = t0 + lane;
-            const bool has = t < nt && ((bitmap[(size_t)t * words + (e >> 5)] >> (e & 31)) & 1u);
-            cnt += __popc(__ballot_sync(0xffffffffu, has));
+        if (e >= 0 && e < ne) {
+            atomicOr(&bitmap[(size_t)(i / k) * words + (e >> 5)], 1u << (e & 31));
+            atomicAdd(&counts[e], 1);
         }
-        if (lane == 0) counts[e] = cnt;
     }
     __syncthreads();
+    const int e0 = blockIdx.x * RTE;
+    if (blockIdx.x == 0) {
+        // number of active experts; the shared expert's segment and identity rows
+        int part = 0;
+        for (int i = tid; i < ne; i += blockDim.x) part += counts[i] > 0 ? 1 : 0;
+        __shared__ int red[8];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+        if (lane == 0) red[warp] = part;
+        __syncthreads();
+        if (tid == 0) {
+            int n_active = 0;
+            for (int w = 0; w < nwarp; ++w) n_active += red[w];
+            if (sg) {
+                seg_gu[n_active] = SegDesc{sg, su, (uint32_t)nt, (uint32_t)(nt * k)};
+                seg_dn[n_active] = SegDesc{sdn, nullptr, (uint32_t)nt, (uint32_t)(nt * k)};
+                n_active++;
+            }
+            *nseg = n_active;
+        }
+        if (sg)
+            for (int t = tid; t < nt; t += blockDim.x) row_token[nt * k + t] = t;
+        if (counts_out)
+            for (int i = tid; i < ne; i += blockDim.x) counts_out[i] = counts[i];
+    }
     // Segment order: token count descending, ties by ascending expert index
-    // (moe_expert.rs:8344), so the heavy segments are scheduled first.  Each
-    // expert finds its own rank and first row by scanning the counts.
-    for (int e = tid; e < ne; e += blockDim.x) {
+    // (moe_expert.rs:8344).  A warp finds the rank and first row of one expert: its
+    // lanes split the other experts and the partial sums meet in an xor tree.
+    for (int ei = warp; ei < RTE; ei += nwarp) {
+        const int e = e0 + ei;
+        if (e >= ne) break;
         const int c = counts[e];
+        if (c == 0) continue;  // uniform across the warp
         int rank = 0, row = 0;
-        if (c > 0) {
-            for (int o = 0; o < ne; ++o) {
-                const int co = counts[o];
-                if (co > c || (co == c && o < e)) {
-                    rank++;
-                    row += co;
-                }
+        for (int o = lane; o < ne; o += 32) {
+            const int co = counts[o];
+            if (co > c || (co == c && o < e)) {
+                rank++;
+                row += co;
             }
         }
-        segi[e] = c > 0 ? rank : -1;
-        offs[e] = row;
-    }
-    if (tid == 0) n_active = 0;
-    __syncthreads();
-    for (int e = tid; e < ne; e += blockDim.x) {
-        if (counts_out) counts_out[e] = counts[e];
-        if (counts[e] > 0) {
-            atomicAdd(&n_active, 1);  // a count: its value does not depend on the order of the adds
-            const int si = segi[e];
-            seg_gu[si] = SegDesc{gate + (size_t)e * eb_g, up + (size_t)e * eb_u, (uint32_t)counts[e], (uint32_t)offs[e]};
-            seg_dn[si] = SegDesc{down + (size_t)e * eb_d, nullptr, (uint32_t)counts[e], (uint32_t)offs[e]};
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            rank += __shfl_xor_sync(0xffffffffu, rank, o);
+            row += __shfl_xor_sync(0xffffffffu, row, o);
         }
-    }
-    __syncthreads();
-    if (tid == 0) {
-        int na = n_active;
-        if (sg) {
-            seg_gu[na] = SegDesc{sg, su, (uint32_t)nt, (uint32_t)(nt * k)};
-            seg_dn[na] = SegDesc{sdn, nullptr, (uint32_t)nt, (uint32_t)(nt * k)};
-            na++;
+        if (lane == 0) {
+            seg_gu[rank] = SegDesc{gate + (size_t)e * eb_g, up + (size_t)e * eb_u, (uint32_t)c, (uint32_t)row};
+            seg_dn[rank] = SegDesc{down + (size_t)e * eb_d, nullptr, (uint32_t)c, (uint32_t)row};
         }
-        *nseg = na;
-    }
-    if (sg)
-        for (int t = tid; t < nt; t += blockDim.x) row_token[nt * k + t] = t;
-    for (int e = warp; e < ne; e += nwarp) {
-        if (counts[e] == 0) continue;
-        int run = offs[e];
+        int run = row;
         for (int t0 = 0; t0 < nt; t0 += 32) {
             const int t = t0 + lane;
             const bool has = t < nt && ((bitmap[(size_t)t * words + (e >> 5)] >> (e & 31)) & 1u);
             const uint32_t b = __ballot_sync(0xffffffffu, has);
             if (has) {
-                const int row = run + __popc(b & ((1u << lane) - 1u));
-                row_token[row] = t;
+                const int prow = run + __popc(b & ((1u << lane) - 1u));
+                row_token[prow] = t;
                 for (int s = 0; s < k; ++s)
-                    if (sels[(size_t)t * k + s] == e) pos[(size_t)t * k + s] = row;
+                    if (sels[(size_t)t * k + s] == e) pos[(size_t)t * k + s] = prow;
             }
             run += __popc(b);
         }
@@ -665,7 +669,7 @@ route_tables_kernel(const int32_t* __restrict__ sels, int nt, int k, int ne, con
 int launch_route_tables(dnb_ctx* c, cudaStream_t st, const int32_t* sels, int nt, int k, int ne, const Layer& L,
                         Workspace& ws, bool fold_shared) {
     const int words = (ne + 31) >> 5;
-    const size_t smem = ((size_t)nt * words + 3 * (size_t)ne) * 4;
+    const size_t smem = ((size_t)nt * words + (size_t)ne) * 4;
     if (smem > 200 * 1024) {
         set_error("route tables: %d tokens x %d experts exceeds one CTA's shared memory", nt, ne);
         return DNB_DECLINED;
@@ -675,12 +679,11 @@ int launch_route_tables(dnb_ctx* c, cudaStream_t st, const int32_t* sels, int nt
         DNB_CUDA(cudaFuncSetAttribute(route_tables_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         smem_set = smem;
     }
-    const int thr = nt * k >= 512 ? 1024 : 256;
     ProfScope prof_(c, st, "route_tables");
-    route_tables_kernel<<<1, thr, smem, st>>>(sels, nt, k, ne, L.m[0].dev, L.m[1].dev, L.m[2].dev, L.m[0].expert_bytes,
-                                              L.m[1].expert_bytes, L.m[2].expert_bytes, fold_shared ? L.m[3].dev : nullptr,
-                                              fold_shared ? L.m[4].dev : nullptr, fold_shared ? L.m[5].dev : nullptr,
-                                              ws.seg_gu, ws.seg_dn, ws.row_token, ws.pos, ws.nseg, ws.counts);
+    route_tables_kernel<<<(ne + RTE - 1) / RTE, 256, smem, st>>>(
+        sels, nt, k, ne, L.m[0].dev, L.m[1].dev, L.m[2].dev, L.m[0].expert_bytes, L.m[1].expert_bytes,
+        L.m[2].expert_bytes, fold_shared ? L.m[3].dev : nullptr, fold_shared ? L.m[4].dev : nullptr,
+        fold_shared ? L.m[5].dev : nullptr, ws.seg_gu, ws.seg_dn, ws.row_token, ws.pos, ws.nseg, ws.counts);
     c->launches++;
     DNB_CUDA(cudaGetLastError());
     return DNB_OK;
