@@ -47,6 +47,10 @@ SIGNATURES = {
     "dnb_router_topk": (_i, [_vp, _i, _vp, _i, _vp, _vp, _vp]),
     "dnb_router_topk_static": (_i, [_vp, _i, _vp, _i, _vp, _vp, _vp]),
     "dnb_grouped_gemm": (_i, [_vp, _i, _i, _vp, _i, _vp, _vp]),
+    "dnb_moe_set_expert_shard": (_i, [_vp, _i, _i]),
+    "dnb_moe_route_dev": (_i, [_vp, _i, _vp, _i, _vp, _vp, _vp]),
+    "dnb_expert_rows_dev": (_i, [_vp, _i, _vp, _vp, _i, _i, _vp]),
+    "dnb_moe_combine_dev": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _i, _vp]),
     "dnb_moe_stack": (_i, [_vp, _vp, _i, _vp]),
     "dnb_moe_stack_dev": (_i, [_vp, _vp, _i]),
 }

@@ -29,7 +29,7 @@ static int dev_alloc(T** p, size_t n) {
 
 static void free_ws(Workspace& w) {
     void* dev[] = {w.xn, w.logits, w.wts, w.act, w.hrow, w.sact, w.sh, w.hin, w.out, w.shcoef, w.sels, w.row_token,
-                   w.pos, w.nseg, w.counts, w.seg_gu, w.seg_dn, w.seg_sh_gu, w.seg_sh_dn, w.xg_hi, w.xg_lo, w.act_hi, w.act_lo};
+                   w.pos, w.nseg, w.counts, w.one, w.seg_gu, w.seg_dn, w.seg_sh_gu, w.seg_sh_dn, w.xg_hi, w.xg_lo, w.act_hi, w.act_lo};
     for (void* p : dev)
         if (p) cudaFree(p);
     if (w.pinned_in) cudaFreeHost(w.pinned_in);
@@ -67,6 +67,11 @@ static int ensure_ws(dnb_ctx* c, int nt) {
     if ((rc = dev_alloc(&w.row_token, rows))) return rc;
     if ((rc = dev_alloc(&w.pos, rows))) return rc;
     if ((rc = dev_alloc(&w.nseg, 1))) return rc;
+    if ((rc = dev_alloc(&w.one, 1))) return rc;
+    {
+        const int32_t one = 1;
+        DNB_CUDA(cudaMemcpy(w.one, &one, sizeof(one), cudaMemcpyHostToDevice));
+    }
     if ((rc = dev_alloc(&w.counts, (size_t)M.ne))) return rc;
     if ((rc = dev_alloc(&w.seg_gu, (size_t)M.ne + 1))) return rc;
     if ((rc = dev_alloc(&w.seg_dn, (size_t)M.ne + 1))) return rc;
@@ -161,6 +166,7 @@ static bool layer_ready(const dnb_ctx* c, int layer, bool need_router) {
     const Layer& L = M.layers[layer];
     if (!L.m[0].dev || !L.m[1].dev || !L.m[2].dev) return false;
     if (need_router && !L.router_w) return false;
+    if (M.shard_count != M.ne) return false;  // only a shard is resident: use the expert-parallel entry points
     return true;
 }
 
@@ -168,13 +174,15 @@ static bool layer_ready(const dnb_ctx* c, int layer, bool need_router) {
 // [nt][e]; sels/wts on the device.  Writes out[nt][e].  The shared expert's
 // segment descriptors must already have been published by launch_prep.
 static int experts_dev(dnb_ctx* c, int layer, const float* x, int nt, const int32_t* sels, const float* wts,
-                       float* out) {
+                       float* out, int k = -1, int ne = -1, int with_shared = -1) {
     const Model& M = c->model;
     const Layer& L = M.layers[layer];
     Workspace& w = c->ws;
     cudaStream_t st = c->stream;
     int rc;
-    const bool shared = L.has_shared();
+    if (k < 0) k = M.k;
+    if (ne < 0) ne = M.ne;
+    const bool shared = with_shared < 0 ? L.has_shared() : (with_shared != 0);
     if (shared) {
         // fork: the shared expert does not depend on the routing
         DNB_CUDA(cudaEventRecord(c->ev_fork, st));
@@ -190,8 +198,8 @@ static int experts_dev(dnb_ctx* c, int layer, const float* x, int nt, const int3
             if ((rc = launch_shared_coef(c, c->side, x, L.shared_gate_row, nt, M.e, w.shcoef))) return rc;
         DNB_CUDA(cudaEventRecord(c->ev_join, c->side));
     }
-    if ((rc = launch_route_tables(c, st, sels, nt, M.k, M.ne, L, w))) return rc;
-    const int nseg_max = nt * M.k < M.ne ? nt * M.k : M.ne;
+    if ((rc = launch_route_tables(c, st, sels, nt, k, ne, L, w))) return rc;
+    const int nseg_max = nt * k < ne ? nt * k : ne;
     if ((rc = launch_seg_matmul(c, st, L.m[0].type, true, w.seg_gu, w.nseg, nseg_max, M.e, M.ff, x, M.e, w.row_token,
                                 w.act, nt)))
         return rc;
@@ -199,7 +207,7 @@ static int experts_dev(dnb_ctx* c, int layer, const float* x, int nt, const int3
                                 w.hrow, nt)))
         return rc;
     if (shared) DNB_CUDA(cudaStreamWaitEvent(st, c->ev_join, 0));
-    return launch_combine(c, st, w.hrow, w.pos, wts, nt, M.k, M.e, shared ? w.sh : nullptr,
+    return launch_combine(c, st, w.hrow, w.pos, wts, nt, k, M.e, shared ? w.sh : nullptr,
                           (shared && L.shared_gate_row) ? w.shcoef : nullptr, out);
 }
 
@@ -260,17 +268,19 @@ static bool umma_eligible(const dnb_ctx* c, const Layer& L, int nt) {
 }
 
 static int experts_dev_umma(dnb_ctx* c, int layer, const float* x, int nt, const int32_t* sels, const float* wts,
-                            float* out) {
+                            float* out, int k = -1, int ne = -1, int with_shared = -1) {
     const Model& M = c->model;
     const Layer& L = M.layers[layer];
     Workspace& w = c->ws;
     cudaStream_t st = c->stream;
-    const bool shared = L.has_shared();
+    if (k < 0) k = M.k;
+    if (ne < 0) ne = M.ne;
+    const bool shared = with_shared < 0 ? L.has_shared() : (with_shared != 0);
     int rc;
-    if ((rc = launch_route_tables(c, st, sels, nt, M.k, M.ne, L, w, shared))) return rc;
-    const int rows = nt * M.k + (shared ? nt : 0);
+    if ((rc = launch_route_tables(c, st, sels, nt, k, ne, L, w, shared))) return rc;
+    const int rows = nt * k + (shared ? nt : 0);
     if ((rc = launch_gather_split(c, st, x, M.e, w.row_token, rows, M.e, w.xg_hi, w.xg_lo))) return rc;
-    const int nseg_max = (nt * M.k < M.ne ? nt * M.k : M.ne) + (shared ? 1 : 0);
+    const int nseg_max = (nt * k < ne ? nt * k : ne) + (shared ? 1 : 0);
     if ((rc = launch_grouped_umma(c, st, true, w.seg_gu, w.nseg, nseg_max, M.e, M.ff, &w.maps_x, nt, w.act_hi, w.act_lo,
                                   nullptr)))
         return rc;
@@ -279,7 +289,7 @@ static int experts_dev_umma(dnb_ctx* c, int layer, const float* x, int nt, const
         return rc;
     if (shared && L.shared_gate_row)
         if ((rc = launch_shared_coef(c, st, x, L.shared_gate_row, nt, M.e, w.shcoef))) return rc;
-    return launch_combine(c, st, w.hrow, w.pos, wts, nt, M.k, M.e, shared ? w.hrow + (size_t)nt * M.k * M.e : nullptr,
+    return launch_combine(c, st, w.hrow, w.pos, wts, nt, k, M.e, shared ? w.hrow + (size_t)nt * k * M.e : nullptr,
                           (shared && L.shared_gate_row) ? w.shcoef : nullptr, out);
 }
 
@@ -621,6 +631,7 @@ int dnb_moe_config(dnb_ctx* c, int n_layer, int e, int ff, int sff, int ne, int 
     free_ws(c->ws);
     Model& M = c->model;
     M.n_layer = n_layer; M.e = e; M.ff = ff; M.sff = sff; M.ne = ne; M.k = k; M.eps = eps; M.norm_topk = norm_topk;
+    M.shard_first = 0; M.shard_count = ne;
     M.layers.assign(n_layer, Layer());
     return DNB_OK;
 }
@@ -640,7 +651,7 @@ static int check_expert_shape(dnb_ctx* c, int layer, int matrix, int type, int n
     const bool shared = matrix >= 3;
     const bool down = (matrix % 3) == 2;
     const int ffx = shared ? (M.sff ? M.sff : M.ff) : M.ff;
-    const int want_in = down ? ffx : M.e, want_out = down ? M.e : ffx, want_ne = shared ? 1 : M.ne;
+    const int want_in = down ? ffx : M.e, want_out = down ? M.e : ffx, want_ne = shared ? 1 : M.shard_count;
     if (n_in != want_in || n_out != want_out || n_expert != want_ne) {
         set_error("experts: matrix %d is [%d x %d] x %d experts, the model needs [%d x %d] x %d", matrix, n_out, n_in,
                   n_expert, want_out, want_in, want_ne);
@@ -889,6 +900,101 @@ int dnb_grouped_gemm(dnb_ctx* c, int layer, int matrix, const uint32_t* segs, in
     cudaFree(dout);
     cudaFree(dsd);
     return rc;
+}
+
+// ---- expert-parallel building blocks ---------------------------------------------------
+
+int dnb_moe_set_expert_shard(dnb_ctx* c, int first_expert, int n_local) {
+    if (!c) return DNB_ERR_ARG;
+    Model& M = c->model;
+    if (M.n_layer < 1 || first_expert < 0 || n_local < 1 || first_expert + n_local > M.ne) {
+        set_error("expert shard [%d, %d) does not fit the %d experts of the model", first_expert, first_expert + n_local, M.ne);
+        return DNB_ERR_ARG;
+    }
+    for (auto& L : M.layers)
+        if (L.m[0].dev || L.m[1].dev || L.m[2].dev) {
+            set_error("expert shard must be set before the expert tensors are registered");
+            return DNB_ERR_STATE;
+        }
+    M.shard_first = first_expert;
+    M.shard_count = n_local;
+    return DNB_OK;
+}
+
+int dnb_moe_route_dev(dnb_ctx* c, int layer, const float* h_dev, int nt, float* x_out_dev, int32_t* sels_dev,
+                      float* wts_dev) {
+    if (!c || !h_dev || !x_out_dev || !sels_dev || !wts_dev || nt < 1) return DNB_ERR_ARG;
+    const Model& M = c->model;
+    if (layer < 0 || layer >= M.n_layer || !M.layers[layer].router_w) {
+        set_error("moe_route: layer %d has no router", layer);
+        return DNB_DECLINED;
+    }
+    int rc = ensure_ws(c, nt);
+    if (rc) return rc;
+    const Layer& L = M.layers[layer];
+    if (L.norm_w) {
+        if ((rc = launch_rmsnorm(c, c->stream, h_dev, L.norm_w, M.eps, nt, M.e, x_out_dev))) return rc;
+    } else if (x_out_dev != h_dev) {
+        DNB_CUDA(cudaMemcpyAsync(x_out_dev, h_dev, (size_t)nt * M.e * 4, cudaMemcpyDeviceToDevice, c->stream));
+    }
+    if ((rc = launch_router_logits(c, c->stream, x_out_dev, nt, M.e, L.router_w, L.router_bias, M.ne, c->ws.logits))) return rc;
+    return launch_topk(c, c->stream, c->ws.logits, nt, M.ne, M.k, M.norm_topk, sels_dev, wts_dev, nullptr);
+}
+
+int dnb_expert_rows_dev(dnb_ctx* c, int layer, const float* x_rows_dev, const int32_t* local_ids_dev, int rows,
+                        int use_shared, float* h_rows_dev) {
+    if (!c || !x_rows_dev || !h_rows_dev || rows < 1 || (!use_shared && !local_ids_dev)) return DNB_ERR_ARG;
+    const Model& M = c->model;
+    if (layer < 0 || layer >= M.n_layer) return DNB_ERR_ARG;
+    const Layer& L = M.layers[layer];
+    if (use_shared ? !L.has_shared() : !(L.m[0].dev && L.m[1].dev && L.m[2].dev)) {
+        set_error("expert_rows: layer %d lacks the %s expert tensors", layer, use_shared ? "shared" : "routed");
+        return DNB_DECLINED;
+    }
+    int rc = ensure_ws(c, rows);
+    if (rc) return rc;
+    Workspace& w = c->ws;
+    cudaStream_t st = c->stream;
+    const bool q4k_routed = L.m[0].type == T_Q4_K && L.m[1].type == T_Q4_K && L.m[2].type == T_Q4_K;
+    const bool q4k_shared = L.has_shared() && L.m[3].type == T_Q4_K && L.m[4].type == T_Q4_K && L.m[5].type == T_Q4_K &&
+                            L.m[3].n_out == M.ff;
+    const bool umma = c->use_umma && w.maps_ok && rows >= 16 && M.e % 256 == 0 && M.ff % 256 == 0;
+    if (!use_shared) {
+        // every row is one (token, slot): a "chunk" of `rows` tokens with one selected expert each and weight 1
+        if (umma && q4k_routed) return experts_dev_umma(c, layer, x_rows_dev, rows, local_ids_dev, nullptr, h_rows_dev, 1, M.shard_count, 0);
+        return experts_dev(c, layer, x_rows_dev, rows, local_ids_dev, nullptr, h_rows_dev, 1, M.shard_count, 0);
+    }
+    // the shared expert on all rows: one segment, rows in place
+    if ((rc = launch_prep(c, st, x_rows_dev, nullptr, M.eps, rows, M.e, nullptr, w.seg_sh_gu, w.seg_sh_dn, L.m[3].dev,
+                          L.m[4].dev, L.m[5].dev)))
+        return rc;
+    const int sff = L.m[3].n_out;
+    if (umma && q4k_shared) {
+        if ((rc = launch_gather_split(c, st, x_rows_dev, M.e, nullptr, rows, M.e, w.xg_hi, w.xg_lo))) return rc;
+        if ((rc = launch_grouped_umma(c, st, true, w.seg_sh_gu, w.one, 1, M.e, M.ff, &w.maps_x, rows, w.act_hi, w.act_lo, nullptr)))
+            return rc;
+        return launch_grouped_umma(c, st, false, w.seg_sh_dn, w.one, 1, M.ff, M.e, &w.maps_act, rows, nullptr, nullptr, h_rows_dev);
+    }
+    if ((rc = launch_seg_matmul(c, st, L.m[3].type, true, w.seg_sh_gu, nullptr, 1, M.e, sff, x_rows_dev, M.e, nullptr, w.sact, rows)))
+        return rc;
+    return launch_seg_matmul(c, st, L.m[5].type, false, w.seg_sh_dn, nullptr, 1, sff, M.e, w.sact, sff, nullptr, h_rows_dev, rows);
+}
+
+int dnb_moe_combine_dev(dnb_ctx* c, int layer, const float* h_slots_dev, const float* wts_dev, const float* shared_dev,
+                        const float* x_dev, int nt, float* out_dev) {
+    if (!c || !h_slots_dev || !wts_dev || !out_dev || nt < 1) return DNB_ERR_ARG;
+    const Model& M = c->model;
+    if (layer < 0 || layer >= M.n_layer) return DNB_ERR_ARG;
+    const Layer& L = M.layers[layer];
+    int rc = ensure_ws(c, nt);
+    if (rc) return rc;
+    const float* coef = nullptr;
+    if (shared_dev && L.shared_gate_row) {
+        if (!x_dev) return DNB_ERR_ARG;
+        if ((rc = launch_shared_coef(c, c->stream, x_dev, L.shared_gate_row, nt, M.e, c->ws.shcoef))) return rc;
+        coef = c->ws.shcoef;
+    }
+    return launch_combine(c, c->stream, h_slots_dev, nullptr, wts_dev, nt, M.k, M.e, shared_dev, coef, out_dev);
 }
 
 int dnb_moe_stack_dev(dnb_ctx* c, float* h_dev, int nt) {

@@ -70,6 +70,7 @@ struct Scratch {               // grow-only device scratch of a context
 
 struct Model {
     int n_layer = 0, e = 0, ff = 0, sff = 0, ne = 0, k = 0;
+    int shard_first = 0, shard_count = 0;  // routed experts resident on this GPU (expert parallel); count == ne: all
     float eps = 1e-6f;
     int norm_topk = 1;
     std::vector<Layer> layers;
@@ -83,7 +84,7 @@ struct Workspace {             // device buffers of the MoE pipeline, sized for 
     int nt_cap = 0;
     float *xn = nullptr, *logits = nullptr, *wts = nullptr, *act = nullptr, *hrow = nullptr, *sact = nullptr,
           *sh = nullptr, *hin = nullptr, *out = nullptr, *shcoef = nullptr;
-    int32_t *sels = nullptr, *row_token = nullptr, *pos = nullptr, *nseg = nullptr, *counts = nullptr;
+    int32_t *sels = nullptr, *row_token = nullptr, *pos = nullptr, *nseg = nullptr, *counts = nullptr, *one = nullptr;
     SegDesc *seg_gu = nullptr, *seg_dn = nullptr, *seg_sh_gu = nullptr, *seg_sh_dn = nullptr;
     uint16_t *xg_hi = nullptr, *xg_lo = nullptr, *act_hi = nullptr, *act_lo = nullptr;  // bf16 hi/lo packed rows
     UmmaMaps maps_x, maps_act;

@@ -699,9 +699,9 @@ combine_kernel(const float* __restrict__ hrow, const int32_t* __restrict__ pos, 
     const int t = blockIdx.x;
     __shared__ int32_t prow[32];
     __shared__ float pw[32];
-    if (threadIdx.x < k) {
-        prow[threadIdx.x] = pos[(size_t)t * k + threadIdx.x];
-        pw[threadIdx.x] = wts[(size_t)t * k + threadIdx.x];
+    if (threadIdx.x < k) {  // pos == null: row t*k+s; wts == null: weight 1 (x * 1.0f is exact)
+        prow[threadIdx.x] = pos ? pos[(size_t)t * k + threadIdx.x] : t * k + (int)threadIdx.x;
+        pw[threadIdx.x] = wts ? wts[(size_t)t * k + threadIdx.x] : 1.0f;
     }
     __syncthreads();
     for (int j = threadIdx.x; j < e; j += 256) {

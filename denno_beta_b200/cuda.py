@@ -157,6 +157,10 @@ class CudaCtx:
                               sff=n_shared_ff or n_ff)
         return ok
 
+    def set_expert_shard(self, first_expert, n_local):
+        """Expert parallel: this context holds routed experts [first, first + n_local)."""
+        check(self.lib.dnb_moe_set_expert_shard(self.h, first_expert, n_local))
+
     def register_experts(self, layer, matrix, ty, n_in, n_out, n_expert, blocks):
         blocks = np.ascontiguousarray(blocks, dtype=np.uint8)
         return check(self.lib.dnb_register_experts(self.h, layer, matrix, ty, n_in, n_out, n_expert, _p(blocks),

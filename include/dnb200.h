@@ -184,6 +184,32 @@ int dnb_router_topk_static(dnb_ctx* ctx, int layer, const float* x_dev, int nt, 
  * [m_total][n_out]. */
 int dnb_grouped_gemm(dnb_ctx* ctx, int layer, int matrix, const uint32_t* segs, int nseg, const float* xs,
                      float* outs);
+/* ---- expert-parallel building blocks ---------------------------------------------
+ * The reference runs on one GPU.  On a multi-GPU box the experts shard naturally:
+ * GPU g keeps experts [g*ne/G, (g+1)*ne/G) of every layer (router, norm and shared
+ * expert replicated), tokens stay data-parallel, and the routed activations are
+ * exchanged with an all-to-all between the three calls below (the exchange itself
+ * is the caller's: NCCL through torch.distributed in denno_beta_b200/ep.py).  All
+ * pointers are device pointers; the calls are asynchronous on the context's stream.
+ *   dnb_moe_set_expert_shard : which routed experts this context holds (call after
+ *       dnb_moe_config and before dnb_register_experts, whose n_expert is then the
+ *       shard's size).  With a proper shard the whole-block entry points decline.
+ *   dnb_moe_route_dev  : (RMSNorm) + router + top-k for the caller's own tokens;
+ *       writes the expert input x [nt][e], sels [nt][k] (global ids), wts [nt][k].
+ *   dnb_expert_rows_dev: h[r] = down(silu(gate x[r]) * up x[r]) of LOCAL expert
+ *       local_ids[r] for each of `rows` received rows; use_shared != 0 applies the
+ *       shared expert to every row instead (local_ids may be NULL).
+ *   dnb_moe_combine_dev: out[t] = sum_s wts[t][s] * h_slots[t*k+s] in ascending slot
+ *       (= ascending expert) order, + shared[t] (times sigmoid(gate row . x[t]) when
+ *       the layer has a shared gate row; x may be NULL otherwise).  The order is
+ *       the single-GPU order, so the result does not depend on G. */
+int dnb_moe_set_expert_shard(dnb_ctx* ctx, int first_expert, int n_local);
+int dnb_moe_route_dev(dnb_ctx* ctx, int layer, const float* h_dev, int nt, float* x_out_dev, int32_t* sels_dev,
+                      float* wts_dev);
+int dnb_expert_rows_dev(dnb_ctx* ctx, int layer, const float* x_rows_dev, const int32_t* local_ids_dev, int rows,
+                        int use_shared, float* h_rows_dev);
+int dnb_moe_combine_dev(dnb_ctx* ctx, int layer, const float* h_slots_dev, const float* wts_dev, const float* shared_dev,
+                        const float* x_dev, int nt, float* out_dev);
 /* A stack of the configured layers with identity mixers: h <- h + block_l(h) for
  * l = 0..n_layer-1 (device-resident between layers).  h host [nt][n_embd] in/out. */
 int dnb_moe_stack(dnb_ctx* ctx, const float* h, int nt, float* out);

@@ -1,0 +1,112 @@
+"""Rank workers of the expert-parallel tests: `python ep_ranks.py cpu|gpu RANK WORLD PORT`.
+Each exits 0 when its checks pass."""
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _init(rank, world, port, backend):
+    import torch.distributed as dist
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group(backend, rank=rank, world_size=world)
+
+
+def cpu_rank(rank, world, port):
+    """Each rank owns 7 tokens; the fake expert e maps a row x to x * (e + 1) + e."""
+    sys.path.insert(0, ROOT)
+    import torch
+    import torch.distributed as dist
+
+    from denno_beta_b200 import ep
+
+    _init(rank, world, port, "gloo")
+    try:
+        ne, k, e, nt = 8, 3, 5, 7
+        n_local = ne // world
+        g = torch.Generator().manual_seed(100 + rank)
+        x = torch.randn(nt, e, generator=g)
+        sels = torch.stack([torch.sort(torch.randperm(ne, generator=g)[:k]).values for _ in range(nt)]).to(torch.int32)
+        wts = torch.rand(nt, k, generator=g)
+        recv_x, recv_ids, state = ep.dispatch(x, sels, n_local)
+        # rows arrive grouped by source rank; every id is local to this rank
+        assert recv_ids.numel() == recv_x.shape[0]
+        assert recv_ids.numel() == 0 or (int(recv_ids.min()) >= 0 and int(recv_ids.max()) < n_local)
+        gid = recv_ids.to(torch.float32) + rank * n_local
+        h_rows = recv_x * (gid + 1).unsqueeze(1) + gid.unsqueeze(1)
+        h_slots = ep.gather_back(h_rows, state)
+        out = (h_slots.reshape(nt, k, e) * wts.unsqueeze(2)).sum(1)
+        ge = sels.to(torch.float32)
+        want = ((x.unsqueeze(1) * (ge + 1).unsqueeze(2) + ge.unsqueeze(2)) * wts.unsqueeze(2)).sum(1)
+        ok = bool(torch.allclose(out, want, rtol=0, atol=1e-6))
+        total = torch.tensor([recv_x.shape[0]])
+        dist.all_reduce(total)
+        assert ok, "rank %d: combined output differs" % rank
+        assert int(total) == world * nt * k
+    finally:
+        dist.destroy_process_group()
+
+
+def gpu_rank(rank, world, port):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import torch
+    import torch.distributed as dist
+
+    import oracle as orc
+    from denno_beta_b200 import cuda as cu, ep
+    from helpers import SEED, make_layer, rel_err
+
+    torch.cuda.set_device(rank)
+    _init(rank, world, port, "nccl")
+    try:
+        e, ff, ne, k, nt = 512, 256, 32, 4, 40
+        results = {}
+        for layer_ty in (orc.Q4_K, orc.IQ3_XXS):
+            # reference on this rank: the whole model on one GPU, all tokens
+            full = cu.CudaCtx(rank)
+            assert full.moe_config(1, e, ff, ne, k)
+            L = make_layer(orc, full, 0, layer_ty, e, ff, ne, k, bias=True, gate_row=True)
+            h_all = orc.synth_normal(SEED, 7700, 1.0, world * nt * e).reshape(world * nt, e)
+            want = full.moe_block(0, h_all)[rank * nt:(rank + 1) * nt]
+            full.close()
+            # expert-parallel: this rank's shard
+            c = cu.CudaCtx(rank)
+            assert c.moe_config(1, e, ff, ne, k)
+            nl = ne // world
+            c.set_expert_shard(rank * nl, nl)
+            kp = L.keep
+            gb, db = kp["gate"].size // ne, kp["down"].size // ne
+            sl = slice(rank * nl * gb, (rank + 1) * nl * gb)
+            sd = slice(rank * nl * db, (rank + 1) * nl * db)
+            assert c.register_experts(0, cu.GATE, layer_ty, e, ff, nl, kp["gate"][sl])
+            assert c.register_experts(0, cu.UP, layer_ty, e, ff, nl, kp["up"][sl])
+            assert c.register_experts(0, cu.DOWN, layer_ty, ff, e, nl, kp["down"][sd])
+            assert c.register_experts(0, cu.SHARED_GATE, layer_ty, e, ff, 1, kp["sg"])
+            assert c.register_experts(0, cu.SHARED_UP, layer_ty, e, ff, 1, kp["su"])
+            assert c.register_experts(0, cu.SHARED_DOWN, layer_ty, ff, e, 1, kp["sd"])
+            c.register_router(0, kp["router_w"], kp["router_bias"], kp["norm_w"], kp["sgr"])
+            blk = ep.ExpertParallelBlock(c, e, ne, k)
+            h = torch.from_numpy(h_all[rank * nt:(rank + 1) * nt].copy()).cuda()
+            out1 = blk.block(0, h).cpu().numpy()
+            out2 = blk.block(0, h).cpu().numpy()
+            results[int(layer_ty)] = (rel_err(out1, want), bool(np.array_equal(out1.view(np.uint32), out2.view(np.uint32))),
+                                      c.device_status())
+            torch.cuda.synchronize()
+            c.close()
+        for ty, (err, same, status) in results.items():
+            print("rank %d type %d: err %.3g bit-identical %s status %d" % (rank, ty, err, same, status), flush=True)
+            assert err <= 5e-4 and same and status == 0
+    finally:
+        dist.destroy_process_group()
+
+
+
+
+if __name__ == "__main__":
+    kind, rank, world, port = sys.argv[1], int(sys.argv[2]), int(sys.argv[3]), int(sys.argv[4])
+    (cpu_rank if kind == "cpu" else gpu_rank)(rank, world, port)
