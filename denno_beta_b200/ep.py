@@ -87,8 +87,11 @@ class ExpertParallelBlock:
         assert n_expert % self.world == 0, "experts must divide evenly over the ranks"
         self.n_local = n_expert // self.world
         self.dev = torch.device("cuda", ctx.device)
-        # the library's kernels and torch's copies/collectives share one stream
-        ctx.set_stream(torch.cuda.current_stream(self.dev).cuda_stream)
+        # The library's kernels and torch's copies/collectives must share one stream.
+        # torch's default stream has handle 0, which the library reads as "use your own
+        # stream", so a dedicated torch stream is created and made current in block().
+        self.stream = torch.cuda.Stream(device=self.dev)
+        ctx.set_stream(self.stream.cuda_stream)
 
     def _p(self, t):
         return C.c_void_p(t.data_ptr())
@@ -126,10 +129,14 @@ class ExpertParallelBlock:
 
     def block(self, layer, h, has_shared=True):
         """h: this rank's tokens [nt, e] (fp32, on this rank's GPU) -> block output [nt, e]."""
-        h = h.contiguous()
-        x, sels, wts = self.route(layer, h)
-        recv_x, recv_ids, state = dispatch(x, sels, self.n_local)
-        sh = self.expert_rows(layer, x, None, shared=True) if has_shared else None
-        h_rows = self.expert_rows(layer, recv_x.contiguous(), recv_ids)
-        h_slots = gather_back(h_rows, state)
-        return self.combine(layer, h_slots, wts, sh, x)
+        self.stream.wait_stream(torch.cuda.current_stream(self.dev))
+        with torch.cuda.stream(self.stream):
+            h = h.contiguous()
+            x, sels, wts = self.route(layer, h)
+            recv_x, recv_ids, state = dispatch(x, sels, self.n_local)
+            sh = self.expert_rows(layer, x, None, shared=True) if has_shared else None
+            h_rows = self.expert_rows(layer, recv_x.contiguous(), recv_ids)
+            h_slots = gather_back(h_rows, state)
+            out = self.combine(layer, h_slots, wts, sh, x)
+        torch.cuda.current_stream(self.dev).wait_stream(self.stream)
+        return out

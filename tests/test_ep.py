@@ -21,7 +21,7 @@ def _run_ranks(kind, world, port, timeout):
             p.kill()
             out, _ = p.communicate()
         outs.append((p.returncode, out))
-    assert all(rc == 0 for rc, _ in outs), "\n".join(o[-2000:] for _, o in outs)
+    assert all(rc == 0 for rc, _ in outs), "\n".join(o[-3000:] for _, o in outs)
     return outs
 
 
