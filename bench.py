@@ -194,8 +194,14 @@ def run_ours(args, rank, world, local_rank):
         t = torch.tensor([ms_dev, ms_e2e], dtype=torch.float64, device="cuda:%d" % local_rank)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_dev, ms_e2e = float(t[0]), float(t[1])
-    if rank != 0:
+    ep_res = None
+    if world > 1 and not args.no_extras:
         ctx.close()
+        ctx = None
+        ep_res = ep_prefill_extras(cu, oracle, rank, world, local_rank)
+    if rank != 0:
+        if ctx is not None:
+            ctx.close()
         return None
 
     hbm_peak, _, peak_kind = peaks()
@@ -233,6 +239,8 @@ def run_ours(args, rank, world, local_rank):
         "block_hbm_gbs": block_bytes / (ms_dev / K_ * 1e-3) / 1e9,
         "kernels_ms": {k: round(v["ms"], 4) for k, v in prof.items()},
     }
+    if ep_res is not None:
+        res["extras"] = {"config2_q4k_prefill_512_expert_parallel": ep_res}
     if world == 1 and not args.no_extras:
         res["extras"] = extras(ctx, cu, oracle)
         ctx.close()
@@ -321,6 +329,47 @@ def prefill_extras(cu, oracle, device, layers=4):
     finally:
         ctx.close()
     return out
+
+
+def ep_prefill_extras(cu, oracle, rank, world, local_rank):
+    """Config 2 across `world` GPUs, expert parallel: 512/world experts per GPU, the
+    512-token chunk split evenly over the ranks (strong scaling), dispatch and return by
+    NCCL all-to-all.  Timed with events on the block's stream, max over ranks."""
+    import torch
+    import torch.distributed as dist
+
+    from denno_beta_b200 import ep
+
+    layers, nt_total = 4, 512
+    nl, nt = NE // world, nt_total // world
+    ctx = cu.CudaCtx(local_rank)
+    assert ctx.moe_config(layers, E, FF, NE, K)
+    ctx.set_expert_shard(rank * nl, nl)
+    for l in range(layers):
+        for m, (ni, no, n) in ((cu.GATE, (E, FF, nl)), (cu.UP, (E, FF, nl)), (cu.DOWN, (FF, E, nl)),
+                               (cu.SHARED_GATE, (E, FF, 1)), (cu.SHARED_UP, (E, FF, 1)), (cu.SHARED_DOWN, (FF, E, 1))):
+            assert ctx.synth_experts(l, m, Q4_K, ni, no, n, SEED + rank)
+        ctx.register_router(l, oracle.synth_normal(SEED, l * 16 + 6, 0.02, NE * E), oracle.synth_zipf_bias(SEED, l * 16 + 7, 1.1, NE),
+                            np.ones(E, np.float32), None)
+    blk = ep.ExpertParallelBlock(ctx, E, NE, K)
+    h = torch.from_numpy(oracle.synth_normal(SEED, 8000, 1.0, nt_total * E).reshape(nt_total, E)[rank * nt:(rank + 1) * nt].copy()).cuda(local_rank)
+    for l in range(2 * layers):
+        blk.block(l % layers, h)
+    torch.cuda.synchronize()
+    dist.barrier()
+    reps = 16
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for l in range(reps):
+        blk.block(l % layers, h)
+    t1.record()
+    torch.cuda.synchronize()
+    ms = torch.tensor([t0.elapsed_time(t1) / reps], dtype=torch.float64, device="cuda:%d" % local_rank)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ctx.close()
+    return {"ms_per_chunk_layer": float(ms), "tok_per_s_layer": nt_total / (float(ms) * 1e-3), "tokens_per_rank": nt,
+            "experts_per_rank": nl, "exchange": "NCCL all_to_all_single (dispatch rows fp32 + ids, return rows fp32)",
+            "scaling": "strong (one 512-token chunk over %d GPUs)" % world}
 
 
 def cpu_layer(oracle, ty=IQ3_XXS):
