@@ -95,12 +95,14 @@ def peaks():
     return 6650.0, 1590.0, "fallback"
 
 
-def build_model(ctx, cu, ty, layers, bias):
+def build_model(ctx, cu, ty, layers, bias, ty_of_layer=None):
     """Expert tables filled on the device; routers (small) from the host generator."""
     import oracle  # only its seeded host generator is used here (inputs, not results)
 
     assert ctx.moe_config(layers, E, FF, NE, K)
+    base_ty = ty
     for l in range(layers):
+        ty = ty_of_layer(l) if ty_of_layer else base_ty
         assert ctx.synth_experts(l, cu.GATE, ty, E, FF, NE, SEED)
         assert ctx.synth_experts(l, cu.UP, ty, E, FF, NE, SEED)
         assert ctx.synth_experts(l, cu.DOWN, ty, FF, E, NE, SEED)
@@ -246,6 +248,8 @@ def run_ours(args, rank, world, local_rank):
         ctx.close()
         ctx = None
         res["extras"]["config2_q4k_prefill_512"] = prefill_extras(cu, oracle, local_rank)
+        if not args.no_stack:
+            res["extras"].update(stack_extras(cu, oracle, local_rank))
     if world == 1 and not args.no_cpu:
         res["cpu_baseline"] = cpu_baseline(oracle, budget_s=10.0)
     if ctx is not None:
@@ -372,6 +376,74 @@ def ep_prefill_extras(cu, oracle, rank, world, local_rank):
             "scaling": "strong (one 512-token chunk over %d GPUs)" % world}
 
 
+def stack_extras(cu, oracle, device):
+    """Configs 3 and 4: the 48-block stack (identity mixers, h <- h + block(h)).
+    Decode: 40 IQ3_XXS + 8 Q4_K layers (every sixth), batch 1 / 8 / 32, one
+    dnb_moe_stack_dev call per step (CUDA-graph replay).  Prefill: all-Q4_K layers with
+    the Zipf router bias, a 14,018-token prompt in 512-token chunks (27 x 512 + 194)."""
+    out = {}
+    g3, d3 = expert_bytes(IQ3_XXS)
+    g4, d4 = expert_bytes(Q4_K)
+    ctx = cu.CudaCtx(device)
+    try:
+        build_model(ctx, cu, IQ3_XXS, 48, False, ty_of_layer=lambda l: Q4_K if l % 6 == 5 else IQ3_XXS)
+        step_bytes = 40 * (NE * E * 4 + 11 * (2 * g3 + d3)) + 8 * (NE * E * 4 + 11 * (2 * g4 + d4))
+        hbm = peaks()[0]
+        for B in (1, 8, 32):
+            h = oracle.synth_normal(SEED, 8100 + B, 1.0, B * E).reshape(B, E)
+            d_src = ctx.dev_alloc(h.nbytes)
+            d_h = ctx.dev_alloc(h.nbytes)
+            ctx.upload(d_src, h)
+            for _ in range(3):
+                ctx.dev_copy(d_h, d_src, h.nbytes)
+                assert ctx.moe_stack_dev(d_h, B)
+            ctx.sync()
+            reps = 12
+            ctx.timer_start()
+            for _ in range(reps):
+                ctx.dev_copy(d_h, d_src, h.nbytes)
+                assert ctx.moe_stack_dev(d_h, B)
+            ms = ctx.timer_stop() / reps
+            res = {"ms_per_step": ms, "tok_per_s": B / (ms * 1e-3)}
+            if B == 1:
+                res["algorithmic_bytes_per_step"] = step_bytes
+                res["hbm_gbs"] = step_bytes / (ms * 1e-3) / 1e9
+                res["frac_of_measured_hbm"] = res["hbm_gbs"] / hbm
+            out["config3_decode_stack48_batch%d" % B] = res
+            ctx.dev_free(d_src)
+            ctx.dev_free(d_h)
+    finally:
+        ctx.close()
+    ctx = cu.CudaCtx(device)
+    try:
+        build_model(ctx, cu, Q4_K, 48, True)
+        n_tok = 14018
+        chunks = [512] * 27 + [194]
+        h = oracle.synth_normal(SEED, 8200, 1.0, 512 * E).reshape(512, E)
+        d_src = ctx.dev_alloc(h.nbytes)
+        d_h = ctx.dev_alloc(h.nbytes)
+        ctx.upload(d_src, h)
+        for nt in (512, 194, 512, 194):  # warm-up: workspace, graphs
+            ctx.dev_copy(d_h, d_src, nt * E * 4)
+            assert ctx.moe_stack_dev(d_h, nt)
+        ctx.sync()
+        ctx.timer_start()
+        for nt in chunks:
+            ctx.dev_copy(d_h, d_src, nt * E * 4)
+            assert ctx.moe_stack_dev(d_h, nt)
+        ms = ctx.timer_stop()
+        flops = n_tok * 48.0 * (11 * 6291456 + 2097152)
+        out["config4_prefill_stack48_14018"] = {"seconds": ms * 1e-3, "tok_per_s": n_tok / (ms * 1e-3),
+                                                "algorithmic_tflops": flops / (ms * 1e-3) / 1e12,
+                                                "frac_of_measured_bf16": flops / (ms * 1e-3) / 1e12 / peaks()[1],
+                                                "chunks": "27 x 512 + 194 (every chunk reuses the same 512 seeded rows)"}
+        ctx.dev_free(d_src)
+        ctx.dev_free(d_h)
+    finally:
+        ctx.close()
+    return out
+
+
 def cpu_layer(oracle, ty=IQ3_XXS):
     nb = lambda rows, cols: rows * cols // 256
     gate = oracle.synth_blocks(ty, SEED, 0, NE * nb(FF, E))
@@ -442,7 +514,8 @@ def main():
     ap.add_argument("--prefill-only", action="store_true",
                     help="run only the config-2 prefill measurement (small: for profiler captures)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--no-extras", action="store_true", help="skip the config-0 GEMV line")
+    ap.add_argument("--no-extras", action="store_true", help="skip the config-0/2/3/4 lines")
+    ap.add_argument("--no-stack", action="store_true", help="skip the 48-layer stack lines (configs 3 and 4)")
     args = ap.parse_args()
     if args.layers > 0:
         LAYERS = args.layers
