@@ -50,8 +50,11 @@ namespace um {
 constexpr int BK = 64;            // K elements per stage (one 128-byte swizzle row of bf16)
 constexpr int TILE_M = 128;       // weight rows per CTA
 constexpr int A_TILE = TILE_M * BK * 2;   // 16 KB
-constexpr int PWARPS = 8;         // producer warps: two threads per weight row (low / high nibble half of a stage)
-constexpr int NTHREADS = (PWARPS + 2) * 32;  // warps 0-7 producers (0-3 also epilogue), warp 8 TMA, warp 9 MMA + TMEM
+constexpr int kMaxSeg = 1055;    // segments the per-CTA tile prefix table holds
+constexpr int PWARPS = 16;        // producer warps: four threads per weight row and matrix (16 elements each per stage)
+constexpr int W_TMA = PWARPS;     // warp that issues the activation tile copies
+constexpr int W_MMA = PWARPS + 1; // warp that issues the MMAs and owns the TMEM allocation
+constexpr int NTHREADS = (PWARPS + 6) * 32;  // + TMA, MMA and four epilogue warps
 
 __device__ __forceinline__ uint32_t s32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mb_init(uint64_t* b, uint32_t n) {
@@ -94,15 +97,12 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
 // start address >> 4 in bits [0,14), leading byte offset (unused for swizzled
 // K-major, set to 1) in [16,30), stride byte offset = 1024 B between 8-row groups in
 // [32,46), version 1 in [46,48), layout type 2 (SWIZZLE_128B) in [61,64).
-__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
-    d |= (uint64_t)1 << 16;
-    d |= (uint64_t)(1024 >> 4) << 32;
-    d |= (uint64_t)1 << 46;
-    d |= (uint64_t)2 << 61;
-    return d;
-}
+// Only the start address varies, and it never carries out of its 14-bit field (shared
+// memory ends below 256 KB), so a descriptor is a constant high word and a low word that
+// advances by plain adds of (byte offset >> 4).
+constexpr uint32_t kDescHi = (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t desc_lo(uint32_t smem_addr) { return ((smem_addr >> 4) & 0x3FFFu) | (1u << 16); }
+__device__ __forceinline__ uint64_t desc_of(uint32_t lo) { return ((uint64_t)kDescHi << 32) | lo; }
 
 // Instruction descriptor, kind::f16: D fp32 (bits 4-5 = 1), A and B bf16 (bits 7-9,
 // 10-12 = 1), both K-major (bits 15, 16 = 0), N >> 3 in bits 17-22, M >> 4 in 24-28.
@@ -145,12 +145,12 @@ __device__ __forceinline__ void split2(float a, float b, uint32_t& hi_pair, uint
     lo_pair = __byte_perm(__float_as_uint(al), __float_as_uint(bl), 0x7632);
 }
 
-// One stage of one Q4_K row: 64 elements (chunk j of block b) -> hi/lo bf16 rows in
-// the swizzled tiles.  hdr = first 16 bytes of the block, q0/q1 = the chunk's 32 qs
-// bytes.  Element k of the stage: k < 32 low nibble of byte k, k >= 32 high nibble of
-// byte k - 32 (kquant.rs:505-526).
-__device__ __forceinline__ void dequant_q4k_stage(const uint4& hdr, const uint4& q0, const uint4& q1, int j, int half,
-                                                  uint8_t* tile_hi, uint8_t* tile_lo, int r) {
+// One producer task: 16 elements of one Q4_K row -> hi/lo bf16 in the swizzled tiles.
+// hdr = first 16 bytes of the block (d, dmin, 12 scale bytes), q = 16 qs bytes: bytes
+// 16p .. 16p+15 of chunk j's 32.  nh = 0 takes the low nibbles (stage elements
+// 16p .. 16p+15), nh = 1 the high nibbles (elements 32+16p ..) (kquant.rs:505-526).
+__device__ __forceinline__ void dequant_q4k_task(const uint4& hdr, const uint4& q, int j, int nh, int p,
+                                                 uint8_t* tile_hi, uint8_t* tile_lo, int r) {
     const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xFFFF)));
     const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
     // scale bytes 0..11 live in hdr.y, hdr.z, hdr.w
@@ -158,37 +158,101 @@ __device__ __forceinline__ void dequant_q4k_stage(const uint4& hdr, const uint4&
         const uint32_t w = i < 4 ? hdr.y : (i < 8 ? hdr.z : hdr.w);
         return (w >> (8 * (i & 3))) & 0xFFu;
     };
-    // this thread's sub-block: 2j (low nibbles, k 0..31) or 2j + 1 (high nibbles, k 32..63)
-    const int a = 2 * j + half;
+    const int a = 2 * j + nh;  // sub-block of these 16 elements
     uint32_t sc, mn;
     if (a < 4) { sc = sb(a) & 63; mn = sb(a + 4) & 63; }
     else { sc = (sb(a + 4) & 0xF) | ((sb(a - 4) >> 6) << 4); mn = (sb(a + 4) >> 4) | ((sb(a) >> 6) << 4); }
     const float d1 = d * (float)sc;
     const float c1 = fmaf(128.0f, d1, dmin * (float)mn);
     const uint32_t rowoff = (uint32_t)(r >> 3) * 1024u + (uint32_t)(r & 7) * 128u;
-    const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-    const int sh = half * 4;
+    const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
+    const int sh = nh * 4;
 #pragma unroll
-    for (int g = 0; g < 4; ++g) {  // 8 elements k = 32*half + 8g .. +7 from bytes 8g..8g+7
+    for (int w2 = 0; w2 < 2; ++w2) {  // 8 elements = one 16-byte column of the swizzled row
         uint32_t hv[4], lv[4];
 #pragma unroll
-        for (int w2 = 0; w2 < 2; ++w2) {
-            const uint32_t nib = (qw[2 * g + w2] >> sh) & 0x0F0F0F0Fu;
+        for (int w1 = 0; w1 < 2; ++w1) {
+            const uint32_t nib = (qw[2 * w2 + w1] >> sh) & 0x0F0F0F0Fu;
             // w = d1 * q - m1 evaluated as d1 * (128 + q) - (128 d1 + m1): one fma on an exact float
             const float a0 = fmaf(d1, magic128<0>(nib), -c1), a1 = fmaf(d1, magic128<1>(nib), -c1);
             const float a2 = fmaf(d1, magic128<2>(nib), -c1), a3 = fmaf(d1, magic128<3>(nib), -c1);
-            split2(a0, a1, hv[2 * w2], lv[2 * w2]);
-            split2(a2, a3, hv[2 * w2 + 1], lv[2 * w2 + 1]);
+            split2(a0, a1, hv[2 * w1], lv[2 * w1]);
+            split2(a2, a3, hv[2 * w1 + 1], lv[2 * w1 + 1]);
         }
-        const uint32_t col = ((uint32_t)((4 * half + g) ^ (r & 7))) << 4;
+        const uint32_t col = ((uint32_t)((4 * nh + 2 * p + w2) ^ (r & 7))) << 4;
         *reinterpret_cast<uint4*>(tile_hi + rowoff + col) = make_uint4(hv[0], hv[1], hv[2], hv[3]);
         *reinterpret_cast<uint4*>(tile_lo + rowoff + col) = make_uint4(lv[0], lv[1], lv[2], lv[3]);
     }
 }
 
+// Weight loads of the producers, as volatile asm so that they are issued where they are
+// written (two chunks ahead of their use) instead of being sunk towards the use.
+__device__ __forceinline__ uint4 ld_weights_stream(const void* p) {  // read once: do not keep in L1
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint4 ld_weights_keep(const void* p) {  // shared by the row's four threads
+    uint4 v;
+    asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+// Ask L2 to fetch `bytes` (a multiple of 16) from a 16-byte aligned address; no register,
+// no shared memory, nothing to wait for.
+__device__ __forceinline__ void prefetch_l2(const void* p, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+
+// A work item of the persistent kernel: which segment, which 128 tokens of it, which
+// 128 weight rows.
+struct Item {
+    const uint8_t* wa;
+    const uint8_t* wb;
+    int prow;    // first packed row of the token tile
+    int m_tile;  // tokens in the tile (1..128)
+    int r0;      // first weight row
+};
+__device__ __forceinline__ Item decode_item(int item, int row_tiles, int nseg, const int* tile_prefix,
+                                            const SegDesc* __restrict__ seg) {
+    const int tile = item / row_tiles, rt = item - tile * row_tiles;
+    int lo = 0, hi = nseg - 1;
+    while (lo < hi) {  // last segment whose first tile is <= tile
+        const int mid = (lo + hi + 1) >> 1;
+        if (tile_prefix[mid] <= tile) lo = mid; else hi = mid - 1;
+    }
+    const SegDesc sd = seg[lo];
+    const int t0 = (tile - tile_prefix[lo]) * 128;
+    Item it;
+    it.wa = sd.wa;
+    it.wb = sd.wb;
+    it.prow = (int)sd.row0 + t0;
+    it.m_tile = min(128, (int)sd.m - t0);
+    it.r0 = rt * TILE_M;
+    return it;
+}
+__device__ __forceinline__ int nsel_of(int m_tile) { return m_tile <= 16 ? 0 : (m_tile <= 32 ? 1 : (m_tile <= 64 ? 2 : 3)); }
+
+// silu(g) * u with the fast exponential and reciprocal: their ~1e-6 relative error
+// is far inside what the bf16 hi/lo products already carry.
+__device__ __forceinline__ float swiglu_fast(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
+
 // NMAT = 2: gate and up tiles together, SwiGLU epilogue to out_hi / out_lo (bf16 packed rows).
 // NMAT = 1: one matrix, fp32 epilogue to out_f32.
-// grid = (n_out / 128, segments, token tiles of 128)
+//
+// Persistent: grid = number of SMs (the stages fill shared memory, one CTA per SM).
+// Work items are (segment, 128-token tile, 128-row tile), item i handled by CTA
+// i mod gridDim.x in increasing order; every role walks the same item sequence on
+// its own, coupled only through mbarriers:
+//   warps 0-15   producers: dequantise the weight rows into the stage (16 elements
+//                per thread and matrix), prefetching raw bytes two chunks ahead and
+//                across item boundaries
+//   warp 16      TMA: activation tiles of the stage
+//   warp 17      MMA issue (one thread); owns the TMEM allocation
+//   warps 18-21  epilogue: read the finished accumulators of item i from TMEM while
+//                the main loop of item i+1 fills the other accumulator buffer
+// Barriers and their phases live across items: chunk counter g keeps running
+// (stage g % STAGES, parity (g / STAGES) & 1); accumulator buffer = item count & 1.
 template <int NMAT>
 __global__ void __launch_bounds__(NTHREADS, 1)
 grouped_q4k_umma_kernel(const SegDesc* __restrict__ seg, const int32_t* __restrict__ nseg_dev, int n_in, int n_out,
@@ -198,35 +262,52 @@ grouped_q4k_umma_kernel(const SegDesc* __restrict__ seg, const int32_t* __restri
     constexpr int A_BYTES = NMAT * 2 * A_TILE;          // hi + lo per matrix
     constexpr int B_BYTES_MAX = 2 * 128 * BK * 2;       // hi + lo, N = 128
     constexpr int STAGE_BYTES = A_BYTES + B_BYTES_MAX;
+    constexpr int ACC_COLS = NMAT * 128;                // TMEM columns of one accumulator buffer
+    constexpr int TM_COLS = 2 * ACC_COLS;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
     uint64_t* empty = full + STAGES;
-    uint64_t* accum = empty + STAGES;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
+    uint64_t* accum = empty + STAGES;     // [2] accumulator buffer complete (one tcgen05.commit)
+    uint64_t* drained = accum + 2;        // [2] accumulator buffer read out (4 epilogue warps)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drained + 2);
+    int* tile_prefix = reinterpret_cast<int*>(tmem_slot + 2);  // [nseg + 1] token tiles before each segment
 
-    const int s = blockIdx.y;
-    if (s >= *nseg_dev) return;
-    const SegDesc sd = seg[s];
-    const int t0 = blockIdx.z * 128;
-    if ((uint32_t)t0 >= sd.m) return;
-    const int m_tile = min(128, (int)sd.m - t0);
-    const int nsel = m_tile <= 16 ? 0 : (m_tile <= 32 ? 1 : (m_tile <= 64 ? 2 : 3));
-    const int N = 16 << nsel;
-    const int r0 = blockIdx.x * TILE_M;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nchunks = n_in / BK;
-    constexpr int TM_COLS = (NMAT == 2) ? 256 : 128;
+    const int row_tiles = n_out / TILE_M;
+    const int nseg = min(*nseg_dev, kMaxSeg);
 
     if (tid == 0) {
         for (int i = 0; i < STAGES; ++i) {
             mb_init(&full[i], PWARPS + 1);  // producer warps + the TMA thread's expect_tx arrival
-            mb_init(&empty[i], 1);   // one tcgen05.commit
+            mb_init(&empty[i], 1);          // one tcgen05.commit
         }
-        mb_init(accum, 1);
+        for (int i = 0; i < 2; ++i) {
+            mb_init(&accum[i], 1);
+            mb_init(&drained[i], 4);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == PWARPS + 1) {
+    // Token tiles per segment (all threads load), then an exclusive scan by warp 0.
+    for (int i = tid; i < nseg; i += NTHREADS) tile_prefix[i + 1] = ((int)seg[i].m + 127) >> 7;
+    __syncthreads();
+    if (warp == 0) {
+        int carry = 0;
+        for (int base = 0; base < nseg; base += 32) {
+            const int i = base + lane;
+            int v = i < nseg ? tile_prefix[i + 1] : 0;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int o = __shfl_up_sync(0xffffffffu, v, d);
+                if (lane >= d) v += o;
+            }
+            if (i < nseg) tile_prefix[i + 1] = carry + v;
+            carry += __shfl_sync(0xffffffffu, v, 31);
+        }
+        if (lane == 0) tile_prefix[0] = 0;
+    }
+    if (warp == W_MMA) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(tmem_slot)), "r"(TM_COLS)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -235,134 +316,194 @@ grouped_q4k_umma_kernel(const SegDesc* __restrict__ seg, const int32_t* __restri
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    const int n_items = nseg > 0 ? tile_prefix[nseg] * row_tiles : 0;
+    const int G = gridDim.x;
+    const int my_items = (int)blockIdx.x < n_items ? (n_items - (int)blockIdx.x + G - 1) / G : 0;
     bool ok = true;
 
     if (warp < PWARPS) {
-        // ---------------- producers: two threads per weight row ----------------
-        const int r = tid & 127, half = tid >> 7;
-        const uint8_t* rowa = sd.wa + (size_t)(r0 + r) * rb;
-        const uint8_t* rowb = (NMAT == 2) ? sd.wb + (size_t)(r0 + r) * rb : nullptr;
-        // Raw bytes of a stage: header + this stage's 32 qs bytes, per matrix.  Four
-        // register buffers keep the loads of three stages ahead in flight (the rows
-        // are 1152 or 288 bytes apart, so these are latency-bound 32-byte reads).
-        struct Raw { uint4 ha, a0, a1, hb, b0, b1; };
-        Raw buf[4];
-        auto fetch = [&](Raw& q, int c) {
-            const int b = c >> 2, j = c & 3;
-            const uint8_t* pa = rowa + b * 144;
-            q.ha = __ldg(reinterpret_cast<const uint4*>(pa));
-            q.a0 = __ldcs(reinterpret_cast<const uint4*>(pa + 16 + 32 * j));
-            q.a1 = __ldcs(reinterpret_cast<const uint4*>(pa + 32 + 32 * j));
-            if constexpr (NMAT == 2) {
-                const uint8_t* pb = rowb + b * 144;
-                q.hb = __ldg(reinterpret_cast<const uint4*>(pb));
-                q.b0 = __ldcs(reinterpret_cast<const uint4*>(pb + 16 + 32 * j));
-                q.b1 = __ldcs(reinterpret_cast<const uint4*>(pb + 32 + 32 * j));
+        // ---------------- producers ----------------
+        // 16 rows x 2 qs pieces per warp (a request covers whole 32-byte sectors);
+        // warps 0-7 take the low nibbles, warps 8-15 the high nibbles of the same bytes.
+        const int r = (warp & 7) * 16 + (lane & 15), p = lane >> 4, nh = warp >> 3;
+        struct Raw { uint4 qa, qb; };   // one chunk's 16 qs bytes per matrix
+        struct Hdr { uint4 ha, hb; };   // one block's d, dmin and scale bytes per matrix
+        Raw buf[2];
+        Hdr hdr_cur, hdr_next;
+        // fetch cursor: runs two chunks ahead of the dequantisation, through item boundaries
+        int f_left = my_items, f_item = blockIdx.x, f_c = 0;
+        const uint8_t* f_pa = nullptr;
+        const uint8_t* f_pb = nullptr;
+        // One thread per weight row asks L2 for the whole row of an item a full item ahead
+        // of its use: the register prefetch below then hits L2, and the bytes in flight
+        // towards HBM are a tile (36-147 KB per matrix), not two chunks.
+        auto l2_prefetch_item = [&](int item) {
+            if (nh == 0 && p == 0 && item < n_items) {
+                const Item it = decode_item(item, row_tiles, nseg, tile_prefix, seg);
+                prefetch_l2(it.wa + (size_t)(it.r0 + r) * rb, (uint32_t)rb);
+                if constexpr (NMAT == 2) prefetch_l2(it.wb + (size_t)(it.r0 + r) * rb, (uint32_t)rb);
             }
         };
-        fetch(buf[0], 0);
-        fetch(buf[1], 1);
-        fetch(buf[2], 2);
-        for (int c4 = 0; c4 < nchunks && ok; c4 += 4) {  // nchunks is a multiple of 4 (n_in % 256 == 0)
+        auto f_open = [&]() {
+            if (f_left > 0) {
+                const Item it = decode_item(f_item, row_tiles, nseg, tile_prefix, seg);
+                f_pa = it.wa + (size_t)(it.r0 + r) * rb;
+                if constexpr (NMAT == 2) f_pb = it.wb + (size_t)(it.r0 + r) * rb;
+                l2_prefetch_item(f_item + G);
+            }
+        };
+        l2_prefetch_item(blockIdx.x);
+        auto fetch = [&](Raw& q) {
+            if (f_left <= 0) return;
+            const int off = (f_c >> 2) * 144;
+            if ((f_c & 3) == 0) {  // a new block: its header is needed two chunks from now
+                hdr_next.ha = ld_weights_keep(f_pa + off);
+                if constexpr (NMAT == 2) hdr_next.hb = ld_weights_keep(f_pb + off);
+            }
+            const int qoff = off + 16 + 32 * (f_c & 3) + 16 * p;
+            q.qa = ld_weights_stream(f_pa + qoff);
+            if constexpr (NMAT == 2) q.qb = ld_weights_stream(f_pb + qoff);
+            if (++f_c == nchunks) {
+                f_c = 0;
+                f_item += G;
+                --f_left;
+                f_open();
+            }
+        };
+        f_open();
+        fetch(buf[0]);
+        fetch(buf[1]);
+        const int total = my_items * nchunks;  // nchunks is a multiple of 4 (n_in % 256 == 0)
+        for (int g4 = 0; g4 < total && ok; g4 += 4) {
+            hdr_cur = hdr_next;  // the fetch cursor entered this block two chunks ago
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                const int c = c4 + i;
-                if (c + 3 < nchunks) fetch(buf[(i + 3) & 3], c + 3);
-                const int st = c % STAGES;
-                const uint32_t ph = (uint32_t)(c / STAGES) & 1u;
-                if (ok && c >= STAGES) ok = mb_wait(&empty[st], ph ^ 1u, status, 2);
+                const int g = g4 + i;
+                const int st = g % STAGES;
+                const uint32_t ph = (uint32_t)(g / STAGES) & 1u;
+                if (ok && g >= STAGES) ok = mb_wait(&empty[st], ph ^ 1u, status, 2);
                 if (ok) {
                     uint8_t* sa = smem + st * STAGE_BYTES;
-                    dequant_q4k_stage(buf[i].ha, buf[i].a0, buf[i].a1, c & 3, half, sa, sa + A_TILE, r);
+                    // The chunk's bytes were requested two chunks ago.  The next request
+                    // is issued only after they have been consumed: a wait on a load must
+                    // never also cover a load issued just before it.
+                    dequant_q4k_task(hdr_cur.ha, buf[i & 1].qa, i, nh, p, sa, sa + A_TILE, r);
                     if constexpr (NMAT == 2)
-                        dequant_q4k_stage(buf[i].hb, buf[i].b0, buf[i].b1, c & 3, half, sa + 2 * A_TILE, sa + 3 * A_TILE, r);
+                        dequant_q4k_task(hdr_cur.hb, buf[i & 1].qb, i, nh, p, sa + 2 * A_TILE, sa + 3 * A_TILE, r);
+                    fetch(buf[i & 1]);  // chunk g + 2
                     fence_async_smem();   // generic-proxy stores -> visible to the tensor core's async proxy
                     __syncwarp();
                     if (lane == 0) mb_arrive(&full[st]);
                 }
             }
         }
-        // ---------------- epilogue: TMEM lane = weight row ----------------
-        if (ok && warp < 4) ok = mb_wait(accum, 0, status, 3);
-        tc_fence_after();
-        if (ok && warp < 4) {
-            const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-            const size_t prow0 = (size_t)sd.row0 + t0;
-            for (int c0 = 0; c0 < N; c0 += 16) {
-                uint32_t g[16], u[16];
-                tmem_ld16(tmem_base + lane_base + (uint32_t)c0, g);
-                if constexpr (NMAT == 2) tmem_ld16(tmem_base + lane_base + (uint32_t)(128 + c0), u);
-                tmem_ld_wait();
-#pragma unroll
-                for (int j2 = 0; j2 < 16; ++j2) {
-                    const int t = c0 + j2;
-                    if (t < m_tile) {
-                        if constexpr (NMAT == 2) {
-                            const float gv = __uint_as_float(g[j2]), uv = __uint_as_float(u[j2]);
-                            const float a = gv / (1.0f + expf(-gv)) * uv;
-                            const uint16_t ah = __bfloat16_as_ushort(__float2bfloat16_rn(a));
-                            const float al = a - __uint_as_float((uint32_t)ah << 16);
-                            const size_t o = (prow0 + t) * (size_t)n_out + r0 + r;
-                            out_hi[o] = ah;
-                            out_lo[o] = (uint16_t)(__float_as_uint(al) >> 16);
-                        } else {
-                            out_f32[(prow0 + t) * (size_t)n_out + r0 + r] = __uint_as_float(g[j2]);
-                        }
-                    }
+    } else if (warp == W_TMA) {
+        // ---------------- TMA: activation tiles ----------------
+        if (lane == 0) {
+            int g = 0;
+            for (int k = 0; k < my_items && ok; ++k) {
+                const Item it = decode_item(blockIdx.x + k * G, row_tiles, nseg, tile_prefix, seg);
+                const int nsel = nsel_of(it.m_tile), N = 16 << nsel;
+                const CUtensorMap* mh = &maps.hi[nsel];
+                const CUtensorMap* ml = &maps.lo[nsel];
+                const uint32_t bbytes = (uint32_t)(2 * N * BK * 2);
+                for (int c = 0; c < nchunks; ++c, ++g) {
+                    const int st = g % STAGES;
+                    const uint32_t ph = (uint32_t)(g / STAGES) & 1u;
+                    if (g >= STAGES && !mb_wait(&empty[st], ph ^ 1u, status, 4)) { ok = false; break; }
+                    uint8_t* sbp = smem + st * STAGE_BYTES + A_BYTES;
+                    mb_expect_tx(&full[st], bbytes);
+                    tma_load_2d(sbp, mh, c * BK, it.prow, &full[st]);
+                    tma_load_2d(sbp + N * BK * 2, ml, c * BK, it.prow, &full[st]);
                 }
             }
         }
-        tc_fence_before();
-    } else if (warp == PWARPS) {
-        // ---------------- TMA: activation tiles ----------------
+    } else if (warp == W_MMA) {
+        // ---------------- MMA issue ----------------
         if (lane == 0) {
-            const CUtensorMap* mh = &maps.hi[nsel];
-            const CUtensorMap* ml = &maps.lo[nsel];
-            const int yrow = (int)sd.row0 + t0;
-            const uint32_t bbytes = (uint32_t)(2 * N * BK * 2);
-            for (int c = 0; c < nchunks; ++c) {
-                const int st = c % STAGES;
-                const uint32_t ph = (uint32_t)(c / STAGES) & 1u;
-                if (c >= STAGES && !mb_wait(&empty[st], ph ^ 1u, status, 4)) break;
-                uint8_t* sbp = smem + st * STAGE_BYTES + A_BYTES;
-                mb_expect_tx(&full[st], bbytes);
-                tma_load_2d(sbp, mh, c * BK, yrow, &full[st]);
-                tma_load_2d(sbp + N * BK * 2, ml, c * BK, yrow, &full[st]);
+            const uint32_t smem_lo = desc_lo(s32(smem));
+            int g = 0;
+            for (int k = 0; k < my_items && ok; ++k) {
+                const Item it = decode_item(blockIdx.x + k * G, row_tiles, nseg, tile_prefix, seg);
+                const int N = 16 << nsel_of(it.m_tile);
+                const uint32_t idesc = make_idesc(N);
+                const int ab = k & 1;
+                // the epilogue must have read this buffer's previous use (item k - 2)
+                if (k >= 2 && !mb_wait(&drained[ab], (uint32_t)((k >> 1) - 1) & 1u, status, 6)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t dbase = tmem_base + (uint32_t)(ab * ACC_COLS);
+                for (int c = 0; c < nchunks; ++c, ++g) {
+                    const int st = g % STAGES;
+                    const uint32_t ph = (uint32_t)(g / STAGES) & 1u;
+                    if (!mb_wait(&full[st], ph, status, 5)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_lo = smem_lo + (uint32_t)(st * (STAGE_BYTES >> 4));
+                    const uint32_t bh_lo = a_lo + (A_BYTES >> 4), bl_lo = bh_lo + (uint32_t)((N * BK * 2) >> 4);
+#pragma unroll
+                    for (int ks = 0; ks < BK / 16; ++ks) {
+                        const uint32_t koff = ks * 2;  // 16 bf16 = 32 bytes inside the swizzle row, >> 4
+                        const uint64_t bh = desc_of(bh_lo + koff), bl = desc_of(bl_lo + koff);
+#pragma unroll
+                        for (int mt = 0; mt < NMAT; ++mt) {
+                            const uint64_t ah = desc_of(a_lo + (uint32_t)(mt * 2 * (A_TILE >> 4)) + koff);
+                            const uint64_t al = desc_of(a_lo + (uint32_t)(mt * 2 * (A_TILE >> 4) + (A_TILE >> 4)) + koff);
+                            const uint32_t d = dbase + (uint32_t)(mt * 128);
+                            mma_bf16(d, ah, bh, idesc, (c > 0 || ks > 0) ? 1u : 0u);
+                            mma_bf16(d, ah, bl, idesc, 1u);
+                            mma_bf16(d, al, bh, idesc, 1u);
+                        }
+                    }
+                    mma_commit(&empty[st]);   // frees the stage once these MMAs have read it
+                }
+                if (ok) mma_commit(&accum[ab]);  // all MMAs of the item done -> accumulators readable
             }
         }
     } else {
-        // ---------------- MMA issue ----------------
-        if (lane == 0) {
-            const uint32_t idesc = make_idesc(N);
-            for (int c = 0; c < nchunks; ++c) {
-                const int st = c % STAGES;
-                const uint32_t ph = (uint32_t)(c / STAGES) & 1u;
-                if (!mb_wait(&full[st], ph, status, 5)) break;
-                tc_fence_after();
-                const uint32_t sa = s32(smem + st * STAGE_BYTES);
-                const uint32_t sbh = sa + A_BYTES, sbl = sbh + N * BK * 2;
+        // ---------------- epilogue: TMEM lane = weight row ----------------
+        const int quad = warp & 3;  // the TMEM lanes a warp may read: 32 * (warp % 4) ..
+        const int r = quad * 32 + lane;
+        for (int k = 0; k < my_items && ok; ++k) {
+            const Item it = decode_item(blockIdx.x + k * G, row_tiles, nseg, tile_prefix, seg);
+            const int N = 16 << nsel_of(it.m_tile);
+            const int ab = k & 1;
+            ok = mb_wait(&accum[ab], (uint32_t)(k >> 1) & 1u, status, 3);
+            tc_fence_after();
+            if (!ok) break;
+            const uint32_t tb = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(ab * ACC_COLS);
+            for (int c0 = 0; c0 < N; c0 += 16) {
+                uint32_t gq[16], uq[16];
+                tmem_ld16(tb + (uint32_t)c0, gq);
+                if constexpr (NMAT == 2) tmem_ld16(tb + (uint32_t)(128 + c0), uq);
+                tmem_ld_wait();
+                const int nv = min(16, it.m_tile - c0);
+                if constexpr (NMAT == 2) {
+                    uint16_t* oh = out_hi + (size_t)(it.prow + c0) * n_out + it.r0 + r;
+                    uint16_t* ol = out_lo + (size_t)(it.prow + c0) * n_out + it.r0 + r;
 #pragma unroll
-                for (int ks = 0; ks < BK / 16; ++ks) {
-                    const uint32_t koff = ks * 32;  // 16 bf16 = 32 bytes inside the swizzle row
-                    const uint64_t bh = make_desc(sbh + koff), bl = make_desc(sbl + koff);
-#pragma unroll
-                    for (int mt = 0; mt < NMAT; ++mt) {
-                        const uint64_t ah = make_desc(sa + mt * 2 * A_TILE + koff);
-                        const uint64_t al = make_desc(sa + mt * 2 * A_TILE + A_TILE + koff);
-                        const uint32_t d = tmem_base + (uint32_t)(mt * 128);
-                        mma_bf16(d, ah, bh, idesc, (c > 0 || ks > 0) ? 1u : 0u);
-                        mma_bf16(d, ah, bl, idesc, 1u);
-                        mma_bf16(d, al, bh, idesc, 1u);
+                    for (int j2 = 0; j2 < 16; ++j2) {
+                        const float a = swiglu_fast(__uint_as_float(gq[j2]), __uint_as_float(uq[j2]));
+                        const uint16_t ah = __bfloat16_as_ushort(__float2bfloat16_rn(a));
+                        const float al = a - __uint_as_float((uint32_t)ah << 16);
+                        if (j2 < nv) {
+                            oh[(size_t)j2 * n_out] = ah;
+                            ol[(size_t)j2 * n_out] = (uint16_t)(__float_as_uint(al) >> 16);
+                        }
                     }
+                } else {
+                    float* of = out_f32 + (size_t)(it.prow + c0) * n_out + it.r0 + r;
+#pragma unroll
+                    for (int j2 = 0; j2 < 16; ++j2)
+                        if (j2 < nv) of[(size_t)j2 * n_out] = __uint_as_float(gq[j2]);
                 }
-                mma_commit(&empty[st]);   // frees the stage once these MMAs have read it
             }
-            mma_commit(accum);            // all MMAs done -> accumulators readable
+            tc_fence_before();  // TMEM reads ordered before the hand-back of the buffer
+            __syncwarp();
+            if (lane == 0) mb_arrive(&drained[ab]);
         }
-        __syncwarp();
     }
+    tc_fence_before();
     __syncthreads();
-    if (warp == PWARPS + 1) {
+    if (warp == W_MMA) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TM_COLS) : "memory");
     }
@@ -454,9 +595,11 @@ int launch_grouped_umma(dnb_ctx* c, cudaStream_t st, bool fused, const SegDesc* 
     if (n_in % 256 || n_out % um::TILE_M) return DNB_DECLINED;
     const int rb = n_in / 256 * 144;
     const um::Maps& M = *reinterpret_cast<const um::Maps*>(maps);
-    const dim3 grid(n_out / um::TILE_M, nseg_max, (nt_max + 127) / 128);
+    if (nseg_max > um::kMaxSeg) return DNB_DECLINED;
+    (void)nt_max;
+    const dim3 grid(c->sm_count);  // persistent: one CTA per SM loops over the tiles
     if (fused) {
-        const size_t smem = 2 * (2 * 2 * um::A_TILE + 2 * 128 * um::BK * 2) + 256 + 1024;
+        const size_t smem = 2 * (2 * 2 * um::A_TILE + 2 * 128 * um::BK * 2) + 256 + (um::kMaxSeg + 1) * 4 + 1024;
         static bool set = false;
         if (!set) {
             DNB_CUDA(cudaFuncSetAttribute(um::grouped_q4k_umma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -466,7 +609,7 @@ int launch_grouped_umma(dnb_ctx* c, cudaStream_t st, bool fused, const SegDesc* 
         um::grouped_q4k_umma_kernel<2><<<grid, um::NTHREADS, smem, st>>>(seg, nseg_dev, n_in, n_out, rb, M, out_hi, out_lo,
                                                                         nullptr, c->status);
     } else {
-        const size_t smem = 3 * (2 * um::A_TILE + 2 * 128 * um::BK * 2) + 256 + 1024;
+        const size_t smem = 3 * (2 * um::A_TILE + 2 * 128 * um::BK * 2) + 256 + (um::kMaxSeg + 1) * 4 + 1024;
         static bool set = false;
         if (!set) {
             DNB_CUDA(cudaFuncSetAttribute(um::grouped_q4k_umma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
