@@ -5,35 +5,38 @@
 // 134-273 (fp32 FMA), kernels_exp_k_pf.cu:188-258 (m-row fp32).  The reference has
 // no tensor-core kernel for Q4_K experts at all.
 //
-// Design (sm_100a).  One CTA computes, for one expert segment, a tile of 128 weight
-// rows x up to 128 token rows over the whole K:
+// Design (sm_100a).  A work item is, for one expert segment, a tile of 128 weight rows
+// x up to 128 token rows over the whole K:
 //   D[128 rows][N tokens] (fp32, in TMEM) = W[128][K] * X[N][K]^T
 // issued as tcgen05.mma (cta_group::1, kind::f16, M=128, K=16 per instruction) by
-// one thread.  W is the A operand and the tokens are the N dimension, so N is only
-// as wide as the segment needs (16/32/64/128) and a 3-token expert does not pay
-// for a 128-token tile.
+// one elected thread.  W is the A operand and the tokens are the N dimension, so N is
+// only as wide as the segment needs (16/32/64/128) and a 3-token expert does not pay
+// for a 128-token tile.  The kernel is persistent: one CTA per SM walks the items
+// i, i + gridDim.x, ... (the segment table is sorted by token count, heavy tiles first).
 //
 // Precision.  The path's bar is max|err| <= 1e-3 of the output RMS, which a single
 // bf16 rounding of both operands misses by several times.  Each operand is
 // therefore split into two bf16 numbers (hi = the value rounded to bf16, lo = the
 // exact remainder truncated to bf16), and three MMAs hi*hi + hi*lo + lo*hi
 // accumulate into the same TMEM tile; the dropped lo*lo term is about 2^-18
-// relative per product.
+// relative per product.  The three products are issued in the same order for every
+// tile width, so a token's result does not depend on which tokens share its chunk.
 //
 // Operands.
-//   A (weights): eight warps dequantise Q4_K bytes straight from global memory,
-//      two threads per row and 64 elements per stage, split to hi/lo bf16 and store
-//      the two tiles in the K-major 128-byte-swizzled layout the MMA reads.
+//   A (weights): sixteen producer warps dequantise Q4_K bytes straight from global
+//      memory (raw bytes prefetched in registers two steps ahead, the whole next tile
+//      prefetched into L2), split to hi/lo bf16 and store the tiles in the K-major
+//      128-byte-swizzled layout the MMA reads.
 //   B (activations): a pre-pass gathers the routed token rows into the expert-major
 //      packed order and splits them into hi/lo bf16 buffers once per layer; the
 //      tiles then arrive by TMA (cp.async.bulk.tensor.2d, 128B swizzle), N rows x 64
 //      elements, signalled on the stage's mbarrier.
 // Pipeline: `full[s]` (8 producer-warp arrivals + TMA bytes) -> MMA thread ->
-// tcgen05.commit -> `empty[s]`; after the last stage a commit on `accum`.
-// Epilogue: producer warps 0-3 read their 32 TMEM lanes (= weight rows) with
-// tcgen05.ld; gate/up tiles are combined as silu(g)*u and written as hi/lo bf16 in
-// packed-row order (the B operand of the down GEMM); down tiles are written as
-// fp32 rows for the weighted combine.
+// tcgen05.commit -> `empty[s]`; after an item's last stage a commit on `accum[b]`.
+// Epilogue: four warps read their 32 TMEM lanes (= weight rows) of accumulator buffer b
+// with tcgen05.ld while the main loop fills buffer 1 - b; gate/up tiles are combined as
+// silu(g)*u and written as hi/lo bf16 in packed-row order (the B operand of the down
+// GEMM); down tiles are written as fp32 rows for the weighted combine.
 //
 // Every wait is bounded; a wait that gives up sets *status and the CTA falls
 // through to the common teardown (TMEM is always freed).
@@ -50,6 +53,7 @@ namespace um {
 constexpr int BK = 64;            // K elements per stage (one 128-byte swizzle row of bf16)
 constexpr int TILE_M = 128;       // weight rows per CTA
 constexpr int A_TILE = TILE_M * BK * 2;   // 16 KB
+constexpr int kLocalItems = 64;   // items of a CTA decoded once into shared memory
 constexpr int kMaxSeg = 1055;    // segments the per-CTA tile prefix table holds
 constexpr int PWARPS = 16;        // producer warps: four threads per weight row and matrix (16 elements each per stage)
 constexpr int W_TMA = PWARPS;     // warp that issues the activation tile copies
@@ -198,6 +202,15 @@ __device__ __forceinline__ uint4 ld_weights_keep(const void* p) {  // shared by 
     return v;
 }
 
+// One lane of a converged warp.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t p;
+    asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}" : "=r"(p));
+    return p != 0;
+}
+// A flag the whole warp agrees on (and the compiler knows it does).
+__device__ __forceinline__ bool warp_all(bool v) { return __all_sync(0xffffffffu, v); }
+
 // Ask L2 to fetch `bytes` (a multiple of 16) from a 16-byte aligned address; no register,
 // no shared memory, nothing to wait for.
 __device__ __forceinline__ void prefetch_l2(const void* p, uint32_t bytes) {
@@ -231,11 +244,121 @@ __device__ __forceinline__ Item decode_item(int item, int row_tiles, int nseg, c
     it.r0 = rt * TILE_M;
     return it;
 }
+// The CTA's k-th item: from the table filled at kernel start, or decoded on the spot when
+// the CTA has more items than the table holds.
+struct ItemTab {
+    const Item* tab;
+    const SegDesc* seg;
+    const int* tile_prefix;
+    int nseg, row_tiles;
+    __device__ __forceinline__ Item get(int k) const {
+        if (k < kLocalItems) return tab[k];
+        return decode_item((int)blockIdx.x + k * (int)gridDim.x, row_tiles, nseg, tile_prefix, seg);
+    }
+};
 __device__ __forceinline__ int nsel_of(int m_tile) { return m_tile <= 16 ? 0 : (m_tile <= 32 ? 1 : (m_tile <= 64 ? 2 : 3)); }
 
 // silu(g) * u with the fast exponential and reciprocal: their ~1e-6 relative error
 // is far inside what the bf16 hi/lo products already carry.
 __device__ __forceinline__ float swiglu_fast(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
+
+// What a producer warp needs from the kernel.
+struct ProducerArgs {
+    ItemTab items;
+    uint8_t* smem;
+    uint64_t* full;
+    uint64_t* empty;
+    int* status;
+    int my_items, nchunks, rb;
+};
+
+// Producer warps.  The sixteen warps form two groups of eight; group GRP dequantises the
+// chunks g with g % 2 == GRP, all 128 rows of them, so the two groups fill two different
+// stages at the same time and one group's waits (stage free, bytes arrived, stores
+// visible) are covered by the other group's arithmetic.  Inside a group a warp owns 16
+// rows x 2 qs pieces (a request covers whole 32-byte sectors) and a thread dequantises
+// both nibbles of its 16 bytes: 32 elements per matrix and chunk.  Raw bytes are
+// requested two of the group's chunks ahead, through item boundaries.
+template <int NMAT, int STAGES, int STAGE_BYTES, int GRP>
+__device__ __forceinline__ bool produce(const ProducerArgs& a, int w8, int lane) {
+    const int r = w8 * 16 + (lane & 15), p = lane >> 4;
+    struct Raw { uint4 qa, qb; };   // one chunk's 16 qs bytes per matrix
+    struct Hdr { uint4 ha, hb; };   // one block's d, dmin and scale bytes per matrix
+    Raw buf[2];
+    Hdr hdr_cur, hdr_next;
+    int f_left = a.my_items, f_k = 0, f_c = GRP;  // fetch cursor: item (CTA-local index) and chunk
+    const uint8_t* f_pa = nullptr;
+    const uint8_t* f_pb = nullptr;
+    // One thread per weight row asks L2 for the whole row of an item a full item ahead of
+    // its use: the register prefetch below then hits L2, and the bytes in flight towards
+    // HBM are a tile (36-147 KB per matrix), not a few chunks.
+    auto l2_prefetch_item = [&](int k) {
+        if (GRP == 0 && p == 0 && k < a.my_items) {
+            const Item it = a.items.get(k);
+            prefetch_l2(it.wa + (size_t)(it.r0 + r) * a.rb, (uint32_t)a.rb);
+            if constexpr (NMAT == 2) prefetch_l2(it.wb + (size_t)(it.r0 + r) * a.rb, (uint32_t)a.rb);
+        }
+    };
+    auto f_open = [&]() {
+        if (f_left > 0) {
+            const Item it = a.items.get(f_k);
+            f_pa = it.wa + (size_t)(it.r0 + r) * a.rb;
+            if constexpr (NMAT == 2) f_pb = it.wb + (size_t)(it.r0 + r) * a.rb;
+            l2_prefetch_item(f_k + 1);
+        }
+    };
+    auto fetch = [&](Raw& q) {
+        if (f_left <= 0) return;
+        const int off = (f_c >> 2) * 144;
+        if ((f_c & 3) == GRP) {  // the group's first chunk of a block: fetch the block header too
+            hdr_next.ha = ld_weights_keep(f_pa + off);
+            if constexpr (NMAT == 2) hdr_next.hb = ld_weights_keep(f_pb + off);
+        }
+        const int qoff = off + 16 + 32 * (f_c & 3) + 16 * p;
+        q.qa = ld_weights_stream(f_pa + qoff);
+        if constexpr (NMAT == 2) q.qb = ld_weights_stream(f_pb + qoff);
+        f_c += 2;
+        if (f_c >= a.nchunks) {
+            f_c = GRP;
+            ++f_k;
+            --f_left;
+            f_open();
+        }
+    };
+    l2_prefetch_item(0);
+    f_open();
+    fetch(buf[0]);
+    fetch(buf[1]);
+    bool ok = true;
+    const int total = a.my_items * a.nchunks;  // a multiple of 4: n_in % 256 == 0
+    for (int g4 = 0; g4 < total && ok; g4 += 4) {
+        hdr_cur = hdr_next;  // fetched one block (two of the group's chunks) ago
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int j = GRP + 2 * i;  // chunk inside the block
+            const int g = g4 + j;
+            const int st = g % STAGES;
+            const uint32_t ph = (uint32_t)(g / STAGES) & 1u;
+            if (ok && g >= STAGES) ok = mb_wait(&a.empty[st], ph ^ 1u, a.status, 2);
+            if (ok) {
+                uint8_t* sa = a.smem + st * STAGE_BYTES;
+                // The chunk's bytes were requested two steps ago.  The next request is
+                // issued only after they have been consumed: a wait on a load must never
+                // also cover a load issued just before it.
+#pragma unroll
+                for (int nh = 0; nh < 2; ++nh) {
+                    dequant_q4k_task(hdr_cur.ha, buf[i].qa, j, nh, p, sa, sa + A_TILE, r);
+                    if constexpr (NMAT == 2) dequant_q4k_task(hdr_cur.hb, buf[i].qb, j, nh, p, sa + 2 * A_TILE, sa + 3 * A_TILE, r);
+                }
+                fetch(buf[i]);
+                fence_async_smem();   // generic-proxy stores -> visible to the tensor core's async proxy
+                __syncwarp();
+                if (lane == 0) mb_arrive(&a.full[st]);
+            }
+        }
+    }
+    return ok;
+}
 
 // NMAT = 2: gate and up tiles together, SwiGLU epilogue to out_hi / out_lo (bf16 packed rows).
 // NMAT = 1: one matrix, fp32 epilogue to out_f32.
@@ -244,9 +367,8 @@ __device__ __forceinline__ float swiglu_fast(float g, float u) { return __fdivid
 // Work items are (segment, 128-token tile, 128-row tile), item i handled by CTA
 // i mod gridDim.x in increasing order; every role walks the same item sequence on
 // its own, coupled only through mbarriers:
-//   warps 0-15   producers: dequantise the weight rows into the stage (16 elements
-//                per thread and matrix), prefetching raw bytes two chunks ahead and
-//                across item boundaries
+//   warps 0-15   producers in two groups of eight; a group dequantises every second
+//                chunk into its stage (32 elements per thread and matrix)
 //   warp 16      TMA: activation tiles of the stage
 //   warp 17      MMA issue (one thread); owns the TMEM allocation
 //   warps 18-21  epilogue: read the finished accumulators of item i from TMEM while
@@ -272,6 +394,7 @@ grouped_q4k_umma_kernel(const SegDesc* __restrict__ seg, const int32_t* __restri
     uint64_t* drained = accum + 2;        // [2] accumulator buffer read out (4 epilogue warps)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drained + 2);
     int* tile_prefix = reinterpret_cast<int*>(tmem_slot + 2);  // [nseg + 1] token tiles before each segment
+    Item* itab = reinterpret_cast<Item*>(smem + STAGES * STAGE_BYTES + 256 + (kMaxSeg + 1) * 4);  // [kLocalItems]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nchunks = n_in / BK;
@@ -280,7 +403,7 @@ grouped_q4k_umma_kernel(const SegDesc* __restrict__ seg, const int32_t* __restri
 
     if (tid == 0) {
         for (int i = 0; i < STAGES; ++i) {
-            mb_init(&full[i], PWARPS + 1);  // producer warps + the TMA thread's expect_tx arrival
+            mb_init(&full[i], PWARPS / 2 + 1);  // one producer group + the TMA thread's expect_tx arrival
             mb_init(&empty[i], 1);          // one tcgen05.commit
         }
         for (int i = 0; i < 2; ++i) {
@@ -319,126 +442,65 @@ grouped_q4k_umma_kernel(const SegDesc* __restrict__ seg, const int32_t* __restri
     const int n_items = nseg > 0 ? tile_prefix[nseg] * row_tiles : 0;
     const int G = gridDim.x;
     const int my_items = (int)blockIdx.x < n_items ? (n_items - (int)blockIdx.x + G - 1) / G : 0;
+    if (tid < min(my_items, kLocalItems)) itab[tid] = decode_item((int)blockIdx.x + tid * G, row_tiles, nseg, tile_prefix, seg);
+    __syncthreads();
+    const ItemTab items{itab, seg, tile_prefix, nseg, row_tiles};
     bool ok = true;
 
     if (warp < PWARPS) {
         // ---------------- producers ----------------
-        // 16 rows x 2 qs pieces per warp (a request covers whole 32-byte sectors);
-        // warps 0-7 take the low nibbles, warps 8-15 the high nibbles of the same bytes.
-        const int r = (warp & 7) * 16 + (lane & 15), p = lane >> 4, nh = warp >> 3;
-        struct Raw { uint4 qa, qb; };   // one chunk's 16 qs bytes per matrix
-        struct Hdr { uint4 ha, hb; };   // one block's d, dmin and scale bytes per matrix
-        Raw buf[2];
-        Hdr hdr_cur, hdr_next;
-        // fetch cursor: runs two chunks ahead of the dequantisation, through item boundaries
-        int f_left = my_items, f_item = blockIdx.x, f_c = 0;
-        const uint8_t* f_pa = nullptr;
-        const uint8_t* f_pb = nullptr;
-        // One thread per weight row asks L2 for the whole row of an item a full item ahead
-        // of its use: the register prefetch below then hits L2, and the bytes in flight
-        // towards HBM are a tile (36-147 KB per matrix), not two chunks.
-        auto l2_prefetch_item = [&](int item) {
-            if (nh == 0 && p == 0 && item < n_items) {
-                const Item it = decode_item(item, row_tiles, nseg, tile_prefix, seg);
-                prefetch_l2(it.wa + (size_t)(it.r0 + r) * rb, (uint32_t)rb);
-                if constexpr (NMAT == 2) prefetch_l2(it.wb + (size_t)(it.r0 + r) * rb, (uint32_t)rb);
-            }
-        };
-        auto f_open = [&]() {
-            if (f_left > 0) {
-                const Item it = decode_item(f_item, row_tiles, nseg, tile_prefix, seg);
-                f_pa = it.wa + (size_t)(it.r0 + r) * rb;
-                if constexpr (NMAT == 2) f_pb = it.wb + (size_t)(it.r0 + r) * rb;
-                l2_prefetch_item(f_item + G);
-            }
-        };
-        l2_prefetch_item(blockIdx.x);
-        auto fetch = [&](Raw& q) {
-            if (f_left <= 0) return;
-            const int off = (f_c >> 2) * 144;
-            if ((f_c & 3) == 0) {  // a new block: its header is needed two chunks from now
-                hdr_next.ha = ld_weights_keep(f_pa + off);
-                if constexpr (NMAT == 2) hdr_next.hb = ld_weights_keep(f_pb + off);
-            }
-            const int qoff = off + 16 + 32 * (f_c & 3) + 16 * p;
-            q.qa = ld_weights_stream(f_pa + qoff);
-            if constexpr (NMAT == 2) q.qb = ld_weights_stream(f_pb + qoff);
-            if (++f_c == nchunks) {
-                f_c = 0;
-                f_item += G;
-                --f_left;
-                f_open();
-            }
-        };
-        f_open();
-        fetch(buf[0]);
-        fetch(buf[1]);
-        const int total = my_items * nchunks;  // nchunks is a multiple of 4 (n_in % 256 == 0)
-        for (int g4 = 0; g4 < total && ok; g4 += 4) {
-            hdr_cur = hdr_next;  // the fetch cursor entered this block two chunks ago
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int g = g4 + i;
-                const int st = g % STAGES;
-                const uint32_t ph = (uint32_t)(g / STAGES) & 1u;
-                if (ok && g >= STAGES) ok = mb_wait(&empty[st], ph ^ 1u, status, 2);
-                if (ok) {
-                    uint8_t* sa = smem + st * STAGE_BYTES;
-                    // The chunk's bytes were requested two chunks ago.  The next request
-                    // is issued only after they have been consumed: a wait on a load must
-                    // never also cover a load issued just before it.
-                    dequant_q4k_task(hdr_cur.ha, buf[i & 1].qa, i, nh, p, sa, sa + A_TILE, r);
-                    if constexpr (NMAT == 2)
-                        dequant_q4k_task(hdr_cur.hb, buf[i & 1].qb, i, nh, p, sa + 2 * A_TILE, sa + 3 * A_TILE, r);
-                    fetch(buf[i & 1]);  // chunk g + 2
-                    fence_async_smem();   // generic-proxy stores -> visible to the tensor core's async proxy
-                    __syncwarp();
-                    if (lane == 0) mb_arrive(&full[st]);
-                }
-            }
-        }
+        ProducerArgs pa{items, smem, full, empty, status, my_items, nchunks, rb};
+        if (warp < PWARPS / 2) ok = produce<NMAT, STAGES, STAGE_BYTES, 0>(pa, warp, lane);
+        else ok = produce<NMAT, STAGES, STAGE_BYTES, 1>(pa, warp - PWARPS / 2, lane);
     } else if (warp == W_TMA) {
         // ---------------- TMA: activation tiles ----------------
-        if (lane == 0) {
-            int g = 0;
-            for (int k = 0; k < my_items && ok; ++k) {
-                const Item it = decode_item(blockIdx.x + k * G, row_tiles, nseg, tile_prefix, seg);
-                const int nsel = nsel_of(it.m_tile), N = 16 << nsel;
-                const CUtensorMap* mh = &maps.hi[nsel];
-                const CUtensorMap* ml = &maps.lo[nsel];
-                const uint32_t bbytes = (uint32_t)(2 * N * BK * 2);
-                for (int c = 0; c < nchunks; ++c, ++g) {
-                    const int st = g % STAGES;
-                    const uint32_t ph = (uint32_t)(g / STAGES) & 1u;
-                    if (g >= STAGES && !mb_wait(&empty[st], ph ^ 1u, status, 4)) { ok = false; break; }
-                    uint8_t* sbp = smem + st * STAGE_BYTES + A_BYTES;
+        // The whole warp walks the loop and waits; one elected lane issues.  Addresses,
+        // coordinates and descriptors are then the same in every lane, which lets the
+        // compiler keep them in the registers the copy and MMA instructions read.
+        int g = 0;
+        for (int k = 0; k < my_items && ok; ++k) {
+            const Item it = items.get(k);
+            const int nsel = nsel_of(it.m_tile), N = 16 << nsel;
+            const CUtensorMap* mh = &maps.hi[nsel];
+            const CUtensorMap* ml = &maps.lo[nsel];
+            const uint32_t bbytes = (uint32_t)(2 * N * BK * 2);
+            for (int c = 0; c < nchunks; ++c, ++g) {
+                const int st = g % STAGES;
+                const uint32_t ph = (uint32_t)(g / STAGES) & 1u;
+                if (g >= STAGES) ok = warp_all(mb_wait(&empty[st], ph ^ 1u, status, 4));
+                if (!ok) break;
+                uint8_t* sbp = smem + st * STAGE_BYTES + A_BYTES;
+                if (elect_one()) {
                     mb_expect_tx(&full[st], bbytes);
                     tma_load_2d(sbp, mh, c * BK, it.prow, &full[st]);
                     tma_load_2d(sbp + N * BK * 2, ml, c * BK, it.prow, &full[st]);
                 }
+                __syncwarp();
             }
         }
     } else if (warp == W_MMA) {
         // ---------------- MMA issue ----------------
-        if (lane == 0) {
-            const uint32_t smem_lo = desc_lo(s32(smem));
-            int g = 0;
-            for (int k = 0; k < my_items && ok; ++k) {
-                const Item it = decode_item(blockIdx.x + k * G, row_tiles, nseg, tile_prefix, seg);
-                const int N = 16 << nsel_of(it.m_tile);
-                const uint32_t idesc = make_idesc(N);
-                const int ab = k & 1;
-                // the epilogue must have read this buffer's previous use (item k - 2)
-                if (k >= 2 && !mb_wait(&drained[ab], (uint32_t)((k >> 1) - 1) & 1u, status, 6)) { ok = false; break; }
+        const uint32_t smem_lo = desc_lo(s32(smem));
+        int g = 0;
+        for (int k = 0; k < my_items && ok; ++k) {
+            const Item it = items.get(k);
+            const int N = 16 << nsel_of(it.m_tile);
+            const uint32_t idesc = make_idesc(N);
+            const int ab = k & 1;
+            // the epilogue must have read this buffer's previous use (item k - 2)
+            if (k >= 2) ok = warp_all(mb_wait(&drained[ab], (uint32_t)((k >> 1) - 1) & 1u, status, 6));
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t dbase = tmem_base + (uint32_t)(ab * ACC_COLS);
+            for (int c = 0; c < nchunks; ++c, ++g) {
+                const int st = g % STAGES;
+                const uint32_t ph = (uint32_t)(g / STAGES) & 1u;
+                ok = warp_all(mb_wait(&full[st], ph, status, 5));
+                if (!ok) break;
                 tc_fence_after();
-                const uint32_t dbase = tmem_base + (uint32_t)(ab * ACC_COLS);
-                for (int c = 0; c < nchunks; ++c, ++g) {
-                    const int st = g % STAGES;
-                    const uint32_t ph = (uint32_t)(g / STAGES) & 1u;
-                    if (!mb_wait(&full[st], ph, status, 5)) { ok = false; break; }
-                    tc_fence_after();
-                    const uint32_t a_lo = smem_lo + (uint32_t)(st * (STAGE_BYTES >> 4));
-                    const uint32_t bh_lo = a_lo + (A_BYTES >> 4), bl_lo = bh_lo + (uint32_t)((N * BK * 2) >> 4);
+                const uint32_t a_lo = smem_lo + (uint32_t)(st * (STAGE_BYTES >> 4));
+                const uint32_t bh_lo = a_lo + (A_BYTES >> 4), bl_lo = bh_lo + (uint32_t)((N * BK * 2) >> 4);
+                if (elect_one()) {
 #pragma unroll
                     for (int ks = 0; ks < BK / 16; ++ks) {
                         const uint32_t koff = ks * 2;  // 16 bf16 = 32 bytes inside the swizzle row, >> 4
@@ -448,14 +510,17 @@ grouped_q4k_umma_kernel(const SegDesc* __restrict__ seg, const int32_t* __restri
                             const uint64_t ah = desc_of(a_lo + (uint32_t)(mt * 2 * (A_TILE >> 4)) + koff);
                             const uint64_t al = desc_of(a_lo + (uint32_t)(mt * 2 * (A_TILE >> 4) + (A_TILE >> 4)) + koff);
                             const uint32_t d = dbase + (uint32_t)(mt * 128);
+                            // the same three products in the same order whatever the tile width:
+                            // a token's result does not depend on who shares its chunk
                             mma_bf16(d, ah, bh, idesc, (c > 0 || ks > 0) ? 1u : 0u);
                             mma_bf16(d, ah, bl, idesc, 1u);
                             mma_bf16(d, al, bh, idesc, 1u);
                         }
                     }
                     mma_commit(&empty[st]);   // frees the stage once these MMAs have read it
+                    if (c == nchunks - 1) mma_commit(&accum[ab]);  // item done -> accumulators readable
                 }
-                if (ok) mma_commit(&accum[ab]);  // all MMAs of the item done -> accumulators readable
+                __syncwarp();
             }
         }
     } else {
@@ -463,7 +528,7 @@ grouped_q4k_umma_kernel(const SegDesc* __restrict__ seg, const int32_t* __restri
         const int quad = warp & 3;  // the TMEM lanes a warp may read: 32 * (warp % 4) ..
         const int r = quad * 32 + lane;
         for (int k = 0; k < my_items && ok; ++k) {
-            const Item it = decode_item(blockIdx.x + k * G, row_tiles, nseg, tile_prefix, seg);
+            const Item it = items.get(k);
             const int N = 16 << nsel_of(it.m_tile);
             const int ab = k & 1;
             ok = mb_wait(&accum[ab], (uint32_t)(k >> 1) & 1u, status, 3);
@@ -599,7 +664,7 @@ int launch_grouped_umma(dnb_ctx* c, cudaStream_t st, bool fused, const SegDesc* 
     (void)nt_max;
     const dim3 grid(c->sm_count);  // persistent: one CTA per SM loops over the tiles
     if (fused) {
-        const size_t smem = 2 * (2 * 2 * um::A_TILE + 2 * 128 * um::BK * 2) + 256 + (um::kMaxSeg + 1) * 4 + 1024;
+        const size_t smem = 2 * (2 * 2 * um::A_TILE + 2 * 128 * um::BK * 2) + 256 + (um::kMaxSeg + 1) * 4 + um::kLocalItems * sizeof(um::Item) + 1024;
         static bool set = false;
         if (!set) {
             DNB_CUDA(cudaFuncSetAttribute(um::grouped_q4k_umma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -609,7 +674,7 @@ int launch_grouped_umma(dnb_ctx* c, cudaStream_t st, bool fused, const SegDesc* 
         um::grouped_q4k_umma_kernel<2><<<grid, um::NTHREADS, smem, st>>>(seg, nseg_dev, n_in, n_out, rb, M, out_hi, out_lo,
                                                                         nullptr, c->status);
     } else {
-        const size_t smem = 3 * (2 * um::A_TILE + 2 * 128 * um::BK * 2) + 256 + (um::kMaxSeg + 1) * 4 + 1024;
+        const size_t smem = 3 * (2 * um::A_TILE + 2 * 128 * um::BK * 2) + 256 + (um::kMaxSeg + 1) * 4 + um::kLocalItems * sizeof(um::Item) + 1024;
         static bool set = false;
         if (!set) {
             DNB_CUDA(cudaFuncSetAttribute(um::grouped_q4k_umma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
