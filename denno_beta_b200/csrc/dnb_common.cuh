@@ -83,7 +83,8 @@ struct alignas(64) UmmaMaps {  // eight TMA tensor maps (4 box heights x hi/lo),
 struct Workspace {             // device buffers of the MoE pipeline, sized for nt_cap tokens
     int nt_cap = 0;
     float *xn = nullptr, *logits = nullptr, *wts = nullptr, *act = nullptr, *hrow = nullptr, *sact = nullptr,
-          *sh = nullptr, *hin = nullptr, *out = nullptr, *shcoef = nullptr;
+          *sh = nullptr, *hin = nullptr, *out = nullptr, *shcoef = nullptr,
+          *act_perm = nullptr;  // [kActRep][(k + 1) * ff]: the decode gate/up result in the down format's slot order
     int32_t *sels = nullptr, *row_token = nullptr, *pos = nullptr, *nseg = nullptr, *counts = nullptr, *one = nullptr;
     SegDesc *seg_gu = nullptr, *seg_dn = nullptr, *seg_sh_gu = nullptr, *seg_sh_dn = nullptr;
     uint16_t *xg_hi = nullptr, *xg_lo = nullptr, *act_hi = nullptr, *act_lo = nullptr;  // bf16 hi/lo packed rows
@@ -229,13 +230,26 @@ int launch_router_decode(dnb_ctx* c, cudaStream_t st, const float* h, const Mode
 // Decode down projection of all segments with the weighted sum fused in:
 // out[r] = (residual ? residual[r] : 0) + sum_s wts[s] * (W_s act_s)[r] (+ coef * shared).
 // DNB_DECLINED = shape not covered.
+// act_perm (optional): kActRep copies of the nseg activation vectors already in the
+// slot order of `type` (see PermOut); each CTA then takes one copy with a single bulk copy
+// instead of staging `act` with its threads.
 int launch_down_combine(dnb_ctx* c, cudaStream_t st, int type, const SegDesc* seg, int nseg, int k, int n_in, int n_out,
                         const float* act, const float* wts, const float* shcoef, bool has_shared,
-                        const float* residual, float* out);
+                        const float* residual, float* out, const float* act_perm = nullptr);
+// Hand-over of the decode gate/up result to the down kernel: besides the plain rows, the
+// values are written kActRep times in the slot order the consumer's format stages its
+// activations in.  Every CTA of the consumer needs all of them; with one copy they all
+// hit the same few L2 lines at once, with replicas CTA b reads copy b % kActRep.
+constexpr int kActRep = 16;
+struct PermOut {
+    float* base = nullptr;  // [kActRep][nseg * n_out]
+    int type = 0;           // format whose slot order to write
+};
 // Decode GEMV staged by the bulk-copy engine (gemv_bulk.cu); DNB_DECLINED = shape not covered.
 int launch_seg_gemv_m1(dnb_ctx* c, cudaStream_t st, int type, bool fused, bool xshared, const SegDesc* seg,
                        const int32_t* nseg_dev, int nseg_max, int n_in, int n_out, const float* x, int ldx,
-                       const int32_t* row_token, float* out, const SegDesc* single, const char* pname);
+                       const int32_t* row_token, float* out, const SegDesc* single, const char* pname,
+                       PermOut perm = PermOut());
 int launch_topk(dnb_ctx* c, cudaStream_t st, const float* logits, int nt, int ne, int k, int norm_topk, int32_t* sels,
                 float* wts, float* rowsum);
 // Builds, from sels[nt][k], the expert-major row space: counts, segment

@@ -42,6 +42,16 @@ __device__ __forceinline__ void slot_of(int i, int& u, int& s) {
     }
 }
 
+// Position of element i in the slot-ordered staging of a vector of `nunits` units, for a
+// format known only at run time.
+__device__ __forceinline__ int slot_index(int type, int i, int nunits) {
+    int u, s;
+    if (type == T_Q4_K || type == T_Q5_K) slot_of<T_Q4_K>(i, u, s);
+    else if (type == T_Q6_K) slot_of<T_Q6_K>(i, u, s);
+    else slot_of<T_IQ3_XXS>(i, u, s);
+    return (((s >> 2) * nunits + u) << 2) + (s & 3);
+}
+
 // kquant.rs:878-887 (get_scale_min_k4) on the 12 scale bytes at `q`.
 __device__ __forceinline__ void scale_min_k4(int j, const uint8_t* q, int& sc, int& m) {
     if (j < 4) {

@@ -70,12 +70,52 @@ constexpr int kWarps = 8;
 constexpr int kMaxRounds = 4;  // row rounds per warp in the decode GEMV
 
 // Stage n_in floats of x into slot order: xs4[k * nunits + u] (float4), see formats.cuh.
+// The loads of a batch of eight are all issued before the first store, so a thread waits
+// for memory once per batch, not once per element.
 template <int T>
 __device__ __forceinline__ void stage_x(float* xs, const float* xr, int n_in, int nunits, int tid, int nthr) {
-    for (int i = tid; i < n_in; i += nthr) {
-        int u, sl;
-        slot_of<T>(i, u, sl);
-        xs[((((sl >> 2)) * nunits + u) << 2) + (sl & 3)] = xr[i];
+    for (int i0 = tid; i0 < n_in; i0 += 8 * nthr) {
+        float v[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const int i = i0 + q * nthr;
+            v[q] = i < n_in ? xr[i] : 0.f;
+        }
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const int i = i0 + q * nthr;
+            if (i < n_in) {
+                int u, sl;
+                slot_of<T>(i, u, sl);
+                xs[((((sl >> 2)) * nunits + u) << 2) + (sl & 3)] = v[q];
+            }
+        }
+    }
+}
+
+// nseg activation vectors of n_in floats each, stored back to back at `act`, staged to
+// nseg slot-ordered vectors at `xs` in one flat pass.
+template <int T>
+__device__ __forceinline__ void stage_x_multi(float* xs, const float* act, int n_in, int nunits, int nseg, int tid,
+                                              int nthr) {
+    const int total = nseg * n_in;
+    for (int i0 = tid; i0 < total; i0 += 8 * nthr) {
+        float v[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const int i = i0 + q * nthr;
+            v[q] = i < total ? act[i] : 0.f;
+        }
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const int i = i0 + q * nthr;
+            if (i < total) {
+                const int sg = i / n_in, ii = i - sg * n_in;
+                int u, sl;
+                slot_of<T>(ii, u, sl);
+                xs[sg * n_in + ((((sl >> 2)) * nunits + u) << 2) + (sl & 3)] = v[q];
+            }
+        }
     }
 }
 
@@ -85,7 +125,8 @@ template <int T, bool FUSED, int LPR, bool XSHARED>
 __global__ void __launch_bounds__(kWarps * 32, 4)
 gemv_bulk_kernel(const SegDesc* __restrict__ seg, const int32_t* __restrict__ nseg_dev, int nseg_host, SegDesc single,
                  int n_in, int n_out, int rb, int rg, int gps, const float* __restrict__ x, int ldx,
-                 const int32_t* __restrict__ row_token, float* __restrict__ out, int* status) {
+                 const int32_t* __restrict__ row_token, float* __restrict__ out, int* status, float* out_perm,
+                 int perm_type) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
     constexpr int lut_bytes = (T == T_IQ3_XXS) ? (int)sizeof(IqLut) : 0;
@@ -174,8 +215,15 @@ gemv_bulk_kernel(const SegDesc* __restrict__ seg, const int32_t* __restrict__ ns
             }
             const int rr = it * GPW + gidx;
             if (rr < rg && sub == 0) {
-                const size_t o = (size_t)sd.row0 * n_out + (size_t)grp * rg + rr;
-                out[o] = FUSED ? silu_b(a) * bq : a;
+                const int j = grp * rg + rr;
+                const float v = FUSED ? silu_b(a) * bq : a;
+                out[(size_t)sd.row0 * n_out + j] = v;
+                if (out_perm) {  // the copies the next kernel's CTAs take whole, in its slot order
+                    const size_t rep = (size_t)nseg * n_out;
+                    float* o = out_perm + (size_t)sd.row0 * n_out + slot_index(perm_type, j, n_out >> 5);
+#pragma unroll
+                    for (int c = 0; c < kActRep; ++c) o[c * rep] = v;
+                }
             }
         }
     }
@@ -196,7 +244,8 @@ template <int T, int LPR>
 __global__ void __launch_bounds__(kDcWarps * 32)
 down_combine_kernel(const SegDesc* __restrict__ seg, int nseg, int k, int n_in, int n_out, int rb,
                     const float* __restrict__ act, const float* __restrict__ wts, const float* __restrict__ shcoef,
-                    int has_shared, const float* __restrict__ residual, float* __restrict__ out, int* status) {
+                    int has_shared, const float* __restrict__ residual, float* __restrict__ out, int* status,
+                    const float* __restrict__ act_perm) {
     constexpr int GPW = 32 / LPR;
     constexpr int R = kDcRows;
     constexpr int NT = kDcWarps * 32;
@@ -217,6 +266,7 @@ down_combine_kernel(const SegDesc* __restrict__ seg, int nseg, int k, int n_in, 
     }
     if (tid == 0) {
         mbar_init(bar, 1);
+        mbar_init(bar + 1, 1);
         mbar_fence_init();
         // The segment table was written two kernels back (the router); the kernel
         // in between waited for the router before it let this one start, so the
@@ -227,10 +277,21 @@ down_combine_kernel(const SegDesc* __restrict__ seg, int nseg, int k, int n_in, 
     }
     pdl_wait();               // act[] comes from the gate/up kernel
     pdl_launch_dependents();
-    for (int s = 0; s < nseg; ++s) stage_x<T>(xs + (size_t)s * n_in, act + (size_t)s * n_in, n_in, nunits, tid, NT);
+    bool x_ok = true;
+    if (act_perm) {
+        // the activations arrive ready-made: one of kActRep identical copies, one bulk copy
+        if (tid == 0) {
+            const uint32_t bytes = (uint32_t)(nseg * n_in * sizeof(float));
+            mbar_expect_tx(bar + 1, bytes);
+            bulk_g2s(xs, act_perm + (size_t)(blockIdx.x % kActRep) * nseg * n_in, bytes, bar + 1);
+        }
+    } else {
+        stage_x_multi<T>(xs, act, n_in, nunits, nseg, tid, NT);
+    }
     if (tid < nseg) ws[tid] = tid < k ? wts[tid] : (shcoef ? shcoef[0] : 1.0f);
     __syncthreads();
-    const bool ok = mbar_wait_bounded(bar, 0, status);
+    if (act_perm) x_ok = mbar_wait_bounded(bar + 1, 0, status);
+    const bool ok = mbar_wait_bounded(bar, 0, status) && x_ok;
     // (segment, row) pairs are dealt to the lane groups of all warps round-robin
     const int sub = lane % LPR;
     const int npairs = nseg * R;
@@ -269,7 +330,7 @@ down_combine_kernel(const SegDesc* __restrict__ seg, int nseg, int k, int n_in, 
 template <int T, int LPR>
 static int launch_dc(dnb_ctx* c, cudaStream_t st, const SegDesc* seg, int nseg, int k, int n_in, int n_out,
                      const float* act, const float* wts, const float* shcoef, bool has_shared, const float* residual,
-                     float* out) {
+                     float* out, const float* act_perm) {
     constexpr int R = kDcRows;
     const int rb = (int)row_bytes(T, n_in);
     if (n_out % R || (R * rb) % 16) return DNB_DECLINED;
@@ -284,22 +345,23 @@ static int launch_dc(dnb_ctx* c, cudaStream_t st, const SegDesc* seg, int nseg, 
     }
     ProfScope prof_(c, st, "gemv_down_combine");
     DNB_CUDA(launch_k(kern, dim3(n_out / R), dim3(kDcWarps * 32), smem, st, c->use_pdl, seg, nseg, k, n_in, n_out, rb, act,
-                      wts, shcoef, has_shared ? 1 : 0, residual, out, c->status));
+                      wts, shcoef, has_shared ? 1 : 0, residual, out, c->status, act_perm));
     c->launches++;
     return DNB_OK;
 }
 
 int launch_down_combine(dnb_ctx* c, cudaStream_t st, int type, const SegDesc* seg, int nseg, int k, int n_in, int n_out,
                         const float* act, const float* wts, const float* shcoef, bool has_shared,
-                        const float* residual, float* out) {
+                        const float* residual, float* out, const float* act_perm) {
     if (row_bytes(type, n_in) == 0 || n_in % 32 || nseg < 1 || nseg > 40) return DNB_DECLINED;
+    if ((nseg * n_in) % 4) act_perm = nullptr;  // the bulk copy moves multiples of 16 bytes
     int rc = upload_tables_b(c->device);
     if (rc != DNB_OK) return rc;
     const bool wide = (n_in / 32) >= 32;
 #define DNB_DC(TT)                                                                                                      \
     case TT:                                                                                                            \
-        return wide ? launch_dc<TT, 32>(c, st, seg, nseg, k, n_in, n_out, act, wts, shcoef, has_shared, residual, out)  \
-                    : launch_dc<TT, 16>(c, st, seg, nseg, k, n_in, n_out, act, wts, shcoef, has_shared, residual, out);
+        return wide ? launch_dc<TT, 32>(c, st, seg, nseg, k, n_in, n_out, act, wts, shcoef, has_shared, residual, out, act_perm)  \
+                    : launch_dc<TT, 16>(c, st, seg, nseg, k, n_in, n_out, act, wts, shcoef, has_shared, residual, out, act_perm);
     switch (type) {
         DNB_DC(T_Q4_K)
         DNB_DC(T_Q5_K)
@@ -317,14 +379,14 @@ static int gcd_i(int a, int b) { return b ? gcd_i(b, a % b) : a; }
 template <int T, bool FUSED, int LPR, bool XSHARED>
 static int launch_cfg(dnb_ctx* c, cudaStream_t st, const SegDesc* seg, const int32_t* nseg_dev, int nseg_max,
                       SegDesc single, int n_in, int n_out, const float* x, int ldx, const int32_t* row_token,
-                      float* out, const char* pname) {
+                      float* out, const char* pname, PermOut perm) {
     const int rb = (int)row_bytes(T, n_in);
     constexpr int GPW = 32 / LPR;
     const int gmin = 16 / gcd_i(rb, 16);            // rows whose bytes make a multiple of 16
     int step = gmin * GPW / gcd_i(gmin, GPW);       // lcm
     if (n_out % step) return DNB_DECLINED;          // caller falls back to the tiled kernel
     int rg = step;
-    const int target = 1600;                        // bytes per warp per matrix: short per-warp chains, many warps
+    const int target = 1500;                        // bytes per warp per matrix: short per-warp chains, many warps
     while (rg * 2 * rb <= target && n_out % (rg * 2) == 0 && rg * 2 <= kMaxRounds * GPW) rg *= 2;
     if (rg > kMaxRounds * GPW) return DNB_DECLINED;
     const int gps = n_out / rg;
@@ -342,7 +404,7 @@ static int launch_cfg(dnb_ctx* c, cudaStream_t st, const SegDesc* seg, const int
     const int grid = (int)((warps + kWarps - 1) / kWarps);
     ProfScope prof_(c, st, pname);
     DNB_CUDA(launch_k(kern, dim3(grid), dim3(kWarps * 32), smem, st, c->use_pdl, seg, nseg_dev, nseg_max, single, n_in, n_out,
-                      rb, rg, gps, x, ldx, row_token, out, c->status));
+                      rb, rg, gps, x, ldx, row_token, out, c->status, nseg_dev ? nullptr : perm.base, perm.type));
     c->launches++;
     return DNB_OK;
 }
@@ -350,10 +412,10 @@ static int launch_cfg(dnb_ctx* c, cudaStream_t st, const SegDesc* seg, const int
 template <int T>
 static int launch_t(dnb_ctx* c, cudaStream_t st, bool fused, bool xshared, const SegDesc* seg, const int32_t* nseg_dev,
                     int nseg_max, SegDesc single, int n_in, int n_out, const float* x, int ldx,
-                    const int32_t* row_token, float* out, const char* pname) {
+                    const int32_t* row_token, float* out, const char* pname, PermOut perm) {
     const bool wide = (n_in / 32) >= 32;
 #define DNB_B(F, L, X) \
-    return launch_cfg<T, F, L, X>(c, st, seg, nseg_dev, nseg_max, single, n_in, n_out, x, ldx, row_token, out, pname)
+    return launch_cfg<T, F, L, X>(c, st, seg, nseg_dev, nseg_max, single, n_in, n_out, x, ldx, row_token, out, pname, perm)
     if (fused) {
         if (wide) { if (xshared) DNB_B(true, 32, true); else DNB_B(true, 32, false); }
         else      { if (xshared) DNB_B(true, 16, true); else DNB_B(true, 16, false); }
@@ -370,19 +432,19 @@ static int launch_t(dnb_ctx* c, cudaStream_t st, bool fused, bool xshared, const
 // uses the tiled kernel of seg_matmul.cu).
 int launch_seg_gemv_m1(dnb_ctx* c, cudaStream_t st, int type, bool fused, bool xshared, const SegDesc* seg,
                        const int32_t* nseg_dev, int nseg_max, int n_in, int n_out, const float* x, int ldx,
-                       const int32_t* row_token, float* out, const SegDesc* single_p, const char* pname) {
+                       const int32_t* row_token, float* out, const SegDesc* single_p, const char* pname, PermOut perm) {
     const SegDesc single = single_p ? *single_p : SegDesc{nullptr, nullptr, 0u, 0u};
     if (!seg && !single_p) return DNB_ERR_ARG;
     if (row_bytes(type, n_in) == 0 || n_in % 32 || n_out <= 0 || nseg_max <= 0) return DNB_DECLINED;
     int rc = upload_tables_b(c->device);
     if (rc != DNB_OK) return rc;
     switch (type) {
-        case T_Q4_K: return launch_t<T_Q4_K>(c, st, fused, xshared, seg, nseg_dev, nseg_max, single, n_in, n_out, x, ldx, row_token, out, pname);
-        case T_Q5_K: return launch_t<T_Q5_K>(c, st, fused, xshared, seg, nseg_dev, nseg_max, single, n_in, n_out, x, ldx, row_token, out, pname);
-        case T_Q6_K: return launch_t<T_Q6_K>(c, st, fused, xshared, seg, nseg_dev, nseg_max, single, n_in, n_out, x, ldx, row_token, out, pname);
-        case T_IQ3_XXS: return launch_t<T_IQ3_XXS>(c, st, fused, xshared, seg, nseg_dev, nseg_max, single, n_in, n_out, x, ldx, row_token, out, pname);
-        case T_Q8_0: return launch_t<T_Q8_0>(c, st, fused, xshared, seg, nseg_dev, nseg_max, single, n_in, n_out, x, ldx, row_token, out, pname);
-        case T_Q5_1: return launch_t<T_Q5_1>(c, st, fused, xshared, seg, nseg_dev, nseg_max, single, n_in, n_out, x, ldx, row_token, out, pname);
+        case T_Q4_K: return launch_t<T_Q4_K>(c, st, fused, xshared, seg, nseg_dev, nseg_max, single, n_in, n_out, x, ldx, row_token, out, pname, perm);
+        case T_Q5_K: return launch_t<T_Q5_K>(c, st, fused, xshared, seg, nseg_dev, nseg_max, single, n_in, n_out, x, ldx, row_token, out, pname, perm);
+        case T_Q6_K: return launch_t<T_Q6_K>(c, st, fused, xshared, seg, nseg_dev, nseg_max, single, n_in, n_out, x, ldx, row_token, out, pname, perm);
+        case T_IQ3_XXS: return launch_t<T_IQ3_XXS>(c, st, fused, xshared, seg, nseg_dev, nseg_max, single, n_in, n_out, x, ldx, row_token, out, pname, perm);
+        case T_Q8_0: return launch_t<T_Q8_0>(c, st, fused, xshared, seg, nseg_dev, nseg_max, single, n_in, n_out, x, ldx, row_token, out, pname, perm);
+        case T_Q5_1: return launch_t<T_Q5_1>(c, st, fused, xshared, seg, nseg_dev, nseg_max, single, n_in, n_out, x, ldx, row_token, out, pname, perm);
         default: return DNB_DECLINED;
     }
 }

@@ -169,6 +169,7 @@ int launch_router_logits(dnb_ctx* c, cudaStream_t st, const float* x, int nt, in
 // The same function serves the per-token kernel and the tail of the fused decode
 // router, so a token gets the same routing bits on either path.
 struct TopkSmem {
+    uint32_t keys[1024];
     float red[128];
     float cand_v[4];
     int cand_i[4];
@@ -220,52 +221,59 @@ __device__ __forceinline__ void topk_block(const float* __restrict__ logit_row, 
     const float sum = sm.bcast;
     if (sum > 0.f) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) p[j] = p[j] / sum;
+        for (int j = 0; j < 8; ++j)
+            if (j * 128 + tid < ne) p[j] = p[j] / sum;  // (the -inf padding would take the division's slow path)
     }
     uint32_t used = 0;
     if (!nan_block) {
-        // Fast path (no NaN anywhere): values map to order-preserving integer keys, a
-        // warp finds its maximum and the lowest index holding it with two redux
-        // instructions, the four warps meet through double-buffered shared slots
-        // (one barrier per round), and only the thread that owned the winner rescans
-        // its entries.  Same rule: larger value first, ties to the lower index.
-        uint32_t key[8];
+        // Fast path (no NaN anywhere): values map to order-preserving integer keys, the
+        // warp finds the maximum and the lowest index holding it with two redux
+        // instructions, and only the lane that owned the winner rescans its entries.
+        // Same rule: larger value first, ties to the lower index.
+        // The keys go to shared memory and warp 0 selects alone: no block barrier inside
+        // the k rounds.
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             const uint32_t ub = __float_as_uint(p[j]);
-            key[j] = (j * 128 + tid < ne) ? ((ub & 0x80000000u) ? ~ub : (ub | 0x80000000u)) : 0u;
+            if (j * 128 + tid < ne) sm.keys[j * 128 + tid] = (ub & 0x80000000u) ? ~ub : (ub | 0x80000000u);
         }
-        uint32_t bk = 0u;
-        int bi = 0x7fffffff;
+        __syncthreads();
+        if (warp == 0) {
+            uint32_t key[32];  // entry 32 * m + lane
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
-            if (j * 128 + tid < ne && key[j] > bk) { bk = key[j]; bi = j * 128 + tid; }
-        for (int round = 0; round < k; ++round) {
-            const uint32_t wm = __reduce_max_sync(0xffffffffu, bk);
-            const uint32_t wi = __reduce_min_sync(0xffffffffu, (bk == wm && bi != 0x7fffffff) ? (uint32_t)bi : 0x7fffffffu);
-            uint32_t* slot = reinterpret_cast<uint32_t*>(sm.red) + (round & 1) * 8;
-            if (lane == 0) { slot[warp] = wm; slot[4 + warp] = wi; }
-            __syncthreads();
-            uint32_t gm = slot[0], gi = slot[4];
+            for (int m = 0; m < 32; ++m) key[m] = (32 * m + lane < ne) ? sm.keys[32 * m + lane] : 0u;
+            // a lane's best: maximum by a pairwise tree (depth 5, not a 32-step chain), then
+            // the lowest entry holding it
+            auto lane_best = [&](uint32_t& bk, int& bm) {
+                uint32_t t[16];
 #pragma unroll
-            for (int w = 1; w < 4; ++w) {
-                const uint32_t om = slot[w], oi = slot[4 + w];
-                if (om > gm || (om == gm && oi < gi)) { gm = om; gi = oi; }
-            }
-            const int win = (int)gi;
-            if ((win & 127) == tid) {
-                used |= 1u << (win >> 7);
-                float wv = 0.f;
+                for (int m = 0; m < 16; ++m) t[m] = max(key[2 * m], key[2 * m + 1]);
 #pragma unroll
-                for (int j = 0; j < 8; ++j)
-                    if (j == (win >> 7)) wv = p[j];
-                sm.sel[round] = win;
-                sm.pv[round] = wv;
-                bk = 0u;
-                bi = 0x7fffffff;
+                for (int w = 8; w > 0; w >>= 1)
 #pragma unroll
-                for (int j = 0; j < 8; ++j)
-                    if (j * 128 + tid < ne && !((used >> j) & 1u) && key[j] > bk) { bk = key[j]; bi = j * 128 + tid; }
+                    for (int m = 0; m < w; ++m) t[m] = max(t[m], t[m + w]);
+                bk = t[0];
+                uint32_t hit = 0u;
+#pragma unroll
+                for (int m = 0; m < 32; ++m) hit |= (key[m] == bk ? 1u : 0u) << m;
+                bm = bk ? __ffs((int)hit) - 1 : -1;
+            };
+            uint32_t bk;
+            int bm;
+            lane_best(bk, bm);
+            for (int round = 0; round < k; ++round) {
+                const uint32_t wm = __reduce_max_sync(0xffffffffu, bk);
+                const uint32_t wi = __reduce_min_sync(0xffffffffu, (bk == wm && bm >= 0) ? (uint32_t)(32 * bm + lane) : 0x7fffffffu);
+                if (lane == 0) {
+                    sm.sel[round] = (int)wi;
+                    sm.pv[round] = __uint_as_float((wm & 0x80000000u) ? (wm ^ 0x80000000u) : ~wm);
+                }
+                if ((int)(wi & 31u) == lane) {  // the owner drops the winner and rescans its entries
+#pragma unroll
+                    for (int m = 0; m < 32; ++m)
+                        if (m == (int)(wi >> 5)) key[m] = 0u;
+                    lane_best(bk, bm);
+                }
             }
         }
         __syncthreads();
@@ -417,11 +425,28 @@ router_decode_kernel(const float* __restrict__ h, const float* __restrict__ norm
 #pragma unroll
         for (int j = 0; j < NV; ++j) wv[j] = __ldg(wr + lane + 32 * j);
     }
+    float nw[NV];  // this thread's norm weights: layer constants as well
+    if (norm_w) {
+#pragma unroll
+        for (int j = 0; j < NV; ++j) nw[j] = __ldg(norm_w + tid + 128 * j);
+    }
     pdl_wait();
     pdl_launch_dependents();
     if (norm_w) {
-        const float inv = rms_inv_128(h, e, eps, red);
-        for (int i = tid; i < e; i += 128) xs[i] = __fmul_rn(__fmul_rn(h[i], inv), norm_w[i]);
+        // rms_inv_128's arithmetic with the row read once and kept in registers
+        float hv[NV];
+#pragma unroll
+        for (int j = 0; j < NV; ++j) hv[j] = h[tid + 128 * j];
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < NV; ++j) ss = fmaf(hv[j], hv[j], ss);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) red[warp] = ss;
+        __syncthreads();
+        const float inv = 1.0f / sqrtf(((red[0] + red[1]) + (red[2] + red[3])) / (float)e + eps);
+#pragma unroll
+        for (int j = 0; j < NV; ++j) xs[tid + 128 * j] = __fmul_rn(__fmul_rn(hv[j], inv), nw[j]);
     } else {
         for (int i = tid; i < e; i += 128) xs[i] = h[i];
     }
