@@ -121,8 +121,8 @@ __device__ __forceinline__ void stage_x_multi(float* xs, const float* act, int n
 
 // grid.x CTAs of 8 warps; warp index wi = blockIdx.x*8 + warp -> (segment wi / gps, row group wi % gps).
 // Dynamic shared memory: [8 mbarriers | pad to 128][IqLut][8 x item bytes (x2 fused)][x]
-template <int T, bool FUSED, int LPR, bool XSHARED>
-__global__ void __launch_bounds__(kWarps * 32, 4)
+template <int T, bool FUSED, int LPR, bool XSHARED, int KR /* row rounds per warp this instance can hold: 1 or kMaxRounds */>
+__global__ void __launch_bounds__(kWarps * 32, (KR == 1 && FUSED) ? 5 : 4)
 gemv_bulk_kernel(const SegDesc* __restrict__ seg, const int32_t* __restrict__ nseg_dev, int nseg_host, SegDesc single,
                  int n_in, int n_out, int rb, int rg, int gps, const float* __restrict__ x, int ldx,
                  const int32_t* __restrict__ row_token, float* __restrict__ out, int* status, float* out_perm,
@@ -188,15 +188,15 @@ gemv_bulk_kernel(const SegDesc* __restrict__ seg, const int32_t* __restrict__ ns
 
     constexpr int GPW = 32 / LPR;
     const int sub = lane % LPR, gidx = lane / LPR;
-    const int rounds = (rg + GPW - 1) / GPW;  // <= kMaxRounds (launcher)
-    float acc_a[kMaxRounds], acc_b[kMaxRounds];
+    const int rounds = (rg + GPW - 1) / GPW;  // <= KR (launcher)
+    float acc_a[KR], acc_b[KR];
 #pragma unroll
-    for (int it = 0; it < kMaxRounds; ++it) { acc_a[it] = 0.f; acc_b[it] = 0.f; }
+    for (int it = 0; it < KR; ++it) { acc_a[it] = 0.f; acc_b[it] = 0.f; }
     for (int u = sub; u < nunits; u += LPR) {
         XUnit<T> X;
         load_x_unit<T>(xs4, nunits, u, X);
 #pragma unroll
-        for (int it = 0; it < kMaxRounds; ++it) {
+        for (int it = 0; it < KR; ++it) {
             const int rr = it * GPW + gidx;
             if (it < rounds && rr < rg) {
                 acc_a[it] += unit_dot<T>(wa + rr * rb, u, lut, X);
@@ -205,7 +205,7 @@ gemv_bulk_kernel(const SegDesc* __restrict__ seg, const int32_t* __restrict__ ns
         }
     }
 #pragma unroll
-    for (int it = 0; it < kMaxRounds; ++it) {
+    for (int it = 0; it < KR; ++it) {
         if (it < rounds) {  // uniform across the warp
             float a = acc_a[it], bq = acc_b[it];
 #pragma unroll
@@ -394,11 +394,14 @@ static int launch_cfg(dnb_ctx* c, cudaStream_t st, const SegDesc* seg, const int
     const size_t smem = 128 + (T == T_IQ3_XXS ? sizeof(IqLut) : 0) + (size_t)kWarps * (FUSED ? 2 : 1) * item_bytes +
                         (size_t)(XSHARED ? 1 : kWarps) * n_in * sizeof(float);
     if (smem > 200 * 1024) return DNB_DECLINED;
-    auto kern = gemv_bulk_kernel<T, FUSED, LPR, XSHARED>;
-    static size_t smem_set = 0;
-    if (smem > smem_set) {
+    // one row round per warp (the decode shapes): a leaner instance; the fused gate/up form of it
+    // is built for five CTAs per SM so that the 704 CTAs of a 512-expert top-10 block are one wave
+    const bool one = (rg + GPW - 1) / GPW == 1;
+    auto kern = one ? gemv_bulk_kernel<T, FUSED, LPR, XSHARED, 1> : gemv_bulk_kernel<T, FUSED, LPR, XSHARED, kMaxRounds>;
+    static size_t smem_set[2] = {0, 0};
+    if (smem > smem_set[one ? 1 : 0]) {
         DNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        smem_set = smem;
+        smem_set[one ? 1 : 0] = smem;
     }
     const long warps = (long)nseg_max * gps;
     const int grid = (int)((warps + kWarps - 1) / kWarps);
