@@ -170,6 +170,8 @@ int launch_router_logits(dnb_ctx* c, cudaStream_t st, const float* x, int nt, in
 // router, so a token gets the same routing bits on either path.
 struct TopkSmem {
     uint32_t keys[1024];
+    uint32_t cand_k[32];
+    int cand_x[32];
     float red[128];
     float cand_v[4];
     int cand_i[4];
@@ -261,7 +263,54 @@ __device__ __forceinline__ void topk_block(const float* __restrict__ logit_row, 
             uint32_t bk;
             int bm;
             lane_best(bk, bm);
-            for (int round = 0; round < k; ++round) {
+            // Shortcut without rounds.  t = the k-th largest of the 32 lane maxima: at least k
+            // entries reach t, so every one of the top k does.  When no more than 32 entries
+            // reach t (the usual case: a dozen or two), each goes to one lane, which ranks it
+            // among the others by value and index; rank r < k is selection r.
+            bool done = false;
+            if (k <= 32) {
+                int above = 0;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) above += (__shfl_sync(0xffffffffu, bk, j) > bk) ? 1 : 0;
+                const uint32_t t = __reduce_min_sync(0xffffffffu, above < k ? bk : 0xffffffffu);
+                uint32_t surv = 0u;
+#pragma unroll
+                for (int m = 0; m < 32; ++m) surv |= ((key[m] >= t && key[m] != 0u) ? 1u : 0u) << m;
+                const int mine = __popc(surv);
+                int incl = mine;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int v = __shfl_up_sync(0xffffffffu, incl, o);
+                    if (lane >= o) incl += v;
+                }
+                const int total = __shfl_sync(0xffffffffu, incl, 31);
+                if (total <= 32 && total >= k) {
+                    int pos = incl - mine;
+                    while (surv) {
+                        const int m = __ffs((int)surv) - 1;
+                        surv &= surv - 1u;
+                        sm.cand_k[pos] = sm.keys[32 * m + lane];
+                        sm.cand_x[pos] = 32 * m + lane;
+                        ++pos;
+                    }
+                    __syncwarp();
+                    const uint32_t ck = lane < total ? sm.cand_k[lane] : 0u;
+                    const int cx = lane < total ? sm.cand_x[lane] : 0x7fffffff;
+                    int rank = 0;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const uint32_t ok = __shfl_sync(0xffffffffu, ck, j);
+                        const int ox = __shfl_sync(0xffffffffu, cx, j);
+                        rank += (ok > ck || (ok == ck && ox < cx)) ? 1 : 0;
+                    }
+                    if (lane < total && rank < k) {
+                        sm.sel[rank] = cx;
+                        sm.pv[rank] = __uint_as_float((ck & 0x80000000u) ? (ck ^ 0x80000000u) : ~ck);
+                    }
+                    done = true;
+                }
+            }
+            for (int round = 0; round < k && !done; ++round) {
                 const uint32_t wm = __reduce_max_sync(0xffffffffu, bk);
                 const uint32_t wi = __reduce_min_sync(0xffffffffu, (bk == wm && bm >= 0) ? (uint32_t)(32 * bm + lane) : 0x7fffffffu);
                 if (lane == 0) {
