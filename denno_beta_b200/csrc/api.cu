@@ -1,5 +1,6 @@
 // extern "C" entry points of libdnb200: context, resident tables and the
 // orchestration of one MoE block (see include/dnb200.h for the contract).
+#include <chrono>
 #include <stdarg.h>
 #include <stdio.h>
 #include <string.h>
@@ -159,6 +160,19 @@ static int run_graphed(dnb_ctx* c, const GraphKey& key, F enqueue) {
     DNB_CUDA(cudaGraphLaunch(it->second.exec, c->stream));
     c->launches += it->second.kernels;
     return DNB_OK;
+}
+
+// Wait for the stream at the end of a host-buffer call.  A decode-sized call lasts a few
+// tens of microseconds, less than it takes a blocked thread to be woken, so the host polls
+// the stream for up to two milliseconds before it falls back to the blocking wait.
+static cudaError_t wait_short(cudaStream_t st) {
+    const auto t0 = std::chrono::steady_clock::now();
+    for (int i = 0;; ++i) {
+        const cudaError_t e = cudaStreamQuery(st);
+        if (e != cudaErrorNotReady) return e;
+        if ((i & 63) == 63 && std::chrono::steady_clock::now() - t0 > std::chrono::milliseconds(2)) break;
+    }
+    return cudaStreamSynchronize(st);
 }
 
 static bool layer_ready(const dnb_ctx* c, int layer, bool need_router) {
@@ -610,7 +624,7 @@ int dnb_gemv(dnb_ctx* c, uint64_t uid, const float* x, float* out) {
     DNB_CUDA(cudaMemcpyAsync(c->gemv_x.p, x, (size_t)m.k * 4, cudaMemcpyHostToDevice, c->stream));
     if ((rc = gemv_dev(c, m.type, m.dev, m.k, m.n, (const float*)c->gemv_x.p, (float*)c->gemv_out.p, 1))) return rc;
     DNB_CUDA(cudaMemcpyAsync(out, c->gemv_out.p, (size_t)m.n * 4, cudaMemcpyDeviceToHost, c->stream));
-    DNB_CUDA(cudaStreamSynchronize(c->stream));
+    DNB_CUDA(wait_short(c->stream));
     return DNB_OK;
 }
 
@@ -783,7 +797,7 @@ int dnb_moe_block(dnb_ctx* c, int layer, const float* h, int nt, float* out, int
         return DNB_OK;
     });
     if (rc) return rc;
-    DNB_CUDA(cudaStreamSynchronize(c->stream));
+    DNB_CUDA(nt <= 64 ? wait_short(c->stream) : cudaStreamSynchronize(c->stream));
     memcpy(out, w.pinned_out, bytes);
     if (sels_out) memcpy(sels_out, w.pinned_sels, (size_t)nt * M.k * 4);
     if (wts_out) memcpy(wts_out, w.pinned_wts, (size_t)nt * M.k * 4);
@@ -823,7 +837,7 @@ int dnb_moe_experts(dnb_ctx* c, int layer, const float* x, int nt, const int32_t
             return rc;
     if ((rc = experts_dev(c, layer, w.hin, nt, w.sels, w.wts, w.out))) return rc;
     DNB_CUDA(cudaMemcpyAsync(w.pinned_out, w.out, bytes, cudaMemcpyDeviceToHost, c->stream));
-    DNB_CUDA(cudaStreamSynchronize(c->stream));
+    DNB_CUDA(nt <= 64 ? wait_short(c->stream) : cudaStreamSynchronize(c->stream));
     memcpy(out, w.pinned_out, bytes);
     return DNB_OK;
 }

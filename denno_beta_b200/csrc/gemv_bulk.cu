@@ -148,24 +148,30 @@ gemv_bulk_kernel(const SegDesc* __restrict__ seg, const int32_t* __restrict__ ns
         mbar_init(bar, 1);
         mbar_fence_init();
     }
-    // Everything above touches nothing another kernel writes.  The segment table,
-    // the token count and x come from the kernel before this one.
-    pdl_wait();
-    pdl_launch_dependents();
-    const int nseg = nseg_dev ? *nseg_dev : nseg_host;
+    // Everything above touches nothing another kernel writes.  A segment table, the token
+    // count and x come from the kernel before this one; a single matrix named by the launch
+    // itself does not, so its bytes are requested before the wait and stream in while the
+    // previous kernel is still running (back-to-back GEMVs then overlap their fetches).
+    const bool early = (seg == nullptr && nseg_dev == nullptr);
     const long wi = (long)blockIdx.x * kWarps + warp;
     const int s = (int)(wi / gps), grp = (int)(wi % gps);
-    bool active = s < nseg;
+    bool active = false;
     SegDesc sd = SegDesc{nullptr, nullptr, 0u, 0u};
-    if (active) sd = seg ? seg[s] : single;
-    active = active && sd.m > 0;
-    if (lane == 0) {
-        if (active) {
+    auto request = [&](int nseg_now) {
+        active = s < nseg_now;
+        if (active) sd = seg ? seg[s] : single;
+        active = active && sd.m > 0;
+        if (lane == 0 && active) {
             mbar_expect_tx(bar, (uint32_t)per_warp);
             bulk_g2s(wa, sd.wa + (size_t)grp * item_bytes, (uint32_t)item_bytes, bar);
             if constexpr (FUSED) bulk_g2s(wb, sd.wb + (size_t)grp * item_bytes, (uint32_t)item_bytes, bar);
         }
-    }
+    };
+    if (early) request(nseg_host);
+    pdl_wait();
+    pdl_launch_dependents();
+    const int nseg = nseg_dev ? *nseg_dev : nseg_host;
+    if (!early) request(nseg);
     __syncwarp();
 
     const int nunits = n_in >> 5;
