@@ -258,33 +258,36 @@ def run_ours(args, rank, world, local_rank):
 
 
 def extras(ctx, cu, oracle):
-    """Config 0 (single Q4_K GEMV 4096x4096, HBM GB/s) on rotating weight copies."""
+    """Config 0 (single Q4_K GEMV 4096x4096, HBM GB/s) on rotating weight copies, and the
+    same GEMV in the path's other block formats (IQ3_XXS, Q6_K, Q8_0)."""
     out = {}
     k = n = 4096
-    rb = 16 * 144
-    copies = 32  # 32 x 9.4 MB = 302 MB > L2
-    w = oracle.synth_blocks(Q4_K, SEED, 9000, n * 16)
-    dw = ctx.dev_alloc(copies * n * rb)
-    for i in range(copies):
-        ctx.upload(dw + i * n * rb, w)
     x = oracle.synth_normal(SEED, 9001, 1.0, k)
     dx = ctx.dev_alloc(k * 4)
     do = ctx.dev_alloc(n * 4)
     ctx.upload(dx, x)
-    for i in range(8):
-        ctx.gemv_dev(Q4_K, dw + (i % copies) * n * rb, k, n, dx, do, 1)
-    ctx.sync()
-    reps = 256
-    ctx.stall(10.0)  # the launches below queue up behind it and then run back to back
-    ctx.timer_start()
-    for i in range(reps):
-        ctx.gemv_dev(Q4_K, dw + (i % copies) * n * rb, k, n, dx, do, 1)
-    ms = ctx.timer_stop()
-    alg = n * rb + k * 4 + n * 4
-    out["config0_q4k_gemv_4096"] = {"us_per_gemv": ms / reps * 1e3, "hbm_gbs": alg / (ms / reps * 1e-3) / 1e9,
-                                    "bytes": alg, "launches": reps, "rotating_copies": copies,
-                                    "frac_of_measured_hbm": alg / (ms / reps * 1e-3) / 1e9 / peaks()[0]}
-    for p in (dw, dx, do):
+    for name, ty in (("q4k", Q4_K), ("iq3xxs", IQ3_XXS), ("q6k", 14), ("q80", 8)):
+        rb = oracle.row_bytes(ty, k)
+        copies = (320 * 1024 * 1024 + n * rb - 1) // (n * rb)  # > 126 MB of L2 several times over
+        w = oracle.synth_blocks(ty, SEED, 9000 + ty, n * (k // oracle.blck_size(ty)))
+        dw = ctx.dev_alloc(copies * n * rb)
+        for i in range(copies):
+            ctx.upload(dw + i * n * rb, w)
+        for i in range(8):
+            ctx.gemv_dev(ty, dw + (i % copies) * n * rb, k, n, dx, do, 1)
+        ctx.sync()
+        reps = 256
+        ctx.stall(10.0)  # the launches below queue up behind it and then run back to back
+        ctx.timer_start()
+        for i in range(reps):
+            ctx.gemv_dev(ty, dw + (i % copies) * n * rb, k, n, dx, do, 1)
+        ms = ctx.timer_stop()
+        alg = n * rb + k * 4 + n * 4
+        out["config0_%s_gemv_4096" % name] = {"us_per_gemv": ms / reps * 1e3, "hbm_gbs": alg / (ms / reps * 1e-3) / 1e9,
+                                              "bytes": alg, "launches": reps, "rotating_copies": copies,
+                                              "frac_of_measured_hbm": alg / (ms / reps * 1e-3) / 1e9 / peaks()[0]}
+        ctx.dev_free(dw)
+    for p in (dx, do):
         ctx.dev_free(p)
     return out
 
