@@ -29,7 +29,7 @@ static int dev_alloc(T** p, size_t n) {
 }
 
 static void free_ws(Workspace& w) {
-    void* dev[] = {w.act_perm, w.xn, w.logits, w.wts, w.act, w.hrow, w.sact, w.sh, w.hin, w.out, w.shcoef, w.sels, w.row_token,
+    void* dev[] = {w.xn_perm, w.act_perm, w.xn, w.logits, w.wts, w.act, w.hrow, w.sact, w.sh, w.hin, w.out, w.shcoef, w.sels, w.row_token,
                    w.pos, w.nseg, w.counts, w.one, w.seg_gu, w.seg_dn, w.seg_sh_gu, w.seg_sh_dn, w.xg_hi, w.xg_lo, w.act_hi, w.act_lo};
     for (void* p : dev)
         if (p) cudaFree(p);
@@ -62,6 +62,7 @@ static int ensure_ws(dnb_ctx* c, int nt) {
     if ((rc = dev_alloc(&w.sels, rows))) return rc;
     if ((rc = dev_alloc(&w.act, rows * M.ff))) return rc;
     if ((rc = dev_alloc(&w.act_perm, (size_t)kActRep * (M.k + 1) * M.ff))) return rc;
+    if ((rc = dev_alloc(&w.xn_perm, (size_t)kActRep * M.e))) return rc;
     if ((rc = dev_alloc(&w.hrow, rows * M.e))) return rc;
     if ((rc = dev_alloc(&w.sact, (size_t)cap * sff))) return rc;
     if ((rc = dev_alloc(&w.sh, (size_t)cap * M.e))) return rc;
@@ -245,7 +246,8 @@ static int block_dev_decode(dnb_ctx* c, int layer, const float* h, float* out, c
     if (rc) return rc;
     const int nseg = M.k + (fold ? 1 : 0);
     rc = launch_seg_gemv_m1(c, st, L.m[0].type, true, true, w.seg_gu, nullptr, nseg, M.e, M.ff, w.xn, M.e, nullptr, w.act,
-                            nullptr, "gemv_gate_up", PermOut{w.act_perm, L.m[2].type});
+                            nullptr, "gemv_gate_up",
+                            PermOut{w.act_perm, L.m[2].type, M.ne >= 4 * kActRep ? w.xn_perm : nullptr});
     const bool have_perm = rc == DNB_OK;  // the tiled fallback below writes plain rows only
     if (rc == DNB_DECLINED)
         rc = launch_seg_matmul(c, st, L.m[0].type, true, w.seg_gu, nullptr, nseg, M.e, M.ff, w.xn, M.e, w.row_token, w.act, 1);

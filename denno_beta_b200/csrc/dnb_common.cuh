@@ -84,7 +84,8 @@ struct Workspace {             // device buffers of the MoE pipeline, sized for 
     int nt_cap = 0;
     float *xn = nullptr, *logits = nullptr, *wts = nullptr, *act = nullptr, *hrow = nullptr, *sact = nullptr,
           *sh = nullptr, *hin = nullptr, *out = nullptr, *shcoef = nullptr,
-          *act_perm = nullptr;  // [kActRep][(k + 1) * ff]: the decode gate/up result in the down format's slot order
+          *act_perm = nullptr,  // [kActRep][(k + 1) * ff]: the decode gate/up result in the down format's slot order
+          *xn_perm = nullptr;   // [kActRep][e]: the decode router's normalised row in the gate format's slot order
     int32_t *sels = nullptr, *row_token = nullptr, *pos = nullptr, *nseg = nullptr, *counts = nullptr, *one = nullptr;
     SegDesc *seg_gu = nullptr, *seg_dn = nullptr, *seg_sh_gu = nullptr, *seg_sh_dn = nullptr;
     uint16_t *xg_hi = nullptr, *xg_lo = nullptr, *act_hi = nullptr, *act_lo = nullptr;  // bf16 hi/lo packed rows
@@ -244,6 +245,10 @@ constexpr int kActRep = 16;
 struct PermOut {
     float* base = nullptr;  // [kActRep][nseg * n_out]
     int type = 0;           // format whose slot order to write
+    // The same hand-over on the input side: kActRep copies of the (shared) activation row
+    // already in this launch's slot order, written by the router kernel; a CTA takes one
+    // with a bulk copy instead of staging x with its threads.
+    const float* x_perm = nullptr;  // [kActRep][n_in]
 };
 // Decode GEMV staged by the bulk-copy engine (gemv_bulk.cu); DNB_DECLINED = shape not covered.
 int launch_seg_gemv_m1(dnb_ctx* c, cudaStream_t st, int type, bool fused, bool xshared, const SegDesc* seg,

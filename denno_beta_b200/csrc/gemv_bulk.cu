@@ -126,7 +126,7 @@ __global__ void __launch_bounds__(kWarps * 32, (KR == 1 && FUSED) ? 5 : 4)
 gemv_bulk_kernel(const SegDesc* __restrict__ seg, const int32_t* __restrict__ nseg_dev, int nseg_host, SegDesc single,
                  int n_in, int n_out, int rb, int rg, int gps, const float* __restrict__ x, int ldx,
                  const int32_t* __restrict__ row_token, float* __restrict__ out, int* status, float* out_perm,
-                 int perm_type) {
+                 int perm_type, const float* __restrict__ x_perm) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
     constexpr int lut_bytes = (T == T_IQ3_XXS) ? (int)sizeof(IqLut) : 0;
@@ -146,6 +146,7 @@ gemv_bulk_kernel(const SegDesc* __restrict__ seg, const int32_t* __restrict__ ns
     }
     if (lane == 0) {
         mbar_init(bar, 1);
+        if (warp == 0) mbar_init(bars + kWarps, 1);  // the CTA's activation row, when it comes by bulk copy
         mbar_fence_init();
     }
     // Everything above touches nothing another kernel writes.  A segment table, the token
@@ -177,7 +178,14 @@ gemv_bulk_kernel(const SegDesc* __restrict__ seg, const int32_t* __restrict__ ns
     const int nunits = n_in >> 5;
     const float4* xs4;
     if constexpr (XSHARED) {
-        stage_x<T>(xbase, x, n_in, nunits, tid, kWarps * 32);
+        if (x_perm) {
+            if (tid == 0) {
+                mbar_expect_tx(bars + kWarps, (uint32_t)(n_in * sizeof(float)));
+                bulk_g2s(xbase, x_perm + (size_t)(blockIdx.x % kActRep) * n_in, (uint32_t)(n_in * sizeof(float)), bars + kWarps);
+            }
+        } else {
+            stage_x<T>(xbase, x, n_in, nunits, tid, kWarps * 32);
+        }
         xs4 = reinterpret_cast<const float4*>(xbase);
     } else {
         float* xw = xbase + (size_t)warp * n_in;
@@ -190,6 +198,7 @@ gemv_bulk_kernel(const SegDesc* __restrict__ seg, const int32_t* __restrict__ ns
     }
     __syncthreads();
     if (!active) return;
+    if (XSHARED && x_perm && !mbar_wait_bounded(bars + kWarps, 0, status)) return;
     if (!mbar_wait_bounded(bar, 0, status)) return;
 
     constexpr int GPW = 32 / LPR;
@@ -413,7 +422,8 @@ static int launch_cfg(dnb_ctx* c, cudaStream_t st, const SegDesc* seg, const int
     const int grid = (int)((warps + kWarps - 1) / kWarps);
     ProfScope prof_(c, st, pname);
     DNB_CUDA(launch_k(kern, dim3(grid), dim3(kWarps * 32), smem, st, c->use_pdl, seg, nseg_dev, nseg_max, single, n_in, n_out,
-                      rb, rg, gps, x, ldx, row_token, out, c->status, nseg_dev ? nullptr : perm.base, perm.type));
+                      rb, rg, gps, x, ldx, row_token, out, c->status, nseg_dev ? nullptr : perm.base, perm.type,
+                      (XSHARED && n_in % 4 == 0) ? perm.x_perm : nullptr));
     c->launches++;
     return DNB_OK;
 }

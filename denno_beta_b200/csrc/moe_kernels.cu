@@ -2,6 +2,7 @@
 // top-k + renorm, the expert-major routing tables, the weighted combine and the
 // shared-expert gate coefficient.
 #include "dnb_common.cuh"
+#include "formats.cuh"
 
 namespace dnb {
 
@@ -459,7 +460,7 @@ router_decode_kernel(const float* __restrict__ h, const float* __restrict__ norm
                      float* __restrict__ wts, const uint8_t* gate, const uint8_t* up, const uint8_t* down, size_t eb_g,
                      size_t eb_u, size_t eb_d, const uint8_t* sg, const uint8_t* su, const uint8_t* sdn,
                      SegDesc* seg_gu, SegDesc* seg_dn, int32_t* row_token, int32_t* pos, int32_t* nseg,
-                     unsigned int* ticket) {
+                     unsigned int* ticket, float* __restrict__ xn_perm, int gate_type) {
     extern __shared__ __align__(16) float xs[];  // [e]
     __shared__ float red[4];
     __shared__ int is_last;
@@ -502,6 +503,12 @@ router_decode_kernel(const float* __restrict__ h, const float* __restrict__ norm
     __syncthreads();
     if (blockIdx.x == 0 && xn)
         for (int i = tid; i < e; i += 128) xn[i] = xs[i];
+    // every CTA holds the normalised row: the first kActRep each publish one copy in the
+    // slot order of the gate/up format, for that kernel's CTAs to take with a bulk copy
+    if (xn_perm && (int)blockIdx.x < kActRep) {
+        float* o = xn_perm + (size_t)blockIdx.x * e;
+        for (int i = tid; i < e; i += 128) o[slot_index(gate_type, i, e >> 5)] = xs[i];
+    }
     if (row < ne) {
         const float4* x4 = reinterpret_cast<const float4*>(xs);
         float acc = 0.f;
@@ -546,6 +553,8 @@ router_decode_kernel(const float* __restrict__ h, const float* __restrict__ norm
     }
 }
 
+static inline bool gridDim_ok(int ne) { return (ne + 3) / 4 >= kActRep; }  // one router CTA per replica
+
 template <int NV>
 static int launch_router_decode_t(dnb_ctx* c, cudaStream_t st, const float* h, const Model& M, const Layer& L,
                                   Workspace& w, bool fold_shared, unsigned int* ticket) {
@@ -558,7 +567,7 @@ static int launch_router_decode_t(dnb_ctx* c, cudaStream_t st, const float* h, c
                       (const uint8_t*)(fold_shared ? L.m[3].dev : nullptr),
                       (const uint8_t*)(fold_shared ? L.m[4].dev : nullptr),
                       (const uint8_t*)(fold_shared ? L.m[5].dev : nullptr), w.seg_gu, w.seg_dn, w.row_token, w.pos,
-                      w.nseg, ticket));
+                      w.nseg, ticket, (gridDim_ok(M.ne) ? w.xn_perm : nullptr), L.m[0].type));
     c->launches++;
     return DNB_OK;
 }
