@@ -51,6 +51,9 @@ SIGNATURES = {
     "dnb_moe_route_dev": (_i, [_vp, _i, _vp, _i, _vp, _vp, _vp]),
     "dnb_expert_rows_dev": (_i, [_vp, _i, _vp, _vp, _i, _i, _vp]),
     "dnb_moe_combine_dev": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _i, _vp]),
+    "dnb_ep_init": (_i, [_vp, _i, _i, _i, _vp]),
+    "dnb_ep_connect": (_i, [_vp, _vp]),
+    "dnb_ep_block_dev": (_i, [_vp, _i, _vp, _i, _vp]),
     "dnb_moe_stack": (_i, [_vp, _vp, _i, _vp]),
     "dnb_moe_stack_dev": (_i, [_vp, _vp, _i]),
 }

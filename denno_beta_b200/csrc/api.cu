@@ -103,6 +103,8 @@ static int ensure_ws(dnb_ctx* c, int nt) {
     return DNB_OK;
 }
 
+int ensure_workspace(dnb_ctx* c, int nt) { return ensure_ws(c, nt); }
+
 static int grow(Scratch& s, size_t bytes) {
     if (bytes <= s.cap) return DNB_OK;
     if (s.p) cudaFree(s.p);
@@ -395,6 +397,7 @@ void dnb_shutdown(dnb_ctx* c) {
     cudaSetDevice(c->device);
     cudaDeviceSynchronize();
     drop_graphs(c);
+    ep_release(c);
     for (auto& kv : c->matrices) cudaFree(kv.second.dev);
     for (auto& L : c->model.layers) free_layer(L);
     free_ws(c->ws);

@@ -148,11 +148,14 @@ struct dnb_ctx {
     bool decode_fast = true;            // one-token calls take the bulk-copy GEMV + fused router path
     bool use_pdl = true;                // programmatic dependent launch between the decode kernels
     bool use_umma = true;               // prefill chunks of Q4_K layers take the tcgen05 grouped GEMM
+    void* ep = nullptr;                 // dnb::EpState of the peer-memory expert-parallel path (ep_p2p.cu)
 };
 
 namespace dnb {
 
 void set_error(const char* fmt, ...);
+void ep_release(dnb_ctx* c);  // frees the peer-memory expert-parallel state, if any (ep_p2p.cu)
+int ensure_workspace(dnb_ctx* c, int nt);  // device buffers of the MoE pipeline for nt tokens (api.cu)
 
 struct ProfScope {
     dnb_ctx* c; cudaStream_t st; cudaEvent_t b = nullptr;
@@ -269,7 +272,7 @@ int launch_gather_split(dnb_ctx* c, cudaStream_t st, const float* x, int ldx, co
                         uint16_t* hi, uint16_t* lo);
 int launch_grouped_umma(dnb_ctx* c, cudaStream_t st, bool fused, const SegDesc* seg, const int32_t* nseg_dev,
                         int nseg_max, int n_in, int n_out, const UmmaMaps* maps, int nt_max, uint16_t* out_hi,
-                        uint16_t* out_lo, float* out_f32);
+                        uint16_t* out_lo, float* out_f32, float* const* row_dst = nullptr);
 int launch_combine(dnb_ctx* c, cudaStream_t st, const float* hrow, const int32_t* pos, const float* wts, int nt,
                    int k, int e, const float* sh, const float* shcoef, float* out);
 int launch_shared_coef(dnb_ctx* c, cudaStream_t st, const float* x, const float* row, int nt, int e, float* coef);

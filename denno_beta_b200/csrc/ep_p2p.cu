@@ -1,0 +1,431 @@
+// Expert-parallel prefill block over peer memory (one process per GPU, one node).
+//
+// The reference is single-GPU.  With G GPUs each rank keeps n_local = ne / G routed
+// experts of every layer, owns its own tokens and runs, per layer,
+//
+//   route (local)                                  existing kernels
+//   plan      counts per expert, row order         ep_plan_kernel      -> peers' cnt + flag
+//   dispatch  x rows -> bf16 hi/lo, stored straight into the OWNER rank's operand buffers
+//             (the B operand the tcgen05 kernel reads by TMA from its own memory)
+//                                                  ep_dispatch_kernel  -> peers' data flag
+//   build     wait for every source's counts and rows (bounded), segment table per
+//             (source, expert), destination pointer of every received row
+//                                                  ep_build_kernel
+//   gate/up   grouped tcgen05 GEMM + SwiGLU        grouped_q4k_umma_kernel<2>
+//   down      grouped tcgen05 GEMM whose epilogue stores each row into the (token, slot)
+//             row of the rank that owns the token  grouped_q4k_umma_kernel<1>, row_dst
+//   signal / wait   release flags to the sources, wait for every owner's flag (bounded)
+//   combine   ascending slot order, as on one GPU  combine_kernel
+//
+// Nothing goes through the host between these launches and no library collective is
+// involved: rows cross NVLink as plain stores of this library's kernels into memory the
+// peers exported with cudaIpcGetMemHandle.  Every rank has one arena (EpArena header,
+// then the row buffers); rank s writes only region s of a peer's buffers and slot s of
+// its flag arrays, so no two ranks ever write the same word.  Flags carry the sequence
+// number of the call and only grow, so they are never reset.  A source's region holds up
+// to `cap` rows (all of its rows may go to one peer), sorted by (expert, token).
+//
+// Every wait polls a flag in the rank's own memory with a limit; when the limit runs out
+// the kernel records a status and returns, the following kernels run on whatever is
+// there and the host reports the status.  No load through TMA ever touches peer memory.
+#include <cuda_bf16.h>
+
+#include "dnb_common.cuh"
+
+namespace dnb {
+
+constexpr int kEpMaxWorld = 16;
+constexpr int kEpMaxLocal = 512;
+
+struct EpArena {                       // head of every rank's exported allocation
+    uint32_t cnt_flag[kEpMaxWorld];    // [s] = seq once source s has written cnt[s][*]
+    uint32_t data_flag[kEpMaxWorld];   // [s] = seq once source s has stored all its rows here
+    uint32_t ret_flag[kEpMaxWorld];    // [d] = seq once owner d has stored all results for my tokens
+    int32_t cnt[kEpMaxWorld][kEpMaxLocal];  // cnt[s][e]: rows of source s for my local expert e
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+// Poll until *p >= seq; gives up after about a quarter of a second.
+__device__ __forceinline__ bool wait_flag(const uint32_t* p, uint32_t seq) {
+    for (int i = 0; i < (1 << 21); ++i) {
+        if ((int32_t)(ld_acquire_sys(p) - seq) >= 0) return true;
+        __nanosleep(100);
+    }
+    return false;
+}
+
+// bf16 hi/lo split of a pair (hi rounded to nearest, lo = the exact remainder truncated):
+// the same arithmetic as the single-GPU gather pass, so the operands are the same bits.
+__device__ __forceinline__ void ep_split2(float a, float b, uint32_t& hi_pair, uint32_t& lo_pair) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    hi_pair = *reinterpret_cast<const uint32_t*>(&h);
+    const float al = a - __uint_as_float(hi_pair << 16), bl = b - __uint_as_float(hi_pair & 0xFFFF0000u);
+    lo_pair = __byte_perm(__float_as_uint(al), __float_as_uint(bl), 0x7632);
+}
+
+struct EpPeers {                 // kernel parameter: every rank's arena as seen from this GPU
+    EpArena* arena[kEpMaxWorld];
+    int32_t* recv_slot[kEpMaxWorld];
+    uint16_t* xg_hi[kEpMaxWorld];
+    uint16_t* xg_lo[kEpMaxWorld];
+    float* h_slots[kEpMaxWorld];
+};
+
+// One CTA.  sels[nt][k] (global expert ids, ascending per token) -> send_row[i], the index
+// of row i = t*k+slot inside this rank's region at its destination: rows of a destination
+// sorted by expert, tokens ascending inside an expert.  The per-expert counts go to the
+// destinations, then the flag.
+__global__ void __launch_bounds__(1024)
+ep_plan_kernel(const int32_t* __restrict__ sels, int nt, int k, int ne, int n_local, int world, int me, uint32_t seq,
+               EpPeers peers, int32_t* __restrict__ send_row) {
+    extern __shared__ uint32_t sm[];
+    const int words = (nt + 31) >> 5;
+    uint32_t* bitmap = sm;                         // [ne][words]: token t selects expert e
+    int* counts = (int*)(sm + (size_t)ne * words); // [ne]
+    int* first = counts + ne;                      // [ne]: offset of expert e inside its destination region
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = blockDim.x >> 5;
+    for (int i = tid; i < ne * words; i += blockDim.x) bitmap[i] = 0;
+    __syncthreads();
+    for (int i = tid; i < nt * k; i += blockDim.x) {
+        const int e = sels[i];
+        if (e >= 0 && e < ne) atomicOr(&bitmap[(size_t)e * words + ((i / k) >> 5)], 1u << ((i / k) & 31));
+    }
+    __syncthreads();
+    for (int e = warp; e < ne; e += nwarp) {
+        int c = 0;
+        for (int w = lane; w < words; w += 32) c += __popc(bitmap[(size_t)e * words + w]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+        if (lane == 0) counts[e] = c;
+    }
+    __syncthreads();
+    if (tid < world) {  // exclusive scan of the counts inside each destination's expert range
+        int run = 0;
+        for (int e = tid * n_local; e < (tid + 1) * n_local; ++e) { first[e] = run; run += counts[e]; }
+    }
+    __syncthreads();
+    for (int i = tid; i < nt * k; i += blockDim.x) {
+        const int e = sels[i], t = i / k;
+        int r = -1;
+        if (e >= 0 && e < ne) {
+            const uint32_t* bm = bitmap + (size_t)e * words;
+            int before = __popc(bm[t >> 5] & ((1u << (t & 31)) - 1u));
+            for (int w = 0; w < (t >> 5); ++w) before += __popc(bm[w]);
+            r = first[e] + before;
+        }
+        send_row[i] = r;
+    }
+    for (int i = tid; i < ne; i += blockDim.x) peers.arena[i / n_local]->cnt[me][i % n_local] = counts[i];
+    __threadfence_system();
+    __syncthreads();
+    if (tid < world) st_release_sys(&peers.arena[tid]->cnt_flag[me], seq);
+}
+
+// One CTA per row i = t*k+slot: split x[t] to bf16 hi/lo and store it as row me*cap + j of
+// the owner's operand buffers; the last CTA to finish raises the data flag at every peer.
+__global__ void __launch_bounds__(256)
+ep_dispatch_kernel(const float* __restrict__ x, const int32_t* __restrict__ sels, const int32_t* __restrict__ send_row,
+                   int k, int e, int n_local, int world, int me, int cap, uint32_t seq, EpPeers peers,
+                   unsigned int* ticket, int* status) {
+    const int i = blockIdx.x, tid = threadIdx.x;
+    const int ex = sels[i], j = send_row[i];
+    if (ex >= 0 && j >= 0) {
+        if (j >= cap) {
+            if (tid == 0) atomicExch(status, 20);
+        } else {
+            const int d = ex / n_local;
+            const size_t r = (size_t)me * cap + j;
+            const float* xr = x + (size_t)(i / k) * e;
+            uint16_t* hi = peers.xg_hi[d] + r * e;
+            uint16_t* lo = peers.xg_lo[d] + r * e;
+            for (int c = tid * 4; c < e; c += 1024) {
+                const float4 v = *reinterpret_cast<const float4*>(xr + c);
+                uint32_t h0, l0, h1, l1;
+                ep_split2(v.x, v.y, h0, l0);
+                ep_split2(v.z, v.w, h1, l1);
+                *reinterpret_cast<uint2*>(hi + c) = make_uint2(h0, h1);
+                *reinterpret_cast<uint2*>(lo + c) = make_uint2(l0, l1);
+            }
+            if (tid == 0) peers.recv_slot[d][r] = i;
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    __shared__ int last;
+    if (tid == 0) {
+        const unsigned int t = atomicAdd(ticket, 1u);
+        last = (t == gridDim.x - 1) ? 1 : 0;
+        if (last) *ticket = 0u;
+    }
+    __syncthreads();
+    if (last && tid < world) st_release_sys(&peers.arena[tid]->data_flag[me], seq);
+}
+
+// One CTA.  Waits for every source's counts and rows, then builds the segment tables of
+// the two grouped GEMMs -- one segment per (source, local expert) with rows, in that
+// order -- and the destination pointer of every received row.
+__global__ void __launch_bounds__(1024)
+ep_build_kernel(EpArena* mine, const int32_t* __restrict__ recv_slot, int world, int n_local, int cap, int e,
+                uint32_t seq, EpPeers peers, const uint8_t* gate, const uint8_t* up, const uint8_t* down, size_t eb_g,
+                size_t eb_u, size_t eb_d, SegDesc* seg_gu, SegDesc* seg_dn, int32_t* nseg, float** row_dst, int* status) {
+    __shared__ int ok_all;
+    __shared__ int seg_base[kEpMaxWorld + 1];
+    __shared__ int rows_of[kEpMaxWorld];
+    const int tid = threadIdx.x;
+    if (tid == 0) ok_all = 1;
+    __syncthreads();
+    if (tid < 2 * world) {
+        const uint32_t* f = tid < world ? &mine->cnt_flag[tid] : &mine->data_flag[tid - world];
+        if (!wait_flag(f, seq)) { atomicExch(status, 21); ok_all = 0; }
+    }
+    __syncthreads();
+    if (!ok_all) {  // nothing to compute: publish an empty table
+        if (tid == 0) *nseg = 0;
+        return;
+    }
+    if (tid < world) {
+        int n = 0, rows = 0;
+        for (int x = 0; x < n_local; ++x) { const int c = mine->cnt[tid][x]; n += c > 0 ? 1 : 0; rows += c; }
+        seg_base[tid + 1] = n;
+        rows_of[tid] = rows;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        seg_base[0] = 0;
+        for (int s = 0; s < world; ++s) seg_base[s + 1] += seg_base[s];
+        *nseg = seg_base[world];
+    }
+    __syncthreads();
+    if (tid < world) {
+        int idx = seg_base[tid], row = tid * cap;
+        for (int x = 0; x < n_local; ++x) {
+            const int c = mine->cnt[tid][x];
+            if (c > 0) {
+                seg_gu[idx] = SegDesc{gate + (size_t)x * eb_g, up + (size_t)x * eb_u, (uint32_t)c, (uint32_t)row};
+                seg_dn[idx] = SegDesc{down + (size_t)x * eb_d, nullptr, (uint32_t)c, (uint32_t)row};
+                ++idx;
+                row += c;
+            }
+        }
+    }
+    for (int s = 0; s < world; ++s)
+        for (int j = tid; j < rows_of[s]; j += blockDim.x) {
+            const size_t r = (size_t)s * cap + j;
+            row_dst[r] = peers.h_slots[s] + (size_t)recv_slot[r] * e;
+        }
+}
+
+// After the down GEMM: everything this rank stored into the owners' result rows is made
+// visible, then the flag goes up at every owner.
+__global__ void ep_signal_kernel(int world, int me, uint32_t seq, EpPeers peers) {
+    __threadfence_system();
+    if ((int)threadIdx.x < world) st_release_sys(&peers.arena[threadIdx.x]->ret_flag[me], seq);
+}
+
+__global__ void ep_wait_ret_kernel(EpArena* mine, int world, uint32_t seq, int* status) {
+    if ((int)threadIdx.x < world && !wait_flag(&mine->ret_flag[threadIdx.x], seq)) atomicExch(status, 22);
+}
+
+}  // namespace dnb
+
+// ---- host side ---------------------------------------------------------------------------
+#include "dnb200.h"
+
+namespace dnb {
+
+struct EpState {
+    int rank = 0, world = 1, max_tokens = 0, cap = 0, rows_total = 0, n_local = 0;
+    uint32_t seq = 0;
+    bool connected = false;
+    uint8_t* arena = nullptr;      // this rank's exported allocation
+    size_t arena_bytes = 0;
+    size_t off_slot = 0, off_hi = 0, off_lo = 0, off_h = 0;  // layout, identical on every rank
+    void* peer_base[kEpMaxWorld] = {nullptr};                // every rank's arena in this process's address space
+    EpPeers peers;
+    // local-only buffers
+    int32_t* send_row = nullptr;
+    float** row_dst = nullptr;
+    uint16_t *act_hi = nullptr, *act_lo = nullptr;
+    SegDesc *seg_gu = nullptr, *seg_dn = nullptr;
+    int32_t* nseg = nullptr;
+    unsigned int* ticket = nullptr;
+    UmmaMaps maps_x, maps_act;
+};
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+void ep_release(dnb_ctx* c) {
+    EpState* s = static_cast<EpState*>(c->ep);
+    if (!s) return;
+    for (int r = 0; r < s->world; ++r)
+        if (r != s->rank && s->peer_base[r]) cudaIpcCloseMemHandle(s->peer_base[r]);
+    void* loc[] = {s->arena, s->send_row, s->row_dst, s->act_hi, s->act_lo, s->seg_gu, s->seg_dn, s->nseg, s->ticket};
+    for (void* p : loc)
+        if (p) cudaFree(p);
+    delete s;
+    c->ep = nullptr;
+}
+
+}  // namespace dnb
+
+using namespace dnb;
+
+extern "C" int dnb_ep_init(dnb_ctx* c, int rank, int world, int max_tokens, void* handle_out) {
+    if (!c || !handle_out || world < 1 || world > kEpMaxWorld || rank < 0 || rank >= world || max_tokens < 1)
+        return DNB_ERR_ARG;
+    const Model& M = c->model;
+    if (M.n_layer < 1 || M.ne % world || M.shard_count != M.ne / world || M.shard_first != rank * (M.ne / world)) {
+        set_error("ep_init: configure the model and call dnb_moe_set_expert_shard(rank * ne / world, ne / world) first");
+        return DNB_DECLINED;
+    }
+    if (M.ne / world > kEpMaxLocal || M.e % 256 || M.ff % 256 || M.k > 32) {
+        set_error("ep_init: shape outside the peer-memory path (e, ff multiples of 256; at most %d local experts)", kEpMaxLocal);
+        return DNB_DECLINED;
+    }
+    DNB_CUDA(cudaSetDevice(c->device));
+    ep_release(c);
+    EpState* s = new EpState();
+    c->ep = s;
+    s->rank = rank; s->world = world; s->max_tokens = max_tokens; s->n_local = M.ne / world;
+    s->cap = max_tokens * M.k;                 // all of a source's rows may go to one owner
+    s->rows_total = world * s->cap;
+    const size_t rows_pad = (size_t)s->rows_total + 128;  // a tile that starts near the end stays inside
+    s->off_slot = align_up(sizeof(EpArena), 256);
+    s->off_hi = align_up(s->off_slot + (size_t)s->rows_total * 4, 256);
+    s->off_lo = align_up(s->off_hi + rows_pad * M.e * 2, 256);
+    s->off_h = align_up(s->off_lo + rows_pad * M.e * 2, 256);
+    s->arena_bytes = align_up(s->off_h + (size_t)s->cap * M.e * 4, 256);
+    DNB_CUDA(cudaMalloc((void**)&s->arena, s->arena_bytes));
+    DNB_CUDA(cudaMemset(s->arena, 0, s->arena_bytes));
+    DNB_CUDA(cudaMalloc((void**)&s->send_row, (size_t)s->cap * 4));
+    DNB_CUDA(cudaMalloc((void**)&s->row_dst, (size_t)s->rows_total * sizeof(float*)));
+    DNB_CUDA(cudaMalloc((void**)&s->act_hi, rows_pad * M.ff * 2));
+    DNB_CUDA(cudaMalloc((void**)&s->act_lo, rows_pad * M.ff * 2));
+    DNB_CUDA(cudaMemset(s->act_hi, 0, rows_pad * M.ff * 2));
+    DNB_CUDA(cudaMemset(s->act_lo, 0, rows_pad * M.ff * 2));
+    DNB_CUDA(cudaMalloc((void**)&s->seg_gu, ((size_t)world * s->n_local + 1) * sizeof(SegDesc)));
+    DNB_CUDA(cudaMalloc((void**)&s->seg_dn, ((size_t)world * s->n_local + 1) * sizeof(SegDesc)));
+    DNB_CUDA(cudaMalloc((void**)&s->nseg, 4));
+    DNB_CUDA(cudaMalloc((void**)&s->ticket, 4));
+    DNB_CUDA(cudaMemset(s->ticket, 0, 4));
+    if (umma_make_maps(s->arena + s->off_hi, s->arena + s->off_lo, rows_pad, (uint64_t)M.e, &s->maps_x) != DNB_OK ||
+        umma_make_maps(s->act_hi, s->act_lo, rows_pad, (uint64_t)M.ff, &s->maps_act) != DNB_OK) {
+        set_error("ep_init: tensor maps of the operand buffers could not be made");
+        return DNB_DECLINED;
+    }
+    DNB_CUDA(cudaDeviceSynchronize());
+    cudaIpcMemHandle_t h;
+    DNB_CUDA(cudaIpcGetMemHandle(&h, s->arena));
+    static_assert(sizeof(h) == 64, "cudaIpcMemHandle_t is 64 bytes");
+    memcpy(handle_out, &h, sizeof(h));
+    return DNB_OK;
+}
+
+extern "C" int dnb_ep_connect(dnb_ctx* c, const void* handles) {
+    if (!c || !c->ep || !handles) return DNB_ERR_ARG;
+    EpState* s = static_cast<EpState*>(c->ep);
+    DNB_CUDA(cudaSetDevice(c->device));
+    for (int r = 0; r < s->world; ++r) {
+        if (r == s->rank) {
+            s->peer_base[r] = s->arena;
+        } else {
+            cudaIpcMemHandle_t h;
+            memcpy(&h, (const uint8_t*)handles + (size_t)r * 64, 64);
+            DNB_CUDA(cudaIpcOpenMemHandle(&s->peer_base[r], h, cudaIpcMemLazyEnablePeerAccess));
+        }
+        uint8_t* b = (uint8_t*)s->peer_base[r];
+        s->peers.arena[r] = (EpArena*)b;
+        s->peers.recv_slot[r] = (int32_t*)(b + s->off_slot);
+        s->peers.xg_hi[r] = (uint16_t*)(b + s->off_hi);
+        s->peers.xg_lo[r] = (uint16_t*)(b + s->off_lo);
+        s->peers.h_slots[r] = (float*)(b + s->off_h);
+    }
+    s->connected = true;
+    return DNB_OK;
+}
+
+extern "C" int dnb_ep_block_dev(dnb_ctx* c, int layer, const float* h_dev, int nt, float* out_dev) {
+    if (!c || !c->ep || !h_dev || !out_dev || nt < 1) return DNB_ERR_ARG;
+    EpState* s = static_cast<EpState*>(c->ep);
+    const Model& M = c->model;
+    if (!s->connected || nt > s->max_tokens || layer < 0 || layer >= M.n_layer) {
+        set_error("ep_block: not connected, layer out of range, or %d tokens exceed the %d the arena was sized for", nt, s->max_tokens);
+        return DNB_ERR_ARG;
+    }
+    const Layer& L = M.layers[layer];
+    for (int i = 0; i < 3; ++i)
+        if (!L.m[i].dev || L.m[i].type != T_Q4_K) {
+            set_error("ep_block: the peer-memory path runs Q4_K expert layers (tcgen05 grouped GEMM)");
+            return DNB_DECLINED;
+        }
+    DNB_CUDA(cudaSetDevice(c->device));
+    int rc;
+    // 1. route the rank's own tokens
+    if ((rc = ensure_workspace(c, nt))) return rc;
+    Workspace& w = c->ws;
+    if ((rc = dnb_moe_route_dev(c, layer, h_dev, nt, w.xn, w.sels, w.wts))) return rc;
+    cudaStream_t st = c->stream;
+    const uint32_t seq = ++s->seq;
+    const int words = (nt + 31) >> 5;
+    const size_t plan_smem = ((size_t)M.ne * words + 2 * (size_t)M.ne) * 4;
+    static size_t plan_set = 0;
+    if (plan_smem > 200 * 1024) return DNB_DECLINED;
+    if (plan_smem > plan_set) {
+        DNB_CUDA(cudaFuncSetAttribute(ep_plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan_smem));
+        plan_set = plan_smem;
+    }
+    {
+        ProfScope p_(c, st, "ep_plan");
+        ep_plan_kernel<<<1, 1024, plan_smem, st>>>(w.sels, nt, M.k, M.ne, s->n_local, s->world, s->rank, seq, s->peers, s->send_row);
+    }
+    {
+        ProfScope p_(c, st, "ep_dispatch");
+        ep_dispatch_kernel<<<nt * M.k, 256, 0, st>>>(w.xn, w.sels, s->send_row, M.k, M.e, s->n_local, s->world, s->rank, s->cap,
+                                                    seq, s->peers, s->ticket, c->status);
+    }
+    c->launches += 2;
+    DNB_CUDA(cudaGetLastError());
+    // 2. the shared expert of the own tokens while the peers' rows arrive
+    const bool shared = L.has_shared();
+    if (shared)
+        if ((rc = dnb_expert_rows_dev(c, layer, w.xn, nullptr, nt, 1, w.sh))) return rc;
+    // 3. the rows this rank owns: tables, the two grouped GEMMs, results stored at the token owners
+    {
+        ProfScope p_(c, st, "ep_build");
+        ep_build_kernel<<<1, 1024, 0, st>>>((EpArena*)s->arena, (const int32_t*)(s->arena + s->off_slot), s->world, s->n_local,
+                                            s->cap, M.e, seq, s->peers, (const uint8_t*)L.m[0].dev, (const uint8_t*)L.m[1].dev,
+                                            (const uint8_t*)L.m[2].dev, L.m[0].expert_bytes, L.m[1].expert_bytes,
+                                            L.m[2].expert_bytes, s->seg_gu, s->seg_dn, s->nseg, s->row_dst, c->status);
+    }
+    c->launches++;
+    DNB_CUDA(cudaGetLastError());
+    const int nseg_max = s->world * s->n_local;
+    if ((rc = launch_grouped_umma(c, st, true, s->seg_gu, s->nseg, nseg_max, M.e, M.ff, &s->maps_x, s->rows_total, s->act_hi,
+                                  s->act_lo, nullptr)))
+        return rc;
+    if ((rc = launch_grouped_umma(c, st, false, s->seg_dn, s->nseg, nseg_max, M.ff, M.e, &s->maps_act, s->rows_total, nullptr,
+                                  nullptr, nullptr, s->row_dst)))
+        return rc;
+    {
+        ProfScope p_(c, st, "ep_signal_wait");
+        ep_signal_kernel<<<1, 32, 0, st>>>(s->world, s->rank, seq, s->peers);
+        ep_wait_ret_kernel<<<1, 32, 0, st>>>((EpArena*)s->arena, s->world, seq, c->status);
+    }
+    c->launches += 2;
+    DNB_CUDA(cudaGetLastError());
+    // 4. weighted sum in ascending slot order, as on one GPU
+    const float* coef = nullptr;
+    if (shared && L.shared_gate_row) {
+        if ((rc = launch_shared_coef(c, st, w.xn, L.shared_gate_row, nt, M.e, w.shcoef))) return rc;
+        coef = w.shcoef;
+    }
+    return launch_combine(c, st, (const float*)(s->arena + s->off_h), nullptr, w.wts, nt, M.k, M.e, shared ? w.sh : nullptr, coef,
+                          out_dev);
+}

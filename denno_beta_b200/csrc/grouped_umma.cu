@@ -379,7 +379,8 @@ template <int NMAT>
 __global__ void __launch_bounds__(NTHREADS, 1)
 grouped_q4k_umma_kernel(const SegDesc* __restrict__ seg, const int32_t* __restrict__ nseg_dev, int n_in, int n_out,
                         int rb, const __grid_constant__ Maps maps, uint16_t* __restrict__ out_hi,
-                        uint16_t* __restrict__ out_lo, float* __restrict__ out_f32, int* status) {
+                        uint16_t* __restrict__ out_lo, float* __restrict__ out_f32, int* status,
+                        float* const* __restrict__ row_dst) {
     constexpr int STAGES = (NMAT == 2) ? 2 : 3;
     constexpr int A_BYTES = NMAT * 2 * A_TILE;          // hi + lo per matrix
     constexpr int B_BYTES_MAX = 2 * 128 * BK * 2;       // hi + lo, N = 128
@@ -555,10 +556,19 @@ grouped_q4k_umma_kernel(const SegDesc* __restrict__ seg, const int32_t* __restri
                         }
                     }
                 } else {
-                    float* of = out_f32 + (size_t)(it.prow + c0) * n_out + it.r0 + r;
+                    if (row_dst) {
+                        // Expert parallel: packed row p's result goes where row_dst[p] points, the
+                        // (token, slot) row of the GPU that owns the token -- a plain store over
+                        // NVLink from this epilogue, no copy pass afterwards.
 #pragma unroll
-                    for (int j2 = 0; j2 < 16; ++j2)
-                        if (j2 < nv) of[(size_t)j2 * n_out] = __uint_as_float(gq[j2]);
+                        for (int j2 = 0; j2 < 16; ++j2)
+                            if (j2 < nv) row_dst[it.prow + c0 + j2][it.r0 + r] = __uint_as_float(gq[j2]);
+                    } else {
+                        float* of = out_f32 + (size_t)(it.prow + c0) * n_out + it.r0 + r;
+#pragma unroll
+                        for (int j2 = 0; j2 < 16; ++j2)
+                            if (j2 < nv) of[(size_t)j2 * n_out] = __uint_as_float(gq[j2]);
+                    }
                 }
             }
             tc_fence_before();  // TMEM reads ordered before the hand-back of the buffer
@@ -656,7 +666,7 @@ int launch_gather_split(dnb_ctx* c, cudaStream_t st, const float* x, int ldx, co
 // hi/lo bf16 packed rows; otherwise seg[].wa, fp32 output rows.
 int launch_grouped_umma(dnb_ctx* c, cudaStream_t st, bool fused, const SegDesc* seg, const int32_t* nseg_dev,
                         int nseg_max, int n_in, int n_out, const UmmaMaps* maps, int nt_max, uint16_t* out_hi,
-                        uint16_t* out_lo, float* out_f32) {
+                        uint16_t* out_lo, float* out_f32, float* const* row_dst) {
     if (n_in % 256 || n_out % um::TILE_M) return DNB_DECLINED;
     const int rb = n_in / 256 * 144;
     const um::Maps& M = *reinterpret_cast<const um::Maps*>(maps);
@@ -672,7 +682,7 @@ int launch_grouped_umma(dnb_ctx* c, cudaStream_t st, bool fused, const SegDesc* 
         }
         ProfScope prof_(c, st, "umma_gate_up");
         um::grouped_q4k_umma_kernel<2><<<grid, um::NTHREADS, smem, st>>>(seg, nseg_dev, n_in, n_out, rb, M, out_hi, out_lo,
-                                                                        nullptr, c->status);
+                                                                        nullptr, c->status, nullptr);
     } else {
         const size_t smem = 3 * (2 * um::A_TILE + 2 * 128 * um::BK * 2) + 256 + (um::kMaxSeg + 1) * 4 + um::kLocalItems * sizeof(um::Item) + 1024;
         static bool set = false;
@@ -682,7 +692,7 @@ int launch_grouped_umma(dnb_ctx* c, cudaStream_t st, bool fused, const SegDesc* 
         }
         ProfScope prof_(c, st, "umma_down");
         um::grouped_q4k_umma_kernel<1><<<grid, um::NTHREADS, smem, st>>>(seg, nseg_dev, n_in, n_out, rb, M, nullptr, nullptr,
-                                                                        out_f32, c->status);
+                                                                        out_f32, c->status, row_dst);
     }
     c->launches++;
     DNB_CUDA(cudaGetLastError());

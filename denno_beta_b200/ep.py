@@ -140,3 +140,41 @@ class ExpertParallelBlock:
             out = self.combine(layer, h_slots, wts, sh, x)
         torch.cuda.current_stream(self.dev).wait_stream(self.stream)
         return out
+
+
+class PeerMemoryExpertParallel:
+    """One rank of an expert-parallel model whose ranks exchange rows through each other's
+    memory (dnb_ep_* entry points): no collective between the kernels of a block and no
+    host round trip.  torch.distributed is used once, to all-gather the 64-byte memory
+    handles.  `ctx`: configured with dnb_moe_config, set_expert_shard(rank * n_local,
+    n_local) and this rank's experts (router, norm, shared expert replicated)."""
+
+    def __init__(self, ctx, max_tokens, rank=None, world=None, group=None):
+        import numpy as np
+
+        from ._lib import check
+
+        self.ctx = ctx
+        self.rank = dist.get_rank() if rank is None else rank
+        self.world = dist.get_world_size() if world is None else world
+        handle = np.zeros(64, np.uint8)
+        check(ctx.lib.dnb_ep_init(ctx.h, self.rank, self.world, max_tokens, C.c_void_p(handle.ctypes.data)))
+        if self.world > 1:
+            # the handles are plain bytes: gather them with whatever backend the group has
+            dev = torch.device("cuda", ctx.device) if dist.get_backend(group) == "nccl" else torch.device("cpu")
+            mine = torch.from_numpy(handle).to(dev)
+            got = [torch.empty_like(mine) for _ in range(self.world)]
+            dist.all_gather(got, mine, group=group)
+            handles = np.concatenate([g.cpu().numpy() for g in got])
+        else:
+            handles = handle
+        handles = np.ascontiguousarray(handles, np.uint8)
+        check(ctx.lib.dnb_ep_connect(ctx.h, C.c_void_p(handles.ctypes.data)))
+        if self.world > 1:
+            dist.barrier(group=group)  # every arena is mapped before anyone stores into one
+
+    def block_dev(self, layer, h_dev, nt, out_dev):
+        """Device pointers (ints): h [nt][e] -> out [nt][e] for this rank's own tokens."""
+        from ._lib import check
+
+        check(self.ctx.lib.dnb_ep_block_dev(self.ctx.h, layer, C.c_void_p(h_dev), nt, C.c_void_p(out_dev)))

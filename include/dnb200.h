@@ -210,6 +210,27 @@ int dnb_expert_rows_dev(dnb_ctx* ctx, int layer, const float* x_rows_dev, const 
                         int use_shared, float* h_rows_dev);
 int dnb_moe_combine_dev(dnb_ctx* ctx, int layer, const float* h_slots_dev, const float* wts_dev, const float* shared_dev,
                         const float* x_dev, int nt, float* out_dev);
+/* ---- expert-parallel block over peer memory (prefill chunks, Q4_K layers) -----------
+ * No counterpart in the reference (single GPU; its multi-device plan stops at keeping
+ * experts resident, src/expert_vram.rs).  One process per GPU of one node.  Instead of
+ * handing the rows to a collective library between the calls above, the ranks store them
+ * into each other's memory from this library's own kernels: the dispatch writes the bf16
+ * operand rows straight into the owner rank's GEMM input buffers, and the epilogue of
+ * the owner's down GEMM stores every result row into the (token, slot) row of the rank
+ * that owns the token.  Flags in the ranks' own memory order the steps; every wait is
+ * bounded and a wait that gives up shows in dnb_device_status (codes 20-22).
+ *   dnb_ep_init    : after dnb_moe_config, dnb_moe_set_expert_shard(rank*ne/world,
+ *       ne/world) and the expert registration.  Allocates this rank's arena for up to
+ *       max_tokens own tokens per call and writes its 64-byte IPC handle to handle_out.
+ *   dnb_ep_connect : handles = world x 64 bytes, rank r's handle at byte 64*r (exchange
+ *       them with any host-side all-gather); maps the peers' arenas.
+ *   dnb_ep_block_dev: one MoE block for this rank's nt tokens, h_dev/out_dev device
+ *       [nt][n_embd].  Every rank of the group must make the same sequence of calls
+ *       (same layer; nt may differ per rank).  The result equals the single-GPU block
+ *       bit for bit: same operands, same accumulation order, same combine order. */
+int dnb_ep_init(dnb_ctx* ctx, int rank, int world, int max_tokens, void* handle_out);
+int dnb_ep_connect(dnb_ctx* ctx, const void* handles);
+int dnb_ep_block_dev(dnb_ctx* ctx, int layer, const float* h_dev, int nt, float* out_dev);
 /* A stack of the configured layers with identity mixers: h <- h + block_l(h) for
  * l = 0..n_layer-1 (device-resident between layers).  h host [nt][n_embd] in/out. */
 int dnb_moe_stack(dnb_ctx* ctx, const float* h, int nt, float* out);

@@ -105,8 +105,66 @@ def gpu_rank(rank, world, port):
         dist.destroy_process_group()
 
 
+def gpu_p2p_rank(rank, world, port):
+    """Peer-memory expert parallel (dnb_ep_*): each rank holds ne/world experts and its own
+    tokens; the output must equal the single-GPU block bit for bit, twice."""
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import torch
+    import torch.distributed as dist
+
+    import oracle as orc
+    from denno_beta_b200 import cuda as cu, ep
+    from helpers import SEED, make_layer, rel_err
+
+    torch.cuda.set_device(rank)
+    _init(rank, world, port, "nccl")
+    try:
+        e, ff, ne, k, nt = 512, 256, 32, 4, 40 + 3 * rank  # ragged: the ranks own different token counts
+        starts = [sum(40 + 3 * r for r in range(q)) for q in range(world + 1)]
+        full = cu.CudaCtx(rank)
+        assert full.moe_config(1, e, ff, ne, k)
+        L = make_layer(orc, full, 0, orc.Q4_K, e, ff, ne, k, bias=True, gate_row=True)
+        h_all = orc.synth_normal(SEED, 7701, 1.0, starts[world] * e).reshape(starts[world], e)
+        want = full.moe_block(0, h_all)[starts[rank]:starts[rank + 1]]
+        full.close()
+        c = cu.CudaCtx(rank)
+        assert c.moe_config(1, e, ff, ne, k)
+        nl = ne // world
+        c.set_expert_shard(rank * nl, nl)
+        kp = L.keep
+        gb, db = kp["gate"].size // ne, kp["down"].size // ne
+        sl = slice(rank * nl * gb, (rank + 1) * nl * gb)
+        sd = slice(rank * nl * db, (rank + 1) * nl * db)
+        assert c.register_experts(0, cu.GATE, orc.Q4_K, e, ff, nl, kp["gate"][sl])
+        assert c.register_experts(0, cu.UP, orc.Q4_K, e, ff, nl, kp["up"][sl])
+        assert c.register_experts(0, cu.DOWN, orc.Q4_K, ff, e, nl, kp["down"][sd])
+        assert c.register_experts(0, cu.SHARED_GATE, orc.Q4_K, e, ff, 1, kp["sg"])
+        assert c.register_experts(0, cu.SHARED_UP, orc.Q4_K, e, ff, 1, kp["su"])
+        assert c.register_experts(0, cu.SHARED_DOWN, orc.Q4_K, ff, e, 1, kp["sd"])
+        c.register_router(0, kp["router_w"], kp["router_bias"], kp["norm_w"], kp["sgr"])
+        pm = ep.PeerMemoryExpertParallel(c, max_tokens=64)
+        h = np.ascontiguousarray(h_all[starts[rank]:starts[rank + 1]])
+        d_h, d_o = c.dev_alloc(h.nbytes), c.dev_alloc(h.nbytes)
+        c.upload(d_h, h)
+        outs = []
+        for _ in range(3):
+            pm.block_dev(0, d_h, nt, d_o)
+            c.sync()
+            outs.append(c.download(d_o, np.empty((nt, e), np.float32)))
+        status = c.device_status()
+        dist.barrier()  # nobody tears its arena down while a peer may still store into it
+        err = rel_err(outs[0], want)
+        same_as_one_gpu = bool(np.array_equal(outs[0].view(np.uint32), want.view(np.uint32)))
+        repeat = all(np.array_equal(outs[0].view(np.uint32), o.view(np.uint32)) for o in outs[1:])
+        print("rank %d p2p: err %.3g equals-single-gpu %s repeatable %s status %d" % (rank, err, same_as_one_gpu, repeat, status),
+              flush=True)
+        assert status == 0 and repeat and err <= 5e-4 and same_as_one_gpu
+        c.close()
+    finally:
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":
     kind, rank, world, port = sys.argv[1], int(sys.argv[2]), int(sys.argv[3]), int(sys.argv[4])
-    (cpu_rank if kind == "cpu" else gpu_rank)(rank, world, port)
+    {"cpu": cpu_rank, "gpu": gpu_rank, "gpu_p2p": gpu_p2p_rank}[kind](rank, world, port)

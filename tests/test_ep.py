@@ -60,3 +60,42 @@ def test_expert_parallel_equals_single_gpu():
     outs = _run_ranks("gpu", 2, 29650, 900)
     for _, o in outs:
         print(o[-600:])
+
+
+@pytest.mark.gpu
+def test_peer_memory_path_on_one_gpu():
+    """World of one: the dispatch, the tables, the down epilogue's row destinations and the
+    flags all run against the rank's own arena.  The block must equal the ordinary
+    single-GPU block bit for bit."""
+    import numpy as np
+
+    import oracle as orc
+    from denno_beta_b200 import cuda as cu, ep
+    from helpers import SEED, make_layer
+
+    e, ff, ne, k, nt = 512, 256, 32, 4, 50
+    c = cu.CudaCtx(0)
+    try:
+        assert c.moe_config(1, e, ff, ne, k)
+        make_layer(orc, c, 0, orc.Q4_K, e, ff, ne, k, bias=True, gate_row=True)
+        h = orc.synth_normal(SEED, 7702, 1.0, nt * e).reshape(nt, e)
+        want = c.moe_block(0, h)
+        pm = ep.PeerMemoryExpertParallel(c, max_tokens=64, rank=0, world=1)
+        d_h, d_o = c.dev_alloc(h.nbytes), c.dev_alloc(h.nbytes)
+        c.upload(d_h, h)
+        for _ in range(2):
+            pm.block_dev(0, d_h, nt, d_o)
+            c.sync()
+            got = c.download(d_o, np.empty((nt, e), np.float32))
+            assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+        assert c.device_status() == 0
+    finally:
+        c.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(_n_gpus() < 2, reason="needs at least 2 GPUs")
+def test_peer_memory_expert_parallel_equals_single_gpu():
+    outs = _run_ranks("gpu_p2p", 2, 29660, 900)
+    for _, o in outs:
+        print(o[-600:])
