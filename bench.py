@@ -358,25 +358,48 @@ def ep_prefill_extras(cu, oracle, rank, world, local_rank):
             assert ctx.synth_experts(l, m, Q4_K, ni, no, n, SEED + rank)
         ctx.register_router(l, oracle.synth_normal(SEED, l * 16 + 6, 0.02, NE * E), oracle.synth_zipf_bias(SEED, l * 16 + 7, 1.1, NE),
                             np.ones(E, np.float32), None)
+    h_all = oracle.synth_normal(SEED, 8000, 1.0, nt_total * E).reshape(nt_total, E)
+
+    def timed(step, reps=16):
+        for l in range(2 * layers):
+            step(l % layers)
+        ctx.sync()
+        dist.barrier()
+        ctx.timer_start()
+        for l in range(reps):
+            step(l % layers)
+        ms = torch.tensor([ctx.timer_stop() / reps], dtype=torch.float64, device="cuda:%d" % local_rank)
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms)
+
+    out = {"experts_per_rank": nl}
+    # (a) rows exchanged by NCCL all-to-all between this library's calls (host plans the split sizes)
     blk = ep.ExpertParallelBlock(ctx, E, NE, K)
-    h = torch.from_numpy(oracle.synth_normal(SEED, 8000, 1.0, nt_total * E).reshape(nt_total, E)[rank * nt:(rank + 1) * nt].copy()).cuda(local_rank)
-    for l in range(2 * layers):
-        blk.block(l % layers, h)
-    torch.cuda.synchronize()
+    h = torch.from_numpy(h_all[rank * nt:(rank + 1) * nt].copy()).cuda(local_rank)
+    ms = timed(lambda l: blk.block(l, h))
+    out["nccl_all_to_all_strong"] = {"ms_per_chunk_layer": ms, "tok_per_s_layer": nt_total / (ms * 1e-3), "tokens_per_rank": nt,
+                                     "exchange": "NCCL all_to_all_single (dispatch rows fp32 + ids, return rows fp32)",
+                                     "scaling": "strong (one 512-token chunk over %d GPUs)" % world}
+    # (b), (c) rows stored into the peers' memory by this library's kernels, no collective, no host round trip
+    pm = ep.PeerMemoryExpertParallel(ctx, max_tokens=nt_total)
+    d_h = ctx.dev_alloc(nt_total * E * 4)
+    d_o = ctx.dev_alloc(nt_total * E * 4)
+    ctx.upload(d_h, np.ascontiguousarray(h_all[rank * nt:(rank + 1) * nt]))
+    ms = timed(lambda l: pm.block_dev(l, d_h, nt, d_o))
+    out["peer_memory_strong"] = {"ms_per_chunk_layer": ms, "tok_per_s_layer": nt_total / (ms * 1e-3), "tokens_per_rank": nt,
+                                 "exchange": "peer stores from the dispatch kernel and the down-GEMM epilogue, flag-ordered",
+                                 "scaling": "strong (one 512-token chunk over %d GPUs)" % world}
+    # every rank owns a whole 512-token chunk (a prompt's chunks spread over the ranks)
+    ctx.upload(d_h, np.ascontiguousarray(oracle.synth_normal(SEED, 8000 + rank, 1.0, nt_total * E)))
+    ms = timed(lambda l: pm.block_dev(l, d_h, nt_total, d_o))
+    out["peer_memory_chunk_per_rank"] = {"ms_per_step_layer": ms, "ms_per_chunk_layer": ms / world,
+                                         "tok_per_s_layer": world * nt_total / (ms * 1e-3), "tokens_per_rank": nt_total,
+                                         "exchange": "peer stores from the dispatch kernel and the down-GEMM epilogue, flag-ordered",
+                                         "scaling": "%d chunks of 512 tokens in flight, one per GPU" % world}
+    out["device_status"] = ctx.device_status()
     dist.barrier()
-    reps = 16
-    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t0.record()
-    for l in range(reps):
-        blk.block(l % layers, h)
-    t1.record()
-    torch.cuda.synchronize()
-    ms = torch.tensor([t0.elapsed_time(t1) / reps], dtype=torch.float64, device="cuda:%d" % local_rank)
-    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     ctx.close()
-    return {"ms_per_chunk_layer": float(ms), "tok_per_s_layer": nt_total / (float(ms) * 1e-3), "tokens_per_rank": nt,
-            "experts_per_rank": nl, "exchange": "NCCL all_to_all_single (dispatch rows fp32 + ids, return rows fp32)",
-            "scaling": "strong (one 512-token chunk over %d GPUs)" % world}
+    return out
 
 
 def stack_extras(cu, oracle, device):

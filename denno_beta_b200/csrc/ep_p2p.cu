@@ -41,8 +41,9 @@ struct EpArena {                       // head of every rank's exported allocati
     uint32_t cnt_flag[kEpMaxWorld];    // [s] = seq once source s has written cnt[s][*]
     uint32_t data_flag[kEpMaxWorld];   // [s] = seq once source s has stored all its rows here
     uint32_t ret_flag[kEpMaxWorld];    // [d] = seq once owner d has stored all results for my tokens
-    int32_t cnt[kEpMaxWorld][kEpMaxLocal];  // cnt[s][e]: rows of source s for my local expert e
+    int32_t cnt[kEpMaxWorld][kEpMaxWorld * kEpMaxLocal / 8];  // cnt[s][e]: rows source s has for GLOBAL expert e (ne <= 1024)
 };
+constexpr int kEpMaxExperts = kEpMaxWorld * kEpMaxLocal / 8;
 
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -78,10 +79,10 @@ struct EpPeers {                 // kernel parameter: every rank's arena as seen
     float* h_slots[kEpMaxWorld];
 };
 
-// One CTA.  sels[nt][k] (global expert ids, ascending per token) -> send_row[i], the index
-// of row i = t*k+slot inside this rank's region at its destination: rows of a destination
-// sorted by expert, tokens ascending inside an expert.  The per-expert counts go to the
-// destinations, then the flag.
+// One CTA.  sels[nt][k] (global expert ids, ascending per token) -> send_row[i] = how many
+// earlier tokens of this rank selected the same expert (the row's index among this rank's
+// rows of that expert).  The per-expert counts go to EVERY rank (each needs the whole count
+// matrix to place its rows), then the flag.
 __global__ void __launch_bounds__(1024)
 ep_plan_kernel(const int32_t* __restrict__ sels, int nt, int k, int ne, int n_local, int world, int me, uint32_t seq,
                EpPeers peers, int32_t* __restrict__ send_row) {
@@ -89,7 +90,6 @@ ep_plan_kernel(const int32_t* __restrict__ sels, int nt, int k, int ne, int n_lo
     const int words = (nt + 31) >> 5;
     uint32_t* bitmap = sm;                         // [ne][words]: token t selects expert e
     int* counts = (int*)(sm + (size_t)ne * words); // [ne]
-    int* first = counts + ne;                      // [ne]: offset of expert e inside its destination region
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = blockDim.x >> 5;
     for (int i = tid; i < ne * words; i += blockDim.x) bitmap[i] = 0;
     __syncthreads();
@@ -106,11 +106,6 @@ ep_plan_kernel(const int32_t* __restrict__ sels, int nt, int k, int ne, int n_lo
         if (lane == 0) counts[e] = c;
     }
     __syncthreads();
-    if (tid < world) {  // exclusive scan of the counts inside each destination's expert range
-        int run = 0;
-        for (int e = tid * n_local; e < (tid + 1) * n_local; ++e) { first[e] = run; run += counts[e]; }
-    }
-    __syncthreads();
     for (int i = tid; i < nt * k; i += blockDim.x) {
         const int e = sels[i], t = i / k;
         int r = -1;
@@ -118,30 +113,64 @@ ep_plan_kernel(const int32_t* __restrict__ sels, int nt, int k, int ne, int n_lo
             const uint32_t* bm = bitmap + (size_t)e * words;
             int before = __popc(bm[t >> 5] & ((1u << (t & 31)) - 1u));
             for (int w = 0; w < (t >> 5); ++w) before += __popc(bm[w]);
-            r = first[e] + before;
+            r = before;
         }
         send_row[i] = r;
     }
-    for (int i = tid; i < ne; i += blockDim.x) peers.arena[i / n_local]->cnt[me][i % n_local] = counts[i];
+    for (int d = 0; d < world; ++d)
+        for (int i = tid; i < ne; i += blockDim.x) peers.arena[d]->cnt[me][i] = counts[i];
     __threadfence_system();
     __syncthreads();
     if (tid < world) st_release_sys(&peers.arena[tid]->cnt_flag[me], seq);
 }
 
-// One CTA per row i = t*k+slot: split x[t] to bf16 hi/lo and store it as row me*cap + j of
-// the owner's operand buffers; the last CTA to finish raises the data flag at every peer.
+// One CTA.  Waits for every rank's counts, then base[e] = where this rank's rows of global
+// expert e start in the owner's buffers: the owner keeps its experts in ascending order,
+// inside an expert the sources in ascending rank, inside a source the tokens ascending.
+__global__ void __launch_bounds__(1024)
+ep_offsets_kernel(const EpArena* mine, int ne, int n_local, int world, int me, uint32_t seq, int32_t* __restrict__ base,
+                  int* status) {
+    __shared__ int tot[kEpMaxExperts];   // rows of expert e over all sources
+    __shared__ int mine_off[kEpMaxExperts];  // rows of expert e from sources before me
+    __shared__ int ok_all;
+    const int tid = threadIdx.x;
+    if (tid == 0) ok_all = 1;
+    __syncthreads();
+    if (tid < world && !wait_flag(&mine->cnt_flag[tid], seq)) { atomicExch(status, 21); ok_all = 0; }
+    __syncthreads();
+    for (int e = tid; e < ne; e += blockDim.x) {
+        int t = 0, b = 0;
+        for (int s = 0; s < world; ++s) {
+            const int c = ok_all ? mine->cnt[s][e] : 0;
+            if (s < me) b += c;
+            t += c;
+        }
+        tot[e] = t;
+        mine_off[e] = b;
+    }
+    __syncthreads();
+    if (tid < world) {  // exclusive scan of the totals inside each owner's expert range
+        int run = 0;
+        for (int e = tid * n_local; e < (tid + 1) * n_local; ++e) { const int t = tot[e]; tot[e] = run; run += t; }
+    }
+    __syncthreads();
+    for (int e = tid; e < ne; e += blockDim.x) base[e] = tot[e] + mine_off[e];
+}
+
+// One CTA per row i = t*k+slot: split x[t] to bf16 hi/lo and store it as row base[expert] + j
+// of the owner's operand buffers; the last CTA to finish raises the data flag at every peer.
 __global__ void __launch_bounds__(256)
 ep_dispatch_kernel(const float* __restrict__ x, const int32_t* __restrict__ sels, const int32_t* __restrict__ send_row,
-                   int k, int e, int n_local, int world, int me, int cap, uint32_t seq, EpPeers peers,
-                   unsigned int* ticket, int* status) {
+                   const int32_t* __restrict__ base, int k, int e, int n_local, int world, int me, int rows_total,
+                   uint32_t seq, EpPeers peers, unsigned int* ticket, int* status) {
     const int i = blockIdx.x, tid = threadIdx.x;
     const int ex = sels[i], j = send_row[i];
     if (ex >= 0 && j >= 0) {
-        if (j >= cap) {
+        const size_t r = (size_t)base[ex] + j;
+        if (r >= (size_t)rows_total) {
             if (tid == 0) atomicExch(status, 20);
         } else {
             const int d = ex / n_local;
-            const size_t r = (size_t)me * cap + j;
             const float* xr = x + (size_t)(i / k) * e;
             uint16_t* hi = peers.xg_hi[d] + r * e;
             uint16_t* lo = peers.xg_lo[d] + r * e;
@@ -153,7 +182,7 @@ ep_dispatch_kernel(const float* __restrict__ x, const int32_t* __restrict__ sels
                 *reinterpret_cast<uint2*>(hi + c) = make_uint2(h0, h1);
                 *reinterpret_cast<uint2*>(lo + c) = make_uint2(l0, l1);
             }
-            if (tid == 0) peers.recv_slot[d][r] = i;
+            if (tid == 0) peers.recv_slot[d][r] = (me << 24) | i;  // who owns the token, and which (token, slot) row
         }
     }
     __threadfence_system();
@@ -168,16 +197,16 @@ ep_dispatch_kernel(const float* __restrict__ x, const int32_t* __restrict__ sels
     if (last && tid < world) st_release_sys(&peers.arena[tid]->data_flag[me], seq);
 }
 
-// One CTA.  Waits for every source's counts and rows, then builds the segment tables of
-// the two grouped GEMMs -- one segment per (source, local expert) with rows, in that
-// order -- and the destination pointer of every received row.
+// One CTA.  Waits for every source's rows, then builds the segment tables of the two grouped
+// GEMMs -- one segment per local expert with rows, heaviest first (ties: expert ascending),
+// rows of all sources together -- and the destination pointer of every received row.
 __global__ void __launch_bounds__(1024)
-ep_build_kernel(EpArena* mine, const int32_t* __restrict__ recv_slot, int world, int n_local, int cap, int e,
-                uint32_t seq, EpPeers peers, const uint8_t* gate, const uint8_t* up, const uint8_t* down, size_t eb_g,
-                size_t eb_u, size_t eb_d, SegDesc* seg_gu, SegDesc* seg_dn, int32_t* nseg, float** row_dst, int* status) {
+ep_build_kernel(EpArena* mine, const int32_t* __restrict__ recv_slot, int world, int n_local, int me, int e, uint32_t seq,
+                EpPeers peers, const uint8_t* gate, const uint8_t* up, const uint8_t* down, size_t eb_g, size_t eb_u,
+                size_t eb_d, SegDesc* seg_gu, SegDesc* seg_dn, int32_t* nseg, float** row_dst, int* status) {
     __shared__ int ok_all;
-    __shared__ int seg_base[kEpMaxWorld + 1];
-    __shared__ int rows_of[kEpMaxWorld];
+    __shared__ int tot[kEpMaxLocal], first[kEpMaxLocal];
+    __shared__ int n_rows;
     const int tid = threadIdx.x;
     if (tid == 0) ok_all = 1;
     __syncthreads();
@@ -190,36 +219,32 @@ ep_build_kernel(EpArena* mine, const int32_t* __restrict__ recv_slot, int world,
         if (tid == 0) *nseg = 0;
         return;
     }
-    if (tid < world) {
-        int n = 0, rows = 0;
-        for (int x = 0; x < n_local; ++x) { const int c = mine->cnt[tid][x]; n += c > 0 ? 1 : 0; rows += c; }
-        seg_base[tid + 1] = n;
-        rows_of[tid] = rows;
+    for (int x = tid; x < n_local; x += blockDim.x) {
+        int t = 0;
+        for (int s = 0; s < world; ++s) t += mine->cnt[s][me * n_local + x];
+        tot[x] = t;
     }
     __syncthreads();
     if (tid == 0) {
-        seg_base[0] = 0;
-        for (int s = 0; s < world; ++s) seg_base[s + 1] += seg_base[s];
-        *nseg = seg_base[world];
+        int run = 0, n = 0;
+        for (int x = 0; x < n_local; ++x) { first[x] = run; run += tot[x]; n += tot[x] > 0 ? 1 : 0; }
+        n_rows = run;
+        *nseg = n;
     }
     __syncthreads();
-    if (tid < world) {
-        int idx = seg_base[tid], row = tid * cap;
-        for (int x = 0; x < n_local; ++x) {
-            const int c = mine->cnt[tid][x];
-            if (c > 0) {
-                seg_gu[idx] = SegDesc{gate + (size_t)x * eb_g, up + (size_t)x * eb_u, (uint32_t)c, (uint32_t)row};
-                seg_dn[idx] = SegDesc{down + (size_t)x * eb_d, nullptr, (uint32_t)c, (uint32_t)row};
-                ++idx;
-                row += c;
-            }
+    for (int x = tid; x < n_local; x += blockDim.x) {
+        const int c = tot[x];
+        if (c > 0) {
+            int rank = 0;  // position in (rows descending, expert ascending) order
+            for (int o = 0; o < n_local; ++o) rank += (tot[o] > c || (tot[o] == c && o < x)) ? 1 : 0;
+            seg_gu[rank] = SegDesc{gate + (size_t)x * eb_g, up + (size_t)x * eb_u, (uint32_t)c, (uint32_t)first[x]};
+            seg_dn[rank] = SegDesc{down + (size_t)x * eb_d, nullptr, (uint32_t)c, (uint32_t)first[x]};
         }
     }
-    for (int s = 0; s < world; ++s)
-        for (int j = tid; j < rows_of[s]; j += blockDim.x) {
-            const size_t r = (size_t)s * cap + j;
-            row_dst[r] = peers.h_slots[s] + (size_t)recv_slot[r] * e;
-        }
+    for (int r = tid; r < n_rows; r += blockDim.x) {
+        const int v = recv_slot[r];
+        row_dst[r] = peers.h_slots[v >> 24] + (size_t)(v & 0xFFFFFF) * e;
+    }
 }
 
 // After the down GEMM: everything this rank stored into the owners' result rows is made
@@ -251,6 +276,7 @@ struct EpState {
     EpPeers peers;
     // local-only buffers
     int32_t* send_row = nullptr;
+    int32_t* base = nullptr;       // [ne]: where this rank's rows of each expert start at the owner
     float** row_dst = nullptr;
     uint16_t *act_hi = nullptr, *act_lo = nullptr;
     SegDesc *seg_gu = nullptr, *seg_dn = nullptr;
@@ -266,7 +292,7 @@ void ep_release(dnb_ctx* c) {
     if (!s) return;
     for (int r = 0; r < s->world; ++r)
         if (r != s->rank && s->peer_base[r]) cudaIpcCloseMemHandle(s->peer_base[r]);
-    void* loc[] = {s->arena, s->send_row, s->row_dst, s->act_hi, s->act_lo, s->seg_gu, s->seg_dn, s->nseg, s->ticket};
+    void* loc[] = {s->arena, s->send_row, s->base, s->row_dst, s->act_hi, s->act_lo, s->seg_gu, s->seg_dn, s->nseg, s->ticket};
     for (void* p : loc)
         if (p) cudaFree(p);
     delete s;
@@ -285,7 +311,7 @@ extern "C" int dnb_ep_init(dnb_ctx* c, int rank, int world, int max_tokens, void
         set_error("ep_init: configure the model and call dnb_moe_set_expert_shard(rank * ne / world, ne / world) first");
         return DNB_DECLINED;
     }
-    if (M.ne / world > kEpMaxLocal || M.e % 256 || M.ff % 256 || M.k > 32) {
+    if (M.ne / world > kEpMaxLocal || M.ne > kEpMaxExperts || M.e % 256 || M.ff % 256 || M.k > 32) {
         set_error("ep_init: shape outside the peer-memory path (e, ff multiples of 256; at most %d local experts)", kEpMaxLocal);
         return DNB_DECLINED;
     }
@@ -305,6 +331,7 @@ extern "C" int dnb_ep_init(dnb_ctx* c, int rank, int world, int max_tokens, void
     DNB_CUDA(cudaMalloc((void**)&s->arena, s->arena_bytes));
     DNB_CUDA(cudaMemset(s->arena, 0, s->arena_bytes));
     DNB_CUDA(cudaMalloc((void**)&s->send_row, (size_t)s->cap * 4));
+    DNB_CUDA(cudaMalloc((void**)&s->base, (size_t)M.ne * 4));
     DNB_CUDA(cudaMalloc((void**)&s->row_dst, (size_t)s->rows_total * sizeof(float*)));
     DNB_CUDA(cudaMalloc((void**)&s->act_hi, rows_pad * M.ff * 2));
     DNB_CUDA(cudaMalloc((void**)&s->act_lo, rows_pad * M.ff * 2));
@@ -374,7 +401,7 @@ extern "C" int dnb_ep_block_dev(dnb_ctx* c, int layer, const float* h_dev, int n
     cudaStream_t st = c->stream;
     const uint32_t seq = ++s->seq;
     const int words = (nt + 31) >> 5;
-    const size_t plan_smem = ((size_t)M.ne * words + 2 * (size_t)M.ne) * 4;
+    const size_t plan_smem = ((size_t)M.ne * words + (size_t)M.ne) * 4;
     static size_t plan_set = 0;
     if (plan_smem > 200 * 1024) return DNB_DECLINED;
     if (plan_smem > plan_set) {
@@ -386,11 +413,15 @@ extern "C" int dnb_ep_block_dev(dnb_ctx* c, int layer, const float* h_dev, int n
         ep_plan_kernel<<<1, 1024, plan_smem, st>>>(w.sels, nt, M.k, M.ne, s->n_local, s->world, s->rank, seq, s->peers, s->send_row);
     }
     {
-        ProfScope p_(c, st, "ep_dispatch");
-        ep_dispatch_kernel<<<nt * M.k, 256, 0, st>>>(w.xn, w.sels, s->send_row, M.k, M.e, s->n_local, s->world, s->rank, s->cap,
-                                                    seq, s->peers, s->ticket, c->status);
+        ProfScope p_(c, st, "ep_offsets");
+        ep_offsets_kernel<<<1, 1024, 0, st>>>((const EpArena*)s->arena, M.ne, s->n_local, s->world, s->rank, seq, s->base, c->status);
     }
-    c->launches += 2;
+    {
+        ProfScope p_(c, st, "ep_dispatch");
+        ep_dispatch_kernel<<<nt * M.k, 256, 0, st>>>(w.xn, w.sels, s->send_row, s->base, M.k, M.e, s->n_local, s->world, s->rank,
+                                                    s->rows_total, seq, s->peers, s->ticket, c->status);
+    }
+    c->launches += 3;
     DNB_CUDA(cudaGetLastError());
     // 2. the shared expert of the own tokens while the peers' rows arrive
     const bool shared = L.has_shared();
@@ -400,13 +431,13 @@ extern "C" int dnb_ep_block_dev(dnb_ctx* c, int layer, const float* h_dev, int n
     {
         ProfScope p_(c, st, "ep_build");
         ep_build_kernel<<<1, 1024, 0, st>>>((EpArena*)s->arena, (const int32_t*)(s->arena + s->off_slot), s->world, s->n_local,
-                                            s->cap, M.e, seq, s->peers, (const uint8_t*)L.m[0].dev, (const uint8_t*)L.m[1].dev,
+                                            s->rank, M.e, seq, s->peers, (const uint8_t*)L.m[0].dev, (const uint8_t*)L.m[1].dev,
                                             (const uint8_t*)L.m[2].dev, L.m[0].expert_bytes, L.m[1].expert_bytes,
                                             L.m[2].expert_bytes, s->seg_gu, s->seg_dn, s->nseg, s->row_dst, c->status);
     }
     c->launches++;
     DNB_CUDA(cudaGetLastError());
-    const int nseg_max = s->world * s->n_local;
+    const int nseg_max = s->n_local;
     if ((rc = launch_grouped_umma(c, st, true, s->seg_gu, s->nseg, nseg_max, M.e, M.ff, &s->maps_x, s->rows_total, s->act_hi,
                                   s->act_lo, nullptr)))
         return rc;
