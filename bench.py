@@ -196,14 +196,12 @@ def run_ours(args, rank, world, local_rank):
         t = torch.tensor([ms_dev, ms_e2e], dtype=torch.float64, device="cuda:%d" % local_rank)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_dev, ms_e2e = float(t[0]), float(t[1])
-    ep_res = None
-    if world > 1 and not args.no_extras:
+    if world > 1 and ctx is not None:
         ctx.close()
         ctx = None
-        ep_res = ep_prefill_extras(cu, oracle, rank, world, local_rank)
     if rank != 0:
-        if ctx is not None:
-            ctx.close()
+        if world > 1 and not args.no_extras:
+            guarded_ep_extras(None, cu, oracle, rank, world, local_rank)
         return None
 
     hbm_peak, _, peak_kind = peaks()
@@ -241,8 +239,8 @@ def run_ours(args, rank, world, local_rank):
         "block_hbm_gbs": block_bytes / (ms_dev / K_ * 1e-3) / 1e9,
         "kernels_ms": {k: round(v["ms"], 4) for k, v in prof.items()},
     }
-    if ep_res is not None:
-        res["extras"] = {"config2_q4k_prefill_512_expert_parallel": ep_res}
+    if world > 1 and not args.no_extras:
+        res["extras"] = {"config2_q4k_prefill_512_expert_parallel": guarded_ep_extras(res, cu, oracle, rank, world, local_rank)}
     if world == 1 and not args.no_extras:
         res["extras"] = extras(ctx, cu, oracle)
         ctx.close()
@@ -338,6 +336,32 @@ def prefill_extras(cu, oracle, device, layers=4):
     return out
 
 
+_EMIT = {"fd": None}
+
+
+def guarded_ep_extras(partial, cu, oracle, rank, world, local_rank, limit_s=420.0):
+    """The expert-parallel extras under a watchdog: whatever happens to them (an exception on
+    one rank leaves the others waiting in a collective), rank 0 still prints the bench line,
+    with the reason in place of the extras, and every rank exits 0."""
+    import threading
+
+    def bail(why):
+        if partial is not None and _EMIT["fd"] is not None:
+            partial["extras"] = {"config2_q4k_prefill_512_expert_parallel": {"error": why}}
+            os.write(_EMIT["fd"], (json.dumps(partial) + "\n").encode())
+        os._exit(0)
+
+    timer = threading.Timer(limit_s, bail, args=("expert-parallel extras did not finish in %.0f s" % limit_s,))
+    timer.daemon = True
+    timer.start()
+    try:
+        out = ep_prefill_extras(cu, oracle, rank, world, local_rank)
+    except Exception as ex:  # the other ranks run into their own watchdog
+        bail("expert-parallel extras failed on rank %d: %s" % (rank, ex))
+    timer.cancel()
+    return out
+
+
 def ep_prefill_extras(cu, oracle, rank, world, local_rank):
     """Config 2 across `world` GPUs, expert parallel: 512/world experts per GPU, the
     512-token chunk split evenly over the ranks (strong scaling), dispatch and return by
@@ -396,6 +420,16 @@ def ep_prefill_extras(cu, oracle, rank, world, local_rank):
                                          "tok_per_s_layer": world * nt_total / (ms * 1e-3), "tokens_per_rank": nt_total,
                                          "exchange": "peer stores from the dispatch kernel and the down-GEMM epilogue, flag-ordered",
                                          "scaling": "%d chunks of 512 tokens in flight, one per GPU" % world}
+    # per-kernel times of one rank's step (events around every launch; waits on peers included)
+    ctx.sync()
+    dist.barrier()
+    ctx.profile(True)
+    for l in range(layers):
+        pm.block_dev(l, d_h, nt_total, d_o)
+    ctx.sync()
+    prof = ctx.profile_read()
+    ctx.profile(False)
+    out["peer_memory_chunk_per_rank"]["kernels_ms_per_layer_rank0"] = {k: round(v["ms"] / layers, 4) for k, v in prof.items()}
     out["device_status"] = ctx.device_status()
     dist.barrier()
     ctx.close()
@@ -531,6 +565,7 @@ def main():
     # line there.  Everything but the final line goes to stderr.
     real_stdout = os.dup(1)
     os.dup2(2, 1)
+    _EMIT["fd"] = real_stdout
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2000)
