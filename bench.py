@@ -433,7 +433,57 @@ def ep_prefill_extras(cu, oracle, rank, world, local_rank):
     out["device_status"] = ctx.device_status()
     dist.barrier()
     ctx.close()
+    out["config4_prefill_stack48_14018"] = ep_stack_prefill(cu, oracle, ep, rank, world, local_rank)
     return out
+
+
+def ep_stack_prefill(cu, oracle, ep, rank, world, local_rank):
+    """Config 4 across `world` GPUs: 48 all-Q4_K blocks, a 14,018-token prompt in 512-token
+    chunks (27 x 512 + 194), the chunks dealt to the ranks round-robin, every chunk-step
+    through all 48 layers with the peer-memory exchange (out of one block is the input of
+    the next; the identity mixers' residual add is left out, it is one more pass over 4 MB)."""
+    import torch
+    import torch.distributed as dist
+
+    n_layer, n_tok = 48, 14018
+    nl = NE // world
+    chunks = [512] * (n_tok // 512) + ([n_tok % 512] if n_tok % 512 else [])
+    steps = (len(chunks) + world - 1) // world
+    mine = [chunks[st * world + rank] if st * world + rank < len(chunks) else 1 for st in range(steps)]  # idle rank: 1 dummy token
+    ctx = cu.CudaCtx(local_rank)
+    assert ctx.moe_config(n_layer, E, FF, NE, K)
+    ctx.set_expert_shard(rank * nl, nl)
+    for l in range(n_layer):
+        for m, (ni, no, n) in ((cu.GATE, (E, FF, nl)), (cu.UP, (E, FF, nl)), (cu.DOWN, (FF, E, nl)),
+                               (cu.SHARED_GATE, (E, FF, 1)), (cu.SHARED_UP, (E, FF, 1)), (cu.SHARED_DOWN, (FF, E, 1))):
+            assert ctx.synth_experts(l, m, Q4_K, ni, no, n, SEED + (rank if m in (cu.GATE, cu.UP, cu.DOWN) else 0))
+        ctx.register_router(l, oracle.synth_normal(SEED, l * 16 + 6, 0.02, NE * E), oracle.synth_zipf_bias(SEED, l * 16 + 7, 1.1, NE),
+                            np.ones(E, np.float32), None)
+    pm = ep.PeerMemoryExpertParallel(ctx, max_tokens=512)
+    d_a = ctx.dev_alloc(512 * E * 4)
+    d_b = ctx.dev_alloc(512 * E * 4)
+    ctx.upload(d_a, oracle.synth_normal(SEED, 8200 + rank, 1.0, 512 * E))
+
+    def prompt():
+        for nt in mine:
+            a, b = d_a, d_b
+            for l in range(n_layer):
+                pm.block_dev(l, a, nt, b)
+                a, b = b, a
+    prompt()
+    ctx.sync()
+    dist.barrier()
+    ctx.timer_start()
+    prompt()
+    ms = torch.tensor([ctx.timer_stop()], dtype=torch.float64, device="cuda:%d" % local_rank)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms = float(ms)
+    status = ctx.device_status()
+    dist.barrier()
+    ctx.close()
+    return {"seconds": ms * 1e-3, "tok_per_s": n_tok / (ms * 1e-3), "chunk_steps": steps, "chunks": len(chunks),
+            "algorithmic_tflops": n_tok * n_layer * (11 * 6291456 + 2097152) / (ms * 1e-3) / 1e12,
+            "exchange": "peer memory (dnb_ep_block_dev), chunks dealt round-robin to %d GPUs" % world, "device_status": status}
 
 
 def stack_extras(cu, oracle, device):
