@@ -215,6 +215,9 @@ def run_ours(args, rank, world, local_rank):
         "seg_matmul_m1": K * d_b + K * FF * 4 + K * E * 4,
         "router_logits": NE * E * 4 + E * 4 + NE * 4,
     }
+    # dram__bytes_read.sum + dram__bytes_write.sum per launch, from one ncu capture of each decode
+    # kernel on this workload (profiles/kernel_gateup.md, kernel_down.md, kernel_router.md)
+    ncu_traffic = {"gemv_gate_up": 8864768, "gemv_down_combine": 4813568, "router_decode_fused": 4271616}
     top = max((k for k in prof if k in alg), key=lambda k: prof[k]["ms"])
     per_launch_s = prof[top]["ms"] / prof[top]["launches"] * 1e-3
     achieved = alg[top] / per_launch_s / 1e9
@@ -234,7 +237,7 @@ def run_ours(args, rank, world, local_rank):
         "gpu_launches": int(launches),
         "clocks": clk,
         "roofline": {"bound": "hbm", "kernel": top, "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
-                     "frac": achieved / hbm_peak, "peak_kind": peak_kind, "traffic": None,
+                     "frac": achieved / hbm_peak, "peak_kind": peak_kind, "traffic": ncu_traffic.get(top),
                      "bytes_per_launch": alg[top], "us_per_launch": per_launch_s * 1e6},
         "block_hbm_gbs": block_bytes / (ms_dev / K_ * 1e-3) / 1e9,
         "kernels_ms": {k: round(v["ms"], 4) for k, v in prof.items()},
