@@ -1,5 +1,6 @@
 // extern "C" entry points of libdnb200: context, resident tables and the
 // orchestration of one MoE block (see include/dnb200.h for the contract).
+#include <algorithm>
 #include <chrono>
 #include <stdarg.h>
 #include <stdio.h>
@@ -61,7 +62,7 @@ static int ensure_ws(dnb_ctx* c, int nt) {
     if ((rc = dev_alloc(&w.wts, rows))) return rc;
     if ((rc = dev_alloc(&w.sels, rows))) return rc;
     if ((rc = dev_alloc(&w.act, rows * M.ff))) return rc;
-    if ((rc = dev_alloc(&w.act_perm, (size_t)kActRep * (M.k + 1) * M.ff))) return rc;
+    if ((rc = dev_alloc(&w.act_perm, (size_t)kActRep * (cap < kDecodeBatchMax ? cap : kDecodeBatchMax) * (M.k + 1) * M.ff))) return rc;
     if ((rc = dev_alloc(&w.xn_perm, (size_t)kActRep * M.e))) return rc;
     if ((rc = dev_alloc(&w.hrow, rows * M.e))) return rc;
     if ((rc = dev_alloc(&w.sact, (size_t)cap * sff))) return rc;
@@ -76,8 +77,10 @@ static int ensure_ws(dnb_ctx* c, int nt) {
         DNB_CUDA(cudaMemcpy(w.one, &one, sizeof(one), cudaMemcpyHostToDevice));
     }
     if ((rc = dev_alloc(&w.counts, (size_t)M.ne))) return rc;
-    if ((rc = dev_alloc(&w.seg_gu, (size_t)M.ne + 1))) return rc;
-    if ((rc = dev_alloc(&w.seg_dn, (size_t)M.ne + 1))) return rc;
+    // one segment per active expert (+ shared) for a chunk, or per (token, slot) for a decode batch
+    const size_t nseg_cap = std::max((size_t)M.ne + 1, (size_t)kDecodeBatchMax * (M.k + 1));
+    if ((rc = dev_alloc(&w.seg_gu, nseg_cap))) return rc;
+    if ((rc = dev_alloc(&w.seg_dn, nseg_cap))) return rc;
     if ((rc = dev_alloc(&w.seg_sh_gu, 1))) return rc;
     if ((rc = dev_alloc(&w.seg_sh_dn, 1))) return rc;
     // bf16 hi/lo operand buffers of the tcgen05 path (a few rows of slack so that a
@@ -272,6 +275,41 @@ static int block_dev_decode(dnb_ctx* c, int layer, const float* h, float* out, c
     return DNB_OK;
 }
 
+// A decode batch (2..kDecodeBatchMax tokens, continuous batching): the one-token kernels over
+// token-major one-row segments.  Router: RMSNorm, logits and top-k kernels of the general
+// path, then the segment tables; gate/up GEMV with the CTA's token selecting the activation
+// row; down GEMV + weighted sum with one grid row per token.  A token's arithmetic is the
+// one-token path's, so its result does not depend on what else is in the batch.
+static int block_dev_decode_batch(dnb_ctx* c, int layer, const float* h, int nt, float* out, const float* residual) {
+    const Model& M = c->model;
+    const Layer& L = M.layers[layer];
+    Workspace& w = c->ws;
+    cudaStream_t st = c->stream;
+    const bool shared = L.has_shared();
+    const bool fold = shared && L.m[3].type == L.m[0].type && L.m[4].type == L.m[1].type &&
+                      L.m[5].type == L.m[2].type && L.m[3].n_out == M.ff;
+    if ((shared && !fold) || L.m[0].type != L.m[1].type) return DNB_DECLINED;
+    const int per = M.k + (fold ? 1 : 0), nseg = nt * per;
+    if (nt < 2 || nt > kDecodeBatchMax || M.k + 1 > 64) return DNB_DECLINED;
+    int rc;
+    if (L.norm_w)
+        if ((rc = launch_rmsnorm(c, st, h, L.norm_w, M.eps, nt, M.e, w.xn))) return rc;
+    const float* x = L.norm_w ? w.xn : h;
+    if ((rc = launch_router_logits(c, st, x, nt, M.e, L.router_w, L.router_bias, M.ne, w.logits))) return rc;
+    if ((rc = launch_topk(c, st, w.logits, nt, M.ne, M.k, M.norm_topk, w.sels, w.wts, nullptr))) return rc;
+    if ((rc = launch_decode_batch_tables(c, st, w.sels, nt, M.k, L, w, fold))) return rc;
+    rc = launch_seg_gemv_m1(c, st, L.m[0].type, true, true, w.seg_gu, nullptr, nseg, M.e, M.ff, x, M.e, w.row_token, w.act,
+                            nullptr, "gemv_gate_up", PermOut{w.act_perm, L.m[2].type, nullptr});
+    if (rc) return rc;  // declined: nothing the later kernels depend on has been replaced, the caller runs the general path
+    const float* coef = nullptr;
+    if (fold && L.shared_gate_row) {
+        if ((rc = launch_shared_coef(c, st, x, L.shared_gate_row, nt, M.e, w.shcoef))) return rc;
+        coef = w.shcoef;
+    }
+    return launch_down_combine(c, st, L.m[2].type, w.seg_dn, per, M.k, M.ff, M.e, w.act, w.wts, coef, fold, residual, out,
+                               w.act_perm, nt);
+}
+
 // Prefill chunks of all-Q4_K layers: expert-major packed rows as bf16 hi/lo, grouped
 // GEMMs on tcgen05 (gate/up with the SwiGLU epilogue, then down), weighted combine.
 static bool umma_eligible(const dnb_ctx* c, const Layer& L, int nt) {
@@ -322,6 +360,10 @@ static int block_dev(dnb_ctx* c, int layer, const float* h, int nt, float* out) 
     int rc;
     if (nt == 1 && c->decode_fast) {
         rc = block_dev_decode(c, layer, h, out, nullptr);
+        if (rc != DNB_DECLINED) return rc;
+    }
+    if (nt > 1 && nt <= kDecodeBatchMax && c->decode_fast) {
+        rc = block_dev_decode_batch(c, layer, h, nt, out, nullptr);
         if (rc != DNB_DECLINED) return rc;
     }
     const bool shared = L.has_shared();
@@ -1033,6 +1075,11 @@ int dnb_moe_stack_dev(dnb_ctx* c, float* h_dev, int nt) {
         for (int l = 0; l < M.n_layer; ++l) {
             if (nt == 1 && c->decode_fast) {
                 const int rd = block_dev_decode(c, l, h_dev, h_dev, h_dev);
+                if (rd == DNB_OK) continue;
+                if (rd != DNB_DECLINED) return rd;
+            }
+            if (nt > 1 && nt <= kDecodeBatchMax && c->decode_fast) {
+                const int rd = block_dev_decode_batch(c, l, h_dev, nt, h_dev, h_dev);
                 if (rd == DNB_OK) continue;
                 if (rd != DNB_DECLINED) return rd;
             }

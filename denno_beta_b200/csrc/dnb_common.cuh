@@ -239,12 +239,13 @@ int launch_router_decode(dnb_ctx* c, cudaStream_t st, const float* h, const Mode
 // instead of staging `act` with its threads.
 int launch_down_combine(dnb_ctx* c, cudaStream_t st, int type, const SegDesc* seg, int nseg, int k, int n_in, int n_out,
                         const float* act, const float* wts, const float* shcoef, bool has_shared,
-                        const float* residual, float* out, const float* act_perm = nullptr);
+                        const float* residual, float* out, const float* act_perm = nullptr, int ntok = 1);
 // Hand-over of the decode gate/up result to the down kernel: besides the plain rows, the
 // values are written kActRep times in the slot order the consumer's format stages its
 // activations in.  Every CTA of the consumer needs all of them; with one copy they all
 // hit the same few L2 lines at once, with replicas CTA b reads copy b % kActRep.
 constexpr int kActRep = 16;
+constexpr int kDecodeBatchMax = 32;  // token counts up to this take the decode kernels (one-row segments)
 struct PermOut {
     float* base = nullptr;  // [kActRep][nseg * n_out]
     int type = 0;           // format whose slot order to write
@@ -258,6 +259,8 @@ int launch_seg_gemv_m1(dnb_ctx* c, cudaStream_t st, int type, bool fused, bool x
                        const int32_t* nseg_dev, int nseg_max, int n_in, int n_out, const float* x, int ldx,
                        const int32_t* row_token, float* out, const SegDesc* single, const char* pname,
                        PermOut perm = PermOut());
+int launch_decode_batch_tables(dnb_ctx* c, cudaStream_t st, const int32_t* sels, int nt, int k, const Layer& L,
+                               Workspace& ws, bool fold_shared);
 int launch_topk(dnb_ctx* c, cudaStream_t st, const float* logits, int nt, int ne, int k, int norm_topk, int32_t* sels,
                 float* wts, float* rowsum);
 // Builds, from sels[nt][k], the expert-major row space: counts, segment

@@ -184,7 +184,14 @@ gemv_bulk_kernel(const SegDesc* __restrict__ seg, const int32_t* __restrict__ ns
                 bulk_g2s(xbase, x_perm + (size_t)(blockIdx.x % kActRep) * n_in, (uint32_t)(n_in * sizeof(float)), bars + kWarps);
             }
         } else {
-            stage_x<T>(xbase, x, n_in, nunits, tid, kWarps * 32);
+            // A batch of tokens: the CTA's warps all belong to one segment (the launcher
+            // checks that), whose token names the row.
+            const float* xr = x;
+            if (row_token && seg) {
+                const int s0 = (int)(((long)blockIdx.x * kWarps) / gps);
+                if (s0 < nseg) xr = x + (size_t)row_token[seg[s0].row0] * ldx;
+            }
+            stage_x<T>(xbase, xr, n_in, nunits, tid, kWarps * 32);
         }
         xs4 = reinterpret_cast<const float4*>(xbase);
     } else {
@@ -276,6 +283,14 @@ down_combine_kernel(const SegDesc* __restrict__ seg, int nseg, int k, int n_in, 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int r0 = blockIdx.x * R;
     const int nunits = n_in >> 5;
+    // blockIdx.y = token of a decode batch: its own nseg segments, weights, activations, rows
+    const int tkn = blockIdx.y;
+    seg += (size_t)tkn * nseg;
+    act += (size_t)tkn * nseg * n_in;
+    wts += (size_t)tkn * k;
+    if (shcoef) shcoef += tkn;
+    if (residual) residual += (size_t)tkn * n_out;
+    out += (size_t)tkn * n_out;
     if constexpr (T == T_IQ3_XXS) {
         for (int i = tid; i < 256; i += NT) lut->grid3xxs[i] = c_grid3xxs_b[i];
     }
@@ -298,7 +313,7 @@ down_combine_kernel(const SegDesc* __restrict__ seg, int nseg, int k, int n_in, 
         if (tid == 0) {
             const uint32_t bytes = (uint32_t)(nseg * n_in * sizeof(float));
             mbar_expect_tx(bar + 1, bytes);
-            bulk_g2s(xs, act_perm + (size_t)(blockIdx.x % kActRep) * nseg * n_in, bytes, bar + 1);
+            bulk_g2s(xs, act_perm + ((size_t)(blockIdx.x % kActRep) * gridDim.y + tkn) * nseg * n_in, bytes, bar + 1);
         }
     } else {
         stage_x_multi<T>(xs, act, n_in, nunits, nseg, tid, NT);
@@ -345,7 +360,7 @@ down_combine_kernel(const SegDesc* __restrict__ seg, int nseg, int k, int n_in, 
 template <int T, int LPR>
 static int launch_dc(dnb_ctx* c, cudaStream_t st, const SegDesc* seg, int nseg, int k, int n_in, int n_out,
                      const float* act, const float* wts, const float* shcoef, bool has_shared, const float* residual,
-                     float* out, const float* act_perm) {
+                     float* out, const float* act_perm, int ntok) {
     constexpr int R = kDcRows;
     const int rb = (int)row_bytes(T, n_in);
     if (n_out % R || (R * rb) % 16) return DNB_DECLINED;
@@ -359,7 +374,7 @@ static int launch_dc(dnb_ctx* c, cudaStream_t st, const SegDesc* seg, int nseg, 
         smem_set = smem;
     }
     ProfScope prof_(c, st, "gemv_down_combine");
-    DNB_CUDA(launch_k(kern, dim3(n_out / R), dim3(kDcWarps * 32), smem, st, c->use_pdl, seg, nseg, k, n_in, n_out, rb, act,
+    DNB_CUDA(launch_k(kern, dim3(n_out / R, ntok), dim3(kDcWarps * 32), smem, st, c->use_pdl, seg, nseg, k, n_in, n_out, rb, act,
                       wts, shcoef, has_shared ? 1 : 0, residual, out, c->status, act_perm));
     c->launches++;
     return DNB_OK;
@@ -367,16 +382,16 @@ static int launch_dc(dnb_ctx* c, cudaStream_t st, const SegDesc* seg, int nseg, 
 
 int launch_down_combine(dnb_ctx* c, cudaStream_t st, int type, const SegDesc* seg, int nseg, int k, int n_in, int n_out,
                         const float* act, const float* wts, const float* shcoef, bool has_shared,
-                        const float* residual, float* out, const float* act_perm) {
-    if (row_bytes(type, n_in) == 0 || n_in % 32 || nseg < 1 || nseg > 40) return DNB_DECLINED;
+                        const float* residual, float* out, const float* act_perm, int ntok) {
+    if (row_bytes(type, n_in) == 0 || n_in % 32 || nseg < 1 || nseg > 40 || ntok < 1 || ntok > 65535) return DNB_DECLINED;
     if ((nseg * n_in) % 4) act_perm = nullptr;  // the bulk copy moves multiples of 16 bytes
     int rc = upload_tables_b(c->device);
     if (rc != DNB_OK) return rc;
     const bool wide = (n_in / 32) >= 32;
 #define DNB_DC(TT)                                                                                                      \
     case TT:                                                                                                            \
-        return wide ? launch_dc<TT, 32>(c, st, seg, nseg, k, n_in, n_out, act, wts, shcoef, has_shared, residual, out, act_perm)  \
-                    : launch_dc<TT, 16>(c, st, seg, nseg, k, n_in, n_out, act, wts, shcoef, has_shared, residual, out, act_perm);
+        return wide ? launch_dc<TT, 32>(c, st, seg, nseg, k, n_in, n_out, act, wts, shcoef, has_shared, residual, out, act_perm, ntok)  \
+                    : launch_dc<TT, 16>(c, st, seg, nseg, k, n_in, n_out, act, wts, shcoef, has_shared, residual, out, act_perm, ntok);
     switch (type) {
         DNB_DC(T_Q4_K)
         DNB_DC(T_Q5_K)
@@ -418,6 +433,7 @@ static int launch_cfg(dnb_ctx* c, cudaStream_t st, const SegDesc* seg, const int
         DNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         smem_set[one ? 1 : 0] = smem;
     }
+    if (XSHARED && row_token && gps % kWarps) return DNB_DECLINED;  // a CTA must not straddle two segments' tokens
     const long warps = (long)nseg_max * gps;
     const int grid = (int)((warps + kWarps - 1) / kWarps);
     ProfScope prof_(c, st, pname);

@@ -772,6 +772,41 @@ int launch_route_tables(dnb_ctx* c, cudaStream_t st, const int32_t* sels, int nt
     return DNB_OK;
 }
 
+// ---- segment tables of a decode batch --------------------------------------------------
+// A few tokens (continuous batching): every (token, slot) pair is its own one-row segment,
+// token-major, the shared expert as slot k -- the layout the one-token decode kernels work
+// on, repeated per token.  One warp per token.
+__global__ void decode_batch_tables_kernel(const int32_t* __restrict__ sels, int nt, int k, const uint8_t* gate,
+                                           const uint8_t* up, const uint8_t* down, size_t eb_g, size_t eb_u, size_t eb_d,
+                                           const uint8_t* sg, const uint8_t* su, const uint8_t* sdn, SegDesc* seg_gu,
+                                           SegDesc* seg_dn, int32_t* row_token) {
+    const int t = blockIdx.x, s = threadIdx.x, per = k + (sg ? 1 : 0);
+    if (t >= nt || s >= per) return;
+    const uint32_t row = (uint32_t)(t * per + s);
+    if (s < k) {
+        const int ex = sels[(size_t)t * k + s];
+        seg_gu[row] = SegDesc{gate + (size_t)ex * eb_g, up + (size_t)ex * eb_u, 1u, row};
+        seg_dn[row] = SegDesc{down + (size_t)ex * eb_d, nullptr, 1u, row};
+    } else {
+        seg_gu[row] = SegDesc{sg, su, 1u, row};
+        seg_dn[row] = SegDesc{sdn, nullptr, 1u, row};
+    }
+    row_token[row] = t;
+}
+
+int launch_decode_batch_tables(dnb_ctx* c, cudaStream_t st, const int32_t* sels, int nt, int k, const Layer& L,
+                               Workspace& ws, bool fold_shared) {
+    ProfScope prof_(c, st, "decode_batch_tables");
+    decode_batch_tables_kernel<<<nt, 64, 0, st>>>(
+        sels, nt, k, (const uint8_t*)L.m[0].dev, (const uint8_t*)L.m[1].dev, (const uint8_t*)L.m[2].dev, L.m[0].expert_bytes,
+        L.m[1].expert_bytes, L.m[2].expert_bytes, (const uint8_t*)(fold_shared ? L.m[3].dev : nullptr),
+        (const uint8_t*)(fold_shared ? L.m[4].dev : nullptr), (const uint8_t*)(fold_shared ? L.m[5].dev : nullptr), ws.seg_gu,
+        ws.seg_dn, ws.row_token);
+    c->launches++;
+    DNB_CUDA(cudaGetLastError());
+    return DNB_OK;
+}
+
 // ---- weighted combine (kernels_dec_epi.cu:28-46 dno_dec_exp_sum;
 // moe_grouped_gpu.rs:540-565 scatter; qwen4exp.rs:12126-12216) --------------------
 // out[t][j] = sum over slots in ascending order of w[t][s] * h[pos[t][s]][j]

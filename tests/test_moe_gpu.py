@@ -56,7 +56,7 @@ def test_batch_equals_token_by_token(orc, small):
             assert np.array_equal(osel[0], bsel[t]) and np.array_equal(ow[0].view(np.uint32), bw[t].view(np.uint32))
             assert rel_err(one[0], batch[t]) <= 5e-4
     h = orc.synth_normal(SEED, 952, 1.0, nt * layers[0].e).reshape(nt, -1)
-    batch = c.moe_block(0, h)  # IQ3_XXS layer: tiled fp32 kernels for every chunk size > 1
+    batch = c.moe_block(0, h)  # IQ3_XXS layer, 21 and 4 tokens: the decode kernels over one-row segments both times
     sub = c.moe_block(0, h[[5, 3, 20, 11]])
     assert np.array_equal(sub.view(np.uint32), batch[[5, 3, 20, 11]].view(np.uint32))
 
@@ -277,3 +277,34 @@ def test_synth_device_equals_host(orc, small):
                 assert np.array_equal(dev, host[ex * eb:(ex + 1) * eb]), "type %d expert %d" % (ty, ex)
     finally:
         c.close()
+
+
+def test_router_topk_ties_and_many_survivors(orc):
+    """The selection rule on exact ties (larger value first, ties to the lower index) in the
+    shapes the top-k kernel treats differently: a few tied rows (threshold shortcut), every
+    row tied (more than 32 candidates reach the threshold: selection rounds), and one clear
+    winner among ties.  Selections and weights must equal the CPU rule's."""
+    from denno_beta_b200 import cuda as cu
+
+    e, ne, k, nt = 256, 128, 6, 9
+    x = orc.synth_normal(SEED, 991, 1.0, nt * e).reshape(nt, e)
+    base = orc.synth_normal(SEED, 992, 0.05, ne * e).reshape(ne, e)
+    cases = {}
+    w = base.copy()
+    w[40] = w[7]; w[90] = w[7]; w[91] = w[12]            # small groups of exactly equal logits
+    cases["few ties"] = w
+    cases["all tied"] = np.repeat(base[:1], ne, axis=0)   # 128 equal probabilities
+    w = np.repeat(base[:1], ne, axis=0)
+    w[77] = base[1] * 4.0
+    cases["one winner"] = w
+    for name, w in cases.items():
+        c = cu.CudaCtx(0)
+        try:
+            assert c.moe_config(1, e, 256, ne, k)
+            c.register_router(0, w, None, None, None)
+            sels, wts, _ = c.router_topk(0, x)
+            osels, owts, _ = orc.router(x, w, None, k)
+            assert np.array_equal(sels, osels), name
+            assert np.max(np.abs(wts - owts)) < 2e-6, name
+        finally:
+            c.close()
