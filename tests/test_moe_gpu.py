@@ -56,9 +56,11 @@ def test_batch_equals_token_by_token(orc, small):
             assert np.array_equal(osel[0], bsel[t]) and np.array_equal(ow[0].view(np.uint32), bw[t].view(np.uint32))
             assert rel_err(one[0], batch[t]) <= 5e-4
     h = orc.synth_normal(SEED, 952, 1.0, nt * layers[0].e).reshape(nt, -1)
-    batch = c.moe_block(0, h)  # IQ3_XXS layer, 21 and 4 tokens: the decode kernels over one-row segments both times
-    sub = c.moe_block(0, h[[5, 3, 20, 11]])
-    assert np.array_equal(sub.view(np.uint32), batch[[5, 3, 20, 11]].view(np.uint32))
+    batch = c.moe_block(0, h[:13])  # IQ3_XXS layer, 13 and 4 tokens: the decode kernels over one-row segments both times
+    sub = c.moe_block(0, h[[5, 3, 12, 11]])
+    assert np.array_equal(sub.view(np.uint32), batch[[5, 3, 12, 11]].view(np.uint32))
+    big = c.moe_block(0, np.concatenate([h, h]))  # 42 and 21 tokens: the tiled fp32 kernels both times
+    assert np.array_equal(big[:nt].view(np.uint32), c.moe_block(0, h).view(np.uint32))
 
 
 def test_tcgen05_grouped_gemm_matches_fp32_kernels(orc, small):
