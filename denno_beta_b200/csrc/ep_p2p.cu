@@ -174,13 +174,16 @@ ep_dispatch_kernel(const float* __restrict__ x, const int32_t* __restrict__ sels
             const float* xr = x + (size_t)(i / k) * e;
             uint16_t* hi = peers.xg_hi[d] + r * e;
             uint16_t* lo = peers.xg_lo[d] + r * e;
-            for (int c = tid * 4; c < e; c += 1024) {
+            for (int c = tid * 8; c < e; c += 2048) {  // 16-byte stores: the peer write is NVLink traffic
                 const float4 v = *reinterpret_cast<const float4*>(xr + c);
-                uint32_t h0, l0, h1, l1;
+                const float4 u = *reinterpret_cast<const float4*>(xr + c + 4);
+                uint32_t h0, l0, h1, l1, h2, l2, h3, l3;
                 ep_split2(v.x, v.y, h0, l0);
                 ep_split2(v.z, v.w, h1, l1);
-                *reinterpret_cast<uint2*>(hi + c) = make_uint2(h0, h1);
-                *reinterpret_cast<uint2*>(lo + c) = make_uint2(l0, l1);
+                ep_split2(u.x, u.y, h2, l2);
+                ep_split2(u.z, u.w, h3, l3);
+                *reinterpret_cast<uint4*>(hi + c) = make_uint4(h0, h1, h2, h3);
+                *reinterpret_cast<uint4*>(lo + c) = make_uint4(l0, l1, l2, l3);
             }
             if (tid == 0) peers.recv_slot[d][r] = (me << 24) | i;  // who owns the token, and which (token, slot) row
         }
