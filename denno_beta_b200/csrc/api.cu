@@ -834,9 +834,13 @@ int dnb_moe_block(dnb_ctx* c, int layer, const float* h, int nt, float* out, int
     const bool routing = sels_out || wts_out;
     rc = run_graphed(c, GraphKey{routing ? 3 : 2, layer, nt, nullptr, nullptr}, [&]() -> int {
         DNB_CUDA(cudaMemcpyAsync(w.hin, w.pinned_in, bytes, cudaMemcpyHostToDevice, c->stream));
-        const int r = block_dev(c, layer, w.hin, nt, w.out);
+        // A few tokens: the last kernel stores the result rows straight into the pinned host
+        // buffer (it is device-addressable), which saves a copy node and its dependency edge
+        // on a call that lasts tens of microseconds.  Larger results go through HBM and one copy.
+        const bool direct = nt <= 8;
+        const int r = block_dev(c, layer, w.hin, nt, direct ? w.pinned_out : w.out);
         if (r) return r;
-        DNB_CUDA(cudaMemcpyAsync(w.pinned_out, w.out, bytes, cudaMemcpyDeviceToHost, c->stream));
+        if (!direct) DNB_CUDA(cudaMemcpyAsync(w.pinned_out, w.out, bytes, cudaMemcpyDeviceToHost, c->stream));
         if (routing) {
             DNB_CUDA(cudaMemcpyAsync(w.pinned_sels, w.sels, (size_t)nt * M.k * 4, cudaMemcpyDeviceToHost, c->stream));
             DNB_CUDA(cudaMemcpyAsync(w.pinned_wts, w.wts, (size_t)nt * M.k * 4, cudaMemcpyDeviceToHost, c->stream));
