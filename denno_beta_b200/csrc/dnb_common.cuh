@@ -16,14 +16,18 @@ namespace dnb {
 
 // ---- block formats ---------------------------------------------------------
 constexpr int T_F32 = 0, T_Q5_1 = 7, T_Q8_0 = 8, T_Q4_K = 12, T_Q5_K = 13, T_Q6_K = 14, T_IQ3_XXS = 18;
+// The block types of real checkpoints' remaining tensors (exp_iq.rs:390-400, cuda.rs:7364-7373):
+// served by the tiled kernels and the sequential checker, not by the decode fast kernels.
+constexpr int T_Q4_0 = 2, T_IQ4_NL = 20, T_IQ3_S = 21, T_IQ2_S = 22, T_IQ4_XS = 23, T_Q2_0 = 42;
 
 __host__ __device__ constexpr int type_size(int t) {
     return t == T_Q4_K ? 144 : t == T_IQ3_XXS ? 98 : t == T_Q6_K ? 210 : t == T_Q8_0 ? 34 : t == T_Q5_K ? 176
-         : t == T_Q5_1 ? 24 : t == T_F32 ? 4 : 0;
+         : t == T_Q5_1 ? 24 : t == T_F32 ? 4 : t == T_Q4_0 ? 18 : t == T_IQ4_NL ? 18 : t == T_IQ3_S ? 110
+         : t == T_IQ2_S ? 82 : t == T_IQ4_XS ? 136 : t == T_Q2_0 ? 18 : 0;
 }
 __host__ __device__ constexpr int block_elems(int t) {
-    return (t == T_Q4_K || t == T_IQ3_XXS || t == T_Q6_K || t == T_Q5_K) ? 256
-         : (t == T_Q8_0 || t == T_Q5_1) ? 32 : t == T_F32 ? 1 : 0;
+    return (t == T_Q4_K || t == T_IQ3_XXS || t == T_Q6_K || t == T_Q5_K || t == T_IQ3_S || t == T_IQ2_S || t == T_IQ4_XS) ? 256
+         : (t == T_Q8_0 || t == T_Q5_1 || t == T_Q4_0 || t == T_IQ4_NL) ? 32 : t == T_Q2_0 ? 64 : t == T_F32 ? 1 : 0;
 }
 inline bool type_supported(int t) { return type_size(t) != 0 && t != T_F32; }
 // Bytes of one row of n_in elements, or 0 when n_in is not a whole number of blocks.

@@ -20,10 +20,19 @@ namespace dnb {
 __device__ __forceinline__ float h2f(uint16_t bits) { return __half2float(__ushort_as_half(bits)); }
 __device__ __forceinline__ uint32_t ld16(const uint8_t* p) { return *reinterpret_cast<const uint16_t*>(p); }
 
-// Shared lookup tables of the IQ formats (copied into shared memory per CTA).
+// Shared lookup tables of the IQ formats (copied into shared memory per CTA).  The kernels
+// pass one pointer; what lies behind it depends on the format.
 struct IqLut {
     uint32_t grid3xxs[256];
 };
+struct IqLut3s { uint32_t grid[512]; };
+struct IqLut2s { uint64_t grid[1024]; };
+struct IqLut4 { int8_t kv[16]; };
+template <int T>
+__host__ __device__ constexpr int lut_bytes_of() {
+    return T == T_IQ3_XXS ? (int)sizeof(IqLut) : T == T_IQ3_S ? (int)sizeof(IqLut3s) : T == T_IQ2_S ? (int)sizeof(IqLut2s)
+         : (T == T_IQ4_NL || T == T_IQ4_XS) ? (int)sizeof(IqLut4) : 0;
+}
 
 // (unit, slot) of element i of a row, per format.
 template <int T>
@@ -152,6 +161,101 @@ __device__ __forceinline__ void decode_unit(const uint8_t* row, int u, const IqL
             const uint32_t v = ld16(blk + 2 + 2 * p);
             w[2 * p] = (float)(int)(int8_t)(v & 0xFF) * d;
             w[2 * p + 1] = (float)(int)(int8_t)(v >> 8) * d;
+        }
+    } else if constexpr (T == T_Q4_0) {  // kquant.rs:357-365
+        const uint8_t* blk = row + u * 18;
+        const float d = h2f(ld16(blk));
+#pragma unroll
+        for (int p = 0; p < 8; ++p) {
+            const uint32_t v = ld16(blk + 2 + 2 * p);
+            w[2 * p] = (float)((int)(v & 0xF) - 8) * d;
+            w[2 * p + 1] = (float)((int)((v >> 8) & 0xF) - 8) * d;
+            w[16 + 2 * p] = (float)((int)((v >> 4) & 0xF) - 8) * d;
+            w[16 + 2 * p + 1] = (float)((int)(v >> 12) - 8) * d;
+        }
+    } else if constexpr (T == T_Q2_0) {  // kquant.rs:347-354: 64 elements per block, two units
+        const uint8_t* blk = row + (u >> 1) * 18;
+        const float d = h2f(ld16(blk));
+        const uint8_t* q = blk + 2 + 8 * (u & 1);
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+            const uint32_t v = ld16(q + 2 * p);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) w[8 * p + j] = (float)((int)((v >> (2 * j)) & 3) - 1) * d;
+        }
+    } else if constexpr (T == T_IQ4_NL) {  // kquant.rs:842-853
+        const IqLut4* l4 = reinterpret_cast<const IqLut4*>(lut);
+        const uint8_t* blk = row + u * 18;
+        const float d = h2f(ld16(blk));
+#pragma unroll
+        for (int p = 0; p < 8; ++p) {
+            const uint32_t v = ld16(blk + 2 + 2 * p);
+            w[2 * p] = d * (float)l4->kv[v & 0xF];
+            w[2 * p + 1] = d * (float)l4->kv[(v >> 8) & 0xF];
+            w[16 + 2 * p] = d * (float)l4->kv[(v >> 4) & 0xF];
+            w[16 + 2 * p + 1] = d * (float)l4->kv[v >> 12];
+        }
+    } else if constexpr (T == T_IQ4_XS) {  // kquant.rs:856-872
+        const IqLut4* l4 = reinterpret_cast<const IqLut4*>(lut);
+        const int b = u >> 3, ib = u & 7;
+        const uint8_t* blk = row + b * 136;
+        const float d = h2f(ld16(blk));
+        const uint32_t scales_h = ld16(blk + 2);
+        const uint32_t sl = blk[4 + (ib >> 1)];
+        const int ls = (int)((sl >> (4 * (ib & 1))) & 0xF) | (int)(((scales_h >> (2 * ib)) & 3) << 4);
+        const float dl = d * (float)(ls - 32);
+        const uint8_t* q = blk + 8 + 16 * ib;
+#pragma unroll
+        for (int p = 0; p < 8; ++p) {
+            const uint32_t v = ld16(q + 2 * p);
+            w[2 * p] = dl * (float)l4->kv[v & 0xF];
+            w[2 * p + 1] = dl * (float)l4->kv[(v >> 8) & 0xF];
+            w[16 + 2 * p] = dl * (float)l4->kv[(v >> 4) & 0xF];
+            w[16 + 2 * p + 1] = dl * (float)l4->kv[v >> 12];
+        }
+    } else if constexpr (T == T_IQ3_S) {  // kquant.rs:683-735
+        const IqLut3s* l3 = reinterpret_cast<const IqLut3s*>(lut);
+        const int b = u >> 3, ib = u & 7;
+        const uint8_t* blk = row + b * 110;
+        const float d = h2f(ld16(blk));
+        const uint8_t *qs = blk + 2, *qh = blk + 66, *signs = blk + 74, *scales = blk + 106;
+        const uint32_t scb = scales[ib >> 1];
+        const float db = d * (1.0f + 2.0f * (float)((ib & 1) ? (scb >> 4) : (scb & 0xF)));
+        const uint32_t qhb = qh[ib];
+#pragma unroll
+        for (int l = 0; l < 4; ++l) {
+            const uint32_t idx = ld16(qs + 8 * ib + 2 * l);
+            const uint32_t g1 = l3->grid[(idx & 0xFF) | ((qhb << (8 - 2 * l)) & 256u)];
+            const uint32_t g2 = l3->grid[(idx >> 8) | ((qhb << (7 - 2 * l)) & 256u)];
+            const uint32_t sg = signs[4 * ib + l];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float v0 = db * (float)((g1 >> (8 * j)) & 0xFF);
+                const float v1 = db * (float)((g2 >> (8 * j)) & 0xFF);
+                w[8 * l + j] = (sg >> j) & 1 ? -v0 : v0;
+                w[8 * l + 4 + j] = (sg >> (j + 4)) & 1 ? -v1 : v1;
+            }
+        }
+    } else if constexpr (T == T_IQ2_S) {  // kquant.rs:632-656
+        const IqLut2s* l2 = reinterpret_cast<const IqLut2s*>(lut);
+        const int b = u >> 3, ib = u & 7;
+        const uint8_t* blk = row + b * 82;
+        const float d = h2f(ld16(blk));
+        const uint8_t *qs = blk + 2, *signs = blk + 34, *qh = blk + 66, *scales = blk + 74;
+        const uint32_t sc = scales[ib];
+        const float db0 = d * (0.5f + (float)(sc & 0xF)) * 0.25f, db1 = d * (0.5f + (float)(sc >> 4)) * 0.25f;
+        const uint32_t qhb = qh[ib];
+#pragma unroll
+        for (int l = 0; l < 4; ++l) {
+            const uint32_t idx = (uint32_t)qs[4 * ib + l] | ((qhb << (8 - 2 * l)) & 0x300u);
+            const uint64_t g = l2->grid[idx];
+            const uint32_t sg = signs[4 * ib + l];
+            const float db = l < 2 ? db0 : db1;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float v = db * (float)((uint32_t)(g >> (8 * j)) & 0xFF);
+                w[8 * l + j] = (sg >> j) & 1 ? -v : v;
+            }
         }
     } else if constexpr (T == T_Q5_1) {  // kquant.rs:394-406
         const uint8_t* blk = row + u * 24;

@@ -18,14 +18,37 @@
 namespace dnb {
 
 __constant__ uint32_t c_iq3xxs_grid[256];
+__constant__ uint32_t c_iq3s_grid[512];
+__constant__ unsigned long long c_iq2s_grid[1024];
+__constant__ int8_t c_kvalues_iq4nl[16];
 static bool g_tables_uploaded[64] = {false};
 
 static int upload_tables(int device) {
     if (device < 0 || device >= 64) return DNB_ERR_ARG;
     if (g_tables_uploaded[device]) return DNB_OK;
     DNB_CUDA(cudaMemcpyToSymbol(c_iq3xxs_grid, dnb_iq3xxs_grid, sizeof(c_iq3xxs_grid)));
+    DNB_CUDA(cudaMemcpyToSymbol(c_iq3s_grid, dnb_iq3s_grid, sizeof(c_iq3s_grid)));
+    DNB_CUDA(cudaMemcpyToSymbol(c_iq2s_grid, dnb_iq2s_grid, sizeof(c_iq2s_grid)));
+    DNB_CUDA(cudaMemcpyToSymbol(c_kvalues_iq4nl, dnb_kvalues_iq4nl, sizeof(c_kvalues_iq4nl)));
     g_tables_uploaded[device] = true;
     return DNB_OK;
+}
+
+// The CTA's copy of the format's codebook, behind the one pointer decode_unit takes.
+template <int T>
+__device__ __forceinline__ void fill_lut(IqLut* lut, int tid, int nthr) {
+    if constexpr (T == T_IQ3_XXS) {
+        for (int i = tid; i < 256; i += nthr) lut->grid3xxs[i] = c_iq3xxs_grid[i];
+    } else if constexpr (T == T_IQ3_S) {
+        IqLut3s* l = reinterpret_cast<IqLut3s*>(lut);
+        for (int i = tid; i < 512; i += nthr) l->grid[i] = c_iq3s_grid[i];
+    } else if constexpr (T == T_IQ2_S) {
+        IqLut2s* l = reinterpret_cast<IqLut2s*>(lut);
+        for (int i = tid; i < 1024; i += nthr) l->grid[i] = c_iq2s_grid[i];
+    } else if constexpr (T == T_IQ4_NL || T == T_IQ4_XS) {
+        IqLut4* l = reinterpret_cast<IqLut4*>(lut);
+        if (tid < 16) l->kv[tid] = c_kvalues_iq4nl[tid];
+    }
 }
 
 __device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
@@ -71,7 +94,7 @@ seg_matmul_kernel(const SegDesc* __restrict__ seg, const int32_t* __restrict__ n
 
     extern __shared__ __align__(16) uint8_t smem[];
     IqLut* lut = reinterpret_cast<IqLut*>(smem);
-    constexpr int lut_bytes = (T == T_IQ3_XXS) ? (int)sizeof(IqLut) : 0;
+    constexpr int lut_bytes = lut_bytes_of<T>();
     const int tile_bytes = (tile_rows * rb + 15) & ~15;
     uint8_t* wa = smem + lut_bytes;
     uint8_t* wb = wa + tile_bytes;
@@ -79,9 +102,7 @@ seg_matmul_kernel(const SegDesc* __restrict__ seg, const int32_t* __restrict__ n
     float* xs = reinterpret_cast<float*>(xs4);
 
     const int tid = threadIdx.x;
-    if constexpr (T == T_IQ3_XXS) {
-        for (int i = tid; i < 256; i += kThreads) lut->grid3xxs[i] = c_iq3xxs_grid[i];
-    }
+    fill_lut<T>(lut, tid, kThreads);
     stage_bytes(wa, sd.wa + (size_t)r0 * rb, rows * rb, tid, kThreads);
     if constexpr (FUSED) stage_bytes(wb, sd.wb + (size_t)r0 * rb, rows * rb, tid, kThreads);
 
@@ -182,7 +203,7 @@ static int launch_cfg(dnb_ctx* c, cudaStream_t st, const SegDesc* seg, const int
     int tile_rows = NGRP * rounds;
     if (tile_rows > n_out) tile_rows = ((n_out + NGRP - 1) / NGRP) * NGRP;
     const int tile_bytes = (tile_rows * rb + 15) & ~15;
-    const size_t smem = (T == T_IQ3_XXS ? sizeof(IqLut) : 0) + (size_t)(FUSED ? 2 : 1) * tile_bytes +
+    const size_t smem = (size_t)lut_bytes_of<T>() + (size_t)(FUSED ? 2 : 1) * tile_bytes +
                         (size_t)TT * n_in * sizeof(float);
     auto kern = seg_matmul_kernel<T, FUSED, LPR, TT>;
     static size_t smem_set = 0;
@@ -244,6 +265,12 @@ int launch_seg_matmul(dnb_ctx* c, cudaStream_t st, int type, bool fused, const S
         DNB_DISPATCH(T_IQ3_XXS)
         DNB_DISPATCH(T_Q8_0)
         DNB_DISPATCH(T_Q5_1)
+        DNB_DISPATCH(T_Q4_0)
+        DNB_DISPATCH(T_IQ4_NL)
+        DNB_DISPATCH(T_IQ4_XS)
+        DNB_DISPATCH(T_IQ3_S)
+        DNB_DISPATCH(T_IQ2_S)
+        DNB_DISPATCH(T_Q2_0)
         default:
             set_error("seg_matmul: no kernel for ggml type %d", type);
             return DNB_DECLINED;
@@ -260,9 +287,10 @@ int launch_seg_matmul(dnb_ctx* c, cudaStream_t st, int type, bool fused, const S
 template <int T>
 __global__ void gemv_seq_kernel(const uint8_t* __restrict__ w, const float* __restrict__ x, float* __restrict__ out,
                                 int n_in, int n_out, int rb) {
-    __shared__ IqLut lut;
-    if constexpr (T == T_IQ3_XXS) {
-        for (int i = threadIdx.x; i < 256; i += blockDim.x) lut.grid3xxs[i] = c_iq3xxs_grid[i];
+    __shared__ __align__(16) uint8_t lut_raw[lut_bytes_of<T>() ? lut_bytes_of<T>() : 16];
+    IqLut& lut = *reinterpret_cast<IqLut*>(lut_raw);
+    if constexpr (lut_bytes_of<T>() != 0) {
+        fill_lut<T>(&lut, threadIdx.x, blockDim.x);
         __syncthreads();
     }
     const int r = blockIdx.x * blockDim.x + threadIdx.x;
@@ -274,7 +302,7 @@ __global__ void gemv_seq_kernel(const uint8_t* __restrict__ w, const float* __re
     // formats whose unit is not 32 consecutive elements the whole block is
     // decoded into a local buffer first.
     constexpr int BE = block_elems(T);
-    if constexpr (BE == 32) {
+    if constexpr (BE == 32 || BE == 64) {  // a unit is 32 consecutive elements of the row
         for (int u = 0; u < nunits; ++u) {
             float wv[32];
             decode_unit<T>(row, u, &lut, wv);
@@ -325,6 +353,12 @@ int launch_gemv_seq(dnb_ctx* c, cudaStream_t st, int type, const uint8_t* w, con
         case T_IQ3_XXS: gemv_seq_kernel<T_IQ3_XXS><<<grid, thr, 0, st>>>(w, x, out, n_in, n_out, rb); break;
         case T_Q8_0: gemv_seq_kernel<T_Q8_0><<<grid, thr, 0, st>>>(w, x, out, n_in, n_out, rb); break;
         case T_Q5_1: gemv_seq_kernel<T_Q5_1><<<grid, thr, 0, st>>>(w, x, out, n_in, n_out, rb); break;
+        case T_Q4_0: gemv_seq_kernel<T_Q4_0><<<grid, thr, 0, st>>>(w, x, out, n_in, n_out, rb); break;
+        case T_IQ4_NL: gemv_seq_kernel<T_IQ4_NL><<<grid, thr, 0, st>>>(w, x, out, n_in, n_out, rb); break;
+        case T_IQ4_XS: gemv_seq_kernel<T_IQ4_XS><<<grid, thr, 0, st>>>(w, x, out, n_in, n_out, rb); break;
+        case T_IQ3_S: gemv_seq_kernel<T_IQ3_S><<<grid, thr, 0, st>>>(w, x, out, n_in, n_out, rb); break;
+        case T_IQ2_S: gemv_seq_kernel<T_IQ2_S><<<grid, thr, 0, st>>>(w, x, out, n_in, n_out, rb); break;
+        case T_Q2_0: gemv_seq_kernel<T_Q2_0><<<grid, thr, 0, st>>>(w, x, out, n_in, n_out, rb); break;
         default: set_error("gemv_seq: no kernel for ggml type %d", type); return DNB_DECLINED;
     }
     c->launches++;

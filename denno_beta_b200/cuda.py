@@ -15,10 +15,13 @@ from ._lib import DnbError, check
 
 # ggml type ids (kquant.rs:72-104)
 Q5_1, Q8_0, Q4_K, Q5_K, Q6_K, IQ3_XXS = 7, 8, 12, 13, 14, 18
+Q4_0, IQ4_NL, IQ3_S, IQ2_S, IQ4_XS, Q2_0 = 2, 20, 21, 22, 23, 42
 GATE, UP, DOWN, SHARED_GATE, SHARED_UP, SHARED_DOWN = range(6)
 
-TYPE_SIZE = {Q5_1: 24, Q8_0: 34, Q4_K: 144, Q5_K: 176, Q6_K: 210, IQ3_XXS: 98}
-BLOCK_ELEMS = {Q5_1: 32, Q8_0: 32, Q4_K: 256, Q5_K: 256, Q6_K: 256, IQ3_XXS: 256}
+TYPE_SIZE = {Q5_1: 24, Q8_0: 34, Q4_K: 144, Q5_K: 176, Q6_K: 210, IQ3_XXS: 98,
+             Q4_0: 18, IQ4_NL: 18, IQ3_S: 110, IQ2_S: 82, IQ4_XS: 136, Q2_0: 18}
+BLOCK_ELEMS = {Q5_1: 32, Q8_0: 32, Q4_K: 256, Q5_K: 256, Q6_K: 256, IQ3_XXS: 256,
+               Q4_0: 32, IQ4_NL: 32, IQ3_S: 256, IQ2_S: 256, IQ4_XS: 256, Q2_0: 64}
 
 
 def row_bytes(ty, n_in):

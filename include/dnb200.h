@@ -44,6 +44,15 @@ extern "C" {
 #define DNB_GGML_Q5_K 13
 #define DNB_GGML_Q6_K 14
 #define DNB_GGML_IQ3_XXS 18
+/* The block types of a real checkpoint's remaining tensors (exp_iq.rs:390-400,
+ * cuda.rs:7364-7373): decoded by the tiled kernels and the sequential checker; calls with
+ * them take those kernels instead of the decode fast kernels. */
+#define DNB_GGML_Q4_0 2
+#define DNB_GGML_IQ4_NL 20
+#define DNB_GGML_IQ3_S 21
+#define DNB_GGML_IQ2_S 22
+#define DNB_GGML_IQ4_XS 23
+#define DNB_GGML_Q2_0 42
 
 /* matrix slots of a MoE layer */
 #define DNB_MAT_GATE 0

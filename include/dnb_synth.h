@@ -34,6 +34,12 @@
 #define DNB_TYPE_Q5_K 13
 #define DNB_TYPE_Q6_K 14
 #define DNB_TYPE_IQ3_XXS 18
+#define DNB_TYPE_Q4_0 2
+#define DNB_TYPE_IQ4_NL 20
+#define DNB_TYPE_IQ3_S 21
+#define DNB_TYPE_IQ2_S 22
+#define DNB_TYPE_IQ4_XS 23
+#define DNB_TYPE_Q2_0 42
 
 #define DNB_SYNTH_NORMAL_SALT 0x6E6F726D616C2121ull
 
@@ -92,6 +98,10 @@ DNB_HD int dnb_synth_type_size(int type) {
         case DNB_TYPE_Q5_K: return 176;
         case DNB_TYPE_Q6_K: return 210;
         case DNB_TYPE_IQ3_XXS: return 98;
+        case DNB_TYPE_Q4_0: case DNB_TYPE_IQ4_NL: case DNB_TYPE_Q2_0: return 18;
+        case DNB_TYPE_IQ3_S: return 110;
+        case DNB_TYPE_IQ2_S: return 82;
+        case DNB_TYPE_IQ4_XS: return 136;
         default: return 0;
     }
 }
@@ -99,8 +109,10 @@ DNB_HD int dnb_synth_type_size(int type) {
 DNB_HD int dnb_synth_block_size(int type) {
     switch (type) {
         case DNB_TYPE_F32: return 1;
-        case DNB_TYPE_Q5_1: case DNB_TYPE_Q8_0: return 32;
-        case DNB_TYPE_Q4_K: case DNB_TYPE_Q5_K: case DNB_TYPE_Q6_K: case DNB_TYPE_IQ3_XXS: return 256;
+        case DNB_TYPE_Q5_1: case DNB_TYPE_Q8_0: case DNB_TYPE_Q4_0: case DNB_TYPE_IQ4_NL: return 32;
+        case DNB_TYPE_Q2_0: return 64;
+        case DNB_TYPE_Q4_K: case DNB_TYPE_Q5_K: case DNB_TYPE_Q6_K: case DNB_TYPE_IQ3_XXS:
+        case DNB_TYPE_IQ3_S: case DNB_TYPE_IQ2_S: case DNB_TYPE_IQ4_XS: return 256;
         default: return 0;
     }
 }
@@ -127,6 +139,8 @@ DNB_HD void dnb_synth_fix_block(int type, uint64_t key, uint64_t b, uint8_t* blk
             blk[2] = (uint8_t)d2; blk[3] = (uint8_t)(d2 >> 8);
             break;
         case DNB_TYPE_IQ3_XXS: case DNB_TYPE_Q8_0:
+        case DNB_TYPE_Q4_0: case DNB_TYPE_IQ4_NL: case DNB_TYPE_IQ3_S: case DNB_TYPE_IQ2_S: case DNB_TYPE_IQ4_XS:
+        case DNB_TYPE_Q2_0:  /* d first in all of these, everything else uniform bytes */
             blk[0] = (uint8_t)d; blk[1] = (uint8_t)(d >> 8);
             break;
         case DNB_TYPE_Q6_K:

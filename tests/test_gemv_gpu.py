@@ -11,7 +11,7 @@ from helpers import SEED, rel_err
 
 pytestmark = pytest.mark.gpu
 
-TYPES = ["Q4_K", "IQ3_XXS", "Q6_K", "Q8_0", "Q5_K", "Q5_1"]
+TYPES = ["Q4_K", "IQ3_XXS", "Q6_K", "Q8_0", "Q5_K", "Q5_1", "Q4_0", "IQ4_NL", "IQ4_XS", "IQ3_S", "IQ2_S", "Q2_0"]
 
 
 @pytest.fixture(scope="module")

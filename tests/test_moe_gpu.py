@@ -310,3 +310,27 @@ def test_router_topk_ties_and_many_survivors(orc):
             assert np.max(np.abs(wts - owts)) < 2e-6, name
         finally:
             c.close()
+
+
+@pytest.mark.parametrize("nt", [1, 4, 40])
+def test_block_remaining_gguf_formats(orc, nt):
+    """The block types real checkpoints use for their other tensors (IQ4_XS / IQ3_S,
+    IQ4_NL / IQ2_S, Q4_0 / Q2_0 as gate+up / down): decode, a small batch and a chunk."""
+    from denno_beta_b200 import cuda as cu
+
+    e, ff, ne, k = 512, 256, 16, 3
+    c = cu.CudaCtx(0)
+    try:
+        assert c.moe_config(3, e, ff, ne, k)
+        layers = [make_layer(orc, c, 0, orc.IQ4_XS, e, ff, ne, k, ty_down=orc.IQ3_S, bias=True),
+                  make_layer(orc, c, 1, orc.IQ4_NL, e, ff, ne, k, ty_down=orc.IQ2_S, gate_row=True),
+                  make_layer(orc, c, 2, orc.Q4_0, e, ff, ne, k, ty_down=orc.Q2_0, shared=False)]
+        for li, L in enumerate(layers):
+            h = orc.synth_normal(SEED, 1200 + 10 * li + nt, 1.0, nt * e).reshape(nt, e)
+            out, sels, wts = c.moe_block(li, h, want_routing=True)
+            err, redo = check_block(orc, L, h, out, sels, wts)
+            assert err <= 1e-3 and redo == 0, "layer %d nt %d: %.3g" % (li, nt, err)
+            assert np.array_equal(out.view(np.uint32), c.moe_block(li, h).view(np.uint32))
+        assert c.device_status() == 0
+    finally:
+        c.close()
