@@ -822,6 +822,45 @@ combine_kernel(const float* __restrict__ hrow, const int32_t* __restrict__ pos, 
         pw[threadIdx.x] = wts ? wts[(size_t)t * k + threadIdx.x] : 1.0f;
     }
     __syncthreads();
+    if ((e & 3) == 0) {
+        // four columns per thread; the rows of up to eight slots are requested before the
+        // first is used (the sum itself stays one slot after the other, ascending)
+        for (int j = threadIdx.x * 4; j < e; j += 1024) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int s0 = 0; s0 < k; s0 += 8) {
+                float4 v[8];
+#pragma unroll
+                for (int q = 0; q < 8; ++q)
+                    if (s0 + q < k) v[q] = *reinterpret_cast<const float4*>(hrow + (size_t)prow[s0 + q] * e + j);
+#pragma unroll
+                for (int q = 0; q < 8; ++q)
+                    if (s0 + q < k) {
+                        const float w = pw[s0 + q];
+                        acc.x = __fadd_rn(acc.x, __fmul_rn(w, v[q].x));
+                        acc.y = __fadd_rn(acc.y, __fmul_rn(w, v[q].y));
+                        acc.z = __fadd_rn(acc.z, __fmul_rn(w, v[q].z));
+                        acc.w = __fadd_rn(acc.w, __fmul_rn(w, v[q].w));
+                    }
+            }
+            if (sh) {
+                const float4 v = *reinterpret_cast<const float4*>(sh + (size_t)t * e + j);
+                if (shcoef) {
+                    const float c = shcoef[t];
+                    acc.x = __fadd_rn(acc.x, __fmul_rn(v.x, c));
+                    acc.y = __fadd_rn(acc.y, __fmul_rn(v.y, c));
+                    acc.z = __fadd_rn(acc.z, __fmul_rn(v.z, c));
+                    acc.w = __fadd_rn(acc.w, __fmul_rn(v.w, c));
+                } else {
+                    acc.x = __fadd_rn(acc.x, v.x);
+                    acc.y = __fadd_rn(acc.y, v.y);
+                    acc.z = __fadd_rn(acc.z, v.z);
+                    acc.w = __fadd_rn(acc.w, v.w);
+                }
+            }
+            *reinterpret_cast<float4*>(out + (size_t)t * e + j) = acc;
+        }
+        return;
+    }
     for (int j = threadIdx.x; j < e; j += 256) {
         float acc = 0.f;
         for (int s = 0; s < k; ++s) acc = __fadd_rn(acc, __fmul_rn(pw[s], hrow[(size_t)prow[s] * e + j]));
