@@ -259,8 +259,8 @@ gemv_bulk_kernel(const SegDesc* __restrict__ seg, const int32_t* __restrict__ ns
 // and R threads then add the segments up in ascending order with separate multiply
 // and add roundings -- the order of kernels_dec_epi.cu:28-46 / qwen4exp.rs:12126-
 // 12216.  No partial results go through global memory and nothing is atomic.
-constexpr int kDcWarps = 16;  // warps per CTA of the down+combine kernel
-constexpr int kDcRows = 8;    // output rows per CTA
+constexpr int kDcWarps = 8;   // warps per CTA of the down+combine kernel
+constexpr int kDcRows = 4;    // output rows per CTA
 
 template <int T, int LPR>
 __global__ void __launch_bounds__(kDcWarps * 32)
