@@ -275,6 +275,18 @@ int launch_topk(dnb_ctx* c, cudaStream_t st, const float* logits, int nt, int ne
 // follow the routed rows (row nt*k + t reads token t).
 int launch_route_tables(dnb_ctx* c, cudaStream_t st, const int32_t* sels, int nt, int k, int ne, const Layer& L,
                         Workspace& ws, bool fold_shared = false);
+// The opt-in dynamic shared memory limit is an attribute of a kernel PER DEVICE: what was
+// granted is remembered per device, so a process that drives several GPUs sets it on each.
+struct SmemGrant { size_t got[64] = {0}; };
+template <class K>
+inline cudaError_t grant_smem(SmemGrant& g, int device, K kern, size_t bytes) {
+    if (device < 0 || device >= 64) return cudaErrorInvalidDevice;
+    if (bytes <= g.got[device]) return cudaSuccess;
+    const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e == cudaSuccess) g.got[device] = bytes;
+    return e;
+}
+
 // tcgen05 grouped GEMM of prefill (grouped_umma.cu)
 int umma_make_maps(void* hi, void* lo, uint64_t rows, uint64_t cols, UmmaMaps* out);
 int launch_gather_split(dnb_ctx* c, cudaStream_t st, const float* x, int ldx, const int32_t* row_token, int rows, int e,

@@ -405,12 +405,9 @@ extern "C" int dnb_ep_block_dev(dnb_ctx* c, int layer, const float* h_dev, int n
     const uint32_t seq = ++s->seq;
     const int words = (nt + 31) >> 5;
     const size_t plan_smem = ((size_t)M.ne * words + (size_t)M.ne) * 4;
-    static size_t plan_set = 0;
+    static SmemGrant plan_grant;
     if (plan_smem > 200 * 1024) return DNB_DECLINED;
-    if (plan_smem > plan_set) {
-        DNB_CUDA(cudaFuncSetAttribute(ep_plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan_smem));
-        plan_set = plan_smem;
-    }
+    DNB_CUDA(grant_smem(plan_grant, c->device, ep_plan_kernel, plan_smem));
     {
         ProfScope p_(c, st, "ep_plan");
         ep_plan_kernel<<<1, 1024, plan_smem, st>>>(w.sels, nt, M.k, M.ne, s->n_local, s->world, s->rank, seq, s->peers, s->send_row);

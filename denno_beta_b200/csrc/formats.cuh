@@ -22,8 +22,16 @@ __device__ __forceinline__ uint32_t ld16(const uint8_t* p) { return *reinterpret
 
 // Shared lookup tables of the IQ formats (copied into shared memory per CTA).  The kernels
 // pass one pointer; what lies behind it depends on the format.
+// The IQ3_XXS codebook is held kLutRep times, entry i of copy r at word i * kLutRep + r: a
+// lane reads copy (lane & 7), so the 32 random lookups of a warp spread over the banks
+// instead of piling up on the few banks a single 1 KB table offers them.
+constexpr int kLutRep = 16;
 struct IqLut {
-    uint32_t grid3xxs[256];
+    uint32_t grid3xxs[256 * kLutRep];
+    __device__ __forceinline__ uint32_t at(uint32_t idx, int rep) const { return grid3xxs[idx * kLutRep + rep]; }
+    __device__ __forceinline__ void fill(const uint32_t* table, int tid, int nthr) {
+        for (int i = tid; i < 256 * kLutRep; i += nthr) grid3xxs[i] = table[i / kLutRep];
+    }
 };
 struct IqLut3s { uint32_t grid[512]; };
 struct IqLut2s { uint64_t grid[1024]; };
@@ -121,7 +129,8 @@ __device__ __forceinline__ void decode_unit(const uint8_t* row, int u, const IqL
             const uint32_t idx = ld16(blk + 2 + 8 * ib + 2 * l);
             const uint32_t code = (aux >> (7 * l)) & 127;
             const uint32_t sg = code | ((__popc(code) & 1) << 7);  // KSIGNS_IQ2XS[code]: bit 7 = parity
-            const uint32_t g1 = lut->grid3xxs[idx & 0xFF], g2 = lut->grid3xxs[idx >> 8];
+            const int rep = (int)(threadIdx.x & (kLutRep - 1));
+            const uint32_t g1 = lut->at(idx & 0xFF, rep), g2 = lut->at(idx >> 8, rep);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const float v0 = db * (float)((g1 >> (8 * j)) & 0xFF);
@@ -369,7 +378,8 @@ __device__ __forceinline__ float unit_dot(const uint8_t* row, int u, const IqLut
             const uint32_t idx = ld16(blk + 2 + 8 * ib + 2 * l);
             const uint32_t code = (aux >> (7 * l)) & 127u;
             const uint32_t sg = code | ((__popc(code) & 1u) << 7);
-            const uint32_t g1 = lut->grid3xxs[idx & 0xFFu], g2 = lut->grid3xxs[idx >> 8];
+            const int rep = (int)(threadIdx.x & (kLutRep - 1));
+            const uint32_t g1 = lut->at(idx & 0xFFu, rep), g2 = lut->at(idx >> 8, rep);
             uint32_t p[4];
             p[0] = __byte_perm(g1, 0x64646464u, 0x5140u);
             p[1] = __byte_perm(g1, 0x64646464u, 0x7362u);

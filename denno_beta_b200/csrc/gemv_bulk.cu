@@ -20,13 +20,17 @@
 
 namespace dnb {
 
-__constant__ uint32_t c_grid3xxs_b[256];
+// The IQ3_XXS codebook in the replicated layout of IqLut, ready to be bulk-copied into a
+// CTA's shared memory (a constant of the library: requested before any wait on other kernels).
+__device__ __align__(16) uint32_t g_grid3xxs_rep[256 * kLutRep];
 static bool g_tables_b[64] = {false};
 
 static int upload_tables_b(int device) {
     if (device < 0 || device >= 64) return DNB_ERR_ARG;
     if (g_tables_b[device]) return DNB_OK;
-    DNB_CUDA(cudaMemcpyToSymbol(c_grid3xxs_b, dnb_iq3xxs_grid, sizeof(c_grid3xxs_b)));
+    static uint32_t rep[256 * kLutRep];
+    for (int i = 0; i < 256 * kLutRep; ++i) rep[i] = dnb_iq3xxs_grid[i / kLutRep];
+    DNB_CUDA(cudaMemcpyToSymbol(g_grid3xxs_rep, rep, sizeof(rep)));
     g_tables_b[device] = true;
     return DNB_OK;
 }
@@ -141,13 +145,19 @@ gemv_bulk_kernel(const SegDesc* __restrict__ seg, const int32_t* __restrict__ ns
     uint8_t* wb = wa + item_bytes;
     uint64_t* bar = bars + warp;
 
-    if constexpr (T == T_IQ3_XXS) {
-        for (int i = tid; i < 256; i += kWarps * 32) lut->grid3xxs[i] = c_grid3xxs_b[i];
-    }
     if (lane == 0) {
         mbar_init(bar, 1);
-        if (warp == 0) mbar_init(bars + kWarps, 1);  // the CTA's activation row, when it comes by bulk copy
+        if (warp == 0) {
+            mbar_init(bars + kWarps, 1);      // the CTA's activation row, when it comes by bulk copy
+            mbar_init(bars + kWarps + 1, 1);  // the codebook
+        }
         mbar_fence_init();
+        if constexpr (T == T_IQ3_XXS) {
+            if (warp == 0) {
+                mbar_expect_tx(bars + kWarps + 1, (uint32_t)sizeof(IqLut));
+                bulk_g2s(lut, g_grid3xxs_rep, (uint32_t)sizeof(IqLut), bars + kWarps + 1);
+            }
+        }
     }
     // Everything above touches nothing another kernel writes.  A segment table, the token
     // count and x come from the kernel before this one; a single matrix named by the launch
@@ -206,6 +216,7 @@ gemv_bulk_kernel(const SegDesc* __restrict__ seg, const int32_t* __restrict__ ns
     __syncthreads();
     if (!active) return;
     if (XSHARED && x_perm && !mbar_wait_bounded(bars + kWarps, 0, status)) return;
+    if (T == T_IQ3_XXS && !mbar_wait_bounded(bars + kWarps + 1, 0, status)) return;
     if (!mbar_wait_bounded(bar, 0, status)) return;
 
     constexpr int GPW = 32 / LPR;
@@ -291,13 +302,15 @@ down_combine_kernel(const SegDesc* __restrict__ seg, int nseg, int k, int n_in, 
     if (shcoef) shcoef += tkn;
     if (residual) residual += (size_t)tkn * n_out;
     out += (size_t)tkn * n_out;
-    if constexpr (T == T_IQ3_XXS) {
-        for (int i = tid; i < 256; i += NT) lut->grid3xxs[i] = c_grid3xxs_b[i];
-    }
     if (tid == 0) {
         mbar_init(bar, 1);
         mbar_init(bar + 1, 1);
+        mbar_init(bar + 2, 1);
         mbar_fence_init();
+        if constexpr (T == T_IQ3_XXS) {
+            mbar_expect_tx(bar + 2, (uint32_t)sizeof(IqLut));
+            bulk_g2s(lut, g_grid3xxs_rep, (uint32_t)sizeof(IqLut), bar + 2);
+        }
         // The segment table was written two kernels back (the router); the kernel
         // in between waited for the router before it let this one start, so the
         // table is complete and the weights can be requested before pdl_wait().
@@ -321,6 +334,7 @@ down_combine_kernel(const SegDesc* __restrict__ seg, int nseg, int k, int n_in, 
     if (tid < nseg) ws[tid] = tid < k ? wts[tid] : (shcoef ? shcoef[0] : 1.0f);
     __syncthreads();
     if (act_perm) x_ok = mbar_wait_bounded(bar + 1, 0, status);
+    if (T == T_IQ3_XXS) x_ok = mbar_wait_bounded(bar + 2, 0, status) && x_ok;
     const bool ok = mbar_wait_bounded(bar, 0, status) && x_ok;
     // (segment, row) pairs are dealt to the lane groups of all warps round-robin
     const int sub = lane % LPR;
@@ -368,11 +382,8 @@ static int launch_dc(dnb_ctx* c, cudaStream_t st, const SegDesc* seg, int nseg, 
                         (size_t)nseg * n_in * sizeof(float) + (size_t)nseg * R * sizeof(float) + (size_t)nseg * 4 + 16;
     if (smem > 200 * 1024) return DNB_DECLINED;
     auto kern = down_combine_kernel<T, LPR>;
-    static size_t smem_set = 0;
-    if (smem > smem_set) {
-        DNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        smem_set = smem;
-    }
+    static SmemGrant grant;
+    DNB_CUDA(grant_smem(grant, c->device, kern, smem));
     ProfScope prof_(c, st, "gemv_down_combine");
     DNB_CUDA(launch_k(kern, dim3(n_out / R, ntok), dim3(kDcWarps * 32), smem, st, c->use_pdl, seg, nseg, k, n_in, n_out, rb, act,
                       wts, shcoef, has_shared ? 1 : 0, residual, out, c->status, act_perm));
@@ -428,11 +439,8 @@ static int launch_cfg(dnb_ctx* c, cudaStream_t st, const SegDesc* seg, const int
     // is built for five CTAs per SM so that the 704 CTAs of a 512-expert top-10 block are one wave
     const bool one = (rg + GPW - 1) / GPW == 1;
     auto kern = one ? gemv_bulk_kernel<T, FUSED, LPR, XSHARED, 1> : gemv_bulk_kernel<T, FUSED, LPR, XSHARED, kMaxRounds>;
-    static size_t smem_set[2] = {0, 0};
-    if (smem > smem_set[one ? 1 : 0]) {
-        DNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        smem_set[one ? 1 : 0] = smem;
-    }
+    static SmemGrant grant[2];
+    DNB_CUDA(grant_smem(grant[one ? 1 : 0], c->device, kern, smem));
     if (XSHARED && row_token && gps % kWarps) return DNB_DECLINED;  // a CTA must not straddle two segments' tokens
     const long warps = (long)nseg_max * gps;
     const int grid = (int)((warps + kWarps - 1) / kWarps);

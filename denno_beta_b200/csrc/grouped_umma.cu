@@ -675,21 +675,15 @@ int launch_grouped_umma(dnb_ctx* c, cudaStream_t st, bool fused, const SegDesc* 
     const dim3 grid(c->sm_count);  // persistent: one CTA per SM loops over the tiles
     if (fused) {
         const size_t smem = 2 * (2 * 2 * um::A_TILE + 2 * 128 * um::BK * 2) + 256 + (um::kMaxSeg + 1) * 4 + um::kLocalItems * sizeof(um::Item) + 1024;
-        static bool set = false;
-        if (!set) {
-            DNB_CUDA(cudaFuncSetAttribute(um::grouped_q4k_umma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            set = true;
-        }
+        static SmemGrant grant;
+        DNB_CUDA(grant_smem(grant, c->device, um::grouped_q4k_umma_kernel<2>, smem));
         ProfScope prof_(c, st, "umma_gate_up");
         um::grouped_q4k_umma_kernel<2><<<grid, um::NTHREADS, smem, st>>>(seg, nseg_dev, n_in, n_out, rb, M, out_hi, out_lo,
                                                                         nullptr, c->status, nullptr);
     } else {
         const size_t smem = 3 * (2 * um::A_TILE + 2 * 128 * um::BK * 2) + 256 + (um::kMaxSeg + 1) * 4 + um::kLocalItems * sizeof(um::Item) + 1024;
-        static bool set = false;
-        if (!set) {
-            DNB_CUDA(cudaFuncSetAttribute(um::grouped_q4k_umma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            set = true;
-        }
+        static SmemGrant grant;
+        DNB_CUDA(grant_smem(grant, c->device, um::grouped_q4k_umma_kernel<1>, smem));
         ProfScope prof_(c, st, "umma_down");
         um::grouped_q4k_umma_kernel<1><<<grid, um::NTHREADS, smem, st>>>(seg, nseg_dev, n_in, n_out, rb, M, nullptr, nullptr,
                                                                         out_f32, c->status, row_dst);

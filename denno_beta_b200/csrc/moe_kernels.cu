@@ -757,11 +757,8 @@ int launch_route_tables(dnb_ctx* c, cudaStream_t st, const int32_t* sels, int nt
         set_error("route tables: %d tokens x %d experts exceeds one CTA's shared memory", nt, ne);
         return DNB_DECLINED;
     }
-    static size_t smem_set = 0;
-    if (smem > smem_set) {
-        DNB_CUDA(cudaFuncSetAttribute(route_tables_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        smem_set = smem;
-    }
+    static SmemGrant grant;
+    DNB_CUDA(grant_smem(grant, c->device, route_tables_kernel, smem));
     ProfScope prof_(c, st, "route_tables");
     route_tables_kernel<<<(ne + RTE - 1) / RTE, 256, smem, st>>>(
         sels, nt, k, ne, L.m[0].dev, L.m[1].dev, L.m[2].dev, L.m[0].expert_bytes, L.m[1].expert_bytes,

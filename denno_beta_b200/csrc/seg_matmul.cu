@@ -38,7 +38,7 @@ static int upload_tables(int device) {
 template <int T>
 __device__ __forceinline__ void fill_lut(IqLut* lut, int tid, int nthr) {
     if constexpr (T == T_IQ3_XXS) {
-        for (int i = tid; i < 256; i += nthr) lut->grid3xxs[i] = c_iq3xxs_grid[i];
+        lut->fill(c_iq3xxs_grid, tid, nthr);
     } else if constexpr (T == T_IQ3_S) {
         IqLut3s* l = reinterpret_cast<IqLut3s*>(lut);
         for (int i = tid; i < 512; i += nthr) l->grid[i] = c_iq3s_grid[i];
@@ -206,15 +206,12 @@ static int launch_cfg(dnb_ctx* c, cudaStream_t st, const SegDesc* seg, const int
     const size_t smem = (size_t)lut_bytes_of<T>() + (size_t)(FUSED ? 2 : 1) * tile_bytes +
                         (size_t)TT * n_in * sizeof(float);
     auto kern = seg_matmul_kernel<T, FUSED, LPR, TT>;
-    static size_t smem_set = 0;
+    static SmemGrant grant;
     if (smem > 200 * 1024) {
         set_error("seg_matmul: shared memory %zu B too large (n_in=%d)", smem, n_in);
         return DNB_DECLINED;
     }
-    if (smem > smem_set) {
-        DNB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        smem_set = smem;
-    }
+    DNB_CUDA(grant_smem(grant, c->device, kern, smem));
     dim3 grid((n_out + tile_rows - 1) / tile_rows, nseg_max);
     const bool sh = (st == c->side);
     const char* pname = FUSED ? (TT == 1 ? (sh ? "seg_gate_up_m1_shared" : "seg_gate_up_m1")
