@@ -214,9 +214,12 @@ gemv_bulk_kernel(const SegDesc* __restrict__ seg, const int32_t* __restrict__ ns
         xs4 = reinterpret_cast<const float4*>(xw);
     }
     __syncthreads();
-    if (!active) return;
-    if (XSHARED && x_perm && !mbar_wait_bounded(bars + kWarps, 0, status)) return;
-    if (T == T_IQ3_XXS && !mbar_wait_bounded(bars + kWarps + 1, 0, status)) return;
+    // Every thread waits for the CTA-wide copies (activation row, codebook) before it may leave:
+    // a CTA must not end while a bulk copy into its shared memory is in flight.
+    bool ready = true;
+    if (XSHARED && x_perm) ready = mbar_wait_bounded(bars + kWarps, 0, status);
+    if (T == T_IQ3_XXS) ready = mbar_wait_bounded(bars + kWarps + 1, 0, status) && ready;
+    if (!active || !ready) return;
     if (!mbar_wait_bounded(bar, 0, status)) return;
 
     constexpr int GPW = 32 / LPR;
