@@ -416,17 +416,23 @@ extern "C" int dnb_ep_block_dev(dnb_ctx* c, int layer, const float* h_dev, int n
         ProfScope p_(c, st, "ep_offsets");
         ep_offsets_kernel<<<1, 1024, 0, st>>>((const EpArena*)s->arena, M.ne, s->n_local, s->world, s->rank, seq, s->base, c->status);
     }
+    // The dispatch stores run on the side stream, beside the shared expert of the own tokens
+    // on the main one: peer stores over NVLink and a local GEMM do not compete for much.
+    DNB_CUDA(cudaEventRecord(c->ev_fork, st));
+    DNB_CUDA(cudaStreamWaitEvent(c->side, c->ev_fork, 0));
     {
-        ProfScope p_(c, st, "ep_dispatch");
-        ep_dispatch_kernel<<<nt * M.k, 256, 0, st>>>(w.xn, w.sels, s->send_row, s->base, M.k, M.e, s->n_local, s->world, s->rank,
-                                                    s->rows_total, seq, s->peers, s->ticket, c->status);
+        ProfScope p_(c, c->side, "ep_dispatch");
+        ep_dispatch_kernel<<<nt * M.k, 256, 0, c->side>>>(w.xn, w.sels, s->send_row, s->base, M.k, M.e, s->n_local, s->world,
+                                                         s->rank, s->rows_total, seq, s->peers, s->ticket, c->status);
     }
+    DNB_CUDA(cudaEventRecord(c->ev_join, c->side));
     c->launches += 3;
     DNB_CUDA(cudaGetLastError());
-    // 2. the shared expert of the own tokens while the peers' rows arrive
+    // 2. the shared expert of the own tokens while the rows travel
     const bool shared = L.has_shared();
     if (shared)
         if ((rc = dnb_expert_rows_dev(c, layer, w.xn, nullptr, nt, 1, w.sh))) return rc;
+    DNB_CUDA(cudaStreamWaitEvent(st, c->ev_join, 0));
     // 3. the rows this rank owns: tables, the two grouped GEMMs, results stored at the token owners
     {
         ProfScope p_(c, st, "ep_build");

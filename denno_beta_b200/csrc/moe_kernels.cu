@@ -194,7 +194,7 @@ __device__ __forceinline__ void topk_block(const float* __restrict__ logit_row, 
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
         const int idx = j * 128 + tid;
-        p[j] = idx < ne ? logit_row[idx] : -INFINITY;
+        p[j] = idx < ne ? __ldcg(logit_row + idx) : -INFINITY;  // L2: other CTAs of this launch may have written them
         mx = fmaxf(mx, p[j]);
     }
 #pragma unroll
@@ -524,16 +524,18 @@ router_decode_kernel(const float* __restrict__ h, const float* __restrict__ norm
         for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
         if (lane == 0) logits[row] = bias ? acc + bias[row] : acc;
     }
-    __threadfence();
+    // Publish: the CTA's stores are ordered before the barrier, the ticket is taken with a
+    // release-acquire atomic at device scope after it, and the last CTA's threads read the
+    // logits after the barrier that follows the acquire -- no separate fences.
     __syncthreads();
     if (tid == 0) {
-        const unsigned int t = atomicAdd(ticket, 1u);
+        unsigned int t;
+        asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(t) : "l"(ticket) : "memory");
         is_last = (t == gridDim.x - 1) ? 1 : 0;
         if (is_last) *ticket = 0u;  // ready for the next launch
     }
     __syncthreads();
     if (!is_last) return;
-    __threadfence();
     topk_block(logits, ne, k, norm_topk, sm, sels, wts, nullptr);
     __syncthreads();
     if (tid < k) {
