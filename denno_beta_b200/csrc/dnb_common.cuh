@@ -151,6 +151,11 @@ struct dnb_ctx {
     int gemv_impl = 0;                  // 0 = fast (default), 1 = sequential bit-exact
     bool decode_fast = true;            // one-token calls take the bulk-copy GEMV + fused router path
     bool use_pdl = true;                // programmatic dependent launch between the decode kernels
+#ifdef DNB_GEMV_MMA_OFF
+    bool gemv_mma = false;
+#else
+    bool gemv_mma = true;               // one-token IQ3_XXS gate/up on mma.sync (gemv_mma.cu) where the shape fits
+#endif
     bool use_umma = true;               // prefill chunks of Q4_K layers take the tcgen05 grouped GEMM
     void* ep = nullptr;                 // dnb::EpState of the peer-memory expert-parallel path (ep_p2p.cu)
 };
@@ -286,6 +291,10 @@ inline cudaError_t grant_smem(SmemGrant& g, int device, K kern, size_t bytes) {
     if (e == cudaSuccess) g.got[device] = bytes;
     return e;
 }
+
+// One-token IQ3_XXS gate/up GEMV on mma.sync (gemv_mma.cu); DNB_DECLINED when the shape does not fit.
+int launch_gate_up_mma(dnb_ctx* c, cudaStream_t st, const SegDesc* seg, int nseg, int n_in, int n_out, const float* x,
+                       float* out, const char* pname, PermOut perm);
 
 // tcgen05 grouped GEMM of prefill (grouped_umma.cu)
 int umma_make_maps(void* hi, void* lo, uint64_t rows, uint64_t cols, UmmaMaps* out);

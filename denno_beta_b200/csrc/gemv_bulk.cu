@@ -16,6 +16,7 @@
 // 259-319 (one warp per row, plain loads).
 #include "dnb_common.cuh"
 #include "formats.cuh"
+#include "bulk.cuh"
 #include "dnb_iq_tables.h"
 
 namespace dnb {
@@ -33,39 +34,6 @@ static int upload_tables_b(int device) {
     DNB_CUDA(cudaMemcpyToSymbol(g_grid3xxs_rep, rep, sizeof(rep)));
     g_tables_b[device] = true;
     return DNB_OK;
-}
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                     smem_u32(dst)),
-                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
-                 : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Bounded wait: gives up after ~2^22 polls (tens of milliseconds), records the
-// failure in *status and reports false; the caller then skips its math.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, int* status) {
-    for (int i = 0; i < (1 << 22); ++i)
-        if (mbar_try_wait(bar, parity)) return true;
-    if (status) atomicExch(status, 1);
-    return false;
 }
 
 __device__ __forceinline__ float silu_b(float v) { return v / (1.0f + expf(-v)); }
@@ -482,7 +450,12 @@ int launch_seg_gemv_m1(dnb_ctx* c, cudaStream_t st, int type, bool fused, bool x
     const SegDesc single = single_p ? *single_p : SegDesc{nullptr, nullptr, 0u, 0u};
     if (!seg && !single_p) return DNB_ERR_ARG;
     if (row_bytes(type, n_in) == 0 || n_in % 32 || n_out <= 0 || nseg_max <= 0) return DNB_DECLINED;
-    int rc = upload_tables_b(c->device);
+    int rc;
+    if (type == T_IQ3_XXS && fused && xshared && seg && !nseg_dev && !row_token && c->gemv_mma) {
+        rc = launch_gate_up_mma(c, st, seg, nseg_max, n_in, n_out, x, out, pname, perm);
+        if (rc != DNB_DECLINED) return rc;
+    }
+    rc = upload_tables_b(c->device);
     if (rc != DNB_OK) return rc;
     switch (type) {
         case T_Q4_K: return launch_t<T_Q4_K>(c, st, fused, xshared, seg, nseg_dev, nseg_max, single, n_in, n_out, x, ldx, row_token, out, pname, perm);
