@@ -30,7 +30,7 @@ static int dev_alloc(T** p, size_t n) {
 }
 
 static void free_ws(Workspace& w) {
-    void* dev[] = {w.xn_perm, w.act_perm, w.xn, w.logits, w.wts, w.act, w.hrow, w.sact, w.sh, w.hin, w.out, w.shcoef, w.sels, w.row_token,
+    void* dev[] = {w.act_h, w.xn_perm, w.act_perm, w.xn, w.logits, w.wts, w.act, w.hrow, w.sact, w.sh, w.hin, w.out, w.shcoef, w.sels, w.row_token,
                    w.pos, w.nseg, w.counts, w.one, w.seg_gu, w.seg_dn, w.seg_sh_gu, w.seg_sh_dn, w.xg_hi, w.xg_lo, w.act_hi, w.act_lo};
     for (void* p : dev)
         if (p) cudaFree(p);
@@ -64,6 +64,7 @@ static int ensure_ws(dnb_ctx* c, int nt) {
     if ((rc = dev_alloc(&w.act, rows * M.ff))) return rc;
     if ((rc = dev_alloc(&w.act_perm, (size_t)kActRep * (cap < kDecodeBatchMax ? cap : kDecodeBatchMax) * (M.k + 1) * M.ff))) return rc;
     if ((rc = dev_alloc(&w.xn_perm, (size_t)kActRep * M.e))) return rc;
+    if ((rc = dev_alloc(&w.act_h, decode_fused_act_halves(M.k + 1, M.ff)))) return rc;
     if ((rc = dev_alloc(&w.hrow, rows * M.e))) return rc;
     if ((rc = dev_alloc(&w.sact, (size_t)cap * sff))) return rc;
     if ((rc = dev_alloc(&w.sh, (size_t)cap * M.e))) return rc;
@@ -250,6 +251,18 @@ static int block_dev_decode(dnb_ctx* c, int layer, const float* h, float* out, c
     int rc = launch_router_decode(c, st, h, M, L, w, fold, c->ticket);
     if (rc) return rc;
     const int nseg = M.k + (fold ? 1 : 0);
+    const float* xperm = M.ne >= 4 * kActRep ? w.xn_perm : nullptr;
+    if (c->gemv_mma && L.m[0].type == T_IQ3_XXS && L.m[2].type == T_IQ3_XXS && decode_fused_fits(c, nseg, M.e, M.ff)) {
+        // gate/up, SwiGLU, down and the weighted sum in one kernel (decode_fused.cu)
+        const float* fcoef = nullptr;
+        if (fold && L.shared_gate_row) {
+            if ((rc = launch_shared_coef(c, st, w.xn, L.shared_gate_row, 1, M.e, w.shcoef))) return rc;
+            fcoef = w.shcoef;
+        }
+        rc = launch_decode_fused(c, st, w.seg_gu, w.seg_dn, nseg, M.k, fold, M.e, M.ff, w.xn, xperm, w.act, w.act_h, w.wts,
+                                 fcoef, residual, out, c->gbar);
+        if (rc != DNB_DECLINED) return rc;
+    }
     rc = launch_seg_gemv_m1(c, st, L.m[0].type, true, true, w.seg_gu, nullptr, nseg, M.e, M.ff, w.xn, M.e, nullptr, w.act,
                             nullptr, "gemv_gate_up",
                             PermOut{w.act_perm, L.m[2].type, M.ne >= 4 * kActRep ? w.xn_perm : nullptr});
@@ -420,6 +433,8 @@ int dnb_init(int device, dnb_ctx** out) {
     DNB_CUDA(cudaMemset(c->status, 0, sizeof(int)));
     DNB_CUDA(cudaMalloc((void**)&c->ticket, sizeof(unsigned int)));
     DNB_CUDA(cudaMemset(c->ticket, 0, sizeof(unsigned int)));
+    DNB_CUDA(cudaMalloc((void**)&c->gbar, sizeof(unsigned long long)));
+    DNB_CUDA(cudaMemset(c->gbar, 0, sizeof(unsigned long long)));
     *out = c;
     return DNB_OK;
 }
@@ -447,6 +462,7 @@ void dnb_shutdown(dnb_ctx* c) {
     if (c->gemv_out.p) cudaFree(c->gemv_out.p);
     if (c->status) cudaFree(c->status);
     if (c->ticket) cudaFree(c->ticket);
+    if (c->gbar) cudaFree(c->gbar);
     if (c->own_stream && c->stream) cudaStreamDestroy(c->stream);
     if (!c->own_stream && c->saved_stream) cudaStreamDestroy(c->saved_stream);
     if (c->flush.p) cudaFree(c->flush.p);

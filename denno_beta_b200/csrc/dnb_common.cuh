@@ -90,6 +90,7 @@ struct Workspace {             // device buffers of the MoE pipeline, sized for 
           *sh = nullptr, *hin = nullptr, *out = nullptr, *shcoef = nullptr,
           *act_perm = nullptr,  // [kActRep][(k + 1) * ff]: the decode gate/up result in the down format's slot order
           *xn_perm = nullptr;   // [kActRep][e]: the decode router's normalised row in the gate format's slot order
+    uint16_t* act_h = nullptr;  // f16 triples of the fused decode kernel's activations (decode_fused.cu)
     int32_t *sels = nullptr, *row_token = nullptr, *pos = nullptr, *nseg = nullptr, *counts = nullptr, *one = nullptr;
     SegDesc *seg_gu = nullptr, *seg_dn = nullptr, *seg_sh_gu = nullptr, *seg_sh_dn = nullptr;
     uint16_t *xg_hi = nullptr, *xg_lo = nullptr, *act_hi = nullptr, *act_lo = nullptr;  // bf16 hi/lo packed rows
@@ -147,6 +148,7 @@ struct dnb_ctx {
     int sm_count = 148;
     int* status = nullptr;              // device status word written by kernels on internal errors
     unsigned int* ticket = nullptr;     // "last CTA" counter of the fused decode router (self-resetting)
+    unsigned long long* gbar = nullptr; // grid barrier of the fused decode kernel: arrivals of all launches so far
     uint64_t launches = 0;              // kernels launched by this context (bench accounting)
     int gemv_impl = 0;                  // 0 = fast (default), 1 = sequential bit-exact
     bool decode_fast = true;            // one-token calls take the bulk-copy GEMV + fused router path
@@ -295,6 +297,13 @@ inline cudaError_t grant_smem(SmemGrant& g, int device, K kern, size_t bytes) {
 // One-token IQ3_XXS gate/up GEMV on mma.sync (gemv_mma.cu); DNB_DECLINED when the shape does not fit.
 int launch_gate_up_mma(dnb_ctx* c, cudaStream_t st, const SegDesc* seg, int nseg, int n_in, int n_out, const float* x,
                        float* out, const char* pname, PermOut perm);
+
+// One-token gate/up + down of an all-IQ3_XXS block in one kernel (decode_fused.cu).
+bool decode_fused_fits(const dnb_ctx* c, int nseg, int e, int ff);
+size_t decode_fused_act_halves(int nseg, int ff);
+int launch_decode_fused(dnb_ctx* c, cudaStream_t st, const SegDesc* seg_gu, const SegDesc* seg_dn, int nseg, int k,
+                        bool has_shared, int e, int ff, const float* x, const float* x_perm, float* act, void* act_h,
+                        const float* wts, const float* shcoef, const float* residual, float* out, unsigned long long* gbar);
 
 // tcgen05 grouped GEMM of prefill (grouped_umma.cu)
 int umma_make_maps(void* hi, void* lo, uint64_t rows, uint64_t cols, UmmaMaps* out);

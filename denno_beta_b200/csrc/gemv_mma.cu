@@ -22,65 +22,9 @@
 //
 // Block layout and decode: crates/denno-engine/src/kquant.rs:659-680 of the
 // reference; kernels of this role there: kernels_exp_iq_v2.cu:259-319.
-#include <cuda_fp16.h>
-
-#include "dnb_common.cuh"
-#include "formats.cuh"
-#include "bulk.cuh"
-#include "dnb_iq_tables.h"
+#include "iq3_mma.cuh"
 
 namespace dnb {
-
-constexpr int kGmRows = 8;     // rows of one matrix per group (x2 matrices = the 16 mma rows)
-constexpr int kGmKs = 4;       // warps that split K within a group
-constexpr int kGmGroups = 5;   // groups a CTA can hold
-constexpr int kGmThreads = kGmGroups * kGmKs * 32;
-constexpr int kGmSplit = 3;    // f16 terms per activation value
-
-// IQ3_XXS codebook as f16 pairs: entry e of copy r at [e * kLutRep + r]; .x = elements 0,1, .y = elements 2,3
-__device__ __align__(16) uint2 g_grid3xxs_h2[256 * kLutRep];
-static bool g_tables_m[64] = {false};
-
-static int upload_tables_m(int device) {
-    if (device < 0 || device >= 64) return DNB_ERR_ARG;
-    if (g_tables_m[device]) return DNB_OK;
-    static uint2 rep[256 * kLutRep];
-    for (int e = 0; e < 256; ++e) {
-        const uint32_t w = dnb_iq3xxs_grid[e];
-        uint32_t h[4];
-        for (int j = 0; j < 4; ++j) h[j] = __half_as_ushort(__float2half((float)((w >> (8 * j)) & 0xFFu)));
-        for (int r = 0; r < kLutRep; ++r) rep[e * kLutRep + r] = make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16));
-    }
-    DNB_CUDA(cudaMemcpyToSymbol(g_grid3xxs_h2, rep, sizeof(rep)));
-    g_tables_m[device] = true;
-    return DNB_OK;
-}
-
-__device__ __forceinline__ uint32_t f16_sat(float v) {
-    uint16_t h;
-    asm("cvt.rn.satfinite.f16.f32 %0, %1;" : "=h"(h) : "f"(v));
-    return h;
-}
-__device__ __forceinline__ float silu_m(float v) { return v / (1.0f + expf(-v)); }
-__device__ __forceinline__ float f16_val(uint32_t h) { return __half2float(__ushort_as_half((unsigned short)h)); }
-
-__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                        uint32_t b1) {
-    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-// Eight weights of one IQ3_XXS sub-block as four signed f16 pairs (without the scale):
-// `idx` = the two codebook indices of this lane's quarter, `code` = its 7 sign bits.
-__device__ __forceinline__ void iq3_pairs(const uint2* lutp, uint32_t idx, uint32_t code, uint32_t (&p)[4]) {
-    const uint32_t sg = code | ((__popc(code) & 1u) << 7);  // bit 7 makes the number of minus signs even
-    const uint2 g1 = lutp[(idx & 0xFFu) * kLutRep], g2 = lutp[(idx >> 8) * kLutRep];
-    p[0] = g1.x ^ ((sg * 0x40008000u) & 0x80008000u);
-    p[1] = g1.y ^ ((sg * 0x10002000u) & 0x80008000u);
-    p[2] = g2.x ^ ((sg * 0x04000800u) & 0x80008000u);
-    p[3] = g2.y ^ ((sg * 0x01000200u) & 0x80008000u);
-}
 
 // Dynamic shared memory: [8 mbarriers | pad to 128][codebook 32 KB][groups x (8 gate rows, 8 up rows)]
 //                        [x fp32 (staging)][x as kGmSplit f16 vectors][K-partials]
@@ -139,19 +83,12 @@ gate_up_mma_kernel(const SegDesc* __restrict__ seg, int nseg, int n_in, int n_ou
             } else {
                 v = *reinterpret_cast<const float2*>(x + i);
             }
-            float r[2] = {v.x, v.y};
-            uint32_t h[kGmSplit][2];
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-#pragma unroll
-                for (int n = 0; n < kGmSplit; ++n) {
-                    h[n][e] = f16_sat(r[e]);
-                    r[e] -= f16_val(h[n][e]);
-                }
-            }
+            uint32_t h0[kGmSplit], h1[kGmSplit];
+            split3(v.x, h0);
+            split3(v.y, h1);
 #pragma unroll
             for (int n = 0; n < kGmSplit; ++n)
-                *reinterpret_cast<uint32_t*>(xh + (size_t)n * n_in + i) = h[n][0] | (h[n][1] << 16);
+                *reinterpret_cast<uint32_t*>(xh + (size_t)n * n_in + i) = h0[n] | (h1[n] << 16);
         }
     }
     __syncthreads();
@@ -168,32 +105,7 @@ gate_up_mma_kernel(const SegDesc* __restrict__ seg, int nseg, int n_in, int n_ou
         const uint2* lutp = lut + (lane & (kLutRep - 1));
         const __half* xb = xh + (size_t)(g < kGmSplit ? g : 0) * n_in + 8 * t;
         const int bpw = (n_in >> 8) / kGmKs;
-        for (int b = ks * bpw; b < (ks + 1) * bpw; ++b) {
-            const uint8_t* bg = rowg + b * 98;
-            const uint8_t* bu = rowu + b * 98;
-            const float dg = h2f(ld16(bg)) * 0.25f, du = h2f(ld16(bu)) * 0.25f;
-#pragma unroll 2
-            for (int ib = 0; ib < 8; ++ib) {
-                uint4 y = make_uint4(0u, 0u, 0u, 0u);
-                if (g < kGmSplit) y = *reinterpret_cast<const uint4*>(xb + (b * 8 + ib) * 32);
-                const uint32_t auxg = ld16(bg + 66 + 4 * ib) | (ld16(bg + 68 + 4 * ib) << 16);
-                const uint32_t auxu = ld16(bu + 66 + 4 * ib) | (ld16(bu + 68 + 4 * ib) << 16);
-                const uint32_t idg = ld16(bg + 2 + 8 * ib + 2 * t), idu = ld16(bu + 2 + 8 * ib + 2 * t);
-                uint32_t p[4], u4[4];
-                iq3_pairs(lutp, idg, (auxg >> (7 * t)) & 127u, p);
-                iq3_pairs(lutp, idu, (auxu >> (7 * t)) & 127u, u4);
-                float c[4] = {0.f, 0.f, 0.f, 0.f};
-                mma_f16(c, p[0], u4[0], p[1], u4[1], y.x, y.y);
-                mma_f16(c, p[2], u4[2], p[3], u4[3], y.z, y.w);
-                // d * (0.5 + s) * 0.5 = (d / 4) * (2 s + 1), exact in fp32 either way (kquant.rs:667)
-                const float dbg = dg * (float)(2u * (auxg >> 28) + 1u), dbu = du * (float)(2u * (auxu >> 28) + 1u);
-                accg = fmaf(dbg, c[0] + c[1], accg);
-                accu = fmaf(dbu, c[2] + c[3], accu);
-            }
-        }
-        // lane t = 0 holds the hi and lo columns, t = 1 the lo2 column, t = 2, 3 nothing
-        accg += __shfl_xor_sync(0xffffffffu, accg, 1);
-        accu += __shfl_xor_sync(0xffffffffu, accu, 1);
+        gate_up_warp(rowg, rowu, lutp, xb, g < kGmSplit, ks * bpw, (ks + 1) * bpw, t, accg, accu);
     }
     float* rq = red + (size_t)q * kGmKs * 16;
     if (t == 0) {

@@ -1,0 +1,124 @@
+// IQ3_XXS decode into mma.sync fragments: what the one-token kernels of gemv_mma.cu and
+// decode_fused.cu share.  Each translation unit that includes this header owns a copy of
+// the f16 codebook and uploads it once per device.
+#pragma once
+#include <cuda_fp16.h>
+
+#include "dnb_common.cuh"
+#include "formats.cuh"
+#include "bulk.cuh"
+#include "dnb_iq_tables.h"
+
+namespace dnb {
+
+constexpr int kGmRows = 8;     // rows of one matrix per group (x2 matrices = the 16 mma rows)
+constexpr int kGmKs = 4;       // warps that split K within a group
+constexpr int kGmGroups = 5;   // groups a CTA can hold
+constexpr int kGmThreads = kGmGroups * kGmKs * 32;
+constexpr int kGmSplit = 3;    // f16 terms per activation value
+
+// IQ3_XXS codebook as f16 pairs: entry e of copy r at [e * kLutRep + r]; .x = elements 0,1, .y = elements 2,3
+static __device__ __align__(16) uint2 g_grid3xxs_h2[256 * kLutRep];
+static bool g_tables_m[64] = {false};
+
+static int upload_tables_m(int device) {
+    if (device < 0 || device >= 64) return DNB_ERR_ARG;
+    if (g_tables_m[device]) return DNB_OK;
+    static uint2 rep[256 * kLutRep];
+    for (int e = 0; e < 256; ++e) {
+        const uint32_t w = dnb_iq3xxs_grid[e];
+        uint32_t h[4];
+        for (int j = 0; j < 4; ++j) h[j] = __half_as_ushort(__float2half((float)((w >> (8 * j)) & 0xFFu)));
+        for (int r = 0; r < kLutRep; ++r) rep[e * kLutRep + r] = make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16));
+    }
+    DNB_CUDA(cudaMemcpyToSymbol(g_grid3xxs_h2, rep, sizeof(rep)));
+    g_tables_m[device] = true;
+    return DNB_OK;
+}
+
+__device__ __forceinline__ uint32_t f16_sat(float v) {
+    uint16_t h;
+    asm("cvt.rn.satfinite.f16.f32 %0, %1;" : "=h"(h) : "f"(v));
+    return h;
+}
+__device__ __forceinline__ float silu_m(float v) { return v / (1.0f + expf(-v)); }
+__device__ __forceinline__ float f16_val(uint32_t h) { return __half2float(__ushort_as_half((unsigned short)h)); }
+
+__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                        uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Eight weights of one IQ3_XXS sub-block as four signed f16 pairs (without the scale):
+// `idx` = the two codebook indices of this lane's quarter, `code` = its 7 sign bits.
+__device__ __forceinline__ void iq3_pairs(const uint2* lutp, uint32_t idx, uint32_t code, uint32_t (&p)[4]) {
+    const uint32_t sg = code | ((__popc(code) & 1u) << 7);  // bit 7 makes the number of minus signs even
+    const uint2 g1 = lutp[(idx & 0xFFu) * kLutRep], g2 = lutp[(idx >> 8) * kLutRep];
+    p[0] = g1.x ^ ((sg * 0x40008000u) & 0x80008000u);
+    p[1] = g1.y ^ ((sg * 0x10002000u) & 0x80008000u);
+    p[2] = g2.x ^ ((sg * 0x04000800u) & 0x80008000u);
+    p[3] = g2.y ^ ((sg * 0x01000200u) & 0x80008000u);
+}
+
+// C = A * B with a zero accumulator
+__device__ __forceinline__ void mma_f16_z(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                          uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
+}
+
+// One sub-block (32 elements) of two IQ3_XXS rows against the B columns: the lane (g, t) decodes
+// elements 8t .. 8t+7 of row `ba` (mma rows 0-7) and of row `bb` (mma rows 8-15); `y` holds the
+// lane's B column for those eight elements.  c[0], c[1] = row g of `ba`, columns 2t, 2t+1;
+// c[2], c[3] = row g of `bb`.  aux_a, aux_b return the sub-block words (scale in the top 4 bits).
+__device__ __forceinline__ void iq3_subblock_mma(const uint8_t* ba, const uint8_t* bb, int ib, int t, const uint2* lutp,
+                                                 const uint4& y, float (&c)[4], uint32_t& aux_a, uint32_t& aux_b) {
+    aux_a = ld16(ba + 66 + 4 * ib) | (ld16(ba + 68 + 4 * ib) << 16);
+    aux_b = ld16(bb + 66 + 4 * ib) | (ld16(bb + 68 + 4 * ib) << 16);
+    const uint32_t ida = ld16(ba + 2 + 8 * ib + 2 * t), idb = ld16(bb + 2 + 8 * ib + 2 * t);
+    uint32_t p[4], u4[4];
+    iq3_pairs(lutp, ida, (aux_a >> (7 * t)) & 127u, p);
+    iq3_pairs(lutp, idb, (aux_b >> (7 * t)) & 127u, u4);
+    mma_f16_z(c, p[0], u4[0], p[1], u4[1], y.x, y.y);
+    mma_f16(c, p[2], u4[2], p[3], u4[3], y.z, y.w);
+}
+// d * (0.5 + s) * 0.5 = (d / 4) * (2 s + 1), exact in fp32 either way (kquant.rs:667); dq = d / 4
+__device__ __forceinline__ float iq3_scale(float dq, uint32_t aux) { return dq * (float)(2u * (aux >> 28) + 1u); }
+
+// Three-way f16 split of an fp32 value: v = h0 + h1 + h2 up to 2^-33 |v| (|v| < 1.9e5).
+__device__ __forceinline__ void split3(float v, uint32_t (&h)[kGmSplit]) {
+#pragma unroll
+    for (int n = 0; n < kGmSplit; ++n) {
+        h[n] = f16_sat(v);
+        v -= f16_val(h[n]);
+    }
+}
+// A gate/up group's share of one warp: blocks [b0, b1) of 8 gate rows (rowg: this lane's row g)
+// and 8 up rows.  After the call lanes t = 0 and t = 1 of every row hold the row's two totals.
+__device__ __forceinline__ void gate_up_warp(const uint8_t* rowg, const uint8_t* rowu, const uint2* lutp,
+                                             const __half* xb, bool has_col, int b0, int b1, int t, float& accg,
+                                             float& accu) {
+    for (int b = b0; b < b1; ++b) {
+        const uint8_t* bg = rowg + b * 98;
+        const uint8_t* bu = rowu + b * 98;
+        const float dg = h2f(ld16(bg)) * 0.25f, du = h2f(ld16(bu)) * 0.25f;
+#pragma unroll 2
+        for (int ib = 0; ib < 8; ++ib) {
+            uint4 y = make_uint4(0u, 0u, 0u, 0u);
+            if (has_col) y = *reinterpret_cast<const uint4*>(xb + (b * 8 + ib) * 32);
+            float c[4];
+            uint32_t auxg, auxu;
+            iq3_subblock_mma(bg, bu, ib, t, lutp, y, c, auxg, auxu);
+            accg = fmaf(iq3_scale(dg, auxg), c[0] + c[1], accg);
+            accu = fmaf(iq3_scale(du, auxu), c[2] + c[3], accu);
+        }
+    }
+    // lane t = 0 holds the hi and lo columns, t = 1 the lo2 column, t = 2, 3 nothing
+    accg += __shfl_xor_sync(0xffffffffu, accg, 1);
+    accu += __shfl_xor_sync(0xffffffffu, accu, 1);
+}
+
+}  // namespace dnb
