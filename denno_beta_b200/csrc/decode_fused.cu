@@ -74,11 +74,11 @@ __global__ void __launch_bounds__(kFdThreads, 1) decode_fused_kernel(const Fused
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem);  // [0..4] gate/up groups, [5] codebook, [6] x, [7] down rows
     int* flags = reinterpret_cast<int*>(smem + 64);      // [0] barrier passed
-    uint2* lut = reinterpret_cast<uint2*>(smem + 128);
+    Iq3Tables* lut = reinterpret_cast<Iq3Tables*>(smem + 128);
     const int e = A.e, ff = A.ff, nseg = A.nseg;
     const int gu_bytes = kGmRows * A.rb_gu, dn_bytes = 8 * A.rb_dn;  // multiples of 16
     const int arow = ff + kFdPad;
-    uint8_t* wgu = smem + 128 + sizeof(uint2) * 256 * kLutRep;
+    uint8_t* wgu = smem + 128 + sizeof(Iq3Tables);
     uint8_t* wdn = wgu + (size_t)kGmGroups * 2 * gu_bytes;
     float* xf = reinterpret_cast<float*>(wdn + (size_t)kFdUnits * kFdSegs * dn_bytes);
     __half* xh = reinterpret_cast<__half*>(xf + e);
@@ -92,8 +92,8 @@ __global__ void __launch_bounds__(kFdThreads, 1) decode_fused_kernel(const Fused
     if (tid == 0) {
         for (int i = 0; i < 8; ++i) mbar_init(bars + i, 1);
         mbar_fence_init();
-        mbar_expect_tx(bars + 5, (uint32_t)(sizeof(uint2) * 256 * kLutRep));
-        bulk_g2s(lut, g_grid3xxs_h2, (uint32_t)(sizeof(uint2) * 256 * kLutRep), bars + 5);
+        mbar_expect_tx(bars + 5, (uint32_t)(sizeof(Iq3Tables)));
+        bulk_g2s(lut, &g_iq3_tables, (uint32_t)(sizeof(Iq3Tables)), bars + 5);
         flags[0] = 0;
     }
     __syncthreads();
@@ -122,15 +122,9 @@ __global__ void __launch_bounds__(kFdThreads, 1) decode_fused_kernel(const Fused
         mbar_expect_tx(bars + 6, (uint32_t)(e * sizeof(float)));
         bulk_g2s(xf, A.x_perm + (size_t)(blockIdx.x % kActRep) * e, (uint32_t)(e * sizeof(float)), bars + 6);
     }
-    if (warp == 2) {  // one lane per (unit, segment): the 2 x nseg requests go out side by side
-        if (lane == 0) mbar_expect_tx(bars + 7, (uint32_t)(my_units * nseg * dn_bytes));
-        __syncwarp();
-        if (lane < my_units * nseg) {
-            const int u = lane / nseg, s = lane - u * nseg;
-            const size_t off = (size_t)(blockIdx.x + u * gridDim.x) * dn_bytes;
-            bulk_g2s(wdn + (size_t)(u * kFdSegs + s) * dn_bytes, A.seg_dn[s].wa + off, (uint32_t)dn_bytes, bars + 7);
-        }
-    }
+    float resid = 0.f;  // the combine threads fetch their residual element now, off the critical path
+    if (A.residual && tid < kFdUnits * 8 && (tid >> 3) < my_units)
+        resid = A.residual[(blockIdx.x + (tid >> 3) * gridDim.x) * 8 + (tid & 7)];
     if (tid >= 96 && tid < 96 + nseg) {
         const int s = tid - 96;
         ws[s] = s < A.k ? A.wts[s] : (A.shcoef ? A.shcoef[0] : 1.0f);
@@ -158,8 +152,20 @@ __global__ void __launch_bounds__(kFdThreads, 1) decode_fused_kernel(const Fused
         }
     }
     __syncthreads();
+    // The down rows are asked for only now, behind the gate/up rows: the two together are ~2 us of
+    // HBM time, and the gate/up phase needs its share first.  One lane per (unit, segment), in a
+    // warp that has no gate/up work.
+    if (warp == kFdWarps - 1) {
+        if (lane == 0) mbar_expect_tx(bars + 7, (uint32_t)(my_units * nseg * dn_bytes));
+        __syncwarp();
+        if (lane < my_units * nseg) {
+            const int u = lane / nseg, s = lane - u * nseg;
+            const size_t off = (size_t)(blockIdx.x + u * gridDim.x) * dn_bytes;
+            bulk_g2s(wdn + (size_t)(u * kFdSegs + s) * dn_bytes, A.seg_dn[s].wa + off, (uint32_t)dn_bytes, bars + 7);
+        }
+    }
     ready = mbar_wait_bounded(bars + 5, 0, A.status) && ready;
-    const uint2* lutp = lut + (lane & (kLutRep - 1));
+    const Iq3Lane lutp(lut, lane);
 
     // ---- gate/up: 8 gate + 8 up rows per group, four warps split K -----------------------------
     if (gactive) {  // all four warps of a group agree
@@ -277,7 +283,7 @@ __global__ void __launch_bounds__(kFdThreads, 1) decode_fused_kernel(const Fused
                 acc = __fadd_rn(acc, A.shcoef ? __fmul_rn(v, ws[A.k]) : v);
             }
             const int r = (blockIdx.x + u * gridDim.x) * 8 + row;
-            if (A.residual) acc = __fadd_rn(A.residual[r], acc);
+            if (A.residual) acc = __fadd_rn(resid, acc);
             A.out[r] = acc;
         }
     }
@@ -292,7 +298,7 @@ bool decode_fused_fits(const dnb_ctx* c, int nseg, int e, int ff) {
 
 static size_t fused_smem(int nseg, int e, int ff) {
     const size_t rb_gu = row_bytes(T_IQ3_XXS, e), rb_dn = row_bytes(T_IQ3_XXS, ff);
-    return 128 + sizeof(uint2) * 256 * kLutRep + (size_t)kGmGroups * 2 * kGmRows * rb_gu +
+    return 128 + sizeof(Iq3Tables) + (size_t)kGmGroups * 2 * kGmRows * rb_gu +
            (size_t)kFdUnits * kFdSegs * 8 * rb_dn + (size_t)e * sizeof(float) + (size_t)kGmSplit * e * sizeof(__half) +
            (size_t)nseg * kGmSplit * (ff + kFdPad) * sizeof(__half) +
            (size_t)(kGmGroups * kGmKs * 16 + kFdUnits * 2 * kFdSegs * 8 + 16) * sizeof(float);

@@ -34,9 +34,9 @@ gate_up_mma_kernel(const SegDesc* __restrict__ seg, int nseg, int n_in, int n_ou
                    float* __restrict__ out_perm, int perm_type, int* status) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem);  // [0..4] groups, [5] codebook, [6] x
-    uint2* lut = reinterpret_cast<uint2*>(smem + 128);
+    Iq3Tables* lut = reinterpret_cast<Iq3Tables*>(smem + 128);
     const int mat_bytes = kGmRows * rb;  // 8 rows of IQ3_XXS: a multiple of 16 bytes
-    uint8_t* wbase = smem + 128 + sizeof(uint2) * 256 * kLutRep;
+    uint8_t* wbase = smem + 128 + sizeof(Iq3Tables);
     float* xf = reinterpret_cast<float*>(wbase + (size_t)kGmGroups * 2 * mat_bytes);
     __half* xh = reinterpret_cast<__half*>(xf + n_in);
     float* red = reinterpret_cast<float*>(xh + (size_t)kGmSplit * n_in);  // [group][ks][16]
@@ -46,8 +46,8 @@ gate_up_mma_kernel(const SegDesc* __restrict__ seg, int nseg, int n_in, int n_ou
     if (tid == 0) {
         for (int i = 0; i < kGmGroups + 2; ++i) mbar_init(bars + i, 1);
         mbar_fence_init();
-        mbar_expect_tx(bars + kGmGroups, (uint32_t)(sizeof(uint2) * 256 * kLutRep));
-        bulk_g2s(lut, g_grid3xxs_h2, (uint32_t)(sizeof(uint2) * 256 * kLutRep), bars + kGmGroups);
+        mbar_expect_tx(bars + kGmGroups, (uint32_t)(sizeof(Iq3Tables)));
+        bulk_g2s(lut, &g_iq3_tables, (uint32_t)(sizeof(Iq3Tables)), bars + kGmGroups);
     }
     __syncthreads();
     pdl_wait();  // the segment table and x come from the router kernel
@@ -102,7 +102,7 @@ gate_up_mma_kernel(const SegDesc* __restrict__ seg, int nseg, int n_in, int n_ou
     if (ok) {
         const uint8_t* rowg = wq + g * rb;
         const uint8_t* rowu = rowg + mat_bytes;
-        const uint2* lutp = lut + (lane & (kLutRep - 1));
+        const Iq3Lane lutp(lut, lane);
         const __half* xb = xh + (size_t)(g < kGmSplit ? g : 0) * n_in + 8 * t;
         const int bpw = (n_in >> 8) / kGmKs;
         gate_up_warp(rowg, rowu, lutp, xb, g < kGmSplit, ks * bpw, (ks + 1) * bpw, t, accg, accu);
@@ -141,7 +141,7 @@ int launch_gate_up_mma(dnb_ctx* c, cudaStream_t st, const SegDesc* seg, int nseg
     const int ngroups = nseg * (n_out / kGmRows);
     const int grid = ngroups < c->sm_count ? ngroups : c->sm_count;
     if ((long)grid * kGmGroups < ngroups) return DNB_DECLINED;
-    const size_t smem = 128 + sizeof(uint2) * 256 * kLutRep + (size_t)kGmGroups * 2 * kGmRows * rb +
+    const size_t smem = 128 + sizeof(Iq3Tables) + (size_t)kGmGroups * 2 * kGmRows * rb +
                         (size_t)n_in * sizeof(float) + (size_t)kGmSplit * n_in * sizeof(__half) +
                         (size_t)kGmGroups * kGmKs * 16 * sizeof(float);
     if (smem > 200 * 1024) return DNB_DECLINED;

@@ -17,24 +17,35 @@ constexpr int kGmGroups = 5;   // groups a CTA can hold
 constexpr int kGmThreads = kGmGroups * kGmKs * 32;
 constexpr int kGmSplit = 3;    // f16 terms per activation value
 
-// IQ3_XXS codebook as f16 pairs: entry e of copy r at [e * kLutRep + r]; .x = elements 0,1, .y = elements 2,3
-static __device__ __align__(16) uint2 g_grid3xxs_h2[256 * kLutRep];
+// What a CTA copies into shared memory in one bulk copy: the IQ3_XXS codebook as f16 pairs,
+// entry e of copy r at [e * kLutRep + r]; .x = elements 0,1, .y = elements 2,3.  (A second table
+// with ready-made sign masks was tried: its 16-byte lookups cost more shared-memory cycles than
+// the multiply-and-mask below costs issue slots, and the kernels got slower.)
+struct Iq3Tables {
+    uint2 grid[256 * kLutRep];
+};
+static __device__ __align__(16) Iq3Tables g_iq3_tables;
 static bool g_tables_m[64] = {false};
 
 static int upload_tables_m(int device) {
     if (device < 0 || device >= 64) return DNB_ERR_ARG;
     if (g_tables_m[device]) return DNB_OK;
-    static uint2 rep[256 * kLutRep];
+    static Iq3Tables tb;
     for (int e = 0; e < 256; ++e) {
         const uint32_t w = dnb_iq3xxs_grid[e];
         uint32_t h[4];
         for (int j = 0; j < 4; ++j) h[j] = __half_as_ushort(__float2half((float)((w >> (8 * j)) & 0xFFu)));
-        for (int r = 0; r < kLutRep; ++r) rep[e * kLutRep + r] = make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16));
+        for (int r = 0; r < kLutRep; ++r) tb.grid[e * kLutRep + r] = make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16));
     }
-    DNB_CUDA(cudaMemcpyToSymbol(g_grid3xxs_h2, rep, sizeof(rep)));
+    DNB_CUDA(cudaMemcpyToSymbol(g_iq3_tables, &tb, sizeof(tb)));
     g_tables_m[device] = true;
     return DNB_OK;
 }
+// A lane's view of the table in shared memory: its own copy
+struct Iq3Lane {
+    const uint2* grid;
+    __device__ __forceinline__ Iq3Lane(const Iq3Tables* tb, int lane) : grid(tb->grid + (lane & (kLutRep - 1))) {}
+};
 
 __device__ __forceinline__ uint32_t f16_sat(float v) {
     uint16_t h;
@@ -53,9 +64,9 @@ __device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1,
 
 // Eight weights of one IQ3_XXS sub-block as four signed f16 pairs (without the scale):
 // `idx` = the two codebook indices of this lane's quarter, `code` = its 7 sign bits.
-__device__ __forceinline__ void iq3_pairs(const uint2* lutp, uint32_t idx, uint32_t code, uint32_t (&p)[4]) {
+__device__ __forceinline__ void iq3_pairs(const Iq3Lane& L, uint32_t idx, uint32_t code, uint32_t (&p)[4]) {
     const uint32_t sg = code | ((__popc(code) & 1u) << 7);  // bit 7 makes the number of minus signs even
-    const uint2 g1 = lutp[(idx & 0xFFu) * kLutRep], g2 = lutp[(idx >> 8) * kLutRep];
+    const uint2 g1 = L.grid[(idx & 0xFFu) * kLutRep], g2 = L.grid[(idx >> 8) * kLutRep];
     p[0] = g1.x ^ ((sg * 0x40008000u) & 0x80008000u);
     p[1] = g1.y ^ ((sg * 0x10002000u) & 0x80008000u);
     p[2] = g2.x ^ ((sg * 0x04000800u) & 0x80008000u);
@@ -74,7 +85,7 @@ __device__ __forceinline__ void mma_f16_z(float (&c)[4], uint32_t a0, uint32_t a
 // elements 8t .. 8t+7 of row `ba` (mma rows 0-7) and of row `bb` (mma rows 8-15); `y` holds the
 // lane's B column for those eight elements.  c[0], c[1] = row g of `ba`, columns 2t, 2t+1;
 // c[2], c[3] = row g of `bb`.  aux_a, aux_b return the sub-block words (scale in the top 4 bits).
-__device__ __forceinline__ void iq3_subblock_mma(const uint8_t* ba, const uint8_t* bb, int ib, int t, const uint2* lutp,
+__device__ __forceinline__ void iq3_subblock_mma(const uint8_t* ba, const uint8_t* bb, int ib, int t, const Iq3Lane& lutp,
                                                  const uint4& y, float (&c)[4], uint32_t& aux_a, uint32_t& aux_b) {
     aux_a = ld16(ba + 66 + 4 * ib) | (ld16(ba + 68 + 4 * ib) << 16);
     aux_b = ld16(bb + 66 + 4 * ib) | (ld16(bb + 68 + 4 * ib) << 16);
@@ -86,7 +97,7 @@ __device__ __forceinline__ void iq3_subblock_mma(const uint8_t* ba, const uint8_
     mma_f16(c, p[2], u4[2], p[3], u4[3], y.z, y.w);
 }
 // d * (0.5 + s) * 0.5 = (d / 4) * (2 s + 1), exact in fp32 either way (kquant.rs:667); dq = d / 4
-__device__ __forceinline__ float iq3_scale(float dq, uint32_t aux) { return dq * (float)(2u * (aux >> 28) + 1u); }
+__device__ __forceinline__ float iq3_scale(float dq, uint32_t aux) { return fmaf((float)(aux >> 28), dq + dq, dq); }
 
 // Three-way f16 split of an fp32 value: v = h0 + h1 + h2 up to 2^-33 |v| (|v| < 1.9e5).
 __device__ __forceinline__ void split3(float v, uint32_t (&h)[kGmSplit]) {
@@ -98,7 +109,7 @@ __device__ __forceinline__ void split3(float v, uint32_t (&h)[kGmSplit]) {
 }
 // A gate/up group's share of one warp: blocks [b0, b1) of 8 gate rows (rowg: this lane's row g)
 // and 8 up rows.  After the call lanes t = 0 and t = 1 of every row hold the row's two totals.
-__device__ __forceinline__ void gate_up_warp(const uint8_t* rowg, const uint8_t* rowu, const uint2* lutp,
+__device__ __forceinline__ void gate_up_warp(const uint8_t* rowg, const uint8_t* rowu, const Iq3Lane& lutp,
                                              const __half* xb, bool has_col, int b0, int b1, int t, float& accg,
                                              float& accu) {
     for (int b = b0; b < b1; ++b) {
