@@ -120,6 +120,8 @@ def run_ours(args, rank, world, local_rank):
     from denno_beta_b200 import cuda as cu
 
     ctx = cu.CudaCtx(local_rank)
+    if args.decode_impl:
+        ctx.set_gemv_impl(args.decode_impl)
     build_model(ctx, cu, IQ3_XXS, LAYERS, False)
     pool = oracle.synth_normal(SEED, 7000 + rank, 1.0, POOL * E).reshape(POOL, E)
     d_pool = ctx.dev_alloc(pool.nbytes)
@@ -207,6 +209,8 @@ def run_ours(args, rank, world, local_rank):
     hbm_peak, _, peak_kind = peaks()
     g_b, d_b = expert_bytes(IQ3_XXS)
     alg = {  # algorithmic bytes per launch: weight bytes + activations in/out
+        # gate/up + down of the block in one kernel: all expert rows once, x in, the block's result out
+        "decode_gate_up_down": (K + 1) * (2 * g_b + d_b) + 3 * E * 4,
         "gemv_gate_up": (K + 1) * 2 * g_b + E * 4 + (K + 1) * FF * 4,
         "gemv_down": (K + 1) * d_b + (K + 1) * FF * 4 + (K + 1) * E * 4,
         "gemv_down_combine": (K + 1) * d_b + (K + 1) * FF * 4 + E * 4,
@@ -216,8 +220,9 @@ def run_ours(args, rank, world, local_rank):
         "router_logits": NE * E * 4 + E * 4 + NE * 4,
     }
     # dram__bytes_read.sum + dram__bytes_write.sum per launch, from one ncu capture of each decode
-    # kernel on this workload (profiles/kernel_gateup.md, kernel_down.md, kernel_router.md)
-    ncu_traffic = {"gemv_gate_up": 8991744, "gemv_down_combine": 4813568, "router_decode_fused": 4275456}
+    # kernel on this workload (profiles/kernel_decode_fused.md, kernel_gateup.md, kernel_down.md, kernel_router.md)
+    ncu_traffic = {"decode_gate_up_down": 13474560, "gemv_gate_up": 8991744, "gemv_down_combine": 4813568,
+                   "router_decode_fused": 4275456}
     top = max((k for k in prof if k in alg), key=lambda k: prof[k]["ms"])
     per_launch_s = prof[top]["ms"] / prof[top]["launches"] * 1e-3
     achieved = alg[top] / per_launch_s / 1e9
@@ -627,6 +632,9 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="rotating layer copies (default %d; fewer for profiler captures)" % LAYERS)
     ap.add_argument("--prefill-only", action="store_true",
                     help="run only the config-2 prefill measurement (small: for profiler captures)")
+    ap.add_argument("--decode-impl", type=int, default=0, choices=[0, 3, 4],
+                    help="one-token kernels of the headline line: 0 fused mma.sync kernel (default), 4 mma.sync gate/up + "
+                         "down kernel, 3 register-decode kernels (for profiler captures of those kernels)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-extras", action="store_true", help="skip the config-0/2/3/4 lines")
     ap.add_argument("--no-stack", action="store_true", help="skip the 48-layer stack lines (configs 3 and 4)")

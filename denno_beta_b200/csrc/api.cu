@@ -252,7 +252,7 @@ static int block_dev_decode(dnb_ctx* c, int layer, const float* h, float* out, c
     if (rc) return rc;
     const int nseg = M.k + (fold ? 1 : 0);
     const float* xperm = M.ne >= 4 * kActRep ? w.xn_perm : nullptr;
-    if (c->gemv_mma && L.m[0].type == T_IQ3_XXS && L.m[2].type == T_IQ3_XXS && decode_fused_fits(c, nseg, M.e, M.ff)) {
+    if (c->gemv_mma && c->decode_fused && L.m[0].type == T_IQ3_XXS && L.m[2].type == T_IQ3_XXS && decode_fused_fits(c, nseg, M.e, M.ff)) {
         // gate/up, SwiGLU, down and the weighted sum in one kernel (decode_fused.cu)
         const float* fcoef = nullptr;
         if (fold && L.shared_gate_row) {
@@ -637,12 +637,14 @@ int dnb_register_matrix(dnb_ctx* c, uint64_t uid, int type, const void* blocks, 
 }
 
 int dnb_set_gemv_impl(dnb_ctx* c, int impl) {
-    if (!c || impl < 0 || impl > 2) return DNB_ERR_ARG;
+    if (!c || impl < 0 || impl > 4) return DNB_ERR_ARG;
     DNB_CUDA(cudaDeviceSynchronize());
     drop_graphs(c);
     c->gemv_impl = impl == 1 ? 1 : 0;
     c->decode_fast = impl != 2;
     c->use_umma = impl != 2;
+    c->gemv_mma = impl != 3;
+    c->decode_fused = impl != 3 && impl != 4;
     return DNB_OK;
 }
 

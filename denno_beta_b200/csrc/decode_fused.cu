@@ -9,7 +9,7 @@
 // and the down phase finds its rows already in shared memory.
 //
 // Both phases run on mma.sync.m16n8k16 as gemv_mma.cu describes (weights decoded
-// straight into f16 A fragments, activations as an exact three-way f16 split in the
+// straight into bf16 A fragments, activations as an exact three-way bf16 split in the
 // B columns).  Down phase: a CTA owns up to two units of 8 output rows for all
 // experts; a warp takes one unit, one PAIR of experts and half of K: rows 0-7 of the
 // A tile are the unit's rows of the first expert, rows 8-15 those of the second, and
@@ -20,7 +20,7 @@
 // the order of kernels_dec_epi.cu:28-46 / qwen4exp.rs:12126-12216 of the reference.
 //
 // The activations cross CTAs through global memory: every CTA writes its SwiGLU
-// outputs as f16 triples into kActRep identical copies (so that the 148 readers do not
+// outputs as bf16 triples into kActRep identical copies (so that the 148 readers do not
 // all hit the same L2 lines), arrives at a counter that only grows, and waits (bounded) until
 // the counter has reached the launch's share.  All CTAs are resident: one per SM, the grid
 // never exceeds the SM count, and the kernel that follows in the stream is not released
@@ -47,7 +47,7 @@ struct FusedArgs {
     const float* x;          // normalised hidden row (natural order)
     const float* x_perm;     // or: kActRep slot-ordered copies of it
     float* act;              // [nseg][ff] SwiGLU outputs (fp32, for inspection)
-    __half* act_h;           // [kActRep][nseg][3][ff + kFdPad]
+    uint16_t* act_h;           // [kActRep][nseg][3][ff + kFdPad]
     const float* wts;        // [k] routing weights
     const float* shcoef;     // shared-expert coefficient or null
     const float* residual;   // or null
@@ -68,8 +68,8 @@ __device__ __forceinline__ unsigned long long atom_add_acq_rel(unsigned long lon
 }
 
 // Dynamic shared memory:
-// [8 mbarriers | flags, pad to 128][codebook 32 KB][gate/up rows][down rows][x fp32][x f16 x3]
-// [activations f16 x3, all segments][gate/up K-partials][down partials][routing weights]
+// [8 mbarriers | flags, pad to 128][codebook 32 KB][gate/up rows][down rows][x fp32][x bf16 x3]
+// [activations bf16 x3, all segments][gate/up K-partials][down partials][routing weights]
 __global__ void __launch_bounds__(kFdThreads, 1) decode_fused_kernel(const FusedArgs A) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem);  // [0..4] gate/up groups, [5] codebook, [6] x, [7] down rows
@@ -81,8 +81,8 @@ __global__ void __launch_bounds__(kFdThreads, 1) decode_fused_kernel(const Fused
     uint8_t* wgu = smem + 128 + sizeof(Iq3Tables);
     uint8_t* wdn = wgu + (size_t)kGmGroups * 2 * gu_bytes;
     float* xf = reinterpret_cast<float*>(wdn + (size_t)kFdUnits * kFdSegs * dn_bytes);
-    __half* xh = reinterpret_cast<__half*>(xf + e);
-    __half* acts = xh + (size_t)kGmSplit * e;
+    uint16_t* xh = reinterpret_cast<uint16_t*>(xf + e);
+    uint16_t* acts = xh + (size_t)kGmSplit * e;
     float* red = reinterpret_cast<float*>(acts + (size_t)nseg * kGmSplit * arow);  // [group][ks][16]
     float* hp = red + kGmGroups * kGmKs * 16;                                      // [unit][half][seg][8]
     float* ws = hp + kFdUnits * 2 * kFdSegs * 8;                                   // [nseg]
@@ -130,7 +130,7 @@ __global__ void __launch_bounds__(kFdThreads, 1) decode_fused_kernel(const Fused
         ws[s] = s < A.k ? A.wts[s] : (A.shcoef ? A.shcoef[0] : 1.0f);
     }
 
-    // ---- x -> three f16 vectors in natural element order ------------------------------------
+    // ---- x -> three bf16 vectors in natural element order ------------------------------------
     bool ready = true;
     if (A.x_perm) ready = mbar_wait_bounded(bars + 6, 0, A.status);
     if (ready) {
@@ -173,7 +173,7 @@ __global__ void __launch_bounds__(kFdThreads, 1) decode_fused_kernel(const Fused
         float accg = 0.f, accu = 0.f;
         if (ok) {
             const uint8_t* rowg = wq + g * A.rb_gu;
-            const __half* xb = xh + (size_t)(g < kGmSplit ? g : 0) * e + 8 * t;
+            const uint16_t* xb = xh + (size_t)(g < kGmSplit ? g : 0) * e + 8 * t;
             const int bpw = (e >> 8) / kGmKs;
             gate_up_warp(rowg, rowg + gu_bytes, lutp, xb, g < kGmSplit, ks * bpw, (ks + 1) * bpw, t, accg, accu);
         }
@@ -193,14 +193,13 @@ __global__ void __launch_bounds__(kFdThreads, 1) decode_fused_kernel(const Fused
             const float v = silu_m(a) * bq;
             const int j = gr0 + g;
             if (t == 0) A.act[(size_t)sd.row0 * ff + j] = v;
-            if (fabsf(v) > 1.9e5f) atomicExch(A.status, 24);  // outside what the f16 triple carries
             uint32_t h[kGmSplit];
             split3(v, h);
             // every lane of the row writes a quarter of the kActRep copies
             for (int c2 = t; c2 < kActRep; c2 += 4) {
-                __half* o = A.act_h + ((size_t)(c2 * nseg + sd.row0) * kGmSplit) * arow + j;
+                uint16_t* o = A.act_h + ((size_t)(c2 * nseg + sd.row0) * kGmSplit) * arow + j;
 #pragma unroll
-                for (int n = 0; n < kGmSplit; ++n) o[(size_t)n * arow] = __ushort_as_half((unsigned short)h[n]);
+                for (int n = 0; n < kGmSplit; ++n) o[(size_t)n * arow] = (uint16_t)h[n];
             }
         }
     }
@@ -241,10 +240,10 @@ __global__ void __launch_bounds__(kFdThreads, 1) decode_fused_kernel(const Fused
         if (dn_ok && u < my_units && sa < nseg) {
             const uint8_t* ra = wdn + ((size_t)(u * kFdSegs + sa) * 8 + g) * A.rb_dn;
             const uint8_t* rbp = wdn + ((size_t)(u * kFdSegs + (two ? sb : sa)) * 8 + g) * A.rb_dn;
-            // B column g: columns 0-2 = the first expert's f16 triple, 4-6 = the second's, 3 and 7 = zero
+            // B column g: columns 0-2 = the first expert's bf16 triple, 4-6 = the second's, 3 and 7 = zero
             const int n = g & 3, which = g >> 2;
             const bool has_col = n < kGmSplit && (which == 0 || two);
-            const __half* xb = acts + ((size_t)((which ? sb : sa) * kGmSplit + (n < kGmSplit ? n : 0))) * arow + 8 * t;
+            const uint16_t* xb = acts + ((size_t)((which ? sb : sa) * kGmSplit + (n < kGmSplit ? n : 0))) * arow + 8 * t;
             const int nblk = ff >> 8, b0 = kh * (nblk >> 1), b1 = b0 + (nblk >> 1);
             float acc = 0.f;
             for (int b = b0; b < b1; ++b) {
@@ -299,8 +298,8 @@ bool decode_fused_fits(const dnb_ctx* c, int nseg, int e, int ff) {
 static size_t fused_smem(int nseg, int e, int ff) {
     const size_t rb_gu = row_bytes(T_IQ3_XXS, e), rb_dn = row_bytes(T_IQ3_XXS, ff);
     return 128 + sizeof(Iq3Tables) + (size_t)kGmGroups * 2 * kGmRows * rb_gu +
-           (size_t)kFdUnits * kFdSegs * 8 * rb_dn + (size_t)e * sizeof(float) + (size_t)kGmSplit * e * sizeof(__half) +
-           (size_t)nseg * kGmSplit * (ff + kFdPad) * sizeof(__half) +
+           (size_t)kFdUnits * kFdSegs * 8 * rb_dn + (size_t)e * sizeof(float) + (size_t)kGmSplit * e * sizeof(uint16_t) +
+           (size_t)nseg * kGmSplit * (ff + kFdPad) * sizeof(uint16_t) +
            (size_t)(kGmGroups * kGmKs * 16 + kFdUnits * 2 * kFdSegs * 8 + 16) * sizeof(float);
 }
 
@@ -322,7 +321,7 @@ int launch_decode_fused(dnb_ctx* c, cudaStream_t st, const SegDesc* seg_gu, cons
     FusedArgs A;
     A.seg_gu = seg_gu; A.seg_dn = seg_dn; A.nseg = nseg; A.k = k; A.has_shared = has_shared ? 1 : 0;
     A.e = e; A.ff = ff; A.rb_gu = (int)row_bytes(T_IQ3_XXS, e); A.rb_dn = (int)row_bytes(T_IQ3_XXS, ff);
-    A.x = x; A.x_perm = x_perm; A.act = act; A.act_h = reinterpret_cast<__half*>(act_h);
+    A.x = x; A.x_perm = x_perm; A.act = act; A.act_h = reinterpret_cast<uint16_t*>(act_h);
     A.wts = wts; A.shcoef = shcoef; A.residual = residual; A.out = out; A.gbar = gbar; A.status = c->status;
     ProfScope prof_(c, st, "decode_gate_up_down");
     DNB_CUDA(launch_k(decode_fused_kernel, dim3(c->sm_count), dim3(kFdThreads), smem, st, c->use_pdl, A));

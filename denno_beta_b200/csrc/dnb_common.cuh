@@ -90,7 +90,7 @@ struct Workspace {             // device buffers of the MoE pipeline, sized for 
           *sh = nullptr, *hin = nullptr, *out = nullptr, *shcoef = nullptr,
           *act_perm = nullptr,  // [kActRep][(k + 1) * ff]: the decode gate/up result in the down format's slot order
           *xn_perm = nullptr;   // [kActRep][e]: the decode router's normalised row in the gate format's slot order
-    uint16_t* act_h = nullptr;  // f16 triples of the fused decode kernel's activations (decode_fused.cu)
+    uint16_t* act_h = nullptr;  // bf16 triples of the fused decode kernel's activations (decode_fused.cu)
     int32_t *sels = nullptr, *row_token = nullptr, *pos = nullptr, *nseg = nullptr, *counts = nullptr, *one = nullptr;
     SegDesc *seg_gu = nullptr, *seg_dn = nullptr, *seg_sh_gu = nullptr, *seg_sh_dn = nullptr;
     uint16_t *xg_hi = nullptr, *xg_lo = nullptr, *act_hi = nullptr, *act_lo = nullptr;  // bf16 hi/lo packed rows
@@ -153,11 +153,8 @@ struct dnb_ctx {
     int gemv_impl = 0;                  // 0 = fast (default), 1 = sequential bit-exact
     bool decode_fast = true;            // one-token calls take the bulk-copy GEMV + fused router path
     bool use_pdl = true;                // programmatic dependent launch between the decode kernels
-#ifdef DNB_GEMV_MMA_OFF
-    bool gemv_mma = false;
-#else
-    bool gemv_mma = true;               // one-token IQ3_XXS gate/up on mma.sync (gemv_mma.cu) where the shape fits
-#endif
+    bool gemv_mma = true;               // one-token IQ3_XXS kernels on mma.sync (gemv_mma.cu, decode_fused.cu) where the shape fits
+    bool decode_fused = true;           // gate/up + down of a one-token IQ3_XXS block as one kernel (decode_fused.cu)
     bool use_umma = true;               // prefill chunks of Q4_K layers take the tcgen05 grouped GEMM
     void* ep = nullptr;                 // dnb::EpState of the peer-memory expert-parallel path (ep_p2p.cu)
 };

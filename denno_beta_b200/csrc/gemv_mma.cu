@@ -3,11 +3,12 @@
 // The register decode of gemv_bulk.cu spends about ten instructions per weight: with
 // 23 M weights per launch the kernel is bound by instruction issue, not by memory.
 // Here a warp decodes weights straight into the A fragment of mma.sync.m16n8k16
-// (f16 x f16 -> f32): sixteen matrix rows (eight gate rows, eight up rows of one
+// (bf16 x bf16 -> f32): sixteen matrix rows (eight gate rows, eight up rows of one
 // expert) against the activation vector, which occupies three of the eight B
-// columns as an exact three-way f16 split of its fp32 values (x = hi + lo + lo2),
+// columns as an exact three-way bf16 split of its fp32 values (x = hi + lo + lo2: 3 x 8
+// mantissa bits, fp32's exponent range, so nothing can overflow),
 // so the products lose nothing against an fp32 FMA chain.  A codebook entry is four
-// small integers (<= 62), exact in f16; the lookup table holds them as two f16 pairs,
+// small integers (<= 62), exact in bf16; the lookup table holds them as two bf16 pairs,
 // the sign bits are xor-ed in, and the sub-block scale multiplies the accumulator of
 // the sub-block's two mma instructions in fp32.  Per weight that leaves a quarter of
 // the instructions: no int-to-float conversion, no FMA, one shared-memory read of
@@ -27,7 +28,7 @@
 namespace dnb {
 
 // Dynamic shared memory: [8 mbarriers | pad to 128][codebook 32 KB][groups x (8 gate rows, 8 up rows)]
-//                        [x fp32 (staging)][x as kGmSplit f16 vectors][K-partials]
+//                        [x fp32 (staging)][x as kGmSplit bf16 vectors][K-partials]
 __global__ void __launch_bounds__(kGmThreads, 1)
 gate_up_mma_kernel(const SegDesc* __restrict__ seg, int nseg, int n_in, int n_out, int rb, int ngroups,
                    const float* __restrict__ x, const float* __restrict__ x_perm, float* __restrict__ out,
@@ -38,7 +39,7 @@ gate_up_mma_kernel(const SegDesc* __restrict__ seg, int nseg, int n_in, int n_ou
     const int mat_bytes = kGmRows * rb;  // 8 rows of IQ3_XXS: a multiple of 16 bytes
     uint8_t* wbase = smem + 128 + sizeof(Iq3Tables);
     float* xf = reinterpret_cast<float*>(wbase + (size_t)kGmGroups * 2 * mat_bytes);
-    __half* xh = reinterpret_cast<__half*>(xf + n_in);
+    uint16_t* xh = reinterpret_cast<uint16_t*>(xf + n_in);
     float* red = reinterpret_cast<float*>(xh + (size_t)kGmSplit * n_in);  // [group][ks][16]
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -70,7 +71,7 @@ gate_up_mma_kernel(const SegDesc* __restrict__ seg, int nseg, int n_in, int n_ou
         mbar_expect_tx(bars + kGmGroups + 1, (uint32_t)(n_in * sizeof(float)));
         bulk_g2s(xf, x_perm + (size_t)(blockIdx.x % kActRep) * n_in, (uint32_t)(n_in * sizeof(float)), bars + kGmGroups + 1);
     }
-    // x -> three f16 vectors in natural element order
+    // x -> three bf16 vectors in natural element order
     bool ready = true;
     if (x_perm) ready = mbar_wait_bounded(bars + kGmGroups + 1, 0, status);
     const int nunits = n_in >> 5;
@@ -103,7 +104,7 @@ gate_up_mma_kernel(const SegDesc* __restrict__ seg, int nseg, int n_in, int n_ou
         const uint8_t* rowg = wq + g * rb;
         const uint8_t* rowu = rowg + mat_bytes;
         const Iq3Lane lutp(lut, lane);
-        const __half* xb = xh + (size_t)(g < kGmSplit ? g : 0) * n_in + 8 * t;
+        const uint16_t* xb = xh + (size_t)(g < kGmSplit ? g : 0) * n_in + 8 * t;
         const int bpw = (n_in >> 8) / kGmKs;
         gate_up_warp(rowg, rowu, lutp, xb, g < kGmSplit, ks * bpw, (ks + 1) * bpw, t, accg, accu);
     }
@@ -142,7 +143,7 @@ int launch_gate_up_mma(dnb_ctx* c, cudaStream_t st, const SegDesc* seg, int nseg
     const int grid = ngroups < c->sm_count ? ngroups : c->sm_count;
     if ((long)grid * kGmGroups < ngroups) return DNB_DECLINED;
     const size_t smem = 128 + sizeof(Iq3Tables) + (size_t)kGmGroups * 2 * kGmRows * rb +
-                        (size_t)n_in * sizeof(float) + (size_t)kGmSplit * n_in * sizeof(__half) +
+                        (size_t)n_in * sizeof(float) + (size_t)kGmSplit * n_in * sizeof(uint16_t) +
                         (size_t)kGmGroups * kGmKs * 16 * sizeof(float);
     if (smem > 200 * 1024) return DNB_DECLINED;
     int rc = upload_tables_m(c->device);

@@ -1,7 +1,8 @@
 // IQ3_XXS decode into mma.sync fragments: what the one-token kernels of gemv_mma.cu and
 // decode_fused.cu share.  Each translation unit that includes this header owns a copy of
-// the f16 codebook and uploads it once per device.
+// the bf16 codebook and uploads it once per device.
 #pragma once
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
 #include "dnb_common.cuh"
@@ -15,9 +16,9 @@ constexpr int kGmRows = 8;     // rows of one matrix per group (x2 matrices = th
 constexpr int kGmKs = 4;       // warps that split K within a group
 constexpr int kGmGroups = 5;   // groups a CTA can hold
 constexpr int kGmThreads = kGmGroups * kGmKs * 32;
-constexpr int kGmSplit = 3;    // f16 terms per activation value
+constexpr int kGmSplit = 3;    // bf16 terms per activation value
 
-// What a CTA copies into shared memory in one bulk copy: the IQ3_XXS codebook as f16 pairs,
+// What a CTA copies into shared memory in one bulk copy: the IQ3_XXS codebook as bf16 pairs,
 // entry e of copy r at [e * kLutRep + r]; .x = elements 0,1, .y = elements 2,3.  (A second table
 // with ready-made sign masks was tried: its 16-byte lookups cost more shared-memory cycles than
 // the multiply-and-mask below costs issue slots, and the kernels got slower.)
@@ -34,7 +35,12 @@ static int upload_tables_m(int device) {
     for (int e = 0; e < 256; ++e) {
         const uint32_t w = dnb_iq3xxs_grid[e];
         uint32_t h[4];
-        for (int j = 0; j < 4; ++j) h[j] = __half_as_ushort(__float2half((float)((w >> (8 * j)) & 0xFFu)));
+        for (int j = 0; j < 4; ++j) {
+            const float f = (float)((w >> (8 * j)) & 0xFFu);  // <= 62: its fp32 pattern has nothing below bit 16
+            uint32_t bits;
+            memcpy(&bits, &f, 4);
+            h[j] = bits >> 16;
+        }
         for (int r = 0; r < kLutRep; ++r) tb.grid[e * kLutRep + r] = make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16));
     }
     DNB_CUDA(cudaMemcpyToSymbol(g_iq3_tables, &tb, sizeof(tb)));
@@ -47,22 +53,18 @@ struct Iq3Lane {
     __device__ __forceinline__ Iq3Lane(const Iq3Tables* tb, int lane) : grid(tb->grid + (lane & (kLutRep - 1))) {}
 };
 
-__device__ __forceinline__ uint32_t f16_sat(float v) {
-    uint16_t h;
-    asm("cvt.rn.satfinite.f16.f32 %0, %1;" : "=h"(h) : "f"(v));
-    return h;
-}
+__device__ __forceinline__ uint32_t bf16_bits(float v) { return __bfloat16_as_ushort(__float2bfloat16_rn(v)); }
 __device__ __forceinline__ float silu_m(float v) { return v / (1.0f + expf(-v)); }
-__device__ __forceinline__ float f16_val(uint32_t h) { return __half2float(__ushort_as_half((unsigned short)h)); }
+__device__ __forceinline__ float bf16_val(uint32_t h) { return __uint_as_float(h << 16); }
 
-__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                         uint32_t b1) {
-    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// Eight weights of one IQ3_XXS sub-block as four signed f16 pairs (without the scale):
+// Eight weights of one IQ3_XXS sub-block as four signed bf16 pairs (without the scale):
 // `idx` = the two codebook indices of this lane's quarter, `code` = its 7 sign bits.
 __device__ __forceinline__ void iq3_pairs(const Iq3Lane& L, uint32_t idx, uint32_t code, uint32_t (&p)[4]) {
     const uint32_t sg = code | ((__popc(code) & 1u) << 7);  // bit 7 makes the number of minus signs even
@@ -74,9 +76,9 @@ __device__ __forceinline__ void iq3_pairs(const Iq3Lane& L, uint32_t idx, uint32
 }
 
 // C = A * B with a zero accumulator
-__device__ __forceinline__ void mma_f16_z(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+__device__ __forceinline__ void mma_bf16_z(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                           uint32_t b1) {
-    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
         : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
 }
@@ -93,24 +95,25 @@ __device__ __forceinline__ void iq3_subblock_mma(const uint8_t* ba, const uint8_
     uint32_t p[4], u4[4];
     iq3_pairs(lutp, ida, (aux_a >> (7 * t)) & 127u, p);
     iq3_pairs(lutp, idb, (aux_b >> (7 * t)) & 127u, u4);
-    mma_f16_z(c, p[0], u4[0], p[1], u4[1], y.x, y.y);
-    mma_f16(c, p[2], u4[2], p[3], u4[3], y.z, y.w);
+    mma_bf16_z(c, p[0], u4[0], p[1], u4[1], y.x, y.y);
+    mma_bf16(c, p[2], u4[2], p[3], u4[3], y.z, y.w);
 }
 // d * (0.5 + s) * 0.5 = (d / 4) * (2 s + 1), exact in fp32 either way (kquant.rs:667); dq = d / 4
 __device__ __forceinline__ float iq3_scale(float dq, uint32_t aux) { return fmaf((float)(aux >> 28), dq + dq, dq); }
 
-// Three-way f16 split of an fp32 value: v = h0 + h1 + h2 up to 2^-33 |v| (|v| < 1.9e5).
+// Three-way bf16 split of an fp32 value: three 8-bit mantissas carry its 24 bits, and bf16 has fp32's
+// exponent range, so v = h0 + h1 + h2 holds for every finite v (the subtractions are exact).
 __device__ __forceinline__ void split3(float v, uint32_t (&h)[kGmSplit]) {
 #pragma unroll
     for (int n = 0; n < kGmSplit; ++n) {
-        h[n] = f16_sat(v);
-        v -= f16_val(h[n]);
+        h[n] = bf16_bits(v);
+        v -= bf16_val(h[n]);
     }
 }
 // A gate/up group's share of one warp: blocks [b0, b1) of 8 gate rows (rowg: this lane's row g)
 // and 8 up rows.  After the call lanes t = 0 and t = 1 of every row hold the row's two totals.
 __device__ __forceinline__ void gate_up_warp(const uint8_t* rowg, const uint8_t* rowu, const Iq3Lane& lutp,
-                                             const __half* xb, bool has_col, int b0, int b1, int t, float& accg,
+                                             const uint16_t* xb, bool has_col, int b0, int b1, int t, float& accg,
                                              float& accu) {
     for (int b = b0; b < b1; ++b) {
         const uint8_t* bg = rowg + b * 98;

@@ -118,7 +118,10 @@ int dnb_gemv_dev(dnb_ctx* ctx, int ggml_type, const void* w_dev, int k, int n, c
  * results equal the CPU scalar path bit for bit (kernels_moe.cu contract,
  * cuda.rs:44991-45057).  2: the general tiled fp32 kernels everywhere -- one-token calls
  * skip the bulk-copy decode kernels and prefill chunks skip the tcgen05 grouped
- * GEMM (A/B checks between kernel families). */
+ * GEMM (A/B checks between kernel families).  3: as 0, but one-token IQ3_XXS blocks
+ * take the register-decode kernels instead of the mma.sync ones.  4: as 0, but
+ * the mma.sync gate/up kernel and the down kernel run as two launches instead of
+ * the fused one. */
 int dnb_set_gemv_impl(dnb_ctx* ctx, int impl);
 
 /* ---- MoE model: resident expert table ----------------------------------------

@@ -192,14 +192,29 @@ def config1(orc):
     c.close()
 
 
-def test_config1_decode(orc, config1):
+@pytest.mark.parametrize("impl", [0, 4, 3])
+def test_config1_decode(orc, config1, impl):
+    """One token of config 1 through each family of one-token kernels: 0 = gate/up, grid barrier
+    and down fused into one mma.sync kernel; 4 = the mma.sync gate/up kernel and the down kernel
+    as two launches; 3 = the register-decode kernels.  Each against the oracle, bit-identical
+    run to run, with and without the residual of the stack entry point."""
     c, L = config1
-    h = orc.synth_normal(SEED, 2000, 1.0, 2048)
-    out, sels, wts = c.moe_block(0, h, want_routing=True)
-    err, redo = check_block(orc, L, h.reshape(1, -1), out, sels, wts)
-    assert err <= 1e-3 and redo == 0
-    out2 = c.moe_block(0, h)
-    assert np.array_equal(out.view(np.uint32), out2.view(np.uint32))
+    c.set_gemv_impl(impl)
+    try:
+        for seed in (2000, 2001, 2002):
+            h = orc.synth_normal(SEED, seed, 1.0, 2048)
+            out, sels, wts = c.moe_block(0, h, want_routing=True)
+            err, redo = check_block(orc, L, h.reshape(1, -1), out, sels, wts)
+            print("impl %d seed %d: %.3g" % (impl, seed, err))
+            assert err <= 1e-3 and redo == 0
+            for _ in range(3):  # the third call replays the captured graph
+                out2 = c.moe_block(0, h)
+                assert np.array_equal(out.view(np.uint32), out2.view(np.uint32))
+            stack = c.moe_stack(h.reshape(1, -1))
+            assert rel_err(stack, (h + out).astype(np.float32).reshape(1, -1)) <= 1e-6
+        assert c.device_status() == 0
+    finally:
+        c.set_gemv_impl(0)
 
 
 def test_config1_batches(orc, config1):
