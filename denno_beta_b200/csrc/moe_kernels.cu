@@ -914,4 +914,23 @@ int launch_add_inplace(dnb_ctx* c, cudaStream_t st, float* h, const float* d, si
     return DNB_OK;
 }
 
+// A few token rows from the caller's pinned host buffer into HBM, as a kernel instead of a copy
+// node: the router kernel behind it is chained with programmatic dependent launch, so its
+// prologue (router rows and norm weights into registers) runs while these loads cross PCIe; a
+// copy node would hold the whole router launch back until the copy has ended.
+__global__ void __launch_bounds__(512) stage_in_kernel(const float4* __restrict__ src, float4* __restrict__ dst, int n4) {
+    pdl_launch_dependents();
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += gridDim.x * blockDim.x) dst[i] = src[i];
+}
+
+int launch_stage_in(dnb_ctx* c, cudaStream_t st, const float* host_pinned, float* dst, size_t n) {
+    if (n % 4 || n / 4 > (1u << 20)) return DNB_DECLINED;
+    const int n4 = (int)(n / 4);
+    ProfScope prof_(c, st, "stage_in");
+    DNB_CUDA(launch_k(stage_in_kernel, dim3((n4 + 511) / 512), dim3(512), 0, st, c->use_pdl,
+                      reinterpret_cast<const float4*>(host_pinned), reinterpret_cast<float4*>(dst), n4));
+    c->launches++;
+    return DNB_OK;
+}
+
 }  // namespace dnb

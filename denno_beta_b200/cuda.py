@@ -35,6 +35,13 @@ def _p(a):
     return None if a is None else a.ctypes.data_as(C.c_void_p)
 
 
+def host_ptr(a):
+    """ctypes pointer to a contiguous array's first byte, for reuse across calls (the array must
+    stay alive and in place)."""
+    assert a.flags["C_CONTIGUOUS"]
+    return C.c_void_p(a.ctypes.data)
+
+
 def _f32(a, shape=None):
     a = np.ascontiguousarray(a, dtype=np.float32)
     return a if shape is None else a.reshape(shape)
@@ -198,9 +205,15 @@ class CudaCtx:
             return None
         return (out, sels, wts) if want_routing else out
 
-    def moe_block_into(self, layer, h, out):
-        """The allocation-free form used in timed loops (h, out: contiguous fp32 arrays)."""
-        return check(self.lib.dnb_moe_block(self.h, layer, _p(h), h.shape[0], _p(out), None, None), True)
+    def moe_block_into(self, layer, h, out, nt=None):
+        """The allocation-free form used in timed loops.  h, out: contiguous fp32 arrays, or the
+        pointers host_ptr() made of them once (building a ctypes pointer from an array costs ~2 us,
+        a tenth of a decode call); with pointers the token count nt must be given."""
+        if nt is None:
+            nt = h.shape[0]
+        hp = h if isinstance(h, C.c_void_p) else _p(h)
+        op = out if isinstance(out, C.c_void_p) else _p(out)
+        return check(self.lib.dnb_moe_block(self.h, layer, hp, nt, op, None, None), True)
 
     def moe_block_dev(self, layer, h_ptr, nt, out_ptr):
         return check(self.lib.dnb_moe_block_dev(self.h, layer, C.c_void_p(h_ptr), nt, C.c_void_p(out_ptr)), True)
