@@ -217,6 +217,36 @@ def test_config1_decode(orc, config1, impl):
         c.set_gemv_impl(0)
 
 
+@pytest.mark.parametrize("shape", [(1024, 512, 32, 4, True), (2048, 1024, 16, 2, False), (1024, 512, 64, 10, True)])
+def test_fused_decode_other_shapes(orc, shape):
+    """The fused one-token kernel away from config 1: fewer down units than CTAs, an odd and an
+    even number of segments, two 256-blocks per K half, the most segments 148 SMs take at ff 512."""
+    from denno_beta_b200 import cuda as cu
+
+    e, ff, ne, k, shared = shape
+    c = cu.CudaCtx(0)
+    try:
+        assert c.moe_config(1, e, ff, ne, k)
+        L = make_layer(orc, c, 0, orc.IQ3_XXS, e, ff, ne, k, shared=shared)
+        for seed in (2300, 2301):
+            h = orc.synth_normal(SEED, seed, 1.0, e)
+            out, sels, wts = c.moe_block(0, h, want_routing=True)
+            err, _ = check_block(orc, L, h.reshape(1, -1), out, sels, wts)
+            assert err <= 1e-3, "%r seed %d: %.3g" % (shape, seed, err)
+            c.set_gemv_impl(3)
+            try:
+                ref = c.moe_block(0, h)
+            finally:
+                c.set_gemv_impl(0)
+            assert rel_err(out, ref) <= 2e-5
+            launches = c.launch_count()
+            c.moe_block(0, h)
+            assert c.launch_count() - launches == 3, "stage-in, router and the fused kernel expected"
+        assert c.device_status() == 0
+    finally:
+        c.close()
+
+
 def test_config1_batches(orc, config1):
     c, L = config1
     for nt in (8, 32):
