@@ -70,7 +70,7 @@ __device__ __forceinline__ unsigned long long atom_add_acq_rel(unsigned long lon
 // Dynamic shared memory:
 // [8 mbarriers | flags, pad to 128][codebook 32 KB][gate/up rows][down rows][x fp32][x bf16 x3]
 // [activations bf16 x3, all segments][gate/up K-partials][down partials][routing weights]
-__global__ void __launch_bounds__(kFdThreads, 1) decode_fused_kernel(const FusedArgs A) {
+__global__ void __maxnreg__(64) decode_fused_kernel(const FusedArgs A) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem);  // [0..4] gate/up groups, [5] codebook, [6] x, [7] down rows
     int* flags = reinterpret_cast<int*>(smem + 64);      // [0] barrier passed
@@ -182,7 +182,7 @@ __global__ void __launch_bounds__(kFdThreads, 1) decode_fused_kernel(const Fused
             rq[ks * 16 + g] = accg;
             rq[ks * 16 + 8 + g] = accu;
         }
-        asm volatile("bar.sync %0, %1;" ::"r"(q + 1), "r"(kGmKs * 32) : "memory");
+        group_barrier(q);
         if (ks == 0 && ok) {
             float a = rq[g], bq = rq[8 + g];
 #pragma unroll
@@ -317,6 +317,9 @@ int launch_decode_fused(dnb_ctx* c, cudaStream_t st, const SegDesc* seg_gu, cons
     int rc = upload_tables_m(c->device);
     if (rc != DNB_OK) return rc;
     static SmemGrant grant;
+    if (grant.got[c->device] < smem)  // first use on this device: also pin the carve-out the router kernel shares
+        DNB_CUDA(cudaFuncSetAttribute(decode_fused_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                      cudaSharedmemCarveoutMaxShared));
     DNB_CUDA(grant_smem(grant, c->device, decode_fused_kernel, smem));
     FusedArgs A;
     A.seg_gu = seg_gu; A.seg_dn = seg_dn; A.nseg = nseg; A.k = k; A.has_shared = has_shared ? 1 : 0;

@@ -451,7 +451,9 @@ int launch_seg_gemv_m1(dnb_ctx* c, cudaStream_t st, int type, bool fused, bool x
     if (!seg && !single_p) return DNB_ERR_ARG;
     if (row_bytes(type, n_in) == 0 || n_in % 32 || n_out <= 0 || nseg_max <= 0) return DNB_DECLINED;
     int rc;
-    if (type == T_IQ3_XXS && fused && xshared && seg && !nseg_dev && !row_token && c->gemv_mma) {
+    // The mma.sync gate/up kernel as a launch of its own is taken only on request (dnb_set_gemv_impl 4):
+    // beside the register-decode down kernel it measured no faster than the register-decode gate/up.
+    if (type == T_IQ3_XXS && fused && xshared && seg && !nseg_dev && !row_token && c->gemv_mma && !c->decode_fused) {
         rc = launch_gate_up_mma(c, st, seg, nseg_max, n_in, n_out, x, out, pname, perm);
         if (rc != DNB_DECLINED) return rc;
     }

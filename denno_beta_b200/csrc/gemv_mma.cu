@@ -113,7 +113,7 @@ gate_up_mma_kernel(const SegDesc* __restrict__ seg, int nseg, int n_in, int n_ou
         rq[ks * 16 + g] = accg;
         rq[ks * 16 + 8 + g] = accu;
     }
-    asm volatile("bar.sync %0, %1;" ::"r"(q + 1), "r"(kGmKs * 32) : "memory");
+    group_barrier(q);
     if (ks != 0 || !ok) return;
     float a = rq[g], bq = rq[8 + g];
 #pragma unroll

@@ -135,4 +135,16 @@ __device__ __forceinline__ void gate_up_warp(const uint8_t* rowg, const uint8_t*
     accu += __shfl_xor_sync(0xffffffffu, accu, 1);
 }
 
+// Barrier of the kGmKs warps of gate/up group q (named barriers 1 .. kGmGroups).  The ids are
+// immediates so that the kernel reserves only the barriers it uses, not all sixteen.
+__device__ __forceinline__ void group_barrier(int q) {
+    switch (q) {
+        case 0: asm volatile("bar.sync 1, %0;" ::"n"(kGmKs * 32) : "memory"); break;
+        case 1: asm volatile("bar.sync 2, %0;" ::"n"(kGmKs * 32) : "memory"); break;
+        case 2: asm volatile("bar.sync 3, %0;" ::"n"(kGmKs * 32) : "memory"); break;
+        case 3: asm volatile("bar.sync 4, %0;" ::"n"(kGmKs * 32) : "memory"); break;
+        default: asm volatile("bar.sync 5, %0;" ::"n"(kGmKs * 32) : "memory"); break;
+    }
+}
+
 }  // namespace dnb

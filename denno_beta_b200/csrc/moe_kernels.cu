@@ -561,6 +561,15 @@ template <int NV>
 static int launch_router_decode_t(dnb_ctx* c, cudaStream_t st, const float* h, const Model& M, const Layer& L,
                                   Workspace& w, bool fold_shared, unsigned int* ticket) {
     const size_t smem = (size_t)M.e * sizeof(float);
+    // The same shared-memory carve-out as the fused gate/up + down kernel, so that this kernel's CTAs can
+    // take their places beside that kernel's (an SM is not re-partitioned while CTAs run on it) and
+    // fetch their router rows while it still computes.
+    static SmemGrant carve;
+    if (carve.got[c->device < 64 && c->device >= 0 ? c->device : 0] == 0) {
+        DNB_CUDA(cudaFuncSetAttribute(router_decode_kernel<NV>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                      cudaSharedmemCarveoutMaxShared));
+        carve.got[c->device < 64 && c->device >= 0 ? c->device : 0] = 1;
+    }
     ProfScope prof_(c, st, "router_decode_fused");
     DNB_CUDA(launch_k(router_decode_kernel<NV>, dim3((M.ne + 3) / 4), dim3(128), smem, st, c->use_pdl, h,
                       (const float*)L.norm_w, M.eps, M.e, (const float*)L.router_w, (const float*)L.router_bias, M.ne, M.k,
