@@ -501,14 +501,6 @@ router_decode_kernel(const float* __restrict__ h, const float* __restrict__ norm
         for (int i = tid; i < e; i += 128) xs[i] = h[i];
     }
     __syncthreads();
-    if (blockIdx.x == 0 && xn)
-        for (int i = tid; i < e; i += 128) xn[i] = xs[i];
-    // every CTA holds the normalised row: the first kActRep each publish one copy in the
-    // slot order of the gate/up format, for that kernel's CTAs to take with a bulk copy
-    if (xn_perm && (int)blockIdx.x < kActRep) {
-        float* o = xn_perm + (size_t)blockIdx.x * e;
-        for (int i = tid; i < e; i += 128) o[slot_index(gate_type, i, e >> 5)] = xs[i];
-    }
     if (row < ne) {
         const float4* x4 = reinterpret_cast<const float4*>(xs);
         float acc = 0.f;
@@ -535,6 +527,16 @@ router_decode_kernel(const float* __restrict__ h, const float* __restrict__ norm
         if (is_last) *ticket = 0u;  // ready for the next launch
     }
     __syncthreads();
+    // The normalised row for the next kernel, written only now: these 16 KB of stores are not what
+    // the last CTA waits for, and in front of the ticket its release would have had to wait for them.
+    if (blockIdx.x == 0 && xn)
+        for (int i = tid; i < e; i += 128) xn[i] = xs[i];
+    // every CTA holds the normalised row: the first kActRep each publish one copy in the
+    // slot order of the gate/up format, for that kernel's CTAs to take with a bulk copy
+    if (xn_perm && (int)blockIdx.x < kActRep) {
+        float* o = xn_perm + (size_t)blockIdx.x * e;
+        for (int i = tid; i < e; i += 128) o[slot_index(gate_type, i, e >> 5)] = xs[i];
+    }
     if (!is_last) return;
     topk_block(logits, ne, k, norm_topk, sm, sels, wts, nullptr);
     __syncthreads();
