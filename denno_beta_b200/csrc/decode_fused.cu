@@ -317,7 +317,7 @@ int launch_decode_fused(dnb_ctx* c, cudaStream_t st, const SegDesc* seg_gu, cons
     int rc = upload_tables_m(c->device);
     if (rc != DNB_OK) return rc;
     static SmemGrant grant;
-    if (grant.got[c->device] < smem)  // first use on this device: also pin the carve-out the router kernel shares
+    if (c->device >= 0 && c->device < 64 && grant.got[c->device] < smem)  // first use on this device: also pin the carve-out the router kernel shares
         DNB_CUDA(cudaFuncSetAttribute(decode_fused_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
                                       cudaSharedmemCarveoutMaxShared));
     DNB_CUDA(grant_smem(grant, c->device, decode_fused_kernel, smem));
