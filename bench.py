@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Benchmark of the quantised-MoE expert path on B200 (one JSON line on stdout).
 
-Headline workload (N=1): BASELINE config 1 -- one sparse-MoE block, decode, 1 token:
+Headline workload (N=1): config 1 of the benchmark set -- one sparse-MoE block, decode, 1 token:
 RMSNorm -> router (512 x 2048 fp32) -> softmax top-10 + renorm -> 10 routed + 1 shared
 IQ3_XXS expert (gate/up 512x2048, down 2048x512) -> SwiGLU -> weighted sum.  A "step"
 is one token through one block; the block rotates over LAYERS independent weight

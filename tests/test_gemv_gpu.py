@@ -71,7 +71,7 @@ def test_sequential_kernel_is_bit_exact(orc, ctx, name):
 
 
 def test_config0_q4k_4096(orc, ctx):
-    """BASELINE config 0: W [4096, 4096] Q4_K, x ~ N(0,1), batch 1."""
+    """Benchmark config 0: W [4096, 4096] Q4_K, x ~ N(0,1), batch 1."""
     from denno_beta_b200 import cuda as cu
 
     w, x = _case(orc, orc.Q4_K, 4096, 4096, 1)

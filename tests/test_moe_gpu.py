@@ -182,7 +182,7 @@ def test_grouped_gemm(orc, small):
 
 @pytest.fixture(scope="module")
 def config1(orc):
-    """BASELINE config 1 at full size: e 2048, ff 512, 512 experts, top-10 + shared, IQ3_XXS."""
+    """Benchmark config 1 at full size: e 2048, ff 512, 512 experts, top-10 + shared, IQ3_XXS."""
     from denno_beta_b200 import cuda as cu
 
     c = cu.CudaCtx(0)
@@ -259,7 +259,7 @@ def test_config1_batches(orc, config1):
 
 @pytest.fixture(scope="module")
 def config2(orc):
-    """BASELINE config 2 at full size: the same block with Q4_K experts and a Zipf router bias."""
+    """Benchmark config 2 at full size: the same block with Q4_K experts and a Zipf router bias."""
     from denno_beta_b200 import cuda as cu
 
     c = cu.CudaCtx(0)
