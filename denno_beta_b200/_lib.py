@@ -20,6 +20,8 @@ SIGNATURES = {
     "dnb_sync": (_i, [_vp]),
     "dnb_launch_count": (_u64, [_vp]),
     "dnb_device_status": (_i, [_vp, C.POINTER(C.c_int)]),
+    "dnb_clear_status": (_i, [_vp]),
+    "dnb_set_wait_limits": (_i, [_vp, _i, _i, _i]),
     "dnb_timer_start": (_i, [_vp]),
     "dnb_timer_stop": (_i, [_vp, _fp]),
     "dnb_use_graphs": (_i, [_vp, _i]),
@@ -47,6 +49,10 @@ SIGNATURES = {
     "dnb_router_topk": (_i, [_vp, _i, _vp, _i, _vp, _vp, _vp]),
     "dnb_router_topk_static": (_i, [_vp, _i, _vp, _i, _vp, _vp, _vp]),
     "dnb_grouped_gemm": (_i, [_vp, _i, _i, _vp, _i, _vp, _vp]),
+    "dnb_build_grouped_batch": (_i, [_vp, _i, _vp, _i, _vp, _vp, _vp, _vp]),
+    "dnb_seg_gemv": (_i, [_vp, _i, _i, _vp, _i, _vp, _sz, _vp, _sz]),
+    "dnb_seg_gemv_pair": (_i, [_vp, _i, _vp, _i, _vp, _sz, _vp, _vp, _sz]),
+    "dnb_router_gemv": (_i, [_vp, _i, _vp, _i, _vp]),
     "dnb_moe_set_expert_shard": (_i, [_vp, _i, _i]),
     "dnb_moe_route_dev": (_i, [_vp, _i, _vp, _i, _vp, _vp, _vp]),
     "dnb_expert_rows_dev": (_i, [_vp, _i, _vp, _vp, _i, _i, _vp]),
@@ -54,6 +60,7 @@ SIGNATURES = {
     "dnb_ep_init": (_i, [_vp, _i, _i, _i, _vp]),
     "dnb_ep_connect": (_i, [_vp, _vp]),
     "dnb_ep_block_dev": (_i, [_vp, _i, _vp, _i, _vp]),
+    "dnb_ep_connect_loopback": (_i, [_vp]),
     "dnb_moe_stack": (_i, [_vp, _vp, _i, _vp]),
     "dnb_moe_stack_dev": (_i, [_vp, _vp, _i]),
 }

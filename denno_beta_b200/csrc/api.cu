@@ -109,12 +109,14 @@ static int ensure_ws(dnb_ctx* c, int nt) {
 
 int ensure_workspace(dnb_ctx* c, int nt) { return ensure_ws(c, nt); }
 
-static int grow(Scratch& s, size_t bytes) {
+static int grow(Scratch& s, size_t bytes, bool pinned_host = false) {
     if (bytes <= s.cap) return DNB_OK;
-    if (s.p) cudaFree(s.p);
+    if (s.p) {
+        if (pinned_host) cudaFreeHost(s.p); else cudaFree(s.p);
+    }
     s.p = nullptr;
     s.cap = 0;
-    DNB_CUDA(cudaMalloc(&s.p, bytes));
+    if (pinned_host) DNB_CUDA(cudaMallocHost(&s.p, bytes)); else DNB_CUDA(cudaMalloc(&s.p, bytes));
     s.cap = bytes;
     return DNB_OK;
 }
@@ -180,6 +182,24 @@ static cudaError_t wait_short(cudaStream_t st) {
         if ((i & 63) == 63 && std::chrono::steady_clock::now() - t0 > std::chrono::milliseconds(2)) break;
     }
     return cudaStreamSynchronize(st);
+}
+
+// After the stream synchronisation of a host-buffer call: did a bounded wait give up on the
+// device since the word was last cleared?  Then the call's result is not valid: nothing is
+// copied to the caller, the word is cleared so that the next call is judged on its own, and
+// the call reports DNB_DECLINED ("did not run, out untouched": cuda.rs:21024-21027,
+// 8785-8788).  A grid barrier that ran out (23) also retires the one-kernel decode form
+// for this context: the two-launch form has no inter-CTA wait.
+static int finish_checked(dnb_ctx* c, const char* what) {
+    const int st = *reinterpret_cast<volatile int*>(c->status_host);
+    if (st == 0) return DNB_OK;
+    *reinterpret_cast<volatile int*>(c->status_host) = 0;
+    if (st == 23 && c->decode_fused) {
+        c->decode_fused = false;
+        drop_graphs(c);
+    }
+    set_error("%s: a bounded device wait gave up (status %d); the result was discarded", what, st);
+    return DNB_DECLINED;
 }
 
 static bool layer_ready(const dnb_ctx* c, int layer, bool need_router) {
@@ -429,8 +449,11 @@ int dnb_init(int device, dnb_ctx** out) {
     DNB_CUDA(cudaEventCreateWithFlags(&c->ev_join, cudaEventDisableTiming));
     DNB_CUDA(cudaEventCreate(&c->ev_t0));
     DNB_CUDA(cudaEventCreate(&c->ev_t1));
-    DNB_CUDA(cudaMalloc((void**)&c->status, sizeof(int)));
-    DNB_CUDA(cudaMemset(c->status, 0, sizeof(int)));
+    // The status word sits in pinned host memory the kernels can address: a wait that gave up is
+    // visible to the host right after the synchronisation every host-buffer call ends with.
+    DNB_CUDA(cudaHostAlloc((void**)&c->status_host, 64, cudaHostAllocMapped | cudaHostAllocPortable));
+    memset(c->status_host, 0, 64);
+    DNB_CUDA(cudaHostGetDevicePointer((void**)&c->status, c->status_host, 0));
     DNB_CUDA(cudaMalloc((void**)&c->ticket, sizeof(unsigned int)));
     DNB_CUDA(cudaMemset(c->ticket, 0, sizeof(unsigned int)));
     DNB_CUDA(cudaMalloc((void**)&c->gbar, sizeof(unsigned long long)));
@@ -460,7 +483,11 @@ void dnb_shutdown(dnb_ctx* c) {
     free_ws(c->ws);
     if (c->gemv_x.p) cudaFree(c->gemv_x.p);
     if (c->gemv_out.p) cudaFree(c->gemv_out.p);
-    if (c->status) cudaFree(c->status);
+    if (c->gemv_host.p) cudaFreeHost(c->gemv_host.p);
+    if (c->gg_x.p) cudaFree(c->gg_x.p);
+    if (c->gg_out.p) cudaFree(c->gg_out.p);
+    if (c->gg_seg.p) cudaFree(c->gg_seg.p);
+    if (c->status_host) cudaFreeHost(c->status_host);
     if (c->ticket) cudaFree(c->ticket);
     if (c->gbar) cudaFree(c->gbar);
     if (c->own_stream && c->stream) cudaStreamDestroy(c->stream);
@@ -494,8 +521,14 @@ int dnb_set_stream(dnb_ctx* c, void* stream) {
 
 int dnb_sync(dnb_ctx* c) {
     if (!c) return DNB_ERR_ARG;
+    DNB_CUDA(cudaSetDevice(c->device));
     DNB_CUDA(cudaStreamSynchronize(c->stream));
     DNB_CUDA(cudaStreamSynchronize(c->side));
+    const int st = *reinterpret_cast<volatile int*>(c->status_host);
+    if (st != 0) {  // sticky until dnb_clear_status: the device-pointer calls since then cannot be trusted
+        set_error("sync: a bounded device wait gave up (status %d) since the status was last cleared", st);
+        return DNB_DECLINED;
+    }
     return DNB_OK;
 }
 
@@ -503,8 +536,30 @@ uint64_t dnb_launch_count(dnb_ctx* c) { return c ? c->launches : 0; }
 
 int dnb_device_status(dnb_ctx* c, int* status) {
     if (!c || !status) return DNB_ERR_ARG;
+    DNB_CUDA(cudaSetDevice(c->device));
     DNB_CUDA(cudaStreamSynchronize(c->stream));
-    DNB_CUDA(cudaMemcpy(status, c->status, sizeof(int), cudaMemcpyDeviceToHost));
+    DNB_CUDA(cudaStreamSynchronize(c->side));
+    *status = *reinterpret_cast<volatile int*>(c->status_host);
+    return DNB_OK;
+}
+
+int dnb_clear_status(dnb_ctx* c) {
+    if (!c) return DNB_ERR_ARG;
+    DNB_CUDA(cudaSetDevice(c->device));
+    DNB_CUDA(cudaStreamSynchronize(c->stream));
+    DNB_CUDA(cudaStreamSynchronize(c->side));
+    *reinterpret_cast<volatile int*>(c->status_host) = 0;
+    return DNB_OK;
+}
+
+int dnb_set_wait_limits(dnb_ctx* c, int barrier_polls, int flag_polls, int barrier_bias) {
+    if (!c || barrier_polls < 1 || flag_polls < 1 || barrier_bias < 0) return DNB_ERR_ARG;
+    DNB_CUDA(cudaSetDevice(c->device));
+    DNB_CUDA(cudaDeviceSynchronize());
+    drop_graphs(c);  // the limits are kernel arguments baked into captured launches
+    c->barrier_polls = barrier_polls;
+    c->flag_polls = flag_polls;
+    c->barrier_bias = (unsigned int)barrier_bias;
     return DNB_OK;
 }
 
@@ -531,6 +586,7 @@ int dnb_dev_alloc(dnb_ctx* c, size_t bytes, void** dev) {
 
 int dnb_dev_free(dnb_ctx* c, void* dev) {
     if (!c) return DNB_ERR_ARG;
+    DNB_CUDA(cudaSetDevice(c->device));
     DNB_CUDA(cudaFree(dev));
     return DNB_OK;
 }
@@ -671,6 +727,7 @@ int dnb_gemv_dev(dnb_ctx* c, int type, const void* w_dev, int k, int n, const fl
         set_error("gemv: ggml type %d with k=%d is not handled", type, k);
         return DNB_DECLINED;
     }
+    DNB_CUDA(cudaSetDevice(c->device));
     return gemv_dev(c, type, (const uint8_t*)w_dev, k, n, x_dev, out_dev, nvec);
 }
 
@@ -688,8 +745,11 @@ int dnb_gemv(dnb_ctx* c, uint64_t uid, const float* x, float* out) {
     if ((rc = grow(c->gemv_out, (size_t)m.n * 4))) return rc;
     DNB_CUDA(cudaMemcpyAsync(c->gemv_x.p, x, (size_t)m.k * 4, cudaMemcpyHostToDevice, c->stream));
     if ((rc = gemv_dev(c, m.type, m.dev, m.k, m.n, (const float*)c->gemv_x.p, (float*)c->gemv_out.p, 1))) return rc;
-    DNB_CUDA(cudaMemcpyAsync(out, c->gemv_out.p, (size_t)m.n * 4, cudaMemcpyDeviceToHost, c->stream));
+    if ((rc = grow(c->gemv_host, (size_t)m.n * 4, true))) return rc;
+    DNB_CUDA(cudaMemcpyAsync(c->gemv_host.p, c->gemv_out.p, (size_t)m.n * 4, cudaMemcpyDeviceToHost, c->stream));
     DNB_CUDA(wait_short(c->stream));
+    if ((rc = finish_checked(c, "gemv"))) return rc;
+    memcpy(out, c->gemv_host.p, (size_t)m.n * 4);
     return DNB_OK;
 }
 
@@ -780,9 +840,12 @@ int dnb_synth_experts(dnb_ctx* c, int layer, int matrix, int type, int n_in, int
     if (rc) return rc;
     DNB_CUDA(cudaSetDevice(c->device));
     if ((rc = install_tensor(c, layer, matrix, type, n_in, n_out, n_expert, rb))) return rc;
-    const uint64_t n_blocks = (uint64_t)n_expert * n_out * (n_in / block_elems(type));
+    const uint64_t per_expert = (uint64_t)n_out * (n_in / block_elems(type));
+    const uint64_t n_blocks = (uint64_t)n_expert * per_expert;
+    // an expert-parallel shard holds experts [shard_first, shard_first + n_expert) of the full tensor
+    const uint64_t first = matrix < 3 ? (uint64_t)c->model.shard_first * per_expert : 0;
     return launch_synth_blocks(c, c->stream, type, seed, (uint64_t)layer * 16 + matrix,
-                               c->model.layers[layer].m[matrix].dev, n_blocks);
+                               c->model.layers[layer].m[matrix].dev, n_blocks, first);
 }
 
 int dnb_download_expert(dnb_ctx* c, int layer, int matrix, int expert, void* dst, size_t bytes) {
@@ -831,6 +894,7 @@ int dnb_moe_block_dev(dnb_ctx* c, int layer, const float* h_dev, int nt, float* 
         set_error("moe_block: layer %d is not fully registered", layer);
         return DNB_DECLINED;
     }
+    DNB_CUDA(cudaSetDevice(c->device));
     int rc = ensure_ws(c, nt);
     if (rc) return rc;
     return run_graphed(c, GraphKey{1, layer, nt, h_dev, out_dev}, [&]() { return block_dev(c, layer, h_dev, nt, out_dev); });
@@ -871,6 +935,7 @@ int dnb_moe_block(dnb_ctx* c, int layer, const float* h, int nt, float* out, int
     });
     if (rc) return rc;
     DNB_CUDA(nt <= 64 ? wait_short(c->stream) : cudaStreamSynchronize(c->stream));
+    if ((rc = finish_checked(c, "moe_block"))) return rc;
     memcpy(out, w.pinned_out, bytes);
     if (sels_out) memcpy(sels_out, w.pinned_sels, (size_t)nt * M.k * 4);
     if (wts_out) memcpy(wts_out, w.pinned_wts, (size_t)nt * M.k * 4);
@@ -911,6 +976,7 @@ int dnb_moe_experts(dnb_ctx* c, int layer, const float* x, int nt, const int32_t
     if ((rc = experts_dev(c, layer, w.hin, nt, w.sels, w.wts, w.out))) return rc;
     DNB_CUDA(cudaMemcpyAsync(w.pinned_out, w.out, bytes, cudaMemcpyDeviceToHost, c->stream));
     DNB_CUDA(nt <= 64 ? wait_short(c->stream) : cudaStreamSynchronize(c->stream));
+    if ((rc = finish_checked(c, "moe_experts"))) return rc;
     memcpy(out, w.pinned_out, bytes);
     return DNB_OK;
 }
@@ -937,6 +1003,7 @@ int dnb_router_topk(dnb_ctx* c, int layer, const float* x, int nt, int32_t* sels
     DNB_CUDA(cudaMemcpyAsync(w.pinned_wts, w.wts, rows * 4, cudaMemcpyDeviceToHost, c->stream));
     if (rowsum) DNB_CUDA(cudaMemcpyAsync(w.pinned_out, w.shcoef, (size_t)nt * 4, cudaMemcpyDeviceToHost, c->stream));
     DNB_CUDA(cudaStreamSynchronize(c->stream));
+    if ((rc = finish_checked(c, "router_topk"))) return rc;
     memcpy(sels, w.pinned_sels, rows * 4);
     memcpy(wts, w.pinned_wts, rows * 4);
     if (rowsum) memcpy(rowsum, w.pinned_out, (size_t)nt * 4);
@@ -967,29 +1034,204 @@ int dnb_grouped_gemm(dnb_ctx* c, int layer, int matrix, const uint32_t* segs, in
         if (m > m_max) m_max = m;
     }
     DNB_CUDA(cudaSetDevice(c->device));
-    float *dx = nullptr, *dout = nullptr;
-    SegDesc* dsd = nullptr;
-    DNB_CUDA(cudaMalloc((void**)&dx, row * t.n_in * sizeof(float)));
-    DNB_CUDA(cudaMalloc((void**)&dout, row * t.n_out * sizeof(float)));
-    DNB_CUDA(cudaMalloc((void**)&dsd, nseg * sizeof(SegDesc)));
+    // Grow-only staging buffers of the context (no allocation per call once they are large enough).
+    int rc;
+    if ((rc = grow(c->gg_x, row * t.n_in * sizeof(float)))) return rc;
+    if ((rc = grow(c->gg_out, row * t.n_out * sizeof(float)))) return rc;
+    if ((rc = grow(c->gg_seg, (size_t)nseg * sizeof(SegDesc) + 16))) return rc;
+    float* dx = (float*)c->gg_x.p;
+    float* dout = (float*)c->gg_out.p;
+    SegDesc* dsd = (SegDesc*)c->gg_seg.p;
+    int32_t* dnseg = (int32_t*)((uint8_t*)c->gg_seg.p + (size_t)nseg * sizeof(SegDesc));
+    const Model& M = c->model;
+    // Q4_K matrices of the model's own shapes with enough rows go to the tcgen05 grouped GEMM
+    // (the packed rows are split to bf16 hi/lo in the workspace's operand buffers first).
+    const bool in_e = t.n_in == M.e, in_ff = t.n_in == M.ff;
+    bool umma = c->use_umma && t.type == T_Q4_K && row >= 64 && (in_e || in_ff) && t.n_in % 256 == 0 && t.n_out % 128 == 0;
+    if (umma) {
+        if ((rc = ensure_ws(c, (int)((row + M.k) / (M.k + 1))))) return rc;
+        umma = c->ws.maps_ok;
+    }
     DNB_CUDA(cudaMemcpyAsync(dx, xs, row * t.n_in * sizeof(float), cudaMemcpyHostToDevice, c->stream));
     DNB_CUDA(cudaMemcpyAsync(dsd, sd.data(), nseg * sizeof(SegDesc), cudaMemcpyHostToDevice, c->stream));
-    int rc = launch_seg_matmul(c, c->stream, t.type, false, dsd, nullptr, nseg, t.n_in, t.n_out, dx, t.n_in, nullptr,
-                               dout, (int)m_max);
+    if (umma) {
+        Workspace& w = c->ws;
+        DNB_CUDA(cudaMemcpyAsync(dnseg, &nseg, sizeof(int32_t), cudaMemcpyHostToDevice, c->stream));
+        uint16_t* hi = in_e ? w.xg_hi : w.act_hi;
+        uint16_t* lo = in_e ? w.xg_lo : w.act_lo;
+        if ((rc = launch_gather_split(c, c->stream, dx, t.n_in, nullptr, (int)row, t.n_in, hi, lo)) == DNB_OK)
+            rc = launch_grouped_umma(c, c->stream, false, dsd, dnseg, nseg, t.n_in, t.n_out, in_e ? &w.maps_x : &w.maps_act,
+                                     (int)row, nullptr, nullptr, dout);
+    } else {
+        rc = launch_seg_matmul(c, c->stream, t.type, false, dsd, nullptr, nseg, t.n_in, t.n_out, dx, t.n_in, nullptr, dout,
+                               (int)m_max);
+    }
     if (rc == DNB_OK) {
         cudaError_t e = cudaMemcpyAsync(outs, dout, row * t.n_out * sizeof(float), cudaMemcpyDeviceToHost, c->stream);
         if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
         if (e != cudaSuccess) {
             set_error("grouped_gemm: %s", cudaGetErrorString(e));
             rc = DNB_ERR_CUDA;
+        } else {
+            rc = finish_checked(c, "grouped_gemm");
         }
     } else {
         cudaStreamSynchronize(c->stream);
     }
-    cudaFree(dx);
-    cudaFree(dout);
-    cudaFree(dsd);
     return rc;
+}
+
+// The routing tables of a chunk as the device builds them (moe_expert.rs:8309-8390
+// build_grouped_batch; exp_pf.rs:23-31 rows[]), returned to the host for inspection.
+int dnb_build_grouped_batch(dnb_ctx* c, int layer, const int32_t* sels, int nt, uint32_t* segs_out, int32_t* nseg_out,
+                            int32_t* row_token_out, int32_t* pos_out) {
+    if (!c || !sels || !segs_out || !nseg_out || nt < 1) return DNB_ERR_ARG;
+    if (!layer_ready(c, layer, false)) {
+        set_error("build_grouped_batch: layer %d has no expert tensors", layer);
+        return DNB_DECLINED;
+    }
+    const Model& M = c->model;
+    const Layer& L = M.layers[layer];
+    for (size_t i = 0; i < (size_t)nt * M.k; ++i)
+        if (sels[i] < 0 || sels[i] >= M.ne) {
+            set_error("build_grouped_batch: expert %d out of range", sels[i]);
+            return DNB_ERR_ARG;
+        }
+    DNB_CUDA(cudaSetDevice(c->device));
+    int rc = ensure_ws(c, nt);
+    if (rc) return rc;
+    Workspace& w = c->ws;
+    const size_t rows = (size_t)nt * M.k;
+    memcpy(w.pinned_sels, sels, rows * 4);
+    DNB_CUDA(cudaMemcpyAsync(w.sels, w.pinned_sels, rows * 4, cudaMemcpyHostToDevice, c->stream));
+    if ((rc = launch_route_tables(c, c->stream, w.sels, nt, M.k, M.ne, L, w, false))) return rc;
+    int32_t nseg = 0;
+    DNB_CUDA(cudaMemcpyAsync(&nseg, w.nseg, 4, cudaMemcpyDeviceToHost, c->stream));
+    DNB_CUDA(cudaStreamSynchronize(c->stream));
+    if (nseg < 0 || nseg > M.ne) return DNB_ERR_STATE;
+    std::vector<SegDesc> sd(nseg);
+    DNB_CUDA(cudaMemcpy(sd.data(), w.seg_gu, nseg * sizeof(SegDesc), cudaMemcpyDeviceToHost));
+    for (int i = 0; i < nseg; ++i) {
+        segs_out[4 * i] = (uint32_t)((sd[i].wa - L.m[0].dev) / L.m[0].expert_bytes);
+        segs_out[4 * i + 1] = sd[i].m;
+        segs_out[4 * i + 2] = sd[i].row0;
+        segs_out[4 * i + 3] = sd[i].row0;
+    }
+    *nseg_out = nseg;
+    if (row_token_out) DNB_CUDA(cudaMemcpy(row_token_out, w.row_token, rows * 4, cudaMemcpyDeviceToHost));
+    if (pos_out) DNB_CUDA(cudaMemcpy(pos_out, w.pos, rows * 4, cudaMemcpyDeviceToHost));
+    return DNB_OK;
+}
+
+// ---- legacy three-launch decode form and the standalone router GEMV ---------------------
+
+// Segment table of the legacy form (expert_batch.rs:143-170; checked like seg_extents,
+// expert_batch.rs:233-260): seg[i] = (expert, m, x_off, out_off), offsets in floats.
+// Token j of segment i reads x[x_off + j*n_in ..] and writes out[out_off + j*n_out ..].
+static int seg_gemv_run(dnb_ctx* c, const ExpertTensor& t, const uint32_t* seg, int nseg, const float* x, size_t x_len,
+                        float* out, size_t out_len, const char* what) {
+    std::vector<SegDesc> sd(nseg);
+    size_t out_rows = 0;
+    uint32_t m_max = 0;
+    for (int i = 0; i < nseg; ++i) {
+        const uint32_t ex = seg[4 * i], m = seg[4 * i + 1], xo = seg[4 * i + 2], oo = seg[4 * i + 3];
+        if (m == 0 || ex >= (uint32_t)t.n_expert || xo % (uint32_t)t.n_in || oo % (uint32_t)t.n_out ||
+            (size_t)xo + (size_t)m * t.n_in > x_len || (size_t)oo + (size_t)m * t.n_out > out_len) {
+            set_error("%s: segment %d (expert %u, m %u, x_off %u, out_off %u) breaks the table contract", what, i, ex, m, xo, oo);
+            return DNB_ERR_ARG;
+        }
+        sd[i] = SegDesc{t.dev + (size_t)ex * t.expert_bytes, nullptr, m, oo / (uint32_t)t.n_out};
+        out_rows = std::max(out_rows, (size_t)(oo / t.n_out + m));
+        m_max = std::max(m_max, m);
+    }
+    std::vector<int32_t> row_token(out_rows, 0);  // output row -> input row
+    for (int i = 0; i < nseg; ++i)
+        for (uint32_t j = 0; j < sd[i].m; ++j) row_token[sd[i].row0 + j] = (int32_t)(seg[4 * i + 2] / (uint32_t)t.n_in + j);
+    int rc;
+    if ((rc = grow(c->gg_x, x_len * sizeof(float)))) return rc;
+    if ((rc = grow(c->gg_out, out_rows * t.n_out * sizeof(float)))) return rc;
+    if ((rc = grow(c->gg_seg, (size_t)nseg * sizeof(SegDesc) + out_rows * sizeof(int32_t)))) return rc;
+    float* dx = (float*)c->gg_x.p;
+    float* dout = (float*)c->gg_out.p;
+    SegDesc* dsd = (SegDesc*)c->gg_seg.p;
+    int32_t* drt = (int32_t*)((uint8_t*)c->gg_seg.p + (size_t)nseg * sizeof(SegDesc));
+    DNB_CUDA(cudaMemcpyAsync(dx, x, x_len * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+    DNB_CUDA(cudaMemcpyAsync(dsd, sd.data(), nseg * sizeof(SegDesc), cudaMemcpyHostToDevice, c->stream));
+    DNB_CUDA(cudaMemcpyAsync(drt, row_token.data(), out_rows * sizeof(int32_t), cudaMemcpyHostToDevice, c->stream));
+    rc = DNB_DECLINED;
+    if (m_max == 1 && c->decode_fast)
+        rc = launch_seg_gemv_m1(c, c->stream, t.type, false, false, dsd, nullptr, nseg, t.n_in, t.n_out, dx, t.n_in, drt, dout,
+                                nullptr, "seg_gemv");
+    if (rc == DNB_DECLINED)
+        rc = launch_seg_matmul(c, c->stream, t.type, false, dsd, nullptr, nseg, t.n_in, t.n_out, dx, t.n_in, drt, dout,
+                               (int)m_max);
+    if (rc) {
+        cudaStreamSynchronize(c->stream);
+        return rc;
+    }
+    // rows no segment names keep whatever the caller had there: copy back segment by segment
+    for (int i = 0; i < nseg; ++i)
+        DNB_CUDA(cudaMemcpyAsync(out + seg[4 * i + 3], dout + (size_t)sd[i].row0 * t.n_out, (size_t)sd[i].m * t.n_out * sizeof(float),
+                                 cudaMemcpyDeviceToHost, c->stream));
+    DNB_CUDA(cudaStreamSynchronize(c->stream));
+    return finish_checked(c, what);
+}
+
+static const ExpertTensor* seg_tensor(dnb_ctx* c, int layer, int matrix, const char* what) {
+    if (layer < 0 || layer >= c->model.n_layer || matrix < 0 || matrix > 5 || !c->model.layers[layer].m[matrix].dev) {
+        set_error("%s: layer %d matrix %d is not registered", what, layer, matrix);
+        return nullptr;
+    }
+    return &c->model.layers[layer].m[matrix];
+}
+
+int dnb_seg_gemv(dnb_ctx* c, int layer, int matrix, const uint32_t* seg, int nseg, const float* x, size_t x_len, float* out,
+                 size_t out_len) {
+    if (!c || !seg || !x || !out || nseg < 1) return DNB_ERR_ARG;
+    const ExpertTensor* t = seg_tensor(c, layer, matrix, "seg_gemv");
+    if (!t) return DNB_DECLINED;
+    DNB_CUDA(cudaSetDevice(c->device));
+    return seg_gemv_run(c, *t, seg, nseg, x, x_len, out, out_len, "seg_gemv");
+}
+
+int dnb_seg_gemv_pair(dnb_ctx* c, int layer, const uint32_t* seg, int nseg, const float* x, size_t x_len, float* out_g,
+                      float* out_u, size_t out_len) {
+    if (!c || !seg || !x || !out_g || !out_u || nseg < 1) return DNB_ERR_ARG;
+    const ExpertTensor* tg = seg_tensor(c, layer, DNB_MAT_GATE, "seg_gemv_pair");
+    const ExpertTensor* tu = seg_tensor(c, layer, DNB_MAT_UP, "seg_gemv_pair");
+    if (!tg || !tu) return DNB_DECLINED;
+    if (tg->row_bytes != tu->row_bytes || tg->n_out != tu->n_out) {  // cuda.rs:7653-7656: rb_g != rb_u -> not run
+        set_error("seg_gemv_pair: gate and up rows differ in size");
+        return DNB_DECLINED;
+    }
+    DNB_CUDA(cudaSetDevice(c->device));
+    int rc = seg_gemv_run(c, *tg, seg, nseg, x, x_len, out_g, out_len, "seg_gemv_pair");
+    if (rc) return rc;
+    return seg_gemv_run(c, *tu, seg, nseg, x, x_len, out_u, out_len, "seg_gemv_pair");
+}
+
+int dnb_router_gemv(dnb_ctx* c, int layer, const float* x, int nt, float* logits) {
+    if (!c || !x || !logits || nt < 1) return DNB_ERR_ARG;
+    const Model& M = c->model;
+    if (layer < 0 || layer >= M.n_layer || !M.layers[layer].router_w) {
+        set_error("router_gemv: layer %d has no router", layer);
+        return DNB_DECLINED;
+    }
+    DNB_CUDA(cudaSetDevice(c->device));
+    int rc = ensure_ws(c, nt);
+    if (rc) return rc;
+    Workspace& w = c->ws;
+    const Layer& L = M.layers[layer];
+    const size_t bytes = (size_t)nt * M.e * sizeof(float), lbytes = (size_t)nt * M.ne * sizeof(float);
+    if ((rc = grow(c->gemv_host, lbytes, true))) return rc;
+    memcpy(w.pinned_in, x, bytes);
+    DNB_CUDA(cudaMemcpyAsync(w.hin, w.pinned_in, bytes, cudaMemcpyHostToDevice, c->stream));
+    if ((rc = launch_router_logits(c, c->stream, w.hin, nt, M.e, L.router_w, L.router_bias, M.ne, w.logits))) return rc;
+    DNB_CUDA(cudaMemcpyAsync(c->gemv_host.p, w.logits, lbytes, cudaMemcpyDeviceToHost, c->stream));
+    DNB_CUDA(cudaStreamSynchronize(c->stream));
+    if ((rc = finish_checked(c, "router_gemv"))) return rc;
+    memcpy(logits, c->gemv_host.p, lbytes);
+    return DNB_OK;
 }
 
 // ---- expert-parallel building blocks ---------------------------------------------------
@@ -1019,6 +1261,7 @@ int dnb_moe_route_dev(dnb_ctx* c, int layer, const float* h_dev, int nt, float* 
         set_error("moe_route: layer %d has no router", layer);
         return DNB_DECLINED;
     }
+    DNB_CUDA(cudaSetDevice(c->device));
     int rc = ensure_ws(c, nt);
     if (rc) return rc;
     const Layer& L = M.layers[layer];
@@ -1041,6 +1284,7 @@ int dnb_expert_rows_dev(dnb_ctx* c, int layer, const float* x_rows_dev, const in
         set_error("expert_rows: layer %d lacks the %s expert tensors", layer, use_shared ? "shared" : "routed");
         return DNB_DECLINED;
     }
+    DNB_CUDA(cudaSetDevice(c->device));
     int rc = ensure_ws(c, rows);
     if (rc) return rc;
     Workspace& w = c->ws;
@@ -1076,6 +1320,7 @@ int dnb_moe_combine_dev(dnb_ctx* c, int layer, const float* h_slots_dev, const f
     const Model& M = c->model;
     if (layer < 0 || layer >= M.n_layer) return DNB_ERR_ARG;
     const Layer& L = M.layers[layer];
+    DNB_CUDA(cudaSetDevice(c->device));
     int rc = ensure_ws(c, nt);
     if (rc) return rc;
     const float* coef = nullptr;
@@ -1095,6 +1340,7 @@ int dnb_moe_stack_dev(dnb_ctx* c, float* h_dev, int nt) {
             set_error("moe_stack: layer %d is not fully registered", l);
             return DNB_DECLINED;
         }
+    DNB_CUDA(cudaSetDevice(c->device));
     int rc = ensure_ws(c, nt);
     if (rc) return rc;
     return run_graphed(c, GraphKey{4, 0, nt, h_dev, nullptr}, [&]() -> int {
@@ -1133,6 +1379,7 @@ int dnb_moe_stack(dnb_ctx* c, const float* h, int nt, float* out) {
     if ((rc = dnb_moe_stack_dev(c, w.hin, nt))) return rc;
     DNB_CUDA(cudaMemcpyAsync(w.pinned_out, w.hin, bytes, cudaMemcpyDeviceToHost, c->stream));
     DNB_CUDA(cudaStreamSynchronize(c->stream));
+    if ((rc = finish_checked(c, "moe_stack"))) return rc;
     memcpy(out, w.pinned_out, bytes);
     return DNB_OK;
 }

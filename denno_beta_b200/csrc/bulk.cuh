@@ -35,7 +35,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, int* status) {
     for (int i = 0; i < (1 << 22); ++i)
         if (mbar_try_wait(bar, parity)) return true;
-    if (status) atomicExch(status, 1);
+    status_set(status, 1);
     return false;
 }
 

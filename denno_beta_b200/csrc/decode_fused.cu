@@ -54,6 +54,8 @@ struct FusedArgs {
     float* out;              // [e]
     unsigned long long* gbar;  // arrivals of all launches so far
     int* status;
+    int barrier_polls;         // acquire loads before the barrier gives up
+    unsigned int barrier_bias; // test hook: added to the arrival count waited for (0 in production)
 };
 
 __device__ __forceinline__ unsigned long long ld_acquire_u64(const unsigned long long* p) {
@@ -212,10 +214,10 @@ __global__ void __maxnreg__(64) decode_fused_kernel(const FusedArgs A) {
         // atomic publishes this CTA's stores (the bar.sync above ordered them before it), the acquire
         // load below makes the other CTAs' stores visible.
         const unsigned long long ticket = atom_add_acq_rel(A.gbar, 1ull);
-        const unsigned long long target = (ticket / gridDim.x + 1ull) * gridDim.x;
+        const unsigned long long target = (ticket / gridDim.x + 1ull) * gridDim.x + A.barrier_bias;
         bool pass = ticket + 1ull == target;
-        for (int i = 0; i < 400000 && !pass; ++i) pass = ld_acquire_u64(A.gbar) >= target;  // ~0.2 s at most
-        if (!pass) atomicExch(A.status, 23);
+        for (int i = 0; i < A.barrier_polls && !pass; ++i) pass = ld_acquire_u64(A.gbar) >= target;  // ~0.2 s at most by default
+        if (!pass) status_set(A.status, 23);
         flags[0] = pass ? 1 : 0;
     }
     __syncthreads();
@@ -321,11 +323,21 @@ int launch_decode_fused(dnb_ctx* c, cudaStream_t st, const SegDesc* seg_gu, cons
         DNB_CUDA(cudaFuncSetAttribute(decode_fused_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
                                       cudaSharedmemCarveoutMaxShared));
     DNB_CUDA(grant_smem(grant, c->device, decode_fused_kernel, smem));
+    // The grid barrier needs every CTA resident at once: one per SM.  Ask the runtime, once per
+    // device and shared-memory size, whether a CTA of this size fits an SM at all.
+    static size_t occ_ok[64] = {0};
+    if (occ_ok[c->device] != smem) {
+        int per_sm = 0;
+        DNB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_fused_kernel, kFdThreads, smem));
+        if (per_sm < 1) return DNB_DECLINED;
+        occ_ok[c->device] = smem;
+    }
     FusedArgs A;
     A.seg_gu = seg_gu; A.seg_dn = seg_dn; A.nseg = nseg; A.k = k; A.has_shared = has_shared ? 1 : 0;
     A.e = e; A.ff = ff; A.rb_gu = (int)row_bytes(T_IQ3_XXS, e); A.rb_dn = (int)row_bytes(T_IQ3_XXS, ff);
     A.x = x; A.x_perm = x_perm; A.act = act; A.act_h = reinterpret_cast<uint16_t*>(act_h);
     A.wts = wts; A.shcoef = shcoef; A.residual = residual; A.out = out; A.gbar = gbar; A.status = c->status;
+    A.barrier_polls = c->barrier_polls; A.barrier_bias = c->barrier_bias;
     ProfScope prof_(c, st, "decode_gate_up_down");
     DNB_CUDA(launch_k(decode_fused_kernel, dim3(c->sm_count), dim3(kFdThreads), smem, st, c->use_pdl, A));
     c->launches++;

@@ -144,9 +144,14 @@ struct dnb_ctx {
     std::map<uint64_t, dnb::Matrix> matrices;
     dnb::Model model;
     dnb::Workspace ws;
-    dnb::Scratch gemv_x, gemv_out;
+    dnb::Scratch gemv_x, gemv_out, gemv_host;   // gemv_host: pinned host staging of dnb_gemv's result
+    dnb::Scratch gg_x, gg_out, gg_seg;           // grow-only buffers of dnb_grouped_gemm
     int sm_count = 148;
-    int* status = nullptr;              // device status word written by kernels on internal errors
+    int* status = nullptr;              // status word the kernels write when a bounded wait gave up: pinned host memory, device address
+    int* status_host = nullptr;         // the same word as the host reads it (valid after a stream synchronisation)
+    int barrier_polls = 400000;         // polls of the fused decode kernel's grid barrier before it gives up (~0.2 s)
+    int flag_polls = 1 << 21;           // polls of an expert-parallel flag wait before it gives up (~0.25 s)
+    unsigned int barrier_bias = 0;      // test hook: added to the barrier's target so that it cannot be reached
     unsigned int* ticket = nullptr;     // "last CTA" counter of the fused decode router (self-resetting)
     unsigned long long* gbar = nullptr; // grid barrier of the fused decode kernel: arrivals of all launches so far
     uint64_t launches = 0;              // kernels launched by this context (bench accounting)
@@ -211,6 +216,15 @@ inline cudaError_t launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_
 #ifdef __CUDACC__
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// Record that a bounded wait gave up.  The status word lives in pinned host memory the device can
+// address, so the host reads it after its next stream synchronisation without a copy; a plain store
+// is enough (several reporters may race: any of their codes will do).
+__device__ __forceinline__ void status_set(int* status, int code) {
+    if (status) {
+        *reinterpret_cast<volatile int*>(status) = code;
+        __threadfence_system();
+    }
+}
 #endif
 
 // ---- launchers (defined in the .cu files) -----------------------------------
@@ -314,7 +328,7 @@ int launch_combine(dnb_ctx* c, cudaStream_t st, const float* hrow, const int32_t
                    int k, int e, const float* sh, const float* shcoef, float* out);
 int launch_shared_coef(dnb_ctx* c, cudaStream_t st, const float* x, const float* row, int nt, int e, float* coef);
 int launch_synth_blocks(dnb_ctx* c, cudaStream_t st, int type, uint64_t seed, uint64_t tensor_id, uint8_t* dst,
-                        uint64_t n_blocks);
+                        uint64_t n_blocks, uint64_t first_block = 0);
 int launch_synth_normal(dnb_ctx* c, cudaStream_t st, uint64_t seed, uint64_t tensor_id, float sigma, float* dst,
                         uint64_t n);
 

@@ -53,9 +53,9 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
-// Poll until *p >= seq; gives up after about a quarter of a second.
-__device__ __forceinline__ bool wait_flag(const uint32_t* p, uint32_t seq) {
-    for (int i = 0; i < (1 << 21); ++i) {
+// Poll until *p >= seq; gives up after `polls` tries (2^21 by default: about a quarter of a second).
+__device__ __forceinline__ bool wait_flag(const uint32_t* p, uint32_t seq, int polls) {
+    for (int i = 0; i < polls; ++i) {
         if ((int32_t)(ld_acquire_sys(p) - seq) >= 0) return true;
         __nanosleep(100);
     }
@@ -129,14 +129,14 @@ ep_plan_kernel(const int32_t* __restrict__ sels, int nt, int k, int ne, int n_lo
 // inside an expert the sources in ascending rank, inside a source the tokens ascending.
 __global__ void __launch_bounds__(1024)
 ep_offsets_kernel(const EpArena* mine, int ne, int n_local, int world, int me, uint32_t seq, int32_t* __restrict__ base,
-                  int* status) {
+                  int* status, int polls) {
     __shared__ int tot[kEpMaxExperts];   // rows of expert e over all sources
     __shared__ int mine_off[kEpMaxExperts];  // rows of expert e from sources before me
     __shared__ int ok_all;
     const int tid = threadIdx.x;
     if (tid == 0) ok_all = 1;
     __syncthreads();
-    if (tid < world && !wait_flag(&mine->cnt_flag[tid], seq)) { atomicExch(status, 21); ok_all = 0; }
+    if (tid < world && !wait_flag(&mine->cnt_flag[tid], seq, polls)) { status_set(status, 21); ok_all = 0; }
     __syncthreads();
     for (int e = tid; e < ne; e += blockDim.x) {
         int t = 0, b = 0;
@@ -168,7 +168,7 @@ ep_dispatch_kernel(const float* __restrict__ x, const int32_t* __restrict__ sels
     if (ex >= 0 && j >= 0) {
         const size_t r = (size_t)base[ex] + j;
         if (r >= (size_t)rows_total) {
-            if (tid == 0) atomicExch(status, 20);
+            if (tid == 0) status_set(status, 20);
         } else {
             const int d = ex / n_local;
             const float* xr = x + (size_t)(i / k) * e;
@@ -206,7 +206,7 @@ ep_dispatch_kernel(const float* __restrict__ x, const int32_t* __restrict__ sels
 __global__ void __launch_bounds__(1024)
 ep_build_kernel(EpArena* mine, const int32_t* __restrict__ recv_slot, int world, int n_local, int me, int e, uint32_t seq,
                 EpPeers peers, const uint8_t* gate, const uint8_t* up, const uint8_t* down, size_t eb_g, size_t eb_u,
-                size_t eb_d, SegDesc* seg_gu, SegDesc* seg_dn, int32_t* nseg, float** row_dst, int* status) {
+                size_t eb_d, SegDesc* seg_gu, SegDesc* seg_dn, int32_t* nseg, float** row_dst, int* status, int polls) {
     __shared__ int ok_all;
     __shared__ int tot[kEpMaxLocal], first[kEpMaxLocal];
     __shared__ int n_rows;
@@ -215,7 +215,7 @@ ep_build_kernel(EpArena* mine, const int32_t* __restrict__ recv_slot, int world,
     __syncthreads();
     if (tid < 2 * world) {
         const uint32_t* f = tid < world ? &mine->cnt_flag[tid] : &mine->data_flag[tid - world];
-        if (!wait_flag(f, seq)) { atomicExch(status, 21); ok_all = 0; }
+        if (!wait_flag(f, seq, polls)) { status_set(status, 21); ok_all = 0; }
     }
     __syncthreads();
     if (!ok_all) {  // nothing to compute: publish an empty table
@@ -257,8 +257,8 @@ __global__ void ep_signal_kernel(int world, int me, uint32_t seq, EpPeers peers)
     if ((int)threadIdx.x < world) st_release_sys(&peers.arena[threadIdx.x]->ret_flag[me], seq);
 }
 
-__global__ void ep_wait_ret_kernel(EpArena* mine, int world, uint32_t seq, int* status) {
-    if ((int)threadIdx.x < world && !wait_flag(&mine->ret_flag[threadIdx.x], seq)) atomicExch(status, 22);
+__global__ void ep_wait_ret_kernel(EpArena* mine, int world, uint32_t seq, int* status, int polls) {
+    if ((int)threadIdx.x < world && !wait_flag(&mine->ret_flag[threadIdx.x], seq, polls)) status_set(status, 22);
 }
 
 }  // namespace dnb
@@ -272,6 +272,7 @@ struct EpState {
     int rank = 0, world = 1, max_tokens = 0, cap = 0, rows_total = 0, n_local = 0;
     uint32_t seq = 0;
     bool connected = false;
+    bool loopback = false;         // every peer pointer is the own arena (time-out test): nothing to close
     uint8_t* arena = nullptr;      // this rank's exported allocation
     size_t arena_bytes = 0;
     size_t off_slot = 0, off_hi = 0, off_lo = 0, off_h = 0;  // layout, identical on every rank
@@ -294,7 +295,7 @@ void ep_release(dnb_ctx* c) {
     EpState* s = static_cast<EpState*>(c->ep);
     if (!s) return;
     for (int r = 0; r < s->world; ++r)
-        if (r != s->rank && s->peer_base[r]) cudaIpcCloseMemHandle(s->peer_base[r]);
+        if (r != s->rank && s->peer_base[r] && !s->loopback) cudaIpcCloseMemHandle(s->peer_base[r]);
     void* loc[] = {s->arena, s->send_row, s->base, s->row_dst, s->act_hi, s->act_lo, s->seg_gu, s->seg_dn, s->nseg, s->ticket};
     for (void* p : loc)
         if (p) cudaFree(p);
@@ -317,6 +318,10 @@ extern "C" int dnb_ep_init(dnb_ctx* c, int rank, int world, int max_tokens, void
     if (M.ne / world > kEpMaxLocal || M.ne > kEpMaxExperts || M.e % 256 || M.ff % 256 || M.k > 32) {
         set_error("ep_init: shape outside the peer-memory path (e, ff multiples of 256; at most %d local experts)", kEpMaxLocal);
         return DNB_DECLINED;
+    }
+    if ((long)max_tokens * M.k >= (1L << 24)) {
+        set_error("ep_init: max_tokens * k = %ld does not fit the 24-bit row field of a receive slot", (long)max_tokens * M.k);
+        return DNB_ERR_ARG;
     }
     DNB_CUDA(cudaSetDevice(c->device));
     ep_release(c);
@@ -381,6 +386,27 @@ extern "C" int dnb_ep_connect(dnb_ctx* c, const void* handles) {
     return DNB_OK;
 }
 
+// Test hook: a group of `world` ranks in which only this one exists.  Every peer pointer is
+// this rank's own arena, so all stores stay on this GPU, and the flags the missing ranks would
+// raise never arrive: a block call then runs into its bounded waits (status 21) instead of a
+// partner.  Used to check that a wait that runs out is reported and does not hang.
+extern "C" int dnb_ep_connect_loopback(dnb_ctx* c) {
+    if (!c || !c->ep) return DNB_ERR_ARG;
+    EpState* s = static_cast<EpState*>(c->ep);
+    for (int r = 0; r < s->world; ++r) {
+        uint8_t* b = s->arena;
+        s->peer_base[r] = s->arena;
+        s->peers.arena[r] = (EpArena*)b;
+        s->peers.recv_slot[r] = (int32_t*)(b + s->off_slot);
+        s->peers.xg_hi[r] = (uint16_t*)(b + s->off_hi);
+        s->peers.xg_lo[r] = (uint16_t*)(b + s->off_lo);
+        s->peers.h_slots[r] = (float*)(b + s->off_h);
+    }
+    s->connected = true;
+    s->loopback = true;
+    return DNB_OK;
+}
+
 extern "C" int dnb_ep_block_dev(dnb_ctx* c, int layer, const float* h_dev, int nt, float* out_dev) {
     if (!c || !c->ep || !h_dev || !out_dev || nt < 1) return DNB_ERR_ARG;
     EpState* s = static_cast<EpState*>(c->ep);
@@ -414,7 +440,7 @@ extern "C" int dnb_ep_block_dev(dnb_ctx* c, int layer, const float* h_dev, int n
     }
     {
         ProfScope p_(c, st, "ep_offsets");
-        ep_offsets_kernel<<<1, 1024, 0, st>>>((const EpArena*)s->arena, M.ne, s->n_local, s->world, s->rank, seq, s->base, c->status);
+        ep_offsets_kernel<<<1, 1024, 0, st>>>((const EpArena*)s->arena, M.ne, s->n_local, s->world, s->rank, seq, s->base, c->status, c->flag_polls);
     }
     // The dispatch stores run on the side stream, beside the shared expert of the own tokens
     // on the main one: peer stores over NVLink and a local GEMM do not compete for much.
@@ -439,7 +465,7 @@ extern "C" int dnb_ep_block_dev(dnb_ctx* c, int layer, const float* h_dev, int n
         ep_build_kernel<<<1, 1024, 0, st>>>((EpArena*)s->arena, (const int32_t*)(s->arena + s->off_slot), s->world, s->n_local,
                                             s->rank, M.e, seq, s->peers, (const uint8_t*)L.m[0].dev, (const uint8_t*)L.m[1].dev,
                                             (const uint8_t*)L.m[2].dev, L.m[0].expert_bytes, L.m[1].expert_bytes,
-                                            L.m[2].expert_bytes, s->seg_gu, s->seg_dn, s->nseg, s->row_dst, c->status);
+                                            L.m[2].expert_bytes, s->seg_gu, s->seg_dn, s->nseg, s->row_dst, c->status, c->flag_polls);
     }
     c->launches++;
     DNB_CUDA(cudaGetLastError());
@@ -453,7 +479,7 @@ extern "C" int dnb_ep_block_dev(dnb_ctx* c, int layer, const float* h_dev, int n
     {
         ProfScope p_(c, st, "ep_signal_wait");
         ep_signal_kernel<<<1, 32, 0, st>>>(s->world, s->rank, seq, s->peers);
-        ep_wait_ret_kernel<<<1, 32, 0, st>>>((EpArena*)s->arena, s->world, seq, c->status);
+        ep_wait_ret_kernel<<<1, 32, 0, st>>>((EpArena*)s->arena, s->world, seq, c->status, c->flag_polls);
     }
     c->launches += 2;
     DNB_CUDA(cudaGetLastError());

@@ -82,7 +82,7 @@ __device__ __forceinline__ bool mb_try(uint64_t* b, uint32_t parity) {
 __device__ __forceinline__ bool mb_wait(uint64_t* b, uint32_t parity, int* status, int code) {
     for (int i = 0; i < (1 << 21); ++i)
         if (mb_try(b, parity)) return true;
-    if (status) atomicExch(status, code);
+    status_set(status, code);
     return false;
 }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }

@@ -631,12 +631,21 @@ extern "C" int dnb_router_topk_static(dnb_ctx* c, int layer, const float* x_dev,
         set_error("router_topk_static: shape outside the router kernels' range");
         return DNB_DECLINED;
     }
-    if (c->device < 0 || c->device >= 64) return DNB_ERR_ARG;
+    if (M.k > M.ne) {
+        set_error("router_topk_static: k %d exceeds the %d experts", M.k, M.ne);
+        return DNB_DECLINED;
+    }
+    if (c->device < 0 || c->device >= 64) {
+        set_error("router_topk_static: device index %d outside the per-device table (0..63)", c->device);
+        return DNB_ERR_ARG;
+    }
+    // The calling thread's current device may be another context's: select this context's
+    // device on every call (cheap, allocates nothing), not only during the set-up below.
+    DNB_CUDA(cudaSetDevice(c->device));
     // One-time set-up per device: in host code the array's name is only a handle,
     // its device address has to be asked for (with that device current).
     const size_t smem = (size_t)RT * M.e * sizeof(float);
     if (!g_static_logits_ptr[c->device]) {
-        DNB_CUDA(cudaSetDevice(c->device));
         float* p = nullptr;
         DNB_CUDA(cudaGetSymbolAddress((void**)&p, g_static_logits));
         const int rc = router_smem_at_least(c->device, 200 * 1024);  // the most the router kernel is ever given
@@ -652,6 +661,7 @@ extern "C" int dnb_router_topk_static(dnb_ctx* c, int layer, const float* x_dev,
     const dim3 grid((M.ne + RROWS * RW - 1) / (RROWS * RW), (nt + RT - 1) / RT);
     // every logit of the [nt][n_expert] range is written before it is read, so the
     // previous call's contents need no clearing
+    // (no per-kernel profiling scope here: it creates events on first use, which may allocate)
     router_logits_kernel<<<grid, RROWS * 32, smem, c->stream>>>(x_dev, nt, M.e, L.router_w, L.router_bias, M.ne, logits);
     topk_kernel<<<nt, 128, 0, c->stream>>>(logits, nt, M.ne, M.k, M.norm_topk, sels_dev, wts_dev, rowsum_dev);
     c->launches += 2;

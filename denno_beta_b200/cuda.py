@@ -87,7 +87,15 @@ class CudaCtx:
         check(self.lib.dnb_set_stream(self.h, C.c_void_p(cuda_stream) if cuda_stream else None))
 
     def sync(self):
-        check(self.lib.dnb_sync(self.h))
+        """Waits for the context's streams; False when a bounded device wait gave up since the
+        status was last cleared (the device-pointer calls since then cannot be trusted)."""
+        return check(self.lib.dnb_sync(self.h), True)
+
+    def clear_status(self):
+        check(self.lib.dnb_clear_status(self.h))
+
+    def set_wait_limits(self, barrier_polls=400000, flag_polls=1 << 21, barrier_bias=0):
+        check(self.lib.dnb_set_wait_limits(self.h, barrier_polls, flag_polls, barrier_bias))
 
     def launch_count(self):
         return int(self.lib.dnb_launch_count(self.h))
@@ -254,6 +262,43 @@ class CudaCtx:
             return None
         return outs
 
+    def build_grouped_batch(self, layer, sels):
+        """moe_expert.rs:8309 build_grouped_batch on the device: (segs[nseg,4], row_token[nt*k], pos[nt,k])."""
+        sels = np.ascontiguousarray(sels, np.int32)
+        nt, k = sels.shape
+        segs = np.zeros((self.model["ne"], 4), np.uint32)
+        nseg = C.c_int32(0)
+        rtok = np.empty(nt * k, np.int32)
+        pos = np.empty((nt, k), np.int32)
+        if not check(self.lib.dnb_build_grouped_batch(self.h, layer, _p(sels), nt, _p(segs), C.byref(nseg), _p(rtok), _p(pos)),
+                     True):
+            return None
+        return segs[:nseg.value].copy(), rtok, pos
+
+    def seg_gemv(self, layer, matrix, seg, x, out):
+        """Legacy segmented GEMV (cuda.rs:7689 moe_gemv_seg_one): seg[nseg,4] = (expert, m, x_off, out_off)."""
+        seg = np.ascontiguousarray(seg, np.uint32)
+        x = _f32(x)
+        assert out.dtype == np.float32 and out.flags["C_CONTIGUOUS"]
+        return check(self.lib.dnb_seg_gemv(self.h, layer, matrix, _p(seg), seg.shape[0], _p(x), x.size, _p(out), out.size), True)
+
+    def seg_gemv_pair(self, layer, seg, x, out_g, out_u):
+        """cuda.rs:7638 moe_gemv_seg_pair: gate and up of the same segments."""
+        seg = np.ascontiguousarray(seg, np.uint32)
+        x = _f32(x)
+        assert out_g.size == out_u.size
+        return check(self.lib.dnb_seg_gemv_pair(self.h, layer, _p(seg), seg.shape[0], _p(x), x.size, _p(out_g), _p(out_u),
+                                                out_g.size), True)
+
+    def router_gemv(self, layer, x):
+        """cuda.rs:25836 maybe_gpu_router_gemv_into: logits[nt, n_expert], or None when declined."""
+        e, ne = self.model["e"], self.model["ne"]
+        x = _f32(x, (-1, e))
+        out = np.empty((x.shape[0], ne), np.float32)
+        if not check(self.lib.dnb_router_gemv(self.h, layer, _p(x), x.shape[0], _p(out)), True):
+            return None
+        return out
+
     def moe_stack(self, h):
         e = self.model["e"]
         h = _f32(h, (-1, e))
@@ -304,3 +349,22 @@ def moe_seg_layer_sum(ctx, layer, sels, w, x):
 def moe_grouped_gemm_layer(ctx, layer, matrix, segs, xs, n_out):
     """cuda.rs:7065-7075 on one matrix: per-segment expert GEMM on packed rows."""
     return ctx.grouped_gemm(layer, matrix, segs, xs, n_out)
+
+
+def moe_gemv_seg_pair(ctx, layer, seg, x, out_g, out_u):
+    """cuda.rs:7638-7650: gate and up segmented GEMVs, results to the host (False = not run)."""
+    return ctx.seg_gemv_pair(layer, seg, x, out_g, out_u)
+
+
+def moe_gemv_seg_one(ctx, layer, seg, x, out):
+    """cuda.rs:7689-7698: the down segmented GEMV of the legacy three-launch form."""
+    return ctx.seg_gemv(layer, DOWN, seg, x, out)
+
+
+def maybe_gpu_router_gemv_into(ctx, layer, x, out):
+    """cuda.rs:25836: router logits of one row into `out`; False = the caller computes them itself."""
+    got = ctx.router_gemv(layer, x)
+    if got is None:
+        return False
+    out[...] = got.reshape(out.shape)
+    return True

@@ -72,11 +72,35 @@ const char* dnb_last_error(void);
 /* Run on a stream the caller owns (e.g. the framework's current stream) instead
  * of the context's own; pass NULL to go back.  cuda.rs:100-111 (stream set-up). */
 int dnb_set_stream(dnb_ctx* ctx, void* cuda_stream);
+/* Waits for the context's streams.  DNB_DECLINED when a bounded device wait has given up since
+ * the status word was last cleared (see dnb_device_status). */
 int dnb_sync(dnb_ctx* ctx);
 /* Kernels launched by this context since creation. */
 uint64_t dnb_launch_count(dnb_ctx* ctx);
-/* Status word the kernels write when a bounded wait gave up (0 = clean). */
+/* Waits inside the kernels (shared-memory barriers, the grid barrier of the one-token
+ * kernel, the flags of the expert-parallel exchange) are bounded.  A wait that gives up
+ * records a code in the context's status word (pinned host memory the device writes):
+ *   1        a bulk copy into shared memory never completed
+ *   2-6      the tcgen05 grouped GEMM (stage, accumulator or drain barrier)
+ *   20-22    expert-parallel exchange: row out of range / a peer's counts or rows did not
+ *            arrive / a peer's results did not arrive
+ *   23       grid barrier of the fused one-token kernel
+ * What the reference promises for a GPU call that did not complete -- "false: out
+ * untouched, the caller recomputes" (cuda.rs:21024-21027, 8785-8788) -- holds here too:
+ * every host-buffer entry point reads the word after its stream synchronisation and, when
+ * it is non-zero, copies nothing to the caller, clears the word and returns DNB_DECLINED
+ * (after a 23 the context also stops using the one-kernel decode form: the two-launch
+ * form has no inter-CTA wait).  Device-pointer entry points are asynchronous; for them the
+ * word stays set until dnb_clear_status, dnb_device_status reads it and dnb_sync returns
+ * DNB_DECLINED while it is non-zero. */
 int dnb_device_status(dnb_ctx* ctx, int* status);
+int dnb_clear_status(dnb_ctx* ctx);
+/* How long those waits last: polls of the grid barrier (default 400000, about 0.2 s) and
+ * of an expert-parallel flag (default 2^21, about 0.25 s).  barrier_bias is a test hook:
+ * it is added to the number of arrivals the grid barrier waits for, so any value > 0 makes
+ * the barrier unreachable and the time-out path can be exercised without faulting or
+ * hanging anything; 0 in production. */
+int dnb_set_wait_limits(dnb_ctx* ctx, int barrier_polls, int flag_polls, int barrier_bias);
 /* Device-side timing on the context's stream: start, ... calls ..., stop -> ms. */
 int dnb_timer_start(dnb_ctx* ctx);
 int dnb_timer_stop(dnb_ctx* ctx, float* ms);
@@ -143,7 +167,10 @@ int dnb_register_router(dnb_ctx* ctx, int layer, const float* w, const float* bi
                         const float* shared_gate_row);
 /* Fill one expert tensor in place on the device from the seeded generator of
  * dnb_synth.h (tensor id = layer*16 + matrix).  For benchmarks whose expert table
- * is too large to stage through the host. */
+ * is too large to stage through the host.  With an expert shard set
+ * (dnb_moe_set_expert_shard) a routed tensor receives the bytes of experts
+ * [first, first + n_expert) of the full tensor, so G ranks together hold exactly what
+ * one GPU would. */
 int dnb_synth_experts(dnb_ctx* ctx, int layer, int matrix, int ggml_type, int n_in, int n_out, int n_expert,
                       uint64_t seed);
 /* Copy expert `expert` of a registered tensor back to the host (parity checks). */
@@ -196,6 +223,32 @@ int dnb_router_topk_static(dnb_ctx* ctx, int layer, const float* x_dev, int nt, 
  * [m_total][n_out]. */
 int dnb_grouped_gemm(dnb_ctx* ctx, int layer, int matrix, const uint32_t* segs, int nseg, const float* xs,
                      float* outs);
+/* The expert-major row space of a chunk as the device builds it (moe_expert.rs:8309-8390
+ * build_grouped_batch; Segment{expert, m, x_off, out_off} :8272-8281; exp_pf.rs:23-31 rows[]):
+ * from sels host [nt][k] -> segs_out [n_expert][4] = (expert, m, first row, first row) ordered by
+ * token count descending, ties by expert ascending; *nseg_out = active experts; row_token_out
+ * [nt*k] = token of each packed row (ascending inside an expert); pos_out [nt*k] = packed row
+ * of (token, slot).  The last two may be NULL.  For parity checks of the routing tables. */
+int dnb_build_grouped_batch(dnb_ctx* ctx, int layer, const int32_t* sels, int nt, uint32_t* segs_out, int32_t* nseg_out,
+                            int32_t* row_token_out, int32_t* pos_out);
+/* The legacy three-launch decode form (cuda.rs:7638-7650 moe_gemv_seg_pair, 7689-7698
+ * moe_gemv_seg_one): segmented GEMVs whose results return to the host, which applies
+ * silu(g)*u and the weighted sum itself.  seg[nseg][4] = (expert, m, x_off, out_off) as in
+ * expert_batch.rs:143-170, offsets in floats and multiples of n_in / n_out: token j of
+ * segment i reads x[x_off + j*n_in ..] and writes out[out_off + j*n_out ..] (gate/up of one
+ * token: x_off = 0, out_off = s*ff; down: x_off = s*ff, out_off = s*e).  Where the reference
+ * passes a table of device addresses (wptrs), the expert index names the resident expert
+ * of (layer, matrix).  x_len / out_len are the lengths of x / out in floats; a segment that
+ * reaches beyond them is refused (expert_batch.rs:233-260 seg_extents). */
+int dnb_seg_gemv(dnb_ctx* ctx, int layer, int matrix, const uint32_t* seg, int nseg, const float* x, size_t x_len,
+                 float* out, size_t out_len);
+int dnb_seg_gemv_pair(dnb_ctx* ctx, int layer, const uint32_t* seg, int nseg, const float* x, size_t x_len, float* out_g,
+                      float* out_u, size_t out_len);
+/* Router logits alone (cuda.rs:25836 maybe_gpu_router_gemv_into; kernels_elem.cu:948-1002):
+ * logits[t][i] = W_r[i] . x[t] + bias[i] for nt rows, host in / host out.  Lane-split with
+ * a fixed tree: deterministic, not the bits of the sequential CPU loop (the reference's
+ * default dno_matvec_f32_r has the same contract). */
+int dnb_router_gemv(dnb_ctx* ctx, int layer, const float* x, int nt, float* logits);
 /* ---- expert-parallel building blocks ---------------------------------------------
  * The reference runs on one GPU.  On a multi-GPU box the experts shard naturally:
  * GPU g keeps experts [g*ne/G, (g+1)*ne/G) of every layer (router, norm and shared
@@ -243,6 +296,16 @@ int dnb_moe_combine_dev(dnb_ctx* ctx, int layer, const float* h_slots_dev, const
 int dnb_ep_init(dnb_ctx* ctx, int rank, int world, int max_tokens, void* handle_out);
 int dnb_ep_connect(dnb_ctx* ctx, const void* handles);
 int dnb_ep_block_dev(dnb_ctx* ctx, int layer, const float* h_dev, int nt, float* out_dev);
+/* Teardown rule of the peer-memory path: a rank's arena is memory its peers store into from
+ * their kernels.  A rank must not call dnb_shutdown (or exit) before a host-side barrier
+ * has shown that no peer still has a dnb_ep_block_dev in flight -- synchronise the own
+ * context, then barrier, then shut down; on an error path wait at least as long as the
+ * longest device wait (dnb_set_wait_limits) before leaving, so that the peers' kernels have
+ * finished or given up.
+ * Test hook: a group of `world` ranks of which only this one exists -- every peer pointer is
+ * this rank's own arena, so the flags of the absent ranks never arrive and a block call runs
+ * into its bounded waits (status 21/22) instead of a partner. */
+int dnb_ep_connect_loopback(dnb_ctx* ctx);
 /* A stack of the configured layers with identity mixers: h <- h + block_l(h) for
  * l = 0..n_layer-1 (device-resident between layers).  h host [nt][n_embd] in/out. */
 int dnb_moe_stack(dnb_ctx* ctx, const float* h, int nt, float* out);

@@ -23,8 +23,8 @@ TYPE_BY_NAME = {
 
 def build(force=False):
     """Compile the oracle with the Makefile next to it (gcc, a second or two)."""
-    src = os.path.join(_HERE, "dnb_oracle.c")
-    if force or not os.path.exists(_SO) or os.path.getmtime(_SO) < os.path.getmtime(src):
+    srcs = [os.path.join(_HERE, f) for f in ("dnb_oracle.c", "dnb_cpu_fast.c", "dnb_oracle.h", "Makefile")]
+    if force or not os.path.exists(_SO) or os.path.getmtime(_SO) < max(os.path.getmtime(f) for f in srcs):
         subprocess.check_call(["make", "-C", _HERE, "-s"] + (["-B"] if force else []))
     return _SO
 
@@ -220,6 +220,38 @@ def moe_block_mt(layer, h):
     h = _f32(h).reshape(-1, layer.e)
     out = np.empty((h.shape[0], layer.e), np.float32)
     lib().orc_moe_block_mt(C.byref(layer.c), _p(h), C.c_long(h.shape[0]), _p(out))
+    return out
+
+
+# ---- the timed CPU baseline (oracle/dnb_cpu_fast.c): AVX2+FMA kernels in the reference's production form ----
+
+def set_threads(n):
+    """OpenMP threads of the timed legs (0 = the runtime's default).  Set explicitly: a launcher
+    such as torch.distributed.run exports OMP_NUM_THREADS=1 to its children."""
+    lib().orc_set_threads(C.c_int(int(n)))
+
+
+def get_threads():
+    return int(lib().orc_get_threads())
+
+
+def fast_gemv(ty, blocks, n_in, n_out, x):
+    blocks, x = _u8(blocks), _f32(x)
+    assert blocks.size == n_out * row_bytes(ty, n_in) and x.size == n_in
+    out = np.empty(n_out, np.float32)
+    if lib().orc_fast_gemv(C.c_int(ty), _p(blocks), C.c_long(n_in), C.c_long(n_out), _p(x), _p(out)) != 0:
+        raise ValueError("fast_gemv: bad type/length")
+    return out
+
+
+def fast_moe_block(layer, h, grouped=False):
+    """One block for nt tokens: token by token in the decode form, or grouped by expert with the
+    k-chunked batch kernels (the prefill form)."""
+    h = _f32(h).reshape(-1, layer.e)
+    out = np.empty((h.shape[0], layer.e), np.float32)
+    fn = lib().orc_fast_moe_block_grouped if grouped else lib().orc_fast_moe_block
+    if fn(C.byref(layer.c), _p(h), C.c_long(h.shape[0]), _p(out)) != 0:
+        raise ValueError("fast_moe_block: layer shape not covered")
     return out
 
 

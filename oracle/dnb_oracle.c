@@ -22,6 +22,7 @@
 
 #include "dnb_iq_tables.h"
 #include "dnb_synth.h"
+#include "dnb_oracle.h"
 
 #define QK_K 256
 
@@ -475,19 +476,6 @@ static void expert_ffn_q(const float* x, int ty_g, const uint8_t* wg, int ty_u, 
     orc_gemv_scalar(ty_d, wd, ff, e, act, h);
 }
 
-typedef struct {
-    long e, ff, ne, k, sff;
-    int norm_topk;
-    int ty_gate, ty_up, ty_down;          /* routed experts */
-    int ty_sgate, ty_sup, ty_sdown;       /* shared expert */
-    float eps;
-    const float* norm_w;                  /* [e] or NULL = no RMSNorm in front */
-    const float* router_w;                /* [ne][e] fp32 */
-    const float* router_bias;             /* [ne] or NULL */
-    const uint8_t *gate, *up, *down;      /* [ne] experts, expert-major (ExpertSlice) */
-    const uint8_t *sgate, *sup, *sdown;   /* shared expert or NULL */
-    const float* shared_gate_row;         /* [e] or NULL: coefficient sigmoid(row . x), else 1.0 */
-} orc_moe_layer;
 
 /* One MoE block for nt tokens, token by token, exactly the decode order:
  * (RMSNorm) -> router -> experts ascending -> out += w*h -> shared expert.
@@ -567,10 +555,7 @@ int orc_moe_experts_given(const orc_moe_layer* L, const float* x, long nt, const
 
 /* ---- grouped (prefill) form ------------------------------------------------ */
 
-/* moe_expert.rs:8272-8281 */
-typedef struct {
-    uint32_t expert, m, x_off, out_off;
-} orc_segment;
+/* orc_segment (moe_expert.rs:8272-8281) is declared in dnb_oracle.h */
 
 /* moe_expert.rs:8309-8390 (build_grouped_batch) from a routing table: by_expert
  * lists are (token ascending) per expert; segments sorted m descending, ties

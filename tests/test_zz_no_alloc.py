@@ -57,3 +57,45 @@ def test_static_router_matches_regular_router_twice(orc):
             c.dev_free(p)
     finally:
         c.close()
+
+
+def _n_gpus():
+    try:
+        import torch
+
+        return torch.cuda.device_count()
+    except Exception:
+        return 0
+
+
+@pytest.mark.skipif(_n_gpus() < 2, reason="needs at least 2 GPUs")
+def test_static_router_on_a_second_device_after_the_first(orc):
+    """Two contexts in one process, one per GPU.  The entry point must select its own context's
+    device on every call: here it runs on GPU 1 right after GPU 0's context was used (so the
+    calling thread's current device is 0), and again on GPU 0 after GPU 1."""
+    from denno_beta_b200 import cuda as cu
+
+    e, ff, ne, k, nt = 512, 256, 64, 6, 33
+    ctxs = [cu.CudaCtx(0), cu.CudaCtx(1)]
+    try:
+        bufs = []
+        for c in ctxs:
+            assert c.moe_config(1, e, ff, ne, k)
+            make_layer(orc, c, 0, orc.Q4_K, e, ff, ne, k, bias=True)
+            bufs.append([c.dev_alloc(nt * e * 4), c.dev_alloc(nt * k * 4), c.dev_alloc(nt * k * 4)])
+        x = orc.synth_normal(SEED, 6100, 1.0, nt * e).reshape(nt, e)
+        want_sels, want_wts, _ = ctxs[0].router_topk(0, x)  # leaves device 0 current
+        for order in ((1, 0), (0, 1)):
+            for d in order:
+                c, (d_x, d_sels, d_wts) = ctxs[d], bufs[d]
+                c.upload(d_x, x)
+                ctxs[1 - d].sync()  # the other context's call makes ITS device the current one
+                assert c.router_topk_static(0, d_x, nt, d_sels, d_wts, None)
+                assert c.sync()
+                sels = c.download(d_sels, np.empty((nt, k), np.int32))
+                wts = c.download(d_wts, np.empty((nt, k), np.float32))
+                assert np.array_equal(sels, want_sels), "device %d" % d
+                assert np.array_equal(wts.view(np.uint32), want_wts.view(np.uint32)), "device %d" % d
+    finally:
+        for c in ctxs:
+            c.close()
