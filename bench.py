@@ -256,6 +256,8 @@ def run_ours(args, rank, world, local_rank):
     g_b, d_b = expert_bytes(IQ3_XXS)
     alg = {  # algorithmic bytes per launch: weight bytes + activations in/out
         # gate/up + down of the block in one kernel: all expert rows once, x in, the block's result out
+        # the whole block in one kernel: router rows, all expert rows once, the token row in, the result out
+        "decode_block": NE * E * 4 + (K + 1) * (2 * g_b + d_b) + 2 * E * 4,
         "decode_gate_up_down": (K + 1) * (2 * g_b + d_b) + 3 * E * 4,
         "gemv_gate_up": (K + 1) * 2 * g_b + E * 4 + (K + 1) * FF * 4,
         "gemv_down": (K + 1) * d_b + (K + 1) * FF * 4 + (K + 1) * E * 4,
@@ -741,9 +743,10 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="rotating layer copies (default %d; fewer for profiler captures)" % LAYERS)
     ap.add_argument("--prefill-only", action="store_true",
                     help="run only the config-2 prefill measurement (small: for profiler captures)")
-    ap.add_argument("--decode-impl", type=int, default=0, choices=[0, 3, 4],
-                    help="one-token kernels of the headline line: 0 fused mma.sync kernel (default), 4 mma.sync gate/up + "
-                         "down kernel, 3 register-decode kernels (for profiler captures of those kernels)")
+    ap.add_argument("--decode-impl", type=int, default=0, choices=[0, 3, 4, 5],
+                    help="one-token kernels of the headline line: 0 the whole block as one mma.sync kernel (default), 5 router "
+                         "kernel + fused gate/up + down kernel, 4 router + mma.sync gate/up + down kernels, 3 register-decode "
+                         "kernels (for A/B runs and profiler captures of those kernels)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-extras", action="store_true", help="skip the config-0/2/3/4 lines")
     ap.add_argument("--no-stack", action="store_true", help="skip the 48-layer stack lines (configs 3 and 4)")

@@ -58,7 +58,7 @@ static int ensure_ws(dnb_ctx* c, int nt) {
     if ((rc = dev_alloc(&w.xn, (size_t)cap * M.e))) return rc;
     if ((rc = dev_alloc(&w.hin, (size_t)cap * M.e))) return rc;
     if ((rc = dev_alloc(&w.out, (size_t)cap * M.e))) return rc;
-    if ((rc = dev_alloc(&w.logits, (size_t)cap * M.ne))) return rc;
+    if ((rc = dev_alloc(&w.logits, std::max((size_t)cap * M.ne, (size_t)kActRep * M.ne)))) return rc;  // one-token block kernel: kActRep copies
     if ((rc = dev_alloc(&w.wts, rows))) return rc;
     if ((rc = dev_alloc(&w.sels, rows))) return rc;
     if ((rc = dev_alloc(&w.act, rows * M.ff))) return rc;
@@ -268,7 +268,13 @@ static int block_dev_decode(dnb_ctx* c, int layer, const float* h, float* out, c
                       L.m[5].type == L.m[2].type && L.m[3].n_out == M.ff;
     if (shared && !fold) return DNB_DECLINED;
     if (L.m[0].type != L.m[1].type) return DNB_DECLINED;
-    int rc = launch_router_decode(c, st, h, M, L, w, fold, c->ticket);
+    int rc;
+    if (c->gemv_mma && c->decode_fused && c->decode_routed && L.m[0].type == T_IQ3_XXS && L.m[2].type == T_IQ3_XXS) {
+        // the whole block, router included, in one kernel (decode_fused.cu, ROUTED)
+        rc = launch_decode_block(c, st, M, L, w, fold, h, residual, out, c->gbar);
+        if (rc != DNB_DECLINED) return rc;
+    }
+    rc = launch_router_decode(c, st, h, M, L, w, fold, c->ticket);
     if (rc) return rc;
     const int nseg = M.k + (fold ? 1 : 0);
     const float* xperm = M.ne >= 4 * kActRep ? w.xn_perm : nullptr;
@@ -693,7 +699,7 @@ int dnb_register_matrix(dnb_ctx* c, uint64_t uid, int type, const void* blocks, 
 }
 
 int dnb_set_gemv_impl(dnb_ctx* c, int impl) {
-    if (!c || impl < 0 || impl > 4) return DNB_ERR_ARG;
+    if (!c || impl < 0 || impl > 5) return DNB_ERR_ARG;
     DNB_CUDA(cudaDeviceSynchronize());
     drop_graphs(c);
     c->gemv_impl = impl == 1 ? 1 : 0;
@@ -701,6 +707,7 @@ int dnb_set_gemv_impl(dnb_ctx* c, int impl) {
     c->use_umma = impl != 2;
     c->gemv_mma = impl != 3;
     c->decode_fused = impl != 3 && impl != 4;
+    c->decode_routed = impl != 5;
     return DNB_OK;
 }
 

@@ -160,6 +160,7 @@ struct dnb_ctx {
     bool use_pdl = true;                // programmatic dependent launch between the decode kernels
     bool gemv_mma = true;               // one-token IQ3_XXS kernels on mma.sync (gemv_mma.cu, decode_fused.cu) where the shape fits
     bool decode_fused = true;           // gate/up + down of a one-token IQ3_XXS block as one kernel (decode_fused.cu)
+    bool decode_routed = true;          // ... with the router folded into the same kernel (one launch per block)
     bool use_umma = true;               // prefill chunks of Q4_K layers take the tcgen05 grouped GEMM
     void* ep = nullptr;                 // dnb::EpState of the peer-memory expert-parallel path (ep_p2p.cu)
 };
@@ -316,6 +317,10 @@ size_t decode_fused_act_halves(int nseg, int ff);
 int launch_decode_fused(dnb_ctx* c, cudaStream_t st, const SegDesc* seg_gu, const SegDesc* seg_dn, int nseg, int k,
                         bool has_shared, int e, int ff, const float* x, const float* x_perm, float* act, void* act_h,
                         const float* wts, const float* shcoef, const float* residual, float* out, unsigned long long* gbar);
+
+// The whole one-token block, router included, of an all-IQ3_XXS layer in one kernel (decode_fused.cu).
+int launch_decode_block(dnb_ctx* c, cudaStream_t st, const Model& M, const Layer& L, Workspace& w, bool fold_shared,
+                        const float* h, const float* residual, float* out, unsigned long long* gbar);
 
 // tcgen05 grouped GEMM of prefill (grouped_umma.cu)
 int umma_make_maps(void* hi, void* lo, uint64_t rows, uint64_t cols, UmmaMaps* out);

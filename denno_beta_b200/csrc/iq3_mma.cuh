@@ -10,6 +10,11 @@
 #include "bulk.cuh"
 #include "dnb_iq_tables.h"
 
+// Sub-blocks of the K loops that are unrolled together (more independent work per warp, more registers).
+#ifndef DNB_IQ3_UNROLL
+#define DNB_IQ3_UNROLL 2
+#endif
+
 namespace dnb {
 
 constexpr int kGmRows = 8;     // rows of one matrix per group (x2 matrices = the 16 mma rows)
@@ -17,6 +22,7 @@ constexpr int kGmKs = 4;       // warps that split K within a group
 constexpr int kGmGroups = 5;   // groups a CTA can hold
 constexpr int kGmThreads = kGmGroups * kGmKs * 32;
 constexpr int kGmSplit = 3;    // bf16 terms per activation value
+constexpr int kIq3Unroll = 2;  // sub-blocks of the gate/up K loop unrolled together
 
 // What a CTA copies into shared memory in one bulk copy: the IQ3_XXS codebook as bf16 pairs,
 // entry e of copy r at [e * kLutRep + r]; .x = elements 0,1, .y = elements 2,3.  (A second table
@@ -119,7 +125,7 @@ __device__ __forceinline__ void gate_up_warp(const uint8_t* rowg, const uint8_t*
         const uint8_t* bg = rowg + b * 98;
         const uint8_t* bu = rowu + b * 98;
         const float dg = h2f(ld16(bg)) * 0.25f, du = h2f(ld16(bu)) * 0.25f;
-#pragma unroll 2
+#pragma unroll kIq3Unroll
         for (int ib = 0; ib < 8; ++ib) {
             uint4 y = make_uint4(0u, 0u, 0u, 0u);
             if (has_col) y = *reinterpret_cast<const uint4*>(xb + (b * 8 + ib) * 32);

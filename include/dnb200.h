@@ -145,7 +145,8 @@ int dnb_gemv_dev(dnb_ctx* ctx, int ggml_type, const void* w_dev, int k, int n, c
  * GEMM (A/B checks between kernel families).  3: as 0, but one-token IQ3_XXS blocks
  * take the register-decode kernels instead of the mma.sync ones.  4: as 0, but
  * the mma.sync gate/up kernel and the down kernel run as two launches instead of
- * the fused one. */
+ * the fused one.  5: as 0, but the router of a one-token IQ3_XXS block runs as a
+ * kernel of its own in front of the fused gate/up + down kernel instead of inside it. */
 int dnb_set_gemv_impl(dnb_ctx* ctx, int impl);
 
 /* ---- MoE model: resident expert table ----------------------------------------

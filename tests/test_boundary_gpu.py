@@ -32,7 +32,7 @@ def test_grid_barrier_that_runs_out_declines_and_leaves_out_untouched(orc):
         want = c.moe_block(0, h)
         n0 = c.launch_count()
         c.moe_block(0, h)
-        assert c.launch_count() - n0 == 3, "the fused one-token kernel should be in use"
+        assert c.launch_count() - n0 == 2, "the one-kernel block should be in use"
         c.set_wait_limits(barrier_polls=4000, barrier_bias=1)
         out = np.full((1, e), 7.25, np.float32)
         assert c.moe_block_into(0, h, out) is False

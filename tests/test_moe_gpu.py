@@ -192,10 +192,11 @@ def config1(orc):
     c.close()
 
 
-@pytest.mark.parametrize("impl", [0, 4, 3])
+@pytest.mark.parametrize("impl", [0, 5, 4, 3])
 def test_config1_decode(orc, config1, impl):
-    """One token of config 1 through each family of one-token kernels: 0 = gate/up, grid barrier
-    and down fused into one mma.sync kernel; 4 = the mma.sync gate/up kernel and the down kernel
+    """One token of config 1 through each family of one-token kernels: 0 = the whole block (router,
+    gate/up, down, two grid barriers) as one mma.sync kernel; 5 = the router as a kernel of its own
+    in front of the fused gate/up + down kernel; 4 = the mma.sync gate/up kernel and the down kernel
     as two launches; 3 = the register-decode kernels.  Each against the oracle, bit-identical
     run to run, with and without the residual of the stack entry point."""
     c, L = config1
@@ -241,7 +242,17 @@ def test_fused_decode_other_shapes(orc, shape):
             assert rel_err(out, ref) <= 2e-5
             launches = c.launch_count()
             c.moe_block(0, h)
-            assert c.launch_count() - launches == 3, "stage-in, router and the fused kernel expected"
+            # stage-in + the one-kernel block; a shape whose shared memory leaves no room for the router
+            # phase (ff 1024) keeps the router as a kernel of its own in front of the fused kernel
+            assert c.launch_count() - launches == (3 if ff == 1024 else 2)
+            c.set_gemv_impl(5)
+            try:
+                split = c.moe_block(0, h, want_routing=True)
+            finally:
+                c.set_gemv_impl(0)
+            # the router inside the block kernel and the router kernel give the same routing bits
+            assert np.array_equal(split[1], sels) and np.array_equal(split[2].view(np.uint32), wts.view(np.uint32))
+            assert np.array_equal(split[0].view(np.uint32), out.view(np.uint32))
         assert c.device_status() == 0
     finally:
         c.close()
