@@ -484,6 +484,7 @@ void dnb_shutdown(dnb_ctx* c) {
     cudaDeviceSynchronize();
     drop_graphs(c);
     ep_release(c);
+    epd_release(c);
     for (auto& kv : c->matrices) cudaFree(kv.second.dev);
     for (auto& L : c->model.layers) free_layer(L);
     free_ws(c->ws);

@@ -178,3 +178,47 @@ class PeerMemoryExpertParallel:
         from ._lib import check
 
         check(self.ctx.lib.dnb_ep_block_dev(self.ctx.h, layer, C.c_void_p(h_dev), nt, C.c_void_p(out_dev)))
+
+
+class PeerMemoryDecode:
+    """One rank of an expert-parallel DECODE group (dnb_epd_* entry points): the residual stream is
+    replicated, every rank computes the (token, slot) pairs of its own experts and stores the result
+    rows into every rank's memory; one flag wait per layer.  `ctx`: configured with dnb_moe_config,
+    set_expert_shard(rank * n_local, n_local) and this rank's experts (router, norm, shared expert
+    replicated).  world == 1 needs no torch.distributed."""
+
+    def __init__(self, ctx, max_tokens, rank=None, world=None, group=None, loopback=False):
+        import numpy as np
+
+        from ._lib import check
+
+        self.ctx = ctx
+        self.rank = (dist.get_rank() if rank is None else rank)
+        self.world = (dist.get_world_size() if world is None else world)
+        handle = np.zeros(64, np.uint8)
+        check(ctx.lib.dnb_epd_init(ctx.h, self.rank, self.world, max_tokens, C.c_void_p(handle.ctypes.data)))
+        if loopback:
+            check(ctx.lib.dnb_epd_connect(ctx.h, None))
+            return
+        if self.world > 1:
+            dev = torch.device("cuda", ctx.device) if dist.get_backend(group) == "nccl" else torch.device("cpu")
+            mine = torch.from_numpy(handle).to(dev)
+            got = [torch.empty_like(mine) for _ in range(self.world)]
+            dist.all_gather(got, mine, group=group)
+            handles = np.concatenate([g.cpu().numpy() for g in got])
+        else:
+            handles = handle
+        handles = np.ascontiguousarray(handles, np.uint8)
+        check(ctx.lib.dnb_epd_connect(ctx.h, C.c_void_p(handles.ctypes.data)))
+        if self.world > 1:
+            dist.barrier(group=group)  # every arena is mapped before anyone stores into one
+
+    def block_dev(self, layer, h_dev, nt, out_dev):
+        from ._lib import check
+
+        check(self.ctx.lib.dnb_epd_block_dev(self.ctx.h, layer, C.c_void_p(h_dev), nt, C.c_void_p(out_dev)))
+
+    def stack_dev(self, h_dev, nt):
+        from ._lib import check
+
+        check(self.ctx.lib.dnb_epd_stack_dev(self.ctx.h, C.c_void_p(h_dev), nt))

@@ -84,6 +84,7 @@ uint64_t dnb_launch_count(dnb_ctx* ctx);
  *   2-6      the tcgen05 grouped GEMM (stage, accumulator or drain barrier)
  *   20-22    expert-parallel exchange: row out of range / a peer's counts or rows did not
  *            arrive / a peer's results did not arrive
+ *   24       expert-parallel decode: a peer's result rows did not arrive
  *   23       grid barrier of the fused one-token kernel
  * What the reference promises for a GPU call that did not complete -- "false: out
  * untouched, the caller recomputes" (cuda.rs:21024-21027, 8785-8788) -- holds here too:
@@ -307,6 +308,28 @@ int dnb_ep_block_dev(dnb_ctx* ctx, int layer, const float* h_dev, int nt, float*
  * this rank's own arena, so the flags of the absent ranks never arrive and a block call runs
  * into its bounded waits (status 21/22) instead of a partner. */
 int dnb_ep_connect_loopback(dnb_ctx* ctx);
+/* ---- expert-parallel DECODE over peer memory -------------------------------------------
+ * No counterpart in the reference (single GPU).  For decode batches (1 to a few dozen tokens) the
+ * exchange is latency, not volume, so the residual stream is REPLICATED: every rank of the group
+ * holds all tokens of the batch and routes them itself (same arithmetic, same bits); it computes
+ * the (token, slot) pairs whose expert it holds and stores each result row into slot (token, slot) of
+ * EVERY rank's arena with plain peer stores; after one bounded flag wait per layer every rank sums
+ * the k slots in ascending expert order (+ shared expert) exactly as one GPU does.  One exchange per
+ * layer, the result does not depend on the number of ranks, every rank ends with the same bits.
+ *   dnb_epd_init    : after dnb_moe_config, dnb_moe_set_expert_shard(rank*ne/world, ne/world) and the
+ *       registration of the rank's experts (router, norm, shared expert replicated).  Allocates the
+ *       arena for batches of up to max_tokens tokens and writes its 64-byte IPC handle to handle_out.
+ *   dnb_epd_connect : handles = world x 64 bytes (rank r's at byte 64*r), exchanged by any host-side
+ *       all-gather.  NULL is a test hook: every peer pointer becomes this rank's own arena, so with
+ *       world > 1 the absent ranks' flags never arrive and a call runs into its bounded wait (status 24).
+ *   dnb_epd_block_dev / dnb_epd_stack_dev: one block, or all configured layers with identity mixers
+ *       (h <- h + block_l(h), in place), for the SAME nt tokens on every rank; device pointers,
+ *       asynchronous.  Every rank must make the same sequence of calls.  The teardown rule of
+ *       dnb_ep_block_dev applies: barrier on the host before any rank shuts down. */
+int dnb_epd_init(dnb_ctx* ctx, int rank, int world, int max_tokens, void* handle_out);
+int dnb_epd_connect(dnb_ctx* ctx, const void* handles);
+int dnb_epd_block_dev(dnb_ctx* ctx, int layer, const float* h_dev, int nt, float* out_dev);
+int dnb_epd_stack_dev(dnb_ctx* ctx, float* h_dev, int nt);
 /* A stack of the configured layers with identity mixers: h <- h + block_l(h) for
  * l = 0..n_layer-1 (device-resident between layers).  h host [nt][n_embd] in/out. */
 int dnb_moe_stack(dnb_ctx* ctx, const float* h, int nt, float* out);

@@ -165,6 +165,79 @@ def gpu_p2p_rank(rank, world, port):
         dist.destroy_process_group()
 
 
+def gpu_epd_rank(rank, world, port):
+    """Expert-parallel decode (dnb_epd_*): every rank holds ne/world experts and ALL tokens of the batch.
+    For batches of 1, 8 and 32 tokens and a two-layer stack the result must be the same bits on every
+    rank, the same bits as the same exchange run with a world of one (all experts on this GPU), and
+    agree with the ordinary single-GPU block to rounding."""
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import torch
+    import torch.distributed as dist
+
+    import oracle as orc
+    from denno_beta_b200 import cuda as cu, ep
+    from helpers import SEED, make_layer, rel_err
+
+    torch.cuda.set_device(rank)
+    _init(rank, world, port, "nccl")
+    try:
+        e, ff, ne, k = 512, 256, 32, 4
+        for ty in (orc.IQ3_XXS, orc.Q4_K):
+            full = cu.CudaCtx(rank)
+            assert full.moe_config(2, e, ff, ne, k)
+            Ls = [make_layer(orc, full, 0, ty, e, ff, ne, k, bias=True, gate_row=True), make_layer(orc, full, 1, ty, e, ff, ne, k)]
+            one = ep.PeerMemoryDecode(full, max_tokens=32, rank=0, world=1)
+            c = cu.CudaCtx(rank)
+            assert c.moe_config(2, e, ff, ne, k)
+            nl = ne // world
+            c.set_expert_shard(rank * nl, nl)
+            for l, L in enumerate(Ls):
+                kp = L.keep
+                gb, db = kp["gate"].size // ne, kp["down"].size // ne
+                sl = slice(rank * nl * gb, (rank + 1) * nl * gb)
+                sd = slice(rank * nl * db, (rank + 1) * nl * db)
+                assert c.register_experts(l, cu.GATE, ty, e, ff, nl, kp["gate"][sl])
+                assert c.register_experts(l, cu.UP, ty, e, ff, nl, kp["up"][sl])
+                assert c.register_experts(l, cu.DOWN, ty, ff, e, nl, kp["down"][sd])
+                assert c.register_experts(l, cu.SHARED_GATE, ty, e, ff, 1, kp["sg"])
+                assert c.register_experts(l, cu.SHARED_UP, ty, e, ff, 1, kp["su"])
+                assert c.register_experts(l, cu.SHARED_DOWN, ty, ff, e, 1, kp["sd"])
+                c.register_router(l, kp["router_w"], kp["router_bias"], kp["norm_w"], kp["sgr"])
+            pd = ep.PeerMemoryDecode(c, max_tokens=32)
+            for nt in (1, 8, 32):
+                h = orc.synth_normal(SEED, 7820 + nt, 1.0, nt * e).reshape(nt, e)
+                want = full.moe_block(0, h)
+                bufs = {}
+                for name, ctx_, pd_ in (("one", full, one), ("ep", c, pd)):
+                    d_h, d_o = ctx_.dev_alloc(h.nbytes), ctx_.dev_alloc(h.nbytes)
+                    ctx_.upload(d_h, h)
+                    pd_.block_dev(0, d_h, nt, d_o)
+                    assert ctx_.sync()
+                    blk = ctx_.download(d_o, np.empty((nt, e), np.float32))
+                    pd_.stack_dev(d_h, nt)
+                    assert ctx_.sync()
+                    bufs[name] = (blk, ctx_.download(d_h, np.empty((nt, e), np.float32)))
+                    ctx_.dev_free(d_h)
+                    ctx_.dev_free(d_o)
+                assert rel_err(bufs["ep"][0], want) <= 5e-4
+                assert np.array_equal(bufs["ep"][0].view(np.uint32), bufs["one"][0].view(np.uint32)), "block differs from world 1"
+                assert np.array_equal(bufs["ep"][1].view(np.uint32), bufs["one"][1].view(np.uint32)), "stack differs from world 1"
+                t = torch.from_numpy(bufs["ep"][1].view(np.int32).astype(np.int64)).cuda()
+                lo, hi = t.clone(), t.clone()
+                dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+                dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+                assert bool(torch.equal(lo, hi)), "ranks ended with different bits"
+                print("rank %d type %d nt %d: err %.3g, same bits as world 1 and on every rank" % (rank, ty, nt, rel_err(bufs["ep"][0], want)), flush=True)
+            assert c.device_status() == 0
+            torch.cuda.synchronize()
+            dist.barrier()  # nobody tears its arena down while a peer may still store into it
+            c.close()
+            full.close()
+    finally:
+        dist.destroy_process_group()
+
+
 if __name__ == "__main__":
     kind, rank, world, port = sys.argv[1], int(sys.argv[2]), int(sys.argv[3]), int(sys.argv[4])
-    {"cpu": cpu_rank, "gpu": gpu_rank, "gpu_p2p": gpu_p2p_rank}[kind](rank, world, port)
+    {"cpu": cpu_rank, "gpu": gpu_rank, "gpu_p2p": gpu_p2p_rank, "gpu_epd": gpu_epd_rank}[kind](rank, world, port)

@@ -99,3 +99,100 @@ def test_peer_memory_expert_parallel_equals_single_gpu():
     outs = _run_ranks("gpu_p2p", 2, 29660, 900)
     for _, o in outs:
         print(o[-600:])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("ty_name", ["IQ3_XXS", "Q4_K"])
+def test_decode_exchange_on_one_gpu(ty_name):
+    """Expert-parallel decode with a world of one: tables, push, flag wait and combine all run against
+    the rank's own arena.  Batches of 1, 5 and 16 tokens take the decode GEMV kernels, 33 the tiled
+    kernels; each must agree with the ordinary single-GPU block to rounding (the kernels differ), be
+    bit-identical run to run, and the stack entry point must equal the layer-by-layer sum."""
+    import numpy as np
+
+    import oracle as orc
+    from denno_beta_b200 import cuda as cu, ep
+    from helpers import SEED, make_layer, rel_err
+
+    ty = orc.TYPE_BY_NAME[ty_name]
+    e, ff, ne, k = 512, 256, 32, 4
+    c = cu.CudaCtx(0)
+    try:
+        assert c.moe_config(2, e, ff, ne, k)
+        make_layer(orc, c, 0, ty, e, ff, ne, k, bias=True, gate_row=True)
+        make_layer(orc, c, 1, ty, e, ff, ne, k)
+        pd = ep.PeerMemoryDecode(c, max_tokens=40, rank=0, world=1)
+        for nt in (1, 5, 16, 33):
+            h = orc.synth_normal(SEED, 7800 + nt, 1.0, nt * e).reshape(nt, e)
+            want = c.moe_block(0, h)
+            d_h, d_o = c.dev_alloc(h.nbytes), c.dev_alloc(h.nbytes)
+            c.upload(d_h, h)
+            outs = []
+            for _ in range(2):
+                pd.block_dev(0, d_h, nt, d_o)
+                assert c.sync()
+                outs.append(c.download(d_o, np.empty((nt, e), np.float32)))
+            assert rel_err(outs[0], want) <= 5e-4, "nt %d: %.3g" % (nt, rel_err(outs[0], want))
+            assert np.array_equal(outs[0].view(np.uint32), outs[1].view(np.uint32))
+            ref = h.copy()
+            for l in range(2):
+                c.upload(d_h, ref)
+                pd.block_dev(l, d_h, nt, d_o)
+                assert c.sync()
+                ref = (ref + c.download(d_o, np.empty((nt, e), np.float32))).astype(np.float32)
+            c.upload(d_h, h)
+            pd.stack_dev(d_h, nt)
+            assert c.sync()
+            got = c.download(d_h, np.empty((nt, e), np.float32))
+            assert np.array_equal(got.view(np.uint32), ref.view(np.uint32)), "stack vs layer by layer, nt %d" % nt
+            c.dev_free(d_h)
+            c.dev_free(d_o)
+        assert c.device_status() == 0
+    finally:
+        c.close()
+
+
+@pytest.mark.gpu
+def test_decode_exchange_waits_for_an_absent_rank_and_gives_up():
+    """A group of two ranks of which only rank 0 exists: the wait for rank 1's rows runs out (status 24),
+    the call returns, dnb_sync reports DECLINED, the output buffer is untouched, the context stays usable."""
+    import numpy as np
+
+    import oracle as orc
+    from denno_beta_b200 import cuda as cu, ep
+    from helpers import SEED
+
+    e, ff, ne, k, nt = 512, 256, 32, 4, 3
+    c = cu.CudaCtx(0)
+    try:
+        assert c.moe_config(1, e, ff, ne, k)
+        nl = ne // 2
+        c.set_expert_shard(0, nl)
+        for m, (ni, no, n) in ((cu.GATE, (e, ff, nl)), (cu.UP, (e, ff, nl)), (cu.DOWN, (ff, e, nl)),
+                               (cu.SHARED_GATE, (e, ff, 1)), (cu.SHARED_UP, (e, ff, 1)), (cu.SHARED_DOWN, (ff, e, 1))):
+            assert c.synth_experts(0, m, orc.IQ3_XXS, ni, no, n, SEED)
+        c.register_router(0, orc.synth_normal(SEED, 6, 0.02, ne * e), None, np.ones(e, np.float32), None)
+        pd = ep.PeerMemoryDecode(c, max_tokens=8, rank=0, world=2, loopback=True)
+        c.set_wait_limits(flag_polls=3000)
+        h = orc.synth_normal(SEED, 7810, 1.0, nt * e).reshape(nt, e)
+        d_h, d_o = c.dev_alloc(h.nbytes), c.dev_alloc(h.nbytes)
+        c.upload(d_h, h)
+        c.upload(d_o, np.full((nt, e), 3.5, np.float32))
+        pd.block_dev(0, d_h, nt, d_o)
+        assert c.sync() is False
+        assert c.device_status() == 24
+        assert np.all(c.download(d_o, np.empty((nt, e), np.float32)) == 3.5), "a call that gave up must not write its output"
+        c.clear_status()
+        assert c.sync() is True
+        c.dev_free(d_h)
+        c.dev_free(d_o)
+    finally:
+        c.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(_n_gpus() < 2, reason="needs at least 2 GPUs")
+def test_decode_exchange_two_gpus_equals_one():
+    outs = _run_ranks("gpu_epd", 2, 29670, 900)
+    for _, o in outs:
+        print(o[-600:])
