@@ -316,6 +316,186 @@ def run_ours(args, rank, world, local_rank):
     return res
 
 
+def build_shard(ctx, cu, oracle, ty_of_layer, layers, rank, world, bias):
+    """Rank `rank`'s part of the model: experts [rank * NE / world, (rank + 1) * NE / world) of every layer
+    (the same bytes the single-GPU model holds there: the generator is indexed by position in the full
+    tensor), router, norm and shared expert replicated."""
+    nl = NE // world
+    assert ctx.moe_config(layers, E, FF, NE, K)
+    ctx.set_expert_shard(rank * nl, nl)
+    for l in range(layers):
+        ty = ty_of_layer(l)
+        for m, (ni, no, n) in ((cu.GATE, (E, FF, nl)), (cu.UP, (E, FF, nl)), (cu.DOWN, (FF, E, nl)),
+                               (cu.SHARED_GATE, (E, FF, 1)), (cu.SHARED_UP, (E, FF, 1)), (cu.SHARED_DOWN, (FF, E, 1))):
+            assert ctx.synth_experts(l, m, ty, ni, no, n, SEED)
+        rw = oracle.synth_normal(SEED, l * 16 + 6, 0.02, NE * E)
+        rb = oracle.synth_zipf_bias(SEED, l * 16 + 7, 1.1, NE) if bias else None
+        ctx.register_router(l, rw, rb, np.ones(E, np.float32), None)
+    ctx.sync()
+
+
+def same_on_all_ranks(arr, local_rank):
+    """True when every rank holds the same bits in `arr`."""
+    import torch
+    import torch.distributed as dist
+
+    t = torch.from_numpy(np.ascontiguousarray(arr).view(np.int32).astype(np.int64)).cuda(local_rank)
+    lo, hi = t.clone(), t.clone()
+    dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+    dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+    return bool(torch.equal(lo, hi))
+
+
+def run_ours_ep(args, rank, world, local_rank):
+    """N > 1: the SAME workload as N = 1 (config 1: one token through one MoE block per step, IQ3_XXS,
+    LAYERS rotating layer copies) with the experts sharded NE / N per GPU.  Strong scaling: the token is
+    not multiplied by N.  The residual stream is replicated, every rank computes the (token, slot)
+    pairs of its own experts and the result rows cross NVLink once per layer (dnb_epd_*)."""
+    import torch
+    import torch.distributed as dist
+
+    import oracle
+    from denno_beta_b200 import cuda as cu, ep
+
+    ctx = cu.CudaCtx(local_rank)
+    build_shard(ctx, cu, oracle, lambda l: IQ3_XXS, LAYERS, rank, world, False)
+    pd = ep.PeerMemoryDecode(ctx, max_tokens=1)
+    pool = oracle.synth_normal(SEED, 7000, 1.0, POOL * E).reshape(POOL, E)  # the same tokens on every rank
+    d_pool = ctx.dev_alloc(pool.nbytes)
+    d_out = ctx.dev_alloc(E * 4)
+    d_h = ctx.dev_alloc(E * 4)
+    ctx.upload(d_pool, pool)
+
+    def barrier():
+        ctx.sync()
+        dist.barrier()
+
+    K_, W_ = args.steps, max(args.warmup, 3)
+    full, rem = divmod(K_, LAYERS)
+
+    def k_steps(s0):
+        for c_ in range(full):
+            ctx.dev_copy(d_h, d_pool + ((s0 + c_) % POOL) * E * 4, E * 4)
+            pd.stack_dev(d_h, 1)
+        for r_ in range(rem):
+            ctx.dev_copy(d_h, d_pool + ((s0 + full + r_) % POOL) * E * 4, E * 4)
+            pd.block_dev(r_ % LAYERS, d_h, 1, d_out)
+
+    # parity with one GPU: rank 0 also holds the whole model and runs the same exchange with a world of one
+    want = None
+    if rank == 0:
+        one = cu.CudaCtx(local_rank)
+        build_shard(one, cu, oracle, lambda l: IQ3_XXS, LAYERS, 0, 1, False)
+        pd1 = ep.PeerMemoryDecode(one, max_tokens=1, rank=0, world=1)
+        d1 = one.dev_alloc(E * 4)
+        one.upload(d1, pool[3])
+        pd1.stack_dev(d1, 1)
+        assert one.sync()
+        want = one.download(d1, np.empty(E, np.float32))
+        one.close()
+    barrier()  # the ranks enter their first exchange together: a peer's wait for this rank's rows is bounded (~a second)
+    ctx.upload(d_h, pool[3])
+    pd.stack_dev(d_h, 1)
+    assert ctx.sync()
+    got = ctx.download(d_h, np.empty(E, np.float32))
+    same_ranks = same_on_all_ranks(got, local_rank)
+    parity = bool(rank == 0 and np.array_equal(got.view(np.uint32), want.view(np.uint32)))
+
+    for s in range(max(3, (W_ + K_ - 1) // K_)):
+        k_steps(s)
+    barrier()
+    ctx.timer_start()
+    k_steps(0)
+    est_ms = max(ctx.timer_stop(), 1e-3)
+    t = torch.tensor([est_ms], dtype=torch.float64, device="cuda:%d" % local_rank)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    repeats = int(min(500, max(5, np.ceil(100.0 / float(t)))))
+    clocks = Clocks(local_rank)
+    clocks.start()
+    rep_ms = []
+    launches = 0
+    for r in range(repeats):
+        barrier()
+        l0 = ctx.launch_count()
+        ctx.timer_start()
+        k_steps(r)
+        rep_ms.append(ctx.timer_stop())
+        launches = ctx.launch_count() - l0
+    barrier()
+    # end to end: the token row from pinned host memory to the device, one block, the result row back
+    out_host = np.empty(E, np.float32)
+    e2e_n = min(K_, 200)
+    for s in range(8):
+        ctx.upload(d_h, pool[s % POOL])
+        pd.block_dev(s % LAYERS, d_h, 1, d_out)
+        ctx.download(d_out, out_host)
+    e2e_ms = []
+    for r in range(5):
+        barrier()
+        t0 = time.perf_counter()
+        for s in range(e2e_n):
+            ctx.upload(d_h, pool[(r * e2e_n + s) % POOL])
+            pd.block_dev(s % LAYERS, d_h, 1, d_out)
+            ctx.download(d_out, out_host)
+        e2e_ms.append((time.perf_counter() - t0) * 1e3 / e2e_n * K_)
+    clk = clocks.stop()
+    barrier()
+    status = ctx.device_status()
+    ctx.profile(True)
+    for s in range(4):
+        k_steps(s) if full else None
+    ctx.sync()
+    prof = ctx.profile_read()
+    ctx.profile(False)
+    barrier()
+    t = torch.tensor(np.concatenate([rep_ms, e2e_ms, [float(status)]]), dtype=torch.float64, device="cuda:%d" % local_rank)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    t = t.cpu().numpy()
+    rep_ms, e2e_ms, status = t[:len(rep_ms)], t[len(rep_ms):-1], int(t[-1])
+    assert status == 0, "a bounded device wait gave up during the timed region (status %d): the numbers are void" % status
+    dist.barrier()
+    ctx.close()
+    if rank != 0:
+        if not args.no_extras:
+            guarded_ep_extras(None, cu, oracle, rank, world, local_rank)
+        return None
+    ms_dev, ms_e2e = float(np.median(rep_ms)), float(np.median(e2e_ms))
+    hbm_peak, _, peak_kind = peaks()
+    g_b, d_b = expert_bytes(IQ3_XXS)
+    block_bytes = NE * E * 4 + (K + 1) * (2 * g_b + d_b)
+    achieved = block_bytes / (ms_dev / K_ * 1e-3) / 1e9
+    res = {
+        "metric": "moe_decode_tok_s", "value": K_ / (ms_dev * 1e-3), "unit": "token*layer/s (1 MoE block per step)",
+        "n_gpus": world, "steps": K_, "warmup": W_, "ms_per_step": ms_dev / K_, "higher_is_better": True,
+        "repeats": int(len(rep_ms)), "timed_region_s": float(np.sum(rep_ms) * 1e-3),
+        "repeat_ms": {"min": float(np.min(rep_ms)), "median": ms_dev, "max": float(np.max(rep_ms)),
+                      "note": "each repeat = exactly `steps` steps, event-timed, max over ranks; value uses the median repeat"},
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "config1: 1 MoE block decode, 1 token, e2048 ff512 512 experts top-10 + 1 shared, IQ3_XXS",
+                   "l2": "inputs larger than L2: %d rotating layer copies (%.0f MB of weights per cycle over all GPUs) and %d tokens"
+                         % (LAYERS, LAYERS * block_bytes / 1e6, POOL),
+                   "call": "value: %d blocks per dnb_epd_stack_dev call on every rank, the last steps %% %d as single "
+                           "dnb_epd_block_dev calls; e2e: token row host -> device, one dnb_epd_block_dev, result row back"
+                           % (LAYERS, LAYERS),
+                   "parallelism": "expert-parallel %d/%d: %d experts per GPU, residual stream replicated, result rows stored "
+                                  "into every rank's memory over NVLink once per layer (no collective library on the data path); "
+                                  "the ONE token is not multiplied by the GPU count, so a step is latency-bound and more GPUs do "
+                                  "not make it faster" % (NE, world, NE // world)},
+        "e2e": {"value": K_ / (ms_e2e * 1e-3), "unit": "token*layer/s", "h2d_bytes_per_step": E * 4, "d2h_bytes_per_step": E * 4,
+                "us_per_call": ms_e2e / K_ * 1e3, "note": "per rank; max over ranks"},
+        "device_status": status, "parity_vs_1gpu": parity, "same_bits_on_every_rank": same_ranks,
+        "gpu_launches": int(launches),
+        "clocks": clk,
+        "roofline": {"bound": "hbm", "kernel": "all kernels of a step (the block's bytes over the step time, %d GPUs)" % world,
+                     "achieved": achieved, "peak": hbm_peak * world, "unit": "GB/s", "frac": achieved / (hbm_peak * world),
+                     "peak_kind": peak_kind, "traffic": None, "bytes_per_launch": block_bytes, "us_per_launch": ms_dev / K_ * 1e3},
+        "kernels_ms_rank0": {k: round(v["ms"], 4) for k, v in prof.items()},
+    }
+    if not args.no_extras:
+        res["extras"] = guarded_ep_extras(res, cu, oracle, rank, world, local_rank)
+    return res
+
+
 def extras(ctx, cu, oracle):
     """Config 0 (single Q4_K GEMV 4096x4096, HBM GB/s) on rotating weight copies, and the
     same GEMV in the path's other block formats (IQ3_XXS, Q6_K, Q8_0)."""
@@ -400,7 +580,7 @@ def prefill_extras(cu, oracle, device, layers=4):
 _EMIT = {"fd": None}
 
 
-def guarded_ep_extras(partial, cu, oracle, rank, world, local_rank, limit_s=420.0):
+def guarded_ep_extras(partial, cu, oracle, rank, world, local_rank, limit_s=600.0):
     """The expert-parallel extras under a watchdog: whatever happens to them (an exception on
     one rank leaves the others waiting in a collective), rank 0 still prints the bench line,
     with the reason in place of the extras, and every rank exits 0."""
@@ -408,7 +588,7 @@ def guarded_ep_extras(partial, cu, oracle, rank, world, local_rank, limit_s=420.
 
     def bail(why):
         if partial is not None and _EMIT["fd"] is not None:
-            partial["extras"] = {"config2_q4k_prefill_512_expert_parallel": {"error": why}}
+            partial["extras"] = {"error": why}
             os.write(_EMIT["fd"], (json.dumps(partial) + "\n").encode())
         # This rank's arena is memory its peers' kernels may still be storing into.  Every device-side
         # wait of the exchange gives up after ~0.25 s (three of them per block at most), so a few
@@ -420,17 +600,82 @@ def guarded_ep_extras(partial, cu, oracle, rank, world, local_rank, limit_s=420.
     timer.daemon = True
     timer.start()
     try:
-        out = ep_prefill_extras(cu, oracle, rank, world, local_rank)
+        out = {"config3_decode_stack48_expert_parallel": ep_decode_stack(cu, oracle, rank, world, local_rank)}
+        out["config2_q4k_prefill_512_expert_parallel"] = ep_prefill_extras(cu, oracle, rank, world, local_rank)
+        out["config4_prefill_stack48_14018_expert_parallel"] = ep_stack_prefill(cu, oracle, rank, world, local_rank)
     except Exception as ex:  # the other ranks run into their own watchdog
         bail("expert-parallel extras failed on rank %d: %s" % (rank, ex))
     timer.cancel()
     return out
 
 
+def ep_decode_stack(cu, oracle, rank, world, local_rank):
+    """Config 3 across `world` GPUs: the 48-layer decode stack (40 IQ3_XXS + 8 Q4_K layers, every sixth),
+    experts sharded 512 / world per GPU, batches of 1, 8 and 32 tokens, one dnb_epd_stack_dev call per
+    step.  The same weights and tokens as the single-GPU line; rank 0 also holds the whole model and
+    checks that the expert-parallel result has the bits of the same exchange run with a world of one."""
+    import torch
+    import torch.distributed as dist
+
+    from denno_beta_b200 import ep
+
+    ty_of = lambda l: Q4_K if l % 6 == 5 else IQ3_XXS
+    ctx = cu.CudaCtx(local_rank)
+    build_shard(ctx, cu, oracle, ty_of, 48, rank, world, False)
+    pd = ep.PeerMemoryDecode(ctx, max_tokens=32)
+    one = pd1 = None
+    if rank == 0:
+        one = cu.CudaCtx(local_rank)
+        build_shard(one, cu, oracle, ty_of, 48, 0, 1, False)
+        pd1 = ep.PeerMemoryDecode(one, max_tokens=32, rank=0, world=1)
+    out = {"experts_per_rank": NE // world,
+           "exchange": "result rows stored into every rank's memory by this library's kernels, one flag wait per layer"}
+    for B in (1, 8, 32):
+        h = oracle.synth_normal(SEED, 8100 + B, 1.0, B * E).reshape(B, E)
+        d_src, d_h = ctx.dev_alloc(h.nbytes), ctx.dev_alloc(h.nbytes)
+        ctx.upload(d_src, h)
+        ctx.sync()
+        dist.barrier()  # enter the exchange together (the waits for a peer's rows are bounded)
+        for _ in range(3):
+            ctx.dev_copy(d_h, d_src, h.nbytes)
+            pd.stack_dev(d_h, B)
+        ctx.sync()
+        got = ctx.download(d_h, np.empty((B, E), np.float32))
+        parity = None
+        if rank == 0:
+            d1 = one.dev_alloc(h.nbytes)
+            one.upload(d1, h)
+            pd1.stack_dev(d1, B)
+            assert one.sync()
+            parity = bool(np.array_equal(got.view(np.uint32), one.download(d1, np.empty((B, E), np.float32)).view(np.uint32)))
+            one.dev_free(d1)
+        dist.barrier()
+        same = same_on_all_ranks(got, local_rank)
+        reps = 10
+        dist.barrier()
+        ctx.timer_start()
+        for _ in range(reps):
+            ctx.dev_copy(d_h, d_src, h.nbytes)
+            pd.stack_dev(d_h, B)
+        ms = torch.tensor([ctx.timer_stop() / reps], dtype=torch.float64, device="cuda:%d" % local_rank)
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        out["batch%d" % B] = {"ms_per_step": float(ms), "tok_per_s": B / (float(ms) * 1e-3), "parity_vs_1gpu": parity,
+                              "same_bits_on_every_rank": same}
+        ctx.dev_free(d_src)
+        ctx.dev_free(d_h)
+    out["device_status"] = ctx.device_status()
+    dist.barrier()
+    ctx.close()
+    if one is not None:
+        one.close()
+    return out
+
+
 def ep_prefill_extras(cu, oracle, rank, world, local_rank):
-    """Config 2 across `world` GPUs, expert parallel: 512/world experts per GPU, the
-    512-token chunk split evenly over the ranks (strong scaling), dispatch and return by
-    NCCL all-to-all.  Timed with events on the block's stream, max over ranks."""
+    """Config 2 across `world` GPUs, expert parallel: 512/world experts per GPU (the same weights as the
+    single-GPU line), the 512-token chunk split evenly over the ranks (strong scaling), or one chunk per
+    rank.  Timed with events on the block's stream, max over ranks.  Rank 0 also holds the whole layer
+    and checks that the expert-parallel output has the single-GPU block's bits."""
     import torch
     import torch.distributed as dist
 
@@ -439,17 +684,12 @@ def ep_prefill_extras(cu, oracle, rank, world, local_rank):
     layers, nt_total = 4, 512
     nl, nt = NE // world, nt_total // world
     ctx = cu.CudaCtx(local_rank)
-    assert ctx.moe_config(layers, E, FF, NE, K)
-    ctx.set_expert_shard(rank * nl, nl)
-    for l in range(layers):
-        for m, (ni, no, n) in ((cu.GATE, (E, FF, nl)), (cu.UP, (E, FF, nl)), (cu.DOWN, (FF, E, nl)),
-                               (cu.SHARED_GATE, (E, FF, 1)), (cu.SHARED_UP, (E, FF, 1)), (cu.SHARED_DOWN, (FF, E, 1))):
-            assert ctx.synth_experts(l, m, Q4_K, ni, no, n, SEED + rank)
-        ctx.register_router(l, oracle.synth_normal(SEED, l * 16 + 6, 0.02, NE * E), oracle.synth_zipf_bias(SEED, l * 16 + 7, 1.1, NE),
-                            np.ones(E, np.float32), None)
+    build_shard(ctx, cu, oracle, lambda l: Q4_K, layers, rank, world, True)
     h_all = oracle.synth_normal(SEED, 8000, 1.0, nt_total * E).reshape(nt_total, E)
 
     def timed(step, reps=16):
+        ctx.sync()
+        dist.barrier()  # enter the exchange together (the device-side waits for a peer are bounded)
         for l in range(2 * layers):
             step(l % layers)
         ctx.sync()
@@ -469,15 +709,34 @@ def ep_prefill_extras(cu, oracle, rank, world, local_rank):
     out["nccl_all_to_all_strong"] = {"ms_per_chunk_layer": ms, "tok_per_s_layer": nt_total / (ms * 1e-3), "tokens_per_rank": nt,
                                      "exchange": "NCCL all_to_all_single (dispatch rows fp32 + ids, return rows fp32)",
                                      "scaling": "strong (one 512-token chunk over %d GPUs)" % world}
+    ctx.set_stream(None)
     # (b), (c) rows stored into the peers' memory by this library's kernels, no collective, no host round trip
     pm = ep.PeerMemoryExpertParallel(ctx, max_tokens=nt_total)
     d_h = ctx.dev_alloc(nt_total * E * 4)
     d_o = ctx.dev_alloc(nt_total * E * 4)
     ctx.upload(d_h, np.ascontiguousarray(h_all[rank * nt:(rank + 1) * nt]))
     ms = timed(lambda l: pm.block_dev(l, d_h, nt, d_o))
+    # parity: the ranks' outputs of layer 0, gathered, against the single-GPU block on the whole chunk
+    pm.block_dev(0, d_h, nt, d_o)
+    ctx.sync()
+    mine = torch.from_numpy(ctx.download(d_o, np.empty((nt, E), np.float32))).cuda(local_rank)
+    parts = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(parts, mine)
+    parity = None
+    if rank == 0:
+        one = cu.CudaCtx(local_rank)
+        build_shard(one, cu, oracle, lambda l: Q4_K, 1, 0, 1, True)
+        d1, d2 = one.dev_alloc(h_all.nbytes), one.dev_alloc(h_all.nbytes)
+        one.upload(d1, h_all)
+        assert one.moe_block_dev(0, d1, nt_total, d2)
+        one.sync()
+        want = one.download(d2, np.empty((nt_total, E), np.float32))
+        one.close()
+        got = torch.cat(parts).cpu().numpy()
+        parity = bool(np.array_equal(got.view(np.uint32), want.view(np.uint32)))
     out["peer_memory_strong"] = {"ms_per_chunk_layer": ms, "tok_per_s_layer": nt_total / (ms * 1e-3), "tokens_per_rank": nt,
                                  "exchange": "peer stores from the dispatch kernel and the down-GEMM epilogue, flag-ordered",
-                                 "scaling": "strong (one 512-token chunk over %d GPUs)" % world}
+                                 "scaling": "strong (one 512-token chunk over %d GPUs)" % world, "parity_vs_1gpu": parity}
     # every rank owns a whole 512-token chunk (a prompt's chunks spread over the ranks)
     ctx.upload(d_h, np.ascontiguousarray(oracle.synth_normal(SEED, 8000 + rank, 1.0, nt_total * E)))
     ms = timed(lambda l: pm.block_dev(l, d_h, nt_total, d_o))
@@ -498,45 +757,53 @@ def ep_prefill_extras(cu, oracle, rank, world, local_rank):
     out["device_status"] = ctx.device_status()
     dist.barrier()
     ctx.close()
-    out["config4_prefill_stack48_14018"] = ep_stack_prefill(cu, oracle, ep, rank, world, local_rank)
     return out
 
 
-def ep_stack_prefill(cu, oracle, ep, rank, world, local_rank):
-    """Config 4 across `world` GPUs: 48 all-Q4_K blocks, a 14,018-token prompt in 512-token
-    chunks (27 x 512 + 194), the chunks dealt to the ranks round-robin, every chunk-step
-    through all 48 layers with the peer-memory exchange (out of one block is the input of
-    the next; the identity mixers' residual add is left out, it is one more pass over 4 MB)."""
+def ep_stack_prefill(cu, oracle, rank, world, local_rank):
+    """Config 4 across `world` GPUs: 48 all-Q4_K blocks (the single-GPU line's weights), a 14,018-token
+    prompt in 512-token chunks (27 x 512 + 194) dealt to the ranks round-robin, every chunk-step through
+    all 48 layers with the peer-memory exchange and the identity mixers' residual add (dnb_ep_stack_dev,
+    direct launches; the single-GPU line replays a CUDA graph).  Rank 0 also holds the whole model and
+    checks that its first chunk comes out with the single-GPU stack's bits."""
     import torch
     import torch.distributed as dist
 
+    from denno_beta_b200 import ep
+
     n_layer, n_tok = 48, 14018
-    nl = NE // world
     chunks = [512] * (n_tok // 512) + ([n_tok % 512] if n_tok % 512 else [])
     steps = (len(chunks) + world - 1) // world
     mine = [chunks[st * world + rank] if st * world + rank < len(chunks) else 1 for st in range(steps)]  # idle rank: 1 dummy token
     ctx = cu.CudaCtx(local_rank)
-    assert ctx.moe_config(n_layer, E, FF, NE, K)
-    ctx.set_expert_shard(rank * nl, nl)
-    for l in range(n_layer):
-        for m, (ni, no, n) in ((cu.GATE, (E, FF, nl)), (cu.UP, (E, FF, nl)), (cu.DOWN, (FF, E, nl)),
-                               (cu.SHARED_GATE, (E, FF, 1)), (cu.SHARED_UP, (E, FF, 1)), (cu.SHARED_DOWN, (FF, E, 1))):
-            assert ctx.synth_experts(l, m, Q4_K, ni, no, n, SEED + (rank if m in (cu.GATE, cu.UP, cu.DOWN) else 0))
-        ctx.register_router(l, oracle.synth_normal(SEED, l * 16 + 6, 0.02, NE * E), oracle.synth_zipf_bias(SEED, l * 16 + 7, 1.1, NE),
-                            np.ones(E, np.float32), None)
+    build_shard(ctx, cu, oracle, lambda l: Q4_K, n_layer, rank, world, True)
     pm = ep.PeerMemoryExpertParallel(ctx, max_tokens=512)
-    d_a = ctx.dev_alloc(512 * E * 4)
-    d_b = ctx.dev_alloc(512 * E * 4)
-    ctx.upload(d_a, oracle.synth_normal(SEED, 8200 + rank, 1.0, 512 * E))
+    h = oracle.synth_normal(SEED, 8200, 1.0, 512 * E).reshape(512, E)  # every chunk reuses these rows, as on one GPU
+    d_src = ctx.dev_alloc(h.nbytes)
+    d_h = ctx.dev_alloc(h.nbytes)
+    ctx.upload(d_src, h)
 
     def prompt():
         for nt in mine:
-            a, b = d_a, d_b
-            for l in range(n_layer):
-                pm.block_dev(l, a, nt, b)
-                a, b = b, a
+            ctx.dev_copy(d_h, d_src, nt * E * 4)
+            pm.stack_dev(d_h, nt)
+    ctx.sync()
+    dist.barrier()
     prompt()
     ctx.sync()
+    parity = None
+    # the last chunk-step this rank ran (nt = mine[-1]) against the single-GPU stack on the same rows
+    got = ctx.download(d_h, np.empty((512, E), np.float32))[:mine[-1]]
+    if rank == 0:
+        one = cu.CudaCtx(local_rank)
+        build_model(one, cu, Q4_K, n_layer, True)
+        d1 = one.dev_alloc(h.nbytes)
+        one.upload(d1, h)
+        assert one.moe_stack_dev(d1, mine[-1])
+        one.sync()
+        want = one.download(d1, np.empty((512, E), np.float32))[:mine[-1]]
+        one.close()
+        parity = bool(np.array_equal(got.view(np.uint32), want.view(np.uint32)))
     dist.barrier()
     ctx.timer_start()
     prompt()
@@ -548,7 +815,8 @@ def ep_stack_prefill(cu, oracle, ep, rank, world, local_rank):
     ctx.close()
     return {"seconds": ms * 1e-3, "tok_per_s": n_tok / (ms * 1e-3), "chunk_steps": steps, "chunks": len(chunks),
             "algorithmic_tflops": n_tok * n_layer * (11 * 6291456 + 2097152) / (ms * 1e-3) / 1e12,
-            "exchange": "peer memory (dnb_ep_block_dev), chunks dealt round-robin to %d GPUs" % world, "device_status": status}
+            "exchange": "peer memory (dnb_ep_stack_dev), chunks dealt round-robin to %d GPUs" % world, "device_status": status,
+            "parity_vs_1gpu": parity}
 
 
 def stack_extras(cu, oracle, device):
@@ -770,7 +1038,7 @@ def main():
 
             torch.cuda.set_device(local_rank)
             dist.init_process_group("nccl", device_id=torch.device("cuda:%d" % local_rank))
-        res = run_ours(args, rank, world, local_rank)
+        res = run_ours_ep(args, rank, world, local_rank) if world > 1 else run_ours(args, rank, world, local_rank)
         if world > 1:
             import torch.distributed as dist
 

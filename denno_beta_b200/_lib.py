@@ -61,6 +61,7 @@ SIGNATURES = {
     "dnb_ep_connect": (_i, [_vp, _vp]),
     "dnb_ep_block_dev": (_i, [_vp, _i, _vp, _i, _vp]),
     "dnb_ep_connect_loopback": (_i, [_vp]),
+    "dnb_ep_stack_dev": (_i, [_vp, _vp, _i]),
     "dnb_epd_init": (_i, [_vp, _i, _i, _i, _vp]),
     "dnb_epd_connect": (_i, [_vp, _vp]),
     "dnb_epd_block_dev": (_i, [_vp, _i, _vp, _i, _vp]),

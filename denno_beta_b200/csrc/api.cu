@@ -171,6 +171,8 @@ static int run_graphed(dnb_ctx* c, const GraphKey& key, F enqueue) {
     return DNB_OK;
 }
 
+int graphed(dnb_ctx* c, const GraphKey& key, const std::function<int()>& enqueue) { return run_graphed(c, key, enqueue); }
+
 // Wait for the stream at the end of a host-buffer call.  A decode-sized call lasts a few
 // tens of microseconds, less than it takes a blocked thread to be woken, so the host polls
 // the stream for up to two milliseconds before it falls back to the blocking wait.

@@ -6,6 +6,7 @@
 #include <cuda_fp16.h>
 #include <stdint.h>
 #include <stddef.h>
+#include <functional>
 #include <map>
 #include <string>
 #include <vector>
@@ -172,6 +173,9 @@ void set_error(const char* fmt, ...);
 void ep_release(dnb_ctx* c);  // frees the peer-memory expert-parallel state, if any (ep_p2p.cu)
 void epd_release(dnb_ctx* c); // the same for the decode exchange (ep_decode.cu)
 int ensure_workspace(dnb_ctx* c, int nt);  // device buffers of the MoE pipeline for nt tokens (api.cu)
+// Run a launch sequence directly the first time `key` is seen, capture it into a CUDA graph the second time,
+// replay it afterwards (api.cu).
+int graphed(dnb_ctx* c, const GraphKey& key, const std::function<int()>& enqueue);
 
 struct ProfScope {
     dnb_ctx* c; cudaStream_t st; cudaEvent_t b = nullptr;

@@ -81,9 +81,12 @@ __global__ void epd_mask_kernel(const int32_t* __restrict__ sels, int n, int fir
 // packed row of the tiled path; else row t*per+s of the decode GEMV path).
 __global__ void __launch_bounds__(256)
 epd_push_kernel(const float* __restrict__ hrow, const int32_t* __restrict__ sels, const int32_t* __restrict__ pos, int k,
-                int per, int e, int first, int n_local, int world, int me, uint32_t seq, size_t slot_stride, EpdPeers peers,
+                int per, int e, int first, int n_local, int world, int me, uint32_t* seq_dev, size_t slot_stride, EpdPeers peers,
                 unsigned int* ticket) {
     const int i = blockIdx.x, tid = threadIdx.x;
+    // The call's sequence number lives on the device (a captured launch sequence can be replayed): this
+    // kernel works with the next number and its last CTA, after every other CTA has read it, stores it back.
+    const uint32_t seq = *reinterpret_cast<volatile uint32_t*>(seq_dev) + 1u;
     const int t = i / k, s = i - t * k;
     const int ex = sels[i] - first;
     if (ex >= 0 && ex < n_local) {
@@ -105,6 +108,7 @@ epd_push_kernel(const float* __restrict__ hrow, const int32_t* __restrict__ sels
     }
     __syncthreads();
     if (last && tid < world) epd_st_release_sys(&peers.arena[tid]->flag[me], seq);
+    if (last && tid == 0) *seq_dev = seq;
 }
 
 // One CTA per token: wait (bounded) until every rank has stored its rows of this call, then the weighted
@@ -113,9 +117,11 @@ epd_push_kernel(const float* __restrict__ hrow, const int32_t* __restrict__ sels
 __global__ void __launch_bounds__(256)
 epd_combine_kernel(const EpdArena* mine, const float* __restrict__ slots, const float* __restrict__ wts, int k, int e,
                    const float* __restrict__ sh, size_t sh_stride, const float* __restrict__ shcoef,
-                   const float* __restrict__ residual, float* __restrict__ out, int world, uint32_t seq, int polls,
-                   int* status) {
+                   const float* __restrict__ residual, float* __restrict__ out, int world, const uint32_t* seq_dev,
+                   size_t slot_stride, int polls, int* status) {
     const int t = blockIdx.x, tid = threadIdx.x;
+    const uint32_t seq = *seq_dev;  // the push kernel before this one stored the call's number
+    slots += (size_t)(seq & 1u) * slot_stride;
     __shared__ int ok_all;
     __shared__ float pw[32];
     if (tid == 0) ok_all = 1;
@@ -173,7 +179,7 @@ epd_combine_kernel(const EpdArena* mine, const float* __restrict__ slots, const 
 
 struct EpdState {
     int rank = 0, world = 1, max_tokens = 0, n_local = 0;
-    uint32_t seq = 0;
+    uint32_t* seq_dev = nullptr;  // calls made so far
     bool connected = false, loopback = false;
     uint8_t* arena = nullptr;
     size_t arena_bytes = 0, off_slots = 0, slot_stride = 0;  // slot_stride: floats of one parity buffer
@@ -191,6 +197,7 @@ void epd_release(dnb_ctx* c) {
     if (s->arena) cudaFree(s->arena);
     if (s->ticket) cudaFree(s->ticket);
     if (s->msel) cudaFree(s->msel);
+    if (s->seq_dev) cudaFree(s->seq_dev);
     delete s;
     c->epd = nullptr;
 }
@@ -216,18 +223,45 @@ static int epd_block(dnb_ctx* c, EpdState* s, int layer, const float* h, int nt,
         return DNB_DECLINED;
     }
     int rc;
-    if (L.norm_w)
-        if ((rc = launch_rmsnorm(c, st, h, L.norm_w, M.eps, nt, M.e, w.xn))) return rc;
-    const float* x = L.norm_w ? w.xn : h;
-    if ((rc = launch_router_logits(c, st, x, nt, M.e, L.router_w, L.router_bias, M.ne, w.logits))) return rc;
-    if ((rc = launch_topk(c, st, w.logits, nt, M.ne, M.k, M.norm_topk, w.sels, w.wts, nullptr))) return rc;
     const int per = M.k + (fold ? 1 : 0);
-    const uint32_t seq = ++s->seq;
     const int32_t* pos = nullptr;
     const float* sh = nullptr;
     size_t sh_stride = 0;
     bool done = false;
-    if (nt <= kDecodeBatchMax && c->decode_fast && per <= 64) {
+    const float* x = nullptr;
+    if (nt == 1 && c->decode_fast) {
+        // one token: the fused router kernel (RMSNorm, logits, top-k and the segment tables, with the other ranks'
+        // slots as empty segments) and the decode GEMV kernels, chained with programmatic dependent launch
+        rc = launch_router_decode(c, st, h, M, L, w, fold, c->ticket);
+        if (rc == DNB_OK) {
+            x = w.xn;
+            rc = launch_seg_gemv_m1(c, st, L.m[0].type, true, true, w.seg_gu, nullptr, per, M.e, M.ff, w.xn, M.e, nullptr, w.act,
+                                    nullptr, "gemv_gate_up", PermOut{nullptr, 0, M.ne >= 4 * kActRep ? w.xn_perm : nullptr});
+            if (rc == DNB_DECLINED)
+                rc = launch_seg_matmul(c, st, L.m[0].type, true, w.seg_gu, nullptr, per, M.e, M.ff, w.xn, M.e, w.row_token, w.act, 1);
+            if (rc) return rc;
+            rc = launch_seg_gemv_m1(c, st, L.m[2].type, false, false, w.seg_dn, nullptr, per, M.ff, M.e, w.act, M.ff, nullptr,
+                                    w.hrow, nullptr, "gemv_down");
+            if (rc == DNB_DECLINED)
+                rc = launch_seg_matmul(c, st, L.m[2].type, false, w.seg_dn, nullptr, per, M.ff, M.e, w.act, M.ff, nullptr, w.hrow, 1);
+            if (rc) return rc;
+            if (fold) {
+                sh = w.hrow + (size_t)M.k * M.e;
+                sh_stride = (size_t)per * M.e;
+            }
+            done = true;
+        } else if (rc != DNB_DECLINED) {
+            return rc;
+        }
+    }
+    if (!done) {
+        if (L.norm_w)
+            if ((rc = launch_rmsnorm(c, st, h, L.norm_w, M.eps, nt, M.e, w.xn))) return rc;
+        x = L.norm_w ? w.xn : h;
+        if ((rc = launch_router_logits(c, st, x, nt, M.e, L.router_w, L.router_bias, M.ne, w.logits))) return rc;
+        if ((rc = launch_topk(c, st, w.logits, nt, M.ne, M.k, M.norm_topk, w.sels, w.wts, nullptr))) return rc;
+    }
+    if (!done && nt <= kDecodeBatchMax && c->decode_fast && per <= 64) {
         // decode GEMV kernels over one-row segments; pairs of other ranks are empty segments
         epd_tables_kernel<<<nt, 64, 0, st>>>(w.sels, nt, M.k, M.shard_first, s->n_local, L.m[0].dev, L.m[1].dev, L.m[2].dev,
                                              L.m[0].expert_bytes, L.m[1].expert_bytes, L.m[2].expert_bytes,
@@ -280,13 +314,13 @@ static int epd_block(dnb_ctx* c, EpdState* s, int layer, const float* h, int nt,
     {
         ProfScope p_(c, st, "epd_push");
         epd_push_kernel<<<nt * M.k, 256, 0, st>>>(w.hrow, w.sels, pos, M.k, per, M.e, M.shard_first, s->n_local, s->world, s->rank,
-                                                  seq, s->slot_stride, s->peers, s->ticket);
+                                                  s->seq_dev, s->slot_stride, s->peers, s->ticket);
     }
     {
         ProfScope p_(c, st, "epd_wait_combine");
-        const float* slots = (const float*)(s->arena + s->off_slots) + (size_t)(seq & 1u) * s->slot_stride;
+        const float* slots = (const float*)(s->arena + s->off_slots);
         epd_combine_kernel<<<nt, 256, 0, st>>>((const EpdArena*)s->arena, slots, w.wts, M.k, M.e, sh, sh_stride, coef, residual, out,
-                                               s->world, seq, c->flag_polls, c->status);
+                                               s->world, s->seq_dev, s->slot_stride, c->flag_polls, c->status);
     }
     c->launches += 2;
     DNB_CUDA(cudaGetLastError());
@@ -321,6 +355,8 @@ extern "C" int dnb_epd_init(dnb_ctx* c, int rank, int world, int max_tokens, voi
     DNB_CUDA(cudaMalloc((void**)&s->ticket, 4));
     DNB_CUDA(cudaMemset(s->ticket, 0, 4));
     DNB_CUDA(cudaMalloc((void**)&s->msel, (size_t)max_tokens * M.k * 4));
+    DNB_CUDA(cudaMalloc((void**)&s->seq_dev, 4));
+    DNB_CUDA(cudaMemset(s->seq_dev, 0, 4));
     DNB_CUDA(cudaDeviceSynchronize());
     cudaIpcMemHandle_t h;
     DNB_CUDA(cudaIpcGetMemHandle(&h, s->arena));
@@ -364,7 +400,7 @@ extern "C" int dnb_epd_block_dev(dnb_ctx* c, int layer, const float* h_dev, int 
     DNB_CUDA(cudaSetDevice(c->device));
     int rc = ensure_workspace(c, nt);
     if (rc) return rc;
-    return epd_block(c, s, layer, h_dev, nt, nullptr, out_dev);
+    return graphed(c, GraphKey{6, layer, nt, h_dev, out_dev}, [&]() { return epd_block(c, s, layer, h_dev, nt, nullptr, out_dev); });
 }
 
 extern "C" int dnb_epd_stack_dev(dnb_ctx* c, float* h_dev, int nt) {
@@ -385,7 +421,12 @@ extern "C" int dnb_epd_stack_dev(dnb_ctx* c, float* h_dev, int nt) {
     DNB_CUDA(cudaSetDevice(c->device));
     int rc = ensure_workspace(c, nt);
     if (rc) return rc;
-    for (int l = 0; l < M.n_layer; ++l)
-        if ((rc = epd_block(c, s, l, h_dev, nt, h_dev, h_dev))) return rc;
-    return DNB_OK;
+    // the launch sequence holds no per-call argument (the sequence number is on the device): replay it as a graph
+    return graphed(c, GraphKey{5, 0, nt, h_dev, nullptr}, [&]() -> int {
+        for (int l = 0; l < M.n_layer; ++l) {
+            const int r = epd_block(c, s, l, h_dev, nt, h_dev, h_dev);
+            if (r) return r;
+        }
+        return DNB_OK;
+    });
 }

@@ -492,3 +492,17 @@ extern "C" int dnb_ep_block_dev(dnb_ctx* c, int layer, const float* h_dev, int n
     return launch_combine(c, st, (const float*)(s->arena + s->off_h), nullptr, w.wts, nt, M.k, M.e, shared ? w.sh : nullptr, coef,
                           out_dev);
 }
+
+// All configured layers with identity mixers for this rank's nt tokens: h <- h + block_l(h), in place
+// (the expert-parallel form of dnb_moe_stack_dev; the residual add is the same separate-rounding add).
+extern "C" int dnb_ep_stack_dev(dnb_ctx* c, float* h_dev, int nt) {
+    if (!c || !c->ep || !h_dev || nt < 1) return DNB_ERR_ARG;
+    const Model& M = c->model;
+    int rc = ensure_workspace(c, nt);
+    if (rc) return rc;
+    for (int l = 0; l < M.n_layer; ++l) {
+        if ((rc = dnb_ep_block_dev(c, l, h_dev, nt, c->ws.out))) return rc;
+        if ((rc = launch_add_inplace(c, c->stream, h_dev, c->ws.out, (size_t)nt * M.e))) return rc;
+    }
+    return DNB_OK;
+}

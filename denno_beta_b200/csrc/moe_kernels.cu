@@ -460,7 +460,7 @@ router_decode_kernel(const float* __restrict__ h, const float* __restrict__ norm
                      float* __restrict__ wts, const uint8_t* gate, const uint8_t* up, const uint8_t* down, size_t eb_g,
                      size_t eb_u, size_t eb_d, const uint8_t* sg, const uint8_t* su, const uint8_t* sdn,
                      SegDesc* seg_gu, SegDesc* seg_dn, int32_t* row_token, int32_t* pos, int32_t* nseg,
-                     unsigned int* ticket, float* __restrict__ xn_perm, int gate_type) {
+                     unsigned int* ticket, float* __restrict__ xn_perm, int gate_type, int shard_first, int shard_count) {
     extern __shared__ __align__(16) float xs[];  // [e]
     __shared__ float red[4];
     __shared__ int is_last;
@@ -541,9 +541,13 @@ router_decode_kernel(const float* __restrict__ h, const float* __restrict__ norm
     topk_block(logits, ne, k, norm_topk, sm, sels, wts, nullptr);
     __syncthreads();
     if (tid < k) {
-        const int ex = sm.ssel[tid];
-        seg_gu[tid] = SegDesc{gate + (size_t)ex * eb_g, up + (size_t)ex * eb_u, 1u, (uint32_t)tid};
-        seg_dn[tid] = SegDesc{down + (size_t)ex * eb_d, nullptr, 1u, (uint32_t)tid};
+        // Expert parallel: only experts [shard_first, shard_first + shard_count) are resident here (indexed from
+        // 0 in the local tensors); the other slots become empty segments, which the GEMV kernels skip.
+        const int li = sm.ssel[tid] - shard_first;
+        const bool mine = li >= 0 && li < shard_count;
+        const size_t ex = mine ? (size_t)li : 0;
+        seg_gu[tid] = SegDesc{gate + ex * eb_g, up + ex * eb_u, mine ? 1u : 0u, (uint32_t)tid};
+        seg_dn[tid] = SegDesc{down + ex * eb_d, nullptr, mine ? 1u : 0u, (uint32_t)tid};
         row_token[tid] = 0;
         pos[tid] = tid;
     }
@@ -580,7 +584,7 @@ static int launch_router_decode_t(dnb_ctx* c, cudaStream_t st, const float* h, c
                       (const uint8_t*)(fold_shared ? L.m[3].dev : nullptr),
                       (const uint8_t*)(fold_shared ? L.m[4].dev : nullptr),
                       (const uint8_t*)(fold_shared ? L.m[5].dev : nullptr), w.seg_gu, w.seg_dn, w.row_token, w.pos,
-                      w.nseg, ticket, (gridDim_ok(M.ne) ? w.xn_perm : nullptr), L.m[0].type));
+                      w.nseg, ticket, (gridDim_ok(M.ne) ? w.xn_perm : nullptr), L.m[0].type, M.shard_first, M.shard_count));
     c->launches++;
     return DNB_OK;
 }

@@ -82,12 +82,18 @@ template <int T, bool FUSED, int LPR, int TT>
 __global__ void __launch_bounds__(kThreads)
 seg_matmul_kernel(const SegDesc* __restrict__ seg, const int32_t* __restrict__ nseg_dev, int nseg_host, int n_in,
                   int n_out, int rb, int tile_rows, const float* __restrict__ x, int ldx,
-                  const int32_t* __restrict__ row_token, float* __restrict__ out, SegDesc single) {
+                  const int32_t* __restrict__ row_token, float* __restrict__ out, SegDesc single, int tok_chunk) {
     const int s = blockIdx.y;
     const int nseg = nseg_dev ? *nseg_dev : nseg_host;
     if (s >= nseg) return;
     const SegDesc sd = seg ? seg[s] : single;
     if (sd.m == 0) return;
+    // blockIdx.z: which tok_chunk tokens of the segment this CTA takes.  A segment with many tokens (the shared
+    // expert of a batch, a hot expert of a chunk) is spread over several CTAs instead of being walked by one;
+    // a token's arithmetic does not depend on the split.
+    const uint32_t t_begin = blockIdx.z * (uint32_t)tok_chunk;
+    if (t_begin >= sd.m) return;
+    const uint32_t t_end = min(sd.m, t_begin + (uint32_t)tok_chunk);
     const int r0 = blockIdx.x * tile_rows;
     const int rows = min(tile_rows, n_out - r0);
     if (rows <= 0) return;
@@ -113,8 +119,8 @@ seg_matmul_kernel(const SegDesc* __restrict__ seg, const int32_t* __restrict__ n
     const int grp = warp * GPW + lane / LPR;    // group index in the CTA
     constexpr int NGRP = (kThreads / 32) * GPW;
 
-    for (uint32_t t0 = 0; t0 < sd.m; t0 += TT) {
-        const int nt = min((uint32_t)TT, sd.m - t0);
+    for (uint32_t t0 = t_begin; t0 < t_end; t0 += TT) {
+        const int nt = min((uint32_t)TT, t_end - t0);
         __syncthreads();  // previous chunk fully consumed (and, first time, nothing)
         for (int tok = 0; tok < nt; ++tok) {
             const uint32_t prow = sd.row0 + t0 + tok;
@@ -193,7 +199,7 @@ seg_matmul_kernel(const SegDesc* __restrict__ seg, const int32_t* __restrict__ n
 
 template <int T, bool FUSED, int LPR, int TT>
 static int launch_cfg(dnb_ctx* c, cudaStream_t st, const SegDesc* seg, const int32_t* nseg_dev, int nseg_max, int n_in,
-                      int n_out, const float* x, int ldx, const int32_t* row_token, float* out, SegDesc single) {
+                      int n_out, const float* x, int ldx, const int32_t* row_token, float* out, SegDesc single, int m_max) {
     const int rb = (int)row_bytes(T, n_in);
     // Aim at ~16 KB of weight bytes per CTA, in whole "group rounds", and keep
     // tile starts 16-byte aligned (tile_rows * rb % 16 == 0) where possible.
@@ -212,7 +218,13 @@ static int launch_cfg(dnb_ctx* c, cudaStream_t st, const SegDesc* seg, const int
         return DNB_DECLINED;
     }
     DNB_CUDA(grant_smem(grant, c->device, kern, smem));
-    dim3 grid((n_out + tile_rows - 1) / tile_rows, nseg_max);
+    // Tokens of a segment per CTA.  Chunks of many tokens (a hot expert of a prefill chunk would otherwise be walked
+    // by one CTA per row tile) are spread over up to eight CTAs; decode batches are not split: measured at 32 tokens,
+    // the empty CTAs of the extra grid dimension cost more (21.2 ms per 48-layer step) than the split saves (18.6 ms).
+    int tok_chunk = m_max > 0 ? m_max : 1;
+    if (m_max >= 64) tok_chunk = ((m_max + 7) / 8 + TT - 1) / TT * TT;
+    const int gz = m_max > tok_chunk ? (m_max + tok_chunk - 1) / tok_chunk : 1;
+    dim3 grid((n_out + tile_rows - 1) / tile_rows, nseg_max, gz);
     const bool sh = (st == c->side);
     const char* pname = FUSED ? (TT == 1 ? (sh ? "seg_gate_up_m1_shared" : "seg_gate_up_m1")
                                          : (sh ? "seg_gate_up_m4_shared" : "seg_gate_up_m4"))
@@ -220,7 +232,7 @@ static int launch_cfg(dnb_ctx* c, cudaStream_t st, const SegDesc* seg, const int
                                          : (sh ? "seg_matmul_m4_shared" : "seg_matmul_m4"));
     ProfScope prof_(c, st, pname);
     kern<<<grid, kThreads, smem, st>>>(seg, nseg_dev, nseg_max, n_in, n_out, rb, tile_rows, x, ldx, row_token, out,
-                                        single);
+                                        single, tok_chunk);
     c->launches++;
     DNB_CUDA(cudaGetLastError());
     return DNB_OK;
@@ -233,11 +245,11 @@ static int launch_t(dnb_ctx* c, cudaStream_t st, const SegDesc* seg, const int32
     const int nunits = n_in / 32;
     const bool wide = nunits >= 32;
     if (m_max <= 1) {
-        return wide ? launch_cfg<T, FUSED, 32, 1>(c, st, seg, nseg_dev, nseg_max, n_in, n_out, x, ldx, row_token, out, single)
-                    : launch_cfg<T, FUSED, 16, 1>(c, st, seg, nseg_dev, nseg_max, n_in, n_out, x, ldx, row_token, out, single);
+        return wide ? launch_cfg<T, FUSED, 32, 1>(c, st, seg, nseg_dev, nseg_max, n_in, n_out, x, ldx, row_token, out, single, m_max)
+                    : launch_cfg<T, FUSED, 16, 1>(c, st, seg, nseg_dev, nseg_max, n_in, n_out, x, ldx, row_token, out, single, m_max);
     }
-    return wide ? launch_cfg<T, FUSED, 32, 4>(c, st, seg, nseg_dev, nseg_max, n_in, n_out, x, ldx, row_token, out, single)
-                : launch_cfg<T, FUSED, 16, 4>(c, st, seg, nseg_dev, nseg_max, n_in, n_out, x, ldx, row_token, out, single);
+    return wide ? launch_cfg<T, FUSED, 32, 4>(c, st, seg, nseg_dev, nseg_max, n_in, n_out, x, ldx, row_token, out, single, m_max)
+                : launch_cfg<T, FUSED, 16, 4>(c, st, seg, nseg_dev, nseg_max, n_in, n_out, x, ldx, row_token, out, single, m_max);
 }
 
 int launch_seg_matmul(dnb_ctx* c, cudaStream_t st, int type, bool fused, const SegDesc* seg, const int32_t* nseg_dev,

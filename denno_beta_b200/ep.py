@@ -179,6 +179,12 @@ class PeerMemoryExpertParallel:
 
         check(self.ctx.lib.dnb_ep_block_dev(self.ctx.h, layer, C.c_void_p(h_dev), nt, C.c_void_p(out_dev)))
 
+    def stack_dev(self, h_dev, nt):
+        """All layers in place with identity mixers: h <- h + block_l(h) for this rank's nt tokens."""
+        from ._lib import check
+
+        check(self.ctx.lib.dnb_ep_stack_dev(self.ctx.h, C.c_void_p(h_dev), nt))
+
 
 class PeerMemoryDecode:
     """One rank of an expert-parallel DECODE group (dnb_epd_* entry points): the residual stream is

@@ -298,6 +298,9 @@ int dnb_moe_combine_dev(dnb_ctx* ctx, int layer, const float* h_slots_dev, const
 int dnb_ep_init(dnb_ctx* ctx, int rank, int world, int max_tokens, void* handle_out);
 int dnb_ep_connect(dnb_ctx* ctx, const void* handles);
 int dnb_ep_block_dev(dnb_ctx* ctx, int layer, const float* h_dev, int nt, float* out_dev);
+/* All configured layers with identity mixers, in place: h <- h + block_l(h) for this rank's nt tokens
+ * (the expert-parallel form of dnb_moe_stack_dev). */
+int dnb_ep_stack_dev(dnb_ctx* ctx, float* h_dev, int nt);
 /* Teardown rule of the peer-memory path: a rank's arena is memory its peers store into from
  * their kernels.  A rank must not call dnb_shutdown (or exit) before a host-side barrier
  * has shown that no peer still has a dnb_ep_block_dev in flight -- synchronise the own
