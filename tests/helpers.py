@@ -64,3 +64,83 @@ def check_block(orc, L, h, out, sels, wts, tol=1e-3):
         want[diff] = orc.moe_experts_given(L, x[diff], sels[diff], wts[diff])
     assert np.max(np.abs(wts - owts)[np.all(osels == sels, axis=1)], initial=0.0) < 2e-6
     return rel_err(out, want), int(diff.size)
+
+
+# ---- a minimal GGUF v3 writer (the tests write their own synthetic model files, as the reference's
+# tests/moe_gguf.rs does) -------------------------------------------------------------------------------
+import struct
+
+_GT = {"u8": 0, "i8": 1, "u16": 2, "i16": 3, "u32": 4, "i32": 5, "f32": 6, "bool": 7, "str": 8, "arr": 9, "u64": 10, "i64": 11, "f64": 12}
+_FMT = {"u8": "<B", "i8": "<b", "u16": "<H", "i16": "<h", "u32": "<I", "i32": "<i", "f32": "<f", "bool": "<B", "u64": "<Q", "i64": "<q", "f64": "<d"}
+
+
+def _gstr(s):
+    b = s.encode()
+    return struct.pack("<Q", len(b)) + b
+
+
+def write_gguf(path, kvs, tensors, alignment=32, version=3):
+    """kvs: [(key, kind, value)] with kind in _GT (arrays: value = (element kind, [values]));
+    tensors: [(name, ggml_type, dims (ne0 first), bytes)].  Returns {name: absolute file offset}."""
+    head = struct.pack("<IIQQ", 0x46554747, version, len(tensors), len(kvs))
+    for key, kind, val in kvs:
+        head += _gstr(key) + struct.pack("<I", _GT[kind])
+        if kind == "str":
+            head += _gstr(val)
+        elif kind == "arr":
+            ek, vals = val
+            head += struct.pack("<IQ", _GT[ek], len(vals))
+            for v in vals:
+                head += _gstr(v) if ek == "str" else struct.pack(_FMT[ek], v)
+        else:
+            head += struct.pack(_FMT[kind], val)
+    rel, infos, off = {}, b"", 0
+    for name, ty, dims, data in tensors:
+        off = (off + alignment - 1) // alignment * alignment
+        rel[name] = off
+        infos += _gstr(name) + struct.pack("<I", len(dims)) + b"".join(struct.pack("<Q", d) for d in dims) + struct.pack("<IQ", ty, off)
+        off += len(data)
+    start = (len(head) + len(infos) + alignment - 1) // alignment * alignment
+    with open(path, "wb") as f:
+        f.write(head + infos)
+        f.write(b"\0" * (start - len(head) - len(infos)))
+        pos = 0
+        for name, ty, dims, data in tensors:
+            f.write(b"\0" * (rel[name] - pos))
+            f.write(bytes(data))
+            pos = rel[name] + len(data)
+    return {n: start + o for n, o in rel.items()}
+
+
+def gguf_moe_layer_tensors(orc, blk, ty, e, ff, ne, seed, ty_down=None, shared=True, gate_row=True, bias=False):
+    """The tensors of one MoE layer under the reference's names (qwen4exp.rs:1018-1025), as (name, type, dims, bytes)
+    plus the oracle's Layer of the same bytes."""
+    ty_down = ty if ty_down is None else ty_down
+    tid = blk * 16
+    nb = lambda t, rows, cols: rows * cols // orc.blck_size(t)
+    gate = orc.synth_blocks(ty, seed, tid + 0, ne * nb(ty, ff, e))
+    up = orc.synth_blocks(ty, seed, tid + 1, ne * nb(ty, ff, e))
+    down = orc.synth_blocks(ty_down, seed, tid + 2, ne * nb(ty_down, e, ff))
+    rw = orc.synth_normal(seed, tid + 6, 0.02, ne * e)
+    p = "blk.%d." % blk
+    ts = [(p + "ffn_gate_inp.weight", 0, [e, ne], rw.tobytes()),
+          (p + "ffn_gate_exps.weight", ty, [e, ff, ne], gate.tobytes()),
+          (p + "ffn_up_exps.weight", ty, [e, ff, ne], up.tobytes()),
+          (p + "ffn_down_exps.weight", ty_down, [ff, e, ne], down.tobytes())]
+    sh = sgr = rb = None
+    if shared:
+        sh = (orc.synth_blocks(ty, seed, tid + 3, nb(ty, ff, e)), orc.synth_blocks(ty, seed, tid + 4, nb(ty, ff, e)),
+              orc.synth_blocks(ty_down, seed, tid + 5, nb(ty_down, e, ff)))
+        ts += [(p + "ffn_gate_shexp.weight", ty, [e, ff], sh[0].tobytes()), (p + "ffn_up_shexp.weight", ty, [e, ff], sh[1].tobytes()),
+               (p + "ffn_down_shexp.weight", ty_down, [ff, e], sh[2].tobytes())]
+        if gate_row:
+            sgr = orc.synth_normal(seed, tid + 8, 0.02, e)
+            ts.append((p + "ffn_gate_inp_shexp.weight", 0, [e], sgr.tobytes()))
+    if bias:
+        rb = orc.synth_zipf_bias(seed, tid + 7, 1.1, ne)
+        ts.append((p + "exp_probs_b.bias", 0, [ne], rb.tobytes()))
+    nw = (1.0 + 0.1 * orc.synth_normal(seed, tid + 9, 1.0, e)).astype(np.float32)
+    ts.append((p + "ffn_norm.weight", 0, [e], nw.tobytes()))
+    L = orc.Layer(e, ff, ne, 0, ty, ty, ty_down, gate, up, down, rw.reshape(ne, e), router_bias=rb, norm_w=nw, shared=sh,
+                  shared_types=(ty, ty, ty_down), shared_gate_row=sgr)
+    return ts, L
