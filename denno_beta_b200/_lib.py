@@ -43,6 +43,17 @@ SIGNATURES = {
     "dnb_register_router": (_i, [_vp, _i, _vp, _vp, _vp, _vp]),
     "dnb_synth_experts": (_i, [_vp, _i, _i, _i, _i, _i, _i, _u64]),
     "dnb_download_expert": (_i, [_vp, _i, _i, _i, _vp, _sz]),
+    "dnb_gguf_open": (_i, [C.POINTER(C.c_char_p), _i, C.POINTER(_vp)]),
+    "dnb_gguf_close": (None, [_vp]),
+    "dnb_gguf_n_tensors": (_i, [_vp]),
+    "dnb_gguf_tensor_name": (C.c_char_p, [_vp, _i]),
+    "dnb_gguf_tensor_info": (_i, [_vp, C.c_char_p, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_uint64), C.POINTER(C.c_int),
+                                  C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
+    "dnb_gguf_tensor_data": (_vp, [_vp, C.c_char_p, C.POINTER(C.c_uint64)]),
+    "dnb_gguf_meta_u64": (_i, [_vp, C.c_char_p, C.POINTER(C.c_uint64)]),
+    "dnb_gguf_meta_f64": (_i, [_vp, C.c_char_p, C.POINTER(C.c_double)]),
+    "dnb_gguf_meta_str": (_i, [_vp, C.c_char_p, C.c_char_p, _sz]),
+    "dnb_load_gguf_layer": (_i, [_vp, _vp, _i, _i, C.c_char_p]),
     "dnb_moe_block": (_i, [_vp, _i, _vp, _i, _vp, _vp, _vp]),
     "dnb_moe_block_dev": (_i, [_vp, _i, _vp, _i, _vp]),
     "dnb_moe_experts": (_i, [_vp, _i, _vp, _i, _vp, _vp, _vp]),
@@ -62,6 +73,9 @@ SIGNATURES = {
     "dnb_ep_block_dev": (_i, [_vp, _i, _vp, _i, _vp]),
     "dnb_ep_connect_loopback": (_i, [_vp]),
     "dnb_ep_stack_dev": (_i, [_vp, _vp, _i]),
+    "dnb_register_hc": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp]),
+    "dnb_hc_moe_block": (_i, [_vp, _i, _vp, _i, _vp]),
+    "dnb_hc_moe_block_dev": (_i, [_vp, _i, _vp, _i, _vp]),
     "dnb_epd_init": (_i, [_vp, _i, _i, _i, _vp]),
     "dnb_epd_connect": (_i, [_vp, _vp]),
     "dnb_epd_block_dev": (_i, [_vp, _i, _vp, _i, _vp]),

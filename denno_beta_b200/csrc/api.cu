@@ -487,6 +487,7 @@ void dnb_shutdown(dnb_ctx* c) {
     drop_graphs(c);
     ep_release(c);
     epd_release(c);
+    hc_release(c);
     for (auto& kv : c->matrices) cudaFree(kv.second.dev);
     for (auto& L : c->model.layers) free_layer(L);
     free_ws(c->ws);
@@ -781,6 +782,7 @@ int dnb_moe_config(dnb_ctx* c, int n_layer, int e, int ff, int sff, int ne, int 
     drop_graphs(c);
     for (auto& L : c->model.layers) free_layer(L);
     free_ws(c->ws);
+    hc_release(c);
     Model& M = c->model;
     M.n_layer = n_layer; M.e = e; M.ff = ff; M.sff = sff; M.ne = ne; M.k = k; M.eps = eps; M.norm_topk = norm_topk;
     M.shard_first = 0; M.shard_count = ne;

@@ -164,6 +164,7 @@ struct dnb_ctx {
     bool decode_routed = true;          // ... with the router folded into the same kernel (one launch per block)
     bool use_umma = true;               // prefill chunks of Q4_K layers take the tcgen05 grouped GEMM
     void* ep = nullptr;                 // dnb::EpState of the peer-memory expert-parallel path (ep_p2p.cu)
+    void* hc = nullptr;                 // dnb::HcState: hyper-connection mix weights and scratch (hc_mix.cu)
     void* epd = nullptr;                // dnb::EpdState of the expert-parallel decode path (ep_decode.cu)
 };
 
@@ -172,6 +173,7 @@ namespace dnb {
 void set_error(const char* fmt, ...);
 void ep_release(dnb_ctx* c);  // frees the peer-memory expert-parallel state, if any (ep_p2p.cu)
 void epd_release(dnb_ctx* c); // the same for the decode exchange (ep_decode.cu)
+void hc_release(dnb_ctx* c);  // hyper-connection weights and scratch (hc_mix.cu)
 int ensure_workspace(dnb_ctx* c, int nt);  // device buffers of the MoE pipeline for nt tokens (api.cu)
 // Run a launch sequence directly the first time `key` is seen, capture it into a CUDA graph the second time,
 // replay it afterwards (api.cu).

@@ -299,6 +299,23 @@ class CudaCtx:
             return None
         return out
 
+    def register_hc(self, layer, hc, low_rank, w_norm, w_down_inject, w_up):
+        """Hyper-connection weights of a layer (model/hyper.rs): fp32, shapes [hc, e], [low_rank + hc, hc * e], [hc * e, low_rank]."""
+        e = self.model["e"]
+        w_norm, w_down_inject, w_up = _f32(w_norm), _f32(w_down_inject), _f32(w_up)
+        assert w_norm.size == hc * e and w_down_inject.size == (low_rank + hc) * hc * e and w_up.size == hc * e * low_rank
+        check(self.lib.dnb_register_hc(self.h, layer, hc, low_rank, _p(w_norm), _p(w_down_inject), _p(w_up)))
+        self.model.setdefault("hc", {})[layer] = hc
+
+    def hc_moe_block(self, layer, res):
+        """res [nt, hc, e] -> out [nt, hc, e] = hc_combine(res, moe_block(hc_mix(res)), inject); None when declined."""
+        e, hc = self.model["e"], self.model["hc"][layer]
+        res = _f32(res, (-1, hc, e))
+        out = np.empty_like(res)
+        if not check(self.lib.dnb_hc_moe_block(self.h, layer, _p(res), res.shape[0], _p(out)), True):
+            return None
+        return out
+
     def moe_stack(self, h):
         e = self.model["e"]
         h = _f32(h, (-1, e))

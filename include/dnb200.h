@@ -178,6 +178,35 @@ int dnb_synth_experts(dnb_ctx* ctx, int layer, int matrix, int ggml_type, int n_
 /* Copy expert `expert` of a registered tensor back to the host (parity checks). */
 int dnb_download_expert(dnb_ctx* ctx, int layer, int matrix, int expert, void* dst, size_t bytes);
 
+/* ---- GGUF files -> the resident expert table ----------------------------------------
+ * crates/denno-engine/src/gguf.rs:163-330 (GgufFile::open / open_split: v2/v3 containers, split
+ * models as parts with split.no / split.count / split.tensors.count) and model/qwen4exp.rs:1915-1963
+ * (ExpertW::load).  The reference keeps expert tensors in the file mapping and moves experts between
+ * SSD, RAM and VRAM on demand (expert_vram.rs); here a layer is read from the mapping once and stays
+ * in HBM.  dnb_gguf_open takes the path of one file or of all parts of a split model (any order) and
+ * needs no GPU; the handle's tensor table, metadata and data pointers (into the read-only mapping,
+ * valid until dnb_gguf_close) can be inspected with the getters.  DNB_DECLINED from a getter = no
+ * such tensor / key.
+ *   dnb_load_gguf_layer: registers blk.<gguf_layer>.{ffn_gate_exps, ffn_up_exps, ffn_down_exps}.weight
+ *       (3-d, ne = [n_in, n_out, n_expert], expert-major as moe_expert.rs:49-82; with an expert shard
+ *       set only this rank's contiguous byte range is copied), the shared expert ffn_{gate,up,down}
+ *       _shexp.weight when present, the router ffn_gate_inp.weight (f32 [n_embd, n_expert]), and, when
+ *       present, exp_probs_b.bias and ffn_gate_inp_shexp.weight (qwen4exp.rs:1018-1025) as layer
+ *       `layer` of the configured model.  norm_name (may be NULL) names an f32 [n_embd] tensor of the
+ *       block to use as the RMSNorm weight in front of the router. */
+typedef struct dnb_gguf dnb_gguf;
+int dnb_gguf_open(const char* const* paths, int n_paths, dnb_gguf** out);
+void dnb_gguf_close(dnb_gguf* g);
+int dnb_gguf_n_tensors(const dnb_gguf* g);
+const char* dnb_gguf_tensor_name(const dnb_gguf* g, int index);
+int dnb_gguf_tensor_info(const dnb_gguf* g, const char* name, int* ggml_type, int* n_dims, uint64_t dims[4], int* part,
+                         uint64_t* file_offset, uint64_t* nbytes);
+const void* dnb_gguf_tensor_data(const dnb_gguf* g, const char* name, uint64_t* nbytes);
+int dnb_gguf_meta_u64(const dnb_gguf* g, const char* key, uint64_t* v);
+int dnb_gguf_meta_f64(const dnb_gguf* g, const char* key, double* v);
+int dnb_gguf_meta_str(const dnb_gguf* g, const char* key, char* buf, size_t cap);
+int dnb_load_gguf_layer(dnb_ctx* ctx, const dnb_gguf* g, int layer, int gguf_layer, const char* norm_name);
+
 /* ---- MoE block -----------------------------------------------------------------
  * One sparse-MoE block for nt tokens: (RMSNorm) -> router -> softmax -> top-k ->
  * renorm -> routed experts (gate/up GEMV, SwiGLU, down GEMV) -> weighted sum in
@@ -251,6 +280,21 @@ int dnb_seg_gemv_pair(dnb_ctx* ctx, int layer, const uint32_t* seg, int nseg, co
  * a fixed tree: deterministic, not the bits of the sequential CPU loop (the reference's
  * default dno_matvec_f32_r has the same contract). */
 int dnb_router_gemv(dnb_ctx* ctx, int layer, const float* x, int nt, float* logits);
+/* ---- hyper-connection mix around the block ------------------------------------------------
+ * model/hyper.rs (hc_mix :369, hc_combine :384; the order of operations :13-36 is its numeric contract);
+ * call sites model/qwen4exp.rs:3722-3765 (hc_mix_quant -> moe_ffn_quant -> hc_combine_inplace).  A layer
+ * carries hc parallel residual streams per token; the mix turns them into the block's input (per-stream
+ * RMSNorm, a low-rank gate: w_down_inject [low_rank + hc][hc*n_embd], w_up [hc*n_embd][low_rank]) and the
+ * combine writes the block's output back into every stream scaled by 2*sigmoid(inject[s]).
+ *   dnb_register_hc   : fp32 host tensors of layer `layer`: w_norm [hc][n_embd] (the gamma the converter
+ *       folded to 1 + w), w_down_inject, w_up.  (Checkpoints store them as BF16; widen first, which is exact.)
+ *   dnb_hc_moe_block  : res, out host [nt][hc][n_embd]: out = combine(res, block(mix(res)), inject).  The
+ *       layer's MoE block must be registered without an RMSNorm weight of its own (the mix normalises).
+ *   dnb_hc_moe_block_dev: the same on device pointers, asynchronous. */
+int dnb_register_hc(dnb_ctx* ctx, int layer, int hc, int low_rank, const float* w_norm, const float* w_down_inject,
+                    const float* w_up);
+int dnb_hc_moe_block(dnb_ctx* ctx, int layer, const float* res, int nt, float* out);
+int dnb_hc_moe_block_dev(dnb_ctx* ctx, int layer, const float* res_dev, int nt, float* out_dev);
 /* ---- expert-parallel building blocks ---------------------------------------------
  * The reference runs on one GPU.  On a multi-GPU box the experts shard naturally:
  * GPU g keeps experts [g*ne/G, (g+1)*ne/G) of every layer (router, norm and shared

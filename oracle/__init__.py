@@ -133,6 +133,34 @@ def softmax(x):
     return x
 
 
+def hc_mix(x, w_norm, w_down_inject, w_up, low_rank, eps=1e-6):
+    """model/hyper.rs:160-222 for one token: x [hc, e] -> (mixed [e], inject [hc], xn [hc, e])."""
+    x = _f32(x)
+    hc, e = x.shape
+    w_norm, w_down_inject, w_up = _f32(w_norm), _f32(w_down_inject), _f32(w_up)
+    assert w_norm.size == hc * e and w_down_inject.size == (low_rank + hc) * hc * e and w_up.size == hc * e * low_rank
+    mixed = np.empty(e, np.float32)
+    inject = np.empty(hc, np.float32)
+    xn = np.empty((hc, e), np.float32)
+    L = lib()
+    L.orc_hc_mix.restype = None
+    L.orc_hc_mix.argtypes = [C.c_void_p] * 4 + [C.c_long] * 3 + [C.c_float] + [C.c_void_p] * 3
+    L.orc_hc_mix(_p(x), _p(w_norm), _p(w_down_inject), _p(w_up), hc, e, low_rank, eps, _p(mixed), _p(inject), _p(xn))
+    return mixed, inject, xn
+
+
+def hc_combine(residual, block, inject):
+    """model/hyper.rs:384-416: residual [hc, e], block [e], inject [hc] -> [hc, e]."""
+    residual, block, inject = _f32(residual), _f32(block), _f32(inject)
+    hc, e = residual.shape
+    out = np.empty((hc, e), np.float32)
+    L = lib()
+    L.orc_hc_combine.restype = None
+    L.orc_hc_combine.argtypes = [C.c_void_p] * 3 + [C.c_long] * 2 + [C.c_void_p]
+    L.orc_hc_combine(_p(residual), _p(block), _p(inject), hc, e, _p(out))
+    return out
+
+
 def select_topk(probs, k):
     probs = _f32(probs)
     out = np.empty(k, np.int32)

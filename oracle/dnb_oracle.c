@@ -372,6 +372,60 @@ void orc_softmax(float* x, long n) {
 float orc_silu(float v) { return v / (1.0f + expf(-v)); }
 float orc_sigmoid(float v) { return 1.0f / (1.0f + expf(-v)); }
 
+/* ---- hyper-connection mix / combine: model/hyper.rs ---------------------------------------------------------------
+ * The file states its order of operations as the numeric contract (hyper.rs:13-36); every product and sum below is
+ * a separate f32 operation in that order (this file is compiled with contraction off).
+ * Pinned by the reference's hard-coded anchor (tests/hyper.rs:321-365: mixed, inject and combine to the bit). */
+
+/* hyper.rs:131-138 (dot_row): sequential f32, multiply then add. */
+static float hc_dot_row(const float* w, const float* x, long n) {
+    float acc = 0.0f;
+    for (long i = 0; i < n; ++i) acc += w[i] * x[i];
+    return acc;
+}
+
+/* hyper.rs:160-222 (mix_internal with w_down_inject) for one token.
+ *   x [hc][e], w_norm [hc][e], w_down_inject [low_rank + hc][hc*e], w_up [hc*e][low_rank]
+ *   -> mixed [e], inject [hc]; xn_out (optional) [hc][e]. */
+void orc_hc_mix(const float* x, const float* w_norm, const float* w_down_inject, const float* w_up, long hc, long e,
+                long low_rank, float eps, float* mixed, float* inject, float* xn_out) {
+    const long hc_dim = hc * e;
+    float* xn = (float*)malloc(sizeof(float) * (size_t)hc_dim);
+    float* lo = (float*)malloc(sizeof(float) * (size_t)low_rank);
+    const float inv_hc = 1.0f / (float)hc;
+    /* steps 1-3: per-stream rmsnorm, gamma folded into the same x*inv*w product (hyper.rs:144-157) */
+    for (long s = 0; s < hc; ++s) orc_rmsnorm(x + s * e, w_norm + s * e, 1, e, eps, xn + s * e);
+    /* steps 4-5 (hc_lo_apply, hyper.rs:255-262): 1/hc after the matmul, then silu(v) = v * sigmoid(v) */
+    for (long r = 0; r < low_rank; ++r) {
+        float v = hc_dot_row(w_down_inject + r * hc_dim, xn, hc_dim);
+        v = v * inv_hc;
+        lo[r] = v * orc_sigmoid(v);
+    }
+    /* inject rows: scaled, no silu (hc_inject_apply, hyper.rs:354-359) */
+    for (long r = 0; r < hc; ++r) inject[r] = hc_dot_row(w_down_inject + (low_rank + r) * hc_dim, xn, hc_dim) * inv_hc;
+    /* steps 6-8 (mixed_range, hyper.rs:279-304): the first stream's term starts the sum, 1/hc last */
+    for (long d = 0; d < e; ++d) {
+        float acc = 0.0f;
+        for (long s = 0; s < hc; ++s) {
+            const float g = hc_dot_row(w_up + (s * e + d) * low_rank, lo, low_rank);
+            const float term = xn[s * e + d] * orc_sigmoid(g);
+            acc = (s == 0) ? term : acc + term;
+        }
+        mixed[d] = acc * inv_hc;
+    }
+    if (xn_out) memcpy(xn_out, xn, sizeof(float) * (size_t)hc_dim);
+    free(lo);
+    free(xn);
+}
+
+/* hyper.rs:384-416 (hc_combine): out[s][d] = residual[s][d] + block[d] * (2 * sigmoid(inject[s])). */
+void orc_hc_combine(const float* residual, const float* block, const float* inject, long hc, long e, float* out) {
+    for (long s = 0; s < hc; ++s) {
+        const float w = 2.0f * orc_sigmoid(inject[s]);
+        for (long d = 0; d < e; ++d) out[s * e + d] = residual[s * e + d] + block[d] * w;
+    }
+}
+
 /* moe.rs:256-279 (select_topk_scan): k passes, strict '>' so ties keep the lower
  * index, NaN only chosen when nothing else is left; output ascending.  The
  * faster forms in moe.rs:188-250 are specified to return the same set. */

@@ -33,6 +33,9 @@ void orc_rmsnorm(const float* x, const float* w, long rows, long cols, float eps
 void orc_softmax(float* x, long n);
 float orc_silu(float v);
 float orc_sigmoid(float v);
+void orc_hc_mix(const float* x, const float* w_norm, const float* w_down_inject, const float* w_up, long hc, long e,
+                long low_rank, float eps, float* mixed, float* inject, float* xn_out);
+void orc_hc_combine(const float* residual, const float* block, const float* inject, long hc, long e, float* out);
 void orc_select_topk(const float* probs, long n, long k, int32_t* out);
 void orc_router_renorm(const float* probs, const int32_t* sel, long k, float* w);
 long orc_build_segments(const int32_t* sels, long nt, long k, long ne, orc_segment* segs, int32_t* row_token,
