@@ -309,8 +309,10 @@ class CudaCtx:
 
     def hc_moe_block(self, layer, res):
         """res [nt, hc, e] -> out [nt, hc, e] = hc_combine(res, moe_block(hc_mix(res)), inject); None when declined."""
-        e, hc = self.model["e"], self.model["hc"][layer]
-        res = _f32(res, (-1, hc, e))
+        e = self.model["e"]
+        res = _f32(res)
+        hc = self.model.get("hc", {}).get(layer, res.shape[-2] if res.ndim >= 2 else 1)
+        res = res.reshape(-1, hc, e)
         out = np.empty_like(res)
         if not check(self.lib.dnb_hc_moe_block(self.h, layer, _p(res), res.shape[0], _p(out)), True):
             return None
