@@ -1018,6 +1018,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-extras", action="store_true", help="skip the config-0/2/3/4 lines")
     ap.add_argument("--no-stack", action="store_true", help="skip the 48-layer stack lines (configs 3 and 4)")
+    ap.add_argument("--gemv-only", action="store_true",
+                    help="only the config-0 single-matrix GEMV lines (small enough for a profiler capture)")
     args = ap.parse_args()
     if args.layers > 0:
         LAYERS = args.layers
@@ -1029,6 +1031,13 @@ def main():
         from denno_beta_b200 import cuda as cu
 
         res = {"config2_q4k_prefill_512": prefill_extras(cu, oracle, local_rank, layers=max(args.layers, 1))}
+    elif args.gemv_only:
+        import oracle
+        from denno_beta_b200 import cuda as cu
+
+        ctx = cu.CudaCtx(local_rank)
+        res = extras(ctx, cu, oracle)
+        ctx.close()
     elif args.impl == "reference":
         res = run_reference(args, rank)
     else:

@@ -353,16 +353,26 @@ static int block_dev_decode_batch(dnb_ctx* c, int layer, const float* h, int nt,
 
 // Prefill chunks of all-Q4_K layers: expert-major packed rows as bf16 hi/lo, grouped
 // GEMMs on tcgen05 (gate/up with the SwiGLU epilogue, then down), weighted combine.
+// The common block format of matrices [first, last) when a tensor-core grouped GEMM takes it
+// (Q4_K: three-product kernel of grouped_umma.cu; IQ3_XXS: exact-weight kernel of grouped_exact.cu), else -1.
+static int tc_type(const Layer& L, int first, int last) {
+    const int ty = L.m[first].type;
+    if (ty != T_Q4_K && ty != T_IQ3_XXS) return -1;
+    for (int i = first; i < last; ++i)
+        if (!L.m[i].dev || L.m[i].type != ty) return -1;
+    return ty;
+}
+// Tokens from which a chunk or decode batch leaves the one-token kernels for the tensor-core grouped GEMM.
+static int tc_min_tokens(const dnb_ctx* c, int ty) { return ty == T_Q4_K ? 16 : c->exact_min_nt; }
+
 static bool umma_eligible(const dnb_ctx* c, const Layer& L, int nt) {
     const Model& M = c->model;
-    if (!c->use_umma || !c->ws.maps_ok || nt < 16) return false;
+    if (!c->use_umma || !c->ws.maps_ok) return false;
     if (M.e % 256 || M.ff % 256 || M.e % 128 || M.ff % 128) return false;
-    for (int i = 0; i < 3; ++i)
-        if (L.m[i].type != T_Q4_K) return false;
-    if (L.has_shared()) {
-        for (int i = 3; i < 6; ++i)
-            if (L.m[i].type != T_Q4_K) return false;
-        if (L.m[3].n_out != M.ff) return false;
+    const int ty = tc_type(L, 0, 3);
+    if (ty < 0 || nt < tc_min_tokens(c, ty)) return false;
+    if (L.has_shared()) {  // the shared expert rides in the same launches as one more segment
+        if (tc_type(L, 3, 6) != ty || L.m[3].n_out != M.ff) return false;
     }
     return true;
 }
@@ -381,11 +391,12 @@ static int experts_dev_umma(dnb_ctx* c, int layer, const float* x, int nt, const
     const int rows = nt * k + (shared ? nt : 0);
     if ((rc = launch_gather_split(c, st, x, M.e, w.row_token, rows, M.e, w.xg_hi, w.xg_lo))) return rc;
     const int nseg_max = (nt * k < ne ? nt * k : ne) + (shared ? 1 : 0);
-    if ((rc = launch_grouped_umma(c, st, true, w.seg_gu, w.nseg, nseg_max, M.e, M.ff, &w.maps_x, nt, w.act_hi, w.act_lo,
-                                  nullptr)))
+    const int ty = L.m[0].type;
+    if ((rc = launch_grouped_tc(c, st, ty, true, w.seg_gu, w.nseg, nseg_max, M.e, M.ff, &w.maps_x, nt, w.act_hi, w.act_lo,
+                                nullptr)))
         return rc;
-    if ((rc = launch_grouped_umma(c, st, false, w.seg_dn, w.nseg, nseg_max, M.ff, M.e, &w.maps_act, nt, nullptr, nullptr,
-                                  w.hrow)))
+    if ((rc = launch_grouped_tc(c, st, ty, false, w.seg_dn, w.nseg, nseg_max, M.ff, M.e, &w.maps_act, nt, nullptr, nullptr,
+                                w.hrow)))
         return rc;
     if (shared && L.shared_gate_row)
         if ((rc = launch_shared_coef(c, st, x, L.shared_gate_row, nt, M.e, w.shcoef))) return rc;
@@ -403,7 +414,7 @@ static int block_dev(dnb_ctx* c, int layer, const float* h, int nt, float* out) 
         rc = block_dev_decode(c, layer, h, out, nullptr);
         if (rc != DNB_DECLINED) return rc;
     }
-    if (nt > 1 && nt <= kDecodeBatchMax && c->decode_fast) {
+    if (nt > 1 && nt <= kDecodeBatchMax && c->decode_fast && !umma_eligible(c, L, nt)) {
         rc = block_dev_decode_batch(c, layer, h, nt, out, nullptr);
         if (rc != DNB_DECLINED) return rc;
     }
@@ -702,6 +713,14 @@ int dnb_register_matrix(dnb_ctx* c, uint64_t uid, int type, const void* blocks, 
     return DNB_OK;
 }
 
+int dnb_set_tc_min_tokens(dnb_ctx* c, int iq3_xxs_min_tokens) {
+    if (!c || iq3_xxs_min_tokens < 1) return DNB_ERR_ARG;
+    DNB_CUDA(cudaDeviceSynchronize());
+    drop_graphs(c);
+    c->exact_min_nt = iq3_xxs_min_tokens;
+    return DNB_OK;
+}
+
 int dnb_set_gemv_impl(dnb_ctx* c, int impl) {
     if (!c || impl < 0 || impl > 5) return DNB_ERR_ARG;
     DNB_CUDA(cudaDeviceSynchronize());
@@ -824,7 +843,8 @@ static int install_tensor(dnb_ctx* c, int layer, int matrix, int type, int n_in,
     t = ExpertTensor();
     t.type = type; t.n_in = n_in; t.n_out = n_out; t.n_expert = n_expert;
     t.row_bytes = rb; t.expert_bytes = rb * (size_t)n_out;
-    DNB_CUDA(cudaMalloc((void**)&t.dev, t.expert_bytes * (size_t)n_expert));
+    // 256 spare bytes: the tensor-core producers fetch whole 16-byte lines around blocks that are not 16-byte sized
+    DNB_CUDA(cudaMalloc((void**)&t.dev, t.expert_bytes * (size_t)n_expert + 256));
     t.owned = true;
     return DNB_OK;
 }
@@ -1059,7 +1079,8 @@ int dnb_grouped_gemm(dnb_ctx* c, int layer, int matrix, const uint32_t* segs, in
     // Q4_K matrices of the model's own shapes with enough rows go to the tcgen05 grouped GEMM
     // (the packed rows are split to bf16 hi/lo in the workspace's operand buffers first).
     const bool in_e = t.n_in == M.e, in_ff = t.n_in == M.ff;
-    bool umma = c->use_umma && t.type == T_Q4_K && row >= 64 && (in_e || in_ff) && t.n_in % 256 == 0 && t.n_out % 128 == 0;
+    bool umma = c->use_umma && ((t.type == T_Q4_K && row >= 64) || (t.type == T_IQ3_XXS && row >= 16)) && (in_e || in_ff) &&
+                t.n_in % 256 == 0 && t.n_out % 128 == 0;
     if (umma) {
         if ((rc = ensure_ws(c, (int)((row + M.k) / (M.k + 1))))) return rc;
         umma = c->ws.maps_ok;
@@ -1072,8 +1093,8 @@ int dnb_grouped_gemm(dnb_ctx* c, int layer, int matrix, const uint32_t* segs, in
         uint16_t* hi = in_e ? w.xg_hi : w.act_hi;
         uint16_t* lo = in_e ? w.xg_lo : w.act_lo;
         if ((rc = launch_gather_split(c, c->stream, dx, t.n_in, nullptr, (int)row, t.n_in, hi, lo)) == DNB_OK)
-            rc = launch_grouped_umma(c, c->stream, false, dsd, dnseg, nseg, t.n_in, t.n_out, in_e ? &w.maps_x : &w.maps_act,
-                                     (int)row, nullptr, nullptr, dout);
+            rc = launch_grouped_tc(c, c->stream, t.type, false, dsd, dnseg, nseg, t.n_in, t.n_out, in_e ? &w.maps_x : &w.maps_act,
+                                   (int)row, nullptr, nullptr, dout);
     } else {
         rc = launch_seg_matmul(c, c->stream, t.type, false, dsd, nullptr, nseg, t.n_in, t.n_out, dx, t.n_in, nullptr, dout,
                                (int)m_max);
@@ -1301,9 +1322,9 @@ int dnb_expert_rows_dev(dnb_ctx* c, int layer, const float* x_rows_dev, const in
     if (rc) return rc;
     Workspace& w = c->ws;
     cudaStream_t st = c->stream;
-    const bool q4k_routed = L.m[0].type == T_Q4_K && L.m[1].type == T_Q4_K && L.m[2].type == T_Q4_K;
-    const bool q4k_shared = L.has_shared() && L.m[3].type == T_Q4_K && L.m[4].type == T_Q4_K && L.m[5].type == T_Q4_K &&
-                            L.m[3].n_out == M.ff;
+    const int ty_routed = use_shared ? -1 : tc_type(L, 0, 3);
+    const int ty_shared = (L.has_shared() && L.m[3].n_out == M.ff) ? tc_type(L, 3, 6) : -1;
+    const bool q4k_routed = ty_routed >= 0, q4k_shared = ty_shared >= 0;
     const bool umma = c->use_umma && w.maps_ok && rows >= 16 && M.e % 256 == 0 && M.ff % 256 == 0;
     if (!use_shared) {
         // every row is one (token, slot): a "chunk" of `rows` tokens with one selected expert each and weight 1
@@ -1317,9 +1338,9 @@ int dnb_expert_rows_dev(dnb_ctx* c, int layer, const float* x_rows_dev, const in
     const int sff = L.m[3].n_out;
     if (umma && q4k_shared) {
         if ((rc = launch_gather_split(c, st, x_rows_dev, M.e, nullptr, rows, M.e, w.xg_hi, w.xg_lo))) return rc;
-        if ((rc = launch_grouped_umma(c, st, true, w.seg_sh_gu, w.one, 1, M.e, M.ff, &w.maps_x, rows, w.act_hi, w.act_lo, nullptr)))
+        if ((rc = launch_grouped_tc(c, st, ty_shared, true, w.seg_sh_gu, w.one, 1, M.e, M.ff, &w.maps_x, rows, w.act_hi, w.act_lo, nullptr)))
             return rc;
-        return launch_grouped_umma(c, st, false, w.seg_sh_dn, w.one, 1, M.ff, M.e, &w.maps_act, rows, nullptr, nullptr, h_rows_dev);
+        return launch_grouped_tc(c, st, ty_shared, false, w.seg_sh_dn, w.one, 1, M.ff, M.e, &w.maps_act, rows, nullptr, nullptr, h_rows_dev);
     }
     if ((rc = launch_seg_matmul(c, st, L.m[3].type, true, w.seg_sh_gu, nullptr, 1, M.e, sff, x_rows_dev, M.e, nullptr, w.sact, rows)))
         return rc;
@@ -1362,7 +1383,7 @@ int dnb_moe_stack_dev(dnb_ctx* c, float* h_dev, int nt) {
                 if (rd == DNB_OK) continue;
                 if (rd != DNB_DECLINED) return rd;
             }
-            if (nt > 1 && nt <= kDecodeBatchMax && c->decode_fast) {
+            if (nt > 1 && nt <= kDecodeBatchMax && c->decode_fast && !umma_eligible(c, M.layers[l], nt)) {
                 const int rd = block_dev_decode_batch(c, l, h_dev, nt, h_dev, h_dev);
                 if (rd == DNB_OK) continue;
                 if (rd != DNB_DECLINED) return rd;

@@ -162,6 +162,7 @@ struct dnb_ctx {
     bool gemv_mma = true;               // one-token IQ3_XXS kernels on mma.sync (gemv_mma.cu, decode_fused.cu) where the shape fits
     bool decode_fused = true;           // gate/up + down of a one-token IQ3_XXS block as one kernel (decode_fused.cu)
     bool decode_routed = true;          // ... with the router folded into the same kernel (one launch per block)
+    int exact_min_nt = 4;               // IQ3_XXS layers: tokens from which a batch takes the exact-weight tcgen05 kernel
     bool use_umma = true;               // prefill chunks of Q4_K layers take the tcgen05 grouped GEMM
     void* ep = nullptr;                 // dnb::EpState of the peer-memory expert-parallel path (ep_p2p.cu)
     void* hc = nullptr;                 // dnb::HcState: hyper-connection mix weights and scratch (hc_mix.cu)
@@ -337,6 +338,14 @@ int launch_gather_split(dnb_ctx* c, cudaStream_t st, const float* x, int ldx, co
 int launch_grouped_umma(dnb_ctx* c, cudaStream_t st, bool fused, const SegDesc* seg, const int32_t* nseg_dev,
                         int nseg_max, int n_in, int n_out, const UmmaMaps* maps, int nt_max, uint16_t* out_hi,
                         uint16_t* out_lo, float* out_f32, float* const* row_dst = nullptr);
+// grouped_exact.cu: IQ3_XXS with exact bf16 weights and the block scales applied after the tensor-core sum
+int launch_grouped_exact(dnb_ctx* c, cudaStream_t st, bool fused, const SegDesc* seg, const int32_t* nseg_dev, int nseg_max,
+                         int n_in, int n_out, const UmmaMaps* maps, uint16_t* out_hi, uint16_t* out_lo, float* out_f32,
+                         float* const* row_dst = nullptr);
+// The tensor-core grouped GEMM of a block format: Q4_K -> launch_grouped_umma, IQ3_XXS -> launch_grouped_exact.
+int launch_grouped_tc(dnb_ctx* c, cudaStream_t st, int type, bool fused, const SegDesc* seg, const int32_t* nseg_dev,
+                      int nseg_max, int n_in, int n_out, const UmmaMaps* maps, int nt_max, uint16_t* out_hi,
+                      uint16_t* out_lo, float* out_f32, float* const* row_dst = nullptr);
 int launch_combine(dnb_ctx* c, cudaStream_t st, const float* hrow, const int32_t* pos, const float* wts, int nt,
                    int k, int e, const float* sh, const float* shcoef, float* out);
 int launch_shared_coef(dnb_ctx* c, cudaStream_t st, const float* x, const float* row, int nt, int e, float* coef);

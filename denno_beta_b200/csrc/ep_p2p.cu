@@ -417,8 +417,8 @@ extern "C" int dnb_ep_block_dev(dnb_ctx* c, int layer, const float* h_dev, int n
     }
     const Layer& L = M.layers[layer];
     for (int i = 0; i < 3; ++i)
-        if (!L.m[i].dev || L.m[i].type != T_Q4_K) {
-            set_error("ep_block: the peer-memory path runs Q4_K expert layers (tcgen05 grouped GEMM)");
+        if (!L.m[i].dev || L.m[i].type != L.m[0].type || (L.m[i].type != T_Q4_K && L.m[i].type != T_IQ3_XXS)) {
+            set_error("ep_block: the peer-memory path runs Q4_K or IQ3_XXS expert layers (tcgen05 grouped GEMMs)");
             return DNB_DECLINED;
         }
     DNB_CUDA(cudaSetDevice(c->device));
@@ -470,11 +470,11 @@ extern "C" int dnb_ep_block_dev(dnb_ctx* c, int layer, const float* h_dev, int n
     c->launches++;
     DNB_CUDA(cudaGetLastError());
     const int nseg_max = s->n_local;
-    if ((rc = launch_grouped_umma(c, st, true, s->seg_gu, s->nseg, nseg_max, M.e, M.ff, &s->maps_x, s->rows_total, s->act_hi,
-                                  s->act_lo, nullptr)))
+    if ((rc = launch_grouped_tc(c, st, L.m[0].type, true, s->seg_gu, s->nseg, nseg_max, M.e, M.ff, &s->maps_x, s->rows_total, s->act_hi,
+                                s->act_lo, nullptr)))
         return rc;
-    if ((rc = launch_grouped_umma(c, st, false, s->seg_dn, s->nseg, nseg_max, M.ff, M.e, &s->maps_act, s->rows_total, nullptr,
-                                  nullptr, nullptr, s->row_dst)))
+    if ((rc = launch_grouped_tc(c, st, L.m[0].type, false, s->seg_dn, s->nseg, nseg_max, M.ff, M.e, &s->maps_act, s->rows_total, nullptr,
+                                nullptr, nullptr, s->row_dst)))
         return rc;
     {
         ProfScope p_(c, st, "ep_signal_wait");

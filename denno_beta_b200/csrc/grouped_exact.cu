@@ -1,0 +1,544 @@
+// Grouped per-expert GEMM for IQ3_XXS experts on the 5th-generation tensor cores, with the weights
+// kept EXACT in bf16 and the block scales applied after the tensor-core sum.
+//
+// Reference kernels of this role: kernels_exp_iq_tc.cu:307-527 (dno_exp_tc_gu_iq3xxs: wmma bf16 64x64x32,
+// weights dequantised to fp32 then rounded to bf16, activations rounded to bf16) and :529-607 (down).
+//
+// Idea.  An IQ3_XXS weight is  db * g * s  with g one of eight small integers (codebook magnitudes
+// <= 62), s = +-1 and db = d * (0.5 + scale) * 0.5 shared by the 32 elements of a sub-block
+// (kquant.rs:659-680).  g * s is exact in bf16, so the A operand needs no hi/lo split and no floating
+// point arithmetic in its producer: two codebook lookups and four sign masks make eight elements.
+// The tensor core sums one sub-block (K = 32) at a time into a small TMEM buffer,
+//     D_g[row][token] = sum_{k in g} (g*s)[row][k] * x[token][k]        (x as bf16 hi + lo: 2 products),
+// and the epilogue warps, which own one weight row per thread, read D_g back and do the fp32
+//     acc[row][token] += db[row][g] * D_g[row][token].
+// Per sub-block that is 32 FMAs per thread for a 32-token tile - far less than dequantising the
+// 128 x 32 weights to fp32 and splitting them, which is what bounds the Q4_K kernel of
+// grouped_umma.cu on the small tiles a Zipf router and the decode batches produce.  The products
+// are exact (8-bit x 8-bit significands into fp32) and each activation carries 16 significant bits,
+// so the result is closer to the sequential fp32 result than the three-product scheme.
+//
+// Work item: (expert segment, 32-token tile, 128-row tile) over the whole K; the kernel is persistent
+// (one CTA per SM walks items i, i + gridDim.x, ...; every item costs the same).
+// Roles (576 threads):
+//   warps 0-7    producers: raw rows arrive by cp.async (16-byte lines that cover the 98-byte blocks,
+//                one 256-element block ahead, double buffered); decode into the K-major 128-byte
+//                swizzled A tiles of a stage (64 K = two sub-blocks); write the sub-block scales
+//   warps 8-15   epilogue: TMEM lane quadrant = warp % 4.  Gate/up kernel: warps 8-11 own the gate
+//                accumulators, 12-15 the up accumulators, exchanged through shared memory for
+//                silu(g) * u.  Down kernel: the two sets take the even / odd sub-blocks and add up.
+//   warp 16      TMA: the stage's activation tiles (hi and lo, 32 rows x 64 K, 128-byte swizzle)
+//   warp 17      MMA issue (one elected thread); owns the TMEM allocation
+// Barriers: full[s] / empty[s] per stage; tfull[b] / tfree[b] per TMEM sub-block buffer;
+// sfull[i] per slot of the scale ring (producers -> epilogue); xfull / xfree for the exchange buffer.
+// Every wait is bounded; one that gives up sets *status and the role leaves its loop (the producers
+// keep meeting at their named barrier so that none of them is left behind); TMEM is always freed.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "dnb_common.cuh"
+#include "dnb_iq_tables.h"
+
+namespace dnb {
+namespace ex {
+
+constexpr int BK = 64;                    // K per stage: one 128-byte swizzle row of bf16 = two sub-blocks
+constexpr int TILE_M = 128;               // weight rows per item
+constexpr int NT = 32;                    // tokens per item
+constexpr int A_TILE = TILE_M * BK * 2;   // 16 KB
+constexpr int B_TILE = NT * BK * 2;       // 4 KB (hi or lo)
+constexpr int STAGE_BYTES = 2 * A_TILE + 2 * B_TILE;
+constexpr int STAGES = 3;
+constexpr int NB = 6;                     // TMEM sub-block buffers
+constexpr int SCL = 16;                   // slots of the scale ring
+static_assert(2 * STAGES + NB <= SCL, "a producer must not lap the epilogue on the scale ring");
+constexpr int RAW_PITCH = 112;            // seven 16-byte lines cover a 98-byte block at any even offset
+constexpr int LUT_REP = 4;
+constexpr int PWARPS = 8, EWARPS = 8;
+constexpr int W_TMA = PWARPS + EWARPS, W_MMA = W_TMA + 1;
+constexpr int NTHREADS = (W_MMA + 1) * 32;
+constexpr int kMaxSeg = 1055;
+constexpr int kLocalItems = 64;
+
+__constant__ uint32_t c_grid[256];
+
+__device__ __forceinline__ uint32_t s32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mb_init(uint64_t* b, uint32_t n) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s32(b)), "r"(n) : "memory");
+}
+__device__ __forceinline__ void mb_arrive(uint64_t* b) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(s32(b)) : "memory");
+}
+__device__ __forceinline__ void mb_expect_tx(uint64_t* b, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s32(b)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mb_try(uint64_t* b, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(s32(b)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mb_wait(uint64_t* b, uint32_t parity, int* status, int code) {
+    for (int i = 0; i < (1 << 21); ++i)
+        if (mb_try(b, parity)) return true;
+    status_set(status, code);
+    return false;
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+            s32(dst)),
+        "l"(map), "r"(x), "r"(y), "r"(s32(bar))
+        : "memory");
+}
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void bar_producers() { asm volatile("bar.sync 1, %0;" ::"n"(PWARPS * 32) : "memory"); }
+
+// K-major, 128-byte swizzle shared memory matrix descriptor (sm_100): start address >> 4 in bits
+// [0,14), leading byte offset (unused here, 1) in [16,30), stride byte offset 1024 B between 8-row
+// groups in [32,46), version 1 in [46,48), layout 2 (SWIZZLE_128B) in [61,64).
+constexpr uint32_t kDescHi = (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t desc_lo(uint32_t smem_addr) { return ((smem_addr >> 4) & 0x3FFFu) | (1u << 16); }
+__device__ __forceinline__ uint64_t desc_of(uint32_t lo) { return ((uint64_t)kDescHi << 32) | lo; }
+// Instruction descriptor, kind::f16: D fp32, A and B bf16, both K-major, N >> 3 in bits 17-22, M >> 4 in 24-28.
+constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NT >> 3) << 17) | ((uint32_t)(TILE_M >> 4) << 24);
+
+__device__ __forceinline__ void mma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(kIdesc), "r"(acc)
+        : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* r) {
+    uint32_t v[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr)
+        : "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) r[i] = __uint_as_float(v[i]);
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ bool elect_one() {
+    uint32_t p;
+    asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}" : "=r"(p));
+    return p != 0;
+}
+__device__ __forceinline__ bool warp_all(bool v) { return __all_sync(0xffffffffu, v); }
+__device__ __forceinline__ uint32_t lds_u16(const uint8_t* p) { return *reinterpret_cast<const uint16_t*>(p); }
+
+struct Maps {  // tensor maps of the B operand: box heights 16, 32, 64, 128 for hi and lo (this kernel uses 32)
+    CUtensorMap hi[4];
+    CUtensorMap lo[4];
+};
+
+struct Item {
+    const uint8_t* wa;
+    const uint8_t* wb;
+    int prow;    // first packed row of the token tile
+    int m_tile;  // tokens in the tile (1..NT)
+    int r0;      // first weight row
+};
+__device__ __forceinline__ Item decode_item(int item, int row_tiles, int nseg, const int* tile_prefix,
+                                            const SegDesc* __restrict__ seg) {
+    const int tile = item / row_tiles, rt = item - tile * row_tiles;
+    int lo = 0, hi = nseg - 1;
+    while (lo < hi) {  // last segment whose first tile is <= tile
+        const int mid = (lo + hi + 1) >> 1;
+        if (tile_prefix[mid] <= tile) lo = mid; else hi = mid - 1;
+    }
+    const SegDesc sd = seg[lo];
+    const int t0 = (tile - tile_prefix[lo]) * NT;
+    Item it;
+    it.wa = sd.wa;
+    it.wb = sd.wb;
+    it.prow = (int)sd.row0 + t0;
+    it.m_tile = min(NT, (int)sd.m - t0);
+    it.r0 = rt * TILE_M;
+    return it;
+}
+struct ItemTab {
+    const Item* tab;
+    const SegDesc* seg;
+    const int* tile_prefix;
+    int nseg, row_tiles;
+    __device__ __forceinline__ Item get(int k) const {
+        if (k < kLocalItems) return tab[k];
+        return decode_item((int)blockIdx.x + k * (int)gridDim.x, row_tiles, nseg, tile_prefix, seg);
+    }
+};
+
+__device__ __forceinline__ float swiglu_fast(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
+
+// NMAT = 2: gate and up together, silu(g) * u written as bf16 hi/lo packed rows (the B operand of
+// the down GEMM).  NMAT = 1: one matrix, fp32 rows (or peer rows through row_dst).
+template <int NMAT>
+__global__ void __launch_bounds__(NTHREADS, 1)
+grouped_iq3_exact_kernel(const SegDesc* __restrict__ seg, const int32_t* __restrict__ nseg_dev, int n_in, int n_out, int rb,
+                         const __grid_constant__ Maps maps, uint16_t* __restrict__ out_hi, uint16_t* __restrict__ out_lo,
+                         float* __restrict__ out_f32, int* status, float* const* __restrict__ row_dst) {
+    constexpr int TM_COLS = NMAT == 2 ? 512 : 256;  // NB buffers of NMAT * 32 columns, rounded to a power of two
+    constexpr int RAW_SLOT = NMAT * TILE_M * RAW_PITCH;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* raw = smem + STAGES * STAGE_BYTES;                        // [2][NMAT][128][RAW_PITCH]
+    float* scl = reinterpret_cast<float*>(raw + 2 * RAW_SLOT);         // [SCL][NMAT][128]
+    float* xbuf = scl + SCL * NMAT * TILE_M;                           // [NT][128]
+    uint2* lut = reinterpret_cast<uint2*>(xbuf + NT * TILE_M);         // [256][LUT_REP]
+    uint64_t* full = reinterpret_cast<uint64_t*>(lut + 256 * LUT_REP);
+    uint64_t* empty = full + STAGES;
+    uint64_t* tfull = empty + STAGES;
+    uint64_t* tfree = tfull + NB;
+    uint64_t* sfull = tfree + NB;
+    uint64_t* xfull = sfull + SCL;
+    uint64_t* xfree = xfull + 1;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xfree + 1);
+    int* tile_prefix = reinterpret_cast<int*>(tmem_slot + 4);          // [nseg + 1]
+    Item* itab = reinterpret_cast<Item*>(tile_prefix + kMaxSeg + 1);   // [kLocalItems]
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int nchunks = n_in / BK;
+    const int nblocks = n_in / 256;
+    const int G = n_in / 32;  // sub-blocks per item (a multiple of 8)
+    const int row_tiles = n_out / TILE_M;
+    const int nseg = min(*nseg_dev, kMaxSeg);
+
+    if (tid == 0) {
+        for (int i = 0; i < STAGES; ++i) {
+            mb_init(&full[i], PWARPS + 1);  // eight producer warps + the TMA thread's expect_tx arrival
+            mb_init(&empty[i], 1);          // one tcgen05.commit
+        }
+        for (int i = 0; i < NB; ++i) {
+            mb_init(&tfull[i], 1);
+            mb_init(&tfree[i], NMAT == 2 ? 8 : 4);  // the epilogue warps that read the buffer
+        }
+        for (int i = 0; i < SCL; ++i) mb_init(&sfull[i], PWARPS / 2);  // the four warps that decode this half of the stage
+        mb_init(xfull, 4);
+        mb_init(xfree, 4);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    for (int i = tid; i < 256 * LUT_REP; i += NTHREADS) {  // codebook magnitudes as bf16 pairs (<= 62: exact)
+        const uint32_t w = c_grid[i / LUT_REP];
+        const uint32_t h0 = __float_as_uint((float)(w & 0xFFu)) >> 16, h1 = __float_as_uint((float)((w >> 8) & 0xFFu)) >> 16;
+        const uint32_t h2 = __float_as_uint((float)((w >> 16) & 0xFFu)) >> 16, h3 = __float_as_uint((float)(w >> 24)) >> 16;
+        lut[i] = make_uint2(h0 | (h1 << 16), h2 | (h3 << 16));
+    }
+    for (int i = tid; i < nseg; i += NTHREADS) tile_prefix[i + 1] = ((int)seg[i].m + NT - 1) / NT;
+    __syncthreads();
+    if (warp == 0) {
+        int carry = 0;
+        for (int base = 0; base < nseg; base += 32) {
+            const int i = base + lane;
+            int v = i < nseg ? tile_prefix[i + 1] : 0;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int o = __shfl_up_sync(0xffffffffu, v, d);
+                if (lane >= d) v += o;
+            }
+            if (i < nseg) tile_prefix[i + 1] = carry + v;
+            carry += __shfl_sync(0xffffffffu, v, 31);
+        }
+        if (lane == 0) tile_prefix[0] = 0;
+    }
+    if (warp == W_MMA) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(tmem_slot)), "r"(TM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const int n_items = nseg > 0 ? tile_prefix[nseg] * row_tiles : 0;
+    const int GR = gridDim.x;
+    const int my_items = (int)blockIdx.x < n_items ? (n_items - (int)blockIdx.x + GR - 1) / GR : 0;
+    if (tid < min(my_items, kLocalItems)) itab[tid] = decode_item((int)blockIdx.x + tid * GR, row_tiles, nseg, tile_prefix, seg);
+    __syncthreads();
+    const ItemTab items{itab, seg, tile_prefix, nseg, row_tiles};
+    bool ok = true;
+
+    if (warp < PWARPS) {
+        // ---------------- producers ----------------
+        const int row = tid & 127, half = tid >> 7;
+        const int total_blocks = my_items * nblocks;
+        // 16-byte lines of block kb of this thread's (row, matrix) [NMAT = 2] or its share of the row's lines [NMAT = 1]
+        auto fetch = [&](int kb) {
+            if (kb < total_blocks) {
+                const int k = kb / nblocks, b = kb - k * nblocks;
+                const Item it = items.get(k);
+                const int mat = NMAT == 2 ? half : 0;
+                const uint8_t* src = mat ? it.wb : it.wa;
+                const size_t off = ((size_t)(it.r0 + row) * rb + (size_t)98 * b) & ~(size_t)15;
+                uint8_t* dst = raw + (kb & 1) * RAW_SLOT + (mat * TILE_M + row) * RAW_PITCH;
+                if constexpr (NMAT == 2) {
+#pragma unroll
+                    for (int l = 0; l < 7; ++l) cp_async16(dst + 16 * l, src + off + 16 * l);
+                } else {
+#pragma unroll
+                    for (int l = 0; l < 4; ++l)
+                        if (2 * l + half < 7) cp_async16(dst + 16 * (2 * l + half), src + off + 16 * (2 * l + half));
+                }
+            }
+            cp_async_commit();
+        };
+        fetch(0);
+        for (int kb = 0; kb < total_blocks; ++kb) {
+            cp_async_wait_all();
+            bar_producers();  // everybody's lines of block kb have landed; everybody is done with block kb - 1
+            fetch(kb + 1);
+            const int k = kb / nblocks, b = kb - k * nblocks;
+            const int sh = (int)(((size_t)row * rb + (size_t)98 * b) & 15);
+            const uint8_t* rw0 = raw + (kb & 1) * RAW_SLOT + row * RAW_PITCH + sh;
+            float d[NMAT];
+#pragma unroll
+            for (int mt = 0; mt < NMAT; ++mt) d[mt] = __half2float(__ushort_as_half((unsigned short)lds_u16(rw0 + mt * TILE_M * RAW_PITCH)));
+#pragma unroll 1
+            for (int j = 0; j < 4; ++j) {
+                const int g = kb * 4 + j;  // running chunk (stage) index of this CTA
+                const int st = g % STAGES;
+                const uint32_t ph = (uint32_t)(g / STAGES) & 1u;
+                if (ok && g >= STAGES) ok = mb_wait(&empty[st], ph ^ 1u, status, 2);
+                if (!ok) continue;
+                const int gp = 2 * j + half;       // sub-block inside the 256-element block
+                const int slot = (2 * g + half) % SCL;
+                uint8_t* sa = smem + st * STAGE_BYTES + (uint32_t)(row >> 3) * 1024u + (uint32_t)(row & 7) * 128u;
+#pragma unroll
+                for (int mt = 0; mt < NMAT; ++mt) {
+                    const uint8_t* rw = rw0 + mt * TILE_M * RAW_PITCH;
+                    const uint32_t aux = lds_u16(rw + 66 + 4 * gp) | (lds_u16(rw + 68 + 4 * gp) << 16);
+                    scl[(slot * NMAT + mt) * TILE_M + row] = d[mt] * (0.5f + (float)(aux >> 28)) * 0.5f;
+#pragma unroll
+                    for (int l = 0; l < 4; ++l) {
+                        const uint32_t idx = lds_u16(rw + 2 + 8 * gp + 2 * l);
+                        const uint32_t code = (aux >> (7 * l)) & 127u;
+                        const uint32_t sg = code | ((__popc(code) & 1u) << 7);  // bit 7 makes the number of minus signs even
+                        const uint2 g1 = lut[(idx & 0xFFu) * LUT_REP + (lane & (LUT_REP - 1))];
+                        const uint2 g2 = lut[(idx >> 8) * LUT_REP + (lane & (LUT_REP - 1))];
+                        uint4 v;
+                        v.x = g1.x ^ ((sg * 0x40008000u) & 0x80008000u);
+                        v.y = g1.y ^ ((sg * 0x10002000u) & 0x80008000u);
+                        v.z = g2.x ^ ((sg * 0x04000800u) & 0x80008000u);
+                        v.w = g2.y ^ ((sg * 0x01000200u) & 0x80008000u);
+                        *reinterpret_cast<uint4*>(sa + mt * A_TILE + (((uint32_t)(4 * half + l) ^ (uint32_t)(row & 7)) << 4)) = v;
+                    }
+                }
+                fence_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
+                __syncwarp();
+                if (lane == 0) {
+                    mb_arrive(&full[st]);
+                    mb_arrive(&sfull[slot]);
+                }
+            }
+        }
+        cp_async_wait_all();
+    } else if (warp == W_TMA) {
+        // ---------------- TMA: activation tiles ----------------
+        int g = 0;
+        for (int k = 0; k < my_items && ok; ++k) {
+            const Item it = items.get(k);
+            for (int c = 0; c < nchunks; ++c, ++g) {
+                const int st = g % STAGES;
+                const uint32_t ph = (uint32_t)(g / STAGES) & 1u;
+                if (g >= STAGES) ok = warp_all(mb_wait(&empty[st], ph ^ 1u, status, 4));
+                if (!ok) break;
+                uint8_t* sbp = smem + st * STAGE_BYTES + 2 * A_TILE;
+                if (elect_one()) {
+                    mb_expect_tx(&full[st], 2u * B_TILE);
+                    tma_load_2d(sbp, &maps.hi[1], c * BK, it.prow, &full[st]);
+                    tma_load_2d(sbp + B_TILE, &maps.lo[1], c * BK, it.prow, &full[st]);
+                }
+                __syncwarp();
+            }
+        }
+    } else if (warp == W_MMA) {
+        // ---------------- MMA issue ----------------
+        const uint32_t smem_lo = desc_lo(s32(smem));
+        const int total = my_items * nchunks;
+        for (int g = 0; g < total && ok; ++g) {
+            const int st = g % STAGES;
+            const uint32_t ph = (uint32_t)(g / STAGES) & 1u;
+            ok = warp_all(mb_wait(&full[st], ph, status, 5));
+            if (!ok) break;
+            const uint32_t a_lo = smem_lo + (uint32_t)(st * (STAGE_BYTES >> 4));
+            const uint32_t bh_lo = a_lo + (uint32_t)((2 * A_TILE) >> 4), bl_lo = bh_lo + (uint32_t)(B_TILE >> 4);
+#pragma unroll
+            for (int grp = 0; grp < 2; ++grp) {
+                const int gc = 2 * g + grp;  // running sub-block index
+                const int b = gc % NB;
+                if (gc >= NB) ok = warp_all(mb_wait(&tfree[b], (uint32_t)(gc / NB - 1) & 1u, status, 6));
+                if (!ok) break;
+                tc_fence_after();
+                if (elect_one()) {
+#pragma unroll
+                    for (int mt = 0; mt < NMAT; ++mt) {
+                        const uint32_t dcol = tmem_base + (uint32_t)(b * NMAT * NT + mt * NT);
+                        const uint32_t am = a_lo + (uint32_t)(mt * (A_TILE >> 4));
+#pragma unroll
+                        for (int ks = 0; ks < 2; ++ks) {
+                            const uint32_t koff = (uint32_t)(2 * grp + ks) * 2u;  // 16 bf16 = 32 bytes, >> 4
+                            const uint64_t a = desc_of(am + koff);
+                            mma_bf16(dcol, a, desc_of(bh_lo + koff), ks);  // the first product of a sub-block overwrites
+                            mma_bf16(dcol, a, desc_of(bl_lo + koff), 1u);
+                        }
+                    }
+                    mma_commit(&tfull[b]);
+                    if (grp == 1) mma_commit(&empty[st]);  // the stage is free once everything issued so far has read it
+                }
+                __syncwarp();
+            }
+        }
+    } else {
+        // ---------------- epilogue: TMEM lane = weight row ----------------
+        const int quad = warp & 3, hsel = (warp - PWARPS) >> 2;
+        const int r = quad * 32 + lane;
+        const int mt = NMAT == 2 ? hsel : 0;
+        const uint32_t tlane = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(mt * NT);
+        for (int k = 0; k < my_items && ok; ++k) {
+            const Item it = items.get(k);
+            float acc[NT];
+#pragma unroll
+            for (int j = 0; j < NT; ++j) acc[j] = 0.f;
+            for (int gi = (NMAT == 2 ? 0 : hsel); gi < G && ok; gi += (NMAT == 2 ? 1 : 2)) {
+                const int gc = k * G + gi;
+                const int b = gc % NB, slot = gc % SCL;
+                ok = mb_wait(&sfull[slot], (uint32_t)(gc / SCL) & 1u, status, 3);
+                if (!ok) break;
+                const float s = scl[(slot * NMAT + mt) * TILE_M + r];
+                ok = mb_wait(&tfull[b], (uint32_t)(gc / NB) & 1u, status, 3);
+                if (!ok) break;
+                tc_fence_after();
+                float dv[NT];
+                tmem_ld16(tlane + (uint32_t)(b * NMAT * NT), dv);
+                tmem_ld16(tlane + (uint32_t)(b * NMAT * NT + 16), dv + 16);
+                tmem_ld_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mb_arrive(&tfree[b]);
+#pragma unroll
+                for (int j = 0; j < NT; ++j) acc[j] = fmaf(s, dv[j], acc[j]);
+            }
+            if (!ok) break;
+            if (hsel == 1) {
+                if (k > 0) ok = mb_wait(xfree, (uint32_t)(k - 1) & 1u, status, 3);
+                if (!ok) break;
+#pragma unroll
+                for (int j = 0; j < NT; ++j) xbuf[j * TILE_M + r] = acc[j];
+                __syncwarp();
+                if (lane == 0) mb_arrive(xfull);
+            } else {
+                ok = mb_wait(xfull, (uint32_t)k & 1u, status, 3);
+                if (!ok) break;
+                if constexpr (NMAT == 2) {
+                    uint16_t* oh = out_hi + (size_t)it.prow * n_out + it.r0 + r;
+                    uint16_t* ol = out_lo + (size_t)it.prow * n_out + it.r0 + r;
+#pragma unroll
+                    for (int j = 0; j < NT; ++j) {
+                        const float a = swiglu_fast(acc[j], xbuf[j * TILE_M + r]);
+                        const uint16_t ah = __bfloat16_as_ushort(__float2bfloat16_rn(a));
+                        const float al = a - __uint_as_float((uint32_t)ah << 16);
+                        if (j < it.m_tile) {
+                            oh[(size_t)j * n_out] = ah;
+                            ol[(size_t)j * n_out] = (uint16_t)(__float_as_uint(al) >> 16);
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < NT; ++j) {
+                        const float a = acc[j] + xbuf[j * TILE_M + r];  // even sub-blocks + odd sub-blocks
+                        if (j < it.m_tile) {
+                            if (row_dst) row_dst[it.prow + j][it.r0 + r] = a;  // expert parallel: the owner's (token, slot) row
+                            else out_f32[(size_t)(it.prow + j) * n_out + it.r0 + r] = a;
+                        }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mb_arrive(xfree);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == W_MMA) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TM_COLS) : "memory");
+    }
+}
+
+}  // namespace ex
+
+static int upload_grid(int device) {
+    static bool done[64] = {false};
+    if (device < 0 || device >= 64) return DNB_ERR_ARG;
+    if (done[device]) return DNB_OK;
+    DNB_CUDA(cudaMemcpyToSymbol(ex::c_grid, dnb_iq3xxs_grid, sizeof(ex::c_grid)));
+    done[device] = true;
+    return DNB_OK;
+}
+
+bool grouped_exact_handles(int type, int n_in, int n_out) {
+    return type == T_IQ3_XXS && n_in % 256 == 0 && n_out % ex::TILE_M == 0;
+}
+
+// Grouped IQ3_XXS GEMM on tcgen05 with exact weights.  fused: seg[].wa/wb are gate/up, output
+// silu(g)*u as hi/lo bf16 packed rows; otherwise seg[].wa, fp32 output rows.
+int launch_grouped_exact(dnb_ctx* c, cudaStream_t st, bool fused, const SegDesc* seg, const int32_t* nseg_dev, int nseg_max,
+                         int n_in, int n_out, const UmmaMaps* maps, uint16_t* out_hi, uint16_t* out_lo, float* out_f32,
+                         float* const* row_dst) {
+    static_assert(sizeof(UmmaMaps) == sizeof(ex::Maps), "UmmaMaps must mirror ex::Maps");
+    if (!grouped_exact_handles(T_IQ3_XXS, n_in, n_out) || nseg_max > ex::kMaxSeg) return DNB_DECLINED;
+    int rc = upload_grid(c->device);
+    if (rc) return rc;
+    const int rb = n_in / 256 * 98;
+    const ex::Maps& M = *reinterpret_cast<const ex::Maps*>(maps);
+    const dim3 grid(c->sm_count);
+    const int nmat = fused ? 2 : 1;
+    const size_t smem = (size_t)ex::STAGES * ex::STAGE_BYTES + 2 * (size_t)nmat * ex::TILE_M * ex::RAW_PITCH +
+                        (size_t)ex::SCL * nmat * ex::TILE_M * 4 + (size_t)ex::NT * ex::TILE_M * 4 + 256 * ex::LUT_REP * 8 +
+                        (2 * ex::STAGES + 2 * ex::NB + ex::SCL + 2) * 8 + 16 + (ex::kMaxSeg + 1) * 4 +
+                        ex::kLocalItems * sizeof(ex::Item) + 1024;
+    if (fused) {
+        static SmemGrant grant;
+        DNB_CUDA(grant_smem(grant, c->device, ex::grouped_iq3_exact_kernel<2>, smem));
+        ProfScope prof_(c, st, "exact_gate_up");
+        ex::grouped_iq3_exact_kernel<2><<<grid, ex::NTHREADS, smem, st>>>(seg, nseg_dev, n_in, n_out, rb, M, out_hi, out_lo, nullptr,
+                                                                         c->status, nullptr);
+    } else {
+        static SmemGrant grant;
+        DNB_CUDA(grant_smem(grant, c->device, ex::grouped_iq3_exact_kernel<1>, smem));
+        ProfScope prof_(c, st, "exact_down");
+        ex::grouped_iq3_exact_kernel<1><<<grid, ex::NTHREADS, smem, st>>>(seg, nseg_dev, n_in, n_out, rb, M, nullptr, nullptr, out_f32,
+                                                                         c->status, row_dst);
+    }
+    c->launches++;
+    DNB_CUDA(cudaGetLastError());
+    return DNB_OK;
+}
+
+int launch_grouped_tc(dnb_ctx* c, cudaStream_t st, int type, bool fused, const SegDesc* seg, const int32_t* nseg_dev,
+                      int nseg_max, int n_in, int n_out, const UmmaMaps* maps, int nt_max, uint16_t* out_hi,
+                      uint16_t* out_lo, float* out_f32, float* const* row_dst) {
+    if (type == T_IQ3_XXS)
+        return launch_grouped_exact(c, st, fused, seg, nseg_dev, nseg_max, n_in, n_out, maps, out_hi, out_lo, out_f32, row_dst);
+    if (type == T_Q4_K)
+        return launch_grouped_umma(c, st, fused, seg, nseg_dev, nseg_max, n_in, n_out, maps, nt_max, out_hi, out_lo, out_f32, row_dst);
+    return DNB_DECLINED;
+}
+
+}  // namespace dnb

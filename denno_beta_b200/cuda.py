@@ -165,6 +165,10 @@ class CudaCtx:
     def set_gemv_impl(self, impl):
         check(self.lib.dnb_set_gemv_impl(self.h, impl))
 
+    def set_tc_min_tokens(self, iq3_xxs_min_tokens):
+        """IQ3_XXS layers: token count from which a batch takes the exact-weight tcgen05 grouped GEMM."""
+        check(self.lib.dnb_set_tc_min_tokens(self.h, iq3_xxs_min_tokens))
+
     # -- MoE model ----------------------------------------------------------------
     def moe_config(self, n_layer, n_embd, n_ff, n_expert, n_expert_used, n_shared_ff=0, rms_eps=1e-6,
                    norm_topk_prob=True):

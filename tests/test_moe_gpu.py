@@ -87,6 +87,43 @@ def test_tcgen05_grouped_gemm_matches_fp32_kernels(orc, small):
     assert c.device_status() == 0
 
 
+def test_exact_weight_tcgen05_kernel_matches_fp32_kernels(orc, small):
+    """IQ3_XXS chunks and decode batches of 4 tokens or more: exact bf16 weights on the tensor cores, sub-block scales
+    applied by the epilogue.  Ragged sizes cover one and several 32-token tiles per expert and tiles with one token;
+    a lowered threshold takes 2- and 3-token batches the same way; a batch's rows do not depend on their companions."""
+    c, layers = small
+    L = layers[0]
+    for nt in (4, 7, 31, 32, 33, 100, 300):
+        h = orc.synth_normal(SEED, 1400 + nt, 1.0, nt * L.e).reshape(nt, L.e)
+        launches = c.launch_count()
+        tc, tsel, tw = c.moe_block(0, h, want_routing=True)
+        c.set_gemv_impl(2)
+        try:
+            fp = c.moe_block(0, h)
+        finally:
+            c.set_gemv_impl(0)
+        print("nt=%d exact-weight tcgen05 vs fp32 kernels: %.3g" % (nt, rel_err(tc, fp)))
+        assert rel_err(tc, fp) <= 2e-4, "nt=%d: %.3g" % (nt, rel_err(tc, fp))
+        idx = sorted({0, nt // 3, nt - 1})
+        err, _ = check_block(orc, L, h[idx], tc[idx], tsel[idx], tw[idx])
+        assert err <= 2e-4, "nt=%d: %.3g vs oracle" % (nt, err)
+        again = c.moe_block(0, h)
+        assert np.array_equal(tc.view(np.uint32), again.view(np.uint32)), "not bit-identical run to run"
+        if nt >= 8:
+            part = c.moe_block(0, h[nt // 2:])
+            assert np.array_equal(part.view(np.uint32), tc[nt // 2:].view(np.uint32)), "a row depends on its companions"
+    c.set_tc_min_tokens(2)
+    try:
+        for nt in (2, 3):
+            h = orc.synth_normal(SEED, 1450 + nt, 1.0, nt * L.e).reshape(nt, L.e)
+            tc, tsel, tw = c.moe_block(0, h, want_routing=True)
+            err, _ = check_block(orc, L, h, tc, tsel, tw)
+            assert err <= 2e-4, "nt=%d: %.3g vs oracle" % (nt, err)
+    finally:
+        c.set_tc_min_tokens(4)
+    assert c.device_status() == 0
+
+
 def test_decode_kernels_agree_with_tiled_kernels(orc, small):
     """One-token calls take the bulk-copy GEMV + fused router kernels; the general
     tiled kernels (set_gemv_impl(2) forces them) must route identically and agree in
