@@ -162,7 +162,7 @@ struct dnb_ctx {
     bool gemv_mma = true;               // one-token IQ3_XXS kernels on mma.sync (gemv_mma.cu, decode_fused.cu) where the shape fits
     bool decode_fused = true;           // gate/up + down of a one-token IQ3_XXS block as one kernel (decode_fused.cu)
     bool decode_routed = true;          // ... with the router folded into the same kernel (one launch per block)
-    int exact_min_nt = 4;               // IQ3_XXS layers: tokens from which a batch takes the exact-weight tcgen05 kernel
+    int exact_min_nt = 16;              // IQ3_XXS layers: tokens from which a batch takes the exact-weight tcgen05 kernel
     bool use_umma = true;               // prefill chunks of Q4_K layers take the tcgen05 grouped GEMM
     void* ep = nullptr;                 // dnb::EpState of the peer-memory expert-parallel path (ep_p2p.cu)
     void* hc = nullptr;                 // dnb::HcState: hyper-connection mix weights and scratch (hc_mix.cu)

@@ -20,15 +20,16 @@
 //
 // Work item: (expert segment, 32-token tile, 128-row tile) over the whole K; the kernel is persistent
 // (one CTA per SM walks items i, i + gridDim.x, ...; every item costs the same).
-// Roles (576 threads):
-//   warps 0-7    producers: raw rows arrive by cp.async (16-byte lines that cover the 98-byte blocks,
-//                one 256-element block ahead, double buffered); decode into the K-major 128-byte
+// Roles (832 threads; 16 producer warps because the decode is a chain of dependent shared-memory lookups
+// and the epilogue warps mostly wait - measured: with 8 producer warps each scheduler issued 0.4 per cycle):
+//   warps 0-15   producers: raw rows arrive by cp.async (16-byte lines that cover the 98-byte blocks, one
+//                256-element block ahead, double buffered; the next items' tiles are asked into L2 first); decode into the K-major 128-byte
 //                swizzled A tiles of a stage (64 K = two sub-blocks); write the sub-block scales
-//   warps 8-15   epilogue: TMEM lane quadrant = warp % 4.  Gate/up kernel: warps 8-11 own the gate
-//                accumulators, 12-15 the up accumulators, exchanged through shared memory for
+//   warps 16-23  epilogue: TMEM lane quadrant = warp % 4.  Gate/up kernel: warps 16-19 own the gate
+//                accumulators, 20-23 the up accumulators, exchanged through shared memory for
 //                silu(g) * u.  Down kernel: the two sets take the even / odd sub-blocks and add up.
-//   warp 16      TMA: the stage's activation tiles (hi and lo, 32 rows x 64 K, 128-byte swizzle)
-//   warp 17      MMA issue (one elected thread); owns the TMEM allocation
+//   warp 24      TMA: the stage's activation tiles (hi and lo, 32 rows x 64 K, 128-byte swizzle)
+//   warp 25      MMA issue (one elected thread); owns the TMEM allocation
 // Barriers: full[s] / empty[s] per stage; tfull[b] / tfree[b] per TMEM sub-block buffer;
 // sfull[i] per slot of the scale ring (producers -> epilogue); xfull / xfree for the exchange buffer.
 // Every wait is bounded; one that gives up sets *status and the role leaves its loop (the producers
@@ -50,16 +51,17 @@ constexpr int A_TILE = TILE_M * BK * 2;   // 16 KB
 constexpr int B_TILE = NT * BK * 2;       // 4 KB (hi or lo)
 constexpr int STAGE_BYTES = 2 * A_TILE + 2 * B_TILE;
 constexpr int STAGES = 3;
-constexpr int NB = 6;                     // TMEM sub-block buffers
-constexpr int SCL = 16;                   // slots of the scale ring
-static_assert(2 * STAGES + NB <= SCL, "a producer must not lap the epilogue on the scale ring");
+constexpr int RAWS = 2;                   // raw slots: one block in flight while one is decoded
+constexpr int NB = 6;                     // TMEM sub-block buffers (NT columns per matrix)
+constexpr int SCL = 12;                   // slots of the scale ring
+static_assert(RAWS == 2 && 2 * STAGES + NB <= SCL && SCL % 2 == 0 && NB % 2 == 0, "a producer must not lap the epilogue on the scale ring");
 constexpr int RAW_PITCH = 112;            // seven 16-byte lines cover a 98-byte block at any even offset
-constexpr int LUT_REP = 4;
-constexpr int PWARPS = 8, EWARPS = 8;
+constexpr int LUT_REP = 8;
+constexpr int PWARPS = 16, EWARPS = 8;
 constexpr int W_TMA = PWARPS + EWARPS, W_MMA = W_TMA + 1;
 constexpr int NTHREADS = (W_MMA + 1) * 32;
 constexpr int kMaxSeg = 1055;
-constexpr int kLocalItems = 64;
+constexpr int kLocalItems = 32;
 
 __constant__ uint32_t c_grid[256];
 
@@ -99,7 +101,7 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
         : "memory");
 }
 __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s32(dst)), "l"(src) : "memory");
+    asm volatile("cp.async.cg.shared.global.L2::128B [%0], [%1], 16;" ::"r"(s32(dst)), "l"(src) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
@@ -112,6 +114,8 @@ constexpr uint32_t kDescHi = (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29);
 __device__ __forceinline__ uint32_t desc_lo(uint32_t smem_addr) { return ((smem_addr >> 4) & 0x3FFFu) | (1u << 16); }
 __device__ __forceinline__ uint64_t desc_of(uint32_t lo) { return ((uint64_t)kDescHi << 32) | lo; }
 // Instruction descriptor, kind::f16: D fp32, A and B bf16, both K-major, N >> 3 in bits 17-22, M >> 4 in 24-28.
+// (One N = 64 product against the hi and lo rows as one B operand reads the weight tile once but doubles the columns the
+// epilogue has to read and add; the kernel is bound by issued instructions, not by shared memory, and it measured the same.)
 constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NT >> 3) << 17) | ((uint32_t)(TILE_M >> 4) << 24);
 
 __device__ __forceinline__ void mma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t acc) {
@@ -194,12 +198,12 @@ __global__ void __launch_bounds__(NTHREADS, 1)
 grouped_iq3_exact_kernel(const SegDesc* __restrict__ seg, const int32_t* __restrict__ nseg_dev, int n_in, int n_out, int rb,
                          const __grid_constant__ Maps maps, uint16_t* __restrict__ out_hi, uint16_t* __restrict__ out_lo,
                          float* __restrict__ out_f32, int* status, float* const* __restrict__ row_dst) {
-    constexpr int TM_COLS = NMAT == 2 ? 512 : 256;  // NB buffers of NMAT * 32 columns, rounded to a power of two
+    constexpr int TM_COLS = NMAT == 2 ? 512 : 256;  // NB buffers of NMAT * NT columns, rounded up to a power of two
     constexpr int RAW_SLOT = NMAT * TILE_M * RAW_PITCH;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* raw = smem + STAGES * STAGE_BYTES;                        // [2][NMAT][128][RAW_PITCH]
-    float* scl = reinterpret_cast<float*>(raw + 2 * RAW_SLOT);         // [SCL][NMAT][128]
+    float* scl = reinterpret_cast<float*>(raw + RAWS * RAW_SLOT);         // [SCL][NMAT][128]
     float* xbuf = scl + SCL * NMAT * TILE_M;                           // [NT][128]
     uint2* lut = reinterpret_cast<uint2*>(xbuf + NT * TILE_M);         // [256][LUT_REP]
     uint64_t* full = reinterpret_cast<uint64_t*>(lut + 256 * LUT_REP);
@@ -222,14 +226,14 @@ grouped_iq3_exact_kernel(const SegDesc* __restrict__ seg, const int32_t* __restr
 
     if (tid == 0) {
         for (int i = 0; i < STAGES; ++i) {
-            mb_init(&full[i], PWARPS + 1);  // eight producer warps + the TMA thread's expect_tx arrival
+            mb_init(&full[i], PWARPS + 1);  // the producer warps + the TMA thread's expect_tx arrival
             mb_init(&empty[i], 1);          // one tcgen05.commit
         }
         for (int i = 0; i < NB; ++i) {
             mb_init(&tfull[i], 1);
             mb_init(&tfree[i], NMAT == 2 ? 8 : 4);  // the epilogue warps that read the buffer
         }
-        for (int i = 0; i < SCL; ++i) mb_init(&sfull[i], PWARPS / 2);  // the four warps that decode this half of the stage
+        for (int i = 0; i < SCL; ++i) mb_init(&sfull[i], PWARPS);  // every producer warp writes 16 rows of every sub-block
         mb_init(xfull, 4);
         mb_init(xfree, 4);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -276,75 +280,101 @@ grouped_iq3_exact_kernel(const SegDesc* __restrict__ seg, const int32_t* __restr
 
     if (warp < PWARPS) {
         // ---------------- producers ----------------
-        const int row = tid & 127, half = tid >> 7;
+        // Decode: a warp owns 8 rows; its lanes are 8 rows x the 4 eight-element units of a sub-block, so the
+        // lanes of a raw-byte load fall in distinct banks (row pitch 28 words) and the unit's 16-byte store
+        // is one column of the swizzled row.
+        const int l = lane >> 3, l7 = 7 * l;
+        const int row0 = warp * 8 + (lane & 7);
+        const uint2* lutl = lut + (lane & (LUT_REP - 1));
+        const uint32_t colb = ((uint32_t)(l ^ (lane & 7))) << 4;   // column of the unit for sub-block half 0; half 1 flips bit 6
+        const uint32_t sa_off = (uint32_t)(row0 >> 3) * 1024u + (uint32_t)(row0 & 7) * 128u;
         const int total_blocks = my_items * nblocks;
-        // 16-byte lines of block kb of this thread's (row, matrix) [NMAT = 2] or its share of the row's lines [NMAT = 1]
-        auto fetch = [&](int kb) {
-            if (kb < total_blocks) {
+        // Part q (0..3) of the fetch of block kb.  Eight consecutive lanes copy the seven 16-byte lines that cover one
+        // row's 98-byte block (cp.async; 112-byte bulk copies measured slower, a second block in flight or a lane per
+        // row no different), one part per stage of the block before.
+        // The tile of the NEXT item (128 rows x row bytes, contiguous in the expert-major layout) is asked into L2 in
+        // sixteen large pieces while the current item is decoded, so that HBM sees long requests.
+        const int f_line = tid & 7, f_rb = tid >> 3;   // f_rb = 0..63
+        auto fetch = [&](int kb, int q) {
+            const int rbi = q * 64 + f_rb;             // (matrix, row) of this lane's line
+            if (kb < total_blocks && rbi < NMAT * TILE_M && f_line < 7) {
                 const int k = kb / nblocks, b = kb - k * nblocks;
                 const Item it = items.get(k);
-                const int mat = NMAT == 2 ? half : 0;
+                const int mat = rbi >> 7, frow = rbi & 127;
                 const uint8_t* src = mat ? it.wb : it.wa;
-                const size_t off = ((size_t)(it.r0 + row) * rb + (size_t)98 * b) & ~(size_t)15;
-                uint8_t* dst = raw + (kb & 1) * RAW_SLOT + (mat * TILE_M + row) * RAW_PITCH;
-                if constexpr (NMAT == 2) {
-#pragma unroll
-                    for (int l = 0; l < 7; ++l) cp_async16(dst + 16 * l, src + off + 16 * l);
-                } else {
-#pragma unroll
-                    for (int l = 0; l < 4; ++l)
-                        if (2 * l + half < 7) cp_async16(dst + 16 * (2 * l + half), src + off + 16 * (2 * l + half));
-                }
+                const size_t off = ((size_t)(it.r0 + frow) * rb + (size_t)98 * b) & ~(size_t)15;
+                uint8_t* dst = raw + (kb & 1) * RAW_SLOT + (mat * TILE_M + frow) * RAW_PITCH;
+                cp_async16(dst + 16 * f_line, src + off + 16 * f_line);
             }
-            cp_async_commit();
+            if (q == 3) cp_async_commit();
         };
-        fetch(0);
+        auto l2_prefetch_item = [&](int k) {
+            if (tid < 16 * NMAT && k < my_items) {
+                const Item it = items.get(k);
+                const uint32_t piece = (uint32_t)(8 * rb);  // a sixteenth of the tile; a multiple of 16 bytes
+                const uint8_t* base = ((tid >> 4) ? it.wb : it.wa) + (size_t)it.r0 * rb + (size_t)(tid & 15) * piece;
+                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base), "r"(piece) : "memory");
+            }
+        };
+        l2_prefetch_item(0);
+        for (int q = 0; q < 4; ++q) fetch(0, q);
+        int st = 0, slot0 = 0, g = 0;   // stage, first scale slot and running chunk index of the next stage
+        uint32_t ph = 0;
+        int kblk = 0;                   // block inside the item
         for (int kb = 0; kb < total_blocks; ++kb) {
             cp_async_wait_all();
             bar_producers();  // everybody's lines of block kb have landed; everybody is done with block kb - 1
-            fetch(kb + 1);
-            const int k = kb / nblocks, b = kb - k * nblocks;
-            const int sh = (int)(((size_t)row * rb + (size_t)98 * b) & 15);
-            const uint8_t* rw0 = raw + (kb & 1) * RAW_SLOT + row * RAW_PITCH + sh;
+            if (kblk == 0) l2_prefetch_item(kb / nblocks + 1);
+            const uint8_t* rw[NMAT];
             float d[NMAT];
-#pragma unroll
-            for (int mt = 0; mt < NMAT; ++mt) d[mt] = __half2float(__ushort_as_half((unsigned short)lds_u16(rw0 + mt * TILE_M * RAW_PITCH)));
-#pragma unroll 1
-            for (int j = 0; j < 4; ++j) {
-                const int g = kb * 4 + j;  // running chunk (stage) index of this CTA
-                const int st = g % STAGES;
-                const uint32_t ph = (uint32_t)(g / STAGES) & 1u;
-                if (ok && g >= STAGES) ok = mb_wait(&empty[st], ph ^ 1u, status, 2);
-                if (!ok) continue;
-                const int gp = 2 * j + half;       // sub-block inside the 256-element block
-                const int slot = (2 * g + half) % SCL;
-                uint8_t* sa = smem + st * STAGE_BYTES + (uint32_t)(row >> 3) * 1024u + (uint32_t)(row & 7) * 128u;
+            {
+                const int sh = (int)(((size_t)row0 * rb + (size_t)98 * kblk) & 15);
 #pragma unroll
                 for (int mt = 0; mt < NMAT; ++mt) {
-                    const uint8_t* rw = rw0 + mt * TILE_M * RAW_PITCH;
-                    const uint32_t aux = lds_u16(rw + 66 + 4 * gp) | (lds_u16(rw + 68 + 4 * gp) << 16);
-                    scl[(slot * NMAT + mt) * TILE_M + row] = d[mt] * (0.5f + (float)(aux >> 28)) * 0.5f;
+                    rw[mt] = raw + (kb & 1) * RAW_SLOT + (mt * TILE_M + row0) * RAW_PITCH + sh;
+                    d[mt] = __half2float(__ushort_as_half((unsigned short)lds_u16(rw[mt])));
+                }
+            }
+            if (++kblk == nblocks) kblk = 0;
+#pragma unroll 1
+            for (int j = 0; j < 4; ++j) {
+                if (ok && g >= STAGES) ok = mb_wait(&empty[st], ph ^ 1u, status, 2);
+                if (ok) {
+                    uint8_t* sa = smem + st * STAGE_BYTES + sa_off;
 #pragma unroll
-                    for (int l = 0; l < 4; ++l) {
-                        const uint32_t idx = lds_u16(rw + 2 + 8 * gp + 2 * l);
-                        const uint32_t code = (aux >> (7 * l)) & 127u;
-                        const uint32_t sg = code | ((__popc(code) & 1u) << 7);  // bit 7 makes the number of minus signs even
-                        const uint2 g1 = lut[(idx & 0xFFu) * LUT_REP + (lane & (LUT_REP - 1))];
-                        const uint2 g2 = lut[(idx >> 8) * LUT_REP + (lane & (LUT_REP - 1))];
-                        uint4 v;
-                        v.x = g1.x ^ ((sg * 0x40008000u) & 0x80008000u);
-                        v.y = g1.y ^ ((sg * 0x10002000u) & 0x80008000u);
-                        v.z = g2.x ^ ((sg * 0x04000800u) & 0x80008000u);
-                        v.w = g2.y ^ ((sg * 0x01000200u) & 0x80008000u);
-                        *reinterpret_cast<uint4*>(sa + mt * A_TILE + (((uint32_t)(4 * half + l) ^ (uint32_t)(row & 7)) << 4)) = v;
+                    for (int h = 0; h < 2; ++h) {
+                        const int gp = 2 * j + h;  // sub-block inside the 256-element block
+#pragma unroll
+                        for (int mt = 0; mt < NMAT; ++mt) {
+                            const uint8_t* r = rw[mt];
+                            const uint32_t aux = lds_u16(r + 66 + 4 * gp) | (lds_u16(r + 68 + 4 * gp) << 16);
+                            if (l == 0) scl[((slot0 + h) * NMAT + mt) * TILE_M + row0] = d[mt] * (0.5f + (float)(aux >> 28)) * 0.5f;
+                            const uint32_t idx = lds_u16(r + 2 + 8 * gp + 2 * l);
+                            const uint32_t code = (aux >> l7) & 127u;
+                            const uint32_t sg = code | ((__popc(code) & 1u) << 7);  // bit 7 makes the number of minus signs even
+                            const uint2 g1 = lutl[(idx & 0xFFu) * LUT_REP];
+                            const uint2 g2 = lutl[(idx >> 8) * LUT_REP];
+                            uint4 v;
+                            v.x = g1.x ^ ((sg * 0x40008000u) & 0x80008000u);
+                            v.y = g1.y ^ ((sg * 0x10002000u) & 0x80008000u);
+                            v.z = g2.x ^ ((sg * 0x04000800u) & 0x80008000u);
+                            v.w = g2.y ^ ((sg * 0x01000200u) & 0x80008000u);
+                            *reinterpret_cast<uint4*>(sa + mt * A_TILE + (colb ^ (uint32_t)(h << 6))) = v;
+                        }
+                    }
+                    fence_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
+                    __syncwarp();
+                    if (lane == 0) {
+                        mb_arrive(&full[st]);
+                        mb_arrive(&sfull[slot0]);
+                        mb_arrive(&sfull[slot0 + 1]);
                     }
                 }
-                fence_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
-                __syncwarp();
-                if (lane == 0) {
-                    mb_arrive(&full[st]);
-                    mb_arrive(&sfull[slot]);
-                }
+                fetch(kb + 1, j);
+                ++g;
+                if (++st == STAGES) { st = 0; ph ^= 1u; }
+                slot0 += 2;
+                if (slot0 >= SCL) slot0 = 0;
             }
         }
         cp_async_wait_all();
@@ -388,7 +418,7 @@ grouped_iq3_exact_kernel(const SegDesc* __restrict__ seg, const int32_t* __restr
                 if (elect_one()) {
 #pragma unroll
                     for (int mt = 0; mt < NMAT; ++mt) {
-                        const uint32_t dcol = tmem_base + (uint32_t)(b * NMAT * NT + mt * NT);
+                        const uint32_t dcol = tmem_base + (uint32_t)((b * NMAT + mt) * NT);
                         const uint32_t am = a_lo + (uint32_t)(mt * (A_TILE >> 4));
 #pragma unroll
                         for (int ks = 0; ks < 2; ++ks) {
@@ -410,29 +440,39 @@ grouped_iq3_exact_kernel(const SegDesc* __restrict__ seg, const int32_t* __restr
         const int r = quad * 32 + lane;
         const int mt = NMAT == 2 ? hsel : 0;
         const uint32_t tlane = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(mt * NT);
+        // running sub-block counter of this warp's reads: TMEM buffer, scale slot and their phase parities
+        int b = NMAT == 2 ? 0 : hsel, slot = NMAT == 2 ? 0 : hsel;
+        uint32_t pb = 0, ps = 0;
+        constexpr int STEP = NMAT == 2 ? 1 : 2;
         for (int k = 0; k < my_items && ok; ++k) {
             const Item it = items.get(k);
             float acc[NT];
 #pragma unroll
             for (int j = 0; j < NT; ++j) acc[j] = 0.f;
-            for (int gi = (NMAT == 2 ? 0 : hsel); gi < G && ok; gi += (NMAT == 2 ? 1 : 2)) {
-                const int gc = k * G + gi;
-                const int b = gc % NB, slot = gc % SCL;
-                ok = mb_wait(&sfull[slot], (uint32_t)(gc / SCL) & 1u, status, 3);
+            for (int gi = 0; gi < G; gi += STEP) {
+                ok = mb_wait(&sfull[slot], ps, status, 3);
                 if (!ok) break;
                 const float s = scl[(slot * NMAT + mt) * TILE_M + r];
-                ok = mb_wait(&tfull[b], (uint32_t)(gc / NB) & 1u, status, 3);
+                ok = mb_wait(&tfull[b], pb, status, 3);
                 if (!ok) break;
                 tc_fence_after();
-                float dv[NT];
-                tmem_ld16(tlane + (uint32_t)(b * NMAT * NT), dv);
-                tmem_ld16(tlane + (uint32_t)(b * NMAT * NT + 16), dv + 16);
+                const uint32_t tb = tlane + (uint32_t)(b * NMAT * NT);
+                float dv[16];
+                tmem_ld16(tb, dv);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 16; ++j) acc[j] = fmaf(s, dv[j], acc[j]);
+                tmem_ld16(tb + 16u, dv);
                 tmem_ld_wait();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mb_arrive(&tfree[b]);
 #pragma unroll
-                for (int j = 0; j < NT; ++j) acc[j] = fmaf(s, dv[j], acc[j]);
+                for (int j = 0; j < 16; ++j) acc[16 + j] = fmaf(s, dv[j], acc[16 + j]);
+                b += STEP;
+                if (b >= NB) { b -= NB; pb ^= 1u; }
+                slot += STEP;
+                if (slot >= SCL) { slot -= SCL; ps ^= 1u; }
             }
             if (!ok) break;
             if (hsel == 1) {
@@ -509,7 +549,7 @@ int launch_grouped_exact(dnb_ctx* c, cudaStream_t st, bool fused, const SegDesc*
     const ex::Maps& M = *reinterpret_cast<const ex::Maps*>(maps);
     const dim3 grid(c->sm_count);
     const int nmat = fused ? 2 : 1;
-    const size_t smem = (size_t)ex::STAGES * ex::STAGE_BYTES + 2 * (size_t)nmat * ex::TILE_M * ex::RAW_PITCH +
+    const size_t smem = (size_t)ex::STAGES * ex::STAGE_BYTES + ex::RAWS * (size_t)nmat * ex::TILE_M * ex::RAW_PITCH +
                         (size_t)ex::SCL * nmat * ex::TILE_M * 4 + (size_t)ex::NT * ex::TILE_M * 4 + 256 * ex::LUT_REP * 8 +
                         (2 * ex::STAGES + 2 * ex::NB + ex::SCL + 2) * 8 + 16 + (ex::kMaxSeg + 1) * 4 +
                         ex::kLocalItems * sizeof(ex::Item) + 1024;
