@@ -92,7 +92,7 @@ def recorded_traffic():
     recorded from one profiler capture of each kernel, not measured in this run."""
     src = "recorded constant: dram__bytes_read.sum + dram__bytes_write.sum of one profiler capture of this kernel on this workload"
     return {k: {"dram_bytes": v, "source": src} for k, v in
-            (("decode_gate_up_down", 13474560), ("gemv_gate_up", 8991744),
+            (("decode_block", 17587584), ("decode_gate_up_down", 13474560), ("gemv_gate_up", 8991744),
              ("gemv_down_combine", 4813568), ("router_decode_fused", 4275456))}
 
 

@@ -60,8 +60,8 @@ int launch_prep(dnb_ctx* c, cudaStream_t st, const float* h, const float* w, flo
 // 1085 are the reference GPU forms) -------------------------------------------
 // logits[t][i] = W_r[i] . x_t + bias[i].  One warp per expert row, the row read
 // once as coalesced float4 and applied to up to RT tokens staged in shared memory.
-constexpr int RT = 8;         // tokens per CTA
-constexpr int RROWS = 4;      // warps per CTA
+constexpr int RT = 8;         // tokens per CTA (16 tokens x 16 warps measured slower: 69 us against 62 us per 512-token chunk)
+constexpr int RROWS = 8;      // warps per CTA (they share the staged tokens)
 constexpr int RW = 4;         // expert rows per warp
 __global__ void __launch_bounds__(RROWS * 32)
 router_logits_kernel(const float* __restrict__ x, int nt, int e, const float* __restrict__ w_r,
@@ -86,10 +86,17 @@ router_logits_kernel(const float* __restrict__ x, int nt, int e, const float* __
     for (int r = 0; r < RW; ++r)
 #pragma unroll
         for (int t = 0; t < RT; ++t) acc[r][t] = 0.f;
+    float4 wn[RW];  // the next step's weights: requested a step ahead (the rows come from L2)
+#pragma unroll
+    for (int r = 0; r < RW; ++r) wn[r] = lane < e4 ? __ldg(wr[r] + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
     for (int i = lane; i < e4; i += 32) {
         float4 wv[RW];
 #pragma unroll
-        for (int r = 0; r < RW; ++r) wv[r] = __ldg(wr[r] + i);
+        for (int r = 0; r < RW; ++r) wv[r] = wn[r];
+        if (i + 32 < e4) {
+#pragma unroll
+            for (int r = 0; r < RW; ++r) wn[r] = __ldg(wr[r] + i + 32);
+        }
 #pragma unroll
         for (int t = 0; t < RT; ++t) {
             if (t < ntok) {
