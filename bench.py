@@ -819,7 +819,7 @@ def ep_stack_prefill(cu, oracle, rank, world, local_rank):
             "parity_vs_1gpu": parity}
 
 
-def stack_extras(cu, oracle, device):
+def stack_extras(cu, oracle, device, n_layer=48, batches=(1, 8, 32), prefill=True):
     """Configs 3 and 4: the 48-block stack (identity mixers, h <- h + block(h)).
     Decode: 40 IQ3_XXS + 8 Q4_K layers (every sixth), batch 1 / 8 / 32, one
     dnb_moe_stack_dev call per step (CUDA-graph replay).  Prefill: all-Q4_K layers with
@@ -829,10 +829,11 @@ def stack_extras(cu, oracle, device):
     g4, d4 = expert_bytes(Q4_K)
     ctx = cu.CudaCtx(device)
     try:
-        build_model(ctx, cu, IQ3_XXS, 48, False, ty_of_layer=lambda l: Q4_K if l % 6 == 5 else IQ3_XXS)
-        step_bytes = 40 * (NE * E * 4 + 11 * (2 * g3 + d3)) + 8 * (NE * E * 4 + 11 * (2 * g4 + d4))
+        build_model(ctx, cu, IQ3_XXS, n_layer, False, ty_of_layer=lambda l: Q4_K if l % 6 == 5 else IQ3_XXS)
+        n4 = n_layer // 6
+        step_bytes = (n_layer - n4) * (NE * E * 4 + 11 * (2 * g3 + d3)) + n4 * (NE * E * 4 + 11 * (2 * g4 + d4))
         hbm = peaks()[0]
-        for B in (1, 8, 32):
+        for B in batches:
             h = oracle.synth_normal(SEED, 8100 + B, 1.0, B * E).reshape(B, E)
             d_src = ctx.dev_alloc(h.nbytes)
             d_h = ctx.dev_alloc(h.nbytes)
@@ -852,11 +853,13 @@ def stack_extras(cu, oracle, device):
                 res["algorithmic_bytes_per_step"] = step_bytes
                 res["hbm_gbs"] = step_bytes / (ms * 1e-3) / 1e9
                 res["frac_of_measured_hbm"] = res["hbm_gbs"] / hbm
-            out["config3_decode_stack48_batch%d" % B] = res
+            out["config3_decode_stack%d_batch%d" % (n_layer, B)] = res
             ctx.dev_free(d_src)
             ctx.dev_free(d_h)
     finally:
         ctx.close()
+    if not prefill:
+        return out
     ctx = cu.CudaCtx(device)
     try:
         build_model(ctx, cu, Q4_K, 48, True)
@@ -1018,6 +1021,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-extras", action="store_true", help="skip the config-0/2/3/4 lines")
     ap.add_argument("--no-stack", action="store_true", help="skip the 48-layer stack lines (configs 3 and 4)")
+    ap.add_argument("--stack-only", type=int, default=0, metavar="BATCH",
+                    help="only the decode stack of config 3 at this batch size, with --layers layers (small enough for a profiler capture)")
     ap.add_argument("--gemv-only", action="store_true",
                     help="only the config-0 single-matrix GEMV lines (small enough for a profiler capture)")
     args = ap.parse_args()
@@ -1031,6 +1036,11 @@ def main():
         from denno_beta_b200 import cuda as cu
 
         res = {"config2_q4k_prefill_512": prefill_extras(cu, oracle, local_rank, layers=max(args.layers, 1))}
+    elif args.stack_only:
+        import oracle
+        from denno_beta_b200 import cuda as cu
+
+        res = stack_extras(cu, oracle, local_rank, n_layer=max(args.layers, 1), batches=(args.stack_only,), prefill=False)
     elif args.gemv_only:
         import oracle
         from denno_beta_b200 import cuda as cu
