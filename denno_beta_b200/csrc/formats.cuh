@@ -23,7 +23,7 @@ __device__ __forceinline__ uint32_t ld16(const uint8_t* p) { return *reinterpret
 // Shared lookup tables of the IQ formats (copied into shared memory per CTA).  The kernels
 // pass one pointer; what lies behind it depends on the format.
 // The IQ3_XXS codebook is held kLutRep times, entry i of copy r at word i * kLutRep + r: a
-// lane reads copy (lane & 7), so the 32 random lookups of a warp spread over the banks
+// lane reads copy (lane & (kLutRep - 1)), so the 32 random lookups of a warp spread over the banks
 // instead of piling up on the few banks a single 1 KB table offers them.
 constexpr int kLutRep = 16;
 struct IqLut {
