@@ -117,8 +117,8 @@ struct FusedArgs {
 // Shared memory of the routing phase (ROUTED).
 struct RouteSmem {
     float probs[1024];
-    uint32_t wmax[32];
-    int wcnt[32];
+    uint32_t tmax[128];
+    int wcnt[4];
     uint32_t cand_k[kFdCand];
     int cand_x[kFdCand];
     float red[128];
@@ -169,28 +169,33 @@ __device__ __forceinline__ uint32_t order_key(float v) {  // larger float -> lar
 // softmax + top-k + renorm of the ne logits in global memory (written by all CTAs before the
 // barrier), by the whole CTA.  Leaves the selection ascending in R.ssel, the routing weights in
 // wts_s[0..k).  Every thread of the CTA must call it (it contains CTA-wide barriers).
+// Barrier of the four routing warps (named barrier 6; 1-5 belong to the gate/up groups).
+__device__ __forceinline__ void route_sync() { asm volatile("bar.sync 6, 128;" ::: "memory"); }
+
+// Softmax, top-k and renorm of one token's logits by threads 0..127 of the CTA (the other warps wait at
+// the CTA barrier that follows the call).  Thread v holds entries v, v + 128, ...; every value that
+// depends on evaluation order is computed as in topk_block (moe_kernels.cu), so a token gets the same
+// routing bits as on the other paths.  Six 128-thread barriers: what only one warp did before (the
+// sum's tree, the threshold) every warp now does for itself instead of waiting for a broadcast.
 __device__ __forceinline__ void route_topk(RouteSmem& R, const float* __restrict__ logits, int ne, int k, int norm_topk,
                                            float* wts_s) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    // ---- softmax: threads 0..127, the arithmetic of topk_block (moe_kernels.cu) ----
     float p[8];
     float mx = -INFINITY;
-    if (tid < 128) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const int idx = j * 128 + tid;
-            p[j] = idx < ne ? __ldcg(logits + idx) : -INFINITY;
-            mx = fmaxf(mx, p[j]);
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-        if (lane == 0) R.cmax[warp] = mx;
+    for (int j = 0; j < 8; ++j) {
+        const int idx = j * 128 + tid;
+        p[j] = idx < ne ? __ldcg(logits + idx) : -INFINITY;
+        mx = fmaxf(mx, p[j]);
     }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (lane == 0) R.cmax[warp] = mx;
     if (tid == 0) R.nan_any = 0;
     DNB_STAMP(16);
-    __syncthreads();
-    if (tid < 128) {
-        mx = fmaxf(fmaxf(R.cmax[0], R.cmax[1]), fmaxf(R.cmax[2], R.cmax[3]));
+    route_sync();
+    mx = fmaxf(fmaxf(R.cmax[0], R.cmax[1]), fmaxf(R.cmax[2], R.cmax[3]));
+    {
         float part = 0.f;
         bool any_nan = false;
 #pragma unroll
@@ -205,76 +210,74 @@ __device__ __forceinline__ void route_topk(RouteSmem& R, const float* __restrict
         if (any_nan) R.nan_any = 1;
     }
     DNB_STAMP(17);
-    __syncthreads();
-    if (warp == 0) {
-        float a = (R.red[lane] + R.red[lane + 64]) + (R.red[lane + 32] + R.red[lane + 96]);
+    route_sync();
+    // the tree of topk_block; the xor butterfly leaves the same bits in every lane of every warp
+    float sum = (R.red[lane] + R.red[lane + 64]) + (R.red[lane + 32] + R.red[lane + 96]);
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
-        if (lane == 0) R.bcast = a;
-    }
-    __syncthreads();
-    if (tid < 128) {
-        const float sum = R.bcast;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const int idx = j * 128 + tid;
-            if (idx < ne) R.probs[idx] = sum > 0.f ? p[j] / sum : p[j];
-        }
-    }
-    DNB_STAMP(18);
-    __syncthreads();
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
     const bool has_nan = R.nan_any != 0;
+    uint32_t key[8];
+    uint32_t km = 0u;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int idx = j * 128 + tid;
+        key[j] = 0u;
+        if (idx < ne) {
+            p[j] = sum > 0.f ? p[j] / sum : p[j];
+            R.probs[idx] = p[j];
+            key[j] = order_key(p[j]);
+            km = max(km, key[j]);
+        }
+    }
+    R.tmax[tid] = km;
+    DNB_STAMP(18);
+    route_sync();
     // ---- selection ----
-    // Fast form (no NaN, ne <= 32 * warps): t = the k-th largest of the warp maxima.  At least k
-    // entries reach t, so every one of the top k does; the entries that reach it (a dozen or two)
-    // are ranked among themselves by (value descending, index ascending) -- the CPU scan's rule.
-    const int nchunk = (ne + 31) >> 5;
-    bool fast = !has_nan && nchunk <= kFdWarps && k <= 32;
+    // Fast form (no NaN): the entries fall into 32 classes by index mod 32 (= lane); t = the k-th largest
+    // of the class maxima.  At least k entries reach t, so every one of the top k does; the entries that
+    // reach it (a dozen or two) are ranked among themselves by (value descending, index ascending) -- the
+    // CPU scan's rule.
+    bool fast = !has_nan && k <= 32;
+    int total = 0;
     if (fast) {
-        uint32_t key = 0u;
-        const int kidx = warp * 32 + lane;
-        if (kidx < ne) key = order_key(R.probs[kidx]);
-        if (warp < nchunk) {
-            const uint32_t wm = __reduce_max_sync(0xffffffffu, key);
-            if (lane == 0) R.wmax[warp] = wm;
-        }
-        __syncthreads();
-        uint32_t bal = 0u;
-        bool surv = false;
-        if (warp < nchunk) {
-            const uint32_t v = lane < nchunk ? R.wmax[lane] : 0u;
-            int above = 0;
+        const uint32_t v = max(max(R.tmax[lane], R.tmax[lane + 32]), max(R.tmax[lane + 64], R.tmax[lane + 96]));
+        int above = 0;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) above += (__shfl_sync(0xffffffffu, v, j) > v) ? 1 : 0;
-            uint32_t t = __reduce_min_sync(0xffffffffu, (above < k && v != 0u) ? v : 0xffffffffu);
-            const int have = __popc(__ballot_sync(0xffffffffu, v != 0u));
-            if (have < k) t = 1u;  // fewer maxima than selections: every entry is a candidate
-            surv = key != 0u && key >= t;
-            bal = __ballot_sync(0xffffffffu, surv);
-            if (lane == 0) R.wcnt[warp] = __popc(bal);
+        for (int j = 0; j < 32; ++j) above += (__shfl_sync(0xffffffffu, v, j) > v) ? 1 : 0;
+        uint32_t t = __reduce_min_sync(0xffffffffu, (above < k && v != 0u) ? v : 0xffffffffu);
+        const int have = __popc(__ballot_sync(0xffffffffu, v != 0u));
+        if (have < k) t = 1u;  // fewer maxima than selections: every entry is a candidate
+        uint32_t smask = 0u;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) smask |= (key[j] != 0u && key[j] >= t) ? (1u << j) : 0u;
+        const int cnt = __popc(smask);
+        int incl = cnt;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int u = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += u;
         }
+        if (lane == 31) R.wcnt[warp] = incl;
         DNB_STAMP(19);
-        __syncthreads();
-        int before = 0, total = 0;
-        {
-            const int c = lane < nchunk ? R.wcnt[lane] : 0;
-            int incl = c;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const int v = __shfl_up_sync(0xffffffffu, incl, o);
-                if (lane >= o) incl += v;
-            }
-            total = __shfl_sync(0xffffffffu, incl, 31);
-            before = __shfl_sync(0xffffffffu, incl - c, warp & 31);
+        route_sync();
+        int before = incl - cnt;
+        for (int w2 = 0; w2 < 4; ++w2) {
+            const int c = R.wcnt[w2];
+            if (w2 < warp) before += c;
+            total += c;
         }
         fast = total >= k && total <= kFdCand;
-        if (fast && surv) {
-            const int pos = before + __popc(bal & ((1u << lane) - 1u));
-            R.cand_k[pos] = key;
-            R.cand_x[pos] = kidx;
+        if (fast) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if ((smask >> j) & 1u) {
+                    R.cand_k[before] = key[j];
+                    R.cand_x[before] = j * 128 + tid;
+                    ++before;
+                }
         }
         DNB_STAMP(20);
-        __syncthreads();
+        route_sync();
         if (fast && tid < total) {
             const uint32_t ck = R.cand_k[tid];
             const int cx = R.cand_x[tid];
@@ -333,7 +336,7 @@ __device__ __forceinline__ void route_topk(RouteSmem& R, const float* __restrict
         }
     }
     DNB_STAMP(21);
-    __syncthreads();
+    route_sync();
     if (tid < k) {
         const int mine = R.sel[tid];
         int rank = 0;
@@ -341,23 +344,17 @@ __device__ __forceinline__ void route_topk(RouteSmem& R, const float* __restrict
         R.ssel[rank] = mine;
         R.spv[rank] = R.pv[tid];
     }
-    __syncthreads();
-    if (tid == 0) {
-        float s = 0.f;
-        for (int j = 0; j < k; ++j) s = __fadd_rn(s, R.spv[j]);
-        R.bcast = s;
-    }
-    DNB_STAMP(22);
-    __syncthreads();
+    route_sync();
     if (tid < k) {
-        const float s = R.bcast;
+        float s = 0.f;  // the selected probabilities in ascending expert index, one add at a time
+        for (int j = 0; j < k; ++j) s = __fadd_rn(s, R.spv[j]);
         float w;
         if (!norm_topk) w = R.spv[tid];
         else if (isfinite(s) && s > 0.f) w = R.spv[tid] / s;
         else w = 1.0f / (float)k;
         wts_s[tid] = w;
     }
-    __syncthreads();
+    DNB_STAMP(22);
 }
 
 // Dynamic shared memory:
@@ -511,7 +508,7 @@ __global__ void __maxnreg__(ROUTED ? 80 : 64) decode_fused_kernel(const FusedArg
         ready = flags[1] != 0 && ready;
         // Every CTA ranks the logits itself.  (After a failed wait the host discards the call; the
         // selection below then runs on whatever is there, and every index stays in range.)
-        route_topk(*R, A.logits + (size_t)(blockIdx.x % kActRep) * A.ne, A.ne, A.k, A.norm_topk, ws);
+        if (tid < 128) route_topk(*R, A.logits + (size_t)(blockIdx.x % kActRep) * A.ne, A.ne, A.k, A.norm_topk, ws);
         DNB_STAMP(7);
         if (tid < A.k) {
             int ex = R->ssel[tid];

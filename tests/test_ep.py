@@ -63,10 +63,11 @@ def test_expert_parallel_equals_single_gpu():
 
 
 @pytest.mark.gpu
-def test_peer_memory_path_on_one_gpu():
+@pytest.mark.parametrize("ty_name", ["Q4_K", "IQ3_XXS"])
+def test_peer_memory_path_on_one_gpu(ty_name):
     """World of one: the dispatch, the tables, the down epilogue's row destinations and the
     flags all run against the rank's own arena.  The block must equal the ordinary
-    single-GPU block bit for bit."""
+    single-GPU block bit for bit (Q4_K: three-product tcgen05 kernel; IQ3_XXS: exact-weight kernel)."""
     import numpy as np
 
     import oracle as orc
@@ -77,7 +78,7 @@ def test_peer_memory_path_on_one_gpu():
     c = cu.CudaCtx(0)
     try:
         assert c.moe_config(1, e, ff, ne, k)
-        make_layer(orc, c, 0, orc.Q4_K, e, ff, ne, k, bias=True, gate_row=True)
+        make_layer(orc, c, 0, getattr(orc, ty_name), e, ff, ne, k, bias=True, gate_row=True)
         h = orc.synth_normal(SEED, 7702, 1.0, nt * e).reshape(nt, e)
         want = c.moe_block(0, h)
         pm = ep.PeerMemoryExpertParallel(c, max_tokens=64, rank=0, world=1)
