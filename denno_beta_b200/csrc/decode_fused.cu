@@ -446,10 +446,9 @@ __global__ void __maxnreg__(ROUTED ? 80 : 64) decode_fused_kernel(const FusedArg
             if (lane == 0) R->red[warp] = ss;
         }
         __syncthreads();
-        if (A.norm_w && tid == 0) R->inv = 1.0f / sqrtf(((R->red[0] + R->red[1]) + (R->red[2] + R->red[3])) / (float)e + A.eps);
-        __syncthreads();
         {
-            const float inv = A.norm_w ? R->inv : 1.0f;
+            // every thread evaluates the same expression on the same four partial sums: no broadcast, no second barrier
+            const float inv = A.norm_w ? 1.0f / sqrtf(((R->red[0] + R->red[1]) + (R->red[2] + R->red[3])) / (float)e + A.eps) : 1.0f;
             for (int i = 2 * tid; i < e; i += 2 * kFdThreads) {
                 float2 v = *reinterpret_cast<const float2*>(hbuf + i);
                 if (A.norm_w) {

@@ -157,36 +157,40 @@ ep_offsets_kernel(const EpArena* mine, int ne, int n_local, int world, int me, u
     for (int e = tid; e < ne; e += blockDim.x) base[e] = tot[e] + mine_off[e];
 }
 
-// One CTA per row i = t*k+slot: split x[t] to bf16 hi/lo and store it as row base[expert] + j
-// of the owner's operand buffers; the last CTA to finish raises the data flag at every peer.
+// Rows i = t*k+slot, dealt to the CTAs round-robin: split x[t] to bf16 hi/lo and store it as row
+// base[expert] + j of the owner's operand buffers; the last CTA to finish raises the data flag at every
+// peer.  A CTA walks many rows and fences once at the end: the kernel runs beside the shared expert's
+// GEMM, which leaves room for about one of these CTAs per SM, and with a CTA (and a system-wide fence,
+// i.e. an NVLink round trip) per row the 4,096 rows of a chunk went out at a third of the link rate.
 __global__ void __launch_bounds__(256)
 ep_dispatch_kernel(const float* __restrict__ x, const int32_t* __restrict__ sels, const int32_t* __restrict__ send_row,
                    const int32_t* __restrict__ base, int k, int e, int n_local, int world, int me, int rows_total,
-                   uint32_t seq, EpPeers peers, unsigned int* ticket, int* status) {
-    const int i = blockIdx.x, tid = threadIdx.x;
-    const int ex = sels[i], j = send_row[i];
-    if (ex >= 0 && j >= 0) {
+                   int n_rows, uint32_t seq, EpPeers peers, unsigned int* ticket, int* status) {
+    const int tid = threadIdx.x;
+    for (int i = blockIdx.x; i < n_rows; i += gridDim.x) {
+        const int ex = sels[i], j = send_row[i];
+        if (ex < 0 || j < 0) continue;
         const size_t r = (size_t)base[ex] + j;
         if (r >= (size_t)rows_total) {
             if (tid == 0) status_set(status, 20);
-        } else {
-            const int d = ex / n_local;
-            const float* xr = x + (size_t)(i / k) * e;
-            uint16_t* hi = peers.xg_hi[d] + r * e;
-            uint16_t* lo = peers.xg_lo[d] + r * e;
-            for (int c = tid * 8; c < e; c += 2048) {  // 16-byte stores: the peer write is NVLink traffic
-                const float4 v = *reinterpret_cast<const float4*>(xr + c);
-                const float4 u = *reinterpret_cast<const float4*>(xr + c + 4);
-                uint32_t h0, l0, h1, l1, h2, l2, h3, l3;
-                ep_split2(v.x, v.y, h0, l0);
-                ep_split2(v.z, v.w, h1, l1);
-                ep_split2(u.x, u.y, h2, l2);
-                ep_split2(u.z, u.w, h3, l3);
-                *reinterpret_cast<uint4*>(hi + c) = make_uint4(h0, h1, h2, h3);
-                *reinterpret_cast<uint4*>(lo + c) = make_uint4(l0, l1, l2, l3);
-            }
-            if (tid == 0) peers.recv_slot[d][r] = (me << 24) | i;  // who owns the token, and which (token, slot) row
+            continue;
         }
+        const int d = ex / n_local;
+        const float* xr = x + (size_t)(i / k) * e;
+        uint16_t* hi = peers.xg_hi[d] + r * e;
+        uint16_t* lo = peers.xg_lo[d] + r * e;
+        for (int c = tid * 8; c < e; c += 2048) {  // 16-byte stores: the peer write is NVLink traffic
+            const float4 v = *reinterpret_cast<const float4*>(xr + c);
+            const float4 u = *reinterpret_cast<const float4*>(xr + c + 4);
+            uint32_t h0, l0, h1, l1, h2, l2, h3, l3;
+            ep_split2(v.x, v.y, h0, l0);
+            ep_split2(v.z, v.w, h1, l1);
+            ep_split2(u.x, u.y, h2, l2);
+            ep_split2(u.z, u.w, h3, l3);
+            *reinterpret_cast<uint4*>(hi + c) = make_uint4(h0, h1, h2, h3);
+            *reinterpret_cast<uint4*>(lo + c) = make_uint4(l0, l1, l2, l3);
+        }
+        if (tid == 0) peers.recv_slot[d][r] = (me << 24) | i;  // who owns the token, and which (token, slot) row
     }
     __threadfence_system();
     __syncthreads();
@@ -448,8 +452,10 @@ extern "C" int dnb_ep_block_dev(dnb_ctx* c, int layer, const float* h_dev, int n
     DNB_CUDA(cudaStreamWaitEvent(c->side, c->ev_fork, 0));
     {
         ProfScope p_(c, c->side, "ep_dispatch");
-        ep_dispatch_kernel<<<nt * M.k, 256, 0, c->side>>>(w.xn, w.sels, s->send_row, s->base, M.k, M.e, s->n_local, s->world,
-                                                         s->rank, s->rows_total, seq, s->peers, s->ticket, c->status);
+        const int n_rows = nt * M.k;
+        const int ctas = n_rows < 4 * c->sm_count ? n_rows : 4 * c->sm_count;
+        ep_dispatch_kernel<<<ctas, 256, 0, c->side>>>(w.xn, w.sels, s->send_row, s->base, M.k, M.e, s->n_local, s->world,
+                                                     s->rank, s->rows_total, n_rows, seq, s->peers, s->ticket, c->status);
     }
     DNB_CUDA(cudaEventRecord(c->ev_join, c->side));
     c->launches += 3;
