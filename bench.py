@@ -296,7 +296,9 @@ def run_ours(args, rank, world, local_rank):
         "roofline": {"bound": "hbm", "kernel": top, "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
                      "frac": achieved / hbm_peak, "peak_kind": peak_kind, "traffic": ncu_traffic.get(top, {}).get("dram_bytes"),
                      "traffic_source": ncu_traffic.get(top, {}).get("source", "none recorded for this kernel"),
-                     "bytes_per_launch": alg[top], "us_per_launch": per_launch_s * 1e6},
+                     "bytes_per_launch": alg[top], "us_per_launch": per_launch_s * 1e6,
+                     "how": "launches separated by events behind a GPU stall (no overlap between neighbouring launches); "
+                            "back to back in the timed region a launch takes ms_per_step, see block_hbm_gbs"},
         "block_hbm_gbs": block_bytes / (ms_dev / K_ * 1e-3) / 1e9,
         "kernels_ms": {k: round(v["ms"], 4) for k, v in prof.items()},
     }
