@@ -104,6 +104,41 @@ def peaks():
     return 6650.0, 1590.0, "fallback"
 
 
+def placed_zipf_bias(rb, shards=8):
+    """The same Zipf bias values, assigned to expert indices so that contiguous shards of NE / shards experts
+    carry about equal expected load (and so do unions of adjacent shards: 4 or 2 GPUs).  Expert placement by
+    expected load, decided at load time from the router bias alone: experts are taken in descending bias
+    (rank r, expected share of a chunk's tokens ~ 1 - exp(-5.5 (r + 1)^-1.1): the hottest experts are chosen by
+    nearly every token, so their load saturates) and each goes to the least loaded shard that still has room.
+    Which expert is hot is arbitrary in a synthetic model; a deployment would permute the expert tensors and
+    the router rows the same way."""
+    ne = rb.size
+    order = np.argsort(-rb, kind="stable")          # expert indices by descending bias
+    w = 1.0 - np.exp(-5.5 * (np.arange(ne) + 1.0) ** -1.1)
+    cap = ne // shards
+    load = np.zeros(shards)
+    members = [[] for _ in range(shards)]
+    for r in range(ne):
+        free = [s_ for s_ in range(shards) if len(members[s_]) < cap]
+        s_ = min(free, key=lambda q: (load[q], q))
+        members[s_].append(r)
+        load[s_] += w[r]
+    out = np.empty_like(rb)
+    vals = rb[order]
+    for s_ in range(shards):
+        for j, r in enumerate(members[s_]):
+            out[s_ * cap + j] = vals[r]
+    return out
+
+
+def router_bias(oracle, l, bias):
+    """bias: False = none, True = the seeded Zipf bias, "placed" = the same values placed by expected load."""
+    if not bias:
+        return None
+    rb = oracle.synth_zipf_bias(SEED, l * 16 + 7, 1.1, NE)
+    return placed_zipf_bias(rb) if bias == "placed" else rb
+
+
 def build_model(ctx, cu, ty, layers, bias, ty_of_layer=None):
     """Expert tables filled on the device; routers (small) from the host generator."""
     import oracle  # only its seeded host generator is used here (inputs, not results)
@@ -119,7 +154,7 @@ def build_model(ctx, cu, ty, layers, bias, ty_of_layer=None):
         assert ctx.synth_experts(l, cu.SHARED_UP, ty, E, FF, 1, SEED)
         assert ctx.synth_experts(l, cu.SHARED_DOWN, ty, FF, E, 1, SEED)
         rw = oracle.synth_normal(SEED, l * 16 + 6, 0.02, NE * E)
-        rb = oracle.synth_zipf_bias(SEED, l * 16 + 7, 1.1, NE) if bias else None
+        rb = router_bias(oracle, l, bias)
         ctx.register_router(l, rw, rb, np.ones(E, np.float32), None)
     ctx.sync()
 
@@ -331,7 +366,7 @@ def build_shard(ctx, cu, oracle, ty_of_layer, layers, rank, world, bias):
                                (cu.SHARED_GATE, (E, FF, 1)), (cu.SHARED_UP, (E, FF, 1)), (cu.SHARED_DOWN, (FF, E, 1))):
             assert ctx.synth_experts(l, m, ty, ni, no, n, SEED)
         rw = oracle.synth_normal(SEED, l * 16 + 6, 0.02, NE * E)
-        rb = oracle.synth_zipf_bias(SEED, l * 16 + 7, 1.1, NE) if bias else None
+        rb = router_bias(oracle, l, bias)
         ctx.register_router(l, rw, rb, np.ones(E, np.float32), None)
     ctx.sync()
 
@@ -605,6 +640,9 @@ def guarded_ep_extras(partial, cu, oracle, rank, world, local_rank, limit_s=600.
         out = {"config3_decode_stack48_expert_parallel": ep_decode_stack(cu, oracle, rank, world, local_rank)}
         out["config2_q4k_prefill_512_expert_parallel"] = ep_prefill_extras(cu, oracle, rank, world, local_rank)
         out["config4_prefill_stack48_14018_expert_parallel"] = ep_stack_prefill(cu, oracle, rank, world, local_rank)
+        # the same two with the hot experts placed by expected load instead of where the seed put them
+        out["config2_q4k_prefill_512_expert_parallel_placed"] = ep_prefill_extras(cu, oracle, rank, world, local_rank, "placed")
+        out["config4_prefill_stack48_14018_expert_parallel_placed"] = ep_stack_prefill(cu, oracle, rank, world, local_rank, "placed")
     except Exception as ex:  # the other ranks run into their own watchdog
         bail("expert-parallel extras failed on rank %d: %s" % (rank, ex))
     timer.cancel()
@@ -673,7 +711,7 @@ def ep_decode_stack(cu, oracle, rank, world, local_rank):
     return out
 
 
-def ep_prefill_extras(cu, oracle, rank, world, local_rank):
+def ep_prefill_extras(cu, oracle, rank, world, local_rank, bias=True):
     """Config 2 across `world` GPUs, expert parallel: 512/world experts per GPU (the same weights as the
     single-GPU line), the 512-token chunk split evenly over the ranks (strong scaling), or one chunk per
     rank.  Timed with events on the block's stream, max over ranks.  Rank 0 also holds the whole layer
@@ -686,7 +724,7 @@ def ep_prefill_extras(cu, oracle, rank, world, local_rank):
     layers, nt_total = 4, 512
     nl, nt = NE // world, nt_total // world
     ctx = cu.CudaCtx(local_rank)
-    build_shard(ctx, cu, oracle, lambda l: Q4_K, layers, rank, world, True)
+    build_shard(ctx, cu, oracle, lambda l: Q4_K, layers, rank, world, bias)
     h_all = oracle.synth_normal(SEED, 8000, 1.0, nt_total * E).reshape(nt_total, E)
 
     def timed(step, reps=16):
@@ -727,7 +765,7 @@ def ep_prefill_extras(cu, oracle, rank, world, local_rank):
     parity = None
     if rank == 0:
         one = cu.CudaCtx(local_rank)
-        build_shard(one, cu, oracle, lambda l: Q4_K, 1, 0, 1, True)
+        build_shard(one, cu, oracle, lambda l: Q4_K, 1, 0, 1, bias)
         d1, d2 = one.dev_alloc(h_all.nbytes), one.dev_alloc(h_all.nbytes)
         one.upload(d1, h_all)
         assert one.moe_block_dev(0, d1, nt_total, d2)
@@ -759,10 +797,11 @@ def ep_prefill_extras(cu, oracle, rank, world, local_rank):
     out["device_status"] = ctx.device_status()
     dist.barrier()
     ctx.close()
+    out["placement"] = "hot experts placed by expected load (placed_zipf_bias)" if bias == "placed" else "experts where the seed put them"
     return out
 
 
-def ep_stack_prefill(cu, oracle, rank, world, local_rank):
+def ep_stack_prefill(cu, oracle, rank, world, local_rank, bias=True):
     """Config 4 across `world` GPUs: 48 all-Q4_K blocks (the single-GPU line's weights), a 14,018-token
     prompt in 512-token chunks (27 x 512 + 194) dealt to the ranks round-robin, every chunk-step through
     all 48 layers with the peer-memory exchange and the identity mixers' residual add (dnb_ep_stack_dev,
@@ -778,7 +817,7 @@ def ep_stack_prefill(cu, oracle, rank, world, local_rank):
     steps = (len(chunks) + world - 1) // world
     mine = [chunks[st * world + rank] if st * world + rank < len(chunks) else 1 for st in range(steps)]  # idle rank: 1 dummy token
     ctx = cu.CudaCtx(local_rank)
-    build_shard(ctx, cu, oracle, lambda l: Q4_K, n_layer, rank, world, True)
+    build_shard(ctx, cu, oracle, lambda l: Q4_K, n_layer, rank, world, bias)
     pm = ep.PeerMemoryExpertParallel(ctx, max_tokens=512)
     h = oracle.synth_normal(SEED, 8200, 1.0, 512 * E).reshape(512, E)  # every chunk reuses these rows, as on one GPU
     d_src = ctx.dev_alloc(h.nbytes)
@@ -798,7 +837,7 @@ def ep_stack_prefill(cu, oracle, rank, world, local_rank):
     got = ctx.download(d_h, np.empty((512, E), np.float32))[:mine[-1]]
     if rank == 0:
         one = cu.CudaCtx(local_rank)
-        build_model(one, cu, Q4_K, n_layer, True)
+        build_model(one, cu, Q4_K, n_layer, bias)
         d1 = one.dev_alloc(h.nbytes)
         one.upload(d1, h)
         assert one.moe_stack_dev(d1, mine[-1])
@@ -815,7 +854,8 @@ def ep_stack_prefill(cu, oracle, rank, world, local_rank):
     status = ctx.device_status()
     dist.barrier()
     ctx.close()
-    return {"seconds": ms * 1e-3, "tok_per_s": n_tok / (ms * 1e-3), "chunk_steps": steps, "chunks": len(chunks),
+    return {"placement": "hot experts placed by expected load (placed_zipf_bias)" if bias == "placed" else "experts where the seed put them",
+            "seconds": ms * 1e-3, "tok_per_s": n_tok / (ms * 1e-3), "chunk_steps": steps, "chunks": len(chunks),
             "algorithmic_tflops": n_tok * n_layer * (11 * 6291456 + 2097152) / (ms * 1e-3) / 1e12,
             "exchange": "peer memory (dnb_ep_stack_dev), chunks dealt round-robin to %d GPUs" % world, "device_status": status,
             "parity_vs_1gpu": parity}
