@@ -813,9 +813,15 @@ def ep_stack_prefill(cu, oracle, rank, world, local_rank, bias=True):
     from denno_beta_b200 import ep
 
     n_layer, n_tok = 48, 14018
-    chunks = [512] * (n_tok // 512) + ([n_tok % 512] if n_tok % 512 else [])
-    steps = (len(chunks) + world - 1) // world
-    mine = [chunks[st * world + rank] if st * world + rank < len(chunks) else 1 for st in range(steps)]  # idle rank: 1 dummy token
+    # 512-token chunks dealt round-robin in waves of `world`; the tokens that do not fill a whole wave (1,730 of
+    # 14,018 at 8 GPUs: three chunks and the 194-token rest) are cut into `world` equal chunks instead, so the
+    # last wave keeps every GPU busy.  A token's result does not depend on the chunk it is in.
+    waves = (n_tok // 512) // world
+    rest = n_tok - waves * world * 512
+    tail = [rest // world + (1 if r_ < rest % world else 0) for r_ in range(world)] if rest else []
+    chunks = [512] * (waves * world) + [t_ for t_ in tail if t_ > 0]
+    steps = waves + (1 if rest else 0)
+    mine = [512] * waves + ([max(tail[rank], 1)] if rest else [])  # a rank with nothing in the tail runs 1 dummy token
     ctx = cu.CudaCtx(local_rank)
     build_shard(ctx, cu, oracle, lambda l: Q4_K, n_layer, rank, world, bias)
     pm = ep.PeerMemoryExpertParallel(ctx, max_tokens=512)
@@ -857,7 +863,7 @@ def ep_stack_prefill(cu, oracle, rank, world, local_rank, bias=True):
     return {"placement": "hot experts placed by expected load (placed_zipf_bias)" if bias == "placed" else "experts where the seed put them",
             "seconds": ms * 1e-3, "tok_per_s": n_tok / (ms * 1e-3), "chunk_steps": steps, "chunks": len(chunks),
             "algorithmic_tflops": n_tok * n_layer * (11 * 6291456 + 2097152) / (ms * 1e-3) / 1e12,
-            "exchange": "peer memory (dnb_ep_stack_dev), chunks dealt round-robin to %d GPUs" % world, "device_status": status,
+            "exchange": "peer memory (dnb_ep_stack_dev), 512-token chunks dealt round-robin to %d GPUs, the last partial wave cut into equal chunks" % world, "device_status": status,
             "parity_vs_1gpu": parity}
 
 
