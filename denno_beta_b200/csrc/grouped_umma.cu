@@ -24,8 +24,8 @@
 //
 // Operands.
 //   A (weights): sixteen producer warps dequantise Q4_K bytes straight from global
-//      memory (raw bytes prefetched in registers two steps ahead, the whole next tile
-//      prefetched into L2), split to hi/lo bf16 and store the tiles in the K-major
+//      memory (raw bytes prefetched in registers two steps ahead), split to hi/lo bf16
+//      and store the tiles in the K-major
 //      128-byte-swizzled layout the MMA reads.
 //   B (activations): a pre-pass gathers the routed token rows into the expert-major
 //      packed order and splits them into hi/lo bf16 buffers once per layer; the
@@ -211,12 +211,6 @@ __device__ __forceinline__ bool elect_one() {
 // A flag the whole warp agrees on (and the compiler knows it does).
 __device__ __forceinline__ bool warp_all(bool v) { return __all_sync(0xffffffffu, v); }
 
-// Ask L2 to fetch `bytes` (a multiple of 16) from a 16-byte aligned address; no register,
-// no shared memory, nothing to wait for.
-__device__ __forceinline__ void prefetch_l2(const void* p, uint32_t bytes) {
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
-}
-
 // A work item of the persistent kernel: which segment, which 128 tokens of it, which
 // 128 weight rows.
 struct Item {
@@ -289,22 +283,14 @@ __device__ __forceinline__ bool produce(const ProducerArgs& a, int w8, int lane)
     int f_left = a.my_items, f_k = 0, f_c = GRP;  // fetch cursor: item (CTA-local index) and chunk
     const uint8_t* f_pa = nullptr;
     const uint8_t* f_pb = nullptr;
-    // One thread per weight row asks L2 for the whole row of an item a full item ahead of
-    // its use: the register prefetch below then hits L2, and the bytes in flight towards
-    // HBM are a tile (36-147 KB per matrix), not a few chunks.
-    auto l2_prefetch_item = [&](int k) {
-        if (GRP == 0 && p == 0 && k < a.my_items) {
-            const Item it = a.items.get(k);
-            prefetch_l2(it.wa + (size_t)(it.r0 + r) * a.rb, (uint32_t)a.rb);
-            if constexpr (NMAT == 2) prefetch_l2(it.wb + (size_t)(it.r0 + r) * a.rb, (uint32_t)a.rb);
-        }
-    };
+    // (Asking L2 for the next item's rows a full item ahead with cp.async.bulk.prefetch.L2 was measured: the same
+    // kernel time with and without, and 1.9x the DRAM traffic with, because most prefetched lines were gone again
+    // by the time they were needed.  The register prefetch two chunks ahead covers the latency by itself.)
     auto f_open = [&]() {
         if (f_left > 0) {
             const Item it = a.items.get(f_k);
             f_pa = it.wa + (size_t)(it.r0 + r) * a.rb;
             if constexpr (NMAT == 2) f_pb = it.wb + (size_t)(it.r0 + r) * a.rb;
-            l2_prefetch_item(f_k + 1);
         }
     };
     auto fetch = [&](Raw& q) {
@@ -325,7 +311,6 @@ __device__ __forceinline__ bool produce(const ProducerArgs& a, int w8, int lane)
             f_open();
         }
     };
-    l2_prefetch_item(0);
     f_open();
     fetch(buf[0]);
     fetch(buf[1]);
