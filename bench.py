@@ -568,14 +568,14 @@ def extras(ctx, cu, oracle):
     return out
 
 
-def prefill_extras(cu, oracle, device, layers=4):
+def prefill_extras(cu, oracle, device, layers=4, ty=Q4_K):
     """Config 2: one MoE block, one 512-token chunk, Q4_K experts, Zipf router bias.
     Rotates over `layers` layer copies (0.9 GB of weights each); tokens stay on the device."""
     nt = 512
     ctx = cu.CudaCtx(device)
     out = {}
     try:
-        build_model(ctx, cu, Q4_K, layers, True)
+        build_model(ctx, cu, ty, layers, True)
         h = oracle.synth_normal(SEED, 8000, 1.0, nt * E).reshape(nt, E)
         d_h = ctx.dev_alloc(h.nbytes)
         d_o = ctx.dev_alloc(h.nbytes)
@@ -599,7 +599,7 @@ def prefill_extras(cu, oracle, device, layers=4):
         counts = np.bincount(sels.ravel(), minlength=NE)
         active = int((counts > 0).sum())
         flops = 2.0 * 3 * E * FF * (nt * K + nt) + 2.0 * nt * NE * E
-        g_b, d_b = expert_bytes(Q4_K)
+        g_b, d_b = expert_bytes(ty)
         bytes_ = (active + 1) * (2 * g_b + d_b) + NE * E * 4 + 2 * nt * E * 4
         hbm, tf, _ = peaks()
         out = {"ms_per_chunk_layer": ms, "tok_per_s_layer": nt / (ms * 1e-3), "algorithmic_tflops": flops / (ms * 1e-3) / 1e12,
@@ -1069,6 +1069,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-extras", action="store_true", help="skip the config-0/2/3/4 lines")
     ap.add_argument("--no-stack", action="store_true", help="skip the 48-layer stack lines (configs 3 and 4)")
+    ap.add_argument("--prefill-type", default="q4k", choices=["q4k", "iq3xxs"],
+                    help="block format of --prefill-only (config 2 is Q4_K; IQ3_XXS runs the exact-weight tcgen05 kernel)")
     ap.add_argument("--stack-only", type=int, default=0, metavar="BATCH",
                     help="only the decode stack of config 3 at this batch size, with --layers layers (small enough for a profiler capture)")
     ap.add_argument("--gemv-only", action="store_true",
@@ -1083,7 +1085,8 @@ def main():
         import oracle
         from denno_beta_b200 import cuda as cu
 
-        res = {"config2_q4k_prefill_512": prefill_extras(cu, oracle, local_rank, layers=max(args.layers, 1))}
+        res = {"config2_%s_prefill_512" % args.prefill_type: prefill_extras(
+            cu, oracle, local_rank, layers=max(args.layers, 1), ty=Q4_K if args.prefill_type == "q4k" else IQ3_XXS)}
     elif args.stack_only:
         import oracle
         from denno_beta_b200 import cuda as cu

@@ -23,8 +23,8 @@
 // tile width, so a token's result does not depend on which tokens share its chunk.
 //
 // Operands.
-//   A (weights): sixteen producer warps dequantise Q4_K bytes straight from global
-//      memory (raw bytes prefetched in registers two steps ahead), split to hi/lo bf16
+//   A (weights): sixteen producer warps dequantise Q4_K bytes (each thread's next 16 qs bytes
+//      per matrix arrive by cp.async in a private shared-memory slot), split to hi/lo bf16
 //      and store the tiles in the K-major
 //      128-byte-swizzled layout the MMA reads.
 //   B (activations): a pre-pass gathers the routed token rows into the expert-major
@@ -189,18 +189,19 @@ __device__ __forceinline__ void dequant_q4k_task(const uint4& hdr, const uint4& 
     }
 }
 
-// Weight loads of the producers, as volatile asm so that they are issued where they are
-// written (two chunks ahead of their use) instead of being sunk towards the use.
-__device__ __forceinline__ uint4 ld_weights_stream(const void* p) {  // read once: do not keep in L1
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
-}
+// Block-header load of the producers, as volatile asm so that it is issued where it is
+// written (a block ahead of its use) instead of being sunk towards the use.
 __device__ __forceinline__ uint4 ld_weights_keep(const void* p) {  // shared by the row's four threads
     uint4 v;
     asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
 }
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
 // One lane of a converged warp.
 __device__ __forceinline__ bool elect_one() {
@@ -260,6 +261,7 @@ __device__ __forceinline__ float swiglu_fast(float g, float u) { return __fdivid
 struct ProducerArgs {
     ItemTab items;
     uint8_t* smem;
+    uint8_t* rawq;   // [16 producer warps][32 lanes][NMAT] x 16 bytes: every thread's slot for its next chunk
     uint64_t* full;
     uint64_t* empty;
     int* status;
@@ -278,14 +280,16 @@ __device__ __forceinline__ bool produce(const ProducerArgs& a, int w8, int lane)
     const int r = w8 * 16 + (lane & 15), p = lane >> 4;
     struct Raw { uint4 qa, qb; };   // one chunk's 16 qs bytes per matrix
     struct Hdr { uint4 ha, hb; };   // one block's d, dmin and scale bytes per matrix
-    Raw buf[2];
+    Raw cur;                        // the chunk being dequantised
     Hdr hdr_cur, hdr_next;
+    // The thread's private 16 bytes per matrix in shared memory: the NEXT chunk's qs bytes arrive there by cp.async.
+    uint4* slot = reinterpret_cast<uint4*>(a.rawq) + (size_t)((GRP * (PWARPS / 2) + w8) * 32 + lane) * NMAT;
     int f_left = a.my_items, f_k = 0, f_c = GRP;  // fetch cursor: item (CTA-local index) and chunk
     const uint8_t* f_pa = nullptr;
     const uint8_t* f_pb = nullptr;
     // (Asking L2 for the next item's rows a full item ahead with cp.async.bulk.prefetch.L2 was measured: the same
     // kernel time with and without, and 1.9x the DRAM traffic with, because most prefetched lines were gone again
-    // by the time they were needed.  The register prefetch two chunks ahead covers the latency by itself.)
+    // by the time they were needed.)
     auto f_open = [&]() {
         if (f_left > 0) {
             const Item it = a.items.get(f_k);
@@ -293,16 +297,24 @@ __device__ __forceinline__ bool produce(const ProducerArgs& a, int w8, int lane)
             if constexpr (NMAT == 2) f_pb = it.wb + (size_t)(it.r0 + r) * a.rb;
         }
     };
-    auto fetch = [&](Raw& q) {
-        if (f_left <= 0) return;
+    // Request the fetch cursor's chunk.  The qs bytes travel by cp.async into the thread's slot and are picked up
+    // with cp.async.wait_group: with plain loads held in registers two chunks ahead, a wait for the older request
+    // also waited for the younger one, and these stalls were 40 % of the kernel (measured by leaving the loads out).
+    // The block header (one load per block, used a whole block later) stays a plain load.
+    auto fetch = [&]() {
+        if (f_left <= 0) {
+            cp_async_commit();
+            return;
+        }
         const int off = (f_c >> 2) * 144;
         if ((f_c & 3) == GRP) {  // the group's first chunk of a block: fetch the block header too
             hdr_next.ha = ld_weights_keep(f_pa + off);
             if constexpr (NMAT == 2) hdr_next.hb = ld_weights_keep(f_pb + off);
         }
         const int qoff = off + 16 + 32 * (f_c & 3) + 16 * p;
-        q.qa = ld_weights_stream(f_pa + qoff);
-        if constexpr (NMAT == 2) q.qb = ld_weights_stream(f_pb + qoff);
+        cp_async16(slot, f_pa + qoff);
+        if constexpr (NMAT == 2) cp_async16(slot + 1, f_pb + qoff);
+        cp_async_commit();
         f_c += 2;
         if (f_c >= a.nchunks) {
             f_c = GRP;
@@ -311,9 +323,17 @@ __device__ __forceinline__ bool produce(const ProducerArgs& a, int w8, int lane)
             f_open();
         }
     };
+    auto take = [&]() {  // the chunk requested last has landed: into registers, and the slot is free again
+        cp_async_wait_all();
+        cur.qa = slot[0];
+        if constexpr (NMAT == 2) cur.qb = slot[1];
+    };
+    // Two chunks of the group are in flight: one in `cur`, one on its way into the slot.  (A third, held in a
+    // second register buffer, measured no faster.)
     f_open();
-    fetch(buf[0]);
-    fetch(buf[1]);
+    fetch();
+    take();
+    fetch();
     bool ok = true;
     const int total = a.my_items * a.nchunks;  // a multiple of 4: n_in % 256 == 0
     for (int g4 = 0; g4 < total && ok; g4 += 4) {
@@ -327,21 +347,20 @@ __device__ __forceinline__ bool produce(const ProducerArgs& a, int w8, int lane)
             if (ok && g >= STAGES) ok = mb_wait(&a.empty[st], ph ^ 1u, a.status, 2);
             if (ok) {
                 uint8_t* sa = a.smem + st * STAGE_BYTES;
-                // The chunk's bytes were requested two steps ago.  The next request is
-                // issued only after they have been consumed: a wait on a load must never
-                // also cover a load issued just before it.
 #pragma unroll
                 for (int nh = 0; nh < 2; ++nh) {
-                    dequant_q4k_task(hdr_cur.ha, buf[i].qa, j, nh, p, sa, sa + A_TILE, r);
-                    if constexpr (NMAT == 2) dequant_q4k_task(hdr_cur.hb, buf[i].qb, j, nh, p, sa + 2 * A_TILE, sa + 3 * A_TILE, r);
+                    dequant_q4k_task(hdr_cur.ha, cur.qa, j, nh, p, sa, sa + A_TILE, r);
+                    if constexpr (NMAT == 2) dequant_q4k_task(hdr_cur.hb, cur.qb, j, nh, p, sa + 2 * A_TILE, sa + 3 * A_TILE, r);
                 }
-                fetch(buf[i]);
+                take();   // the group's next chunk, requested one chunk of work ago
+                fetch();  // and the one after it
                 fence_async_smem();   // generic-proxy stores -> visible to the tensor core's async proxy
                 __syncwarp();
                 if (lane == 0) mb_arrive(&a.full[st]);
             }
         }
     }
+    cp_async_wait_all();
     return ok;
 }
 
@@ -435,7 +454,7 @@ grouped_q4k_umma_kernel(const SegDesc* __restrict__ seg, const int32_t* __restri
 
     if (warp < PWARPS) {
         // ---------------- producers ----------------
-        ProducerArgs pa{items, smem, full, empty, status, my_items, nchunks, rb};
+        ProducerArgs pa{items, smem, reinterpret_cast<uint8_t*>(itab + kLocalItems), full, empty, status, my_items, nchunks, rb};
         if (warp < PWARPS / 2) ok = produce<NMAT, STAGES, STAGE_BYTES, 0>(pa, warp, lane);
         else ok = produce<NMAT, STAGES, STAGE_BYTES, 1>(pa, warp - PWARPS / 2, lane);
     } else if (warp == W_TMA) {
@@ -659,14 +678,16 @@ int launch_grouped_umma(dnb_ctx* c, cudaStream_t st, bool fused, const SegDesc* 
     (void)nt_max;
     const dim3 grid(c->sm_count);  // persistent: one CTA per SM loops over the tiles
     if (fused) {
-        const size_t smem = 2 * (2 * 2 * um::A_TILE + 2 * 128 * um::BK * 2) + 256 + (um::kMaxSeg + 1) * 4 + um::kLocalItems * sizeof(um::Item) + 1024;
+        const size_t smem = 2 * (2 * 2 * um::A_TILE + 2 * 128 * um::BK * 2) + 256 + (um::kMaxSeg + 1) * 4 + um::kLocalItems * sizeof(um::Item) +
+                            um::PWARPS * 32 * 2 * 16 + 1024;
         static SmemGrant grant;
         DNB_CUDA(grant_smem(grant, c->device, um::grouped_q4k_umma_kernel<2>, smem));
         ProfScope prof_(c, st, "umma_gate_up");
         um::grouped_q4k_umma_kernel<2><<<grid, um::NTHREADS, smem, st>>>(seg, nseg_dev, n_in, n_out, rb, M, out_hi, out_lo,
                                                                         nullptr, c->status, nullptr);
     } else {
-        const size_t smem = 3 * (2 * um::A_TILE + 2 * 128 * um::BK * 2) + 256 + (um::kMaxSeg + 1) * 4 + um::kLocalItems * sizeof(um::Item) + 1024;
+        const size_t smem = 3 * (2 * um::A_TILE + 2 * 128 * um::BK * 2) + 256 + (um::kMaxSeg + 1) * 4 + um::kLocalItems * sizeof(um::Item) +
+                            um::PWARPS * 32 * 1 * 16 + 1024;
         static SmemGrant grant;
         DNB_CUDA(grant_smem(grant, c->device, um::grouped_q4k_umma_kernel<1>, smem));
         ProfScope prof_(c, st, "umma_down");
