@@ -189,14 +189,6 @@ __device__ __forceinline__ void dequant_q4k_task(const uint4& hdr, const uint4& 
     }
 }
 
-// Block-header load of the producers, as volatile asm so that it is issued where it is
-// written (a block ahead of its use) instead of being sunk towards the use.
-__device__ __forceinline__ uint4 ld_weights_keep(const void* p) {  // shared by the row's four threads
-    uint4 v;
-    asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
-}
-
 __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s32(dst)), "l"(src) : "memory");
 }
@@ -261,7 +253,8 @@ __device__ __forceinline__ float swiglu_fast(float g, float u) { return __fdivid
 struct ProducerArgs {
     ItemTab items;
     uint8_t* smem;
-    uint8_t* rawq;   // [16 producer warps][32 lanes][NMAT] x 16 bytes: every thread's slot for its next chunk
+    uint8_t* rawq;   // [16 producer warps][32 lanes][NMAT] x 16 bytes: every thread's slot for its next chunk; then
+                     // [2 groups][128 rows][NMAT] x 16 bytes: the block headers
     uint64_t* full;
     uint64_t* empty;
     int* status;
@@ -281,9 +274,12 @@ __device__ __forceinline__ bool produce(const ProducerArgs& a, int w8, int lane)
     struct Raw { uint4 qa, qb; };   // one chunk's 16 qs bytes per matrix
     struct Hdr { uint4 ha, hb; };   // one block's d, dmin and scale bytes per matrix
     Raw cur;                        // the chunk being dequantised
-    Hdr hdr_cur, hdr_next;
+    Hdr hdr_cur;
     // The thread's private 16 bytes per matrix in shared memory: the NEXT chunk's qs bytes arrive there by cp.async.
     uint4* slot = reinterpret_cast<uint4*>(a.rawq) + (size_t)((GRP * (PWARPS / 2) + w8) * 32 + lane) * NMAT;
+    // The row's block header (16 bytes per matrix), one slot per group and row: requested by the lane with p = 0
+    // together with the block's first chunk, read by both lanes of the row at the top of the block.
+    uint4* hslot = reinterpret_cast<uint4*>(a.rawq) + (size_t)PWARPS * 32 * NMAT + (size_t)(GRP * TILE_M + r) * NMAT;
     int f_left = a.my_items, f_k = 0, f_c = GRP;  // fetch cursor: item (CTA-local index) and chunk
     const uint8_t* f_pa = nullptr;
     const uint8_t* f_pb = nullptr;
@@ -300,16 +296,16 @@ __device__ __forceinline__ bool produce(const ProducerArgs& a, int w8, int lane)
     // Request the fetch cursor's chunk.  The qs bytes travel by cp.async into the thread's slot and are picked up
     // with cp.async.wait_group: with plain loads held in registers two chunks ahead, a wait for the older request
     // also waited for the younger one, and these stalls were 40 % of the kernel (measured by leaving the loads out).
-    // The block header (one load per block, used a whole block later) stays a plain load.
+    // The block header comes the same way (as a plain load a block ahead it cost 9 % of the gate/up kernel).
     auto fetch = [&]() {
         if (f_left <= 0) {
             cp_async_commit();
             return;
         }
         const int off = (f_c >> 2) * 144;
-        if ((f_c & 3) == GRP) {  // the group's first chunk of a block: fetch the block header too
-            hdr_next.ha = ld_weights_keep(f_pa + off);
-            if constexpr (NMAT == 2) hdr_next.hb = ld_weights_keep(f_pb + off);
+        if ((f_c & 3) == GRP && p == 0) {  // the group's first chunk of a block: fetch the block header too
+            cp_async16(hslot, f_pa + off);
+            if constexpr (NMAT == 2) cp_async16(hslot + 1, f_pb + off);
         }
         const int qoff = off + 16 + 32 * (f_c & 3) + 16 * p;
         cp_async16(slot, f_pa + qoff);
@@ -337,7 +333,12 @@ __device__ __forceinline__ bool produce(const ProducerArgs& a, int w8, int lane)
     bool ok = true;
     const int total = a.my_items * a.nchunks;  // a multiple of 4: n_in % 256 == 0
     for (int g4 = 0; g4 < total && ok; g4 += 4) {
-        hdr_cur = hdr_next;  // fetched one block (two of the group's chunks) ago
+        // Requested with the block's first chunk, which the last take() has waited for; the other lane of the row
+        // sees it after the warp barrier, and both lanes have their copy before the next header is requested.
+        __syncwarp();
+        hdr_cur.ha = hslot[0];
+        if constexpr (NMAT == 2) hdr_cur.hb = hslot[1];
+        __syncwarp();
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             const int j = GRP + 2 * i;  // chunk inside the block
@@ -679,7 +680,7 @@ int launch_grouped_umma(dnb_ctx* c, cudaStream_t st, bool fused, const SegDesc* 
     const dim3 grid(c->sm_count);  // persistent: one CTA per SM loops over the tiles
     if (fused) {
         const size_t smem = 2 * (2 * 2 * um::A_TILE + 2 * 128 * um::BK * 2) + 256 + (um::kMaxSeg + 1) * 4 + um::kLocalItems * sizeof(um::Item) +
-                            um::PWARPS * 32 * 2 * 16 + 1024;
+                            um::PWARPS * 32 * 2 * 16 + 2 * um::TILE_M * 2 * 16 + 1024;
         static SmemGrant grant;
         DNB_CUDA(grant_smem(grant, c->device, um::grouped_q4k_umma_kernel<2>, smem));
         ProfScope prof_(c, st, "umma_gate_up");
@@ -687,7 +688,7 @@ int launch_grouped_umma(dnb_ctx* c, cudaStream_t st, bool fused, const SegDesc* 
                                                                         nullptr, c->status, nullptr);
     } else {
         const size_t smem = 3 * (2 * um::A_TILE + 2 * 128 * um::BK * 2) + 256 + (um::kMaxSeg + 1) * 4 + um::kLocalItems * sizeof(um::Item) +
-                            um::PWARPS * 32 * 1 * 16 + 1024;
+                            um::PWARPS * 32 * 1 * 16 + 2 * um::TILE_M * 1 * 16 + 1024;
         static SmemGrant grant;
         DNB_CUDA(grant_smem(grant, c->device, um::grouped_q4k_umma_kernel<1>, smem));
         ProfScope prof_(c, st, "umma_down");
