@@ -8,7 +8,7 @@
 // <= 62), s = +-1 and db = d * (0.5 + scale) * 0.5 shared by the 32 elements of a sub-block
 // (kquant.rs:659-680).  g * s is exact in bf16, so the A operand needs no hi/lo split and no floating
 // point arithmetic in its producer: two codebook lookups and four sign masks make eight elements.
-// The tensor core sums one sub-block (K = 32) at a time into a small TMEM buffer,
+// The tensor core sums one sub-block (K = 32) at a time into its own TMEM columns,
 //     D_g[row][token] = sum_{k in g} (g*s)[row][k] * x[token][k]        (x as bf16 hi + lo: 2 products),
 // and the epilogue warps, which own one weight row per thread, read D_g back and do the fp32
 //     acc[row][token] += db[row][g] * D_g[row][token].
@@ -30,8 +30,10 @@
 //                silu(g) * u.  Down kernel: the two sets take the even / odd sub-blocks and add up.
 //   warp 24      TMA: the stage's activation tiles (hi and lo, 32 rows x 64 K, 128-byte swizzle)
 //   warp 25      MMA issue (one elected thread); owns the TMEM allocation
-// Barriers: full[s] / empty[s] per stage; tfull[b] / tfree[b] per TMEM sub-block buffer;
-// sfull[i] per slot of the scale ring (producers -> epilogue); xfull / xfree for the exchange buffer.
+// Barriers: full[s] / empty[s] per stage; tfull[b] / tfree[b] per TMEM buffer (one per stage in flight, both
+// of its sub-blocks: one hand-over per stage costs half the waits of one per sub-block, and the waits were
+// half of this kernel's time); sfull[i] per slot of the scale ring (producers -> epilogue); xfull / xfree for
+// the exchange buffer.
 // Every wait is bounded; one that gives up sets *status and the role leaves its loop (the producers
 // keep meeting at their named barrier so that none of them is left behind); TMEM is always freed.
 #include <cuda.h>
@@ -52,11 +54,11 @@ constexpr int B_TILE = NT * BK * 2;       // 4 KB (hi or lo)
 constexpr int STAGE_BYTES = 2 * A_TILE + 2 * B_TILE;
 constexpr int STAGES = 3;
 constexpr int RAWS = 2;                   // raw slots: one block in flight while one is decoded
-constexpr int NB = 6;                     // TMEM sub-block buffers (NT columns per matrix)
-constexpr int SCL = 12;                   // slots of the scale ring
-static_assert(RAWS == 2 && 2 * STAGES + NB <= SCL && SCL % 2 == 0 && NB % 2 == 0, "a producer must not lap the epilogue on the scale ring");
+constexpr int NB = 4;                     // TMEM buffers, one per stage in flight: 2 sub-blocks x NMAT x NT columns
+constexpr int SCL = 8;                    // slots of the scale ring, one per stage: [2 sub-blocks][NMAT][128]
+static_assert(RAWS == 2 && STAGES + NB <= SCL, "a producer must not lap the epilogue on the scale ring");
 constexpr int RAW_PITCH = 112;            // seven 16-byte lines cover a 98-byte block at any even offset
-constexpr int LUT_REP = 8;
+constexpr int LUT_REP = 4;
 constexpr int PWARPS = 16, EWARPS = 8;
 constexpr int W_TMA = PWARPS + EWARPS, W_MMA = W_TMA + 1;
 constexpr int NTHREADS = (W_MMA + 1) * 32;
@@ -198,13 +200,13 @@ __global__ void __launch_bounds__(NTHREADS, 1)
 grouped_iq3_exact_kernel(const SegDesc* __restrict__ seg, const int32_t* __restrict__ nseg_dev, int n_in, int n_out, int rb,
                          const __grid_constant__ Maps maps, uint16_t* __restrict__ out_hi, uint16_t* __restrict__ out_lo,
                          float* __restrict__ out_f32, int* status, float* const* __restrict__ row_dst) {
-    constexpr int TM_COLS = NMAT == 2 ? 512 : 256;  // NB buffers of NMAT * NT columns, rounded up to a power of two
+    constexpr int TM_COLS = NMAT == 2 ? 512 : 256;  // NB buffers of 2 * NMAT * NT columns
     constexpr int RAW_SLOT = NMAT * TILE_M * RAW_PITCH;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* raw = smem + STAGES * STAGE_BYTES;                        // [2][NMAT][128][RAW_PITCH]
     float* scl = reinterpret_cast<float*>(raw + RAWS * RAW_SLOT);         // [SCL][NMAT][128]
-    float* xbuf = scl + SCL * NMAT * TILE_M;                           // [NT][128]
+    float* xbuf = scl + SCL * 2 * NMAT * TILE_M;                           // [NT][128]
     uint2* lut = reinterpret_cast<uint2*>(xbuf + NT * TILE_M);         // [256][LUT_REP]
     uint64_t* full = reinterpret_cast<uint64_t*>(lut + 256 * LUT_REP);
     uint64_t* empty = full + STAGES;
@@ -220,7 +222,6 @@ grouped_iq3_exact_kernel(const SegDesc* __restrict__ seg, const int32_t* __restr
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nchunks = n_in / BK;
     const int nblocks = n_in / 256;
-    const int G = n_in / 32;  // sub-blocks per item (a multiple of 8)
     const int row_tiles = n_out / TILE_M;
     const int nseg = min(*nseg_dev, kMaxSeg);
 
@@ -231,9 +232,9 @@ grouped_iq3_exact_kernel(const SegDesc* __restrict__ seg, const int32_t* __restr
         }
         for (int i = 0; i < NB; ++i) {
             mb_init(&tfull[i], 1);
-            mb_init(&tfree[i], NMAT == 2 ? 8 : 4);  // the epilogue warps that read the buffer
+            mb_init(&tfree[i], EWARPS);     // every epilogue warp reads its part of the buffer
         }
-        for (int i = 0; i < SCL; ++i) mb_init(&sfull[i], PWARPS);  // every producer warp writes 16 rows of every sub-block
+        for (int i = 0; i < SCL; ++i) mb_init(&sfull[i], PWARPS);  // every producer warp writes 8 rows of the stage's scales
         mb_init(xfull, 4);
         mb_init(xfree, 4);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -348,7 +349,7 @@ grouped_iq3_exact_kernel(const SegDesc* __restrict__ seg, const int32_t* __restr
                         for (int mt = 0; mt < NMAT; ++mt) {
                             const uint8_t* r = rw[mt];
                             const uint32_t aux = lds_u16(r + 66 + 4 * gp) | (lds_u16(r + 68 + 4 * gp) << 16);
-                            if (l == 0) scl[((slot0 + h) * NMAT + mt) * TILE_M + row0] = d[mt] * (0.5f + (float)(aux >> 28)) * 0.5f;
+                            if (l == 0) scl[((slot0 * 2 + h) * NMAT + mt) * TILE_M + row0] = d[mt] * (0.5f + (float)(aux >> 28)) * 0.5f;
                             const uint32_t idx = lds_u16(r + 2 + 8 * gp + 2 * l);
                             const uint32_t code = (aux >> l7) & 127u;
                             const uint32_t sg = code | ((__popc(code) & 1u) << 7);  // bit 7 makes the number of minus signs even
@@ -367,14 +368,12 @@ grouped_iq3_exact_kernel(const SegDesc* __restrict__ seg, const int32_t* __restr
                     if (lane == 0) {
                         mb_arrive(&full[st]);
                         mb_arrive(&sfull[slot0]);
-                        mb_arrive(&sfull[slot0 + 1]);
                     }
                 }
                 fetch(kb + 1, j);
                 ++g;
                 if (++st == STAGES) { st = 0; ph ^= 1u; }
-                slot0 += 2;
-                if (slot0 >= SCL) slot0 = 0;
+                if (++slot0 == SCL) slot0 = 0;
             }
         }
         cp_async_wait_all();
@@ -408,17 +407,16 @@ grouped_iq3_exact_kernel(const SegDesc* __restrict__ seg, const int32_t* __restr
             if (!ok) break;
             const uint32_t a_lo = smem_lo + (uint32_t)(st * (STAGE_BYTES >> 4));
             const uint32_t bh_lo = a_lo + (uint32_t)((2 * A_TILE) >> 4), bl_lo = bh_lo + (uint32_t)(B_TILE >> 4);
+            const int b = g % NB;  // one TMEM buffer, one commit and one hand-over to the epilogue per stage
+            if (g >= NB) ok = warp_all(mb_wait(&tfree[b], (uint32_t)(g / NB - 1) & 1u, status, 6));
+            if (!ok) break;
+            tc_fence_after();
+            if (elect_one()) {
 #pragma unroll
-            for (int grp = 0; grp < 2; ++grp) {
-                const int gc = 2 * g + grp;  // running sub-block index
-                const int b = gc % NB;
-                if (gc >= NB) ok = warp_all(mb_wait(&tfree[b], (uint32_t)(gc / NB - 1) & 1u, status, 6));
-                if (!ok) break;
-                tc_fence_after();
-                if (elect_one()) {
+                for (int grp = 0; grp < 2; ++grp) {
 #pragma unroll
                     for (int mt = 0; mt < NMAT; ++mt) {
-                        const uint32_t dcol = tmem_base + (uint32_t)((b * NMAT + mt) * NT);
+                        const uint32_t dcol = tmem_base + (uint32_t)(((b * 2 + grp) * NMAT + mt) * NT);
                         const uint32_t am = a_lo + (uint32_t)(mt * (A_TILE >> 4));
 #pragma unroll
                         for (int ks = 0; ks < 2; ++ks) {
@@ -428,11 +426,11 @@ grouped_iq3_exact_kernel(const SegDesc* __restrict__ seg, const int32_t* __restr
                             mma_bf16(dcol, a, desc_of(bl_lo + koff), 1u);
                         }
                     }
-                    mma_commit(&tfull[b]);
-                    if (grp == 1) mma_commit(&empty[st]);  // the stage is free once everything issued so far has read it
                 }
-                __syncwarp();
+                mma_commit(&tfull[b]);
+                mma_commit(&empty[st]);  // the stage is free once everything issued so far has read it
             }
+            __syncwarp();
         }
     } else {
         // ---------------- epilogue: TMEM lane = weight row ----------------
@@ -440,39 +438,43 @@ grouped_iq3_exact_kernel(const SegDesc* __restrict__ seg, const int32_t* __restr
         const int r = quad * 32 + lane;
         const int mt = NMAT == 2 ? hsel : 0;
         const uint32_t tlane = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(mt * NT);
-        // running sub-block counter of this warp's reads: TMEM buffer, scale slot and their phase parities
-        int b = NMAT == 2 ? 0 : hsel, slot = NMAT == 2 ? 0 : hsel;
+        // running stage counter of this warp's reads: TMEM buffer, scale slot and their phase parities
+        int b = 0, slot = 0;
         uint32_t pb = 0, ps = 0;
-        constexpr int STEP = NMAT == 2 ? 1 : 2;
         for (int k = 0; k < my_items && ok; ++k) {
             const Item it = items.get(k);
             float acc[NT];
 #pragma unroll
             for (int j = 0; j < NT; ++j) acc[j] = 0.f;
-            for (int gi = 0; gi < G; gi += STEP) {
+            for (int c = 0; c < nchunks; ++c) {
                 ok = mb_wait(&sfull[slot], ps, status, 3);
                 if (!ok) break;
-                const float s = scl[(slot * NMAT + mt) * TILE_M + r];
                 ok = mb_wait(&tfull[b], pb, status, 3);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t tb = tlane + (uint32_t)(b * NMAT * NT);
-                float dv[16];
-                tmem_ld16(tb, dv);
-                tmem_ld_wait();
+                // gate/up: this warp's matrix, both sub-blocks of the stage; down: the sub-block of this warp's half
 #pragma unroll
-                for (int j = 0; j < 16; ++j) acc[j] = fmaf(s, dv[j], acc[j]);
-                tmem_ld16(tb + 16u, dv);
-                tmem_ld_wait();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mb_arrive(&tfree[b]);
+                for (int gq = 0; gq < (NMAT == 2 ? 2 : 1); ++gq) {
+                    const int grp = NMAT == 2 ? gq : hsel;
+                    const float s = scl[((slot * 2 + grp) * NMAT + mt) * TILE_M + r];
+                    const uint32_t tb = tlane + (uint32_t)((b * 2 + grp) * NMAT * NT);
+                    float dv[16];
+                    tmem_ld16(tb, dv);
+                    tmem_ld_wait();
 #pragma unroll
-                for (int j = 0; j < 16; ++j) acc[16 + j] = fmaf(s, dv[j], acc[16 + j]);
-                b += STEP;
-                if (b >= NB) { b -= NB; pb ^= 1u; }
-                slot += STEP;
-                if (slot >= SCL) { slot -= SCL; ps ^= 1u; }
+                    for (int j = 0; j < 16; ++j) acc[j] = fmaf(s, dv[j], acc[j]);
+                    tmem_ld16(tb + 16u, dv);
+                    tmem_ld_wait();
+                    if (gq == (NMAT == 2 ? 1 : 0)) {
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mb_arrive(&tfree[b]);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) acc[16 + j] = fmaf(s, dv[j], acc[16 + j]);
+                }
+                if (++b == NB) { b = 0; pb ^= 1u; }
+                if (++slot == SCL) { slot = 0; ps ^= 1u; }
             }
             if (!ok) break;
             if (hsel == 1) {
@@ -550,7 +552,7 @@ int launch_grouped_exact(dnb_ctx* c, cudaStream_t st, bool fused, const SegDesc*
     const dim3 grid(c->sm_count);
     const int nmat = fused ? 2 : 1;
     const size_t smem = (size_t)ex::STAGES * ex::STAGE_BYTES + ex::RAWS * (size_t)nmat * ex::TILE_M * ex::RAW_PITCH +
-                        (size_t)ex::SCL * nmat * ex::TILE_M * 4 + (size_t)ex::NT * ex::TILE_M * 4 + 256 * ex::LUT_REP * 8 +
+                        (size_t)ex::SCL * 2 * nmat * ex::TILE_M * 4 + (size_t)ex::NT * ex::TILE_M * 4 + 256 * ex::LUT_REP * 8 +
                         (2 * ex::STAGES + 2 * ex::NB + ex::SCL + 2) * 8 + 16 + (ex::kMaxSeg + 1) * 4 +
                         ex::kLocalItems * sizeof(ex::Item) + 1024;
     if (fused) {
