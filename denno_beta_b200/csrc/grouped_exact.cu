@@ -25,15 +25,14 @@
 //   warps 0-15   producers: raw rows arrive by cp.async (16-byte lines that cover the 98-byte blocks, one
 //                256-element block ahead, double buffered; the next items' tiles are asked into L2 first); decode into the K-major 128-byte
 //                swizzled A tiles of a stage (64 K = two sub-blocks); write the sub-block scales
-//   warps 16-23  epilogue: TMEM lane quadrant = warp % 4.  Gate/up kernel: warps 16-19 own the gate
-//                accumulators, 20-23 the up accumulators, exchanged through shared memory for
-//                silu(g) * u.  Down kernel: the two sets take the even / odd sub-blocks and add up.
+//   warps 16-23  epilogue: TMEM lane quadrant = warp % 4; warps 16-19 own token columns 0-15 of the tile,
+//                20-23 columns 16-31, of every matrix: silu(g) * u needs no exchange between warps
 //   warp 24      TMA: the stage's activation tiles (hi and lo, 32 rows x 64 K, 128-byte swizzle)
 //   warp 25      MMA issue (one elected thread); owns the TMEM allocation
 // Barriers: full[s] / empty[s] per stage; tfull[b] / tfree[b] per TMEM buffer (one per stage in flight, both
 // of its sub-blocks: one hand-over per stage costs half the waits of one per sub-block, and the waits were
-// half of this kernel's time); sfull[i] per slot of the scale ring (producers -> epilogue); xfull / xfree for
-// the exchange buffer.
+// half of this kernel's time); sfull[i] per slot of the scale ring (producers -> epilogue).  The down kernel
+// has eight TMEM buffers = a whole K = 512 item, so the MMAs of the next item run during an item's stores.
 // Every wait is bounded; one that gives up sets *status and the role leaves its loop (the producers
 // keep meeting at their named barrier so that none of them is left behind); TMEM is always freed.
 #include <cuda.h>
@@ -54,11 +53,12 @@ constexpr int B_TILE = NT * BK * 2;       // 4 KB (hi or lo)
 constexpr int STAGE_BYTES = 2 * A_TILE + 2 * B_TILE;
 constexpr int STAGES = 3;
 constexpr int RAWS = 2;                   // raw slots: one block in flight while one is decoded
-constexpr int NB = 4;                     // TMEM buffers, one per stage in flight: 2 sub-blocks x NMAT x NT columns
-constexpr int SCL = 8;                    // slots of the scale ring, one per stage: [2 sub-blocks][NMAT][128]
+constexpr int NB = 8;                     // TMEM buffers at most (one per stage in flight: 2 sub-blocks x NMAT x NT columns);
+                                          // the gate/up kernel has 4 (512 columns), the down kernel 8: a whole K = 512 item
+constexpr int SCL = 12;                   // slots of the scale ring, one per stage: [2 sub-blocks][NMAT][128]
 static_assert(RAWS == 2 && STAGES + NB <= SCL, "a producer must not lap the epilogue on the scale ring");
 constexpr int RAW_PITCH = 112;            // seven 16-byte lines cover a 98-byte block at any even offset
-constexpr int LUT_REP = 4;
+constexpr int LUT_REP = 8;
 constexpr int PWARPS = 16, EWARPS = 8;
 constexpr int W_TMA = PWARPS + EWARPS, W_MMA = W_TMA + 1;
 constexpr int NTHREADS = (W_MMA + 1) * 32;
@@ -200,22 +200,20 @@ __global__ void __launch_bounds__(NTHREADS, 1)
 grouped_iq3_exact_kernel(const SegDesc* __restrict__ seg, const int32_t* __restrict__ nseg_dev, int n_in, int n_out, int rb,
                          const __grid_constant__ Maps maps, uint16_t* __restrict__ out_hi, uint16_t* __restrict__ out_lo,
                          float* __restrict__ out_f32, int* status, float* const* __restrict__ row_dst) {
-    constexpr int TM_COLS = NMAT == 2 ? 512 : 256;  // NB buffers of 2 * NMAT * NT columns
+    constexpr int TM_COLS = 512;                   // NBUF buffers of 2 * NMAT * NT columns
+    constexpr int NBUF = NMAT == 2 ? 4 : 8;
     constexpr int RAW_SLOT = NMAT * TILE_M * RAW_PITCH;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* raw = smem + STAGES * STAGE_BYTES;                        // [2][NMAT][128][RAW_PITCH]
     float* scl = reinterpret_cast<float*>(raw + RAWS * RAW_SLOT);         // [SCL][NMAT][128]
-    float* xbuf = scl + SCL * 2 * NMAT * TILE_M;                           // [NT][128]
-    uint2* lut = reinterpret_cast<uint2*>(xbuf + NT * TILE_M);         // [256][LUT_REP]
+    uint2* lut = reinterpret_cast<uint2*>(scl + SCL * 2 * NMAT * TILE_M);  // [256][LUT_REP]
     uint64_t* full = reinterpret_cast<uint64_t*>(lut + 256 * LUT_REP);
     uint64_t* empty = full + STAGES;
     uint64_t* tfull = empty + STAGES;
     uint64_t* tfree = tfull + NB;
     uint64_t* sfull = tfree + NB;
-    uint64_t* xfull = sfull + SCL;
-    uint64_t* xfree = xfull + 1;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xfree + 1);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sfull + SCL);
     int* tile_prefix = reinterpret_cast<int*>(tmem_slot + 4);          // [nseg + 1]
     Item* itab = reinterpret_cast<Item*>(tile_prefix + kMaxSeg + 1);   // [kLocalItems]
 
@@ -235,8 +233,6 @@ grouped_iq3_exact_kernel(const SegDesc* __restrict__ seg, const int32_t* __restr
             mb_init(&tfree[i], EWARPS);     // every epilogue warp reads its part of the buffer
         }
         for (int i = 0; i < SCL; ++i) mb_init(&sfull[i], PWARPS);  // every producer warp writes 8 rows of the stage's scales
-        mb_init(xfull, 4);
-        mb_init(xfree, 4);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     for (int i = tid; i < 256 * LUT_REP; i += NTHREADS) {  // codebook magnitudes as bf16 pairs (<= 62: exact)
@@ -407,8 +403,8 @@ grouped_iq3_exact_kernel(const SegDesc* __restrict__ seg, const int32_t* __restr
             if (!ok) break;
             const uint32_t a_lo = smem_lo + (uint32_t)(st * (STAGE_BYTES >> 4));
             const uint32_t bh_lo = a_lo + (uint32_t)((2 * A_TILE) >> 4), bl_lo = bh_lo + (uint32_t)(B_TILE >> 4);
-            const int b = g % NB;  // one TMEM buffer, one commit and one hand-over to the epilogue per stage
-            if (g >= NB) ok = warp_all(mb_wait(&tfree[b], (uint32_t)(g / NB - 1) & 1u, status, 6));
+            const int b = g % NBUF;  // one TMEM buffer, one commit and one hand-over to the epilogue per stage
+            if (g >= NBUF) ok = warp_all(mb_wait(&tfree[b], (uint32_t)(g / NBUF - 1) & 1u, status, 6));
             if (!ok) break;
             tc_fence_after();
             if (elect_one()) {
@@ -434,84 +430,70 @@ grouped_iq3_exact_kernel(const SegDesc* __restrict__ seg, const int32_t* __restr
         }
     } else {
         // ---------------- epilogue: TMEM lane = weight row ----------------
+        // A warp owns 32 weight rows (its TMEM lane quadrant) x 16 token columns (hsel) of every matrix: the gate and
+        // the up value of a (row, token) meet in one thread, and nothing is exchanged between warps.
         const int quad = warp & 3, hsel = (warp - PWARPS) >> 2;
         const int r = quad * 32 + lane;
-        const int mt = NMAT == 2 ? hsel : 0;
-        const uint32_t tlane = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(mt * NT);
+        const uint32_t tlane = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(16 * hsel);
         // running stage counter of this warp's reads: TMEM buffer, scale slot and their phase parities
         int b = 0, slot = 0;
         uint32_t pb = 0, ps = 0;
         for (int k = 0; k < my_items && ok; ++k) {
             const Item it = items.get(k);
-            float acc[NT];
+            float acc[NMAT][16];
 #pragma unroll
-            for (int j = 0; j < NT; ++j) acc[j] = 0.f;
+            for (int mt = 0; mt < NMAT; ++mt)
+#pragma unroll
+                for (int j = 0; j < 16; ++j) acc[mt][j] = 0.f;
             for (int c = 0; c < nchunks; ++c) {
                 ok = mb_wait(&sfull[slot], ps, status, 3);
                 if (!ok) break;
                 ok = mb_wait(&tfull[b], pb, status, 3);
                 if (!ok) break;
                 tc_fence_after();
-                // gate/up: this warp's matrix, both sub-blocks of the stage; down: the sub-block of this warp's half
 #pragma unroll
-                for (int gq = 0; gq < (NMAT == 2 ? 2 : 1); ++gq) {
-                    const int grp = NMAT == 2 ? gq : hsel;
-                    const float s = scl[((slot * 2 + grp) * NMAT + mt) * TILE_M + r];
-                    const uint32_t tb = tlane + (uint32_t)((b * 2 + grp) * NMAT * NT);
-                    float dv[16];
-                    tmem_ld16(tb, dv);
-                    tmem_ld_wait();
+                for (int grp = 0; grp < 2; ++grp) {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) acc[j] = fmaf(s, dv[j], acc[j]);
-                    tmem_ld16(tb + 16u, dv);
-                    tmem_ld_wait();
-                    if (gq == (NMAT == 2 ? 1 : 0)) {
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mb_arrive(&tfree[b]);
+                    for (int mt = 0; mt < NMAT; ++mt) {
+                        const float s = scl[((slot * 2 + grp) * NMAT + mt) * TILE_M + r];
+                        float dv[16];
+                        tmem_ld16(tlane + (uint32_t)(((b * 2 + grp) * NMAT + mt) * NT), dv);
+                        tmem_ld_wait();
+                        if (grp == 1 && mt == NMAT - 1) {  // the buffer has been read: hand it back before the arithmetic
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mb_arrive(&tfree[b]);
+                        }
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) acc[mt][j] = fmaf(s, dv[j], acc[mt][j]);
                     }
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) acc[16 + j] = fmaf(s, dv[j], acc[16 + j]);
                 }
-                if (++b == NB) { b = 0; pb ^= 1u; }
+                if (++b == NBUF) { b = 0; pb ^= 1u; }
                 if (++slot == SCL) { slot = 0; ps ^= 1u; }
             }
             if (!ok) break;
-            if (hsel == 1) {
-                if (k > 0) ok = mb_wait(xfree, (uint32_t)(k - 1) & 1u, status, 3);
-                if (!ok) break;
+            const int t0 = 16 * hsel;
+            if constexpr (NMAT == 2) {
+                uint16_t* oh = out_hi + (size_t)(it.prow + t0) * n_out + it.r0 + r;
+                uint16_t* ol = out_lo + (size_t)(it.prow + t0) * n_out + it.r0 + r;
 #pragma unroll
-                for (int j = 0; j < NT; ++j) xbuf[j * TILE_M + r] = acc[j];
-                __syncwarp();
-                if (lane == 0) mb_arrive(xfull);
-            } else {
-                ok = mb_wait(xfull, (uint32_t)k & 1u, status, 3);
-                if (!ok) break;
-                if constexpr (NMAT == 2) {
-                    uint16_t* oh = out_hi + (size_t)it.prow * n_out + it.r0 + r;
-                    uint16_t* ol = out_lo + (size_t)it.prow * n_out + it.r0 + r;
-#pragma unroll
-                    for (int j = 0; j < NT; ++j) {
-                        const float a = swiglu_fast(acc[j], xbuf[j * TILE_M + r]);
-                        const uint16_t ah = __bfloat16_as_ushort(__float2bfloat16_rn(a));
-                        const float al = a - __uint_as_float((uint32_t)ah << 16);
-                        if (j < it.m_tile) {
-                            oh[(size_t)j * n_out] = ah;
-                            ol[(size_t)j * n_out] = (uint16_t)(__float_as_uint(al) >> 16);
-                        }
-                    }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < NT; ++j) {
-                        const float a = acc[j] + xbuf[j * TILE_M + r];  // even sub-blocks + odd sub-blocks
-                        if (j < it.m_tile) {
-                            if (row_dst) row_dst[it.prow + j][it.r0 + r] = a;  // expert parallel: the owner's (token, slot) row
-                            else out_f32[(size_t)(it.prow + j) * n_out + it.r0 + r] = a;
-                        }
+                for (int j = 0; j < 16; ++j) {
+                    const float a = swiglu_fast(acc[0][j], acc[NMAT - 1][j]);
+                    const uint16_t ah = __bfloat16_as_ushort(__float2bfloat16_rn(a));
+                    const float al = a - __uint_as_float((uint32_t)ah << 16);
+                    if (t0 + j < it.m_tile) {
+                        oh[(size_t)j * n_out] = ah;
+                        ol[(size_t)j * n_out] = (uint16_t)(__float_as_uint(al) >> 16);
                     }
                 }
-                __syncwarp();
-                if (lane == 0) mb_arrive(xfree);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    if (t0 + j < it.m_tile) {
+                        if (row_dst) row_dst[it.prow + t0 + j][it.r0 + r] = acc[0][j];  // expert parallel: the owner's (token, slot) row
+                        else out_f32[(size_t)(it.prow + t0 + j) * n_out + it.r0 + r] = acc[0][j];
+                    }
+                }
             }
         }
     }
@@ -552,8 +534,8 @@ int launch_grouped_exact(dnb_ctx* c, cudaStream_t st, bool fused, const SegDesc*
     const dim3 grid(c->sm_count);
     const int nmat = fused ? 2 : 1;
     const size_t smem = (size_t)ex::STAGES * ex::STAGE_BYTES + ex::RAWS * (size_t)nmat * ex::TILE_M * ex::RAW_PITCH +
-                        (size_t)ex::SCL * 2 * nmat * ex::TILE_M * 4 + (size_t)ex::NT * ex::TILE_M * 4 + 256 * ex::LUT_REP * 8 +
-                        (2 * ex::STAGES + 2 * ex::NB + ex::SCL + 2) * 8 + 16 + (ex::kMaxSeg + 1) * 4 +
+                        (size_t)ex::SCL * 2 * nmat * ex::TILE_M * 4 + 256 * ex::LUT_REP * 8 +
+                        (2 * ex::STAGES + 2 * ex::NB + ex::SCL) * 8 + 16 + (ex::kMaxSeg + 1) * 4 +
                         ex::kLocalItems * sizeof(ex::Item) + 1024;
     if (fused) {
         static SmemGrant grant;
