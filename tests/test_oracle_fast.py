@@ -50,3 +50,28 @@ def test_fast_block_matches_the_oracle(orc, name):
         assert np.max(np.abs(grouped - want)) / rms <= 2e-5
     finally:
         orc.set_threads(0)
+
+
+def test_placed_zipf_bias_keeps_the_values_and_balances_contiguous_shards(orc):
+    """bench.py's expert placement for the expert-parallel prefill lines: the same bias values on other expert
+    indices, such that contiguous shards of 64 / 128 / 256 experts see about equal numbers of routed rows."""
+    import os
+    import sys
+
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import bench
+
+    rb = orc.synth_zipf_bias(bench.SEED, 7, 1.1, bench.NE)
+    pb = bench.placed_zipf_bias(rb)
+    assert sorted(pb.tolist()) == sorted(rb.tolist())
+    assert np.array_equal(pb, bench.placed_zipf_bias(rb)), "placement is deterministic"
+    nt = 256
+    h = orc.synth_normal(bench.SEED, 8000, 1.0, nt * bench.E).reshape(nt, bench.E)
+    rw = orc.synth_normal(bench.SEED, 6, 0.02, bench.NE * bench.E).reshape(bench.NE, bench.E)
+    x = orc.rmsnorm(h, np.ones(bench.E, np.float32))
+    worst = {}
+    for name, b in (("seeded", rb), ("placed", pb)):
+        counts = np.bincount(orc.router(x, rw, b, bench.K)[0].ravel(), minlength=bench.NE)
+        worst[name] = {g: float(counts.reshape(g, -1).sum(1).max() / counts.reshape(g, -1).sum(1).mean()) for g in (2, 4, 8)}
+    assert worst["placed"][8] <= 1.2 and worst["placed"][4] <= 1.12 and worst["placed"][2] <= 1.06, worst
+    assert worst["seeded"][8] >= 1.5, worst
