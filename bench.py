@@ -1078,6 +1078,10 @@ def main():
     args = ap.parse_args()
     if args.layers > 0:
         LAYERS = args.layers
+    else:
+        # The rotating layer copies are walked by ONE stack call; a step count they divide needs no single-block
+        # calls for the remainder (20 steps: 20 copies, one call).  16 to 32 copies: 279 to 557 MB per cycle, all > L2.
+        LAYERS = next((l_ for l_ in (16, 20, 24, 25, 18, 30, 32, 28, 21, 27, 22, 26, 17, 19, 23, 29, 31) if args.steps % l_ == 0), 16)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
