@@ -1007,6 +1007,20 @@ def cpu_baseline(oracle, budget_s, with_other_configs=True):
         out["config2_q4k_prefill_512"] = {"ms_per_chunk_layer": dt * 1e3, "tok_per_s_layer": 512 / dt,
                                           "algorithmic_tflops": (2.0 * 3 * E * FF * (512 * K + 512) + 2.0 * 512 * NE * E) / dt / 1e12,
                                           "sample": "one 512-token chunk, once"}
+        # configs 3 and 4 (48 layers) are not run on the CPU: extrapolated from the per-block times above
+        t_chunk = dt
+        for i in range(2):
+            oracle.fast_moe_block(L2, h[i:i + 1])
+        m, t0 = 0, time.perf_counter()
+        while time.perf_counter() - t0 < 1.0:
+            oracle.fast_moe_block(L2, h[m % 64:m % 64 + 1])
+            m += 1
+        t_q4 = (time.perf_counter() - t0) / m
+        t_iq3 = 1.0 / out["value"]
+        out["config3_decode_stack48_batch1"] = {"tok_per_s": 1.0 / (40 * t_iq3 + 8 * t_q4), "extrapolated": True,
+                                                "from": "40 x the IQ3_XXS block time + 8 x a Q4_K block time (%d one-token blocks in 1 s)" % m}
+        out["config4_prefill_stack48_14018"] = {"seconds": 48 * (14018 / 512.0) * t_chunk, "tok_per_s": 14018 / (48 * (14018 / 512.0) * t_chunk),
+                                                "extrapolated": True, "from": "48 layers x 27.4 chunks x the config-2 chunk time"}
     return out
 
 
