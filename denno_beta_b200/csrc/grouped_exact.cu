@@ -23,15 +23,16 @@
 // Roles (832 threads; 16 producer warps because the decode is a chain of dependent shared-memory lookups
 // and the epilogue warps mostly wait - measured: with 8 producer warps each scheduler issued 0.4 per cycle):
 //   warps 0-15   producers: raw rows arrive by cp.async (16-byte lines that cover the 98-byte blocks, one
-//                256-element block ahead, double buffered; the next items' tiles are asked into L2 first); decode into the K-major 128-byte
-//                swizzled A tiles of a stage (64 K = two sub-blocks); write the sub-block scales
+//                256-element block ahead, double buffered; the next item's tile is asked into L2 first);
+//                decode into the K-major 128-byte swizzled A tiles of a stage (64 K = two sub-blocks);
+//                write the sub-block scales
 //   warps 16-23  epilogue: TMEM lane quadrant = warp % 4; warps 16-19 own token columns 0-15 of the tile,
 //                20-23 columns 16-31, of every matrix: silu(g) * u needs no exchange between warps
 //   warp 24      TMA: the stage's activation tiles (hi and lo, 32 rows x 64 K, 128-byte swizzle)
 //   warp 25      MMA issue (one elected thread); owns the TMEM allocation
 // Barriers: full[s] / empty[s] per stage; tfull[b] / tfree[b] per TMEM buffer (one per stage in flight, both
-// of its sub-blocks: one hand-over per stage costs half the waits of one per sub-block, and the waits were
-// half of this kernel's time); sfull[i] per slot of the scale ring (producers -> epilogue).  The down kernel
+// of its sub-blocks: one hand-over per stage costs half the waits of one per sub-block, and with everything
+// but the barriers left out the kernel still took 40-65 % of its time); sfull[i] per slot of the scale ring (producers -> epilogue).  The down kernel
 // has eight TMEM buffers = a whole K = 512 item, so the MMAs of the next item run during an item's stores.
 // Every wait is bounded; one that gives up sets *status and the role leaves its loop (the producers
 // keep meeting at their named barrier so that none of them is left behind); TMEM is always freed.
