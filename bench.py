@@ -563,6 +563,29 @@ def extras(ctx, cu, oracle):
                                               "bytes": alg, "launches": reps, "rotating_copies": copies,
                                               "frac_of_measured_hbm": alg / (ms / reps * 1e-3) / 1e9 / peaks()[0]}
         ctx.dev_free(dw)
+    # The same kernel on a launch 16 times as large (4096 x 65536: 100-290 MB per launch, two rotating copies):
+    # what it reaches when a launch is not mostly ramp and drain.
+    n_big = 16 * n
+    do_big = ctx.dev_alloc(n_big * 4)
+    for name, ty in (("q4k", Q4_K), ("iq3xxs", IQ3_XXS), ("q6k", 14), ("q80", 8)):
+        rb = oracle.row_bytes(ty, k)
+        w = oracle.synth_blocks(ty, SEED, 9000 + ty, n * (k // oracle.blck_size(ty)))
+        dw = ctx.dev_alloc(2 * n_big * rb)
+        for i in range(32):
+            ctx.upload(dw + i * n * rb, w)
+        for i in range(3):
+            ctx.gemv_dev(ty, dw + (i % 2) * n_big * rb, k, n_big, dx, do_big, 1)
+        ctx.sync()
+        reps = 16
+        ctx.timer_start()
+        for i in range(reps):
+            ctx.gemv_dev(ty, dw + (i % 2) * n_big * rb, k, n_big, dx, do_big, 1)
+        ms = ctx.timer_stop()
+        alg = n_big * rb + k * 4 + n_big * 4
+        out["config0_x16_%s_gemv_4096x65536" % name] = {"us_per_gemv": ms / reps * 1e3, "hbm_gbs": alg / (ms / reps * 1e-3) / 1e9, "bytes": alg,
+                                                        "frac_of_measured_hbm": alg / (ms / reps * 1e-3) / 1e9 / peaks()[0]}
+        ctx.dev_free(dw)
+    ctx.dev_free(do_big)
     for p in (dx, do):
         ctx.dev_free(p)
     return out
