@@ -38,13 +38,17 @@ def test_config0_other_formats_4096(orc, name):
     assert np.array_equal(out.view(np.uint32), again.view(np.uint32))
 
 
-def test_config2_every_token(orc):
+@pytest.mark.parametrize("ty_name,seam", [("Q4_K", 128), ("IQ3_XXS", 32)])
+def test_config2_every_token(orc, ty_name, seam):
+    """Config 2 (Q4_K: three-product tcgen05 kernel, 128-token tiles) and the same chunk with IQ3_XXS experts
+    (exact-weight tcgen05 kernel, 32-token tiles): every token against the fp32 kernels, a sample that covers the
+    hottest expert's tile seams against the oracle."""
     from denno_beta_b200 import cuda as cu
 
     c = cu.CudaCtx(0)
     try:
         assert c.moe_config(1, E, FF, NE, K)
-        L = make_layer(orc, c, 0, orc.Q4_K, E, FF, NE, K, bias=True)
+        L = make_layer(orc, c, 0, getattr(orc, ty_name), E, FF, NE, K, bias=True)
         nt = 512
         h = orc.synth_normal(SEED, 3000, 1.0, nt * E).reshape(nt, E)
         n0 = c.launch_count()
@@ -65,7 +69,8 @@ def test_config2_every_token(orc):
         hot = int(counts.argmax())
         assert counts[hot] > 256, "the Zipf bias should give one expert several 128-token tiles"
         hot_tokens = np.nonzero(np.any(sels == hot, axis=1))[0]  # ascending = packed order inside the expert
-        seams = [i for i in (0, 1, 127, 128, 129, 255, 256, 257, 383, 384, 385, len(hot_tokens) - 1) if i < len(hot_tokens)]
+        seams = [i for i in (0, 1, seam - 1, seam, seam + 1, 2 * seam - 1, 2 * seam, 2 * seam + 1, 3 * seam - 1, 3 * seam,
+                             3 * seam + 1, len(hot_tokens) - 1) if i < len(hot_tokens)]
         pick = set(hot_tokens[seams].tolist()) | set(hot_tokens[::37].tolist())
         cold = np.nonzero(~np.any(sels == hot, axis=1))[0]
         pick |= set(cold.tolist()[:8])
