@@ -214,7 +214,7 @@ struct Item {
     int r0;      // first weight row
 };
 __device__ __forceinline__ Item decode_item(int item, int row_tiles, int nseg, const int* tile_prefix,
-                                            const SegDesc* __restrict__ seg) {
+                                            const SegDesc* __restrict__ seg, int rows_per_item = TILE_M) {
     const int tile = item / row_tiles, rt = item - tile * row_tiles;
     int lo = 0, hi = nseg - 1;
     while (lo < hi) {  // last segment whose first tile is <= tile
@@ -228,7 +228,7 @@ __device__ __forceinline__ Item decode_item(int item, int row_tiles, int nseg, c
     it.wb = sd.wb;
     it.prow = (int)sd.row0 + t0;
     it.m_tile = min(128, (int)sd.m - t0);
-    it.r0 = rt * TILE_M;
+    it.r0 = rt * rows_per_item;
     return it;
 }
 // The CTA's k-th item: from the table filled at kernel start, or decoded on the spot when
@@ -237,10 +237,10 @@ struct ItemTab {
     const Item* tab;
     const SegDesc* seg;
     const int* tile_prefix;
-    int nseg, row_tiles;
+    int nseg, row_tiles, rows_per_item;
     __device__ __forceinline__ Item get(int k) const {
         if (k < kLocalItems) return tab[k];
-        return decode_item((int)blockIdx.x + k * (int)gridDim.x, row_tiles, nseg, tile_prefix, seg);
+        return decode_item((int)blockIdx.x + k * (int)gridDim.x, row_tiles, nseg, tile_prefix, seg, rows_per_item);
     }
 };
 __device__ __forceinline__ int nsel_of(int m_tile) { return m_tile <= 16 ? 0 : (m_tile <= 32 ? 1 : (m_tile <= 64 ? 2 : 3)); }
@@ -268,7 +268,7 @@ struct ProducerArgs {
 // rows x 2 qs pieces (a request covers whole 32-byte sectors) and a thread dequantises
 // both nibbles of its 16 bytes: 32 elements per matrix and chunk.  Raw bytes are
 // requested two of the group's chunks ahead, through item boundaries.
-template <int NMAT, int STAGES, int STAGE_BYTES, int GRP>
+template <int NMAT, bool PAIR, int STAGES, int STAGE_BYTES, int GRP>
 __device__ __forceinline__ bool produce(const ProducerArgs& a, int w8, int lane) {
     const int r = w8 * 16 + (lane & 15), p = lane >> 4;
     struct Raw { uint4 qa, qb; };   // one chunk's 16 qs bytes per matrix
@@ -290,7 +290,7 @@ __device__ __forceinline__ bool produce(const ProducerArgs& a, int w8, int lane)
         if (f_left > 0) {
             const Item it = a.items.get(f_k);
             f_pa = it.wa + (size_t)(it.r0 + r) * a.rb;
-            if constexpr (NMAT == 2) f_pb = it.wb + (size_t)(it.r0 + r) * a.rb;
+            if constexpr (NMAT == 2) f_pb = PAIR ? it.wa + (size_t)(it.r0 + TILE_M + r) * a.rb : it.wb + (size_t)(it.r0 + r) * a.rb;
         }
     };
     // Request the fetch cursor's chunk.  The qs bytes travel by cp.async into the thread's slot and are picked up
@@ -366,7 +366,9 @@ __device__ __forceinline__ bool produce(const ProducerArgs& a, int w8, int lane)
 }
 
 // NMAT = 2: gate and up tiles together, SwiGLU epilogue to out_hi / out_lo (bf16 packed rows).
-// NMAT = 1: one matrix, fp32 epilogue to out_f32.
+// NMAT = 2, PAIR: two 128-row tiles of ONE matrix (rows r0.. and r0 + 128..) against the same activation tile, fp32
+//   epilogue: the down GEMM (K = 512: 8 stages per item) with half the stages, hand-overs and activation copies of
+// NMAT = 1: one matrix, one 128-row tile, fp32 epilogue to out_f32 (output widths that are not a multiple of 256).
 //
 // Persistent: grid = number of SMs (the stages fill shared memory, one CTA per SM).
 // Work items are (segment, 128-token tile, 128-row tile), item i handled by CTA
@@ -380,7 +382,7 @@ __device__ __forceinline__ bool produce(const ProducerArgs& a, int w8, int lane)
 //                the main loop of item i+1 fills the other accumulator buffer
 // Barriers and their phases live across items: chunk counter g keeps running
 // (stage g % STAGES, parity (g / STAGES) & 1); accumulator buffer = item count & 1.
-template <int NMAT>
+template <int NMAT, bool PAIR = false>
 __global__ void __launch_bounds__(NTHREADS, 1)
 grouped_q4k_umma_kernel(const SegDesc* __restrict__ seg, const int32_t* __restrict__ nseg_dev, int n_in, int n_out,
                         int rb, const __grid_constant__ Maps maps, uint16_t* __restrict__ out_hi,
@@ -404,7 +406,8 @@ grouped_q4k_umma_kernel(const SegDesc* __restrict__ seg, const int32_t* __restri
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nchunks = n_in / BK;
-    const int row_tiles = n_out / TILE_M;
+    constexpr int ROWS_ITEM = PAIR ? 2 * TILE_M : TILE_M;
+    const int row_tiles = n_out / ROWS_ITEM;
     const int nseg = min(*nseg_dev, kMaxSeg);
 
     if (tid == 0) {
@@ -448,16 +451,16 @@ grouped_q4k_umma_kernel(const SegDesc* __restrict__ seg, const int32_t* __restri
     const int n_items = nseg > 0 ? tile_prefix[nseg] * row_tiles : 0;
     const int G = gridDim.x;
     const int my_items = (int)blockIdx.x < n_items ? (n_items - (int)blockIdx.x + G - 1) / G : 0;
-    if (tid < min(my_items, kLocalItems)) itab[tid] = decode_item((int)blockIdx.x + tid * G, row_tiles, nseg, tile_prefix, seg);
+    if (tid < min(my_items, kLocalItems)) itab[tid] = decode_item((int)blockIdx.x + tid * G, row_tiles, nseg, tile_prefix, seg, ROWS_ITEM);
     __syncthreads();
-    const ItemTab items{itab, seg, tile_prefix, nseg, row_tiles};
+    const ItemTab items{itab, seg, tile_prefix, nseg, row_tiles, ROWS_ITEM};
     bool ok = true;
 
     if (warp < PWARPS) {
         // ---------------- producers ----------------
         ProducerArgs pa{items, smem, reinterpret_cast<uint8_t*>(itab + kLocalItems), full, empty, status, my_items, nchunks, rb};
-        if (warp < PWARPS / 2) ok = produce<NMAT, STAGES, STAGE_BYTES, 0>(pa, warp, lane);
-        else ok = produce<NMAT, STAGES, STAGE_BYTES, 1>(pa, warp - PWARPS / 2, lane);
+        if (warp < PWARPS / 2) ok = produce<NMAT, PAIR, STAGES, STAGE_BYTES, 0>(pa, warp, lane);
+        else ok = produce<NMAT, PAIR, STAGES, STAGE_BYTES, 1>(pa, warp - PWARPS / 2, lane);
     } else if (warp == W_TMA) {
         // ---------------- TMA: activation tiles ----------------
         // The whole warp walks the loop and waits; one elected lane issues.  Addresses,
@@ -547,7 +550,25 @@ grouped_q4k_umma_kernel(const SegDesc* __restrict__ seg, const int32_t* __restri
                 if constexpr (NMAT == 2) tmem_ld16(tb + (uint32_t)(128 + c0), uq);
                 tmem_ld_wait();
                 const int nv = min(16, it.m_tile - c0);
-                if constexpr (NMAT == 2) {
+                if constexpr (NMAT == 2 && PAIR) {
+                    if (row_dst) {
+#pragma unroll
+                        for (int j2 = 0; j2 < 16; ++j2)
+                            if (j2 < nv) {
+                                float* dst = row_dst[it.prow + c0 + j2] + it.r0 + r;
+                                dst[0] = __uint_as_float(gq[j2]);
+                                dst[TILE_M] = __uint_as_float(uq[j2]);
+                            }
+                    } else {
+                        float* of = out_f32 + (size_t)(it.prow + c0) * n_out + it.r0 + r;
+#pragma unroll
+                        for (int j2 = 0; j2 < 16; ++j2)
+                            if (j2 < nv) {
+                                of[(size_t)j2 * n_out] = __uint_as_float(gq[j2]);
+                                of[(size_t)j2 * n_out + TILE_M] = __uint_as_float(uq[j2]);
+                            }
+                    }
+                } else if constexpr (NMAT == 2) {
                     uint16_t* oh = out_hi + (size_t)(it.prow + c0) * n_out + it.r0 + r;
                     uint16_t* ol = out_lo + (size_t)(it.prow + c0) * n_out + it.r0 + r;
 #pragma unroll
@@ -686,6 +707,14 @@ int launch_grouped_umma(dnb_ctx* c, cudaStream_t st, bool fused, const SegDesc* 
         ProfScope prof_(c, st, "umma_gate_up");
         um::grouped_q4k_umma_kernel<2><<<grid, um::NTHREADS, smem, st>>>(seg, nseg_dev, n_in, n_out, rb, M, out_hi, out_lo,
                                                                         nullptr, c->status, nullptr);
+    } else if (n_out % (2 * um::TILE_M) == 0) {
+        const size_t smem = 2 * (2 * 2 * um::A_TILE + 2 * 128 * um::BK * 2) + 256 + (um::kMaxSeg + 1) * 4 + um::kLocalItems * sizeof(um::Item) +
+                            um::PWARPS * 32 * 2 * 16 + 2 * um::TILE_M * 2 * 16 + 1024;
+        static SmemGrant grant;
+        DNB_CUDA(grant_smem(grant, c->device, um::grouped_q4k_umma_kernel<2, true>, smem));
+        ProfScope prof_(c, st, "umma_down");
+        um::grouped_q4k_umma_kernel<2, true><<<grid, um::NTHREADS, smem, st>>>(seg, nseg_dev, n_in, n_out, rb, M, nullptr, nullptr,
+                                                                              out_f32, c->status, row_dst);
     } else {
         const size_t smem = 3 * (2 * um::A_TILE + 2 * 128 * um::BK * 2) + 256 + (um::kMaxSeg + 1) * 4 + um::kLocalItems * sizeof(um::Item) +
                             um::PWARPS * 32 * 1 * 16 + 2 * um::TILE_M * 1 * 16 + 1024;
