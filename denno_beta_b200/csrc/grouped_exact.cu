@@ -163,7 +163,7 @@ struct Item {
     int m_tile;  // tokens in the tile (1..NT)
     int r0;      // first weight row
 };
-__device__ __forceinline__ Item decode_item(int item, int row_tiles, int nseg, const int* tile_prefix,
+__device__ __forceinline__ Item decode_item(int item, int row_tiles, int rows_per_item, int nseg, const int* tile_prefix,
                                             const SegDesc* __restrict__ seg) {
     const int tile = item / row_tiles, rt = item - tile * row_tiles;
     int lo = 0, hi = nseg - 1;
@@ -178,25 +178,27 @@ __device__ __forceinline__ Item decode_item(int item, int row_tiles, int nseg, c
     it.wb = sd.wb;
     it.prow = (int)sd.row0 + t0;
     it.m_tile = min(NT, (int)sd.m - t0);
-    it.r0 = rt * TILE_M;
+    it.r0 = rt * rows_per_item;
     return it;
 }
 struct ItemTab {
     const Item* tab;
     const SegDesc* seg;
     const int* tile_prefix;
-    int nseg, row_tiles;
+    int nseg, row_tiles, rows_per_item;
     __device__ __forceinline__ Item get(int k) const {
         if (k < kLocalItems) return tab[k];
-        return decode_item((int)blockIdx.x + k * (int)gridDim.x, row_tiles, nseg, tile_prefix, seg);
+        return decode_item((int)blockIdx.x + k * (int)gridDim.x, row_tiles, rows_per_item, nseg, tile_prefix, seg);
     }
 };
 
 __device__ __forceinline__ float swiglu_fast(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
 
 // NMAT = 2: gate and up together, silu(g) * u written as bf16 hi/lo packed rows (the B operand of
-// the down GEMM).  NMAT = 1: one matrix, fp32 rows (or peer rows through row_dst).
-template <int NMAT>
+// the down GEMM).  NMAT = 1: one matrix, fp32 rows (or peer rows through row_dst).  PAIR (with NMAT = 2):
+// the two A tiles of an item are rows r0.. and r0 + 128.. of ONE matrix against the same activation tile, fp32
+// rows out: half the stages, hand-overs and activation loads of the NMAT = 1 form.
+template <int NMAT, bool PAIR = false>
 __global__ void __launch_bounds__(NTHREADS, 1)
 grouped_iq3_exact_kernel(const SegDesc* __restrict__ seg, const int32_t* __restrict__ nseg_dev, int n_in, int n_out, int rb,
                          const __grid_constant__ Maps maps, uint16_t* __restrict__ out_hi, uint16_t* __restrict__ out_lo,
@@ -221,7 +223,8 @@ grouped_iq3_exact_kernel(const SegDesc* __restrict__ seg, const int32_t* __restr
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nchunks = n_in / BK;
     const int nblocks = n_in / 256;
-    const int row_tiles = n_out / TILE_M;
+    constexpr int ROWS_ITEM = PAIR ? 2 * TILE_M : TILE_M;
+    const int row_tiles = n_out / ROWS_ITEM;
     const int nseg = min(*nseg_dev, kMaxSeg);
 
     if (tid == 0) {
@@ -271,9 +274,9 @@ grouped_iq3_exact_kernel(const SegDesc* __restrict__ seg, const int32_t* __restr
     const int n_items = nseg > 0 ? tile_prefix[nseg] * row_tiles : 0;
     const int GR = gridDim.x;
     const int my_items = (int)blockIdx.x < n_items ? (n_items - (int)blockIdx.x + GR - 1) / GR : 0;
-    if (tid < min(my_items, kLocalItems)) itab[tid] = decode_item((int)blockIdx.x + tid * GR, row_tiles, nseg, tile_prefix, seg);
+    if (tid < min(my_items, kLocalItems)) itab[tid] = decode_item((int)blockIdx.x + tid * GR, row_tiles, ROWS_ITEM, nseg, tile_prefix, seg);
     __syncthreads();
-    const ItemTab items{itab, seg, tile_prefix, nseg, row_tiles};
+    const ItemTab items{itab, seg, tile_prefix, nseg, row_tiles, ROWS_ITEM};
     bool ok = true;
 
     if (warp < PWARPS) {
@@ -299,8 +302,8 @@ grouped_iq3_exact_kernel(const SegDesc* __restrict__ seg, const int32_t* __restr
                 const int k = kb / nblocks, b = kb - k * nblocks;
                 const Item it = items.get(k);
                 const int mat = rbi >> 7, frow = rbi & 127;
-                const uint8_t* src = mat ? it.wb : it.wa;
-                const size_t off = ((size_t)(it.r0 + frow) * rb + (size_t)98 * b) & ~(size_t)15;
+                const uint8_t* src = (mat && !PAIR) ? it.wb : it.wa;
+                const size_t off = ((size_t)(it.r0 + (PAIR ? mat * TILE_M : 0) + frow) * rb + (size_t)98 * b) & ~(size_t)15;
                 uint8_t* dst = raw + (kb & 1) * RAW_SLOT + (mat * TILE_M + frow) * RAW_PITCH;
                 cp_async16(dst + 16 * f_line, src + off + 16 * f_line);
             }
@@ -310,7 +313,8 @@ grouped_iq3_exact_kernel(const SegDesc* __restrict__ seg, const int32_t* __restr
             if (tid < 16 * NMAT && k < my_items) {
                 const Item it = items.get(k);
                 const uint32_t piece = (uint32_t)(8 * rb);  // a sixteenth of the tile; a multiple of 16 bytes
-                const uint8_t* base = ((tid >> 4) ? it.wb : it.wa) + (size_t)it.r0 * rb + (size_t)(tid & 15) * piece;
+                const uint8_t* base = PAIR ? it.wa + (size_t)it.r0 * rb + (size_t)tid * piece   // 256 contiguous rows
+                                           : ((tid >> 4) ? it.wb : it.wa) + (size_t)it.r0 * rb + (size_t)(tid & 15) * piece;
                 asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base), "r"(piece) : "memory");
             }
         };
@@ -474,7 +478,7 @@ grouped_iq3_exact_kernel(const SegDesc* __restrict__ seg, const int32_t* __restr
             }
             if (!ok) break;
             const int t0 = 16 * hsel;
-            if constexpr (NMAT == 2) {
+            if constexpr (NMAT == 2 && !PAIR) {
                 uint16_t* oh = out_hi + (size_t)(it.prow + t0) * n_out + it.r0 + r;
                 uint16_t* ol = out_lo + (size_t)(it.prow + t0) * n_out + it.r0 + r;
 #pragma unroll
@@ -491,8 +495,10 @@ grouped_iq3_exact_kernel(const SegDesc* __restrict__ seg, const int32_t* __restr
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
                     if (t0 + j < it.m_tile) {
-                        if (row_dst) row_dst[it.prow + t0 + j][it.r0 + r] = acc[0][j];  // expert parallel: the owner's (token, slot) row
-                        else out_f32[(size_t)(it.prow + t0 + j) * n_out + it.r0 + r] = acc[0][j];
+                        float* o = row_dst ? row_dst[it.prow + t0 + j] + it.r0 + r   // expert parallel: the owner's (token, slot) row
+                                           : out_f32 + (size_t)(it.prow + t0 + j) * n_out + it.r0 + r;
+#pragma unroll
+                        for (int mt = 0; mt < NMAT; ++mt) o[mt * TILE_M] = acc[mt][j];
                     }
                 }
             }
@@ -533,7 +539,8 @@ int launch_grouped_exact(dnb_ctx* c, cudaStream_t st, bool fused, const SegDesc*
     const int rb = n_in / 256 * 98;
     const ex::Maps& M = *reinterpret_cast<const ex::Maps*>(maps);
     const dim3 grid(c->sm_count);
-    const int nmat = fused ? 2 : 1;
+    const bool pair = !fused && n_out % (2 * ex::TILE_M) == 0;
+    const int nmat = (fused || pair) ? 2 : 1;
     const size_t smem = (size_t)ex::STAGES * ex::STAGE_BYTES + ex::RAWS * (size_t)nmat * ex::TILE_M * ex::RAW_PITCH +
                         (size_t)ex::SCL * 2 * nmat * ex::TILE_M * 4 + 256 * ex::LUT_REP * 8 +
                         (2 * ex::STAGES + 2 * ex::NB + ex::SCL) * 8 + 16 + (ex::kMaxSeg + 1) * 4 +
@@ -544,6 +551,12 @@ int launch_grouped_exact(dnb_ctx* c, cudaStream_t st, bool fused, const SegDesc*
         ProfScope prof_(c, st, "exact_gate_up");
         ex::grouped_iq3_exact_kernel<2><<<grid, ex::NTHREADS, smem, st>>>(seg, nseg_dev, n_in, n_out, rb, M, out_hi, out_lo, nullptr,
                                                                          c->status, nullptr);
+    } else if (pair) {
+        static SmemGrant grant;
+        DNB_CUDA(grant_smem(grant, c->device, ex::grouped_iq3_exact_kernel<2, true>, smem));
+        ProfScope prof_(c, st, "exact_down");
+        ex::grouped_iq3_exact_kernel<2, true><<<grid, ex::NTHREADS, smem, st>>>(seg, nseg_dev, n_in, n_out, rb, M, nullptr, nullptr,
+                                                                               out_f32, c->status, row_dst);
     } else {
         static SmemGrant grant;
         DNB_CUDA(grant_smem(grant, c->device, ex::grouped_iq3_exact_kernel<1>, smem));
