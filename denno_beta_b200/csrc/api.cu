@@ -31,7 +31,8 @@ static int dev_alloc(T** p, size_t n) {
 
 static void free_ws(Workspace& w) {
     void* dev[] = {w.act_h, w.xn_perm, w.act_perm, w.xn, w.logits, w.wts, w.act, w.hrow, w.sact, w.sh, w.hin, w.out, w.shcoef, w.sels, w.row_token,
-                   w.pos, w.nseg, w.counts, w.one, w.seg_gu, w.seg_dn, w.seg_sh_gu, w.seg_sh_dn, w.xg_hi, w.xg_lo, w.act_hi, w.act_lo};
+                   w.pos, w.nseg, w.counts, w.one, w.seg_gu, w.seg_dn, w.seg_sh_gu, w.seg_sh_dn, w.xg_hi, w.xg_lo, w.act_hi, w.act_lo,
+                   w.x3, w.rpart};
     for (void* p : dev)
         if (p) cudaFree(p);
     if (w.pinned_in) cudaFreeHost(w.pinned_in);
@@ -98,6 +99,7 @@ static int ensure_ws(dnb_ctx* c, int nt) {
     w.maps_ok = (M.e % 64 == 0 && M.ff % 64 == 0) &&
                 umma_make_maps(w.xg_hi, w.xg_lo, rows_pad, (uint64_t)M.e, &w.maps_x) == DNB_OK &&
                 umma_make_maps(w.act_hi, w.act_lo, rows_pad, (uint64_t)M.ff, &w.maps_act) == DNB_OK;
+    if ((rc = router_tc_workspace(c, w, cap, M.ne, M.e))) return rc;
     w.pinned_cap = (size_t)cap * M.e * sizeof(float);
     DNB_CUDA(cudaMallocHost((void**)&w.pinned_in, w.pinned_cap));
     DNB_CUDA(cudaMallocHost((void**)&w.pinned_out, w.pinned_cap));
@@ -404,6 +406,13 @@ static int experts_dev_umma(dnb_ctx* c, int layer, const float* x, int nt, const
                           (shared && L.shared_gate_row) ? w.shcoef : nullptr, out);
 }
 
+// Router logits of nt rows: the tensor-core kernel from kRouterTcMin tokens, the fp32 kernel below.
+static int router_logits(dnb_ctx* c, cudaStream_t st, const float* x, int nt, const Layer& L, float* logits) {
+    const Model& M = c->model;
+    if (router_tc_eligible(c, L, nt)) return launch_router_logits_tc(c, st, x, nt, M.e, L, M.ne, logits);
+    return launch_router_logits(c, st, x, nt, M.e, L.router_w, L.router_bias, M.ne, logits);
+}
+
 static int block_dev(dnb_ctx* c, int layer, const float* h, int nt, float* out) {
     const Model& M = c->model;
     const Layer& L = M.layers[layer];
@@ -425,7 +434,7 @@ static int block_dev(dnb_ctx* c, int layer, const float* h, int nt, float* out) 
             return rc;
     }
     const float* x = L.norm_w ? w.xn : h;
-    if ((rc = launch_router_logits(c, st, x, nt, M.e, L.router_w, L.router_bias, M.ne, w.logits))) return rc;
+    if ((rc = router_logits(c, st, x, nt, L, w.logits))) return rc;
     if ((rc = launch_topk(c, st, w.logits, nt, M.ne, M.k, M.norm_topk, w.sels, w.wts, nullptr))) return rc;
     if (umma_eligible(c, L, nt)) return experts_dev_umma(c, layer, x, nt, w.sels, w.wts, out);
     return experts_dev(c, layer, x, nt, w.sels, w.wts, out);
@@ -485,6 +494,7 @@ static void free_layer(Layer& L) {
     for (auto& t : L.m)
         if (t.dev && t.owned) cudaFree(t.dev);
     if (L.router_w) cudaFree(L.router_w);
+    if (L.router_w3) cudaFree(L.router_w3);
     if (L.router_bias) cudaFree(L.router_bias);
     if (L.norm_w) cudaFree(L.norm_w);
     if (L.shared_gate_row) cudaFree(L.shared_gate_row);
@@ -721,6 +731,14 @@ int dnb_set_tc_min_tokens(dnb_ctx* c, int iq3_xxs_min_tokens) {
     return DNB_OK;
 }
 
+int dnb_set_router_tc(dnb_ctx* c, int on) {
+    if (!c) return DNB_ERR_ARG;
+    DNB_CUDA(cudaDeviceSynchronize());
+    drop_graphs(c);
+    c->router_tc = on != 0;
+    return DNB_OK;
+}
+
 int dnb_set_gemv_impl(dnb_ctx* c, int impl) {
     if (!c || impl < 0 || impl > 5) return DNB_ERR_ARG;
     DNB_CUDA(cudaDeviceSynchronize());
@@ -915,7 +933,7 @@ int dnb_register_router(dnb_ctx* c, int layer, const float* w, const float* bias
     if ((rc = upload_f32(&L.router_bias, bias, (size_t)M.ne))) return rc;
     if ((rc = upload_f32(&L.norm_w, norm_w, (size_t)M.e))) return rc;
     if ((rc = upload_f32(&L.shared_gate_row, shared_gate_row, (size_t)M.e))) return rc;
-    return DNB_OK;
+    return router_tc_prepare(c, L, M.ne, M.e);
 }
 
 // ---- block ----------------------------------------------------------------------------
@@ -1028,7 +1046,7 @@ int dnb_router_topk(dnb_ctx* c, int layer, const float* x, int nt, int32_t* sels
     const size_t bytes = (size_t)nt * M.e * sizeof(float), rows = (size_t)nt * M.k;
     memcpy(w.pinned_in, x, bytes);
     DNB_CUDA(cudaMemcpyAsync(w.hin, w.pinned_in, bytes, cudaMemcpyHostToDevice, c->stream));
-    if ((rc = launch_router_logits(c, c->stream, w.hin, nt, M.e, L.router_w, L.router_bias, M.ne, w.logits))) return rc;
+    if ((rc = router_logits(c, c->stream, w.hin, nt, L, w.logits))) return rc;
     if ((rc = launch_topk(c, c->stream, w.logits, nt, M.ne, M.k, M.norm_topk, w.sels, w.wts, rowsum ? w.shcoef : nullptr)))
         return rc;
     DNB_CUDA(cudaMemcpyAsync(w.pinned_sels, w.sels, rows * 4, cudaMemcpyDeviceToHost, c->stream));
@@ -1259,7 +1277,7 @@ int dnb_router_gemv(dnb_ctx* c, int layer, const float* x, int nt, float* logits
     if ((rc = grow(c->gemv_host, lbytes, true))) return rc;
     memcpy(w.pinned_in, x, bytes);
     DNB_CUDA(cudaMemcpyAsync(w.hin, w.pinned_in, bytes, cudaMemcpyHostToDevice, c->stream));
-    if ((rc = launch_router_logits(c, c->stream, w.hin, nt, M.e, L.router_w, L.router_bias, M.ne, w.logits))) return rc;
+    if ((rc = router_logits(c, c->stream, w.hin, nt, L, w.logits))) return rc;
     DNB_CUDA(cudaMemcpyAsync(c->gemv_host.p, w.logits, lbytes, cudaMemcpyDeviceToHost, c->stream));
     DNB_CUDA(cudaStreamSynchronize(c->stream));
     if ((rc = finish_checked(c, "router_gemv"))) return rc;
@@ -1303,7 +1321,7 @@ int dnb_moe_route_dev(dnb_ctx* c, int layer, const float* h_dev, int nt, float* 
     } else if (x_out_dev != h_dev) {
         DNB_CUDA(cudaMemcpyAsync(x_out_dev, h_dev, (size_t)nt * M.e * 4, cudaMemcpyDeviceToDevice, c->stream));
     }
-    if ((rc = launch_router_logits(c, c->stream, x_out_dev, nt, M.e, L.router_w, L.router_bias, M.ne, c->ws.logits))) return rc;
+    if ((rc = router_logits(c, c->stream, x_out_dev, nt, L, c->ws.logits))) return rc;
     return launch_topk(c, c->stream, c->ws.logits, nt, M.ne, M.k, M.norm_topk, sels_dev, wts_dev, nullptr);
 }
 

@@ -47,9 +47,16 @@ struct ExpertTensor {          // one of gate / up / down of a layer, expert-maj
     bool owned = false;
 };
 
+struct alignas(64) RouterMaps {  // three TMA tensor maps (bf16 hi / mid / lo parts of one fp32 matrix), opaque here
+    unsigned char bytes[3 * 128];
+};
+
 struct Layer {
     ExpertTensor m[6];         // 0 gate 1 up 2 down 3 shared-gate 4 shared-up 5 shared-down
     float* router_w = nullptr;         // [ne][e]
+    uint16_t* router_w3 = nullptr;     // [3][ne][e]: router_w as three bf16 parts (tensor-core router of prefill chunks)
+    RouterMaps rmaps;
+    bool router_tc = false;            // router_w3 and rmaps are valid
     float* router_bias = nullptr;      // [ne] or null
     float* norm_w = nullptr;           // [e] or null
     float* shared_gate_row = nullptr;  // [e] or null
@@ -97,6 +104,11 @@ struct Workspace {             // device buffers of the MoE pipeline, sized for 
     uint16_t *xg_hi = nullptr, *xg_lo = nullptr, *act_hi = nullptr, *act_lo = nullptr;  // bf16 hi/lo packed rows
     UmmaMaps maps_x, maps_act;
     bool maps_ok = false;
+    uint16_t* x3 = nullptr;    // [3][nt_cap + 128][e]: the chunk's rows as three bf16 parts (router_tc.cu)
+    size_t x3_part = 0;        // elements between the parts
+    float* rpart = nullptr;    // [K splits][nt][ne]: partial router sums
+    RouterMaps xmaps;
+    bool router_tc = false;    // x3, rpart and xmaps are valid
     float* pinned_in = nullptr; float* pinned_out = nullptr; size_t pinned_cap = 0;
     int32_t* pinned_sels = nullptr; float* pinned_wts = nullptr;
 };
@@ -157,6 +169,7 @@ struct dnb_ctx {
     unsigned long long* gbar = nullptr; // grid barrier of the fused decode kernel: arrivals of all launches so far
     uint64_t launches = 0;              // kernels launched by this context (bench accounting)
     int gemv_impl = 0;                  // 0 = fast (default), 1 = sequential bit-exact
+    bool router_tc = true;              // router logits of large chunks on the tensor cores (router_tc.cu)
     bool decode_fast = true;            // one-token calls take the bulk-copy GEMV + fused router path
     bool use_pdl = true;                // programmatic dependent launch between the decode kernels
     bool gemv_mma = true;               // one-token IQ3_XXS kernels on mma.sync (gemv_mma.cu, decode_fused.cu) where the shape fits
@@ -330,6 +343,15 @@ int launch_decode_fused(dnb_ctx* c, cudaStream_t st, const SegDesc* seg_gu, cons
 // The whole one-token block, router included, of an all-IQ3_XXS layer in one kernel (decode_fused.cu).
 int launch_decode_block(dnb_ctx* c, cudaStream_t st, const Model& M, const Layer& L, Workspace& w, bool fold_shared,
                         const float* h, const float* residual, float* out, unsigned long long* gbar);
+
+// Router logits of chunks of kRouterTcMin tokens or more on tcgen05 (router_tc.cu)
+constexpr int kRouterTcMin = 128;
+int router_tc_prepare(dnb_ctx* c, Layer& L, int ne, int e);
+int router_tc_workspace(dnb_ctx* c, Workspace& w, int cap, int ne, int e);
+bool router_tc_eligible(const dnb_ctx* c, const Layer& L, int nt);
+int launch_router_logits_tc(dnb_ctx* c, cudaStream_t st, const float* x, int nt, int e, const Layer& L, int ne, float* logits);
+// One tensor map: [rows][cols] bf16 row-major, box = 64 columns x box_rows rows, 128-byte swizzle.  map: 128 bytes.
+int tc_make_map(void* map, void* base, uint64_t rows, uint64_t cols, uint32_t box_rows);
 
 // tcgen05 grouped GEMM of prefill (grouped_umma.cu)
 int umma_make_maps(void* hi, void* lo, uint64_t rows, uint64_t cols, UmmaMaps* out);

@@ -668,6 +668,10 @@ static int make_map(CUtensorMap* m, void* base, uint64_t rows, uint64_t cols, ui
     return DNB_OK;
 }
 
+int tc_make_map(void* map, void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+    return make_map(reinterpret_cast<CUtensorMap*>(map), base, rows, cols, box_rows);
+}
+
 int umma_make_maps(void* hi, void* lo, uint64_t rows, uint64_t cols, UmmaMaps* out) {
     static_assert(sizeof(UmmaMaps) == sizeof(um::Maps), "UmmaMaps must mirror um::Maps");
     um::Maps* m = reinterpret_cast<um::Maps*>(out);

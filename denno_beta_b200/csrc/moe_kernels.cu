@@ -687,50 +687,67 @@ namespace dnb {
 // From sels[nt][k] build the expert-major packed row space the grouped matmuls
 // work in (qwen4exp.rs:18172-18185 by_expert; moe_expert.rs:8309-8390
 // build_grouped_batch; exp_pf.rs:23-31 rows[]): segments by token count descending
-// (ties: expert ascending), the rows of an expert in ascending token order.  A grid
-// of CTAs, 16 experts each; every CTA rebuilds the membership bitmap and the counts
-// in shared memory, so the result does not depend on timing.
+// (ties: expert ascending), the rows of an expert in ascending token order.
 //   row_token[row] = token of the packed row       pos[t*k+slot] = packed row
 //   seg_gu/seg_dn[i] = i-th active expert's matrices, m and first row; *nseg
-constexpr int RTE = 16;  // experts per CTA of the routing-table kernel
+// A grid of CTAs with RTE experts each, one per warp, dealt round-robin (expert = CTA + warp * grid: under a
+// skewed router the hot experts are neighbours and would otherwise share a CTA).  Every CTA counts all
+// experts and keeps, for its own, a bit per token; everything is integer work on the whole of sels, so the
+// result does not depend on timing.  Phase 2: a warp ranks its expert among all (its lanes split the other
+// experts), writes the two segment descriptors, scans the popcounts of its token words and lists the tokens.
+// Phase 3: all threads walk sels again; a pair (token, slot) of one of this CTA's experts gets
+// first row + tokens of the expert below this one.
+constexpr int RTE = 8;  // experts per CTA of the routing-table kernel = warps
 
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(RTE * 32)
 route_tables_kernel(const int32_t* __restrict__ sels, int nt, int k, int ne, const uint8_t* gate, const uint8_t* up,
                     const uint8_t* down, size_t eb_g, size_t eb_u, size_t eb_d, const uint8_t* sg, const uint8_t* su,
                     const uint8_t* sdn, SegDesc* seg_gu, SegDesc* seg_dn, int32_t* row_token, int32_t* pos,
                     int32_t* nseg, int32_t* counts_out) {
-    // Every CTA rebuilds the (small) membership bitmap and the per-expert counts from
-    // sels, then finishes the table entries of its own RTE experts.  Counts are
-    // integer sums, so their value does not depend on the order of the atomic adds.
     extern __shared__ uint32_t sm[];
-    const int words = (ne + 31) >> 5;
-    uint32_t* bitmap = sm;                          // [nt][words]
-    int* counts = (int*)(sm + (size_t)nt * words);  // [ne]
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = blockDim.x >> 5;
-    for (int i = tid; i < nt * words; i += blockDim.x) bitmap[i] = 0;
-    for (int i = tid; i < ne; i += blockDim.x) counts[i] = 0;
+    const int words = (nt + 31) >> 5;
+    uint32_t* bits = sm;                         // [RTE][words]: tokens of this CTA's experts
+    int* before = (int*)(bits + RTE * words);    // [RTE][words]: tokens of the expert in the words below
+    int* counts = before + RTE * words;          // [ne]
+    __shared__ int first_row[RTE];
+    __shared__ int red[RTE];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int G = gridDim.x, me = blockIdx.x;
+    for (int i = tid; i < RTE * words; i += RTE * 32) bits[i] = 0;
+    for (int i = tid; i < ne; i += RTE * 32) counts[i] = 0;
     __syncthreads();
-    for (int i = tid; i < nt * k; i += blockDim.x) {
-        const int e = sels[i];
-        if (e >= 0 && e < ne) {
-            atomicOr(&bitmap[(size_t)(i / k) * words + (e >> 5)], 1u << (e & 31));
-            atomicAdd(&counts[e], 1);
+    constexpr int RTB = 8;  // selections a thread requests before it uses the first (the loop is bound by their latency)
+    for (int i0 = tid; i0 < nt * k; i0 += RTE * 32 * RTB) {
+        int ev[RTB];
+#pragma unroll
+        for (int u = 0; u < RTB; ++u) {
+            const int i = i0 + u * RTE * 32;
+            ev[u] = i < nt * k ? sels[i] : -1;
+        }
+#pragma unroll
+        for (int u = 0; u < RTB; ++u) {
+            const int e = ev[u];
+            if (e >= 0 && e < ne) {
+                atomicAdd(&counts[e], 1);  // integer sums: the value does not depend on the order of the adds
+                if (e % G == me) {
+                    const int t = (i0 + u * RTE * 32) / k;
+                    atomicOr(&bits[(e / G) * words + (t >> 5)], 1u << (t & 31));
+                }
+            }
         }
     }
     __syncthreads();
-    const int e0 = blockIdx.x * RTE;
-    if (blockIdx.x == 0) {
+    if (me == 0) {
         // number of active experts; the shared expert's segment and identity rows
         int part = 0;
-        for (int i = tid; i < ne; i += blockDim.x) part += counts[i] > 0 ? 1 : 0;
-        __shared__ int red[8];
+        for (int i = tid; i < ne; i += RTE * 32) part += counts[i] > 0 ? 1 : 0;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
         if (lane == 0) red[warp] = part;
         __syncthreads();
         if (tid == 0) {
             int n_active = 0;
-            for (int w = 0; w < nwarp; ++w) n_active += red[w];
+            for (int w = 0; w < RTE; ++w) n_active += red[w];
             if (sg) {
                 seg_gu[n_active] = SegDesc{sg, su, (uint32_t)nt, (uint32_t)(nt * k)};
                 seg_dn[n_active] = SegDesc{sdn, nullptr, (uint32_t)nt, (uint32_t)(nt * k)};
@@ -739,18 +756,14 @@ route_tables_kernel(const int32_t* __restrict__ sels, int nt, int k, int ne, con
             *nseg = n_active;
         }
         if (sg)
-            for (int t = tid; t < nt; t += blockDim.x) row_token[nt * k + t] = t;
+            for (int t = tid; t < nt; t += RTE * 32) row_token[nt * k + t] = t;
         if (counts_out)
-            for (int i = tid; i < ne; i += blockDim.x) counts_out[i] = counts[i];
+            for (int i = tid; i < ne; i += RTE * 32) counts_out[i] = counts[i];
     }
-    // Segment order: token count descending, ties by ascending expert index
-    // (moe_expert.rs:8344).  A warp finds the rank and first row of one expert: its
-    // lanes split the other experts and the partial sums meet in an xor tree.
-    for (int ei = warp; ei < RTE; ei += nwarp) {
-        const int e = e0 + ei;
-        if (e >= ne) break;
-        const int c = counts[e];
-        if (c == 0) continue;  // uniform across the warp
+    // Segment order: token count descending, ties by ascending expert index (moe_expert.rs:8344).
+    const int e = me + warp * G;
+    const int c = e < ne ? counts[e] : 0;
+    if (c > 0) {  // uniform across the warp
         int rank = 0, row = 0;
         for (int o = lane; o < ne; o += 32) {
             const int co = counts[o];
@@ -767,27 +780,53 @@ route_tables_kernel(const int32_t* __restrict__ sels, int nt, int k, int ne, con
         if (lane == 0) {
             seg_gu[rank] = SegDesc{gate + (size_t)e * eb_g, up + (size_t)e * eb_u, (uint32_t)c, (uint32_t)row};
             seg_dn[rank] = SegDesc{down + (size_t)e * eb_d, nullptr, (uint32_t)c, (uint32_t)row};
+            first_row[warp] = row;
         }
-        int run = row;
-        for (int t0 = 0; t0 < nt; t0 += 32) {
-            const int t = t0 + lane;
-            const bool has = t < nt && ((bitmap[(size_t)t * words + (e >> 5)] >> (e & 31)) & 1u);
-            const uint32_t b = __ballot_sync(0xffffffffu, has);
-            if (has) {
-                const int prow = run + __popc(b & ((1u << lane) - 1u));
-                row_token[prow] = t;
-                for (int s = 0; s < k; ++s)
-                    if (sels[(size_t)t * k + s] == e) pos[(size_t)t * k + s] = prow;
+        int run = 0;  // tokens of the expert in the words before this round of 32
+        for (int g0 = 0; g0 < words; g0 += 32) {
+            const int g = g0 + lane;
+            uint32_t w = g < words ? bits[warp * words + g] : 0u;
+            const int n = __popc(w);
+            int incl = n;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int o = __shfl_up_sync(0xffffffffu, incl, d);
+                if (lane >= d) incl += o;
             }
-            run += __popc(b);
+            int at = run + incl - n;
+            if (g < words) before[warp * words + g] = at;
+            while (w) {  // ascending tokens
+                const int b = __ffs(w) - 1;
+                w &= w - 1;
+                row_token[row + at++] = g * 32 + b;
+            }
+            run += __shfl_sync(0xffffffffu, incl, 31);
+        }
+    }
+    __syncthreads();
+    for (int i0 = tid; i0 < nt * k; i0 += RTE * 32 * RTB) {
+        int ev[RTB];
+#pragma unroll
+        for (int u = 0; u < RTB; ++u) {
+            const int i = i0 + u * RTE * 32;
+            ev[u] = i < nt * k ? sels[i] : -1;
+        }
+#pragma unroll
+        for (int u = 0; u < RTB; ++u) {
+            const int ex = ev[u], i = i0 + u * RTE * 32;
+            if (ex >= 0 && ex < ne && ex % G == me) {
+                const int j = ex / G, t = i / k;
+                const uint32_t w = bits[j * words + (t >> 5)];
+                pos[i] = first_row[j] + before[j * words + (t >> 5)] + __popc(w & ((1u << (t & 31)) - 1u));
+            }
         }
     }
 }
 
 int launch_route_tables(dnb_ctx* c, cudaStream_t st, const int32_t* sels, int nt, int k, int ne, const Layer& L,
                         Workspace& ws, bool fold_shared) {
-    const int words = (ne + 31) >> 5;
-    const size_t smem = ((size_t)nt * words + (size_t)ne) * 4;
+    const int words = (nt + 31) >> 5;
+    const size_t smem = ((size_t)2 * RTE * words + (size_t)ne) * 4;
     if (smem > 200 * 1024) {
         set_error("route tables: %d tokens x %d experts exceeds one CTA's shared memory", nt, ne);
         return DNB_DECLINED;
@@ -795,7 +834,7 @@ int launch_route_tables(dnb_ctx* c, cudaStream_t st, const int32_t* sels, int nt
     static SmemGrant grant;
     DNB_CUDA(grant_smem(grant, c->device, route_tables_kernel, smem));
     ProfScope prof_(c, st, "route_tables");
-    route_tables_kernel<<<(ne + RTE - 1) / RTE, 256, smem, st>>>(
+    route_tables_kernel<<<(ne + RTE - 1) / RTE, RTE * 32, smem, st>>>(
         sels, nt, k, ne, L.m[0].dev, L.m[1].dev, L.m[2].dev, L.m[0].expert_bytes, L.m[1].expert_bytes,
         L.m[2].expert_bytes, fold_shared ? L.m[3].dev : nullptr, fold_shared ? L.m[4].dev : nullptr,
         fold_shared ? L.m[5].dev : nullptr, ws.seg_gu, ws.seg_dn, ws.row_token, ws.pos, ws.nseg, ws.counts);

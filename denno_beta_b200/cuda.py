@@ -169,6 +169,10 @@ class CudaCtx:
         """IQ3_XXS layers: token count from which a batch takes the exact-weight tcgen05 grouped GEMM."""
         check(self.lib.dnb_set_tc_min_tokens(self.h, iq3_xxs_min_tokens))
 
+    def set_router_tc(self, on):
+        """Router logits of chunks of 128 tokens or more: tcgen05 kernel (default) or the fp32 FMA kernel."""
+        check(self.lib.dnb_set_router_tc(self.h, int(on)))
+
     # -- MoE model ----------------------------------------------------------------
     def moe_config(self, n_layer, n_embd, n_ff, n_expert, n_expert_used, n_shared_ff=0, rms_eps=1e-6,
                    norm_topk_prob=True):

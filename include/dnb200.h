@@ -86,6 +86,7 @@ uint64_t dnb_launch_count(dnb_ctx* ctx);
  *            arrive / a peer's results did not arrive
  *   24       expert-parallel decode: a peer's result rows did not arrive
  *   23       grid barrier of the fused one-token kernel
+ *   25       the tensor-core router GEMM of a prefill chunk (stage or accumulator barrier)
  * What the reference promises for a GPU call that did not complete -- "false: out
  * untouched, the caller recomputes" (cuda.rs:21024-21027, 8785-8788) -- holds here too:
  * every host-buffer entry point reads the word after its stream synchronisation and, when
@@ -154,6 +155,11 @@ int dnb_set_gemv_impl(dnb_ctx* ctx, int impl);
  * 1.7x / 2.1x faster at 64 / 194 tokens; Q4_K layers switch to their tcgen05 kernel at 16 too).  A tuning
  * and A/B knob with no reference counterpart; results stay within the path's tolerance either way. */
 int dnb_set_tc_min_tokens(dnb_ctx* ctx, int iq3_xxs_min_tokens);
+/* Router logits of chunks of 128 tokens or more (cuda.rs:48695 pf_router_dev_topk over kernels_elem.cu:1085
+ * dno_gemm_f32_mt): on = 1 (default) the tcgen05 kernel -- both operands as three bf16 parts, six products,
+ * fp32 accumulation: the accuracy of an fp32 sum -- on = 0 the fp32 FMA kernel that smaller calls use.  The
+ * two differ by summation order only; an A/B knob. */
+int dnb_set_router_tc(dnb_ctx* ctx, int on);
 
 /* ---- MoE model: resident expert table ----------------------------------------
  * Replaces the VRAM/RAM/SSD expert tiers (expert_vram.rs:1-60; use at

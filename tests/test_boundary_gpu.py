@@ -154,6 +154,44 @@ def test_router_gemv_alone(orc, q4k_layer):
     assert np.array_equal(out.view(np.uint32), again.view(np.uint32))
 
 
+@pytest.mark.parametrize("e,ne,nt", [(2048, 512, 512), (2048, 512, 300), (512, 128, 128), (1024, 132, 257)])
+def test_router_logits_on_tensor_cores(orc, e, ne, nt):
+    """cuda.rs:48695 pf_router_dev_topk: the router of a chunk.  From 128 tokens the logits come from the tcgen05
+    kernel (three bf16 parts per operand, six products).  They must be as close to the exact sum as the fp32 FMA
+    kernel's are, the top-k built on them must be the CPU router's, and two runs must agree bit for bit.  Shapes:
+    full tiles, a ragged token tile, the smallest chunk and expert count, and an expert count that is no multiple of 128."""
+    from denno_beta_b200 import cuda as cu
+
+    k = 8
+    c = cu.CudaCtx(0)
+    try:
+        assert c.moe_config(1, e, 256, ne, k)
+        rw = orc.synth_normal(SEED, 8830, 0.02, ne * e).reshape(ne, e)
+        rb = orc.synth_zipf_bias(SEED, 8831, 1.1, ne)
+        c.register_router(0, rw, rb, None, None)
+        x = orc.synth_normal(SEED, 8832, 1.0, nt * e).reshape(nt, e)
+        want = x.astype(np.float64) @ rw.astype(np.float64).T + rb
+        n0 = c.launch_count()
+        tc = c.router_gemv(0, x)
+        assert c.launch_count() - n0 >= 2, "split + tensor-core GEMM (+ reduce)"
+        assert np.array_equal(tc.view(np.uint32), c.router_gemv(0, x).view(np.uint32))
+        c.set_router_tc(False)
+        n0 = c.launch_count()
+        fp = c.router_gemv(0, x)
+        assert c.launch_count() - n0 == 1
+        c.set_router_tc(True)
+        err_tc, err_fp = np.max(np.abs(tc - want)), np.max(np.abs(fp - want))
+        scale = np.max(np.abs(want))
+        print("router logits max|err|: tcgen05 %.3g  fp32 FMA %.3g  (max|logit| %.3g)" % (err_tc, err_fp, scale))
+        assert err_tc <= max(2.0 * err_fp, 4e-7 * scale)
+        sels, wts, _ = c.router_topk(0, x)
+        osel, owts, _ = orc.router(x, rw, rb, k)
+        assert np.array_equal(sels, osel)
+        assert np.max(np.abs(wts - owts)) <= 2e-6
+    finally:
+        c.close()
+
+
 def test_grouped_gemm_entry_point_on_tcgen05(orc, q4k_layer):
     """cuda.rs:7065 moe_grouped_gemm_layer with enough rows for the tensor-core kernel: ragged
     segments (one above 128 tokens, one single row) on the gate matrix (K = n_embd) and the down
