@@ -40,6 +40,7 @@ SIGNATURES = {
     "dnb_set_gemv_impl": (_i, [_vp, _i]),
     "dnb_set_tc_min_tokens": (_i, [_vp, _i]),
     "dnb_set_router_tc": (_i, [_vp, _i]),
+    "dnb_set_q4k_int": (_i, [_vp, _i]),
     "dnb_moe_config": (_i, [_vp, _i, _i, _i, _i, _i, _i, _f, _i]),
     "dnb_register_experts": (_i, [_vp, _i, _i, _i, _i, _i, _i, _vp, _sz]),
     "dnb_register_router": (_i, [_vp, _i, _vp, _vp, _vp, _vp]),

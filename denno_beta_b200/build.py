@@ -14,7 +14,7 @@ ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libdnb200.so")
 OBJ = os.path.join(HERE, "build")
-SOURCES = ["api.cu", "router_tc.cu", "seg_matmul.cu", "gemv_bulk.cu", "gemv_mma.cu", "decode_fused.cu", "grouped_umma.cu", "grouped_exact.cu", "moe_kernels.cu", "synth.cu", "ep_p2p.cu", "ep_decode.cu", "gguf_loader.cu", "hc_mix.cu"]
+SOURCES = ["api.cu", "router_tc.cu", "seg_matmul.cu", "gemv_bulk.cu", "gemv_mma.cu", "decode_fused.cu", "grouped_umma.cu", "grouped_exact.cu", "grouped_q4k_int.cu", "moe_kernels.cu", "synth.cu", "ep_p2p.cu", "ep_decode.cu", "gguf_loader.cu", "hc_mix.cu"]
 NVCC = os.environ.get("DNB_NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

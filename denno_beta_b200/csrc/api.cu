@@ -32,7 +32,7 @@ static int dev_alloc(T** p, size_t n) {
 static void free_ws(Workspace& w) {
     void* dev[] = {w.act_h, w.xn_perm, w.act_perm, w.xn, w.logits, w.wts, w.act, w.hrow, w.sact, w.sh, w.hin, w.out, w.shcoef, w.sels, w.row_token,
                    w.pos, w.nseg, w.counts, w.one, w.seg_gu, w.seg_dn, w.seg_sh_gu, w.seg_sh_dn, w.xg_hi, w.xg_lo, w.act_hi, w.act_lo,
-                   w.x3, w.rpart};
+                   w.x3, w.rpart, w.xq_hi, w.xq_lo, w.aq_hi, w.aq_lo, w.xq_scale, w.aq_scale};
     for (void* p : dev)
         if (p) cudaFree(p);
     if (w.pinned_in) cudaFreeHost(w.pinned_in);
@@ -99,6 +99,21 @@ static int ensure_ws(dnb_ctx* c, int nt) {
     w.maps_ok = (M.e % 64 == 0 && M.ff % 64 == 0) &&
                 umma_make_maps(w.xg_hi, w.xg_lo, rows_pad, (uint64_t)M.e, &w.maps_x) == DNB_OK &&
                 umma_make_maps(w.act_hi, w.act_lo, rows_pad, (uint64_t)M.ff, &w.maps_act) == DNB_OK;
+    if (c->q4k_int && w.maps_ok && q4k_int_handles(M.e, M.ff, true) && q4k_int_handles(M.ff, M.e, false)) {
+        const size_t xp = (size_t)M.e + kQ4kIntXcols, ap = (size_t)M.ff + kQ4kIntXcols;
+        if ((rc = dev_alloc(&w.xq_hi, rows_pad * xp))) return rc;
+        if ((rc = dev_alloc(&w.xq_lo, rows_pad * xp))) return rc;
+        if ((rc = dev_alloc(&w.aq_hi, rows_pad * ap))) return rc;
+        if ((rc = dev_alloc(&w.aq_lo, rows_pad * ap))) return rc;
+        if ((rc = dev_alloc(&w.xq_scale, rows_pad))) return rc;
+        if ((rc = dev_alloc(&w.aq_scale, rows_pad))) return rc;
+        DNB_CUDA(cudaMemset(w.xq_hi, 0, rows_pad * xp * 2));  // the padding columns behind the sub-block sums stay zero
+        DNB_CUDA(cudaMemset(w.xq_lo, 0, rows_pad * xp * 2));
+        DNB_CUDA(cudaMemset(w.aq_hi, 0, rows_pad * ap * 2));
+        DNB_CUDA(cudaMemset(w.aq_lo, 0, rows_pad * ap * 2));
+        w.q4k_int_ok = umma_make_maps(w.xq_hi, w.xq_lo, rows_pad, xp, &w.maps_xq) == DNB_OK &&
+                       umma_make_maps(w.aq_hi, w.aq_lo, rows_pad, ap, &w.maps_aq) == DNB_OK;
+    }
     if ((rc = router_tc_workspace(c, w, cap, M.ne, M.e))) return rc;
     w.pinned_cap = (size_t)cap * M.e * sizeof(float);
     DNB_CUDA(cudaMallocHost((void**)&w.pinned_in, w.pinned_cap));
@@ -391,9 +406,20 @@ static int experts_dev_umma(dnb_ctx* c, int layer, const float* x, int nt, const
     int rc;
     if ((rc = launch_route_tables(c, st, sels, nt, k, ne, L, w, shared))) return rc;
     const int rows = nt * k + (shared ? nt : 0);
-    if ((rc = launch_gather_split(c, st, x, M.e, w.row_token, rows, M.e, w.xg_hi, w.xg_lo))) return rc;
     const int nseg_max = (nt * k < ne ? nt * k : ne) + (shared ? 1 : 0);
     const int ty = L.m[0].type;
+    if (ty == T_Q4_K && c->q4k_int && w.q4k_int_ok) {
+        // integer weights, block scales after the tensor-core sum: fp16 rows in, fp32 activations between the two GEMMs
+        if ((rc = launch_rows_f16(c, st, x, M.e, w.row_token, rows, M.e, w.xq_hi, w.xq_lo, w.xq_scale, "rows_f16_x"))) return rc;
+        if ((rc = launch_grouped_q4k_int(c, st, true, w.seg_gu, w.nseg, nseg_max, M.e, M.ff, &w.maps_xq, w.xq_scale, w.act))) return rc;
+        if ((rc = launch_rows_f16(c, st, w.act, M.ff, nullptr, rows, M.ff, w.aq_hi, w.aq_lo, w.aq_scale, "rows_f16_act"))) return rc;
+        if ((rc = launch_grouped_q4k_int(c, st, false, w.seg_dn, w.nseg, nseg_max, M.ff, M.e, &w.maps_aq, w.aq_scale, w.hrow))) return rc;
+        if (shared && L.shared_gate_row)
+            if ((rc = launch_shared_coef(c, st, x, L.shared_gate_row, nt, M.e, w.shcoef))) return rc;
+        return launch_combine(c, st, w.hrow, w.pos, wts, nt, k, M.e, shared ? w.hrow + (size_t)nt * k * M.e : nullptr,
+                              (shared && L.shared_gate_row) ? w.shcoef : nullptr, out);
+    }
+    if ((rc = launch_gather_split(c, st, x, M.e, w.row_token, rows, M.e, w.xg_hi, w.xg_lo))) return rc;
     if ((rc = launch_grouped_tc(c, st, ty, true, w.seg_gu, w.nseg, nseg_max, M.e, M.ff, &w.maps_x, nt, w.act_hi, w.act_lo,
                                 nullptr)))
         return rc;
@@ -728,6 +754,15 @@ int dnb_set_tc_min_tokens(dnb_ctx* c, int iq3_xxs_min_tokens) {
     DNB_CUDA(cudaDeviceSynchronize());
     drop_graphs(c);
     c->exact_min_nt = iq3_xxs_min_tokens;
+    return DNB_OK;
+}
+
+int dnb_set_q4k_int(dnb_ctx* c, int on) {
+    if (!c) return DNB_ERR_ARG;
+    DNB_CUDA(cudaDeviceSynchronize());
+    drop_graphs(c);
+    if (c->q4k_int != (on != 0)) free_ws(c->ws);  // its operand buffers exist only while it is on: the next call sizes the workspace again
+    c->q4k_int = on != 0;
     return DNB_OK;
 }
 

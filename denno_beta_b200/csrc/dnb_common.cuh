@@ -104,6 +104,11 @@ struct Workspace {             // device buffers of the MoE pipeline, sized for 
     uint16_t *xg_hi = nullptr, *xg_lo = nullptr, *act_hi = nullptr, *act_lo = nullptr;  // bf16 hi/lo packed rows
     UmmaMaps maps_x, maps_act;
     bool maps_ok = false;
+    // integer-weight Q4_K kernel (grouped_q4k_int.cu): fp16 hi / lo rows with the sub-block sums appended, row scales
+    uint16_t *xq_hi = nullptr, *xq_lo = nullptr, *aq_hi = nullptr, *aq_lo = nullptr;
+    float *xq_scale = nullptr, *aq_scale = nullptr;
+    UmmaMaps maps_xq, maps_aq;
+    bool q4k_int_ok = false;
     uint16_t* x3 = nullptr;    // [3][nt_cap + 128][e]: the chunk's rows as three bf16 parts (router_tc.cu)
     size_t x3_part = 0;        // elements between the parts
     float* rpart = nullptr;    // [K splits][nt][ne]: partial router sums
@@ -169,6 +174,7 @@ struct dnb_ctx {
     unsigned long long* gbar = nullptr; // grid barrier of the fused decode kernel: arrivals of all launches so far
     uint64_t launches = 0;              // kernels launched by this context (bench accounting)
     int gemv_impl = 0;                  // 0 = fast (default), 1 = sequential bit-exact
+    bool q4k_int = false;               // Q4_K chunks on the integer-weight tcgen05 kernel (grouped_q4k_int.cu): more exact, measured slower
     bool router_tc = true;              // router logits of large chunks on the tensor cores (router_tc.cu)
     bool decode_fast = true;            // one-token calls take the bulk-copy GEMV + fused router path
     bool use_pdl = true;                // programmatic dependent launch between the decode kernels
@@ -352,6 +358,15 @@ bool router_tc_eligible(const dnb_ctx* c, const Layer& L, int nt);
 int launch_router_logits_tc(dnb_ctx* c, cudaStream_t st, const float* x, int nt, int e, const Layer& L, int ne, float* logits);
 // One tensor map: [rows][cols] bf16 row-major, box = 64 columns x box_rows rows, 128-byte swizzle.  map: 128 bytes.
 int tc_make_map(void* map, void* base, uint64_t rows, uint64_t cols, uint32_t box_rows);
+
+// Q4_K grouped GEMM with integer fp16 weights and block scales after the tensor-core sum (grouped_q4k_int.cu)
+constexpr int kQ4kIntXcols = 64;  // sub-block sum columns appended to an activation row
+bool q4k_int_handles(int n_in, int n_out, bool fused);
+int launch_rows_f16(dnb_ctx* c, cudaStream_t st, const float* x, int ldx, const int32_t* row_token, int rows, int K,
+                    uint16_t* hi, uint16_t* lo, float* rowscale, const char* name);
+int launch_grouped_q4k_int(dnb_ctx* c, cudaStream_t st, bool fused, const SegDesc* seg, const int32_t* nseg_dev, int nseg_max,
+                           int n_in, int n_out, const UmmaMaps* maps, const float* rowscale, float* out_f32,
+                           float* const* row_dst = nullptr);
 
 // tcgen05 grouped GEMM of prefill (grouped_umma.cu)
 int umma_make_maps(void* hi, void* lo, uint64_t rows, uint64_t cols, UmmaMaps* out);

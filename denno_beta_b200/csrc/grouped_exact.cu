@@ -42,9 +42,11 @@
 
 #include "dnb_common.cuh"
 #include "dnb_iq_tables.h"
+#include "tc_ptx.cuh"
 
 namespace dnb {
 namespace ex {
+using namespace tcp;
 
 constexpr int BK = 64;                    // K per stage: one 128-byte swizzle row of bf16 = two sub-blocks
 constexpr int TILE_M = 128;               // weight rows per item
@@ -68,87 +70,22 @@ constexpr int kLocalItems = 32;
 
 __constant__ uint32_t c_grid[256];
 
-__device__ __forceinline__ uint32_t s32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mb_init(uint64_t* b, uint32_t n) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s32(b)), "r"(n) : "memory");
-}
-__device__ __forceinline__ void mb_arrive(uint64_t* b) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(s32(b)) : "memory");
-}
-__device__ __forceinline__ void mb_expect_tx(uint64_t* b, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s32(b)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mb_try(uint64_t* b, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(s32(b)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool mb_wait(uint64_t* b, uint32_t parity, int* status, int code) {
-    for (int i = 0; i < (1 << 21); ++i)
-        if (mb_try(b, parity)) return true;
-    status_set(status, code);
-    return false;
-}
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
-            s32(dst)),
-        "l"(map), "r"(x), "r"(y), "r"(s32(bar))
-        : "memory");
-}
-__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
-    asm volatile("cp.async.cg.shared.global.L2::128B [%0], [%1], 16;" ::"r"(s32(dst)), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void bar_producers() { asm volatile("bar.sync 1, %0;" ::"n"(PWARPS * 32) : "memory"); }
 
-// K-major, 128-byte swizzle shared memory matrix descriptor (sm_100): start address >> 4 in bits
-// [0,14), leading byte offset (unused here, 1) in [16,30), stride byte offset 1024 B between 8-row
-// groups in [32,46), version 1 in [46,48), layout 2 (SWIZZLE_128B) in [61,64).
-constexpr uint32_t kDescHi = (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29);
-__device__ __forceinline__ uint32_t desc_lo(uint32_t smem_addr) { return ((smem_addr >> 4) & 0x3FFFu) | (1u << 16); }
-__device__ __forceinline__ uint64_t desc_of(uint32_t lo) { return ((uint64_t)kDescHi << 32) | lo; }
 // Instruction descriptor, kind::f16: D fp32, A and B bf16, both K-major, N >> 3 in bits 17-22, M >> 4 in 24-28.
 // (One N = 64 product against the hi and lo rows as one B operand reads the weight tile once but doubles the columns the
 // epilogue has to read and add; the kernel is bound by issued instructions, not by shared memory, and it measured the same.)
 constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NT >> 3) << 17) | ((uint32_t)(TILE_M >> 4) << 24);
 
 __device__ __forceinline__ void mma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t acc) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-        "l"(adesc), "l"(bdesc), "r"(kIdesc), "r"(acc)
-        : "memory");
-}
-__device__ __forceinline__ void mma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s32(bar)) : "memory");
+    tcp::mma_bf16(d_tmem, adesc, bdesc, kIdesc, acc);
 }
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* r) {
     uint32_t v[16];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-        : "r"(taddr)
-        : "memory");
+    tcp::tmem_ld16(taddr, v);
 #pragma unroll
     for (int i = 0; i < 16; ++i) r[i] = __uint_as_float(v[i]);
 }
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ bool elect_one() {
-    uint32_t p;
-    asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}" : "=r"(p));
-    return p != 0;
-}
-__device__ __forceinline__ bool warp_all(bool v) { return __all_sync(0xffffffffu, v); }
 __device__ __forceinline__ uint32_t lds_u16(const uint8_t* p) { return *reinterpret_cast<const uint16_t*>(p); }
 
 struct Maps {  // tensor maps of the B operand: box heights 16, 32, 64, 128 for hi and lo (this kernel uses 32)

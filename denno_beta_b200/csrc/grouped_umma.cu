@@ -45,10 +45,12 @@
 
 #include "dnb_common.cuh"
 #include "formats.cuh"
+#include "tc_ptx.cuh"
 
 namespace dnb {
 
 namespace um {
+using namespace tcp;
 
 constexpr int BK = 64;            // K elements per stage (one 128-byte swizzle row of bf16)
 constexpr int TILE_M = 128;       // weight rows per CTA
@@ -60,79 +62,7 @@ constexpr int W_TMA = PWARPS;     // warp that issues the activation tile copies
 constexpr int W_MMA = PWARPS + 1; // warp that issues the MMAs and owns the TMEM allocation
 constexpr int NTHREADS = (PWARPS + 6) * 32;  // + TMA, MMA and four epilogue warps
 
-__device__ __forceinline__ uint32_t s32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mb_init(uint64_t* b, uint32_t n) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s32(b)), "r"(n) : "memory");
-}
-__device__ __forceinline__ void mb_arrive(uint64_t* b) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(s32(b)) : "memory");
-}
-__device__ __forceinline__ void mb_expect_tx(uint64_t* b, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s32(b)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mb_try(uint64_t* b, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(s32(b)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool mb_wait(uint64_t* b, uint32_t parity, int* status, int code) {
-    for (int i = 0; i < (1 << 21); ++i)
-        if (mb_try(b, parity)) return true;
-    status_set(status, code);
-    return false;
-}
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
-            s32(dst)),
-        "l"(map), "r"(x), "r"(y), "r"(s32(bar))
-        : "memory");
-}
-
-// K-major, 128-byte swizzle shared memory matrix descriptor (sm_100 format):
-// start address >> 4 in bits [0,14), leading byte offset (unused for swizzled
-// K-major, set to 1) in [16,30), stride byte offset = 1024 B between 8-row groups in
-// [32,46), version 1 in [46,48), layout type 2 (SWIZZLE_128B) in [61,64).
-// Only the start address varies, and it never carries out of its 14-bit field (shared
-// memory ends below 256 KB), so a descriptor is a constant high word and a low word that
-// advances by plain adds of (byte offset >> 4).
-constexpr uint32_t kDescHi = (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29);
-__device__ __forceinline__ uint32_t desc_lo(uint32_t smem_addr) { return ((smem_addr >> 4) & 0x3FFFu) | (1u << 16); }
-__device__ __forceinline__ uint64_t desc_of(uint32_t lo) { return ((uint64_t)kDescHi << 32) | lo; }
-
-// Instruction descriptor, kind::f16: D fp32 (bits 4-5 = 1), A and B bf16 (bits 7-9,
-// 10-12 = 1), both K-major (bits 15, 16 = 0), N >> 3 in bits 17-22, M >> 4 in 24-28.
-__device__ __forceinline__ uint32_t make_idesc(int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TILE_M >> 4) << 24);
-}
-
-__device__ __forceinline__ void mma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
-        : "memory");
-}
-__device__ __forceinline__ void mma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s32(bar)) : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ uint32_t make_idesc(int n) { return idesc_bf16(TILE_M, n); }
 
 struct Maps {            // tensor maps of the B operand: box heights 16, 32, 64, 128 for hi and lo
     CUtensorMap hi[4];
@@ -188,21 +118,6 @@ __device__ __forceinline__ void dequant_q4k_task(const uint4& hdr, const uint4& 
         *reinterpret_cast<uint4*>(tile_lo + rowoff + col) = make_uint4(lv[0], lv[1], lv[2], lv[3]);
     }
 }
-
-__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s32(dst)), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
-
-// One lane of a converged warp.
-__device__ __forceinline__ bool elect_one() {
-    uint32_t p;
-    asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}" : "=r"(p));
-    return p != 0;
-}
-// A flag the whole warp agrees on (and the compiler knows it does).
-__device__ __forceinline__ bool warp_all(bool v) { return __all_sync(0xffffffffu, v); }
 
 // A work item of the persistent kernel: which segment, which 128 tokens of it, which
 // 128 weight rows.
@@ -304,12 +219,12 @@ __device__ __forceinline__ bool produce(const ProducerArgs& a, int w8, int lane)
         }
         const int off = (f_c >> 2) * 144;
         if ((f_c & 3) == GRP && p == 0) {  // the group's first chunk of a block: fetch the block header too
-            cp_async16(hslot, f_pa + off);
-            if constexpr (NMAT == 2) cp_async16(hslot + 1, f_pb + off);
+            cp_async16<false>(hslot, f_pa + off);
+            if constexpr (NMAT == 2) cp_async16<false>(hslot + 1, f_pb + off);
         }
         const int qoff = off + 16 + 32 * (f_c & 3) + 16 * p;
-        cp_async16(slot, f_pa + qoff);
-        if constexpr (NMAT == 2) cp_async16(slot + 1, f_pb + qoff);
+        cp_async16<false>(slot, f_pa + qoff);
+        if constexpr (NMAT == 2) cp_async16<false>(slot + 1, f_pb + qoff);
         cp_async_commit();
         f_c += 2;
         if (f_c >= a.nchunks) {

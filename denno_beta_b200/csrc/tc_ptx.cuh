@@ -48,8 +48,11 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
         "l"(map), "r"(x), "r"(y), "r"(s32(bar))
         : "memory");
 }
+// 16 bytes global -> shared, bypassing L1.  WHOLE_LINE asks L2 to bring in the 128-byte line the bytes sit in.
+template <bool WHOLE_LINE = true>
 __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
-    asm volatile("cp.async.cg.shared.global.L2::128B [%0], [%1], 16;" ::"r"(s32(dst)), "l"(src) : "memory");
+    if constexpr (WHOLE_LINE) asm volatile("cp.async.cg.shared.global.L2::128B [%0], [%1], 16;" ::"r"(s32(dst)), "l"(src) : "memory");
+    else asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s32(dst)), "l"(src) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
@@ -66,7 +69,7 @@ __device__ __forceinline__ uint64_t desc_of(uint32_t lo) { return ((uint64_t)kDe
 
 // Instruction descriptor, kind::f16: D fp32 (bits 4-5 = 1), A and B bf16 (bits 7-9, 10-12 = 1), both
 // K-major (bits 15, 16 = 0), N >> 3 in bits 17-22, M >> 4 in bits 24-28.
-constexpr uint32_t idesc_bf16(int m, int n) {
+__host__ __device__ constexpr uint32_t idesc_bf16(int m, int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 // D (+)= A * B; acc = 0 overwrites the accumulator.

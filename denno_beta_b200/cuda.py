@@ -169,6 +169,10 @@ class CudaCtx:
         """IQ3_XXS layers: token count from which a batch takes the exact-weight tcgen05 grouped GEMM."""
         check(self.lib.dnb_set_tc_min_tokens(self.h, iq3_xxs_min_tokens))
 
+    def set_q4k_int(self, on):
+        """Q4_K chunks: three-product bf16 tcgen05 kernel (default, on=False) or the integer-weight kernel (more exact, slower)."""
+        check(self.lib.dnb_set_q4k_int(self.h, int(on)))
+
     def set_router_tc(self, on):
         """Router logits of chunks of 128 tokens or more: tcgen05 kernel (default) or the fp32 FMA kernel."""
         check(self.lib.dnb_set_router_tc(self.h, int(on)))

@@ -155,6 +155,12 @@ int dnb_set_gemv_impl(dnb_ctx* ctx, int impl);
  * 1.7x / 2.1x faster at 64 / 194 tokens; Q4_K layers switch to their tcgen05 kernel at 16 too).  A tuning
  * and A/B knob with no reference counterpart; results stay within the path's tolerance either way. */
 int dnb_set_tc_min_tokens(dnb_ctx* ctx, int iq3_xxs_min_tokens);
+/* Q4_K chunks on tcgen05: on = 0 (default) the kernel that folds the scales into bf16 hi / lo weights (three
+ * products per element); on = 1 the kernel with integer fp16 weights (sc * q, exact) and the block scales d,
+ * dmin * m applied after the tensor-core sum, where the shape fits (n_embd, n_ff <= 2048, multiples of 256): a
+ * sixth of the error (1e-5 against 7e-5 of the output RMS) at 1.2x the time of a 512-token chunk.  Both are far
+ * inside the path's tolerance of the CPU reference; an A/B knob with no reference counterpart. */
+int dnb_set_q4k_int(dnb_ctx* ctx, int on);
 /* Router logits of chunks of 128 tokens or more (cuda.rs:48695 pf_router_dev_topk over kernels_elem.cu:1085
  * dno_gemm_f32_mt): on = 1 (default) the tcgen05 kernel -- both operands as three bf16 parts, six products,
  * fp32 accumulation: the accuracy of an fp32 sum -- on = 0 the fp32 FMA kernel that smaller calls use.  The

@@ -63,28 +63,34 @@ def test_batch_equals_token_by_token(orc, small):
     assert np.array_equal(big[:nt].view(np.uint32), c.moe_block(0, h).view(np.uint32))
 
 
-def test_tcgen05_grouped_gemm_matches_fp32_kernels(orc, small):
-    """Q4_K prefill chunks run on the tensor cores with both operands split into two bf16
-    halves (three MMAs per product); the result must stay at fp32-kernel accuracy, far
-    inside the 1e-3 bar, for ragged chunk sizes that exercise every N tile width."""
+@pytest.mark.parametrize("int_weights", [True, False])
+def test_tcgen05_grouped_gemm_matches_fp32_kernels(orc, small, int_weights):
+    """Q4_K prefill chunks on the tensor cores, both kernels: scales folded into bf16 hi / lo weights (three MMAs per
+    product, the default), and integer fp16 weights sc * q with the block scales applied after the sum.
+    The result must stay at fp32-kernel accuracy, far inside the 1e-3 bar, for ragged chunk sizes that
+    exercise every N tile width, one and several token tiles per expert and tiles with one token."""
     c, layers = small
     L = layers[1]
-    for nt in (16, 17, 40, 100, 130, 300):
-        h = orc.synth_normal(SEED, 1300 + nt, 1.0, nt * L.e).reshape(nt, L.e)
-        tc, tsel, tw = c.moe_block(1, h, want_routing=True)
-        c.set_gemv_impl(2)
-        try:
-            fp = c.moe_block(1, h)
-        finally:
-            c.set_gemv_impl(0)
-        print("nt=%d tcgen05 vs fp32 kernels: %.3g" % (nt, rel_err(tc, fp)))
-        assert rel_err(tc, fp) <= 5e-4, "nt=%d: tcgen05 vs fp32 kernels %.3g" % (nt, rel_err(tc, fp))
-        idx = sorted({0, nt // 3, nt - 1})
-        err, _ = check_block(orc, L, h[idx], tc[idx], tsel[idx], tw[idx])
-        assert err <= 5e-4, "nt=%d: %.3g vs oracle" % (nt, err)
-        again = c.moe_block(1, h)
-        assert np.array_equal(tc.view(np.uint32), again.view(np.uint32)), "tcgen05 path not bit-identical run to run"
-    assert c.device_status() == 0
+    c.set_q4k_int(int_weights)
+    try:
+        for nt in (16, 17, 33, 40, 100, 130, 300):
+            h = orc.synth_normal(SEED, 1300 + nt, 1.0, nt * L.e).reshape(nt, L.e)
+            tc, tsel, tw = c.moe_block(1, h, want_routing=True)
+            c.set_gemv_impl(2)
+            try:
+                fp = c.moe_block(1, h)
+            finally:
+                c.set_gemv_impl(0)
+            print("nt=%d tcgen05 (%s) vs fp32 kernels: %.3g" % (nt, "integer" if int_weights else "bf16 x 3", rel_err(tc, fp)))
+            assert rel_err(tc, fp) <= 5e-4, "nt=%d: tcgen05 vs fp32 kernels %.3g" % (nt, rel_err(tc, fp))
+            idx = sorted({0, nt // 3, nt - 1})
+            err, _ = check_block(orc, L, h[idx], tc[idx], tsel[idx], tw[idx])
+            assert err <= 5e-4, "nt=%d: %.3g vs oracle" % (nt, err)
+            again = c.moe_block(1, h)
+            assert np.array_equal(tc.view(np.uint32), again.view(np.uint32)), "tcgen05 path not bit-identical run to run"
+        assert c.device_status() == 0
+    finally:
+        c.set_q4k_int(False)
 
 
 def test_exact_weight_tcgen05_kernel_matches_fp32_kernels(orc, small):
