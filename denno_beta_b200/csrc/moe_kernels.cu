@@ -713,6 +713,11 @@ route_tables_kernel(const int32_t* __restrict__ sels, int nt, int k, int ne, con
     __shared__ int red[RTE];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int G = gridDim.x, me = blockIdx.x;
+    // Divisions by k and by the grid size as multiply-high with ceil(2^32 / d): exact while the dividend times d stays
+    // below 2^32 (pairs: nt * k * k, experts: ne * G), which the launcher checks.  (As plain divisions they were most of
+    // the kernel's instructions.)
+    const uint32_t rk = (uint32_t)((0x100000000ull + (uint32_t)k - 1) / (uint32_t)k);
+    const uint32_t rg = (uint32_t)((0x100000000ull + (uint32_t)G - 1) / (uint32_t)G);
     for (int i = tid; i < RTE * words; i += RTE * 32) bits[i] = 0;
     for (int i = tid; i < ne; i += RTE * 32) counts[i] = 0;
     __syncthreads();
@@ -729,9 +734,10 @@ route_tables_kernel(const int32_t* __restrict__ sels, int nt, int k, int ne, con
             const int e = ev[u];
             if (e >= 0 && e < ne) {
                 atomicAdd(&counts[e], 1);  // integer sums: the value does not depend on the order of the adds
-                if (e % G == me) {
-                    const int t = (i0 + u * RTE * 32) / k;
-                    atomicOr(&bits[(e / G) * words + (t >> 5)], 1u << (t & 31));
+                const int j = (int)__umulhi((uint32_t)e, rg);  // e / G
+                if (e - j * G == me) {
+                    const int t = (int)__umulhi((uint32_t)(i0 + u * RTE * 32), rk);  // pair index / k
+                    atomicOr(&bits[j * words + (t >> 5)], 1u << (t & 31));
                 }
             }
         }
@@ -814,8 +820,9 @@ route_tables_kernel(const int32_t* __restrict__ sels, int nt, int k, int ne, con
 #pragma unroll
         for (int u = 0; u < RTB; ++u) {
             const int ex = ev[u], i = i0 + u * RTE * 32;
-            if (ex >= 0 && ex < ne && ex % G == me) {
-                const int j = ex / G, t = i / k;
+            const int j = (int)__umulhi((uint32_t)max(ex, 0), rg);
+            if (ex >= 0 && ex < ne && ex - j * G == me) {
+                const int t = (int)__umulhi((uint32_t)i, rk);
                 const uint32_t w = bits[j * words + (t >> 5)];
                 pos[i] = first_row[j] + before[j * words + (t >> 5)] + __popc(w & ((1u << (t & 31)) - 1u));
             }
@@ -827,8 +834,8 @@ int launch_route_tables(dnb_ctx* c, cudaStream_t st, const int32_t* sels, int nt
                         Workspace& ws, bool fold_shared) {
     const int words = (nt + 31) >> 5;
     const size_t smem = ((size_t)2 * RTE * words + (size_t)ne) * 4;
-    if (smem > 200 * 1024) {
-        set_error("route tables: %d tokens x %d experts exceeds one CTA's shared memory", nt, ne);
+    if (smem > 200 * 1024 || (uint64_t)nt * k * k >= (1ull << 32) || (uint64_t)ne * ((ne + RTE - 1) / RTE) >= (1ull << 32)) {
+        set_error("route tables: %d tokens x %d experts exceeds the kernel's limits", nt, ne);
         return DNB_DECLINED;
     }
     static SmemGrant grant;
