@@ -716,8 +716,11 @@ route_tables_kernel(const int32_t* __restrict__ sels, int nt, int k, int ne, con
     // Divisions by k and by the grid size as multiply-high with ceil(2^32 / d): exact while the dividend times d stays
     // below 2^32 (pairs: nt * k * k, experts: ne * G), which the launcher checks.  (As plain divisions they were most of
     // the kernel's instructions.)
-    const uint32_t rk = (uint32_t)((0x100000000ull + (uint32_t)k - 1) / (uint32_t)k);
-    const uint32_t rg = (uint32_t)((0x100000000ull + (uint32_t)G - 1) / (uint32_t)G);
+    // A divisor of 1 has no 32-bit reciprocal: div_k / div_g pass the dividend through.
+    const uint32_t rk = k > 1 ? (uint32_t)((0x100000000ull + (uint32_t)k - 1) / (uint32_t)k) : 0u;
+    const uint32_t rg = G > 1 ? (uint32_t)((0x100000000ull + (uint32_t)G - 1) / (uint32_t)G) : 0u;
+    auto div_k = [&](int x) { return k > 1 ? (int)__umulhi((uint32_t)x, rk) : x; };
+    auto div_g = [&](int x) { return G > 1 ? (int)__umulhi((uint32_t)x, rg) : x; };
     for (int i = tid; i < RTE * words; i += RTE * 32) bits[i] = 0;
     for (int i = tid; i < ne; i += RTE * 32) counts[i] = 0;
     __syncthreads();
@@ -734,9 +737,9 @@ route_tables_kernel(const int32_t* __restrict__ sels, int nt, int k, int ne, con
             const int e = ev[u];
             if (e >= 0 && e < ne) {
                 atomicAdd(&counts[e], 1);  // integer sums: the value does not depend on the order of the adds
-                const int j = (int)__umulhi((uint32_t)e, rg);  // e / G
+                const int j = div_g(e);  // e / G
                 if (e - j * G == me) {
-                    const int t = (int)__umulhi((uint32_t)(i0 + u * RTE * 32), rk);  // pair index / k
+                    const int t = div_k(i0 + u * RTE * 32);  // pair index / k
                     atomicOr(&bits[j * words + (t >> 5)], 1u << (t & 31));
                 }
             }
@@ -820,9 +823,9 @@ route_tables_kernel(const int32_t* __restrict__ sels, int nt, int k, int ne, con
 #pragma unroll
         for (int u = 0; u < RTB; ++u) {
             const int ex = ev[u], i = i0 + u * RTE * 32;
-            const int j = (int)__umulhi((uint32_t)max(ex, 0), rg);
+            const int j = div_g(max(ex, 0));
             if (ex >= 0 && ex < ne && ex - j * G == me) {
-                const int t = (int)__umulhi((uint32_t)i, rk);
+                const int t = div_k(i);
                 const uint32_t w = bits[j * words + (t >> 5)];
                 pos[i] = first_row[j] + before[j * words + (t >> 5)] + __popc(w & ((1u << (t & 31)) - 1u));
             }

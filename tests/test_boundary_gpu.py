@@ -218,11 +218,13 @@ def test_grouped_gemm_entry_point_on_tcgen05(orc, q4k_layer):
     assert c.device_status() == 0
 
 
-@pytest.mark.parametrize("shape", [(300, 4, 32, 0.0), (512, 10, 512, 1.1), (194, 10, 512, 1.1), (7, 3, 16, 0.0)])
+@pytest.mark.parametrize("shape", [(300, 4, 32, 0.0), (512, 10, 512, 1.1), (194, 10, 512, 1.1), (7, 3, 16, 0.0), (90, 1, 16, 0.0),
+                                   (33, 1, 8, 0.0), (65, 2, 8, 1.1)])
 def test_routing_tables_equal_build_grouped_batch(orc, shape):
     """moe_expert.rs:8309-8390: segments by token count descending, ties by expert ascending; the
     rows of an expert in ascending token order.  The device-built table (route_tables_kernel) must
-    equal the CPU construction entry for entry."""
+    equal the CPU construction entry for entry.  The shapes include one selection per token (the rows an
+    expert-parallel rank receives) and expert counts that fit one CTA of the kernel."""
     from denno_beta_b200 import cuda as cu
 
     nt, k, ne, zipf = shape
