@@ -351,7 +351,8 @@ int launch_decode_block(dnb_ctx* c, cudaStream_t st, const Model& M, const Layer
                         const float* h, const float* residual, float* out, unsigned long long* gbar);
 
 // Router logits of chunks of kRouterTcMin tokens or more on tcgen05 (router_tc.cu)
-constexpr int kRouterTcMin = 128;
+constexpr int kRouterTcMin = 16;   // the token count from which the tensor-core expert kernels take a call, too: a token's bits then do not
+                                  // depend on the size of its chunk or on how an expert-parallel group split it
 int router_tc_prepare(dnb_ctx* c, Layer& L, int ne, int e);
 int router_tc_workspace(dnb_ctx* c, Workspace& w, int cap, int ne, int e);
 bool router_tc_eligible(const dnb_ctx* c, const Layer& L, int nt);

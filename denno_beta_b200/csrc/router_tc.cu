@@ -1,4 +1,4 @@
-// Router logits of a prefill chunk on the tensor cores:  logits[t][i] = W_r[i] . x_t + bias[i]  for 128 tokens or more.
+// Router logits of a prefill chunk on the tensor cores:  logits[t][i] = W_r[i] . x_t + bias[i]  for calls of 16 tokens or more.
 //
 // Reference forms of this contraction: kernels_elem.cu:1085 (dno_gemm_f32_mt, fp32 FMA) under cuda.rs:48695
 // (pf_router_dev_topk); on the CPU linear_gguf.rs:836-964.  The routing decision is a comparison of these
@@ -10,7 +10,8 @@
 // The small terms have their own accumulator so that they are not rounded at the magnitude of the large one.
 //
 // Shape.  D[128 expert rows][128 tokens] per CTA, K = n_embd split over gridDim.z CTAs (a 512 x 512 output has only 16
-// tiles); the split is a constant of the model, so a token's logits do not depend on the size of its chunk.  The partial
+// tiles); the split is a constant of the model and a column's sum does not depend on what else is in its tile, so a token's
+// logits do not depend on the size of its chunk (nor on how an expert-parallel group divides a chunk among its ranks).  The partial
 // sums go to a scratch array and a second kernel adds them in ascending order and adds the bias: deterministic.
 // W_r is split once at registration; the chunk's rows are split by a pre-pass.  Warp 0 moves tiles by TMA (three A and
 // three B tiles of 16 KB per 64-element K step, two stages), warp 1 issues the MMAs, warps 2-5 read the accumulators.

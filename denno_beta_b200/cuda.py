@@ -174,7 +174,7 @@ class CudaCtx:
         check(self.lib.dnb_set_q4k_int(self.h, int(on)))
 
     def set_router_tc(self, on):
-        """Router logits of chunks of 128 tokens or more: tcgen05 kernel (default) or the fp32 FMA kernel."""
+        """Router logits of calls of 16 tokens or more: tcgen05 kernel (default) or the fp32 FMA kernel."""
         check(self.lib.dnb_set_router_tc(self.h, int(on)))
 
     # -- MoE model ----------------------------------------------------------------

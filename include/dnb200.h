@@ -161,10 +161,11 @@ int dnb_set_tc_min_tokens(dnb_ctx* ctx, int iq3_xxs_min_tokens);
  * sixth of the error (1e-5 against 7e-5 of the output RMS) at 1.2x the time of a 512-token chunk.  Both are far
  * inside the path's tolerance of the CPU reference; an A/B knob with no reference counterpart. */
 int dnb_set_q4k_int(dnb_ctx* ctx, int on);
-/* Router logits of chunks of 128 tokens or more (cuda.rs:48695 pf_router_dev_topk over kernels_elem.cu:1085
+/* Router logits of calls of 16 tokens or more (cuda.rs:48695 pf_router_dev_topk over kernels_elem.cu:1085
  * dno_gemm_f32_mt): on = 1 (default) the tcgen05 kernel -- both operands as three bf16 parts, six products,
  * fp32 accumulation: the accuracy of an fp32 sum -- on = 0 the fp32 FMA kernel that smaller calls use.  The
- * two differ by summation order only; an A/B knob. */
+ * two differ by summation order only; an A/B knob.  (dnb_router_topk_static always runs the fp32 kernel: where
+ * the tcgen05 kernel would take the call its weights agree within rounding, not bit for bit.) */
 int dnb_set_router_tc(dnb_ctx* ctx, int on);
 
 /* ---- MoE model: resident expert table ----------------------------------------

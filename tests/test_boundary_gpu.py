@@ -154,12 +154,13 @@ def test_router_gemv_alone(orc, q4k_layer):
     assert np.array_equal(out.view(np.uint32), again.view(np.uint32))
 
 
-@pytest.mark.parametrize("e,ne,nt", [(2048, 512, 512), (2048, 512, 300), (512, 128, 128), (1024, 132, 257)])
+@pytest.mark.parametrize("e,ne,nt", [(2048, 512, 512), (2048, 512, 300), (512, 128, 128), (1024, 132, 257), (2048, 512, 16), (2048, 512, 40)])
 def test_router_logits_on_tensor_cores(orc, e, ne, nt):
-    """cuda.rs:48695 pf_router_dev_topk: the router of a chunk.  From 128 tokens the logits come from the tcgen05
+    """cuda.rs:48695 pf_router_dev_topk: the router of a chunk.  From 16 tokens the logits come from the tcgen05
     kernel (three bf16 parts per operand, six products).  They must be as close to the exact sum as the fp32 FMA
     kernel's are, the top-k built on them must be the CPU router's, and two runs must agree bit for bit.  Shapes:
-    full tiles, a ragged token tile, the smallest chunk and expert count, and an expert count that is no multiple of 128."""
+    full tiles, ragged token tiles down to the smallest call, the smallest expert count, and an expert count that is no
+    multiple of 128.  A token's logits must not depend on what else is in the call."""
     from denno_beta_b200 import cuda as cu
 
     k = 8
@@ -184,6 +185,9 @@ def test_router_logits_on_tensor_cores(orc, e, ne, nt):
         scale = np.max(np.abs(want))
         print("router logits max|err|: tcgen05 %.3g  fp32 FMA %.3g  (max|logit| %.3g)" % (err_tc, err_fp, scale))
         assert err_tc <= max(2.0 * err_fp, 4e-7 * scale)
+        if nt >= 32:  # the same rows in a smaller call (another tile occupancy): the same bits
+            part = c.router_gemv(0, x[5:5 + 16])
+            assert np.array_equal(part.view(np.uint32), tc[5:5 + 16].view(np.uint32))
         sels, wts, _ = c.router_topk(0, x)
         osel, owts, _ = orc.router(x, rw, rb, k)
         assert np.array_equal(sels, osel)
