@@ -433,7 +433,7 @@ static int experts_dev_umma(dnb_ctx* c, int layer, const float* x, int nt, const
 }
 
 // Router logits of nt rows: the tensor-core kernel from kRouterTcMin tokens, the fp32 kernel below.
-static int router_logits(dnb_ctx* c, cudaStream_t st, const float* x, int nt, const Layer& L, float* logits) {
+int router_logits(dnb_ctx* c, cudaStream_t st, const float* x, int nt, const Layer& L, float* logits) {
     const Model& M = c->model;
     if (router_tc_eligible(c, L, nt)) return launch_router_logits_tc(c, st, x, nt, M.e, L, M.ne, logits);
     return launch_router_logits(c, st, x, nt, M.e, L.router_w, L.router_bias, M.ne, logits);

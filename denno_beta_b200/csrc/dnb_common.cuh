@@ -357,6 +357,8 @@ int router_tc_prepare(dnb_ctx* c, Layer& L, int ne, int e);
 int router_tc_workspace(dnb_ctx* c, Workspace& w, int cap, int ne, int e);
 bool router_tc_eligible(const dnb_ctx* c, const Layer& L, int nt);
 int launch_router_logits_tc(dnb_ctx* c, cudaStream_t st, const float* x, int nt, int e, const Layer& L, int ne, float* logits);
+// The router logits of a call: the tensor-core kernel where it is eligible, else the fp32 kernel (api.cu).
+int router_logits(dnb_ctx* c, cudaStream_t st, const float* x, int nt, const Layer& L, float* logits);
 // One tensor map: [rows][cols] bf16 row-major, box = 64 columns x box_rows rows, 128-byte swizzle.  map: 128 bytes.
 int tc_make_map(void* map, void* base, uint64_t rows, uint64_t cols, uint32_t box_rows);
 
