@@ -439,6 +439,21 @@ int router_logits(dnb_ctx* c, cudaStream_t st, const float* x, int nt, const Lay
     return launch_router_logits(c, st, x, nt, M.e, L.router_w, L.router_bias, M.ne, logits);
 }
 
+int router_topk_dev(dnb_ctx* c, cudaStream_t st, const float* x, int nt, const Layer& L, int32_t* sels, float* wts,
+                    float* rowsum) {
+    const Model& M = c->model;
+    Workspace& w = c->ws;
+    int rc;
+    if (router_tc_eligible(c, L, nt)) {
+        // the top-k kernel adds the K splits' partial sums itself (the reduce kernel's order: the same logits)
+        if ((rc = launch_router_logits_tc(c, st, x, nt, M.e, L, M.ne, w.logits, false))) return rc;
+        const int ns = router_tc_split(M.e);
+        return launch_topk(c, st, ns > 1 ? w.rpart : w.logits, nt, M.ne, M.k, M.norm_topk, sels, wts, rowsum, ns, L.router_bias);
+    }
+    if ((rc = launch_router_logits(c, st, x, nt, M.e, L.router_w, L.router_bias, M.ne, w.logits))) return rc;
+    return launch_topk(c, st, w.logits, nt, M.ne, M.k, M.norm_topk, sels, wts, rowsum);
+}
+
 static int block_dev(dnb_ctx* c, int layer, const float* h, int nt, float* out) {
     const Model& M = c->model;
     const Layer& L = M.layers[layer];
@@ -460,8 +475,7 @@ static int block_dev(dnb_ctx* c, int layer, const float* h, int nt, float* out) 
             return rc;
     }
     const float* x = L.norm_w ? w.xn : h;
-    if ((rc = router_logits(c, st, x, nt, L, w.logits))) return rc;
-    if ((rc = launch_topk(c, st, w.logits, nt, M.ne, M.k, M.norm_topk, w.sels, w.wts, nullptr))) return rc;
+    if ((rc = router_topk_dev(c, st, x, nt, L, w.sels, w.wts, nullptr))) return rc;
     if (umma_eligible(c, L, nt)) return experts_dev_umma(c, layer, x, nt, w.sels, w.wts, out);
     return experts_dev(c, layer, x, nt, w.sels, w.wts, out);
 }
@@ -1081,8 +1095,7 @@ int dnb_router_topk(dnb_ctx* c, int layer, const float* x, int nt, int32_t* sels
     const size_t bytes = (size_t)nt * M.e * sizeof(float), rows = (size_t)nt * M.k;
     memcpy(w.pinned_in, x, bytes);
     DNB_CUDA(cudaMemcpyAsync(w.hin, w.pinned_in, bytes, cudaMemcpyHostToDevice, c->stream));
-    if ((rc = router_logits(c, c->stream, w.hin, nt, L, w.logits))) return rc;
-    if ((rc = launch_topk(c, c->stream, w.logits, nt, M.ne, M.k, M.norm_topk, w.sels, w.wts, rowsum ? w.shcoef : nullptr)))
+    if ((rc = router_topk_dev(c, c->stream, w.hin, nt, L, w.sels, w.wts, rowsum ? w.shcoef : nullptr)))
         return rc;
     DNB_CUDA(cudaMemcpyAsync(w.pinned_sels, w.sels, rows * 4, cudaMemcpyDeviceToHost, c->stream));
     DNB_CUDA(cudaMemcpyAsync(w.pinned_wts, w.wts, rows * 4, cudaMemcpyDeviceToHost, c->stream));
@@ -1356,8 +1369,7 @@ int dnb_moe_route_dev(dnb_ctx* c, int layer, const float* h_dev, int nt, float* 
     } else if (x_out_dev != h_dev) {
         DNB_CUDA(cudaMemcpyAsync(x_out_dev, h_dev, (size_t)nt * M.e * 4, cudaMemcpyDeviceToDevice, c->stream));
     }
-    if ((rc = router_logits(c, c->stream, x_out_dev, nt, L, c->ws.logits))) return rc;
-    return launch_topk(c, c->stream, c->ws.logits, nt, M.ne, M.k, M.norm_topk, sels_dev, wts_dev, nullptr);
+    return router_topk_dev(c, c->stream, x_out_dev, nt, L, sels_dev, wts_dev, nullptr);
 }
 
 int dnb_expert_rows_dev(dnb_ctx* c, int layer, const float* x_rows_dev, const int32_t* local_ids_dev, int rows,

@@ -316,7 +316,7 @@ int launch_seg_gemv_m1(dnb_ctx* c, cudaStream_t st, int type, bool fused, bool x
 int launch_decode_batch_tables(dnb_ctx* c, cudaStream_t st, const int32_t* sels, int nt, int k, const Layer& L,
                                Workspace& ws, bool fold_shared);
 int launch_topk(dnb_ctx* c, cudaStream_t st, const float* logits, int nt, int ne, int k, int norm_topk, int32_t* sels,
-                float* wts, float* rowsum);
+                float* wts, float* rowsum, int nsplit = 1, const float* bias = nullptr);
 // Builds, from sels[nt][k], the expert-major row space: counts, segment
 // descriptors for gate/up and down, row_token[], pos[t][slot] and *nseg.
 // fold_shared: the shared expert becomes one more segment (m = nt) whose packed rows
@@ -351,14 +351,22 @@ int launch_decode_block(dnb_ctx* c, cudaStream_t st, const Model& M, const Layer
                         const float* h, const float* residual, float* out, unsigned long long* gbar);
 
 // Router logits of chunks of kRouterTcMin tokens or more on tcgen05 (router_tc.cu)
+constexpr int kRouterSplitMax = 8;  // K splits of the tensor-core router at most (the top-k kernel adds that many partial sums)
 constexpr int kRouterTcMin = 16;   // the token count from which the tensor-core expert kernels take a call, too: a token's bits then do not
                                   // depend on the size of its chunk or on how an expert-parallel group split it
 int router_tc_prepare(dnb_ctx* c, Layer& L, int ne, int e);
 int router_tc_workspace(dnb_ctx* c, Workspace& w, int cap, int ne, int e);
 bool router_tc_eligible(const dnb_ctx* c, const Layer& L, int nt);
-int launch_router_logits_tc(dnb_ctx* c, cudaStream_t st, const float* x, int nt, int e, const Layer& L, int ne, float* logits);
+// reduce = false leaves the K splits' partial sums in the workspace (rpart, router_tc_split(e) of them) for launch_topk
+// to add; with one split the logits are complete either way.
+int router_tc_split(int e);
+int launch_router_logits_tc(dnb_ctx* c, cudaStream_t st, const float* x, int nt, int e, const Layer& L, int ne, float* logits,
+                            bool reduce = true);
 // The router logits of a call: the tensor-core kernel where it is eligible, else the fp32 kernel (api.cu).
 int router_logits(dnb_ctx* c, cudaStream_t st, const float* x, int nt, const Layer& L, float* logits);
+// Router logits + softmax / top-k / renorm of a call (w.logits and, on the tensor-core path, w.rpart are its scratch).
+int router_topk_dev(dnb_ctx* c, cudaStream_t st, const float* x, int nt, const Layer& L, int32_t* sels, float* wts,
+                    float* rowsum);
 // One tensor map: [rows][cols] bf16 row-major, box = 64 columns x box_rows rows, 128-byte swizzle.  map: 128 bytes.
 int tc_make_map(void* map, void* base, uint64_t rows, uint64_t cols, uint32_t box_rows);
 

@@ -258,8 +258,7 @@ static int epd_block(dnb_ctx* c, EpdState* s, int layer, const float* h, int nt,
         if (L.norm_w)
             if ((rc = launch_rmsnorm(c, st, h, L.norm_w, M.eps, nt, M.e, w.xn))) return rc;
         x = L.norm_w ? w.xn : h;
-        if ((rc = router_logits(c, st, x, nt, L, w.logits))) return rc;
-        if ((rc = launch_topk(c, st, w.logits, nt, M.ne, M.k, M.norm_topk, w.sels, w.wts, nullptr))) return rc;
+        if ((rc = router_topk_dev(c, st, x, nt, L, w.sels, w.wts, nullptr))) return rc;
     }
     if (!done && nt <= kDecodeBatchMax && c->decode_fast && per <= 64) {
         // decode GEMV kernels over one-row segments; pairs of other ranks are empty segments

@@ -193,16 +193,34 @@ struct TopkSmem {
     float spv[32];
 };
 
+// nsplit > 1: logit_row points at the first of nsplit partial sums of the row, split_stride floats apart (the
+// tensor-core router's K splits); they are added in ascending order, then the bias: the sequence of adds of
+// router_reduce_kernel, so the logits are the same bits whether that kernel ran or not.
 __device__ __forceinline__ void topk_block(const float* __restrict__ logit_row, int ne, int k, int norm_topk,
                                            TopkSmem& sm, int32_t* __restrict__ sels_out, float* __restrict__ wts_out,
-                                           float* __restrict__ rowsum_out) {
+                                           float* __restrict__ rowsum_out, int nsplit = 1, size_t split_stride = 0,
+                                           const float* __restrict__ bias = nullptr) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     float p[8];
     float mx = -INFINITY;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
         const int idx = j * 128 + tid;
-        p[j] = idx < ne ? __ldcg(logit_row + idx) : -INFINITY;  // L2: other CTAs of this launch may have written them
+        float v = -INFINITY;
+        if (idx < ne) {
+            v = __ldcg(logit_row + idx);  // L2: other CTAs of this launch may have written them
+            if (nsplit > 1) {
+                float part[kRouterSplitMax];  // all requested before the first is used
+#pragma unroll
+                for (int s = 1; s < kRouterSplitMax; ++s)
+                    part[s] = s < nsplit ? __ldcg(logit_row + (size_t)s * split_stride + idx) : 0.f;
+#pragma unroll
+                for (int s = 1; s < kRouterSplitMax; ++s)
+                    if (s < nsplit) v = __fadd_rn(v, part[s]);
+                if (bias) v = __fadd_rn(v, bias[idx]);
+            }
+        }
+        p[j] = v;
         mx = fmaxf(mx, p[j]);
     }
 #pragma unroll
@@ -430,21 +448,23 @@ __device__ __forceinline__ void topk_block(const float* __restrict__ logit_row, 
 
 __global__ void __launch_bounds__(128)
 topk_kernel(const float* __restrict__ logits, int nt, int ne, int k, int norm_topk, int32_t* __restrict__ sels,
-            float* __restrict__ wts, float* __restrict__ rowsum) {
+            float* __restrict__ wts, float* __restrict__ rowsum, int nsplit, const float* __restrict__ bias) {
     __shared__ TopkSmem sm;
     const int t = blockIdx.x;
     topk_block(logits + (size_t)t * ne, ne, k, norm_topk, sm, sels + (size_t)t * k, wts + (size_t)t * k,
-               rowsum ? rowsum + t : nullptr);
+               rowsum ? rowsum + t : nullptr, nsplit, (size_t)nt * ne, bias);
 }
 
+// nsplit > 1: `logits` is [nsplit][nt][ne] partial sums (router_tc.cu), added here with `bias`.
 int launch_topk(dnb_ctx* c, cudaStream_t st, const float* logits, int nt, int ne, int k, int norm_topk, int32_t* sels,
-                float* wts, float* rowsum) {
-    if (ne > 1024 || k > 32 || k < 1 || k > ne) {
-        set_error("topk: n_expert %d / k %d outside the kernel's range (<=1024, <=32)", ne, k);
+                float* wts, float* rowsum, int nsplit, const float* bias) {
+    if (ne > 1024 || k > 32 || k < 1 || k > ne || nsplit < 1 || nsplit > kRouterSplitMax) {
+        set_error("topk: n_expert %d / k %d / %d partial sums outside the kernel's range (<=1024, <=32, <=%d)", ne, k, nsplit,
+                  kRouterSplitMax);
         return DNB_DECLINED;
     }
     ProfScope prof_(c, st, "router_topk");
-    topk_kernel<<<nt, 128, 0, st>>>(logits, nt, ne, k, norm_topk, sels, wts, rowsum);
+    topk_kernel<<<nt, 128, 0, st>>>(logits, nt, ne, k, norm_topk, sels, wts, rowsum, nsplit, nsplit > 1 ? bias : nullptr);
     c->launches++;
     DNB_CUDA(cudaGetLastError());
     return DNB_OK;
@@ -675,7 +695,7 @@ extern "C" int dnb_router_topk_static(dnb_ctx* c, int layer, const float* x_dev,
     // previous call's contents need no clearing
     // (no per-kernel profiling scope here: it creates events on first use, which may allocate)
     router_logits_kernel<<<grid, RROWS * 32, smem, c->stream>>>(x_dev, nt, M.e, L.router_w, L.router_bias, M.ne, logits);
-    topk_kernel<<<nt, 128, 0, c->stream>>>(logits, nt, M.ne, M.k, M.norm_topk, sels_dev, wts_dev, rowsum_dev);
+    topk_kernel<<<nt, 128, 0, c->stream>>>(logits, nt, M.ne, M.k, M.norm_topk, sels_dev, wts_dev, rowsum_dev, 1, nullptr);
     c->launches += 2;
     DNB_CUDA(cudaGetLastError());
     return DNB_OK;

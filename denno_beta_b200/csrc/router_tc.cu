@@ -12,7 +12,8 @@
 // Shape.  D[128 expert rows][128 tokens] per CTA, K = n_embd split over gridDim.z CTAs (a 512 x 512 output has only 16
 // tiles); the split is a constant of the model and a column's sum does not depend on what else is in its tile, so a token's
 // logits do not depend on the size of its chunk (nor on how an expert-parallel group divides a chunk among its ranks).  The partial
-// sums go to a scratch array and a second kernel adds them in ascending order and adds the bias: deterministic.
+// sums go to a scratch array; the top-k kernel (or router_reduce_kernel, where the logits themselves are wanted) adds them
+// in ascending order and then the bias: deterministic, and the same bits either way.
 // W_r is split once at registration; the chunk's rows are split by a pre-pass.  Warp 0 moves tiles by TMA (three A and
 // three B tiles of 16 KB per 64-element K step, two stages), warp 1 issues the MMAs, warps 2-5 read the accumulators.
 // Every wait is bounded; a wait that gives up sets *status and the CTA falls through to the teardown.
@@ -200,9 +201,9 @@ router_reduce_kernel(const float4* __restrict__ part, int nsplit, size_t n4, int
 
 static_assert(sizeof(RouterMaps) == 3 * sizeof(CUtensorMap), "RouterMaps must hold three tensor maps");
 
-int router_tc_split(int e) {  // K splits: the largest divisor of the K steps that is at most 8
+int router_tc_split(int e) {  // K splits: the largest divisor of the K steps that is at most kRouterSplitMax
     const int nchunks = e / rt::BK;
-    for (int s = 8; s > 1; --s)
+    for (int s = kRouterSplitMax; s > 1; --s)
         if (nchunks % s == 0) return s;
     return 1;
 }
@@ -256,7 +257,8 @@ bool router_tc_eligible(const dnb_ctx* c, const Layer& L, int nt) {
     return c->router_tc && L.router_tc && c->ws.router_tc && nt >= kRouterTcMin && nt <= c->ws.nt_cap;
 }
 
-int launch_router_logits_tc(dnb_ctx* c, cudaStream_t st, const float* x, int nt, int e, const Layer& L, int ne, float* logits) {
+int launch_router_logits_tc(dnb_ctx* c, cudaStream_t st, const float* x, int nt, int e, const Layer& L, int ne, float* logits,
+                            bool reduce) {
     Workspace& w = c->ws;
     int rc = launch_split3(c, st, x, (size_t)nt * e, w.x3, w.x3_part, "router_split_x");
     if (rc) return rc;
@@ -275,7 +277,7 @@ int launch_router_logits_tc(dnb_ctx* c, cudaStream_t st, const float* x, int nt,
         c->launches++;
         DNB_CUDA(cudaGetLastError());
     }
-    if (nsplit > 1) {
+    if (nsplit > 1 && reduce) {
         ProfScope prof_(c, st, "router_reduce");
         const size_t n4 = (size_t)nt * ne / 4;
         rt::router_reduce_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(
