@@ -440,13 +440,13 @@ int router_logits(dnb_ctx* c, cudaStream_t st, const float* x, int nt, const Lay
 }
 
 int router_topk_dev(dnb_ctx* c, cudaStream_t st, const float* x, int nt, const Layer& L, int32_t* sels, float* wts,
-                    float* rowsum) {
+                    float* rowsum, bool x_is_split) {
     const Model& M = c->model;
     Workspace& w = c->ws;
     int rc;
     if (router_tc_eligible(c, L, nt)) {
         // the top-k kernel adds the K splits' partial sums itself (the reduce kernel's order: the same logits)
-        if ((rc = launch_router_logits_tc(c, st, x, nt, M.e, L, M.ne, w.logits, false))) return rc;
+        if ((rc = launch_router_logits_tc(c, st, x, nt, M.e, L, M.ne, w.logits, false, x_is_split))) return rc;
         const int ns = router_tc_split(M.e);
         return launch_topk(c, st, ns > 1 ? w.rpart : w.logits, nt, M.ne, M.k, M.norm_topk, sels, wts, rowsum, ns, L.router_bias);
     }
@@ -469,13 +469,16 @@ static int block_dev(dnb_ctx* c, int layer, const float* h, int nt, float* out) 
         if (rc != DNB_DECLINED) return rc;
     }
     const bool shared = L.has_shared();
+    // the RMSNorm kernel writes the router's operand (three bf16 parts of the normalised rows) in the same pass
+    const bool split_in_prep = L.norm_w && router_tc_eligible(c, L, nt);
     if (L.norm_w || shared) {
         if ((rc = launch_prep(c, st, h, L.norm_w, M.eps, nt, M.e, w.xn, shared ? w.seg_sh_gu : nullptr,
-                              shared ? w.seg_sh_dn : nullptr, L.m[3].dev, L.m[4].dev, L.m[5].dev)))
+                              shared ? w.seg_sh_dn : nullptr, L.m[3].dev, L.m[4].dev, L.m[5].dev,
+                              split_in_prep ? w.x3 : nullptr, w.x3_part)))
             return rc;
     }
     const float* x = L.norm_w ? w.xn : h;
-    if ((rc = router_topk_dev(c, st, x, nt, L, w.sels, w.wts, nullptr))) return rc;
+    if ((rc = router_topk_dev(c, st, x, nt, L, w.sels, w.wts, nullptr, split_in_prep))) return rc;
     if (umma_eligible(c, L, nt)) return experts_dev_umma(c, layer, x, nt, w.sels, w.wts, out);
     return experts_dev(c, layer, x, nt, w.sels, w.wts, out);
 }

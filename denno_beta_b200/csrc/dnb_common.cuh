@@ -273,8 +273,10 @@ int launch_gemv_seq(dnb_ctx* c, cudaStream_t st, int type, const uint8_t* w, con
 int launch_rmsnorm(dnb_ctx* c, cudaStream_t st, const float* h, const float* w, float eps, int nt, int e, float* out);
 // RMSNorm (skipped when w is null) that also publishes the shared expert's two
 // one-segment descriptors for this call.
+// x3 (optional, needs w): the normalised rows also as three bf16 parts, x3_part elements apart (the tensor-core router's operand).
 int launch_prep(dnb_ctx* c, cudaStream_t st, const float* h, const float* w, float eps, int nt, int e, float* out,
-                SegDesc* sh_gu, SegDesc* sh_dn, const uint8_t* sg, const uint8_t* su, const uint8_t* sdn);
+                SegDesc* sh_gu, SegDesc* sh_dn, const uint8_t* sg, const uint8_t* su, const uint8_t* sdn,
+                uint16_t* x3 = nullptr, size_t x3_part = 0);
 int launch_add_inplace(dnb_ctx* c, cudaStream_t st, float* h, const float* d, size_t n);
 int launch_stage_in(dnb_ctx* c, cudaStream_t st, const float* host_pinned, float* dst, size_t n);  // DNB_DECLINED: use a copy
 int launch_stall(dnb_ctx* c, cudaStream_t st, float ms);
@@ -360,13 +362,14 @@ bool router_tc_eligible(const dnb_ctx* c, const Layer& L, int nt);
 // reduce = false leaves the K splits' partial sums in the workspace (rpart, router_tc_split(e) of them) for launch_topk
 // to add; with one split the logits are complete either way.
 int router_tc_split(int e);
+// x_is_split: the chunk's rows are already in the workspace as three bf16 parts (written by launch_prep).
 int launch_router_logits_tc(dnb_ctx* c, cudaStream_t st, const float* x, int nt, int e, const Layer& L, int ne, float* logits,
-                            bool reduce = true);
+                            bool reduce = true, bool x_is_split = false);
 // The router logits of a call: the tensor-core kernel where it is eligible, else the fp32 kernel (api.cu).
 int router_logits(dnb_ctx* c, cudaStream_t st, const float* x, int nt, const Layer& L, float* logits);
 // Router logits + softmax / top-k / renorm of a call (w.logits and, on the tensor-core path, w.rpart are its scratch).
 int router_topk_dev(dnb_ctx* c, cudaStream_t st, const float* x, int nt, const Layer& L, int32_t* sels, float* wts,
-                    float* rowsum);
+                    float* rowsum, bool x_is_split = false);
 // One tensor map: [rows][cols] bf16 row-major, box = 64 columns x box_rows rows, 128-byte swizzle.  map: 128 bytes.
 int tc_make_map(void* map, void* base, uint64_t rows, uint64_t cols, uint32_t box_rows);
 

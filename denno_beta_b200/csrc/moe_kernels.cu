@@ -3,6 +3,7 @@
 // shared-expert gate coefficient.
 #include "dnb_common.cuh"
 #include "formats.cuh"
+#include "tc_ptx.cuh"
 
 namespace dnb {
 
@@ -26,7 +27,8 @@ __device__ __forceinline__ float rms_inv_128(const float* __restrict__ xr, int e
 
 __global__ void __launch_bounds__(128)
 prep_kernel(const float* __restrict__ h, const float* __restrict__ w, float eps, int e, float* __restrict__ out,
-            SegDesc* sh_gu, SegDesc* sh_dn, const uint8_t* sg, const uint8_t* su, const uint8_t* sdn, uint32_t nt) {
+            SegDesc* sh_gu, SegDesc* sh_dn, const uint8_t* sg, const uint8_t* su, const uint8_t* sdn, uint32_t nt,
+            uint16_t* __restrict__ x3, size_t x3_part) {
     if (blockIdx.x == 0 && threadIdx.x == 0 && sh_gu) {
         sh_gu[0] = SegDesc{sg, su, nt, 0u};
         sh_dn[0] = SegDesc{sdn, nullptr, nt, 0u};
@@ -36,21 +38,35 @@ prep_kernel(const float* __restrict__ h, const float* __restrict__ w, float eps,
     const float* xr = h + (size_t)blockIdx.x * e;
     const float inv = rms_inv_128(xr, e, eps, red);
     float* o = out + (size_t)blockIdx.x * e;
-    for (int i = threadIdx.x; i < e; i += 128) o[i] = __fmul_rn(__fmul_rn(xr[i], inv), w[i]);
+    if (!x3) {
+        for (int i = threadIdx.x; i < e; i += 128) o[i] = __fmul_rn(__fmul_rn(xr[i], inv), w[i]);
+        return;
+    }
+    uint16_t* p3 = x3 + (size_t)blockIdx.x * e;  // the row again as three bf16 parts for the tensor-core router
+    for (int i = threadIdx.x; i < e; i += 128) {
+        const float v = __fmul_rn(__fmul_rn(xr[i], inv), w[i]);
+        o[i] = v;
+        uint16_t a, b, c;
+        tcp::split3_bf16(v, a, b, c);
+        p3[i] = a;
+        p3[x3_part + i] = b;
+        p3[2 * x3_part + i] = c;
+    }
 }
 
 int launch_rmsnorm(dnb_ctx* c, cudaStream_t st, const float* h, const float* w, float eps, int nt, int e, float* out) {
     ProfScope prof_(c, st, "rmsnorm");
-    prep_kernel<<<nt, 128, 0, st>>>(h, w, eps, e, out, nullptr, nullptr, nullptr, nullptr, nullptr, 0u);
+    prep_kernel<<<nt, 128, 0, st>>>(h, w, eps, e, out, nullptr, nullptr, nullptr, nullptr, nullptr, 0u, nullptr, 0);
     c->launches++;
     DNB_CUDA(cudaGetLastError());
     return DNB_OK;
 }
 
 int launch_prep(dnb_ctx* c, cudaStream_t st, const float* h, const float* w, float eps, int nt, int e, float* out,
-                SegDesc* sh_gu, SegDesc* sh_dn, const uint8_t* sg, const uint8_t* su, const uint8_t* sdn) {
+                SegDesc* sh_gu, SegDesc* sh_dn, const uint8_t* sg, const uint8_t* su, const uint8_t* sdn, uint16_t* x3,
+                size_t x3_part) {
     ProfScope prof_(c, st, "prep_rmsnorm");
-    prep_kernel<<<nt, 128, 0, st>>>(h, w, eps, e, out, sh_gu, sh_dn, sg, su, sdn, (uint32_t)nt);
+    prep_kernel<<<nt, 128, 0, st>>>(h, w, eps, e, out, sh_gu, sh_dn, sg, su, sdn, (uint32_t)nt, w ? x3 : nullptr, x3_part);
     c->launches++;
     DNB_CUDA(cudaGetLastError());
     return DNB_OK;

@@ -41,16 +41,6 @@ struct Maps {
     CUtensorMap x[3];
 };
 
-__device__ __forceinline__ void split3(float v, uint16_t& h, uint16_t& m, uint16_t& l) {
-    const __nv_bfloat16 bh = __float2bfloat16_rn(v);
-    const float r1 = v - __bfloat162float(bh);   // exact
-    const __nv_bfloat16 bm = __float2bfloat16_rn(r1);
-    const float r2 = r1 - __bfloat162float(bm);  // exact
-    h = __bfloat16_as_ushort(bh);
-    m = __bfloat16_as_ushort(bm);
-    l = __bfloat16_as_ushort(__float2bfloat16_rn(r2));
-}
-
 // n4 float4 groups of x -> three bf16 arrays of the same shape, `part` elements apart.
 __global__ void __launch_bounds__(256)
 split3_kernel(const float4* __restrict__ x, size_t n4, uint16_t* __restrict__ out, size_t part) {
@@ -58,10 +48,10 @@ split3_kernel(const float4* __restrict__ x, size_t n4, uint16_t* __restrict__ ou
     if (i >= n4) return;
     const float4 v = x[i];
     uint16_t h[4], m[4], l[4];
-    split3(v.x, h[0], m[0], l[0]);
-    split3(v.y, h[1], m[1], l[1]);
-    split3(v.z, h[2], m[2], l[2]);
-    split3(v.w, h[3], m[3], l[3]);
+    split3_bf16(v.x, h[0], m[0], l[0]);
+    split3_bf16(v.y, h[1], m[1], l[1]);
+    split3_bf16(v.z, h[2], m[2], l[2]);
+    split3_bf16(v.w, h[3], m[3], l[3]);
     uint2* o = reinterpret_cast<uint2*>(out) + i;
     const size_t p2 = part / 4;
     o[0] = make_uint2(h[0] | ((uint32_t)h[1] << 16), h[2] | ((uint32_t)h[3] << 16));
@@ -258,10 +248,12 @@ bool router_tc_eligible(const dnb_ctx* c, const Layer& L, int nt) {
 }
 
 int launch_router_logits_tc(dnb_ctx* c, cudaStream_t st, const float* x, int nt, int e, const Layer& L, int ne, float* logits,
-                            bool reduce) {
+                            bool reduce, bool x_is_split) {
     Workspace& w = c->ws;
-    int rc = launch_split3(c, st, x, (size_t)nt * e, w.x3, w.x3_part, "router_split_x");
-    if (rc) return rc;
+    if (!x_is_split) {  // else the kernel that produced x wrote its three parts into w.x3 as well
+        int rc = launch_split3(c, st, x, (size_t)nt * e, w.x3, w.x3_part, "router_split_x");
+        if (rc) return rc;
+    }
     const int nsplit = router_tc_split(e);
     rt::Maps maps;
     memcpy(maps.w, &L.rmaps, sizeof(maps.w));

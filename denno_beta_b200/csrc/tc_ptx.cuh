@@ -2,6 +2,7 @@
 // cp.async, shared-memory matrix descriptors, tcgen05.mma / commit / ld.
 #pragma once
 #include <cuda.h>
+#include <cuda_bf16.h>
 #include <stdint.h>
 
 #include "dnb_common.cuh"
@@ -109,6 +110,18 @@ __device__ __forceinline__ bool elect_one() {
     return p != 0;
 }
 __device__ __forceinline__ bool warp_all(bool v) { return __all_sync(0xffffffffu, v); }
+
+// An fp32 value as three bf16 numbers whose sum is the value: hi = the value rounded to bf16, mid = the remainder
+// rounded, lo = what is left (3 x 8 mantissa bits carry the 24 of an fp32).
+__device__ __forceinline__ void split3_bf16(float v, uint16_t& h, uint16_t& m, uint16_t& l) {
+    const __nv_bfloat16 bh = __float2bfloat16_rn(v);
+    const float r1 = v - __bfloat162float(bh);   // exact
+    const __nv_bfloat16 bm = __float2bfloat16_rn(r1);
+    const float r2 = r1 - __bfloat162float(bm);  // exact
+    h = __bfloat16_as_ushort(bh);
+    m = __bfloat16_as_ushort(bm);
+    l = __bfloat16_as_ushort(__float2bfloat16_rn(r2));
+}
 
 }  // namespace tcp
 }  // namespace dnb

@@ -53,7 +53,7 @@ def test_config2_every_token(orc, ty_name, seam):
         h = orc.synth_normal(SEED, 3000, 1.0, nt * E).reshape(nt, E)
         n0 = c.launch_count()
         out, sels, wts = c.moe_block(0, h, want_routing=True)
-        assert c.launch_count() - n0 == 9, "prep, router (split, tcgen05 GEMM), top-k (adds the K splits), tables, gather, 2 x tcgen05, combine"
+        assert c.launch_count() - n0 == 8, "prep (RMSNorm + the router operand), router GEMM on tcgen05, top-k (adds the K splits), tables, gather, 2 x tcgen05, combine"
         c.set_gemv_impl(2)
         try:
             fp, fsels, fwts = c.moe_block(0, h, want_routing=True)
