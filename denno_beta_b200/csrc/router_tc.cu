@@ -14,7 +14,8 @@
 // logits do not depend on the size of its chunk (nor on how an expert-parallel group divides a chunk among its ranks).  The partial
 // sums go to a scratch array; the top-k kernel (or router_reduce_kernel, where the logits themselves are wanted) adds them
 // in ascending order and then the bias: deterministic, and the same bits either way.
-// W_r is split once at registration; the chunk's rows are split by a pre-pass.  Warp 0 moves tiles by TMA (three A and
+// W_r is split once at registration; the chunk's rows are split by the RMSNorm kernel as it writes them (prep_kernel,
+// moe_kernels.cu) or, for rows that come from elsewhere, by split3_kernel.  Warp 0 moves tiles by TMA (three A and
 // three B tiles of 16 KB per 64-element K step, two stages), warp 1 issues the MMAs, warps 2-5 read the accumulators.
 // Every wait is bounded; a wait that gives up sets *status and the CTA falls through to the teardown.
 #include <cuda.h>
